@@ -1,0 +1,673 @@
+/*
+ * CPU oracle for the RNS-CKKS evaluation hot path.  TEST INFRASTRUCTURE ONLY.
+ *
+ * This file is a plain-C restatement of the arithmetic that the Cerium runtime
+ * performs on the GPU (forward / inverse negacyclic NTT, fast base conversion,
+ * subtract-and-divide, Galois automorphism, hybrid key switching, rescale).  It
+ * exists so that the CUDA kernels can be checked bit-for-bit against an
+ * independent implementation.  Nothing in the shipped library links, imports or
+ * calls it; only the test-suite, the smoke check and the CPU-baseline leg of
+ * the benchmark do.
+ *
+ * Conventions: every residue array holds canonical values in [0, q) stored as
+ * uint64_t regardless of the limb width the GPU uses (32 or 64 bit), because
+ * the reference's lazy 32-bit residues are only defined modulo q
+ * (cerium/compiler/backend/kernels/fhe_arith.cuh:28-50 returns values in
+ * [q, 2q) for some inputs).  Parity is therefore "equal after reduction mod q".
+ *
+ * Each function cites the reference file:line whose behaviour it restates.
+ * The third-party dependency behind the reference's host math is Microsoft
+ * SEAL 4.1.1 (docker/scripts/install_seal.sh:4); its sources are not part of
+ * the reference tree, so the algorithms are restated from their published
+ * definitions (Harvey lazy butterflies, minimal primitive 2N-th root,
+ * bit-reversed twiddle order) and from the reference's own call sites.
+ *
+ * Parity status: pinned for the 32-bit path against the reference's own CUDA
+ * device headers (see ref_cuda_harness.cu, run on a GPU, and the fixtures in
+ * tests/golden/); for 64-bit parameter sets the reference cannot run at all, so
+ * 64-bit parity is pinned against big-integer arithmetic (tests) only:
+ * "parity unpinned" with respect to SEAL itself.
+ */
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+typedef unsigned __int128 u128;
+typedef uint64_t u64;
+
+#define ORC_API __attribute__((visibility("default")))
+
+/* ------------------------------------------------------------------------ */
+/* scalar modular arithmetic                                                 */
+/* ------------------------------------------------------------------------ */
+
+ORC_API u64 orc_mulmod(u64 a, u64 b, u64 q) { return (u64)(((u128)a * b) % q); }
+
+ORC_API u64 orc_powmod(u64 a, u64 e, u64 q) {
+  u64 r = 1 % q;
+  a %= q;
+  while (e) {
+    if (e & 1) r = orc_mulmod(r, a, q);
+    a = orc_mulmod(a, a, q);
+    e >>= 1;
+  }
+  return r;
+}
+
+/* q is prime in every use, so Fermat inversion is enough. */
+ORC_API u64 orc_invmod(u64 a, u64 q) { return orc_powmod(a % q, q - 2, q); }
+
+static inline u64 addmod(u64 a, u64 b, u64 q) {
+  u64 s = a + b;
+  return s >= q ? s - q : s;
+}
+static inline u64 submod(u64 a, u64 b, u64 q) { return a >= b ? a - b : q - (b - a); }
+
+ORC_API int orc_is_prime(u64 n) {
+  static const u64 bases[] = {2, 3, 5, 7, 11, 13, 17, 19, 23, 29, 31, 37};
+  if (n < 2) return 0;
+  for (size_t i = 0; i < sizeof(bases) / sizeof(bases[0]); i++) {
+    if (n % bases[i] == 0) return n == bases[i];
+  }
+  u64 d = n - 1;
+  int s = 0;
+  while (!(d & 1)) { d >>= 1; s++; }
+  for (size_t i = 0; i < sizeof(bases) / sizeof(bases[0]); i++) {
+    u64 x = orc_powmod(bases[i], d, n);
+    if (x == 1 || x == n - 1) continue;
+    int comp = 1;
+    for (int r = 1; r < s; r++) {
+      x = orc_mulmod(x, x, n);
+      if (x == n - 1) { comp = 0; break; }
+    }
+    if (comp) return 0;
+  }
+  return 1;
+}
+
+static inline uint32_t brev(uint32_t x, int bits) {
+  uint32_t r = 0;
+  for (int i = 0; i < bits; i++) { r = (r << 1) | (x & 1); x >>= 1; }
+  return r;
+}
+
+/*
+ * Minimal primitive 2N-th root of unity modulo q.
+ * Restates the contract of seal::util::try_minimal_primitive_root as used at
+ * cerium/runtime/math/ntt.cpp:105 and cerium/runtime/execution/evaluator.cpp:140:
+ * among all primitive 2N-th roots (the odd powers of any one of them) take the
+ * numerically smallest.  Returns 0 if q != 1 mod 2N.
+ */
+ORC_API u64 orc_min_primitive_root(u64 q, int logn) {
+  u64 two_n = (u64)2 << logn;
+  if ((q - 1) % two_n) return 0;
+  u64 e = (q - 1) / two_n, r = 0;
+  for (u64 g = 2; g < q; g++) {
+    r = orc_powmod(g, e, q);
+    if (orc_powmod(r, two_n >> 1, q) == q - 1) break; /* r^N = -1: order 2N */
+    r = 0;
+  }
+  if (!r) return 0;
+  u64 sq = orc_mulmod(r, r, q), cur = r, best = r;
+  for (u64 i = 0; i < (two_n >> 1); i++) {
+    if (cur < best) best = cur;
+    cur = orc_mulmod(cur, sq, q);
+  }
+  return best;
+}
+
+/* ------------------------------------------------------------------------ */
+/* context: one NTT table set per prime                                      */
+/* ------------------------------------------------------------------------ */
+
+typedef struct {
+  u64 q, psi, psi_inv, n_inv, n_inv_shoup;
+  u64 *w, *w_shoup;   /* w[brev(i)] = psi^i            (ntt.cpp:118-125) */
+  u64 *wi, *wi_shoup; /* wi[brev(i)] = psi^-i: inverse of w at the same index */
+} orc_prime;
+
+typedef struct {
+  int logn;
+  size_t n;
+  int n_primes;
+  orc_prime *p;
+} orc_ctx;
+
+static inline u64 shoup_of(u64 w, u64 q) { return (u64)(((u128)w << 64) / q); }
+
+/* x*w mod q in [0, 2q) for any x < 2^64 (Harvey / Shoup lazy product). */
+static inline u64 mul_shoup_lazy(u64 x, u64 w, u64 ws, u64 q) {
+  u64 h = (u64)(((u128)x * ws) >> 64);
+  return x * w - h * q;
+}
+
+ORC_API orc_ctx *orc_ctx_create(int logn, const u64 *moduli, int n_primes) {
+  orc_ctx *c = (orc_ctx *)calloc(1, sizeof(orc_ctx));
+  c->logn = logn;
+  c->n = (size_t)1 << logn;
+  c->n_primes = n_primes;
+  c->p = (orc_prime *)calloc((size_t)n_primes, sizeof(orc_prime));
+  int ok = 1;
+#pragma omp parallel for schedule(dynamic)
+  for (int k = 0; k < n_primes; k++) {
+    orc_prime *P = &c->p[k];
+    u64 q = moduli[k];
+    P->q = q;
+    P->psi = orc_min_primitive_root(q, logn);
+    if (!P->psi || q >= ((u64)1 << 62)) { ok = 0; continue; }
+    P->psi_inv = orc_invmod(P->psi, q);
+    P->n_inv = orc_invmod((u64)c->n % q, q);
+    P->n_inv_shoup = shoup_of(P->n_inv, q);
+    size_t n = c->n;
+    P->w = (u64 *)malloc(4 * n * sizeof(u64));
+    P->w_shoup = P->w + n;
+    P->wi = P->w + 2 * n;
+    P->wi_shoup = P->w + 3 * n;
+    u64 pw = 1, pwi = 1;
+    for (size_t i = 0; i < n; i++) {
+      uint32_t r = brev((uint32_t)i, logn);
+      P->w[r] = pw;
+      P->w_shoup[r] = shoup_of(pw, q);
+      P->wi[r] = pwi;
+      P->wi_shoup[r] = shoup_of(pwi, q);
+      pw = orc_mulmod(pw, P->psi, q);
+      pwi = orc_mulmod(pwi, P->psi_inv, q);
+    }
+  }
+  if (!ok) {
+    for (int k = 0; k < n_primes; k++) free(c->p[k].w);
+    free(c->p);
+    free(c);
+    return NULL;
+  }
+  return c;
+}
+
+ORC_API void orc_ctx_destroy(orc_ctx *c) {
+  if (!c) return;
+  for (int k = 0; k < c->n_primes; k++) free(c->p[k].w);
+  free(c->p);
+  free(c);
+}
+
+ORC_API u64 orc_ctx_modulus(const orc_ctx *c, int k) { return c->p[k].q; }
+ORC_API u64 orc_ctx_root(const orc_ctx *c, int k) { return c->p[k].psi; }
+/* twiddle at table position i (bit-reversed order), for table-level tests */
+ORC_API u64 orc_ctx_twiddle(const orc_ctx *c, int k, size_t i) { return c->p[k].w[i]; }
+
+/* ------------------------------------------------------------------------ */
+/* NTT                                                                       */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * Forward negacyclic NTT, standard order in, bit-reversed order out, canonical
+ * output.  Restates ntt_negacyclic_harvey (cerium/runtime/math/ntt.cpp:173-198:
+ * lazy transform_to_rev with root_powers in bit-reversed order followed by the
+ * correction from [0,4q) to [0,q)) and the GPU butterflies of
+ * cerium/compiler/backend/kernels/fhe_ntt.cuh:76-88.
+ */
+ORC_API void orc_ntt_forward(const orc_ctx *c, int k, u64 *x) {
+  const orc_prime *P = &c->p[k];
+  const u64 q = P->q, two_q = 2 * q;
+  size_t n = c->n, t = n;
+  for (size_t m = 1; m < n; m <<= 1) {
+    t >>= 1;
+    for (size_t i = 0; i < m; i++) {
+      const u64 w = P->w[m + i], ws = P->w_shoup[m + i];
+      u64 *a = x + 2 * i * t, *b = a + t;
+      for (size_t j = 0; j < t; j++) {
+        u64 u = a[j];
+        u = u >= two_q ? u - two_q : u;
+        u64 v = mul_shoup_lazy(b[j], w, ws, q);
+        a[j] = u + v;
+        b[j] = u + two_q - v;
+      }
+    }
+  }
+  for (size_t i = 0; i < n; i++) {
+    u64 v = x[i];
+    v = v >= two_q ? v - two_q : v;
+    x[i] = v >= q ? v - q : v;
+  }
+}
+
+/*
+ * Inverse negacyclic NTT, bit-reversed in, standard order out, scaled by 1/N,
+ * canonical output.  Restates inverse_ntt_negacyclic_harvey
+ * (cerium/runtime/math/ntt.cpp:229-250) and the GPU path
+ * (fhe_ntt.cuh:380-392,470-601), which folds 1/2 into every layer; the value
+ * is the same x with NTT(x) = input.
+ */
+ORC_API void orc_ntt_inverse(const orc_ctx *c, int k, u64 *x) {
+  const orc_prime *P = &c->p[k];
+  const u64 q = P->q, two_q = 2 * q;
+  size_t n = c->n, t = 1;
+  for (size_t m = n >> 1; m >= 1; m >>= 1) {
+    for (size_t i = 0; i < m; i++) {
+      const u64 w = P->wi[m + i], ws = P->wi_shoup[m + i];
+      u64 *a = x + 2 * i * t, *b = a + t;
+      for (size_t j = 0; j < t; j++) {
+        u64 u = a[j], v = b[j];
+        u64 s = u + v;
+        a[j] = s >= two_q ? s - two_q : s;
+        b[j] = mul_shoup_lazy(u + two_q - v, w, ws, q);
+      }
+    }
+    t <<= 1;
+  }
+  for (size_t i = 0; i < n; i++) {
+    u64 v = mul_shoup_lazy(x[i], P->n_inv, P->n_inv_shoup, q);
+    x[i] = v >= q ? v - q : v;
+  }
+}
+
+/* Batched forms: `count` limbs of N words, limb i uses prime prime_idx[i]. */
+ORC_API void orc_ntt_forward_batch(const orc_ctx *c, u64 *x, const uint32_t *prime_idx, int count) {
+#pragma omp parallel for schedule(dynamic)
+  for (int i = 0; i < count; i++) orc_ntt_forward(c, (int)prime_idx[i], x + (size_t)i * c->n);
+}
+ORC_API void orc_ntt_inverse_batch(const orc_ctx *c, u64 *x, const uint32_t *prime_idx, int count) {
+#pragma omp parallel for schedule(dynamic)
+  for (int i = 0; i < count; i++) orc_ntt_inverse(c, (int)prime_idx[i], x + (size_t)i * c->n);
+}
+
+/* Schoolbook negacyclic product mod q (O(N^2)); cross-check for small N. */
+ORC_API void orc_negacyclic_mul_schoolbook(u64 q, size_t n, const u64 *a, const u64 *b, u64 *out) {
+  for (size_t i = 0; i < n; i++) out[i] = 0;
+  for (size_t i = 0; i < n; i++)
+    for (size_t j = 0; j < n; j++) {
+      u64 p = orc_mulmod(a[i], b[j], q);
+      size_t k = i + j;
+      if (k < n) out[k] = addmod(out[k], p, q);
+      else out[k - n] = submod(out[k - n], p, q);
+    }
+}
+
+/* ------------------------------------------------------------------------ */
+/* element-wise operations (generated generic kernels,                       */
+/* cerium/compiler/backend/cuda_kernel.cc:64-399)                            */
+/* ------------------------------------------------------------------------ */
+
+ORC_API void orc_ew_add(u64 q, size_t n, const u64 *a, const u64 *b, u64 *o) {
+  for (size_t i = 0; i < n; i++) o[i] = addmod(a[i], b[i], q);
+}
+ORC_API void orc_ew_sub(u64 q, size_t n, const u64 *a, const u64 *b, u64 *o) {
+  for (size_t i = 0; i < n; i++) o[i] = submod(a[i], b[i], q);
+}
+ORC_API void orc_ew_neg(u64 q, size_t n, const u64 *a, u64 *o) {
+  for (size_t i = 0; i < n; i++) o[i] = a[i] ? q - a[i] : 0;
+}
+ORC_API void orc_ew_mul(u64 q, size_t n, const u64 *a, const u64 *b, u64 *o) {
+  for (size_t i = 0; i < n; i++) o[i] = orc_mulmod(a[i], b[i], q);
+}
+/* o = a*b + c */
+ORC_API void orc_ew_mad(u64 q, size_t n, const u64 *a, const u64 *b, const u64 *c, u64 *o) {
+  for (size_t i = 0; i < n; i++) o[i] = addmod(orc_mulmod(a[i], b[i], q), c[i], q);
+}
+/* o = a + b*s   (PMU kernel, cuda_kernel.cc:2669-2765) */
+ORC_API void orc_ew_pmu(u64 q, size_t n, const u64 *a, const u64 *b, u64 s, u64 *o) {
+  for (size_t i = 0; i < n; i++) o[i] = addmod(a[i], orc_mulmod(b[i], s, q), q);
+}
+
+/* ------------------------------------------------------------------------ */
+/* Galois automorphism                                                       */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * Galois element for a rotation step (cerium/runtime/math/galois.cpp:79-113):
+ * step 0 -> 2N-1 (conjugation); step>0 -> 5^step mod 2N;
+ * step<0 -> 5^(N/2-|step|) mod 2N.
+ */
+ORC_API uint32_t orc_galois_elt_from_step(int step, int logn) {
+  u64 n = (u64)1 << logn, m = 2 * n;
+  if (step == 0) return (uint32_t)(m - 1);
+  u64 s = step < 0 ? (n >> 1) - (u64)(-step) : (u64)step;
+  u64 e = 1;
+  while (s--) e = (e * 5) & (m - 1);
+  return (uint32_t)e;
+}
+
+/*
+ * NTT-domain permutation table (galois.cpp:30-62):
+ * table[i] = brev_logn( ((elt * brev_{logn+1}(i+N)) >> 1) & (N-1) ),
+ * result[i] = operand[table[i]]  (galois.h:63-64).
+ */
+ORC_API void orc_galois_table_ntt(uint32_t elt, int logn, uint32_t *table) {
+  uint32_t n = (uint32_t)1 << logn;
+  for (uint32_t i = 0; i < n; i++) {
+    uint32_t r = brev(i + n, logn + 1);
+    u64 raw = (((u64)elt * r) >> 1) & (n - 1);
+    table[i] = brev((uint32_t)raw, logn);
+  }
+}
+
+ORC_API void orc_apply_galois_ntt(uint32_t elt, int logn, const u64 *in, u64 *out) {
+  size_t n = (size_t)1 << logn;
+  uint32_t *t = (uint32_t *)malloc(n * sizeof(uint32_t));
+  orc_galois_table_ntt(elt, logn, t);
+  for (size_t i = 0; i < n; i++) out[i] = in[t[i]];
+  free(t);
+}
+
+/* Coefficient-domain definition x -> x^elt in Z_q[x]/(x^N+1); cross-check. */
+ORC_API void orc_apply_galois_coeff(uint32_t elt, int logn, u64 q, const u64 *in, u64 *out) {
+  size_t n = (size_t)1 << logn;
+  for (size_t i = 0; i < n; i++) {
+    u64 idx = ((u64)i * elt) & (2 * n - 1);
+    if (idx < n) out[idx] = in[i];
+    else out[idx - n] = in[i] ? q - in[i] : 0;
+  }
+}
+
+/* ------------------------------------------------------------------------ */
+/* fast base conversion                                                      */
+/* ------------------------------------------------------------------------ */
+
+#define ORC_BCONV_LAZY 0  /* Cerium: factors fold [Qhat_i^-1]_{q_i}, no inner reduction */
+#define ORC_BCONV_EXACT 1 /* textbook / SEAL-style: y_i = x_i*[Qhat_i^-1] mod q_i first    */
+
+/*
+ * in:  [I][n] residues mod in_mod[i];  out: [O][n] residues mod out_mod[j].
+ * Lazy mode restates DeviceBaseConverter::set_output_bases
+ * (cerium/runtime/execution/evaluator.cpp:1539-1578:
+ *   F[j][i] = ([Qhat_i^-1]_{q_i} mod p_j) * (Qhat_i mod p_j) mod p_j)
+ * and convert<I,O> (cerium/compiler/backend/kernels/fhe_bconv.cuh:123-150:
+ *   out_j = sum_i x_i * F[j][i]  mod p_j, with x_i NOT reduced by q_i first).
+ * Exact mode computes y_i = x_i * [Qhat_i^-1]_{q_i} mod q_i and then
+ * out_j = sum_i y_i * (Qhat_i mod p_j) mod p_j.
+ */
+ORC_API void orc_bconv(int mode, size_t n, int I, const u64 *in_mod, const u64 *in, int O,
+                       const u64 *out_mod, u64 *out) {
+  u64 *inv = (u64 *)malloc((size_t)I * sizeof(u64));           /* [Qhat_i^-1]_{q_i} */
+  u64 *qhat = (u64 *)malloc((size_t)I * (size_t)O * sizeof(u64)); /* Qhat_i mod p_j  */
+  for (int i = 0; i < I; i++) {
+    u64 prod = 1;
+    for (int k = 0; k < I; k++)
+      if (k != i) prod = orc_mulmod(prod, in_mod[k] % in_mod[i], in_mod[i]);
+    inv[i] = orc_invmod(prod, in_mod[i]);
+    for (int j = 0; j < O; j++) {
+      u64 pj = out_mod[j], pr = 1 % pj;
+      for (int k = 0; k < I; k++)
+        if (k != i) pr = orc_mulmod(pr, in_mod[k] % pj, pj);
+      qhat[(size_t)j * I + i] = pr;
+    }
+  }
+#pragma omp parallel for schedule(static)
+  for (int j = 0; j < O; j++) {
+    u64 pj = out_mod[j];
+    for (size_t c = 0; c < n; c++) {
+      u64 acc = 0;
+      for (int i = 0; i < I; i++) {
+        u64 x = in[(size_t)i * n + c], f;
+        if (mode == ORC_BCONV_LAZY) {
+          f = orc_mulmod(inv[i] % pj, qhat[(size_t)j * I + i], pj);
+          acc = addmod(acc, orc_mulmod(x % pj, f, pj), pj);
+        } else {
+          u64 y = orc_mulmod(x, inv[i], in_mod[i]);
+          acc = addmod(acc, orc_mulmod(y % pj, qhat[(size_t)j * I + i], pj), pj);
+        }
+      }
+      out[(size_t)j * n + c] = acc;
+    }
+  }
+  free(inv);
+  free(qhat);
+}
+
+/* ------------------------------------------------------------------------ */
+/* SuD: subtract-and-divide fused with the forward NTT                       */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * out = (in1 - NTT_k(in2)) * factor mod q_k.
+ * Restates ntt1_sud (cerium/compiler/backend/kernels/fhe_ntt.cuh:278-359) and
+ * the factor of compute_sud_factors (cerium/runtime/execution/function.cpp:
+ * 708-729): factor = [(prod of divide bases)^-1]_{q_k}.  in2 is in coefficient
+ * form with residues already taken mod q_k by the caller.
+ */
+ORC_API void orc_sud(const orc_ctx *c, int k, const u64 *in1, const u64 *in2_coeff, u64 factor,
+                     u64 *out) {
+  size_t n = c->n;
+  u64 q = c->p[k].q;
+  u64 *t = (u64 *)malloc(n * sizeof(u64));
+  for (size_t i = 0; i < n; i++) t[i] = in2_coeff[i] % q;
+  orc_ntt_forward(c, k, t);
+  for (size_t i = 0; i < n; i++) out[i] = orc_mulmod(submod(in1[i], t[i], q), factor, q);
+  free(t);
+}
+
+/* ------------------------------------------------------------------------ */
+/* hybrid key switching, ModDown, rescale                                    */
+/* ------------------------------------------------------------------------ */
+
+#define ORC_ROUND_FLOOR 0 /* Cerium: no rounding term (fhe_ntt.cuh:346-358)            */
+#define ORC_ROUND_HALF 1  /* add floor(P/2) before the division (SEAL-style rounding)  */
+
+static u64 prod_mod(const orc_ctx *c, const uint32_t *idx, int cnt, u64 q) {
+  u64 p = 1 % q;
+  for (int i = 0; i < cnt; i++) p = orc_mulmod(p, c->p[idx[i]].q % q, q);
+  return p;
+}
+
+/* floor(P/2) mod q where P = prod of c->p[idx[i]].q; computed on a small bignum. */
+static u64 half_prod_mod(const orc_ctx *c, const uint32_t *idx, int cnt, u64 q) {
+  /* P is odd, so floor(P/2) = (P-1)/2 = (P-1) * 2^-1 mod q for odd q. */
+  u64 p = prod_mod(c, idx, cnt, q);
+  u64 pm1 = submod(p, 1 % q, q);
+  return orc_mulmod(pm1, orc_invmod(2, q), q);
+}
+
+/*
+ * ModDown: given t over Q u P in NTT form (tq: [L][n] on q_idx, tp: [K][n] on
+ * p_idx) return out[L][n] = (tq - NTT(BConv_{P->Q}(iNTT(tp)))) * P^-1 mod q_i.
+ * Restates steps 8-10 of the key switch
+ * (cerium/compiler/backend/compiler_keyswitch.cc:382-417: INTT on the
+ * extension limbs, BCONV Ext->Par, SUD).
+ */
+ORC_API void orc_moddown(const orc_ctx *c, int bconv_mode, int round_mode, int L,
+                         const uint32_t *q_idx, int K, const uint32_t *p_idx, const u64 *tq,
+                         const u64 *tp, u64 *out) {
+  size_t n = c->n;
+  u64 *pc = (u64 *)malloc((size_t)K * n * sizeof(u64));
+  u64 *conv = (u64 *)malloc((size_t)L * n * sizeof(u64));
+  u64 *pm = (u64 *)malloc((size_t)K * sizeof(u64));
+  u64 *qm = (u64 *)malloc((size_t)L * sizeof(u64));
+  memcpy(pc, tp, (size_t)K * n * sizeof(u64));
+  orc_ntt_inverse_batch(c, pc, p_idx, K);
+  for (int k = 0; k < K; k++) pm[k] = c->p[p_idx[k]].q;
+  for (int i = 0; i < L; i++) qm[i] = c->p[q_idx[i]].q;
+  if (round_mode == ORC_ROUND_HALF) {
+    for (int k = 0; k < K; k++) {
+      u64 h = half_prod_mod(c, p_idx, K, pm[k]);
+      for (size_t j = 0; j < n; j++) pc[(size_t)k * n + j] = addmod(pc[(size_t)k * n + j], h, pm[k]);
+    }
+  }
+  orc_bconv(bconv_mode, n, K, pm, pc, L, qm, conv);
+#pragma omp parallel for schedule(dynamic)
+  for (int i = 0; i < L; i++) {
+    u64 q = qm[i];
+    u64 *cv = conv + (size_t)i * n;
+    if (round_mode == ORC_ROUND_HALF) {
+      u64 h = half_prod_mod(c, p_idx, K, q);
+      for (size_t j = 0; j < n; j++) cv[j] = submod(cv[j], h, q);
+    }
+    u64 f = orc_invmod(prod_mod(c, p_idx, K, q), q);
+    orc_sud(c, (int)q_idx[i], tq + (size_t)i * n, cv, f, out + (size_t)i * n);
+  }
+  free(pc); free(conv); free(pm); free(qm);
+}
+
+/*
+ * Hybrid key switch of one polynomial.
+ *   cpoly : [L][n], NTT form, limb i over prime q_idx[i]
+ *   evk   : [dnum][2][L+K][n]; limb order inside a key polynomial is
+ *           q_idx[0..L-1] then p_idx[0..K-1]
+ *   digit of limb i = i % dnum (stride split,
+ *           cerium/compiler/backend/compiler_keyswitch.cc:68-99)
+ *   out0,out1 : [L][n] = ModDown( sum_d ModUp(c restricted to digit d) * evk_d )
+ * Restates keyswitch_ciphertext_impl
+ * (cerium/compiler/backend/compiler_keyswitch.cc:253-432) without the P*c0
+ * pre-addition (PMU), which the caller performs as an ordinary modular add
+ * after ModDown: (t + P*c0 - b)/P = (t - b)/P + c0 exactly mod q.
+ * The digit's own limbs are copied from the NTT-form input instead of being
+ * converted (kernel_instruction.h:823-838).
+ */
+ORC_API void orc_keyswitch(const orc_ctx *c, int bconv_mode, int round_mode, int L,
+                           const uint32_t *q_idx, int K, const uint32_t *p_idx, int dnum,
+                           const u64 *cpoly, const u64 *evk, u64 *out0, u64 *out1) {
+  size_t n = c->n;
+  int LK = L + K;
+  uint32_t *all_idx = (uint32_t *)malloc((size_t)LK * sizeof(uint32_t));
+  for (int i = 0; i < L; i++) all_idx[i] = q_idx[i];
+  for (int k = 0; k < K; k++) all_idx[L + k] = p_idx[k];
+  u64 *coef = (u64 *)malloc((size_t)L * n * sizeof(u64));
+  memcpy(coef, cpoly, (size_t)L * n * sizeof(u64));
+  orc_ntt_inverse_batch(c, coef, q_idx, L);
+  u64 *acc0 = (u64 *)calloc((size_t)LK * n, sizeof(u64));
+  u64 *acc1 = (u64 *)calloc((size_t)LK * n, sizeof(u64));
+  u64 *raised = (u64 *)malloc((size_t)LK * n * sizeof(u64));
+  u64 *din = (u64 *)malloc((size_t)L * n * sizeof(u64));
+  u64 *dmod = (u64 *)malloc((size_t)LK * sizeof(u64));
+  u64 *omod = (u64 *)malloc((size_t)LK * sizeof(u64));
+  uint32_t *oidx = (uint32_t *)malloc((size_t)LK * sizeof(uint32_t));
+  int *opos = (int *)malloc((size_t)LK * sizeof(int));
+  u64 *obuf = (u64 *)malloc((size_t)LK * n * sizeof(u64));
+  for (int d = 0; d < dnum; d++) {
+    int a = 0, o = 0;
+    for (int i = 0; i < LK; i++) {
+      if (i < L && i % dnum == d) {
+        memcpy(din + (size_t)a * n, coef + (size_t)i * n, n * sizeof(u64));
+        dmod[a++] = c->p[all_idx[i]].q;
+        memcpy(raised + (size_t)i * n, cpoly + (size_t)i * n, n * sizeof(u64));
+      } else {
+        omod[o] = c->p[all_idx[i]].q;
+        oidx[o] = all_idx[i];
+        opos[o++] = i;
+      }
+    }
+    if (a == 0) continue;
+    orc_bconv(bconv_mode, n, a, dmod, din, o, omod, obuf);
+    orc_ntt_forward_batch(c, obuf, oidx, o);
+    for (int t = 0; t < o; t++)
+      memcpy(raised + (size_t)opos[t] * n, obuf + (size_t)t * n, n * sizeof(u64));
+    const u64 *k0 = evk + ((size_t)d * 2 + 0) * LK * n;
+    const u64 *k1 = evk + ((size_t)d * 2 + 1) * LK * n;
+#pragma omp parallel for schedule(static)
+    for (int i = 0; i < LK; i++) {
+      u64 q = c->p[all_idx[i]].q;
+      const u64 *r = raised + (size_t)i * n;
+      orc_ew_mad(q, n, r, k0 + (size_t)i * n, acc0 + (size_t)i * n, acc0 + (size_t)i * n);
+      orc_ew_mad(q, n, r, k1 + (size_t)i * n, acc1 + (size_t)i * n, acc1 + (size_t)i * n);
+    }
+  }
+  orc_moddown(c, bconv_mode, round_mode, L, q_idx, K, p_idx, acc0, acc0 + (size_t)L * n, out0);
+  orc_moddown(c, bconv_mode, round_mode, L, q_idx, K, p_idx, acc1, acc1 + (size_t)L * n, out1);
+  free(all_idx); free(coef); free(acc0); free(acc1); free(raised); free(din);
+  free(dmod); free(omod); free(oidx); free(opos); free(obuf);
+}
+
+/*
+ * Rescale by the last limb: out[i] = (c[i] - NTT_i(iNTT_last(c[L-1]))) * q_last^-1
+ * for i < L-1.  Restates rescale (cerium/compiler/backend/compiler_rescale.cc:
+ * 209-284): the last limb's coefficient-form residues are used as they are
+ * (no centring, floor semantics).  ORC_ROUND_HALF adds floor(q_last/2) first and
+ * subtracts it again mod q_i (rounding to nearest).
+ */
+ORC_API void orc_rescale(const orc_ctx *c, int round_mode, int L, const uint32_t *q_idx,
+                         const u64 *cpoly, u64 *out) {
+  size_t n = c->n;
+  int last = (int)q_idx[L - 1];
+  u64 ql = c->p[last].q;
+  u64 *lc = (u64 *)malloc(n * sizeof(u64));
+  memcpy(lc, cpoly + (size_t)(L - 1) * n, n * sizeof(u64));
+  orc_ntt_inverse(c, last, lc);
+  u64 half = ql >> 1;
+  if (round_mode == ORC_ROUND_HALF)
+    for (size_t j = 0; j < n; j++) lc[j] = addmod(lc[j], half, ql);
+#pragma omp parallel for schedule(dynamic)
+  for (int i = 0; i < L - 1; i++) {
+    u64 q = c->p[q_idx[i]].q;
+    u64 *t = (u64 *)malloc(n * sizeof(u64));
+    for (size_t j = 0; j < n; j++) {
+      u64 v = lc[j] % q;
+      t[j] = round_mode == ORC_ROUND_HALF ? submod(v, half % q, q) : v;
+    }
+    orc_sud(c, (int)q_idx[i], cpoly + (size_t)i * n, t, orc_invmod(ql % q, q), out + (size_t)i * n);
+    free(t);
+  }
+  free(lc);
+}
+
+/*
+ * HRot: rotate (c0,c1) by Galois element elt and key-switch back.
+ * Restates rotate_internal (cerium/compiler/backend/compiler.cc:701-726):
+ * automorphism of both polynomials in NTT form, key switch of the rotated c1,
+ * rotated c0 added to the first output.
+ */
+ORC_API void orc_hrot(const orc_ctx *c, int bconv_mode, int round_mode, int L, const uint32_t *q_idx,
+                      int K, const uint32_t *p_idx, int dnum, uint32_t elt, const u64 *c0,
+                      const u64 *c1, const u64 *evk, u64 *out0, u64 *out1) {
+  size_t n = c->n;
+  u64 *r0 = (u64 *)malloc((size_t)L * n * sizeof(u64));
+  u64 *r1 = (u64 *)malloc((size_t)L * n * sizeof(u64));
+  for (int i = 0; i < L; i++) {
+    orc_apply_galois_ntt(elt, c->logn, c0 + (size_t)i * n, r0 + (size_t)i * n);
+    orc_apply_galois_ntt(elt, c->logn, c1 + (size_t)i * n, r1 + (size_t)i * n);
+  }
+  orc_keyswitch(c, bconv_mode, round_mode, L, q_idx, K, p_idx, dnum, r1, evk, out0, out1);
+  for (int i = 0; i < L; i++)
+    orc_ew_add(c->p[q_idx[i]].q, n, out0 + (size_t)i * n, r0 + (size_t)i * n, out0 + (size_t)i * n);
+  free(r0); free(r1);
+}
+
+/*
+ * HMult + relinearize (+ optional rescale by the last limb).
+ * Restates mul (cerium/compiler/backend/compiler.cc:443-467:
+ * (d0,d1,d2) = (a0*b0, a0*b1 + a1*b0, a1*b1)), relinearisation as a key switch
+ * of d2 (compiler_keyswitch.cc:262-266, 360-380) and rescale.
+ * out0/out1 hold L limbs without rescale, L-1 limbs with it.
+ */
+ORC_API void orc_hmult_relin(const orc_ctx *c, int bconv_mode, int round_mode, int do_rescale, int L,
+                             const uint32_t *q_idx, int K, const uint32_t *p_idx, int dnum,
+                             const u64 *a0, const u64 *a1, const u64 *b0, const u64 *b1,
+                             const u64 *evk, u64 *out0, u64 *out1) {
+  size_t n = c->n, sz = (size_t)L * n;
+  u64 *d0 = (u64 *)malloc(sz * sizeof(u64)), *d1 = (u64 *)malloc(sz * sizeof(u64));
+  u64 *d2 = (u64 *)malloc(sz * sizeof(u64)), *k0 = (u64 *)malloc(sz * sizeof(u64));
+  u64 *k1 = (u64 *)malloc(sz * sizeof(u64));
+#pragma omp parallel for schedule(static)
+  for (int i = 0; i < L; i++) {
+    u64 q = c->p[q_idx[i]].q;
+    size_t o = (size_t)i * n;
+    orc_ew_mul(q, n, a0 + o, b0 + o, d0 + o);
+    orc_ew_mul(q, n, a0 + o, b1 + o, d1 + o);
+    orc_ew_mad(q, n, a1 + o, b0 + o, d1 + o, d1 + o);
+    orc_ew_mul(q, n, a1 + o, b1 + o, d2 + o);
+  }
+  orc_keyswitch(c, bconv_mode, round_mode, L, q_idx, K, p_idx, dnum, d2, evk, k0, k1);
+  for (int i = 0; i < L; i++) {
+    u64 q = c->p[q_idx[i]].q;
+    size_t o = (size_t)i * n;
+    orc_ew_add(q, n, k0 + o, d0 + o, k0 + o);
+    orc_ew_add(q, n, k1 + o, d1 + o, k1 + o);
+  }
+  if (do_rescale) {
+    orc_rescale(c, round_mode, L, q_idx, k0, out0);
+    orc_rescale(c, round_mode, L, q_idx, k1, out1);
+  } else {
+    memcpy(out0, k0, sz * sizeof(u64));
+    memcpy(out1, k1, sz * sizeof(u64));
+  }
+  free(d0); free(d1); free(d2); free(k0); free(k1);
+}
+
+ORC_API int orc_num_threads(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}

@@ -1,0 +1,151 @@
+"""Pins the CPU oracle against big-integer definitions (no GPU needed)."""
+import numpy as np
+import pytest
+
+import oracle
+from cerium_b200 import params
+from tests import bigint_ref as B
+
+
+def _rand_limbs(rng, moduli, n):
+    return np.stack([rng.integers(0, q, size=n, dtype=np.uint64) for q in moduli])
+
+
+@pytest.mark.parametrize("bits,logn", [(28, 4), (50, 5), (60, 6)])
+def test_ntt_matches_definition(bits, logn):
+    q = params.ntt_primes_below(bits, 1, logn)[0]
+    ctx = oracle.OracleContext(logn, [q])
+    psi = ctx.root(0)
+    assert pow(psi, 1 << logn, q) == q - 1
+    # minimal among all primitive 2N-th roots
+    assert psi == min(pow(psi, 2 * k + 1, q) for k in range(1 << logn))
+    rng = np.random.default_rng(1)
+    x = rng.integers(0, q, size=1 << logn, dtype=np.uint64)
+    got = ctx.ntt_forward(x, [0])[0]
+    assert np.array_equal(got, B.ntt_by_definition(x, q, psi, logn))
+    assert np.array_equal(ctx.ntt_inverse(got, [0])[0], x)
+    # table order of cerium/runtime/math/ntt.cpp:118-125
+    for i in range(1, 1 << logn):
+        assert ctx.twiddle(0, B.brev(i, logn)) == pow(psi, i, q)
+
+
+def test_ntt_roundtrip_and_convolution_full_size():
+    logn = 16
+    mods = params.ntt_primes_below(50, 2, logn) + params.reference_primes_28bit(1) + params.ntt_primes_below(60, 1, logn)
+    ctx = oracle.OracleContext(logn, mods)
+    rng = np.random.default_rng(2)
+    x = _rand_limbs(rng, mods, 1 << logn)
+    idx = list(range(len(mods)))
+    f = ctx.ntt_forward(x, idx)
+    assert np.array_equal(ctx.ntt_inverse(f, idx), x)
+    for k, q in enumerate(mods):
+        assert f[k].max() < q
+
+
+def test_negacyclic_convolution_small():
+    logn = 6
+    q = params.ntt_primes_below(50, 1, logn)[0]
+    ctx = oracle.OracleContext(logn, [q])
+    rng = np.random.default_rng(3)
+    a = rng.integers(0, q, size=64, dtype=np.uint64)
+    b = rng.integers(0, q, size=64, dtype=np.uint64)
+    fa, fb = ctx.ntt_forward(a, [0])[0], ctx.ntt_forward(b, [0])[0]
+    prod = oracle.ew("mul", q, fa, fb)
+    assert np.array_equal(ctx.ntt_inverse(prod, [0])[0], oracle.negacyclic_mul_schoolbook(q, a, b))
+
+
+def test_galois_step_elements():
+    logn = 16
+    n = 1 << logn
+    assert oracle.galois_elt_from_step(0, logn) == 2 * n - 1
+    assert oracle.galois_elt_from_step(1, logn) == 5
+    assert oracle.galois_elt_from_step(3, logn) == 125
+    assert oracle.galois_elt_from_step(-1, logn) == pow(5, n // 2 - 1, 2 * n)
+
+
+@pytest.mark.parametrize("step", [0, 1, 5, -3])
+def test_galois_ntt_matches_coefficient_definition(step):
+    logn = 6
+    q = params.ntt_primes_below(28, 1, logn)[0]
+    ctx = oracle.OracleContext(logn, [q])
+    elt = oracle.galois_elt_from_step(step, logn)
+    rng = np.random.default_rng(4)
+    x = rng.integers(0, q, size=1 << logn, dtype=np.uint64)
+    via_coeff = ctx.ntt_forward(oracle.apply_galois_coeff(elt, logn, q, x), [0])[0]
+    via_ntt = oracle.apply_galois_ntt(elt, logn, ctx.ntt_forward(x, [0])[0])
+    assert np.array_equal(via_coeff, via_ntt)
+    t = oracle.galois_table_ntt(elt, logn)
+    assert sorted(t.tolist()) == list(range(1 << logn))
+
+
+@pytest.mark.parametrize("bits", [28, 50])
+def test_bconv_both_modes_vs_bigint(bits):
+    logn = 4
+    mods = params.ntt_primes_below(bits, 9, logn)
+    in_mod, out_mod = mods[:4], mods[4:]
+    rng = np.random.default_rng(5)
+    x = _rand_limbs(rng, in_mod, 16)
+    lazy = oracle.bconv(oracle.BCONV_LAZY, in_mod, x, out_mod)
+    exact = oracle.bconv(oracle.BCONV_EXACT, in_mod, x, out_mod)
+    Q = int(np.prod([int(m) for m in in_mod], dtype=object))
+    for c in range(16):
+        col = [int(v) for v in x[:, c]]
+        assert [int(v) for v in lazy[:, c]] == B.bconv_lazy(col, in_mod, out_mod)
+        assert [int(v) for v in exact[:, c]] == B.bconv_exact(col, in_mod, out_mod)
+        # exact mode overshoots the true value by less than I multiples of Q
+        X = B.crt_reconstruct(col, in_mod)
+        s = sum((int(r) * pow(Q // m, -1, m) % m) * (Q // m) for r, m in zip(col, in_mod))
+        assert (s - X) % Q == 0 and 0 <= (s - X) // Q < len(in_mod)
+
+
+def test_single_limb_bconv_is_plain_reduction():
+    mods = params.ntt_primes_below(50, 3, 4)
+    rng = np.random.default_rng(6)
+    x = _rand_limbs(rng, mods[:1], 16)
+    for mode in (oracle.BCONV_LAZY, oracle.BCONV_EXACT):
+        out = oracle.bconv(mode, mods[:1], x, mods[1:])
+        for j, p in enumerate(mods[1:]):
+            assert np.array_equal(out[j], x[0] % np.uint64(p))
+
+
+@pytest.mark.parametrize("round_mode", [oracle.ROUND_FLOOR, oracle.ROUND_HALF])
+def test_moddown_vs_bigint_division(round_mode):
+    logn = 4
+    n = 1 << logn
+    q = params.ntt_primes_below(50, 3, logn)
+    p = params.ntt_primes_below(60, 2, logn)
+    ctx = oracle.OracleContext(logn, q + p)
+    rng = np.random.default_rng(7)
+    Q = q[0] * q[1] * q[2]
+    P = p[0] * p[1]
+    # integer polynomial T in [0, QP), reduced to every prime and transformed
+    T = [int(rng.integers(0, 2**62)) * int(rng.integers(0, 2**62)) * int(rng.integers(0, 2**62)) % (Q * P)
+         for _ in range(n)]
+    coeffs = np.array([[t % m for t in T] for m in q + p], dtype=np.uint64)
+    ntt = ctx.ntt_forward(coeffs, list(range(5)))
+    out = ctx.moddown(oracle.BCONV_EXACT, round_mode, [0, 1, 2], [3, 4], ntt[:3], ntt[3:])
+    got = ctx.ntt_inverse(out, [0, 1, 2])
+    for c in range(n):
+        t = T[c]
+        want = (t + P // 2) // P if round_mode == oracle.ROUND_HALF else t // P
+        # fast base conversion may overshoot [t]_P by u*P with 0 <= u < K: result is off by -u
+        cands = [[(want - u) % m for m in q] for u in range(3)]
+        assert [int(v) for v in got[:, c]] in cands
+
+
+def test_rescale_vs_bigint_division():
+    logn = 4
+    n = 1 << logn
+    q = params.ntt_primes_below(50, 3, logn)
+    ctx = oracle.OracleContext(logn, q)
+    rng = np.random.default_rng(8)
+    Q = q[0] * q[1] * q[2]
+    T = [int(rng.integers(0, 2**62)) * int(rng.integers(0, 2**62)) * int(rng.integers(0, 2**50)) % Q
+         for _ in range(n)]
+    coeffs = np.array([[t % m for t in T] for m in q], dtype=np.uint64)
+    ntt = ctx.ntt_forward(coeffs, [0, 1, 2])
+    for mode in (oracle.ROUND_FLOOR, oracle.ROUND_HALF):
+        got = ctx.ntt_inverse(ctx.rescale(mode, [0, 1, 2], ntt), [0, 1])
+        for c in range(n):
+            want = (T[c] + q[2] // 2) // q[2] if mode == oracle.ROUND_HALF else T[c] // q[2]
+            assert [int(v) for v in got[:, c]] == [want % q[0], want % q[1]]
