@@ -1,0 +1,254 @@
+"""ctypes binding of ``include/cerium_b200.h``.
+
+``Library(path)`` declares every entry point of the C ABI; ``load()`` opens the in-tree CUDA
+build and raises if it is missing: there is no CPU implementation to fall back to.
+Arguments that the C ABI takes as device pointers are plain integers here (``tensor.data_ptr()``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional, Sequence
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libcerium_b200.so")
+
+OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED = 0, 1, 2, 3
+BCONV_LAZY, BCONV_EXACT = 0, 1
+ROUND_FLOOR, ROUND_HALF = 0, 1
+EW_ADD, EW_SUB, EW_NEG, EW_MUL, EW_MAD, EW_PMU, EW_MUL_SCALAR = range(7)
+
+_vp = C.c_void_p
+_u32p = C.POINTER(C.c_uint32)
+_u64p = C.POINTER(C.c_uint64)
+_sz = C.c_size_t
+
+# name -> (restype, argtypes); the list is also what the symbol-export test checks
+SIGNATURES = {
+    "cerium_version": (C.c_int, []),
+    "cerium_last_error": (C.c_char_p, []),
+    "cerium_context_create": (C.c_int, [C.POINTER(_vp), C.c_int, C.c_int, C.c_int, _u64p, C.c_int]),
+    "cerium_context_destroy": (C.c_int, [_vp]),
+    "cerium_context_word_bits": (C.c_int, [_vp]),
+    "cerium_context_num_moduli": (C.c_int, [_vp]),
+    "cerium_context_modulus": (C.c_uint64, [_vp, C.c_int]),
+    "cerium_context_root": (C.c_uint64, [_vp, C.c_int]),
+    "cerium_ntt_forward": (C.c_int, [_vp, _vp, _sz, _vp, _sz, _u32p, C.c_int, _vp]),
+    "cerium_ntt_inverse": (C.c_int, [_vp, _vp, _sz, _vp, _sz, _u32p, C.c_int, _vp]),
+    "cerium_ntt_forward_ptrs": (C.c_int, [_vp, _vp, _vp, _vp, _sz, _vp]),
+    "cerium_ntt_inverse_ptrs": (C.c_int, [_vp, _vp, _vp, _vp, _sz, _vp]),
+    "cerium_sud": (C.c_int, [_vp, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _u32p, C.c_int, _u32p, C.c_int, _vp]),
+    "cerium_ewise": (C.c_int, [_vp, C.c_int, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _u64p, _u32p, C.c_int, _vp]),
+    "cerium_tensor": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _u32p, C.c_int, _vp]),
+    "cerium_galois_elt_from_step": (C.c_uint32, [C.c_int, C.c_int]),
+    "cerium_automorph": (C.c_int, [_vp, _vp, _sz, _vp, _sz, C.c_uint32, C.c_int, _vp]),
+    "cerium_bconv_create": (C.c_int, [_vp, C.POINTER(_vp), C.c_int, _u32p, C.c_int, _u32p, C.c_int]),
+    "cerium_bconv_destroy": (C.c_int, [_vp]),
+    "cerium_bconv_apply": (C.c_int, [_vp, _vp, _sz, _vp, _sz, _vp]),
+    "cerium_keyswitch_create": (C.c_int, [_vp, C.POINTER(_vp), C.c_int, C.c_int, _u32p, C.c_int, _u32p, C.c_int, C.c_int]),
+    "cerium_keyswitch_destroy": (C.c_int, [_vp]),
+    "cerium_keyswitch_workspace_bytes": (_sz, [_vp]),
+    "cerium_keyswitch_apply": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "cerium_hrot": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, C.c_uint32, _vp]),
+    "cerium_hmult": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_int, _vp]),
+    "cerium_rescale": (C.c_int, [_vp, C.c_int, _vp, _vp, _u32p, C.c_int, C.c_int, _vp, _vp]),
+}
+
+
+class CeriumError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__("cerium_b200 error %d: %s" % (code, message))
+        self.code = code
+        self.message = message
+
+
+def _u32(values: Sequence[int]):
+    arr = (C.c_uint32 * len(values))(*[int(v) for v in values])
+    return arr
+
+
+def _u64(values: Sequence[int]):
+    arr = (C.c_uint64 * len(values))(*[int(v) for v in values])
+    return arr
+
+
+class Library:
+    """One loaded copy of the C ABI."""
+
+    def __init__(self, path: str):
+        if not os.path.exists(path):
+            raise FileNotFoundError(
+                "%s not found: build it with `python -m cerium_b200.build` (there is no CPU fallback)" % path)
+        self.path = path
+        self.dll = C.CDLL(path)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(self.dll, name)
+            fn.restype = res
+            fn.argtypes = args
+
+    def check(self, rc: int) -> None:
+        if rc != OK:
+            raise CeriumError(rc, self.dll.cerium_last_error().decode())
+
+    def galois_elt_from_step(self, step: int, logn: int = 16) -> int:
+        return int(self.dll.cerium_galois_elt_from_step(step, logn))
+
+
+class Context:
+    """Device tables for a prime list (handle of ``cerium_context``)."""
+
+    def __init__(self, lib: Library, moduli: Sequence[int], word_bits: int, device: int = 0, logn: int = 16):
+        self.lib = lib
+        self.moduli = [int(m) for m in moduli]
+        self.word_bits = int(word_bits)
+        self.logn = logn
+        self.n = 1 << logn
+        self.device = device
+        h = _vp()
+        lib.check(lib.dll.cerium_context_create(C.byref(h), device, logn, word_bits, _u64(self.moduli), len(self.moduli)))
+        self.h = h
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.dll.cerium_context_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def word_bytes(self) -> int:
+        return self.word_bits // 8
+
+    def root(self, k: int) -> int:
+        return int(self.lib.dll.cerium_context_root(self.h, k))
+
+    # -- transforms ------------------------------------------------------------------
+    def ntt_forward(self, out: int, inp: int, prime_idx: Sequence[int], out_stride: Optional[int] = None,
+                    in_stride: Optional[int] = None, stream: int = 0):
+        n = self.n
+        self.lib.check(self.lib.dll.cerium_ntt_forward(self.h, out, out_stride or n, inp, in_stride or n,
+                                                       _u32(prime_idx), len(prime_idx), stream))
+
+    def ntt_inverse(self, out: int, inp: int, prime_idx: Sequence[int], out_stride: Optional[int] = None,
+                    in_stride: Optional[int] = None, stream: int = 0):
+        n = self.n
+        self.lib.check(self.lib.dll.cerium_ntt_inverse(self.h, out, out_stride or n, inp, in_stride or n,
+                                                       _u32(prime_idx), len(prime_idx), stream))
+
+    def ntt_forward_ptrs(self, outs: int, ins: int, bases: int, num_bases: int, stream: int = 0):
+        self.lib.check(self.lib.dll.cerium_ntt_forward_ptrs(self.h, outs, ins, bases, num_bases, stream))
+
+    def ntt_inverse_ptrs(self, outs: int, ins: int, bases: int, num_bases: int, stream: int = 0):
+        self.lib.check(self.lib.dll.cerium_ntt_inverse_ptrs(self.h, outs, ins, bases, num_bases, stream))
+
+    def sud(self, out: int, minuend: int, in_coeff: int, prime_idx: Sequence[int], divide_primes: Sequence[int],
+            addend: int = 0, stream: int = 0):
+        n = self.n
+        self.lib.check(self.lib.dll.cerium_sud(self.h, out, n, minuend, n, in_coeff, n, addend or None, n,
+                                               _u32(prime_idx), len(prime_idx), _u32(divide_primes),
+                                               len(divide_primes), stream))
+
+    # -- element-wise ----------------------------------------------------------------
+    def ewise(self, op: int, out: int, a: int, prime_idx: Sequence[int], b: int = 0, c: int = 0,
+              scalars: Optional[Sequence[int]] = None, stream: int = 0):
+        n = self.n
+        sc = _u64(scalars) if scalars is not None else None
+        self.lib.check(self.lib.dll.cerium_ewise(self.h, op, out, n, a, n, b or None, n, c or None, n, sc,
+                                                 _u32(prime_idx), len(prime_idx), stream))
+
+    def tensor(self, d0: int, d1: int, d2: int, a0: int, a1: int, b0: int, b1: int, prime_idx: Sequence[int],
+               stream: int = 0):
+        self.lib.check(self.lib.dll.cerium_tensor(self.h, d0, d1, d2, a0, a1, b0, b1, self.n, _u32(prime_idx),
+                                                  len(prime_idx), stream))
+
+    def automorph(self, out: int, inp: int, galois_elt: int, count: int, stream: int = 0):
+        n = self.n
+        self.lib.check(self.lib.dll.cerium_automorph(self.h, out, n, inp, n, galois_elt, count, stream))
+
+    def rescale(self, out: int, inp: int, q_idx: Sequence[int], n_polys: int, scratch: int,
+                round_mode: int = ROUND_FLOOR, stream: int = 0):
+        self.lib.check(self.lib.dll.cerium_rescale(self.h, round_mode, out, inp, _u32(q_idx), len(q_idx), n_polys,
+                                                   scratch, stream))
+
+
+class BaseConverter:
+    """Fast base conversion between two prime sets (handle of ``cerium_bconv``)."""
+
+    def __init__(self, ctx: Context, in_primes: Sequence[int], out_primes: Sequence[int], mode: int = BCONV_LAZY):
+        self.ctx = ctx
+        self.n_in, self.n_out = len(in_primes), len(out_primes)
+        h = _vp()
+        ctx.lib.check(ctx.lib.dll.cerium_bconv_create(ctx.h, C.byref(h), mode, _u32(in_primes), len(in_primes),
+                                                      _u32(out_primes), len(out_primes)))
+        self.h = h
+
+    def apply(self, out: int, inp: int, out_stride: Optional[int] = None, in_stride: Optional[int] = None,
+              stream: int = 0):
+        n = self.ctx.n
+        self.ctx.lib.check(self.ctx.lib.dll.cerium_bconv_apply(self.h, out, out_stride or n, inp, in_stride or n, stream))
+
+    def close(self):
+        if getattr(self, "h", None) and self.ctx.h:
+            self.ctx.lib.dll.cerium_bconv_destroy(self.h)
+        self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class KeySwitch:
+    """Hybrid key-switching plan (handle of ``cerium_keyswitch``)."""
+
+    def __init__(self, ctx: Context, q_idx: Sequence[int], p_idx: Sequence[int], dnum: int,
+                 bconv_mode: int = BCONV_LAZY, round_mode: int = ROUND_FLOOR):
+        self.ctx = ctx
+        self.q_idx, self.p_idx, self.dnum = list(q_idx), list(p_idx), dnum
+        h = _vp()
+        ctx.lib.check(ctx.lib.dll.cerium_keyswitch_create(ctx.h, C.byref(h), bconv_mode, round_mode, _u32(q_idx),
+                                                          len(q_idx), _u32(p_idx), len(p_idx), dnum))
+        self.h = h
+
+    @property
+    def workspace_bytes(self) -> int:
+        return int(self.ctx.lib.dll.cerium_keyswitch_workspace_bytes(self.h))
+
+    def apply(self, out0: int, out1: int, cpoly: int, evk: int, add0: int = 0, add1: int = 0, stream: int = 0):
+        self.ctx.lib.check(self.ctx.lib.dll.cerium_keyswitch_apply(self.h, out0, out1, cpoly, evk, add0 or None,
+                                                                   add1 or None, stream))
+
+    def hrot(self, out0: int, out1: int, c0: int, c1: int, evk: int, galois_elt: int, stream: int = 0):
+        self.ctx.lib.check(self.ctx.lib.dll.cerium_hrot(self.h, out0, out1, c0, c1, evk, galois_elt, stream))
+
+    def hmult(self, out0: int, out1: int, a0: int, a1: int, b0: int, b1: int, evk: int, do_rescale: bool,
+              stream: int = 0):
+        self.ctx.lib.check(self.ctx.lib.dll.cerium_hmult(self.h, out0, out1, a0, a1, b0, b1, evk,
+                                                         1 if do_rescale else 0, stream))
+
+    def close(self):
+        if getattr(self, "h", None) and self.ctx.h:
+            self.ctx.lib.dll.cerium_keyswitch_destroy(self.h)
+        self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+_default: Optional[Library] = None
+
+
+def load() -> Library:
+    """The shipped CUDA build.  Raises if the shared object is missing."""
+    global _default
+    if _default is None:
+        _default = Library(LIB_PATH)
+    return _default

@@ -1,0 +1,237 @@
+// Element-wise limb kernels: modular add / sub / neg / mul / multiply-add, P-multiply,
+// ciphertext tensor product, Galois automorphism and the key-switching inner product.
+//
+// Replaces the kernels Cerium's compiler generates per program
+// (cerium/compiler/backend/cuda_kernel.cc:64-399 handlers, :1142-1280 generic kernel,
+// :2669-2765 PMU) with a fixed hand-written set.  Differences from the generated code:
+// 16-byte vector accesses (2 u64 / 4 u32 per thread) instead of one word per thread, the
+// automorphism index computed from bit reversals instead of a permutation table in global
+// memory, and the evaluation-key inner product accumulated over all digits in registers
+// (two-word sums, one Barrett reduction at the end) instead of one Mul/Mad launch per digit
+// with a reduction mod q^2 after every term.
+#pragma once
+#include "modarith.cuh"
+
+namespace cerium {
+
+constexpr int kEwThreads = 256;
+constexpr int kEwMaxLimbs = 128;  // limbs per launch (per-limb scalars travel as parameters)
+
+template <typename W>
+struct Vec16;
+template <>
+struct Vec16<uint64_t> {
+  static constexpr int kLanes = 2;
+  uint64_t v[2];
+  static __device__ __forceinline__ Vec16 load(const uint64_t* p) {
+    const ulonglong2 t = *reinterpret_cast<const ulonglong2*>(p);
+    Vec16 r;
+    r.v[0] = t.x;
+    r.v[1] = t.y;
+    return r;
+  }
+  __device__ __forceinline__ void store(uint64_t* p) const {
+    *reinterpret_cast<ulonglong2*>(p) = make_ulonglong2(v[0], v[1]);
+  }
+};
+template <>
+struct Vec16<uint32_t> {
+  static constexpr int kLanes = 4;
+  uint32_t v[4];
+  static __device__ __forceinline__ Vec16 load(const uint32_t* p) {
+    const uint4 t = *reinterpret_cast<const uint4*>(p);
+    Vec16 r;
+    r.v[0] = t.x;
+    r.v[1] = t.y;
+    r.v[2] = t.z;
+    r.v[3] = t.w;
+    return r;
+  }
+  __device__ __forceinline__ void store(uint32_t* p) const {
+    *reinterpret_cast<uint4*>(p) = make_uint4(v[0], v[1], v[2], v[3]);
+  }
+};
+
+// A stack of limbs: limb b at p + b * stride (words).
+template <typename W>
+struct Limbs {
+  W* p;
+  size_t stride;
+  __device__ __forceinline__ W* at(int b, int idx) const { return p + (size_t)b * stride + idx; }
+};
+
+enum EwOp : int {
+  kEwAdd = 0,   // out = a + b
+  kEwSub = 1,   // out = a - b
+  kEwNeg = 2,   // out = -a
+  kEwMul = 3,   // out = a * b
+  kEwMad = 4,   // out = a * b + c
+  kEwPmu = 5,   // out = a + b * s[limb]
+  kEwMulScalar = 6,  // out = a * s[limb]
+};
+
+template <typename W>
+struct EwArgs {
+  Limbs<W> out, a, b, c;
+  W scalar[kEwMaxLimbs];        // per limb (kEwPmu, kEwMulScalar)
+  W scalar_shoup[kEwMaxLimbs];  // per limb
+  uint8_t prime[kEwMaxLimbs];
+};
+
+// grid = (N / (256 * lanes), limbs), block = 256.
+template <typename W, int kOp>
+__global__ void __launch_bounds__(kEwThreads)
+    ewise_kernel(const EwArgs<W> g, const PrimeConst<W>* __restrict__ pcs) {
+  using V = Vec16<W>;
+  const int b = blockIdx.y;
+  const uint32_t pi = g.prime[b];
+  const PrimeConst<W> pc = pcs[pi];
+  const int idx = (blockIdx.x * kEwThreads + threadIdx.x) * V::kLanes;
+  V a = V::load(g.a.at(b, idx)), o;
+  V bb, cc;
+  if (kOp == kEwAdd || kOp == kEwSub || kOp == kEwMul || kOp == kEwMad || kOp == kEwPmu)
+    bb = V::load(g.b.at(b, idx));
+  if (kOp == kEwMad) cc = V::load(g.c.at(b, idx));
+  W s = 0, ss = 0;
+  if (kOp == kEwPmu || kOp == kEwMulScalar) {
+    s = g.scalar[b];
+    ss = g.scalar_shoup[b];
+  }
+#pragma unroll
+  for (int l = 0; l < V::kLanes; l++) {
+    if (kOp == kEwAdd) o.v[l] = add_mod<W>(a.v[l], bb.v[l], pc.q);
+    if (kOp == kEwSub) o.v[l] = sub_mod<W>(a.v[l], bb.v[l], pc.q);
+    if (kOp == kEwNeg) o.v[l] = a.v[l] ? pc.q - a.v[l] : (W)0;
+    if (kOp == kEwMul) o.v[l] = mul_mod<W>(a.v[l], bb.v[l], pc);
+    if (kOp == kEwMad) o.v[l] = add_mod<W>(mul_mod<W>(a.v[l], bb.v[l], pc), cc.v[l], pc.q);
+    if (kOp == kEwPmu)
+      o.v[l] = add_mod<W>(a.v[l], csub<W>(mul_shoup_lazy<W>(bb.v[l], s, ss, pc.q), pc.q), pc.q);
+    if (kOp == kEwMulScalar) o.v[l] = csub<W>(mul_shoup_lazy<W>(a.v[l], s, ss, pc.q), pc.q);
+  }
+  o.store(g.out.at(b, idx));
+}
+
+// Ciphertext tensor product (cerium/compiler/backend/compiler.cc:443-467):
+// d0 = a0*b0, d1 = a0*b1 + a1*b0, d2 = a1*b1.  Reads 4 limbs, writes 3, one pass.
+template <typename W>
+struct TensorArgs {
+  Limbs<W> a0, a1, b0, b1, d0, d1, d2;
+  uint8_t prime[kEwMaxLimbs];
+};
+
+template <typename W>
+__global__ void __launch_bounds__(kEwThreads)
+    tensor_kernel(const TensorArgs<W> g, const PrimeConst<W>* __restrict__ pcs) {
+  using V = Vec16<W>;
+  const int b = blockIdx.y;
+  const PrimeConst<W> pc = pcs[g.prime[b]];
+  const int idx = (blockIdx.x * kEwThreads + threadIdx.x) * V::kLanes;
+  const V a0 = V::load(g.a0.at(b, idx)), a1 = V::load(g.a1.at(b, idx));
+  const V b0 = V::load(g.b0.at(b, idx)), b1 = V::load(g.b1.at(b, idx));
+  V d0, d1, d2;
+#pragma unroll
+  for (int l = 0; l < V::kLanes; l++) {
+    d0.v[l] = mul_mod<W>(a0.v[l], b0.v[l], pc);
+    d2.v[l] = mul_mod<W>(a1.v[l], b1.v[l], pc);
+    Acc2<W> acc;
+    acc.clear();
+    acc.mad(a0.v[l], b1.v[l]);
+    acc.mad(a1.v[l], b0.v[l]);
+    d1.v[l] = barrett2<W>(acc.hi, acc.lo, pc);
+  }
+  d0.store(g.d0.at(b, idx));
+  d1.store(g.d1.at(b, idx));
+  d2.store(g.d2.at(b, idx));
+}
+
+// NTT-domain Galois automorphism out[i] = in[pi(i)] with
+//   pi(i) = brev16( ((elt * (2*brev16(i) + 1)) >> 1) & (N-1) )
+// (cerium/runtime/math/galois.cpp:30-62 builds this as a table; the reference kernels scatter
+// through its inverse, cerium/compiler/backend/cuda_kernel.cc:228-300).  The map sends every
+// aligned block of 2^k indices onto an aligned block of 2^k indices, so a warp's 32 gathered
+// words always come from one aligned 32-word segment: the gather is sector-exact without a
+// table and without staging.
+__device__ __forceinline__ uint32_t galois_source_index(uint32_t i, uint32_t elt) {
+  const uint32_t r = (__brev(i) >> (32 - kLogN)) * 2u + 1u;
+  const uint32_t raw = ((elt * r) >> 1) & (uint32_t)(kN - 1);
+  return __brev(raw) >> (32 - kLogN);
+}
+
+template <typename W>
+struct AutomorphArgs {
+  Limbs<W> out, in;
+  uint32_t elt;
+};
+
+// grid = (N / 256, limbs), block = 256; in and out must not overlap.
+template <typename W>
+__global__ void __launch_bounds__(kEwThreads) automorph_kernel(const AutomorphArgs<W> g) {
+  const int b = blockIdx.y;
+  const uint32_t i = blockIdx.x * kEwThreads + threadIdx.x;
+  *g.out.at(b, (int)i) = *g.in.at(b, (int)galois_source_index(i, g.elt));
+}
+
+// Key-switching inner product over the extended basis (L + K limbs):
+//   out0[b] = sum_d a_d[b] * evk[d][0][b],   out1[b] = sum_d a_d[b] * evk[d][1][b]
+// where a_d[b] is the raised digit d at limb b.  For the limbs that belong to digit d itself
+// (b < L and b % dnum == d) the raised value is the NTT-form input limb, which is read in
+// place from `own` instead of from `raised` (cerium/compiler/backend/kernel_instruction.h:
+// 823-838 moves it; here it is never copied).
+// Restates the EVKMUL / EVKMUL_EXT groups of cerium/compiler/backend/compiler_keyswitch.cc:
+// 336-358 and :695-772 as one launch.
+template <typename W>
+struct InnerProductArgs {
+  const W* raised;        // [dnum][LK][N]
+  size_t raised_digit_stride;
+  size_t raised_limb_stride;
+  const W* own;           // [L][N] NTT-form input
+  size_t own_stride;
+  const W* evk;           // [dnum][2][LK][N]
+  size_t evk_digit_stride;
+  size_t evk_poly_stride;
+  size_t evk_limb_stride;
+  Limbs<W> out0, out1;    // [LK][N]
+  int L;
+  int dnum;
+  uint8_t prime[kEwMaxLimbs];  // prime index of extended limb b
+};
+
+template <typename W>
+__global__ void __launch_bounds__(kEwThreads)
+    inner_product_kernel(const InnerProductArgs<W> g, const PrimeConst<W>* __restrict__ pcs) {
+  using V = Vec16<W>;
+  const int b = blockIdx.y;
+  const PrimeConst<W> pc = pcs[g.prime[b]];
+  const int idx = (blockIdx.x * kEwThreads + threadIdx.x) * V::kLanes;
+  Acc2<W> acc0[V::kLanes], acc1[V::kLanes];
+#pragma unroll
+  for (int l = 0; l < V::kLanes; l++) {
+    acc0[l].clear();
+    acc1[l].clear();
+  }
+  for (int d = 0; d < g.dnum; d++) {
+    const bool is_own = b < g.L && (b % g.dnum) == d;
+    const W* ap = is_own ? g.own + (size_t)b * g.own_stride + idx
+                         : g.raised + (size_t)d * g.raised_digit_stride +
+                               (size_t)b * g.raised_limb_stride + idx;
+    const W* kp = g.evk + (size_t)d * g.evk_digit_stride + (size_t)b * g.evk_limb_stride + idx;
+    const V a = V::load(ap);
+    const V k0 = V::load(kp);
+    const V k1 = V::load(kp + g.evk_poly_stride);
+#pragma unroll
+    for (int l = 0; l < V::kLanes; l++) {
+      acc0[l].mad(a.v[l], k0.v[l]);
+      acc1[l].mad(a.v[l], k1.v[l]);
+    }
+  }
+  V o0, o1;
+#pragma unroll
+  for (int l = 0; l < V::kLanes; l++) {
+    o0.v[l] = barrett2<W>(acc0[l].hi, acc0[l].lo, pc);
+    o1.v[l] = barrett2<W>(acc1[l].hi, acc1[l].lo, pc);
+  }
+  o0.store(g.out0.at(b, idx));
+  o1.store(g.out1.at(b, idx));
+}
+
+}  // namespace cerium

@@ -1,0 +1,160 @@
+// Internal host-side structures behind the opaque handles of include/cerium_b200.h.
+#pragma once
+#if defined(CERIUM_EMU)
+#include "emu_cuda.h"  // test-only host stand-ins; the shipped library is never built this way
+#else
+#include <cuda_runtime.h>
+#endif
+
+#include <cstdint>
+#include <cstdio>
+#include <string>
+#include <vector>
+
+#include "../../include/cerium_b200.h"
+#include "bconv_kernels.cuh"
+#include "ewise_kernels.cuh"
+#include "host_math.h"
+#include "ntt_kernels.cuh"
+
+namespace cerium {
+
+void set_error(const std::string& msg);
+int fail(int code, const std::string& msg);
+
+#define CERIUM_CUDA(call)                                                              \
+  do {                                                                                 \
+    cudaError_t e__ = (call);                                                          \
+    if (e__ != cudaSuccess)                                                            \
+      return ::cerium::fail(CERIUM_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(e__)); \
+  } while (0)
+
+#define CERIUM_LAUNCH_CHECK(what)                                                      \
+  do {                                                                                 \
+    cudaError_t e__ = cudaGetLastError();                                              \
+    if (e__ != cudaSuccess)                                                            \
+      return ::cerium::fail(CERIUM_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e__)); \
+  } while (0)
+
+// Kernel launch through a function pointer (template-ids with commas stay out of the macro).
+#if defined(CERIUM_EMU)
+#define CERIUM_LAUNCH(kfn, grid, block, smem, stream, ...) \
+  ::cerium_emu::launch((grid), (block), (smem), [=]() { kfn(__VA_ARGS__); })
+#else
+#define CERIUM_LAUNCH(kfn, grid, block, smem, stream, ...) kfn<<<(grid), (block), (smem), (stream)>>>(__VA_ARGS__)
+#endif
+
+// Runs fn(W{}) with W = uint32_t or uint64_t according to the context's word size.
+template <typename F>
+inline int dispatch_word(int word_bits, F&& fn) {
+  if (word_bits == 32) return fn(uint32_t{});
+  return fn(uint64_t{});
+}
+
+// RAII switch to the context's device for the duration of a call.
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = true;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) != cudaSuccess) ok = false;
+    if (ok && prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+    if (prev == dev) prev = -1;
+  }
+  ~DeviceGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+}  // namespace cerium
+
+struct cerium_context {
+  int device = 0;
+  int logn = 0;
+  int word_bits = 0;
+  int n_primes = 0;
+  std::vector<uint64_t> moduli;
+  std::vector<uint64_t> psi;
+  void* d_tw_fwd = nullptr;  // Pair[n_primes][N], bit-reversed powers of psi
+  void* d_tw_inv = nullptr;  // Pair[n_primes][N], bit-reversed powers of psi^-1
+  void* d_pcs = nullptr;     // PrimeConst<W>[n_primes]
+  size_t word_bytes() const { return (size_t)word_bits / 8; }
+};
+
+struct cerium_bconv {
+  cerium_context* ctx = nullptr;
+  int mode = 0;
+  int I = 0, O = 0;
+  std::vector<uint32_t> in_primes, out_primes;
+  // one device allocation holding every table below
+  void* d_block = nullptr;
+  void* d_factors = nullptr;    // W[O][I]
+  void* d_inv = nullptr;        // W[I] (exact mode, unless the caller pre-scales)
+  void* d_inv_shoup = nullptr;  // W[I]
+  void* d_in_add = nullptr;     // W[I]  rounding term, or null
+  void* d_out_sub = nullptr;    // W[O]  rounding term, or null
+  uint32_t* d_in_prime = nullptr;
+  uint32_t* d_out_prime = nullptr;
+  uint32_t* d_out_pos = nullptr;  // or null
+  std::vector<uint64_t> inv_host;  // [Qhat_i^-1]_{q_i}
+};
+
+namespace cerium {
+
+// Options of create_bconv beyond the public entry point.
+struct BconvOptions {
+  bool prescaled = false;            // exact mode, inputs already multiplied by [Qhat_i^-1]
+  bool round_half = false;           // add floor(prod_in/2) to inputs, subtract it from outputs
+  std::vector<uint32_t> out_pos;     // output limb slots (empty = 0..O-1)
+};
+
+int create_bconv(cerium_context* ctx, cerium_bconv** out, int mode, const uint32_t* in_primes, int n_in,
+                 const uint32_t* out_primes, int n_out, const BconvOptions& opt);
+
+// One entry of a batched conversion launch.
+struct BconvCall {
+  cerium_bconv* bc;
+  void* out;
+  size_t out_stride;
+  const void* in;
+  size_t in_stride;
+};
+int launch_bconv(cerium_context* ctx, const BconvCall* calls, int count, cudaStream_t stream);
+
+// Batched transforms with explicit limb slots (pos[b]) and prime indices.
+struct NttCall {
+  const void* in;
+  void* out;
+  size_t in_stride, out_stride;
+  const uint32_t* pos;    // count entries, or null for 0..count-1
+  const uint32_t* prime;  // count entries
+  int count;
+};
+int launch_ntt_forward(cerium_context* ctx, const NttCall& c, cudaStream_t stream);
+// scale / scale_shoup: device arrays with one word per batch entry, or null.
+int launch_ntt_inverse(cerium_context* ctx, const NttCall& c, const void* scale, const void* scale_shoup,
+                       cudaStream_t stream);
+
+// SuD over `count` limbs (count <= kSudMaxBatch per launch; chunked internally).
+struct SudCall {
+  const void* src;       // coefficient-form source; src_stride == 0 broadcasts one limb
+  size_t src_stride;
+  void* work;            // column-pass output / row-pass input (may equal src when src_stride != 0)
+  size_t work_stride;
+  void* dst;
+  size_t dst_stride;
+  const void* minuend;
+  size_t minuend_stride;
+  const void* addend;    // or null
+  size_t addend_stride;
+  const uint32_t* prime;  // count prime indices
+  const uint64_t* factor; // count canonical residues (host)
+  int count;
+  // source re-reduction (only when reduce_src): residues of modulus src_q, optional rounding
+  bool reduce_src = false;
+  uint64_t src_q = 0;
+  uint64_t pre_add = 0;
+  const uint64_t* post_sub = nullptr;  // count residues (host) or null
+};
+int launch_sud(cerium_context* ctx, const SudCall& c, cudaStream_t stream);
+
+}  // namespace cerium

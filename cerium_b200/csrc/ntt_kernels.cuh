@@ -1,0 +1,405 @@
+// Negacyclic NTT kernels for N = 2^16 over batches of RNS limbs.
+//
+// Replaces the reference's four NTT kernels and their launchers:
+//   forward  ntt0/ntt1   cerium/compiler/backend/kernels/fhe_ntt.cuh:114-273,
+//                        cerium/compiler/backend/kernels/function.cu:22-99
+//   inverse  intt0/intt1 cerium/compiler/backend/kernels/fhe_ntt.cuh:470-601,
+//                        cerium/compiler/backend/kernels/function.cu:199-280
+//   SuD tail ntt1_sud    cerium/compiler/backend/kernels/fhe_ntt.cuh:278-359
+// Same contract (standard order in -> bit-reversed order out for the forward transform,
+// the inverse undoes it and scales by 1/N), different design:
+//
+//  * The 16 radix-2 layers are four radix-16 levels.  A level keeps 16 coefficients of one
+//    thread in registers; two levels make a pass, with one shared-memory exchange between
+//    them, so one limb crosses HBM twice per transform (once per pass) and the exchange
+//    never leaves the SM.
+//  * Twiddles are addressed through the "root prefix" S of a radix-16 group: layer t of the
+//    group uses table entries (S << t) + (j >> (4 - t)), j the register index.  Level 0 has
+//    S = 1, level 1 S = 16 + a, level 2 S = 256 + h, level 3 S = 4096 + 16 h + u.
+//    The 255 twiddles of the column pass are the same for every column and sit in shared
+//    memory; the row pass reads its twiddles in contiguous runs of 1, 2, 4, 8 entries.
+//  * The column pass moves 128-byte row segments (16 u64 / 32 u32 columns per CTA); the row
+//    pass gives each thread 16 consecutive coefficients and stores them as 16-byte vectors.
+//  * Values stay lazy inside a transform ([0,4q) forward, [0,2q) inverse) and are reduced to
+//    [0,q) by the last pass, so every buffer a caller sees is canonical.
+#pragma once
+#include "modarith.cuh"
+
+namespace cerium {
+
+template <typename W>
+struct NttCfg;
+template <>
+struct NttCfg<uint64_t> {
+  static constexpr int kCols = 16;  // 16 * 8 B = 128 B segments in the column pass
+};
+template <>
+struct NttCfg<uint32_t> {
+  static constexpr int kCols = 32;  // 32 * 4 B = 128 B
+};
+
+constexpr int kRowsPerCta = 16;    // row pass: 16 rows of 256 coefficients, 256 threads
+constexpr int kMaxBatch = 512;     // limbs per launch
+
+// Addressing of a batch of limbs: batch entry b lives at base + pos[b] * stride; its modulus
+// is prime[b] (index into the context's prime list).  Passed by value as a kernel parameter.
+// in_stride = 0 makes every entry read the same source limb (rescale broadcasts the last limb).
+template <typename W>
+struct StridedBatch {
+  const W* in;
+  W* out;
+  size_t in_stride;   // in words
+  size_t out_stride;  // in words
+  uint16_t pos[kMaxBatch];
+  uint8_t prime[kMaxBatch];
+  __device__ __forceinline__ const W* in_limb(int b) const { return in + (size_t)pos[b] * in_stride; }
+  __device__ __forceinline__ W* out_limb(int b) const { return out + (size_t)pos[b] * out_stride; }
+  __device__ __forceinline__ uint32_t prime_of(int b) const { return prime[b]; }
+};
+
+// Addressing through device-resident pointer tables, the layout the reference's launchers
+// take (args_outputs / args_inputs / bases, cerium/compiler/backend/kernels/function.cu:22-39).
+template <typename W>
+struct PointerBatch {
+  W* const* outs;
+  const W* const* ins;
+  const uint32_t* bases;
+  __device__ __forceinline__ const W* in_limb(int b) const { return ins[b]; }
+  __device__ __forceinline__ W* out_limb(int b) const { return outs[b]; }
+  __device__ __forceinline__ uint32_t prime_of(int b) const { return bases[b]; }
+};
+
+// ---------------------------------------------------------------------------------------
+// radix-16 register kernels
+// ---------------------------------------------------------------------------------------
+
+template <typename W, bool kGlobalTw>
+__device__ __forceinline__ typename WordTraits<W>::Pair load_tw(const typename WordTraits<W>::Pair* t,
+                                                                 uint32_t idx) {
+  if (kGlobalTw) return __ldg(t + idx);
+  return t[idx];
+}
+
+// Four forward layers on x[0..15]; layer t pairs (j, j + (8 >> t)).
+template <typename W, bool kGlobalTw>
+__device__ __forceinline__ void radix16_fwd(W (&x)[16], const typename WordTraits<W>::Pair* tw,
+                                            uint32_t S, W q, W q2) {
+#pragma unroll
+  for (int t = 0; t < 4; t++) {
+    const int half = 8 >> t;
+#pragma unroll
+    for (int g = 0; g < (1 << t); g++) {
+      const auto w = load_tw<W, kGlobalTw>(tw, (S << t) + g);
+#pragma unroll
+      for (int k = 0; k < half; k++) {
+        const int j = g * 2 * half + k;
+        butterfly_fwd<W>(x[j], x[j + half], w.x, w.y, q, q2);
+      }
+    }
+  }
+}
+
+// The four inverse layers of the same group, in reverse order.
+template <typename W, bool kGlobalTw>
+__device__ __forceinline__ void radix16_inv(W (&x)[16], const typename WordTraits<W>::Pair* twi,
+                                            uint32_t S, W q, W q2) {
+#pragma unroll
+  for (int t = 3; t >= 0; t--) {
+    const int half = 8 >> t;
+#pragma unroll
+    for (int g = 0; g < (1 << t); g++) {
+      const auto w = load_tw<W, kGlobalTw>(twi, (S << t) + g);
+#pragma unroll
+      for (int k = 0; k < half; k++) {
+        const int j = g * 2 * half + k;
+        butterfly_inv<W>(x[j], x[j + half], w.x, w.y, q, q2);
+      }
+    }
+  }
+}
+
+// Level 0 of the inverse transform (S = 1): the last layer also multiplies by N^-1 and
+// reduces to [0, q).
+template <typename W>
+__device__ __forceinline__ void radix16_inv_final(W (&x)[16], const typename WordTraits<W>::Pair* twi,
+                                                  const PrimeConst<W>& pc) {
+  const W q = pc.q, q2 = pc.q2;
+#pragma unroll
+  for (int t = 3; t >= 1; t--) {
+    const int half = 8 >> t;
+#pragma unroll
+    for (int g = 0; g < (1 << t); g++) {
+      const auto w = twi[(1u << t) + g];
+#pragma unroll
+      for (int k = 0; k < half; k++) {
+        const int j = g * 2 * half + k;
+        butterfly_inv<W>(x[j], x[j + half], w.x, w.y, q, q2);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const W s = x[j] + x[j + 8];         // < 4q
+    const W d = x[j] + q2 - x[j + 8];    // < 4q
+    x[j] = csub<W>(mul_shoup_lazy<W>(s, pc.ninv, pc.ninv_shoup, q), q);
+    x[j + 8] = csub<W>(mul_shoup_lazy<W>(d, pc.w1ninv, pc.w1ninv_shoup, q), q);
+  }
+}
+
+// Row-pass exchange buffer: one pad word after every 16 keeps both the strided and the
+// consecutive access pattern free of bank conflicts.
+__device__ __forceinline__ int row_pos(int i) { return i + (i >> 4); }
+constexpr int kRowPitch = 256 + 16;
+
+// ---------------------------------------------------------------------------------------
+// forward transform
+// ---------------------------------------------------------------------------------------
+
+// What the column pass does with a word it has just read.
+template <typename W>
+struct PlainLoader {
+  __device__ __forceinline__ W apply(W x, int /*b*/, const PrimeConst<W>& /*pc*/) const { return x; }
+};
+
+constexpr int kSudMaxBatch = 64;  // limbs per launch when per-limb scalars travel as parameters
+
+// Source residues belong to another (possibly larger) modulus src_q: optionally add pre_add
+// mod src_q (rounding), reduce into [0, q) of the target prime, optionally subtract
+// post_sub[b] mod q.  Used when one coefficient-form limb is re-read under many primes
+// (rescale, cerium/compiler/backend/compiler_rescale.cc:262-284).
+template <typename W>
+struct ReduceLoader {
+  W src_q;
+  W pre_add;
+  W post_sub[kSudMaxBatch];
+  __device__ __forceinline__ W apply(W x, int b, const PrimeConst<W>& pc) const {
+    W v = csub<W>(x + pre_add, src_q);
+    v = reduce_word<W>(v, pc);
+    return sub_mod<W>(v, post_sub[b], pc.q);
+  }
+};
+
+// Column pass (levels 0 and 1).  grid = (256 / kCols, limbs), block = 16 * kCols.
+// Element (h, l) of a limb is word h * 256 + l; the CTA owns kCols adjacent columns.
+template <typename W, typename Batch, typename Loader>
+__global__ void __launch_bounds__(NttCfg<W>::kCols * 16)
+    ntt_fwd_cols_kernel(const Batch batch, const Loader loader,
+                        const typename WordTraits<W>::Pair* __restrict__ tw_all,
+                        const PrimeConst<W>* __restrict__ pcs) {
+  using Pair = typename WordTraits<W>::Pair;
+  constexpr int kCols = NttCfg<W>::kCols;
+  __shared__ W tile[256 * kCols];
+  __shared__ Pair stw[256];
+  const int b = blockIdx.y;
+  const uint32_t pi = batch.prime_of(b);
+  const PrimeConst<W> pc = pcs[pi];
+  const W q = pc.q, q2 = pc.q2;
+  const Pair* tw = tw_all + (size_t)pi * kN;
+  const int tid = threadIdx.x, c = tid % kCols, u = tid / kCols;
+  const int col = blockIdx.x * kCols + c;
+  if (tid < 256) stw[tid] = __ldg(tw + tid);
+  const W* in = batch.in_limb(b);
+  W* out = batch.out_limb(b);
+  W x[16];
+#pragma unroll
+  for (int j = 0; j < 16; j++) x[j] = loader.apply(in[(j * 16 + u) * 256 + col], b, pc);
+  __syncthreads();
+  radix16_fwd<W, false>(x, stw, 1u, q, q2);
+#pragma unroll
+  for (int j = 0; j < 16; j++) tile[(j * 16 + u) * kCols + c] = x[j];
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 16; j++) x[j] = tile[(u * 16 + j) * kCols + c];
+  radix16_fwd<W, false>(x, stw, 16u + (uint32_t)u, q, q2);
+#pragma unroll
+  for (int j = 0; j < 16; j++) out[(u * 16 + j) * 256 + col] = x[j];
+}
+
+// What the row pass does with the finished (canonical) NTT value.
+template <typename W>
+struct StoreEpilogue {
+  __device__ __forceinline__ W apply(W x, int /*b*/, int /*idx*/, uint32_t /*pi*/,
+                                     const PrimeConst<W>& /*pc*/) const {
+    return x;
+  }
+};
+
+// SuD tail: out = (minuend - NTT(in)) * factor[b] [+ addend]   (all mod q).
+// minuend / addend are stacks of limbs: entry b at base + b * stride.
+template <typename W>
+struct SudEpilogue {
+  const W* minuend;
+  size_t minuend_stride;
+  const W* addend;  // may be null
+  size_t addend_stride;
+  W factor[kSudMaxBatch];
+  W factor_shoup[kSudMaxBatch];
+  __device__ __forceinline__ W apply(W x, int b, int idx, uint32_t /*pi*/,
+                                     const PrimeConst<W>& pc) const {
+    const W m = minuend[(size_t)b * minuend_stride + idx];
+    W d = sub_mod<W>(m, x, pc.q);
+    d = csub<W>(mul_shoup_lazy<W>(d, factor[b], factor_shoup[b], pc.q), pc.q);
+    if (addend != nullptr) d = add_mod<W>(d, addend[(size_t)b * addend_stride + idx], pc.q);
+    return d;
+  }
+};
+
+template <typename W>
+__device__ __forceinline__ void store16(W* dst, const W (&x)[16]);
+template <>
+__device__ __forceinline__ void store16<uint64_t>(uint64_t* dst, const uint64_t (&x)[16]) {
+  ulonglong2* d = reinterpret_cast<ulonglong2*>(dst);
+#pragma unroll
+  for (int j = 0; j < 8; j++) d[j] = make_ulonglong2(x[2 * j], x[2 * j + 1]);
+}
+template <>
+__device__ __forceinline__ void store16<uint32_t>(uint32_t* dst, const uint32_t (&x)[16]) {
+  uint4* d = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int j = 0; j < 4; j++) d[j] = make_uint4(x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
+}
+template <typename W>
+__device__ __forceinline__ void load16(const W* src, W (&x)[16]);
+template <>
+__device__ __forceinline__ void load16<uint64_t>(const uint64_t* src, uint64_t (&x)[16]) {
+  const ulonglong2* s = reinterpret_cast<const ulonglong2*>(src);
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const ulonglong2 v = s[j];
+    x[2 * j] = v.x;
+    x[2 * j + 1] = v.y;
+  }
+}
+template <>
+__device__ __forceinline__ void load16<uint32_t>(const uint32_t* src, uint32_t (&x)[16]) {
+  const uint4* s = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const uint4 v = s[j];
+    x[4 * j] = v.x;
+    x[4 * j + 1] = v.y;
+    x[4 * j + 2] = v.z;
+    x[4 * j + 3] = v.w;
+  }
+}
+
+// Row pass (levels 2 and 3): reads the column pass's result from the batch's `in` stack and
+// writes the finished transform to its `out` stack (the two may be the same buffer).
+// grid = (256 / kRowsPerCta, limbs), block = 16 * kRowsPerCta; 16 threads own one row.
+template <typename W, typename Batch, typename Epilogue>
+__global__ void __launch_bounds__(kRowsPerCta * 16)
+    ntt_fwd_rows_kernel(const Batch batch, const Epilogue epi,
+                        const typename WordTraits<W>::Pair* __restrict__ tw_all,
+                        const PrimeConst<W>* __restrict__ pcs) {
+  using Pair = typename WordTraits<W>::Pair;
+  __shared__ W tile[kRowsPerCta * kRowPitch];
+  const int b = blockIdx.y;
+  const uint32_t pi = batch.prime_of(b);
+  const PrimeConst<W> pc = pcs[pi];
+  const W q = pc.q, q2 = pc.q2;
+  const Pair* tw = tw_all + (size_t)pi * kN;
+  const int tid = threadIdx.x, r = tid >> 4, u = tid & 15;
+  const int h = blockIdx.x * kRowsPerCta + r;
+  const W* row = batch.in_limb(b) + h * 256;
+  W* drow = batch.out_limb(b) + h * 256;
+  W* trow = tile + r * kRowPitch;
+  W x[16];
+#pragma unroll
+  for (int j = 0; j < 16; j++) x[j] = row[j * 16 + u];
+  radix16_fwd<W, true>(x, tw, 256u + (uint32_t)h, q, q2);
+#pragma unroll
+  for (int j = 0; j < 16; j++) trow[row_pos(j * 16 + u)] = x[j];
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 16; j++) x[j] = trow[row_pos(u * 16 + j)];
+  radix16_fwd<W, true>(x, tw, (256u + (uint32_t)h) * 16u + (uint32_t)u, q, q2);
+#pragma unroll
+  for (int j = 0; j < 16; j++) {
+    const W v = csub<W>(csub<W>(x[j], q2), q);
+    x[j] = epi.apply(v, b, h * 256 + u * 16 + j, pi, pc);
+  }
+  store16<W>(drow + u * 16, x);
+}
+
+// ---------------------------------------------------------------------------------------
+// inverse transform
+// ---------------------------------------------------------------------------------------
+
+// Row pass (levels 3 and 2): in -> out, values in [0, 2q).
+template <typename W, typename Batch>
+__global__ void __launch_bounds__(kRowsPerCta * 16)
+    ntt_inv_rows_kernel(const Batch batch, const typename WordTraits<W>::Pair* __restrict__ twi_all,
+                        const PrimeConst<W>* __restrict__ pcs) {
+  using Pair = typename WordTraits<W>::Pair;
+  __shared__ W tile[kRowsPerCta * kRowPitch];
+  const int b = blockIdx.y;
+  const uint32_t pi = batch.prime_of(b);
+  const W q = pcs[pi].q, q2 = pcs[pi].q2;
+  const Pair* twi = twi_all + (size_t)pi * kN;
+  const int tid = threadIdx.x, r = tid >> 4, u = tid & 15;
+  const int h = blockIdx.x * kRowsPerCta + r;
+  const W* src = batch.in_limb(b) + h * 256;
+  W* dst = batch.out_limb(b) + h * 256;
+  W* trow = tile + r * kRowPitch;
+  W x[16];
+  load16<W>(src + u * 16, x);
+  radix16_inv<W, true>(x, twi, (256u + (uint32_t)h) * 16u + (uint32_t)u, q, q2);
+#pragma unroll
+  for (int j = 0; j < 16; j++) trow[row_pos(u * 16 + j)] = x[j];
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 16; j++) x[j] = trow[row_pos(j * 16 + u)];
+  radix16_inv<W, true>(x, twi, 256u + (uint32_t)h, q, q2);
+#pragma unroll
+  for (int j = 0; j < 16; j++) dst[j * 16 + u] = x[j];
+}
+
+// Optional per-limb scalar applied to the finished inverse transform (exact base
+// conversion wants x * [Qhat^-1] mod q; null = none).
+template <typename W>
+struct InvScale {
+  const W* scale;        // per batch entry, may be null
+  const W* scale_shoup;  // per batch entry
+};
+
+// Column pass (levels 1 and 0), in place on the output limb of the row pass; scales by
+// N^-1 and reduces to [0, q).
+template <typename W, typename Batch>
+__global__ void __launch_bounds__(NttCfg<W>::kCols * 16)
+    ntt_inv_cols_kernel(const Batch batch, const InvScale<W> sc,
+                        const typename WordTraits<W>::Pair* __restrict__ twi_all,
+                        const PrimeConst<W>* __restrict__ pcs) {
+  using Pair = typename WordTraits<W>::Pair;
+  constexpr int kCols = NttCfg<W>::kCols;
+  __shared__ W tile[256 * kCols];
+  __shared__ Pair stw[256];
+  const int b = blockIdx.y;
+  const uint32_t pi = batch.prime_of(b);
+  const PrimeConst<W> pc = pcs[pi];
+  const W q = pc.q, q2 = pc.q2;
+  const Pair* twi = twi_all + (size_t)pi * kN;
+  const int tid = threadIdx.x, c = tid % kCols, u = tid / kCols;
+  const int col = blockIdx.x * kCols + c;
+  if (tid < 256) stw[tid] = __ldg(twi + tid);
+  W* buf = batch.out_limb(b);
+  W x[16];
+#pragma unroll
+  for (int j = 0; j < 16; j++) x[j] = buf[(u * 16 + j) * 256 + col];
+  __syncthreads();
+  radix16_inv<W, false>(x, stw, 16u + (uint32_t)u, q, q2);
+#pragma unroll
+  for (int j = 0; j < 16; j++) tile[(u * 16 + j) * kCols + c] = x[j];
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 16; j++) x[j] = tile[(j * 16 + u) * kCols + c];
+  radix16_inv_final<W>(x, stw, pc);
+  if (sc.scale != nullptr) {
+    const W s = __ldg(sc.scale + b), ss = __ldg(sc.scale_shoup + b);
+#pragma unroll
+    for (int j = 0; j < 16; j++) x[j] = csub<W>(mul_shoup_lazy<W>(x[j], s, ss, q), q);
+  }
+#pragma unroll
+  for (int j = 0; j < 16; j++) buf[(j * 16 + u) * 256 + col] = x[j];
+}
+
+}  // namespace cerium

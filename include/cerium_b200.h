@@ -1,0 +1,213 @@
+/*
+ * cerium_b200 - C ABI of the B200-native RNS-CKKS evaluation core.
+ *
+ * This is the boundary a Cerium runtime binds instead of the per-program
+ * function_map_<p>.so it loads today (cerium/runtime/execution/function.cpp:144-177) and the
+ * execute_* shims behind it (cerium/runtime/execution/device_utils.h:29-150).  Every entry
+ * point is extern "C", takes plain pointers and sizes, returns a status code (no exceptions
+ * cross the boundary; the reference throws std::runtime_error from CHECK_CUDA_ERROR,
+ * cerium/compiler/backend/kernels/fhe.cuh:34-42) and enqueues work on the given CUDA stream
+ * without synchronising.  Nothing here allocates device memory except the *_create calls.
+ *
+ * Data model
+ *   - Ring degree N = 2^16 (fixed, as in cerium/compiler/backend/kernels/fhe_ntt.cuh:27).
+ *   - A "limb" is N residues of one RNS prime: uint32_t words (primes below 2^30; the
+ *     reference's 28-bit chain) or uint64_t words (primes below 2^60).  The word size is a
+ *     property of the context.
+ *   - A stack of limbs is addressed as base + i * stride (stride in WORDS); `prime_idx[i]`
+ *     names the modulus of limb i as an index into the context's prime list.  The *_ptrs
+ *     variants take device-resident pointer tables instead, the layout of the reference's
+ *     launchers (cerium/compiler/backend/kernels/function.cu:22-39).
+ *   - All residues that enter or leave a call are canonical, in [0, q).  (The reference's
+ *     32-bit Barrett may leave values in [q, 2q); compare modulo q.)
+ *   - NTT form is bit-reversed order with psi = the minimal primitive 2N-th root, i.e. the
+ *     order of cerium/runtime/math/ntt.cpp:118-125.
+ *   - Pointers must be 16-byte aligned and strides multiples of 16 bytes.
+ */
+#ifndef CERIUM_B200_H_
+#define CERIUM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CERIUM_OK 0
+#define CERIUM_ERR_INVALID 1     /* bad argument (null, size, alignment, unknown prime index) */
+#define CERIUM_ERR_CUDA 2        /* a CUDA runtime call failed; see cerium_last_error()        */
+#define CERIUM_ERR_UNSUPPORTED 3 /* parameter outside what the kernels are built for          */
+
+/* base-conversion semantics */
+#define CERIUM_BCONV_LAZY 0  /* Cerium: factors fold the CRT inverse (evaluator.cpp:1539-1578) */
+#define CERIUM_BCONV_EXACT 1 /* inputs are multiplied by [Qhat_i^-1] mod q_i first             */
+/* division semantics of ModDown / rescale */
+#define CERIUM_ROUND_FLOOR 0 /* Cerium: no rounding term (fhe_ntt.cuh:346-358)                 */
+#define CERIUM_ROUND_HALF 1  /* add floor(P/2) before dividing                                 */
+
+/* element-wise operations of cerium_ewise() */
+#define CERIUM_EW_ADD 0        /* out = a + b            */
+#define CERIUM_EW_SUB 1        /* out = a - b            */
+#define CERIUM_EW_NEG 2        /* out = -a               */
+#define CERIUM_EW_MUL 3        /* out = a * b            */
+#define CERIUM_EW_MAD 4        /* out = a * b + c        */
+#define CERIUM_EW_PMU 5        /* out = a + b * s[i]     */
+#define CERIUM_EW_MUL_SCALAR 6 /* out = a * s[i]         */
+
+typedef struct cerium_context cerium_context;
+typedef struct cerium_bconv cerium_bconv;
+typedef struct cerium_keyswitch cerium_keyswitch;
+
+/* Library version (major * 10000 + minor * 100 + patch). */
+int cerium_version(void);
+
+/* Message of the last failing call on this host thread ("" if none). */
+const char *cerium_last_error(void);
+
+/*
+ * Context: device tables for a list of primes (moduli, Barrett constants, forward and
+ * inverse twiddles with Shoup companions).  Replaces EvaluatorContext
+ * (cerium/runtime/execution/evaluator.h:94-136, evaluator.cpp:58-269).
+ * word_bits is 32 or 64; log_n must be 16; every modulus must be a prime = 1 mod 2N,
+ * below 2^30 (32-bit words) or 2^60 (64-bit words); at most 255 moduli.
+ */
+int cerium_context_create(cerium_context **out, int device, int log_n, int word_bits,
+                          const uint64_t *moduli, int n_moduli);
+int cerium_context_destroy(cerium_context *ctx);
+int cerium_context_word_bits(const cerium_context *ctx);
+int cerium_context_num_moduli(const cerium_context *ctx);
+uint64_t cerium_context_modulus(const cerium_context *ctx, int k);
+uint64_t cerium_context_root(const cerium_context *ctx, int k); /* psi of prime k */
+
+/*
+ * Forward / inverse negacyclic NTT of `count` limbs.  in == out is allowed.
+ * Replaces _function_ntt_ / _function_int_ (cerium/compiler/backend/kernels/function.cu:
+ * 58-72, 237-256) and Evaluator::fn_ntt / fn_int
+ * (cerium/runtime/execution/evaluator.cpp:444-463, 540-551).
+ */
+int cerium_ntt_forward(cerium_context *ctx, void *out, size_t out_stride, const void *in,
+                       size_t in_stride, const uint32_t *prime_idx, int count, void *stream);
+int cerium_ntt_inverse(cerium_context *ctx, void *out, size_t out_stride, const void *in,
+                       size_t in_stride, const uint32_t *prime_idx, int count, void *stream);
+
+/*
+ * The same with the reference launchers' argument layout: outs/ins are DEVICE arrays of
+ * `num_bases` limb pointers, bases a DEVICE array of prime indices
+ * (cerium/runtime/execution/device_utils.h:42-53).
+ */
+int cerium_ntt_forward_ptrs(cerium_context *ctx, void *const *outs, const void *const *ins,
+                            const uint32_t *bases, size_t num_bases, void *stream);
+int cerium_ntt_inverse_ptrs(cerium_context *ctx, void *const *outs, const void *const *ins,
+                            const uint32_t *bases, size_t num_bases, void *stream);
+
+/*
+ * SuD: out[i] = (minuend[i] - NTT(in_coeff[i])) * [(prod divide primes)^-1] mod q_i,
+ * optionally + addend[i] (addend may be NULL).  in_coeff holds coefficient-form residues
+ * already reduced mod q_i.  out may alias minuend; in_coeff is overwritten (it is the
+ * transform's work buffer).  Replaces _function_sud_
+ * (cerium/compiler/backend/kernels/function.cu:151-169) and compute_sud_factors
+ * (cerium/runtime/execution/function.cpp:685-732).
+ */
+int cerium_sud(cerium_context *ctx, void *out, size_t out_stride, const void *minuend,
+               size_t minuend_stride, void *in_coeff, size_t in_stride, const void *addend,
+               size_t addend_stride, const uint32_t *prime_idx, int count,
+               const uint32_t *divide_primes, int n_divide, void *stream);
+
+/*
+ * Element-wise modular arithmetic over `count` limbs (op = CERIUM_EW_*).  Unused operands
+ * may be NULL.  `scalars` (host array, one canonical residue per limb) feeds PMU and
+ * MUL_SCALAR.  Replaces the generated generic and PMU kernels
+ * (cerium/compiler/backend/cuda_kernel.cc:1142-1280, 2669-2765) and Evaluator::fn_ewi
+ * (cerium/runtime/execution/evaluator.cpp:279-463).
+ */
+int cerium_ewise(cerium_context *ctx, int op, void *out, size_t out_stride, const void *a,
+                 size_t a_stride, const void *b, size_t b_stride, const void *c, size_t c_stride,
+                 const uint64_t *scalars, const uint32_t *prime_idx, int count, void *stream);
+
+/*
+ * Ciphertext tensor product d0 = a0*b0, d1 = a0*b1 + a1*b0, d2 = a1*b1 over `count` limbs
+ * (all seven stacks share `stride`).  Restates mul_ct_ct
+ * (cerium/compiler/backend/compiler.cc:443-467) as one kernel.
+ */
+int cerium_tensor(cerium_context *ctx, void *d0, void *d1, void *d2, const void *a0,
+                  const void *a1, const void *b0, const void *b1, size_t stride,
+                  const uint32_t *prime_idx, int count, void *stream);
+
+/*
+ * Galois automorphism in NTT form: out[i][k] = in[i][pi(k)] for `count` limbs, pi as built by
+ * GaloisTool::generate_table_ntt (cerium/runtime/math/galois.cpp:30-62).  in and out must not
+ * overlap.  cerium_galois_elt_from_step restates get_elt_from_step (galois.cpp:79-113):
+ * step 0 is conjugation.  Replaces the ROT_WRITE path of the generated kernels
+ * (cerium/compiler/backend/cuda_kernel.cc:228-300) and
+ * EvaluatorContext::get_rotation_map_ptr (evaluator.cpp:233-260); no table is uploaded.
+ */
+uint32_t cerium_galois_elt_from_step(int step, int log_n);
+int cerium_automorph(cerium_context *ctx, void *out, size_t out_stride, const void *in,
+                     size_t in_stride, uint32_t galois_elt, int count, void *stream);
+
+/*
+ * Base converter from the primes in_primes[0..n_in) to out_primes[0..n_out).
+ * Replaces DeviceBaseConverter (cerium/runtime/execution/evaluator.h:30-92,
+ * evaluator.cpp:1483-1608) and _function_bco_ (cerium/compiler/backend/kernels/function.cuh:
+ * 80-99).  Input limbs are in coefficient form.
+ */
+int cerium_bconv_create(cerium_context *ctx, cerium_bconv **out, int mode,
+                        const uint32_t *in_primes, int n_in, const uint32_t *out_primes, int n_out);
+int cerium_bconv_destroy(cerium_bconv *bc);
+int cerium_bconv_apply(cerium_bconv *bc, void *out, size_t out_stride, const void *in,
+                       size_t in_stride, void *stream);
+
+/*
+ * Hybrid key-switching plan for ciphertexts over q_idx[0..L) with extension primes
+ * p_idx[0..K) and dnum digits (limb i belongs to digit i % dnum, the stride split of
+ * cerium/compiler/backend/compiler_keyswitch.cc:68-99).  Holds the per-digit converters,
+ * P^-1 mod q_i and a device workspace of cerium_keyswitch_workspace_bytes().
+ * An evaluation key is dnum x 2 x (L+K) limbs, [digit][c0|c1][q_idx..., p_idx...][N]
+ * (cerium/runtime/io/ckks-encryptor.cpp:534-599).
+ */
+int cerium_keyswitch_create(cerium_context *ctx, cerium_keyswitch **out, int bconv_mode,
+                            int round_mode, const uint32_t *q_idx, int L, const uint32_t *p_idx,
+                            int K, int dnum);
+int cerium_keyswitch_destroy(cerium_keyswitch *ks);
+size_t cerium_keyswitch_workspace_bytes(const cerium_keyswitch *ks);
+
+/*
+ * out0,out1 [L][N] = ModDown( sum_d ModUp(digit d of cpoly) * evk[d] ); if add0 / add1 are
+ * non-NULL they are added to out0 / out1 (the P*c0 pre-addition of the reference's PMU
+ * group, which commutes with ModDown).  Restates keyswitch_ciphertext_impl
+ * (cerium/compiler/backend/compiler_keyswitch.cc:253-432): INTT, BCONV, NTT, EVKMUL,
+ * INTT, BCONV, SUD.  All stacks are contiguous ([limb][N], stride N).
+ */
+int cerium_keyswitch_apply(cerium_keyswitch *ks, void *out0, void *out1, const void *cpoly,
+                           const void *evk, const void *add0, const void *add1, void *stream);
+
+/*
+ * HRot: (out0,out1) = KeySwitch(phi(c1)) + (phi(c0), 0), phi the automorphism galois_elt.
+ * Restates rotate_internal (cerium/compiler/backend/compiler.cc:701-726).
+ */
+int cerium_hrot(cerium_keyswitch *ks, void *out0, void *out1, const void *c0, const void *c1,
+                const void *evk, uint32_t galois_elt, void *stream);
+
+/*
+ * HMult + relinearize (+ rescale by the last limb when do_rescale != 0): tensor product,
+ * key switch of d2, addition of d0/d1 (cerium/compiler/backend/compiler.cc:443-467,
+ * compiler_keyswitch.cc:360-380) and rescale (compiler_rescale.cc:209-284).  Outputs hold
+ * L limbs, or L-1 with rescale.
+ */
+int cerium_hmult(cerium_keyswitch *ks, void *out0, void *out1, const void *a0, const void *a1,
+                 const void *b0, const void *b1, const void *evk, int do_rescale, void *stream);
+
+/*
+ * Rescale `n_polys` polynomials of L limbs each ([poly][limb][N] contiguous) by their last
+ * limb: out [poly][L-1][N].  `scratch` is a caller-owned device buffer of n_polys * N words.
+ * Restates rescale (cerium/compiler/backend/compiler_rescale.cc:209-284): INTT of the last
+ * limb, SuD on the others.
+ */
+int cerium_rescale(cerium_context *ctx, int round_mode, void *out, const void *in,
+                   const uint32_t *q_idx, int L, int n_polys, void *scratch, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CERIUM_B200_H_ */

@@ -1,0 +1,89 @@
+// Host stand-ins for the CUDA built-ins and the few runtime calls the library uses, so that
+// the kernel sources and the host glue compile with g++ and run on the CPU.  TEST
+// INFRASTRUCTURE ONLY: it exists to check index arithmetic, barrier placement and host
+// orchestration on a machine without a GPU.  The shipped library is never built with
+// CERIUM_EMU and has no CPU path.
+//
+// Execution model: a launch runs its thread blocks one after another (spread over OpenMP
+// threads); the threads of a block are ucontext fibers on one OS thread, scheduled round
+// robin, and __syncthreads() yields to the next fiber.  Because every fiber runs to its next
+// barrier before any fiber continues, barriers that all threads of a block reach (the only
+// kind the kernels use) behave as on the device.  __shared__ variables become
+// static thread_local, i.e. one copy per OS thread = per running block.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cstdlib>
+#include <cstring>
+#include <functional>
+
+struct uint2 { unsigned x, y; };
+struct uint3 { unsigned x, y, z; };
+struct alignas(16) uint4 { unsigned x, y, z, w; };
+struct alignas(16) ulonglong2 { unsigned long long x, y; };
+struct dim3 {
+  unsigned x, y, z;
+  dim3(unsigned x_ = 1, unsigned y_ = 1, unsigned z_ = 1) : x(x_), y(y_), z(z_) {}
+};
+static inline uint2 make_uint2(unsigned a, unsigned b) { return uint2{a, b}; }
+static inline uint4 make_uint4(unsigned a, unsigned b, unsigned c, unsigned d) { return uint4{a, b, c, d}; }
+static inline ulonglong2 make_ulonglong2(unsigned long long a, unsigned long long b) { return ulonglong2{a, b}; }
+
+#define __global__
+#define __device__
+#define __host__
+#define __forceinline__ inline
+#define __launch_bounds__(...)
+#define __restrict__
+#define __shared__ static thread_local
+#define __align__(n) alignas(n)
+
+namespace cerium_emu {
+extern thread_local uint3 t_threadIdx, t_blockIdx;
+extern thread_local dim3 t_blockDim, t_gridDim;
+unsigned char* dyn_smem();
+void sync_threads();
+void launch(dim3 grid, dim3 block, size_t smem_bytes, const std::function<void()>& body);
+long launches();  // number of launches so far (tests use it to see that kernels ran)
+}  // namespace cerium_emu
+
+#define threadIdx (::cerium_emu::t_threadIdx)
+#define blockIdx (::cerium_emu::t_blockIdx)
+#define blockDim (::cerium_emu::t_blockDim)
+#define gridDim (::cerium_emu::t_gridDim)
+
+static inline void __syncthreads() { ::cerium_emu::sync_threads(); }
+static inline void __syncwarp() { ::cerium_emu::sync_threads(); }
+static inline unsigned __umulhi(unsigned a, unsigned b) { return (unsigned)(((uint64_t)a * b) >> 32); }
+static inline unsigned long long __umul64hi(unsigned long long a, unsigned long long b) {
+  return (unsigned long long)(((unsigned __int128)a * b) >> 64);
+}
+static inline unsigned __brev(unsigned x) {
+  unsigned r = 0;
+  for (int i = 0; i < 32; i++) { r = (r << 1) | (x & 1); x >>= 1; }
+  return r;
+}
+template <typename T>
+static inline T __ldg(const T* p) { return *p; }
+
+// ---- runtime API subset ----
+typedef int cudaError_t;
+typedef void* cudaStream_t;
+enum { cudaSuccess = 0, cudaErrorMemoryAllocation = 2 };
+enum cudaMemcpyKind { cudaMemcpyHostToDevice = 1, cudaMemcpyDeviceToHost = 2, cudaMemcpyDeviceToDevice = 3 };
+enum cudaFuncAttribute { cudaFuncAttributeMaxDynamicSharedMemorySize = 8 };
+static inline cudaError_t cudaMalloc(void** p, size_t n) {
+  *p = std::aligned_alloc(256, (n + 255) / 256 * 256);
+  return *p ? cudaSuccess : cudaErrorMemoryAllocation;
+}
+template <typename T>
+static inline cudaError_t cudaMalloc(T** p, size_t n) { return cudaMalloc(reinterpret_cast<void**>(p), n); }
+static inline cudaError_t cudaFree(void* p) { std::free(p); return cudaSuccess; }
+static inline cudaError_t cudaMemcpy(void* d, const void* s, size_t n, cudaMemcpyKind) { std::memcpy(d, s, n); return cudaSuccess; }
+static inline cudaError_t cudaGetDeviceCount(int* n) { *n = 1; return cudaSuccess; }
+static inline cudaError_t cudaGetDevice(int* d) { *d = 0; return cudaSuccess; }
+static inline cudaError_t cudaSetDevice(int) { return cudaSuccess; }
+static inline cudaError_t cudaGetLastError() { return cudaSuccess; }
+static inline const char* cudaGetErrorString(cudaError_t) { return "emulated"; }
+template <typename F>
+static inline cudaError_t cudaFuncSetAttribute(F, cudaFuncAttribute, int) { return cudaSuccess; }

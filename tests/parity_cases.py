@@ -1,0 +1,329 @@
+"""Parity cases: the C ABI against the CPU oracle on the same seeded inputs.
+
+Every case takes a backend (tests/backends.py) so that it runs both on the emulation build
+(no GPU; checks index arithmetic and host orchestration) and on the CUDA build (the parity
+tests proper).  Comparison is bit-exact: all residues are canonical on both sides.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+import oracle
+from cerium_b200 import _capi, params
+
+LOGN = 16
+N = 1 << LOGN
+
+
+def wdtype(word_bits):
+    return np.uint64 if word_bits == 64 else np.uint32
+
+
+def moduli_for(word_bits, count, sixty=0):
+    """`count` primes for the word size; for 64-bit the first `sixty` are 60-bit, the rest 50-bit."""
+    if word_bits == 32:
+        return params.reference_primes_28bit(count, LOGN)
+    return params.ntt_primes_below(60, sixty, LOGN) + params.ntt_primes_below(50, count - sixty, LOGN)
+
+
+def rand_limbs(rng, moduli, prime_idx, extra=()):
+    """[len(prime_idx)] + extra + [N] uniform residues below each limb's modulus (uint64)."""
+    rows = [rng.integers(0, moduli[p], size=tuple(extra) + (N,), dtype=np.uint64) for p in prime_idx]
+    return np.stack(rows)
+
+
+def edge_limbs(moduli, prime_idx):
+    """Extreme residues: 0, 1, q-1 patterns."""
+    rows = []
+    for k, p in enumerate(prime_idx):
+        q = moduli[p]
+        r = np.zeros(N, dtype=np.uint64)
+        if k % 3 == 0:
+            r[:] = q - 1
+        elif k % 3 == 1:
+            r[::2] = q - 1
+            r[1::2] = 1
+        rows.append(r)
+    return np.stack(rows)
+
+
+class Harness:
+    def __init__(self, backend, word_bits, moduli):
+        self.be = backend
+        self.word_bits = word_bits
+        self.moduli = list(moduli)
+        self.dt = wdtype(word_bits)
+        self.ctx = _capi.Context(backend.lib, moduli, word_bits)
+        self.orc = oracle.OracleContext(LOGN, moduli)
+
+    def up(self, a):
+        return self.be.to_dev(np.ascontiguousarray(a).astype(self.dt))
+
+    def down(self, buf):
+        return self.be.to_host(buf).astype(np.uint64)
+
+    def new(self, *shape):
+        return self.be.empty(shape, self.dt)
+
+    def p(self, buf):
+        return self.be.ptr(buf)
+
+
+# ---------------------------------------------------------------------------------------
+
+def case_ntt(be, word_bits, n_limbs=3, sixty=1):
+    mods = moduli_for(word_bits, n_limbs, sixty)
+    h = Harness(be, word_bits, mods)
+    rng = np.random.default_rng(100 + word_bits)
+    idx = list(range(n_limbs)) + [0]
+    x = rand_limbs(rng, mods, idx)
+    x[-1] = edge_limbs(mods, [0])[0]
+    want = h.orc.ntt_forward(x, idx)
+    d_in = h.up(x)
+    d_out = h.new(len(idx), N)
+    h.ctx.ntt_forward(h.p(d_out), h.p(d_in), idx)
+    got = h.down(d_out)
+    assert np.array_equal(got, want), "forward NTT differs from the oracle"
+    assert np.array_equal(h.down(d_in), x), "out-of-place forward NTT modified its input"
+    # inverse, out of place then in place
+    d_back = h.new(len(idx), N)
+    h.ctx.ntt_inverse(h.p(d_back), h.p(d_out), idx)
+    assert np.array_equal(h.down(d_back), x), "inverse NTT does not undo the forward NTT"
+    h.ctx.ntt_forward(h.p(d_in), h.p(d_in), idx)
+    assert np.array_equal(h.down(d_in), want), "in-place forward NTT differs"
+    h.ctx.ntt_inverse(h.p(d_in), h.p(d_in), idx)
+    assert np.array_equal(h.down(d_in), x), "in-place inverse NTT differs"
+    # inverse against the oracle on arbitrary NTT-domain data
+    y = rand_limbs(rng, mods, idx)
+    d_y = h.up(y)
+    h.ctx.ntt_inverse(h.p(d_y), h.p(d_y), idx)
+    assert np.array_equal(h.down(d_y), h.orc.ntt_inverse(y, idx)), "inverse NTT differs from the oracle"
+    # empty batch is a no-op
+    h.ctx.ntt_forward(h.p(d_y), h.p(d_y), [])
+
+
+def case_ntt_ptrs(be, word_bits):
+    """Pointer-table entry points (the reference launchers' layout), ragged limb placement."""
+    mods = moduli_for(word_bits, 2, 0)
+    h = Harness(be, word_bits, mods)
+    rng = np.random.default_rng(7)
+    idx = [1, 0, 1]
+    x = rand_limbs(rng, mods, idx)
+    pool = h.new(8, N)          # limbs scattered inside a larger pool
+    host_pool = np.zeros((8, N), dtype=np.uint64)
+    in_slots, out_slots = [6, 0, 3], [1, 7, 4]
+    for s, row in zip(in_slots, x):
+        host_pool[s] = row
+    pool = h.up(host_pool)
+    base = h.p(pool)
+    limb_bytes = N * h.ctx.word_bytes
+    ins = be.to_dev(np.array([base + s * limb_bytes for s in in_slots], dtype=np.uint64))
+    outs = be.to_dev(np.array([base + s * limb_bytes for s in out_slots], dtype=np.uint64))
+    bases = be.to_dev(np.array(idx, dtype=np.uint32))
+    h.ctx.ntt_forward_ptrs(be.ptr(outs), be.ptr(ins), be.ptr(bases), 3)
+    got = h.down(pool)
+    want = h.orc.ntt_forward(x, idx)
+    for s, row in zip(out_slots, want):
+        assert np.array_equal(got[s], row)
+    # inverse back into the input slots
+    h.ctx.ntt_inverse_ptrs(be.ptr(ins), be.ptr(outs), be.ptr(bases), 3)
+    got = h.down(pool)
+    for s, row in zip(in_slots, x):
+        assert np.array_equal(got[s], row)
+
+
+def case_ewise(be, word_bits):
+    mods = moduli_for(word_bits, 3, 1)
+    h = Harness(be, word_bits, mods)
+    rng = np.random.default_rng(8)
+    idx = [2, 0, 1, 0]
+    a, b, c = (rand_limbs(rng, mods, idx) for _ in range(3))
+    a[3] = edge_limbs(mods, [0])[0]
+    b[3] = edge_limbs(mods, [0])[0]
+    da, db, dc = h.up(a), h.up(b), h.up(c)
+    out = h.new(len(idx), N)
+    scal = [int(rng.integers(0, mods[p])) for p in idx]
+
+    def expect(op, **kw):
+        return np.stack([oracle.ew(op, mods[p], *[arr[i] for arr in kw["arrs"]], scalar=kw.get("scalars", [None] * 9)[i])
+                         for i, p in enumerate(idx)])
+
+    h.ctx.ewise(_capi.EW_ADD, h.p(out), h.p(da), idx, b=h.p(db))
+    assert np.array_equal(h.down(out), expect("add", arrs=(a, b)))
+    h.ctx.ewise(_capi.EW_SUB, h.p(out), h.p(da), idx, b=h.p(db))
+    assert np.array_equal(h.down(out), expect("sub", arrs=(a, b)))
+    h.ctx.ewise(_capi.EW_NEG, h.p(out), h.p(da), idx)
+    assert np.array_equal(h.down(out), expect("neg", arrs=(a,)))
+    h.ctx.ewise(_capi.EW_MUL, h.p(out), h.p(da), idx, b=h.p(db))
+    assert np.array_equal(h.down(out), expect("mul", arrs=(a, b)))
+    h.ctx.ewise(_capi.EW_MAD, h.p(out), h.p(da), idx, b=h.p(db), c=h.p(dc))
+    assert np.array_equal(h.down(out), expect("mad", arrs=(a, b, c)))
+    h.ctx.ewise(_capi.EW_PMU, h.p(out), h.p(da), idx, b=h.p(db), scalars=scal)
+    assert np.array_equal(h.down(out), expect("pmu", arrs=(a, b), scalars=scal))
+    h.ctx.ewise(_capi.EW_MUL_SCALAR, h.p(out), h.p(da), idx, scalars=scal)
+    want = np.stack([oracle.ew("mul", mods[p], a[i], np.full(N, scal[i], dtype=np.uint64)) for i, p in enumerate(idx)])
+    assert np.array_equal(h.down(out), want)
+    # tensor product
+    a1, b1 = rand_limbs(rng, mods, idx), rand_limbs(rng, mods, idx)
+    d0, d1, d2 = h.new(len(idx), N), h.new(len(idx), N), h.new(len(idx), N)
+    da1, db1 = h.up(a1), h.up(b1)
+    h.ctx.tensor(h.p(d0), h.p(d1), h.p(d2), h.p(da), h.p(da1), h.p(db), h.p(db1), idx)
+    assert np.array_equal(h.down(d0), expect("mul", arrs=(a, b)))
+    assert np.array_equal(h.down(d2), expect("mul", arrs=(a1, b1)))
+    w = np.stack([oracle.ew("mad", mods[p], a[i], b1[i], oracle.ew("mul", mods[p], a1[i], b[i])) for i, p in enumerate(idx)])
+    assert np.array_equal(h.down(d1), w)
+
+
+def case_automorph(be, word_bits):
+    mods = moduli_for(word_bits, 2, 0)
+    h = Harness(be, word_bits, mods)
+    rng = np.random.default_rng(9)
+    idx = [0, 1]
+    x = rand_limbs(rng, mods, idx)
+    dx = h.up(x)
+    out = h.new(2, N)
+    for step in (0, 1, 7, -3, 12345, -(N // 2 - 1)):
+        elt = be.lib.galois_elt_from_step(step, LOGN)
+        assert elt == oracle.galois_elt_from_step(step, LOGN)
+        h.ctx.automorph(h.p(out), h.p(dx), elt, 2)
+        want = np.stack([oracle.apply_galois_ntt(elt, LOGN, x[i]) for i in range(2)])
+        assert np.array_equal(h.down(out), want), "automorphism differs for step %d" % step
+    assert be.lib.galois_elt_from_step(N // 2, LOGN) == 0  # step count too large
+
+
+def case_bconv(be, word_bits, n_in, n_out, mode):
+    mods = moduli_for(word_bits, n_in + n_out, min(2, n_in))
+    h = Harness(be, word_bits, mods)
+    rng = np.random.default_rng(10 + n_in)
+    in_idx = list(range(n_in))
+    out_idx = list(range(n_in, n_in + n_out))
+    x = rand_limbs(rng, mods, in_idx)
+    x[0, :8] = mods[0] - 1
+    dx = h.up(x)
+    out = h.new(n_out, N)
+    bc = _capi.BaseConverter(h.ctx, in_idx, out_idx, mode)
+    bc.apply(h.p(out), h.p(dx))
+    want = oracle.bconv(mode, [mods[i] for i in in_idx], x, [mods[j] for j in out_idx])
+    assert np.array_equal(h.down(out), want), "base conversion differs (mode %d, %d -> %d)" % (mode, n_in, n_out)
+    bc.close()
+
+
+def case_sud(be, word_bits):
+    mods = moduli_for(word_bits, 5, 1)
+    h = Harness(be, word_bits, mods)
+    rng = np.random.default_rng(11)
+    idx = [0, 1, 2]
+    div = [3, 4]
+    minuend = rand_limbs(rng, mods, idx)
+    coeff = rand_limbs(rng, mods, idx)
+    addend = rand_limbs(rng, mods, idx)
+    want = []
+    for i, p in enumerate(idx):
+        q = mods[p]
+        f = pow(mods[3] * mods[4] % q, -1, q)
+        want.append(h.orc.sud(p, minuend[i], coeff[i], f))
+    want = np.stack(want)
+    dm, dc, da = h.up(minuend), h.up(coeff), h.up(addend)
+    out = h.new(3, N)
+    h.ctx.sud(h.p(out), h.p(dm), h.p(dc), idx, div)
+    assert np.array_equal(h.down(out), want)
+    dc = h.up(coeff)
+    h.ctx.sud(h.p(dm), h.p(dm), h.p(dc), idx, div, addend=h.p(da))  # in place on the minuend, with addend
+    want2 = np.stack([oracle.ew("add", mods[p], want[i], addend[i]) for i, p in enumerate(idx)])
+    assert np.array_equal(h.down(dm), want2)
+
+
+def case_rescale(be, word_bits, round_mode, L=4, n_polys=2):
+    mods = moduli_for(word_bits, L, 1)
+    if word_bits == 64:
+        mods = mods[1:] + mods[:1]   # 60-bit prime last: the dropped limb is wider than the rest
+    h = Harness(be, word_bits, mods)
+    rng = np.random.default_rng(12)
+    q_idx = list(range(L))
+    x = np.stack([rand_limbs(rng, mods, q_idx) for _ in range(n_polys)])
+    dx = h.up(x)
+    out = h.new(n_polys, L - 1, N)
+    scratch = h.new(n_polys, N)
+    h.ctx.rescale(h.p(out), h.p(dx), q_idx, n_polys, h.p(scratch), round_mode)
+    want = np.stack([h.orc.rescale(round_mode, q_idx, x[p]) for p in range(n_polys)])
+    assert np.array_equal(h.down(out), want)
+
+
+def make_keyswitch_inputs(rng, prm: params.CkksParams):
+    all_idx = prm.q_idx + prm.p_idx
+    c0 = rand_limbs(rng, prm.moduli, prm.q_idx)
+    c1 = rand_limbs(rng, prm.moduli, prm.q_idx)
+    evk = np.stack([np.stack([rand_limbs(rng, prm.moduli, all_idx) for _ in range(2)]) for _ in range(prm.dnum)])
+    return c0, c1, evk
+
+
+def small_params(word_bits, L, K, dnum):
+    if word_bits == 32:
+        return params.config_ref28(LOGN, L, K, dnum, total=L + K)
+    q = params.ntt_primes_below(60, 1, LOGN) + params.ntt_primes_below(50, L - 1, LOGN)
+    p = params.ntt_primes_below(60, K + 1, LOGN)[1:]
+    return params.CkksParams(LOGN, 64, q + p[::-1], L, K, dnum)
+
+
+def case_keyswitch(be, word_bits, L, K, dnum, bconv_mode, round_mode):
+    prm = small_params(word_bits, L, K, dnum)
+    h = Harness(be, word_bits, prm.moduli)
+    rng = np.random.default_rng(13)
+    c0, c1, evk = make_keyswitch_inputs(rng, prm)
+    ks = _capi.KeySwitch(h.ctx, prm.q_idx, prm.p_idx, dnum, bconv_mode, round_mode)
+    assert ks.workspace_bytes > 0
+    d_c1, d_evk = h.up(c1), h.up(evk)
+    o0, o1 = h.new(L, N), h.new(L, N)
+    ks.apply(h.p(o0), h.p(o1), h.p(d_c1), h.p(d_evk))
+    w0, w1 = h.orc.keyswitch(bconv_mode, round_mode, prm.q_idx, prm.p_idx, dnum, c1, evk)
+    assert np.array_equal(h.down(o0), w0), "key switch c0 differs"
+    assert np.array_equal(h.down(o1), w1), "key switch c1 differs"
+    # HRot
+    elt = be.lib.galois_elt_from_step(5, LOGN)
+    d_c0 = h.up(c0)
+    ks.hrot(h.p(o0), h.p(o1), h.p(d_c0), h.p(d_c1), h.p(d_evk), elt)
+    w0, w1 = h.orc.hrot(bconv_mode, round_mode, prm.q_idx, prm.p_idx, dnum, elt, c0, c1, evk)
+    assert np.array_equal(h.down(o0), w0), "HRot c0 differs"
+    assert np.array_equal(h.down(o1), w1), "HRot c1 differs"
+    # HMult + relinearise, with and without rescale
+    b0, b1 = rand_limbs(rng, prm.moduli, prm.q_idx), rand_limbs(rng, prm.moduli, prm.q_idx)
+    d_b0, d_b1 = h.up(b0), h.up(b1)
+    ks.hmult(h.p(o0), h.p(o1), h.p(d_c0), h.p(d_c1), h.p(d_b0), h.p(d_b1), h.p(d_evk), False)
+    w0, w1 = h.orc.hmult_relin(bconv_mode, round_mode, False, prm.q_idx, prm.p_idx, dnum, c0, c1, b0, b1, evk)
+    assert np.array_equal(h.down(o0), w0) and np.array_equal(h.down(o1), w1), "HMult differs"
+    if L >= 2:
+        r0, r1 = h.new(L - 1, N), h.new(L - 1, N)
+        ks.hmult(h.p(r0), h.p(r1), h.p(d_c0), h.p(d_c1), h.p(d_b0), h.p(d_b1), h.p(d_evk), True)
+        w0, w1 = h.orc.hmult_relin(bconv_mode, round_mode, True, prm.q_idx, prm.p_idx, dnum, c0, c1, b0, b1, evk)
+        assert np.array_equal(h.down(r0), w0) and np.array_equal(h.down(r1), w1), "HMult+rescale differs"
+    ks.close()
+
+
+def case_errors(be, word_bits=64):
+    """Error behaviour of the boundary: status codes and messages instead of exceptions or faults."""
+    import pytest
+    mods = moduli_for(word_bits, 2, 0)
+    with pytest.raises(_capi.CeriumError) as e:
+        _capi.Context(be.lib, [mods[0], mods[0]], word_bits)
+    assert e.value.code == _capi.ERR_INVALID
+    with pytest.raises(_capi.CeriumError):
+        _capi.Context(be.lib, [mods[0] + 2], word_bits)          # not prime / not 1 mod 2N
+    with pytest.raises(_capi.CeriumError) as e:
+        _capi.Context(be.lib, mods, word_bits, logn=15)
+    assert e.value.code == _capi.ERR_UNSUPPORTED
+    h = Harness(be, word_bits, mods)
+    buf = h.new(2, N)
+    with pytest.raises(_capi.CeriumError):
+        h.ctx.ntt_forward(h.p(buf), h.p(buf), [0, 5])             # unknown prime index
+    with pytest.raises(_capi.CeriumError):
+        h.ctx.ntt_forward(0, h.p(buf), [0])                       # null pointer
+    with pytest.raises(_capi.CeriumError):
+        h.ctx.ntt_forward(h.p(buf) + 8, h.p(buf), [0])            # misaligned
+    with pytest.raises(_capi.CeriumError):
+        h.ctx.automorph(h.p(buf), h.p(buf), 5, 1)                 # aliasing
+    with pytest.raises(_capi.CeriumError):
+        h.ctx.automorph(h.p(buf), h.p(buf) + N * h.ctx.word_bytes, 4, 1)  # even Galois element
+    with pytest.raises(_capi.CeriumError):
+        _capi.KeySwitch(h.ctx, [0, 1], [1], 1)                    # prime used twice
+    with pytest.raises(_capi.CeriumError):
+        _capi.KeySwitch(h.ctx, [0], [1], 2)                       # dnum > L
