@@ -1,0 +1,504 @@
+#!/usr/bin/env python
+"""Benchmark of the RNS-CKKS evaluation hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload hrot|hmult|ntt] [--impl reference]
+
+One "step" is one pass of the hot path over one batch of synthetic, seeded input that is
+already resident in HBM:
+  hrot   one homomorphic rotation with hybrid key switching, N=2^16, L=35 primes of 50 bits,
+         K=5 extension primes of 60 bits, dnum=7 (uniform ciphertext limbs and key limbs);
+         metric: key-switch ops/s                                            [default]
+  hmult  one HMult + relinearise + rescale, L=24 (60-bit first prime, 50-bit rest), K=1, dnum=24
+  ntt    forward + inverse NTT of 48 limbs x 8 polynomials of 50-bit primes
+With N > 1 ranks (torchrun) every rank runs the same workload on its own ciphertexts
+(independent ciphertexts, no data-path collective): weak scaling, value = all ranks' ops / max
+time over ranks.
+
+Prints one JSON line.  `value` is device-resident throughput timed with CUDA events; `e2e` is the
+same metric through the C ABI with host buffers (pinned), host->device and device->host copies
+inside the timed region; `roofline` describes the dominant kernel pair (forward NTT) timed live
+with CUDA events; `cpu_baseline` is the oracle (a port of the reference algorithm) on a bounded
+sample on the host cores.  `--impl reference` times that CPU port alone.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from cerium_b200 import params  # noqa: E402
+
+LOGN = 16
+N = 1 << LOGN
+
+
+def env_int(name, default):
+    try:
+        return int(os.environ.get(name, default))
+    except ValueError:
+        return default
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(smax)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------
+# workloads
+# ---------------------------------------------------------------------------------------
+
+class Workload:
+    name = ""
+    metric = ""
+    unit = ""
+
+    def setup(self, lib, torch, rank):
+        raise NotImplementedError
+
+    def step(self):
+        raise NotImplementedError
+
+
+def _rand_limbs_gpu(torch, moduli, prime_idx, lead, gen):
+    """[lead..., len(prime_idx), N] int64 uniform residues on the GPU (seeded)."""
+    q = torch.tensor([moduli[p] for p in prime_idx], dtype=torch.int64, device="cuda").view(-1, 1)
+    shape = tuple(lead) + (len(prime_idx), N)
+    x = torch.randint(0, 1 << 62, shape, dtype=torch.int64, device="cuda", generator=gen)
+    return (x % q).contiguous()
+
+
+class HRotWorkload(Workload):
+    name = "hrot_N65536_L35_K5_dnum7_u64"
+    metric = "hrot_keyswitch_ops_per_s"
+    unit = "ops/s"
+    ops_per_step = 1
+
+    def __init__(self, n_cts=4):
+        self.prm = params.config_hrot(LOGN, 35, 5, 7)
+        self.n_cts = n_cts  # rotating set of ciphertexts so consecutive ops do not reuse inputs
+
+    def setup(self, lib, torch, rank):
+        from cerium_b200 import _capi
+        self.torch = torch
+        prm = self.prm
+        self.ctx = _capi.Context(lib, prm.moduli, 64, device=torch.cuda.current_device())
+        self.ks = _capi.KeySwitch(self.ctx, prm.q_idx, prm.p_idx, prm.dnum, _capi.BCONV_LAZY, _capi.ROUND_FLOOR)
+        gen = torch.Generator(device="cuda").manual_seed(0xCE210003 + rank)
+        all_idx = prm.q_idx + prm.p_idx
+        self.evk = _rand_limbs_gpu(torch, prm.moduli, all_idx, (prm.dnum, 2), gen)
+        self.cts = [_rand_limbs_gpu(torch, prm.moduli, prm.q_idx, (2,), gen) for _ in range(self.n_cts)]
+        self.outs = [torch.empty_like(self.cts[0]) for _ in range(self.n_cts)]
+        self.elt = hrot_galois_elt()
+        self.i = 0
+        self.ct_bytes = self.cts[0].numel() * 8
+        # algorithmic (compulsory) bytes of one HRot: ciphertext in + key + ciphertext out
+        self.alg_bytes = (2 * prm.L + prm.dnum * 2 * (prm.L + prm.K) + 2 * prm.L) * N * 8
+        self.host_in = torch.empty(self.cts[0].shape, dtype=torch.int64).pin_memory()
+        self.host_in.copy_(self.cts[0].cpu())
+        self.host_out = torch.empty(self.cts[0].shape, dtype=torch.int64).pin_memory()
+        self.gpu_launches_per_step = 2 + (2 + 1 + 2 + 1 + 2 + 1 + 4)
+
+    def step(self):
+        k = self.i % self.n_cts
+        self.i += 1
+        ct, out = self.cts[k], self.outs[k]
+        self.ks.hrot(out[0].data_ptr(), out[1].data_ptr(), ct[0].data_ptr(), ct[1].data_ptr(), self.evk.data_ptr(),
+                     self.elt, self.torch.cuda.current_stream().cuda_stream)
+
+    def e2e_step(self):
+        ct, out = self.cts[0], self.outs[0]
+        ct.copy_(self.host_in, non_blocking=True)
+        self.ks.hrot(out[0].data_ptr(), out[1].data_ptr(), ct[0].data_ptr(), ct[1].data_ptr(), self.evk.data_ptr(),
+                     self.elt, self.torch.cuda.current_stream().cuda_stream)
+        self.host_out.copy_(out, non_blocking=True)
+        return self.ct_bytes, self.ct_bytes
+
+    # dominant kernel pair: forward NTT over the raised limbs (dnum*(L+K) - L limb transforms)
+    def roofline_setup(self):
+        prm = self.prm
+        self.rl_idx = []
+        for d in range(prm.dnum):
+            for i, p in enumerate(prm.q_idx + prm.p_idx):
+                if not (i < prm.L and i % prm.dnum == d):
+                    self.rl_idx.append(p)
+        gen = self.torch.Generator(device="cuda").manual_seed(5)
+        self.rl_buf = _rand_limbs_gpu(self.torch, prm.moduli, self.rl_idx, (), gen)
+        self.rl_bytes = 2 * len(self.rl_idx) * N * 8  # read once + write once
+        self.rl_name = "forward NTT (column pass + row pass), %d limbs u64" % len(self.rl_idx)
+
+    def roofline_step(self):
+        self.ctx.ntt_forward(self.rl_buf.data_ptr(), self.rl_buf.data_ptr(), self.rl_idx,
+                             stream=self.torch.cuda.current_stream().cuda_stream)
+
+    # CPU baseline: the oracle's HRot on the same parameter set (one op)
+    def cpu_sample(self, orc_mod):
+        prm = self.prm
+        rng = np.random.default_rng(1)
+        octx = orc_mod.OracleContext(LOGN, prm.moduli)
+        all_idx = prm.q_idx + prm.p_idx
+
+        def rl(idx, lead=()):
+            return np.stack([rng.integers(0, prm.moduli[p], size=tuple(lead) + (N,), dtype=np.uint64) for p in idx])
+        c0, c1 = rl(prm.q_idx), rl(prm.q_idx)
+        evk = np.stack([np.stack([rl(all_idx) for _ in range(2)]) for _ in range(prm.dnum)])
+        t0 = time.perf_counter()
+        octx.hrot(orc_mod.BCONV_LAZY, orc_mod.ROUND_FLOOR, prm.q_idx, prm.p_idx, prm.dnum, hrot_galois_elt(), c0, c1, evk)
+        dt = time.perf_counter() - t0
+        return 1.0 / dt, "1 HRot (L=35, K=5, dnum=7), oracle port with OpenMP over limbs"
+
+
+def hrot_galois_elt():
+    """Galois element 5^step mod 2N of the seeded rotation step in [1, 2^15)."""
+    step = int(np.random.default_rng(0xCE210003).integers(1, 1 << 15))
+    return pow(5, step, 2 * N)
+
+
+class HMultWorkload(Workload):
+    name = "hmult_relin_rescale_N65536_L24_K1_dnum24_u64"
+    metric = "hmult_keyswitch_ops_per_s"
+    unit = "ops/s"
+    ops_per_step = 1
+
+    def __init__(self):
+        self.prm = params.config_hmult(LOGN, 24)
+
+    def setup(self, lib, torch, rank):
+        from cerium_b200 import _capi
+        self.torch = torch
+        prm = self.prm
+        self.ctx = _capi.Context(lib, prm.moduli, 64, device=torch.cuda.current_device())
+        self.ks = _capi.KeySwitch(self.ctx, prm.q_idx, prm.p_idx, prm.dnum, _capi.BCONV_EXACT, _capi.ROUND_HALF)
+        gen = torch.Generator(device="cuda").manual_seed(0xCE210001 + rank)
+        all_idx = prm.q_idx + prm.p_idx
+        self.evk = _rand_limbs_gpu(torch, prm.moduli, all_idx, (prm.dnum, 2), gen)
+        self.a = _rand_limbs_gpu(torch, prm.moduli, prm.q_idx, (2,), gen)
+        self.b = _rand_limbs_gpu(torch, prm.moduli, prm.q_idx, (2,), gen)
+        self.out = torch.empty((2, prm.L - 1, N), dtype=torch.int64, device="cuda")
+        self.alg_bytes = (4 * prm.L + prm.dnum * 2 * (prm.L + prm.K) + 2 * (prm.L - 1)) * N * 8
+        self.host_in = torch.empty((2,) + tuple(self.a.shape), dtype=torch.int64).pin_memory()
+        self.host_in[0].copy_(self.a.cpu())
+        self.host_in[1].copy_(self.b.cpu())
+        self.host_out = torch.empty(self.out.shape, dtype=torch.int64).pin_memory()
+        self.gpu_launches_per_step = 1 + 13 + 2 * 4
+
+    def step(self):
+        s = self.torch.cuda.current_stream().cuda_stream
+        a, b, o = self.a, self.b, self.out
+        self.ks.hmult(o[0].data_ptr(), o[1].data_ptr(), a[0].data_ptr(), a[1].data_ptr(), b[0].data_ptr(),
+                      b[1].data_ptr(), self.evk.data_ptr(), True, s)
+
+    def e2e_step(self):
+        self.a.copy_(self.host_in[0], non_blocking=True)
+        self.b.copy_(self.host_in[1], non_blocking=True)
+        self.step()
+        self.host_out.copy_(self.out, non_blocking=True)
+        return self.host_in.numel() * 8, self.host_out.numel() * 8
+
+    def roofline_setup(self):
+        prm = self.prm
+        self.rl_idx = []
+        for d in range(prm.dnum):
+            for i, p in enumerate(prm.q_idx + prm.p_idx):
+                if not (i < prm.L and i % prm.dnum == d):
+                    self.rl_idx.append(p)
+        gen = self.torch.Generator(device="cuda").manual_seed(5)
+        self.rl_buf = _rand_limbs_gpu(self.torch, prm.moduli, self.rl_idx, (), gen)
+        self.rl_bytes = 2 * len(self.rl_idx) * N * 8
+        self.rl_name = "forward NTT (column pass + row pass), %d limbs u64" % len(self.rl_idx)
+
+    def roofline_step(self):
+        self.ctx.ntt_forward(self.rl_buf.data_ptr(), self.rl_buf.data_ptr(), self.rl_idx,
+                             stream=self.torch.cuda.current_stream().cuda_stream)
+
+    def cpu_sample(self, orc_mod):
+        prm = self.prm
+        rng = np.random.default_rng(1)
+        octx = orc_mod.OracleContext(LOGN, prm.moduli)
+        all_idx = prm.q_idx + prm.p_idx
+
+        def rl(idx):
+            return np.stack([rng.integers(0, prm.moduli[p], size=N, dtype=np.uint64) for p in idx])
+        a0, a1, b0, b1 = rl(prm.q_idx), rl(prm.q_idx), rl(prm.q_idx), rl(prm.q_idx)
+        evk = np.stack([np.stack([rl(all_idx) for _ in range(2)]) for _ in range(prm.dnum)])
+        t0 = time.perf_counter()
+        octx.hmult_relin(orc_mod.BCONV_EXACT, orc_mod.ROUND_HALF, True, prm.q_idx, prm.p_idx, prm.dnum, a0, a1, b0, b1, evk)
+        dt = time.perf_counter() - t0
+        return 1.0 / dt, "1 HMult+relin+rescale (L=24, K=1, dnum=24), oracle port with OpenMP over limbs"
+
+
+class NttWorkload(Workload):
+    name = "ntt_fwd_inv_N65536_48limbs_x8_u64"
+    metric = "ntt_limb_transforms_per_s"
+    unit = "limb-NTT/s"
+
+    def __init__(self):
+        self.moduli = params.config_ntt(LOGN, 48)
+        self.idx = [l for _ in range(8) for l in range(48)]
+        self.ops_per_step = 2 * len(self.idx)  # forward + inverse
+
+    def setup(self, lib, torch, rank):
+        from cerium_b200 import _capi
+        self.torch = torch
+        self.ctx = _capi.Context(lib, self.moduli, 64, device=torch.cuda.current_device())
+        gen = torch.Generator(device="cuda").manual_seed(0xCE210002 + rank)
+        self.x = _rand_limbs_gpu(torch, self.moduli, self.idx, (), gen)
+        self.y = torch.empty_like(self.x)
+        self.alg_bytes = 2 * 2 * len(self.idx) * N * 8
+        self.host_in = torch.empty(self.x.shape, dtype=torch.int64).pin_memory()
+        self.host_in.copy_(self.x.cpu())
+        self.host_out = torch.empty(self.x.shape, dtype=torch.int64).pin_memory()
+        self.gpu_launches_per_step = 4
+
+    def step(self):
+        s = self.torch.cuda.current_stream().cuda_stream
+        self.ctx.ntt_forward(self.y.data_ptr(), self.x.data_ptr(), self.idx, stream=s)
+        self.ctx.ntt_inverse(self.y.data_ptr(), self.y.data_ptr(), self.idx, stream=s)
+
+    def e2e_step(self):
+        self.x.copy_(self.host_in, non_blocking=True)
+        self.step()
+        self.host_out.copy_(self.y, non_blocking=True)
+        return self.host_in.numel() * 8, self.host_out.numel() * 8
+
+    def roofline_setup(self):
+        self.rl_bytes = 2 * len(self.idx) * N * 8
+        self.rl_name = "forward NTT (column pass + row pass), %d limbs u64" % len(self.idx)
+
+    def roofline_step(self):
+        self.ctx.ntt_forward(self.y.data_ptr(), self.x.data_ptr(), self.idx,
+                             stream=self.torch.cuda.current_stream().cuda_stream)
+
+    def cpu_sample(self, orc_mod):
+        rng = np.random.default_rng(1)
+        octx = orc_mod.OracleContext(LOGN, self.moduli)
+        x = np.stack([rng.integers(0, self.moduli[p], size=N, dtype=np.uint64) for p in self.idx])
+        t0 = time.perf_counter()
+        f = octx.ntt_forward(x, self.idx)
+        octx.ntt_inverse(f, self.idx)
+        dt = time.perf_counter() - t0
+        return self.ops_per_step / dt, "forward+inverse NTT of 384 limbs, oracle port (Harvey lazy butterflies), OpenMP over limbs"
+
+
+WORKLOADS = {"hrot": HRotWorkload, "hmult": HMultWorkload, "ntt": NttWorkload}
+
+
+# ---------------------------------------------------------------------------------------
+
+def run_reference_arm(args, wl):
+    """The reference's own CPU implementation of the path cannot be built here (it needs Microsoft
+    SEAL 4.1.1, absent), so this arm times the oracle port of the same algorithm on the host cores."""
+    rank = env_int("RANK", 0)
+    if rank != 0:
+        return
+    import oracle
+    vals = []
+    sample = ""
+    for _ in range(max(1, min(args.warmup, 1))):
+        wl.cpu_sample(oracle)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        v, sample = wl.cpu_sample(oracle)
+        vals.append(v)
+    wall = time.perf_counter() - t0
+    value = float(np.mean(vals))
+    ops = getattr(wl, "ops_per_step", 1)
+    line = {
+        "impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * ops / value,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+        "config": {"workload": wl.name, "note": "CPU port of the reference algorithm (SEAL-based reference runtime not buildable here)"},
+        "cpu_baseline": {"value": value, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": wall,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="hrot")
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]()
+    if args.impl == "reference":
+        args.steps = args.steps if args.steps is not None else 3
+        args.warmup = args.warmup if args.warmup is not None else 1
+        run_reference_arm(args, wl)
+        return
+    args.steps = args.steps if args.steps is not None else 200
+    args.warmup = max(3, args.warmup if args.warmup is not None else 20)
+
+    import torch
+    import torch.distributed as dist
+    from cerium_b200 import _capi
+
+    world = env_int("WORLD_SIZE", 1)
+    rank = env_int("RANK", 0)
+    local_rank = env_int("LOCAL_RANK", 0)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    lib = _capi.load()
+    wl.setup(lib, torch, rank)
+    ops = wl.ops_per_step
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        wl.step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        wl.step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+
+    # dominant kernel pair, timed live with CUDA events on the launching stream
+    wl.roofline_setup()
+    for _ in range(3):
+        wl.roofline_step()
+    torch.cuda.synchronize()
+    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    rl_iters = 20
+    r0.record()
+    for _ in range(rl_iters):
+        wl.roofline_step()
+    r1.record()
+    torch.cuda.synchronize()
+    rl_ms = r0.elapsed_time(r1) / rl_iters
+    clocks = sampler.stop() if rank == 0 else None
+
+    # end to end: host buffers in, host buffers out, through the same C ABI calls
+    e2e_steps = max(5, min(args.steps, 50))
+    for _ in range(3):
+        wl.e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    h2d = d2h = 0
+    for _ in range(e2e_steps):
+        h2d, d2h = wl.e2e_step()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        value = world * ops * args.steps / (ms / 1e3)
+        achieved = wl.rl_bytes / (rl_ms / 1e3) / 1e9
+        line = {
+            "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+            "config": {"workload": wl.name, "l2": "working set larger than L2 (keys + ciphertexts + workspace > 126 MB)",
+                       "parallelism": "independent ciphertexts per GPU" if world > 1 else "single GPU"},
+            "e2e": {"value": world * ops * e2e_steps / e2e_s, "unit": wl.unit, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h},
+            "gpu_launches": wl.gpu_launches_per_step * args.steps,
+            "roofline": {"bound": "hbm", "kernel": wl.rl_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                         "ms_per_launch_pair": rl_ms, "algorithmic_bytes": wl.rl_bytes},
+            "step_algorithmic_gbs": wl.alg_bytes * args.steps / (ms / 1e3) / 1e9,
+            "clocks": clocks,
+        }
+        if not args.no_cpu_baseline:
+            import oracle
+            v, sample = wl.cpu_sample(oracle)
+            line["cpu_baseline"] = {"value": v, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",
+                                    "sample": sample}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -30,6 +30,12 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#if defined(__GNUC__)
+#define CERIUM_API __attribute__((visibility("default")))
+#else
+#define CERIUM_API
+#endif
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -60,10 +66,10 @@ typedef struct cerium_bconv cerium_bconv;
 typedef struct cerium_keyswitch cerium_keyswitch;
 
 /* Library version (major * 10000 + minor * 100 + patch). */
-int cerium_version(void);
+CERIUM_API int cerium_version(void);
 
 /* Message of the last failing call on this host thread ("" if none). */
-const char *cerium_last_error(void);
+CERIUM_API const char *cerium_last_error(void);
 
 /*
  * Context: device tables for a list of primes (moduli, Barrett constants, forward and
@@ -72,13 +78,13 @@ const char *cerium_last_error(void);
  * word_bits is 32 or 64; log_n must be 16; every modulus must be a prime = 1 mod 2N,
  * below 2^30 (32-bit words) or 2^60 (64-bit words); at most 255 moduli.
  */
-int cerium_context_create(cerium_context **out, int device, int log_n, int word_bits,
+CERIUM_API int cerium_context_create(cerium_context **out, int device, int log_n, int word_bits,
                           const uint64_t *moduli, int n_moduli);
-int cerium_context_destroy(cerium_context *ctx);
-int cerium_context_word_bits(const cerium_context *ctx);
-int cerium_context_num_moduli(const cerium_context *ctx);
-uint64_t cerium_context_modulus(const cerium_context *ctx, int k);
-uint64_t cerium_context_root(const cerium_context *ctx, int k); /* psi of prime k */
+CERIUM_API int cerium_context_destroy(cerium_context *ctx);
+CERIUM_API int cerium_context_word_bits(const cerium_context *ctx);
+CERIUM_API int cerium_context_num_moduli(const cerium_context *ctx);
+CERIUM_API uint64_t cerium_context_modulus(const cerium_context *ctx, int k);
+CERIUM_API uint64_t cerium_context_root(const cerium_context *ctx, int k); /* psi of prime k */
 
 /*
  * Forward / inverse negacyclic NTT of `count` limbs.  in == out is allowed.
@@ -86,9 +92,9 @@ uint64_t cerium_context_root(const cerium_context *ctx, int k); /* psi of prime 
  * 58-72, 237-256) and Evaluator::fn_ntt / fn_int
  * (cerium/runtime/execution/evaluator.cpp:444-463, 540-551).
  */
-int cerium_ntt_forward(cerium_context *ctx, void *out, size_t out_stride, const void *in,
+CERIUM_API int cerium_ntt_forward(cerium_context *ctx, void *out, size_t out_stride, const void *in,
                        size_t in_stride, const uint32_t *prime_idx, int count, void *stream);
-int cerium_ntt_inverse(cerium_context *ctx, void *out, size_t out_stride, const void *in,
+CERIUM_API int cerium_ntt_inverse(cerium_context *ctx, void *out, size_t out_stride, const void *in,
                        size_t in_stride, const uint32_t *prime_idx, int count, void *stream);
 
 /*
@@ -96,9 +102,9 @@ int cerium_ntt_inverse(cerium_context *ctx, void *out, size_t out_stride, const 
  * `num_bases` limb pointers, bases a DEVICE array of prime indices
  * (cerium/runtime/execution/device_utils.h:42-53).
  */
-int cerium_ntt_forward_ptrs(cerium_context *ctx, void *const *outs, const void *const *ins,
+CERIUM_API int cerium_ntt_forward_ptrs(cerium_context *ctx, void *const *outs, const void *const *ins,
                             const uint32_t *bases, size_t num_bases, void *stream);
-int cerium_ntt_inverse_ptrs(cerium_context *ctx, void *const *outs, const void *const *ins,
+CERIUM_API int cerium_ntt_inverse_ptrs(cerium_context *ctx, void *const *outs, const void *const *ins,
                             const uint32_t *bases, size_t num_bases, void *stream);
 
 /*
@@ -109,7 +115,7 @@ int cerium_ntt_inverse_ptrs(cerium_context *ctx, void *const *outs, const void *
  * (cerium/compiler/backend/kernels/function.cu:151-169) and compute_sud_factors
  * (cerium/runtime/execution/function.cpp:685-732).
  */
-int cerium_sud(cerium_context *ctx, void *out, size_t out_stride, const void *minuend,
+CERIUM_API int cerium_sud(cerium_context *ctx, void *out, size_t out_stride, const void *minuend,
                size_t minuend_stride, void *in_coeff, size_t in_stride, const void *addend,
                size_t addend_stride, const uint32_t *prime_idx, int count,
                const uint32_t *divide_primes, int n_divide, void *stream);
@@ -121,7 +127,7 @@ int cerium_sud(cerium_context *ctx, void *out, size_t out_stride, const void *mi
  * (cerium/compiler/backend/cuda_kernel.cc:1142-1280, 2669-2765) and Evaluator::fn_ewi
  * (cerium/runtime/execution/evaluator.cpp:279-463).
  */
-int cerium_ewise(cerium_context *ctx, int op, void *out, size_t out_stride, const void *a,
+CERIUM_API int cerium_ewise(cerium_context *ctx, int op, void *out, size_t out_stride, const void *a,
                  size_t a_stride, const void *b, size_t b_stride, const void *c, size_t c_stride,
                  const uint64_t *scalars, const uint32_t *prime_idx, int count, void *stream);
 
@@ -130,7 +136,7 @@ int cerium_ewise(cerium_context *ctx, int op, void *out, size_t out_stride, cons
  * (all seven stacks share `stride`).  Restates mul_ct_ct
  * (cerium/compiler/backend/compiler.cc:443-467) as one kernel.
  */
-int cerium_tensor(cerium_context *ctx, void *d0, void *d1, void *d2, const void *a0,
+CERIUM_API int cerium_tensor(cerium_context *ctx, void *d0, void *d1, void *d2, const void *a0,
                   const void *a1, const void *b0, const void *b1, size_t stride,
                   const uint32_t *prime_idx, int count, void *stream);
 
@@ -142,8 +148,8 @@ int cerium_tensor(cerium_context *ctx, void *d0, void *d1, void *d2, const void 
  * (cerium/compiler/backend/cuda_kernel.cc:228-300) and
  * EvaluatorContext::get_rotation_map_ptr (evaluator.cpp:233-260); no table is uploaded.
  */
-uint32_t cerium_galois_elt_from_step(int step, int log_n);
-int cerium_automorph(cerium_context *ctx, void *out, size_t out_stride, const void *in,
+CERIUM_API uint32_t cerium_galois_elt_from_step(int step, int log_n);
+CERIUM_API int cerium_automorph(cerium_context *ctx, void *out, size_t out_stride, const void *in,
                      size_t in_stride, uint32_t galois_elt, int count, void *stream);
 
 /*
@@ -152,10 +158,10 @@ int cerium_automorph(cerium_context *ctx, void *out, size_t out_stride, const vo
  * evaluator.cpp:1483-1608) and _function_bco_ (cerium/compiler/backend/kernels/function.cuh:
  * 80-99).  Input limbs are in coefficient form.
  */
-int cerium_bconv_create(cerium_context *ctx, cerium_bconv **out, int mode,
+CERIUM_API int cerium_bconv_create(cerium_context *ctx, cerium_bconv **out, int mode,
                         const uint32_t *in_primes, int n_in, const uint32_t *out_primes, int n_out);
-int cerium_bconv_destroy(cerium_bconv *bc);
-int cerium_bconv_apply(cerium_bconv *bc, void *out, size_t out_stride, const void *in,
+CERIUM_API int cerium_bconv_destroy(cerium_bconv *bc);
+CERIUM_API int cerium_bconv_apply(cerium_bconv *bc, void *out, size_t out_stride, const void *in,
                        size_t in_stride, void *stream);
 
 /*
@@ -166,11 +172,11 @@ int cerium_bconv_apply(cerium_bconv *bc, void *out, size_t out_stride, const voi
  * An evaluation key is dnum x 2 x (L+K) limbs, [digit][c0|c1][q_idx..., p_idx...][N]
  * (cerium/runtime/io/ckks-encryptor.cpp:534-599).
  */
-int cerium_keyswitch_create(cerium_context *ctx, cerium_keyswitch **out, int bconv_mode,
+CERIUM_API int cerium_keyswitch_create(cerium_context *ctx, cerium_keyswitch **out, int bconv_mode,
                             int round_mode, const uint32_t *q_idx, int L, const uint32_t *p_idx,
                             int K, int dnum);
-int cerium_keyswitch_destroy(cerium_keyswitch *ks);
-size_t cerium_keyswitch_workspace_bytes(const cerium_keyswitch *ks);
+CERIUM_API int cerium_keyswitch_destroy(cerium_keyswitch *ks);
+CERIUM_API size_t cerium_keyswitch_workspace_bytes(const cerium_keyswitch *ks);
 
 /*
  * out0,out1 [L][N] = ModDown( sum_d ModUp(digit d of cpoly) * evk[d] ); if add0 / add1 are
@@ -179,14 +185,14 @@ size_t cerium_keyswitch_workspace_bytes(const cerium_keyswitch *ks);
  * (cerium/compiler/backend/compiler_keyswitch.cc:253-432): INTT, BCONV, NTT, EVKMUL,
  * INTT, BCONV, SUD.  All stacks are contiguous ([limb][N], stride N).
  */
-int cerium_keyswitch_apply(cerium_keyswitch *ks, void *out0, void *out1, const void *cpoly,
+CERIUM_API int cerium_keyswitch_apply(cerium_keyswitch *ks, void *out0, void *out1, const void *cpoly,
                            const void *evk, const void *add0, const void *add1, void *stream);
 
 /*
  * HRot: (out0,out1) = KeySwitch(phi(c1)) + (phi(c0), 0), phi the automorphism galois_elt.
  * Restates rotate_internal (cerium/compiler/backend/compiler.cc:701-726).
  */
-int cerium_hrot(cerium_keyswitch *ks, void *out0, void *out1, const void *c0, const void *c1,
+CERIUM_API int cerium_hrot(cerium_keyswitch *ks, void *out0, void *out1, const void *c0, const void *c1,
                 const void *evk, uint32_t galois_elt, void *stream);
 
 /*
@@ -195,7 +201,7 @@ int cerium_hrot(cerium_keyswitch *ks, void *out0, void *out1, const void *c0, co
  * compiler_keyswitch.cc:360-380) and rescale (compiler_rescale.cc:209-284).  Outputs hold
  * L limbs, or L-1 with rescale.
  */
-int cerium_hmult(cerium_keyswitch *ks, void *out0, void *out1, const void *a0, const void *a1,
+CERIUM_API int cerium_hmult(cerium_keyswitch *ks, void *out0, void *out1, const void *a0, const void *a1,
                  const void *b0, const void *b1, const void *evk, int do_rescale, void *stream);
 
 /*
@@ -204,7 +210,7 @@ int cerium_hmult(cerium_keyswitch *ks, void *out0, void *out1, const void *a0, c
  * Restates rescale (cerium/compiler/backend/compiler_rescale.cc:209-284): INTT of the last
  * limb, SuD on the others.
  */
-int cerium_rescale(cerium_context *ctx, int round_mode, void *out, const void *in,
+CERIUM_API int cerium_rescale(cerium_context *ctx, int round_mode, void *out, const void *in,
                    const uint32_t *q_idx, int L, int n_polys, void *scratch, void *stream);
 
 #ifdef __cplusplus
