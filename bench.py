@@ -60,7 +60,7 @@ def measured_peaks():
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
 
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,utilization.gpu,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -73,7 +73,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except Exception:
@@ -81,7 +81,11 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
+
+    def mark_start(self):
+        """Samples taken before this call (idle GPU, start-up) are not part of the record."""
+        self.t_start = time.perf_counter()
 
     def stop(self):
         if self.proc is None:
@@ -93,9 +97,10 @@ class ClockSampler:
             self.proc.kill()
         sm, smax, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        t_start = getattr(self, "t_start", 0.0)
+        for ts, ln in self.lines:
             f = [x.strip() for x in ln.split(",")]
-            if len(f) < 9:
+            if len(f) < 9 or ts < t_start:
                 continue
             try:
                 sm.append(float(f[1]))
@@ -397,8 +402,8 @@ def main():
         args.warmup = args.warmup if args.warmup is not None else 1
         run_reference_arm(args, wl)
         return
-    args.steps = args.steps if args.steps is not None else 200
-    args.warmup = max(3, args.warmup if args.warmup is not None else 20)
+    args.steps = args.steps if args.steps is not None else 2000
+    args.warmup = max(3, args.warmup if args.warmup is not None else 50)
 
     import torch
     import torch.distributed as dist
@@ -421,12 +426,13 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        wl.step()
-    barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(args.warmup):
+        wl.step()
+    barrier()
+    sampler.mark_start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()

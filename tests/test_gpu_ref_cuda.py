@@ -1,0 +1,86 @@
+"""On a GPU: the reference's own CUDA kernels (oracle/_ref/libref_cuda.so), the product's 32-bit
+kernels and the CPU oracle agree modulo q on the same inputs."""
+import numpy as np
+import pytest
+
+import oracle
+from cerium_b200 import _capi
+from tests import ref_cuda
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not ref_cuda.available(), reason="oracle/_ref/libref_cuda.so not built")]
+
+N = 1 << 16
+
+
+@pytest.fixture(scope="module")
+def env():
+    import importlib.util, os
+    from tests.backends import CudaBackend
+    here = os.path.dirname(os.path.abspath(__file__))
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(here, "golden", "make_ref_cuda_golden.py"))
+    G = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(G)
+    be = CudaBackend()
+    return be, G, ref_cuda.RefCuda(G.PRIMES), _capi.Context(be.lib, G.PRIMES, 32), oracle.OracleContext(16, G.PRIMES)
+
+
+def _canon(t, mods):
+    return t.cpu().numpy().view(np.uint32) % np.array(mods, dtype=np.uint32)[:, None]
+
+
+@pytest.mark.parametrize("name", ["ntt_fwd", "ntt_inv"])
+def test_ntt_three_way(env, name):
+    be, G, ref, ctx, octx = env
+    torch = be.torch
+    _, _, d = G.CASES[name]
+    x = G.case_inputs(name)["x"]
+    dx = torch.from_numpy(x.view(np.int32)).cuda()
+    r = torch.zeros_like(dx)
+    o = torch.zeros_like(dx)
+    ref.ntt(r.data_ptr(), dx.data_ptr(), d["bases"], inverse=d["inverse"])
+    (ctx.ntt_inverse if d["inverse"] else ctx.ntt_forward)(o.data_ptr(), dx.data_ptr(), d["bases"])
+    torch.cuda.synchronize()
+    mods = [G.PRIMES[b] for b in d["bases"]]
+    want = (octx.ntt_inverse if d["inverse"] else octx.ntt_forward)(x.astype(np.uint64), d["bases"]).astype(np.uint32)
+    assert np.array_equal(_canon(r, mods), want), "oracle differs from the reference CUDA kernel"
+    assert np.array_equal(o.cpu().numpy().view(np.uint32), want), "product differs from the oracle"
+
+
+@pytest.mark.parametrize("name", ["bconv_5_35", "bconv_5_30", "bconv_18_12"])
+def test_bconv_three_way(env, name):
+    be, G, ref, ctx, octx = env
+    torch = be.torch
+    _, _, d = G.CASES[name]
+    x = G.case_inputs(name)["x"]
+    dx = torch.from_numpy(x.view(np.int32)).cuda()
+    r = torch.zeros((len(d["out_idx"]), N), dtype=torch.int32, device="cuda")
+    o = torch.zeros_like(r)
+    ref.bconv(r.data_ptr(), dx.data_ptr(), d["in_idx"], d["out_idx"])
+    bc = _capi.BaseConverter(ctx, d["in_idx"], d["out_idx"], _capi.BCONV_LAZY)
+    bc.apply(o.data_ptr(), dx.data_ptr())
+    torch.cuda.synchronize()
+    mods = [G.PRIMES[j] for j in d["out_idx"]]
+    want = oracle.bconv(oracle.BCONV_LAZY, [G.PRIMES[i] for i in d["in_idx"]], x.astype(np.uint64), mods).astype(np.uint32)
+    assert np.array_equal(_canon(r, mods), want), "oracle differs from the reference CUDA kernel"
+    assert np.array_equal(o.cpu().numpy().view(np.uint32), want), "product differs from the oracle"
+
+
+def test_sud_three_way(env):
+    be, G, ref, ctx, octx = env
+    torch = be.torch
+    _, _, d = G.CASES["sud"]
+    inp = G.case_inputs("sud")
+    in1 = torch.from_numpy(inp["in1"].view(np.int32)).cuda()
+    in2 = torch.from_numpy(inp["in2"].view(np.int32)).cuda()
+    r = torch.zeros_like(in1)
+    o = torch.zeros_like(in1)
+    f = G.sud_factors(d["divide"])
+    ref.sud(r.data_ptr(), in1.data_ptr(), in2.data_ptr(), d["bases"], f)
+    work = in2.clone()
+    ctx.sud(o.data_ptr(), in1.data_ptr(), work.data_ptr(), d["bases"], d["divide"])
+    torch.cuda.synchronize()
+    mods = [G.PRIMES[b] for b in d["bases"]]
+    want = np.stack([octx.sud(b, inp["in1"][i].astype(np.uint64), inp["in2"][i].astype(np.uint64), f[b])
+                     for i, b in enumerate(d["bases"])]).astype(np.uint32)
+    assert np.array_equal(_canon(r, mods), want), "oracle differs from the reference CUDA kernel"
+    assert np.array_equal(o.cpu().numpy().view(np.uint32), want), "product differs from the oracle"
