@@ -64,7 +64,7 @@ int launch_ntt_forward(cerium_context* ctx, const NttCall& c, cudaStream_t strea
       rows.in = static_cast<const W*>(c.out);
       rows.in_stride = c.out_stride;
       { auto kfn = ntt_fwd_cols_kernel<W, StridedBatch<W>, PlainLoader<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kCols, cnt), kCols * 16, 0, stream, cols, PlainLoader<W>{}, static_cast<const Pair*>(ctx->d_tw_fwd), static_cast<const PrimeConst<W>*>(ctx->d_pcs)); }
-      { auto kfn = ntt_fwd_rows_kernel<W, StridedBatch<W>, StoreEpilogue<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kRowsPerCta, cnt), kRowsPerCta * 16, 0, stream, rows, StoreEpilogue<W>{}, static_cast<const Pair*>(ctx->d_tw_fwd), static_cast<const PrimeConst<W>*>(ctx->d_pcs)); }
+      { auto kfn = ntt_fwd_rows_kernel<W, StridedBatch<W>, StoreEpilogue<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kRowsPerCta, cnt), kRowsPerCta * 16, 0, stream, rows, StoreEpilogue<W>{}, static_cast<const Pair*>(ctx->d_tw_fwd), static_cast<const Pair*>(ctx->d_twr_fwd), static_cast<const PrimeConst<W>*>(ctx->d_pcs)); }
     }
     CERIUM_LAUNCH_CHECK("ntt_forward");
     return CERIUM_OK;
@@ -91,7 +91,7 @@ int launch_ntt_inverse(cerium_context* ctx, const NttCall& c, const void* scale,
         sc.scale = static_cast<const W*>(scale) + first;
         sc.scale_shoup = static_cast<const W*>(scale_shoup) + first;
       }
-      { auto kfn = ntt_inv_rows_kernel<W, StridedBatch<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kRowsPerCta, cnt), kRowsPerCta * 16, 0, stream, sb, static_cast<const Pair*>(ctx->d_tw_inv), static_cast<const PrimeConst<W>*>(ctx->d_pcs)); }
+      { auto kfn = ntt_inv_rows_kernel<W, StridedBatch<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kRowsPerCta, cnt), kRowsPerCta * 16, 0, stream, sb, static_cast<const Pair*>(ctx->d_tw_inv), static_cast<const Pair*>(ctx->d_twr_inv), static_cast<const PrimeConst<W>*>(ctx->d_pcs)); }
       { auto kfn = ntt_inv_cols_kernel<W, StridedBatch<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kCols, cnt), kCols * 16, 0, stream, sb, sc, static_cast<const Pair*>(ctx->d_tw_inv), static_cast<const PrimeConst<W>*>(ctx->d_pcs)); }
     }
     CERIUM_LAUNCH_CHECK("ntt_inverse");
@@ -142,7 +142,7 @@ int launch_sud(cerium_context* ctx, const SudCall& c, cudaStream_t stream) {
       } else {
         { auto kfn = ntt_fwd_cols_kernel<W, StridedBatch<W>, PlainLoader<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kCols, cnt), kCols * 16, 0, stream, cols, PlainLoader<W>{}, tw, pcs); }
       }
-      { auto kfn = ntt_fwd_rows_kernel<W, StridedBatch<W>, SudEpilogue<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kRowsPerCta, cnt), kRowsPerCta * 16, 0, stream, rows, epi, tw, pcs); }
+      { auto kfn = ntt_fwd_rows_kernel<W, StridedBatch<W>, SudEpilogue<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kRowsPerCta, cnt), kRowsPerCta * 16, 0, stream, rows, epi, tw, static_cast<const Pair*>(ctx->d_twr_fwd), pcs); }
     }
     CERIUM_LAUNCH_CHECK("sud");
     return CERIUM_OK;
@@ -302,9 +302,7 @@ int launch_bconv(cerium_context* ctx, const BconvCall* calls, int count, cudaStr
         d.out_pos = bc->d_out_pos;
         d.I = bc->I;
         d.O = bc->O;
-        size_t need = (size_t)bc->O * bc->I * sizeof(W);
-        if (bc->I > kBconvRegInputs) need += (size_t)bc->I * kBconvThreads * sizeof(W);
-        smem = std::max(smem, need);
+        smem = std::max(smem, bconv_smem_bytes<W>(bc->I, bc->O));
       }
       if (smem > 48 * 1024) {
         if (smem > 200 * 1024) return fail(CERIUM_ERR_UNSUPPORTED, "bconv: conversion needs more than 200 KiB of shared memory");
@@ -367,6 +365,7 @@ int cerium_context_create(cerium_context** out, int device, int log_n, int word_
     using W = decltype(tag);
     using Pair = typename WordTraits<W>::Pair;
     std::vector<Pair> fwd(n * n_moduli), inv(n * n_moduli);
+    std::vector<Pair> rfwd((size_t)kRowTwPerPrime * n_moduli), rinv((size_t)kRowTwPerPrime * n_moduli);
     std::vector<PrimeConst<W>> pcs(n_moduli);
     for (int k = 0; k < n_moduli; k++) {
       const uint64_t q = moduli[k];
@@ -376,6 +375,15 @@ int cerium_context_create(cerium_context** out, int device, int log_n, int word_
         fwd[k * n + i] = WordTraits<W>::make((W)t.w[i], (W)host::shoup(t.w[i], q, word_bits));
         inv[k * n + i] = WordTraits<W>::make((W)t.wi[i], (W)host::shoup(t.wi[i], q, word_bits));
       }
+      for (int h = 0; h < 256; h++)
+        for (int t = 0; t < 4; t++)
+          for (int g = 0; g < (1 << t); g++)
+            for (int u = 0; u < 16; u++) {
+              const size_t src = k * n + (((size_t)(4096 + 16 * h + u)) << t) + g;
+              const size_t dst = (size_t)k * kRowTwPerPrime + ((size_t)h * 15 + ((1 << t) - 1 + g)) * 16 + u;
+              rfwd[dst] = fwd[src];
+              rinv[dst] = inv[src];
+            }
       PrimeConst<W>& pc = pcs[k];
       std::memset(&pc, 0, sizeof(pc));
       pc.q = (W)q;
@@ -388,10 +396,15 @@ int cerium_context_create(cerium_context** out, int device, int log_n, int word_
       const uint64_t w1 = host::mulmod(t.wi[1], t.ninv, q);
       pc.w1ninv = (W)w1;
       pc.w1ninv_shoup = (W)host::shoup(w1, q, word_bits);
+      pc.lazy_ok = (W)((word_bits == 64 && q < ((uint64_t)1 << 52)) ? 1 : 0);
     }
     CERIUM_CUDA(cudaMalloc(&ctx->d_tw_fwd, fwd.size() * sizeof(Pair)));
     CERIUM_CUDA(cudaMalloc(&ctx->d_tw_inv, inv.size() * sizeof(Pair)));
     CERIUM_CUDA(cudaMalloc(&ctx->d_pcs, pcs.size() * sizeof(PrimeConst<W>)));
+    CERIUM_CUDA(cudaMalloc(&ctx->d_twr_fwd, rfwd.size() * sizeof(Pair)));
+    CERIUM_CUDA(cudaMalloc(&ctx->d_twr_inv, rinv.size() * sizeof(Pair)));
+    CERIUM_CUDA(cudaMemcpy(ctx->d_twr_fwd, rfwd.data(), rfwd.size() * sizeof(Pair), cudaMemcpyHostToDevice));
+    CERIUM_CUDA(cudaMemcpy(ctx->d_twr_inv, rinv.data(), rinv.size() * sizeof(Pair), cudaMemcpyHostToDevice));
     CERIUM_CUDA(cudaMemcpy(ctx->d_tw_fwd, fwd.data(), fwd.size() * sizeof(Pair), cudaMemcpyHostToDevice));
     CERIUM_CUDA(cudaMemcpy(ctx->d_tw_inv, inv.data(), inv.size() * sizeof(Pair), cudaMemcpyHostToDevice));
     CERIUM_CUDA(cudaMemcpy(ctx->d_pcs, pcs.data(), pcs.size() * sizeof(PrimeConst<W>), cudaMemcpyHostToDevice));
@@ -411,6 +424,8 @@ int cerium_context_destroy(cerium_context* ctx) {
   cudaFree(ctx->d_tw_fwd);
   cudaFree(ctx->d_tw_inv);
   cudaFree(ctx->d_pcs);
+  cudaFree(ctx->d_twr_fwd);
+  cudaFree(ctx->d_twr_inv);
   delete ctx;
   return CERIUM_OK;
 }
@@ -468,10 +483,10 @@ static int ntt_ptrs_common(cerium_context* ctx, bool forward, void* const* outs,
     if (forward) {
       const Pair* tw = static_cast<const Pair*>(ctx->d_tw_fwd);
       { auto kfn = ntt_fwd_cols_kernel<W, PointerBatch<W>, PlainLoader<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kCols, cnt), kCols * 16, 0, s, pb, PlainLoader<W>{}, tw, pcs); }
-      { auto kfn = ntt_fwd_rows_kernel<W, PointerBatch<W>, StoreEpilogue<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kRowsPerCta, cnt), kRowsPerCta * 16, 0, s, inplace, StoreEpilogue<W>{}, tw, pcs); }
+      { auto kfn = ntt_fwd_rows_kernel<W, PointerBatch<W>, StoreEpilogue<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kRowsPerCta, cnt), kRowsPerCta * 16, 0, s, inplace, StoreEpilogue<W>{}, tw, static_cast<const Pair*>(ctx->d_twr_fwd), pcs); }
     } else {
       const Pair* tw = static_cast<const Pair*>(ctx->d_tw_inv);
-      { auto kfn = ntt_inv_rows_kernel<W, PointerBatch<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kRowsPerCta, cnt), kRowsPerCta * 16, 0, s, pb, tw, pcs); }
+      { auto kfn = ntt_inv_rows_kernel<W, PointerBatch<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kRowsPerCta, cnt), kRowsPerCta * 16, 0, s, pb, tw, static_cast<const Pair*>(ctx->d_twr_inv), pcs); }
       { auto kfn = ntt_inv_cols_kernel<W, PointerBatch<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kCols, cnt), kCols * 16, 0, s, pb, InvScale<W>{}, tw, pcs); }
     }
     CERIUM_LAUNCH_CHECK("ntt_ptrs");

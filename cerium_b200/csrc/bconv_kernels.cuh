@@ -12,9 +12,9 @@
 //
 // One thread owns one coefficient: it reads the I input residues once (coalesced across the
 // warp), keeps them in registers (I <= 8) or in its own shared-memory column (larger I), and
-// streams over the O output primes with the factor matrix broadcast from shared memory.  Sums
-// are kept in a two-word accumulator and reduced once per output (primes below 2^60 leave room
-// for 256 terms), instead of the reference's trims at i = 15, 30.
+// streams over the O output primes with the factor matrix and the per-output constants
+// broadcast from shared memory.  Sums are reduced once per output (primes below 2^60 leave
+// room for 256 terms), instead of the reference's trims at i = 15, 30.
 #pragma once
 #include "modarith.cuh"
 
@@ -41,41 +41,98 @@ struct BconvDesc {
   int O;
 };
 
-template <typename W, int kRegI>
-__device__ __forceinline__ void bconv_body(const BconvDesc<W>& d, const PrimeConst<W>* __restrict__ pcs,
-                                           W* sfac, W* scol, int coeff) {
-  const int tid = threadIdx.x;
+// Per-output constants staged in shared memory next to the factor matrix, so the output loop
+// has no dependent global loads.
+template <typename W>
+struct BconvOut {
+  W q, q2, mu_hi, mu_lo, sub;  // sub = rounding term (0 when unused)
+  uint32_t pos;                // limb slot of this output
+  uint32_t pad;
+};
+
+// Barrett reduction with the 3-multiply high products: qhat may be up to 7 short, so the
+// remainder lies in [0, 8q) (q < 2^60) and takes three conditional subtractions.
+__device__ __forceinline__ uint64_t barrett2_fast(uint64_t hi, uint64_t lo, uint64_t q, uint64_t q2, uint64_t mu_hi,
+                                                  uint64_t mu_lo) {
+  const uint64_t qhat = hi * mu_hi + mulhi_approx64(lo, mu_hi) + mulhi_approx64(hi, mu_lo);
+  uint64_t r = lo - qhat * q;
+  r = csub<uint64_t>(r, q2 + q2);
+  r = csub<uint64_t>(r, q2);
+  return csub<uint64_t>(r, q);
+}
+
+template <typename W>
+__device__ __forceinline__ W bconv_input(const BconvDesc<W>& d, const PrimeConst<W>* __restrict__ pcs, int i,
+                                         int coeff) {
+  W v = d.in[(size_t)i * d.in_stride + coeff];
+  if (d.in_add != nullptr || d.inv != nullptr) {
+    const W qi = pcs[d.in_prime[i]].q;
+    if (d.in_add != nullptr) v = add_mod<W>(v, d.in_add[i], qi);
+    if (d.inv != nullptr) v = csub<W>(mul_shoup_lazy<W>(v, d.inv[i], d.inv_shoup[i], qi), qi);
+  }
+  return v;
+}
+
+// 64-bit words, at most 8 inputs: residues and factors are split at bit 30 so that every
+// partial product is a 32x32->64 multiply-add into one of three column sums (y0*f0,
+// y0*f1 + y1*f0, y1*f1).  With pieces below 2^30 and at most 8 terms no column overflows, so
+// a multiply-accumulate is four IMAD.WIDE and no carry handling.
+template <int kRegI>
+__device__ __forceinline__ void bconv_body_split64(const BconvDesc<uint64_t>& d,
+                                                   const PrimeConst<uint64_t>* __restrict__ pcs,
+                                                   const uint2* sfac, const BconvOut<uint64_t>* sout, int coeff) {
   const int I = d.I, O = d.O;
-  W y[kRegI > 0 ? kRegI : 1];
-  // gather (and pre-scale) the inputs
-  if (kRegI > 0) {
+  uint32_t y0[kRegI], y1[kRegI];
+#pragma unroll
+  for (int i = 0; i < kRegI; i++) {
+    const uint64_t v = i < I ? bconv_input<uint64_t>(d, pcs, i, coeff) : 0;
+    y0[i] = (uint32_t)v & 0x3fffffffu;
+    y1[i] = (uint32_t)(v >> 30);
+  }
+#pragma unroll 2
+  for (int j = 0; j < O; j++) {
+    const uint2* f = sfac + j * I;
+    uint64_t c0 = 0, c1 = 0, c2 = 0;
 #pragma unroll
     for (int i = 0; i < kRegI; i++) {
       if (i < I) {
-        W v = d.in[(size_t)i * d.in_stride + coeff];
-        if (d.in_add != nullptr || d.inv != nullptr) {
-          const W qi = pcs[d.in_prime[i]].q;
-          if (d.in_add != nullptr) v = add_mod<W>(v, d.in_add[i], qi);
-          if (d.inv != nullptr) v = csub<W>(mul_shoup_lazy<W>(v, d.inv[i], d.inv_shoup[i], qi), qi);
-        }
-        y[i] = v;
-      } else {
-        y[i] = 0;
+        const uint2 fi = f[i];
+        c0 += (uint64_t)y0[i] * fi.x;
+        c1 += (uint64_t)y0[i] * fi.y;
+        c1 += (uint64_t)y1[i] * fi.x;
+        c2 += (uint64_t)y1[i] * fi.y;
       }
     }
-  } else {
-    for (int i = 0; i < I; i++) {
-      W v = d.in[(size_t)i * d.in_stride + coeff];
-      if (d.in_add != nullptr || d.inv != nullptr) {
-        const W qi = pcs[d.in_prime[i]].q;
-        if (d.in_add != nullptr) v = add_mod<W>(v, d.in_add[i], qi);
-        if (d.inv != nullptr) v = csub<W>(mul_shoup_lazy<W>(v, d.inv[i], d.inv_shoup[i], qi), qi);
-      }
-      scol[i * kBconvThreads + tid] = v;
-    }
+    // value = c0 + c1 * 2^30 + c2 * 2^60 as hi:lo
+    uint64_t lo = c0, hi = (c1 >> 34) + (c2 >> 4);
+    const uint64_t t1 = c1 << 30, t2 = c2 << 60;
+    lo += t1;
+    hi += lo < t1 ? 1 : 0;
+    lo += t2;
+    hi += lo < t2 ? 1 : 0;
+    const BconvOut<uint64_t> o = sout[j];
+    uint64_t r = barrett2_fast(hi, lo, o.q, o.q2, o.mu_hi, o.mu_lo);
+    r = sub_mod<uint64_t>(r, o.sub, o.q);
+    d.out[(size_t)o.pos * d.out_stride + coeff] = r;
   }
+}
+
+// Generic path (32-bit words, or more than 8 inputs): two-word accumulator, one Barrett
+// reduction per output; inputs in registers (kRegI > 0) or in the thread's shared-memory column.
+template <typename W, int kRegI>
+__device__ __forceinline__ void bconv_body(const BconvDesc<W>& d, const PrimeConst<W>* __restrict__ pcs,
+                                           const W* sfac, const BconvOut<W>* sout, W* scol, int coeff) {
+  const int tid = threadIdx.x;
+  const int I = d.I, O = d.O;
+  W y[kRegI > 0 ? kRegI : 1];
+  if (kRegI > 0) {
+#pragma unroll
+    for (int i = 0; i < kRegI; i++) y[i] = i < I ? bconv_input<W>(d, pcs, i, coeff) : (W)0;
+  } else {
+    for (int i = 0; i < I; i++) scol[i * kBconvThreads + tid] = bconv_input<W>(d, pcs, i, coeff);
+  }
+#pragma unroll 2
   for (int j = 0; j < O; j++) {
-    const PrimeConst<W> pc = pcs[d.out_prime[j]];
     const W* f = sfac + j * I;
     Acc2<W> acc;
     acc.clear();
@@ -86,14 +143,18 @@ __device__ __forceinline__ void bconv_body(const BconvDesc<W>& d, const PrimeCon
     } else {
       for (int i = 0; i < I; i++) acc.mad(scol[i * kBconvThreads + tid], f[i]);
     }
+    const BconvOut<W> o = sout[j];
+    PrimeConst<W> pc;
+    pc.q = o.q;
+    pc.q2 = o.q2;
+    pc.mu_hi = o.mu_hi;
+    pc.mu_lo = o.mu_lo;
     W r = barrett2<W>(acc.hi, acc.lo, pc);
-    if (d.out_sub != nullptr) r = sub_mod<W>(r, d.out_sub[j], pc.q);
-    d.out[(size_t)(d.out_pos != nullptr ? d.out_pos[j] : (uint32_t)j) * d.out_stride + coeff] = r;
+    r = sub_mod<W>(r, o.sub, o.q);
+    d.out[(size_t)o.pos * d.out_stride + coeff] = r;
   }
 }
 
-// grid = (N / 256, conversions), block = 256,
-// dynamic smem = O*I*sizeof(W) (+ I*256*sizeof(W) when I > kBconvRegInputs), maxima over the batch.
 constexpr int kBconvMaxBatch = 24;  // conversions per launch (descriptors travel as parameters)
 
 template <typename W>
@@ -101,22 +162,67 @@ struct BconvBatch {
   BconvDesc<W> d[kBconvMaxBatch];
 };
 
+// Shared-memory need of one conversion (bytes): factor matrix, per-output constants and, for
+// more than kBconvRegInputs inputs, one column of inputs per thread.
+template <typename W>
+__host__ __device__ inline size_t bconv_smem_bytes(int I, int O) {
+  size_t n = (size_t)O * I * sizeof(W);
+  n = (n + 15) / 16 * 16 + (size_t)O * sizeof(BconvOut<W>);
+  if (I > kBconvRegInputs) n += (size_t)I * kBconvThreads * sizeof(W);
+  return n;
+}
+
+// grid = (N / 256, conversions), block = 256, dynamic smem = max bconv_smem_bytes over the batch.
 template <typename W>
 __global__ void __launch_bounds__(kBconvThreads)
     bconv_kernel(const BconvBatch<W> batch, const PrimeConst<W>* __restrict__ pcs) {
   CERIUM_DYN_SMEM(smem_raw);
   const BconvDesc<W>& d = batch.d[blockIdx.y];
+  const int I = d.I, O = d.O;
   W* sfac = reinterpret_cast<W*>(smem_raw);
-  W* scol = sfac + d.O * d.I;
-  for (int k = threadIdx.x; k < d.O * d.I; k += kBconvThreads) sfac[k] = d.factors[k];
+  const size_t fac_bytes = ((size_t)O * I * sizeof(W) + 15) / 16 * 16;
+  BconvOut<W>* sout = reinterpret_cast<BconvOut<W>*>(smem_raw + fac_bytes);
+  W* scol = reinterpret_cast<W*>(smem_raw + fac_bytes + (size_t)O * sizeof(BconvOut<W>));
+  const bool split = sizeof(W) == 8 && I <= kBconvRegInputs;
+  for (int k = threadIdx.x; k < O * I; k += kBconvThreads) {
+    const W f = d.factors[k];
+    if (split) {
+      // the split path reads the factor as two 30-bit pieces
+      const uint64_t f64 = (uint64_t)f;
+      reinterpret_cast<uint2*>(sfac)[k] = make_uint2((uint32_t)f64 & 0x3fffffffu, (uint32_t)(f64 >> 30));
+    } else {
+      sfac[k] = f;
+    }
+  }
+  for (int j = threadIdx.x; j < O; j += kBconvThreads) {
+    const PrimeConst<W> pc = pcs[d.out_prime[j]];
+    BconvOut<W> o;
+    o.q = pc.q;
+    o.q2 = pc.q2;
+    o.mu_hi = pc.mu_hi;
+    o.mu_lo = pc.mu_lo;
+    o.sub = d.out_sub != nullptr ? d.out_sub[j] : (W)0;
+    o.pos = d.out_pos != nullptr ? d.out_pos[j] : (uint32_t)j;
+    o.pad = 0;
+    sout[j] = o;
+  }
   __syncthreads();
   const int coeff = blockIdx.x * kBconvThreads + threadIdx.x;
-  if (d.I <= 4)
-    bconv_body<W, 4>(d, pcs, sfac, scol, coeff);
-  else if (d.I <= kBconvRegInputs)
-    bconv_body<W, kBconvRegInputs>(d, pcs, sfac, scol, coeff);
-  else
-    bconv_body<W, 0>(d, pcs, sfac, scol, coeff);
+  if (sizeof(W) == 8 && I <= kBconvRegInputs) {
+    const BconvDesc<uint64_t>& d64 = reinterpret_cast<const BconvDesc<uint64_t>&>(d);
+    const PrimeConst<uint64_t>* p64 = reinterpret_cast<const PrimeConst<uint64_t>*>(pcs);
+    const uint2* f2 = reinterpret_cast<const uint2*>(sfac);
+    const BconvOut<uint64_t>* so = reinterpret_cast<const BconvOut<uint64_t>*>(sout);
+    if (I <= 2) bconv_body_split64<2>(d64, p64, f2, so, coeff);
+    else if (I <= 5) bconv_body_split64<5>(d64, p64, f2, so, coeff);
+    else bconv_body_split64<kBconvRegInputs>(d64, p64, f2, so, coeff);
+  } else if (I <= 5) {
+    bconv_body<W, 5>(d, pcs, sfac, sout, scol, coeff);
+  } else if (I <= kBconvRegInputs) {
+    bconv_body<W, kBconvRegInputs>(d, pcs, sfac, sout, scol, coeff);
+  } else {
+    bconv_body<W, 0>(d, pcs, sfac, sout, scol, coeff);
+  }
 }
 
 }  // namespace cerium

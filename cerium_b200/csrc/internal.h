@@ -76,6 +76,8 @@ struct cerium_context {
   std::vector<uint64_t> psi;
   void* d_tw_fwd = nullptr;  // Pair[n_primes][N], bit-reversed powers of psi
   void* d_tw_inv = nullptr;  // Pair[n_primes][N], bit-reversed powers of psi^-1
+  void* d_twr_fwd = nullptr; // Pair[n_primes][256][15][16], lane-interleaved level-3 twiddles (row pass)
+  void* d_twr_inv = nullptr; // same for the inverse transform
   void* d_pcs = nullptr;     // PrimeConst<W>[n_primes]
   size_t word_bytes() const { return (size_t)word_bits / 8; }
 };

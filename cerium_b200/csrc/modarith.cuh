@@ -61,7 +61,8 @@ struct PrimeConst {
   W ninv_shoup;  //
   W w1ninv;      // psi^-(N/2) * N^-1 mod q  (inverse twiddle of index 1 times N^-1)
   W w1ninv_shoup;
-  W pad[7];
+  W lazy_ok;     // 1 when q < 2^52 (64-bit words only): butterflies may skip range corrections
+  W pad[6];
 };
 
 // x * w mod q in [0, 2q) for ANY word x, given ws = floor(w * 2^B / q) with w < q.
@@ -123,6 +124,86 @@ struct Acc2 {
     hi += (lo < a ? (W)1 : (W)0);
   }
 };
+
+// ---------------------------------------------------------------------------------------
+// 64-bit fast path.  On sm_100 a 32-bit IMAD / IMAD.WIDE issues at half rate (64 lanes per
+// SM per clock) and a 64-bit butterfly is bound by that pipe plus the carry/compare/select
+// instructions around it, so the products are spelled out in 32-bit pieces:
+//   mulhi_approx64  3 wide multiplies instead of the 4 (+ carries) of mul.hi.u64; drops the
+//                   low partial product, so it returns floor(a*b / 2^64) - e with e in {0,1,2}
+//   lo_madd64       low 64 bits of x*w + h*nq as 2 wide multiply-adds + 4 mad.lo, no carries
+// A Shoup product built from them is x*w mod q in [0, 4q) for any 64-bit x.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t mulhi_approx64(uint64_t a, uint64_t b) {
+#if defined(CERIUM_EMU)
+  const uint64_t a0 = (uint32_t)a, a1 = a >> 32, b0 = (uint32_t)b, b1 = b >> 32;
+  return a1 * b1 + ((a0 * b1) >> 32) + ((a1 * b0) >> 32);
+#else
+  uint32_t a0, a1, b0, b1;
+  asm("mov.b64 {%0,%1}, %2;" : "=r"(a0), "=r"(a1) : "l"(a));
+  asm("mov.b64 {%0,%1}, %2;" : "=r"(b0), "=r"(b1) : "l"(b));
+  uint64_t t, u, h;
+  asm("mul.wide.u32 %0, %1, %2;" : "=l"(t) : "r"(a0), "r"(b1));
+  asm("mul.wide.u32 %0, %1, %2;" : "=l"(u) : "r"(a1), "r"(b0));
+  asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(h) : "r"(a1), "r"(b1), "l"(t >> 32));
+  return h + (u >> 32);
+#endif
+}
+
+__device__ __forceinline__ uint64_t lo_madd64(uint64_t x, uint64_t w, uint64_t h, uint64_t nq) {
+#if defined(CERIUM_EMU)
+  return x * w + h * nq;
+#else
+  uint32_t x0, x1, w0, w1, h0, h1, n0, n1, lo, hi;
+  asm("mov.b64 {%0,%1}, %2;" : "=r"(x0), "=r"(x1) : "l"(x));
+  asm("mov.b64 {%0,%1}, %2;" : "=r"(w0), "=r"(w1) : "l"(w));
+  asm("mov.b64 {%0,%1}, %2;" : "=r"(h0), "=r"(h1) : "l"(h));
+  asm("mov.b64 {%0,%1}, %2;" : "=r"(n0), "=r"(n1) : "l"(nq));
+  uint64_t acc;
+  asm("mul.wide.u32 %0, %1, %2;" : "=l"(acc) : "r"(x0), "r"(w0));
+  asm("mad.wide.u32 %0, %1, %2, %0;" : "+l"(acc) : "r"(h0), "r"(n0));
+  asm("mov.b64 {%0,%1}, %2;" : "=r"(lo), "=r"(hi) : "l"(acc));
+  asm("mad.lo.u32 %0, %1, %2, %0;" : "+r"(hi) : "r"(x0), "r"(w1));
+  asm("mad.lo.u32 %0, %1, %2, %0;" : "+r"(hi) : "r"(x1), "r"(w0));
+  asm("mad.lo.u32 %0, %1, %2, %0;" : "+r"(hi) : "r"(h0), "r"(n1));
+  asm("mad.lo.u32 %0, %1, %2, %0;" : "+r"(hi) : "r"(h1), "r"(n0));
+  uint64_t r;
+  asm("mov.b64 %0, {%1,%2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+#endif
+}
+
+// x*w mod q in [0, 4q) for any 64-bit x; nq = 2^64 - q.
+__device__ __forceinline__ uint64_t mul_shoup_approx(uint64_t x, uint64_t w, uint64_t ws, uint64_t nq) {
+  return lo_madd64(x, w, mulhi_approx64(x, ws), nq);
+}
+// 32-bit words have no fast path: the exact product (in [0, 2q)) stands in.
+__device__ __forceinline__ uint32_t mul_shoup_approx(uint32_t x, uint32_t w, uint32_t ws, uint32_t nq) {
+  return x * w + __umulhi(x, ws) * nq;
+}
+
+// Lazy butterflies (primes below 2^52): no range correction inside a pass.
+//   forward: inputs below B -> outputs below B + 4q           (B <= 61q keeps 16 layers exact)
+//   inverse: layer k of a pass takes inputs below 4q * 2^k, c = 4q * 2^k keeps a - b positive;
+//            sums double per layer, products come back below 4q
+template <typename W>
+__device__ __forceinline__ void butterfly_fwd_lazy(W& a, W& b, W w, W ws, W nq, W q4) {
+  const W v = mul_shoup_approx(b, w, ws, nq);
+  const W u = a;
+  a = u + v;
+  b = u + q4 - v;
+}
+template <typename W>
+__device__ __forceinline__ void butterfly_inv_lazy(W& a, W& b, W w, W ws, W nq, W c) {
+  const W d = a + c - b;
+  a = a + b;
+  b = mul_shoup_approx(d, w, ws, nq);
+}
+// any value -> [0, 4q)
+template <typename W>
+__device__ __forceinline__ W reduce_lazy(W x, W one_shoup, W nq) {
+  return mul_shoup_approx(x, (W)1, one_shoup, nq);
+}
 
 // Harvey forward butterfly: a, b in [0, 4q) -> [0, 4q).
 template <typename W>

@@ -39,6 +39,9 @@ struct NttCfg<uint32_t> {
 };
 
 constexpr int kRowsPerCta = 16;    // row pass: 16 rows of 256 coefficients, 256 threads
+// Lane-interleaved level-3 twiddles: [row h (256)][e = 2^t - 1 + g (15)][thread u (16)] pairs per
+// prime; entry = bit-reversed table[((4096 + 16 h + u) << t) + g].
+constexpr int kRowTwPerPrime = 256 * 15 * 16;
 constexpr int kMaxBatch = 512;     // limbs per launch
 
 // Addressing of a batch of limbs: batch entry b lives at base + pos[b] * stride; its modulus
@@ -70,6 +73,34 @@ struct PointerBatch {
 };
 
 // ---------------------------------------------------------------------------------------
+// arithmetic policies
+// ---------------------------------------------------------------------------------------
+
+// Strict (Harvey) butterflies keep every value below 4q (forward) / 2q (inverse) with one
+// correction per butterfly; they serve 32-bit words and 64-bit primes of 52 bits or more.
+// Lazy butterflies (64-bit words, primes below 2^52) use the headroom above the prime instead
+// of corrections and the 32-bit-piece products of modarith.cuh.
+template <typename W, bool kLazy>
+struct Arith {
+  W q, q2, q4, nq;
+  __device__ __forceinline__ explicit Arith(W q_) : q(q_), q2(q_ + q_), q4(q_ * 4), nq((W)0 - q_) {}
+  __device__ __forceinline__ void fwd(W& a, W& b, W w, W ws) const {
+    if (kLazy) butterfly_fwd_lazy<W>(a, b, w, ws, nq, q4);
+    else butterfly_fwd<W>(a, b, w, ws, q, q2);
+  }
+  // k = layer number inside the pass (0..7)
+  __device__ __forceinline__ void inv(W& a, W& b, W w, W ws, int k) const {
+    if (kLazy) butterfly_inv_lazy<W>(a, b, w, ws, nq, q4 << k);
+    else butterfly_inv<W>(a, b, w, ws, q, q2);
+  }
+  // value at the end of a forward transform -> [0, q)
+  __device__ __forceinline__ W finish_fwd(W x, W one_shoup) const {
+    if (kLazy) x = reduce_lazy<W>(x, one_shoup, nq);
+    return csub<W>(csub<W>(x, q2), q);
+  }
+};
+
+// ---------------------------------------------------------------------------------------
 // radix-16 register kernels
 // ---------------------------------------------------------------------------------------
 
@@ -80,50 +111,58 @@ __device__ __forceinline__ typename WordTraits<W>::Pair load_tw(const typename W
   return t[idx];
 }
 
+// Twiddle addressing of a radix-16 group.  Plain: entry (S << t) + g of the bit-reversed table.
+// Lane-interleaved (kLaneTable): the group's 15 twiddles sit at entries e * 16, e = 2^t - 1 + g,
+// of a table pre-permuted so that the 16 threads of a row read 16 consecutive entries.
+template <bool kLaneTable>
+__device__ __forceinline__ uint32_t tw_index(uint32_t S, int t, int g) {
+  return kLaneTable ? (uint32_t)(((1 << t) - 1 + g) * 16) : (S << t) + (uint32_t)g;
+}
+
 // Four forward layers on x[0..15]; layer t pairs (j, j + (8 >> t)).
-template <typename W, bool kGlobalTw>
+template <typename W, bool kGlobalTw, bool kLazy, bool kLaneTable = false>
 __device__ __forceinline__ void radix16_fwd(W (&x)[16], const typename WordTraits<W>::Pair* tw,
-                                            uint32_t S, W q, W q2) {
+                                            uint32_t S, const Arith<W, kLazy>& ar) {
 #pragma unroll
   for (int t = 0; t < 4; t++) {
     const int half = 8 >> t;
 #pragma unroll
     for (int g = 0; g < (1 << t); g++) {
-      const auto w = load_tw<W, kGlobalTw>(tw, (S << t) + g);
+      const auto w = load_tw<W, kGlobalTw>(tw, tw_index<kLaneTable>(S, t, g));
 #pragma unroll
       for (int k = 0; k < half; k++) {
         const int j = g * 2 * half + k;
-        butterfly_fwd<W>(x[j], x[j + half], w.x, w.y, q, q2);
+        ar.fwd(x[j], x[j + half], w.x, w.y);
       }
     }
   }
 }
 
-// The four inverse layers of the same group, in reverse order.
-template <typename W, bool kGlobalTw>
+// The four inverse layers of the same group, in reverse order; kLayer0 is the pass-local
+// number of the first layer executed (0 for the first level of a pass, 4 for the second).
+template <typename W, bool kGlobalTw, bool kLazy, int kLayer0, bool kLaneTable = false>
 __device__ __forceinline__ void radix16_inv(W (&x)[16], const typename WordTraits<W>::Pair* twi,
-                                            uint32_t S, W q, W q2) {
+                                            uint32_t S, const Arith<W, kLazy>& ar) {
 #pragma unroll
   for (int t = 3; t >= 0; t--) {
     const int half = 8 >> t;
 #pragma unroll
     for (int g = 0; g < (1 << t); g++) {
-      const auto w = load_tw<W, kGlobalTw>(twi, (S << t) + g);
+      const auto w = load_tw<W, kGlobalTw>(twi, tw_index<kLaneTable>(S, t, g));
 #pragma unroll
       for (int k = 0; k < half; k++) {
         const int j = g * 2 * half + k;
-        butterfly_inv<W>(x[j], x[j + half], w.x, w.y, q, q2);
+        ar.inv(x[j], x[j + half], w.x, w.y, kLayer0 + 3 - t);
       }
     }
   }
 }
 
-// Level 0 of the inverse transform (S = 1): the last layer also multiplies by N^-1 and
-// reduces to [0, q).
-template <typename W>
+// Level 0 of the inverse transform (S = 1, layers 4..7 of the column pass): the last layer
+// also multiplies by N^-1 and reduces to [0, q).
+template <typename W, bool kLazy>
 __device__ __forceinline__ void radix16_inv_final(W (&x)[16], const typename WordTraits<W>::Pair* twi,
-                                                  const PrimeConst<W>& pc) {
-  const W q = pc.q, q2 = pc.q2;
+                                                  const PrimeConst<W>& pc, const Arith<W, kLazy>& ar) {
 #pragma unroll
   for (int t = 3; t >= 1; t--) {
     const int half = 8 >> t;
@@ -133,16 +172,21 @@ __device__ __forceinline__ void radix16_inv_final(W (&x)[16], const typename Wor
 #pragma unroll
       for (int k = 0; k < half; k++) {
         const int j = g * 2 * half + k;
-        butterfly_inv<W>(x[j], x[j + half], w.x, w.y, q, q2);
+        ar.inv(x[j], x[j + half], w.x, w.y, 4 + 3 - t);
       }
     }
   }
 #pragma unroll
   for (int j = 0; j < 8; j++) {
-    const W s = x[j] + x[j + 8];         // < 4q
-    const W d = x[j] + q2 - x[j + 8];    // < 4q
-    x[j] = csub<W>(mul_shoup_lazy<W>(s, pc.ninv, pc.ninv_shoup, q), q);
-    x[j + 8] = csub<W>(mul_shoup_lazy<W>(d, pc.w1ninv, pc.w1ninv_shoup, q), q);
+    const W s = x[j] + x[j + 8];
+    const W d = x[j] + (kLazy ? (ar.q4 << 7) : ar.q2) - x[j + 8];
+    if (kLazy) {
+      x[j] = csub<W>(csub<W>(mul_shoup_approx(s, pc.ninv, pc.ninv_shoup, ar.nq), ar.q2), ar.q);
+      x[j + 8] = csub<W>(csub<W>(mul_shoup_approx(d, pc.w1ninv, pc.w1ninv_shoup, ar.nq), ar.q2), ar.q);
+    } else {
+      x[j] = csub<W>(mul_shoup_lazy<W>(s, pc.ninv, pc.ninv_shoup, ar.q), ar.q);
+      x[j + 8] = csub<W>(mul_shoup_lazy<W>(d, pc.w1ninv, pc.w1ninv_shoup, ar.q), ar.q);
+    }
   }
 }
 
@@ -150,6 +194,40 @@ __device__ __forceinline__ void radix16_inv_final(W (&x)[16], const typename Wor
 // consecutive access pattern free of bank conflicts.
 __device__ __forceinline__ int row_pos(int i) { return i + (i >> 4); }
 constexpr int kRowPitch = 256 + 16;
+
+// Staging buffer that turns "each thread owns 16 consecutive words of its row" into
+// "consecutive threads own consecutive 16-byte vectors" (and back) without bank conflicts.
+// A row is 256 words = kVecPerRow vectors of 16 bytes; thread u owns vectors u * kVecPerThread
+// + jj.  Vector v is stored at slot v ^ ((v >> 3) & (kVecPerThread - 1)) of its row: both the
+// owner's accesses (8 threads, same jj) and the coalesced accesses (8 consecutive v) then fall
+// into 8 different 16-byte bank groups.
+template <typename W>
+struct RowVec;
+template <>
+struct RowVec<uint64_t> {
+  using Vec = ulonglong2;
+  static constexpr int kWords = 2, kPerThread = 8, kPerRow = 128;
+};
+template <>
+struct RowVec<uint32_t> {
+  using Vec = uint4;
+  static constexpr int kWords = 4, kPerThread = 4, kPerRow = 64;
+};
+template <typename W>
+__device__ __forceinline__ int row_vec_slot(int v) {
+  return v ^ ((v >> 3) & (RowVec<W>::kPerThread - 1));
+}
+__device__ __forceinline__ void vec_unpack(const ulonglong2& v, uint64_t* w) { w[0] = v.x; w[1] = v.y; }
+__device__ __forceinline__ void vec_unpack(const uint4& v, uint32_t* w) { w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; }
+__device__ __forceinline__ ulonglong2 vec_pack(const uint64_t* w) { return make_ulonglong2(w[0], w[1]); }
+__device__ __forceinline__ uint4 vec_pack(const uint32_t* w) { return make_uint4(w[0], w[1], w[2], w[3]); }
+
+// Runs body(bool_constant<lazy>) with the arithmetic policy of this CTA's prime.
+#define CERIUM_DISPATCH_LAZY(W, pc, CALL_LAZY, CALL_STRICT) \
+  do {                                                       \
+    if (sizeof(W) == 8 && (pc).lazy_ok != 0) { CALL_LAZY; }  \
+    else { CALL_STRICT; }                                    \
+  } while (0)
 
 // ---------------------------------------------------------------------------------------
 // forward transform
@@ -179,10 +257,35 @@ struct ReduceLoader {
   }
 };
 
+template <typename W, bool kLazy, typename Batch, typename Loader>
+__device__ __forceinline__ void ntt_fwd_cols_body(const Batch& batch, const Loader& loader, int b,
+                                                  const PrimeConst<W>& pc, W* tile,
+                                                  const typename WordTraits<W>::Pair* stw) {
+  constexpr int kCols = NttCfg<W>::kCols;
+  const Arith<W, kLazy> ar(pc.q);
+  const int tid = threadIdx.x, c = tid % kCols, u = tid / kCols;
+  const int col = blockIdx.x * kCols + c;
+  const W* in = batch.in_limb(b);
+  W* out = batch.out_limb(b);
+  W x[16];
+#pragma unroll
+  for (int j = 0; j < 16; j++) x[j] = loader.apply(in[(j * 16 + u) * 256 + col], b, pc);
+  __syncthreads();
+  radix16_fwd<W, false, kLazy>(x, stw, 1u, ar);
+#pragma unroll
+  for (int j = 0; j < 16; j++) tile[(j * 16 + u) * kCols + c] = x[j];
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 16; j++) x[j] = tile[(u * 16 + j) * kCols + c];
+  radix16_fwd<W, false, kLazy>(x, stw, 16u + (uint32_t)u, ar);
+#pragma unroll
+  for (int j = 0; j < 16; j++) out[(u * 16 + j) * 256 + col] = x[j];
+}
+
 // Column pass (levels 0 and 1).  grid = (256 / kCols, limbs), block = 16 * kCols.
 // Element (h, l) of a limb is word h * 256 + l; the CTA owns kCols adjacent columns.
 template <typename W, typename Batch, typename Loader>
-__global__ void __launch_bounds__(NttCfg<W>::kCols * 16)
+__global__ void __launch_bounds__(NttCfg<W>::kCols * 16, sizeof(W) == 8 ? 3 : 2)
     ntt_fwd_cols_kernel(const Batch batch, const Loader loader,
                         const typename WordTraits<W>::Pair* __restrict__ tw_all,
                         const PrimeConst<W>* __restrict__ pcs) {
@@ -193,26 +296,9 @@ __global__ void __launch_bounds__(NttCfg<W>::kCols * 16)
   const int b = blockIdx.y;
   const uint32_t pi = batch.prime_of(b);
   const PrimeConst<W> pc = pcs[pi];
-  const W q = pc.q, q2 = pc.q2;
-  const Pair* tw = tw_all + (size_t)pi * kN;
-  const int tid = threadIdx.x, c = tid % kCols, u = tid / kCols;
-  const int col = blockIdx.x * kCols + c;
-  if (tid < 256) stw[tid] = __ldg(tw + tid);
-  const W* in = batch.in_limb(b);
-  W* out = batch.out_limb(b);
-  W x[16];
-#pragma unroll
-  for (int j = 0; j < 16; j++) x[j] = loader.apply(in[(j * 16 + u) * 256 + col], b, pc);
-  __syncthreads();
-  radix16_fwd<W, false>(x, stw, 1u, q, q2);
-#pragma unroll
-  for (int j = 0; j < 16; j++) tile[(j * 16 + u) * kCols + c] = x[j];
-  __syncthreads();
-#pragma unroll
-  for (int j = 0; j < 16; j++) x[j] = tile[(u * 16 + j) * kCols + c];
-  radix16_fwd<W, false>(x, stw, 16u + (uint32_t)u, q, q2);
-#pragma unroll
-  for (int j = 0; j < 16; j++) out[(u * 16 + j) * 256 + col] = x[j];
+  if (threadIdx.x < 256) stw[threadIdx.x] = __ldg(tw_all + (size_t)pi * kN + threadIdx.x);
+  CERIUM_DISPATCH_LAZY(W, pc, (ntt_fwd_cols_body<W, true>(batch, loader, b, pc, tile, stw)),
+                       (ntt_fwd_cols_body<W, false>(batch, loader, b, pc, tile, stw)));
 }
 
 // What the row pass does with the finished (canonical) NTT value.
@@ -283,21 +369,14 @@ __device__ __forceinline__ void load16<uint32_t>(const uint32_t* src, uint32_t (
   }
 }
 
-// Row pass (levels 2 and 3): reads the column pass's result from the batch's `in` stack and
-// writes the finished transform to its `out` stack (the two may be the same buffer).
-// grid = (256 / kRowsPerCta, limbs), block = 16 * kRowsPerCta; 16 threads own one row.
-template <typename W, typename Batch, typename Epilogue>
-__global__ void __launch_bounds__(kRowsPerCta * 16)
-    ntt_fwd_rows_kernel(const Batch batch, const Epilogue epi,
-                        const typename WordTraits<W>::Pair* __restrict__ tw_all,
-                        const PrimeConst<W>* __restrict__ pcs) {
-  using Pair = typename WordTraits<W>::Pair;
-  __shared__ W tile[kRowsPerCta * kRowPitch];
-  const int b = blockIdx.y;
-  const uint32_t pi = batch.prime_of(b);
-  const PrimeConst<W> pc = pcs[pi];
-  const W q = pc.q, q2 = pc.q2;
-  const Pair* tw = tw_all + (size_t)pi * kN;
+template <typename W, bool kLazy, typename Batch, typename Epilogue>
+__device__ __forceinline__ void ntt_fwd_rows_body(const Batch& batch, const Epilogue& epi, int b, uint32_t pi,
+                                                  const PrimeConst<W>& pc, W* tile,
+                                                  const typename WordTraits<W>::Pair* tw,
+                                                  const typename WordTraits<W>::Pair* twr) {
+  using RV = RowVec<W>;
+  using Vec = typename RV::Vec;
+  const Arith<W, kLazy> ar(pc.q);
   const int tid = threadIdx.x, r = tid >> 4, u = tid & 15;
   const int h = blockIdx.x * kRowsPerCta + r;
   const W* row = batch.in_limb(b) + h * 256;
@@ -306,52 +385,109 @@ __global__ void __launch_bounds__(kRowsPerCta * 16)
   W x[16];
 #pragma unroll
   for (int j = 0; j < 16; j++) x[j] = row[j * 16 + u];
-  radix16_fwd<W, true>(x, tw, 256u + (uint32_t)h, q, q2);
+  radix16_fwd<W, true, kLazy>(x, tw, 256u + (uint32_t)h, ar);
 #pragma unroll
   for (int j = 0; j < 16; j++) trow[row_pos(j * 16 + u)] = x[j];
   __syncthreads();
 #pragma unroll
   for (int j = 0; j < 16; j++) x[j] = trow[row_pos(u * 16 + j)];
-  radix16_fwd<W, true>(x, tw, (256u + (uint32_t)h) * 16u + (uint32_t)u, q, q2);
+  // level 3: this thread's 15 twiddles from the lane-interleaved table of row h
+  radix16_fwd<W, true, kLazy, true>(x, twr + ((size_t)h * 15 * 16 + u), 0u, ar);
 #pragma unroll
-  for (int j = 0; j < 16; j++) {
-    const W v = csub<W>(csub<W>(x[j], q2), q);
-    x[j] = epi.apply(v, b, h * 256 + u * 16 + j, pi, pc);
+  for (int j = 0; j < 16; j++) x[j] = ar.finish_fwd(x[j], pc.one_shoup);
+  // own 16 words -> swizzled vectors -> coalesced vectors, then epilogue and store
+  __syncthreads();
+  Vec* vrow = reinterpret_cast<Vec*>(tile) + r * RV::kPerRow;
+#pragma unroll
+  for (int jj = 0; jj < RV::kPerThread; jj++)
+    vrow[row_vec_slot<W>(u * RV::kPerThread + jj)] = vec_pack(&x[jj * RV::kWords]);
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < RV::kPerThread; k++) {
+    const int v = u + 16 * k;
+    W w[RV::kWords];
+    vec_unpack(vrow[row_vec_slot<W>(v)], w);
+#pragma unroll
+    for (int e = 0; e < RV::kWords; e++) w[e] = epi.apply(w[e], b, h * 256 + v * RV::kWords + e, pi, pc);
+    reinterpret_cast<Vec*>(drow)[v] = vec_pack(w);
   }
-  store16<W>(drow + u * 16, x);
+}
+
+// Row pass (levels 2 and 3): reads the column pass's result from the batch's `in` stack and
+// writes the finished transform to its `out` stack (the two may be the same buffer).
+// grid = (256 / kRowsPerCta, limbs), block = 16 * kRowsPerCta; 16 threads own one row.
+template <typename W, typename Batch, typename Epilogue>
+__global__ void __launch_bounds__(kRowsPerCta * 16, 3)
+    ntt_fwd_rows_kernel(const Batch batch, const Epilogue epi,
+                        const typename WordTraits<W>::Pair* __restrict__ tw_all,
+                        const typename WordTraits<W>::Pair* __restrict__ twr_all,
+                        const PrimeConst<W>* __restrict__ pcs) {
+  using Pair = typename WordTraits<W>::Pair;
+  __shared__ __align__(16) W tile[kRowsPerCta * kRowPitch];
+  const int b = blockIdx.y;
+  const uint32_t pi = batch.prime_of(b);
+  const PrimeConst<W> pc = pcs[pi];
+  const Pair* tw = tw_all + (size_t)pi * kN;
+  const Pair* twr = twr_all + (size_t)pi * kRowTwPerPrime;
+  CERIUM_DISPATCH_LAZY(W, pc, (ntt_fwd_rows_body<W, true>(batch, epi, b, pi, pc, tile, tw, twr)),
+                       (ntt_fwd_rows_body<W, false>(batch, epi, b, pi, pc, tile, tw, twr)));
 }
 
 // ---------------------------------------------------------------------------------------
 // inverse transform
 // ---------------------------------------------------------------------------------------
 
-// Row pass (levels 3 and 2): in -> out, values in [0, 2q).
-template <typename W, typename Batch>
-__global__ void __launch_bounds__(kRowsPerCta * 16)
-    ntt_inv_rows_kernel(const Batch batch, const typename WordTraits<W>::Pair* __restrict__ twi_all,
-                        const PrimeConst<W>* __restrict__ pcs) {
-  using Pair = typename WordTraits<W>::Pair;
-  __shared__ W tile[kRowsPerCta * kRowPitch];
-  const int b = blockIdx.y;
-  const uint32_t pi = batch.prime_of(b);
-  const W q = pcs[pi].q, q2 = pcs[pi].q2;
-  const Pair* twi = twi_all + (size_t)pi * kN;
+template <typename W, bool kLazy, typename Batch>
+__device__ __forceinline__ void ntt_inv_rows_body(const Batch& batch, int b, const PrimeConst<W>& pc, W* tile,
+                                                  const typename WordTraits<W>::Pair* twi,
+                                                  const typename WordTraits<W>::Pair* twri) {
+  using RV = RowVec<W>;
+  using Vec = typename RV::Vec;
+  const Arith<W, kLazy> ar(pc.q);
   const int tid = threadIdx.x, r = tid >> 4, u = tid & 15;
   const int h = blockIdx.x * kRowsPerCta + r;
   const W* src = batch.in_limb(b) + h * 256;
   W* dst = batch.out_limb(b) + h * 256;
   W* trow = tile + r * kRowPitch;
+  // coalesced vectors -> swizzled staging -> own 16 consecutive words
+  Vec* vrow = reinterpret_cast<Vec*>(tile) + r * RV::kPerRow;
+#pragma unroll
+  for (int k = 0; k < RV::kPerThread; k++) {
+    const int v = u + 16 * k;
+    vrow[row_vec_slot<W>(v)] = reinterpret_cast<const Vec*>(src)[v];
+  }
+  __syncthreads();
   W x[16];
-  load16<W>(src + u * 16, x);
-  radix16_inv<W, true>(x, twi, (256u + (uint32_t)h) * 16u + (uint32_t)u, q, q2);
+#pragma unroll
+  for (int jj = 0; jj < RV::kPerThread; jj++)
+    vec_unpack(vrow[row_vec_slot<W>(u * RV::kPerThread + jj)], &x[jj * RV::kWords]);
+  radix16_inv<W, true, kLazy, 0, true>(x, twri + ((size_t)h * 15 * 16 + u), 0u, ar);
+  __syncthreads();
 #pragma unroll
   for (int j = 0; j < 16; j++) trow[row_pos(u * 16 + j)] = x[j];
   __syncthreads();
 #pragma unroll
   for (int j = 0; j < 16; j++) x[j] = trow[row_pos(j * 16 + u)];
-  radix16_inv<W, true>(x, twi, 256u + (uint32_t)h, q, q2);
+  radix16_inv<W, true, kLazy, 4>(x, twi, 256u + (uint32_t)h, ar);
 #pragma unroll
   for (int j = 0; j < 16; j++) dst[j * 16 + u] = x[j];
+}
+
+// Row pass (levels 3 and 2): in -> out; values leave in [0, 2q) (strict) or below 2^10 q (lazy).
+template <typename W, typename Batch>
+__global__ void __launch_bounds__(kRowsPerCta * 16, 3)
+    ntt_inv_rows_kernel(const Batch batch, const typename WordTraits<W>::Pair* __restrict__ twi_all,
+                        const typename WordTraits<W>::Pair* __restrict__ twri_all,
+                        const PrimeConst<W>* __restrict__ pcs) {
+  using Pair = typename WordTraits<W>::Pair;
+  __shared__ __align__(16) W tile[kRowsPerCta * kRowPitch];
+  const int b = blockIdx.y;
+  const uint32_t pi = batch.prime_of(b);
+  const PrimeConst<W> pc = pcs[pi];
+  const Pair* twi = twi_all + (size_t)pi * kN;
+  const Pair* twri = twri_all + (size_t)pi * kRowTwPerPrime;
+  CERIUM_DISPATCH_LAZY(W, pc, (ntt_inv_rows_body<W, true>(batch, b, pc, tile, twi, twri)),
+                       (ntt_inv_rows_body<W, false>(batch, b, pc, tile, twi, twri)));
 }
 
 // Optional per-limb scalar applied to the finished inverse transform (exact base
@@ -362,10 +498,43 @@ struct InvScale {
   const W* scale_shoup;  // per batch entry
 };
 
+template <typename W, bool kLazy, typename Batch>
+__device__ __forceinline__ void ntt_inv_cols_body(const Batch& batch, const InvScale<W>& sc, int b,
+                                                  const PrimeConst<W>& pc, W* tile,
+                                                  const typename WordTraits<W>::Pair* stw) {
+  constexpr int kCols = NttCfg<W>::kCols;
+  const Arith<W, kLazy> ar(pc.q);
+  const W q = pc.q;
+  const int tid = threadIdx.x, c = tid % kCols, u = tid / kCols;
+  const int col = blockIdx.x * kCols + c;
+  W* buf = batch.out_limb(b);
+  W x[16];
+#pragma unroll
+  for (int j = 0; j < 16; j++) {
+    x[j] = buf[(u * 16 + j) * 256 + col];
+    if (kLazy) x[j] = reduce_lazy<W>(x[j], pc.one_shoup, ar.nq);  // back below 4q for the second pass
+  }
+  __syncthreads();
+  radix16_inv<W, false, kLazy, 0>(x, stw, 16u + (uint32_t)u, ar);
+#pragma unroll
+  for (int j = 0; j < 16; j++) tile[(u * 16 + j) * kCols + c] = x[j];
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 16; j++) x[j] = tile[(j * 16 + u) * kCols + c];
+  radix16_inv_final<W, kLazy>(x, stw, pc, ar);
+  if (sc.scale != nullptr) {
+    const W s = __ldg(sc.scale + b), ss = __ldg(sc.scale_shoup + b);
+#pragma unroll
+    for (int j = 0; j < 16; j++) x[j] = csub<W>(mul_shoup_lazy<W>(x[j], s, ss, q), q);
+  }
+#pragma unroll
+  for (int j = 0; j < 16; j++) buf[(j * 16 + u) * 256 + col] = x[j];
+}
+
 // Column pass (levels 1 and 0), in place on the output limb of the row pass; scales by
 // N^-1 and reduces to [0, q).
 template <typename W, typename Batch>
-__global__ void __launch_bounds__(NttCfg<W>::kCols * 16)
+__global__ void __launch_bounds__(NttCfg<W>::kCols * 16, sizeof(W) == 8 ? 3 : 2)
     ntt_inv_cols_kernel(const Batch batch, const InvScale<W> sc,
                         const typename WordTraits<W>::Pair* __restrict__ twi_all,
                         const PrimeConst<W>* __restrict__ pcs) {
@@ -376,30 +545,9 @@ __global__ void __launch_bounds__(NttCfg<W>::kCols * 16)
   const int b = blockIdx.y;
   const uint32_t pi = batch.prime_of(b);
   const PrimeConst<W> pc = pcs[pi];
-  const W q = pc.q, q2 = pc.q2;
-  const Pair* twi = twi_all + (size_t)pi * kN;
-  const int tid = threadIdx.x, c = tid % kCols, u = tid / kCols;
-  const int col = blockIdx.x * kCols + c;
-  if (tid < 256) stw[tid] = __ldg(twi + tid);
-  W* buf = batch.out_limb(b);
-  W x[16];
-#pragma unroll
-  for (int j = 0; j < 16; j++) x[j] = buf[(u * 16 + j) * 256 + col];
-  __syncthreads();
-  radix16_inv<W, false>(x, stw, 16u + (uint32_t)u, q, q2);
-#pragma unroll
-  for (int j = 0; j < 16; j++) tile[(u * 16 + j) * kCols + c] = x[j];
-  __syncthreads();
-#pragma unroll
-  for (int j = 0; j < 16; j++) x[j] = tile[(j * 16 + u) * kCols + c];
-  radix16_inv_final<W>(x, stw, pc);
-  if (sc.scale != nullptr) {
-    const W s = __ldg(sc.scale + b), ss = __ldg(sc.scale_shoup + b);
-#pragma unroll
-    for (int j = 0; j < 16; j++) x[j] = csub<W>(mul_shoup_lazy<W>(x[j], s, ss, q), q);
-  }
-#pragma unroll
-  for (int j = 0; j < 16; j++) buf[(j * 16 + u) * 256 + col] = x[j];
+  if (threadIdx.x < 256) stw[threadIdx.x] = __ldg(twi_all + (size_t)pi * kN + threadIdx.x);
+  CERIUM_DISPATCH_LAZY(W, pc, (ntt_inv_cols_body<W, true>(batch, sc, b, pc, tile, stw)),
+                       (ntt_inv_cols_body<W, false>(batch, sc, b, pc, tile, stw)));
 }
 
 }  // namespace cerium

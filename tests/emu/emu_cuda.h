@@ -36,7 +36,7 @@ static inline ulonglong2 make_ulonglong2(unsigned long long a, unsigned long lon
 #define __launch_bounds__(...)
 #define __restrict__
 #define __shared__ static thread_local
-#define __align__(n) alignas(n)
+#define __align__(n) __attribute__((aligned(n)))
 
 namespace cerium_emu {
 extern thread_local uint3 t_threadIdx, t_blockIdx;
