@@ -52,6 +52,7 @@ SIGNATURES = {
     "cerium_hrot": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, C.c_uint32, _vp]),
     "cerium_hmult": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_int, _vp]),
     "cerium_rescale": (C.c_int, [_vp, C.c_int, _vp, _vp, _u32p, C.c_int, C.c_int, _vp, _vp]),
+    "cerium_rescale_static": (C.c_int, [_vp, C.c_int, _vp, _vp, _u32p, C.c_int, C.c_int, _vp]),
 }
 
 
@@ -173,6 +174,13 @@ class Context:
                 round_mode: int = ROUND_FLOOR, stream: int = 0):
         self.lib.check(self.lib.dll.cerium_rescale(self.h, round_mode, out, inp, _u32(q_idx), len(q_idx), n_polys,
                                                    scratch, stream))
+
+
+    def rescale_static(self, out: int, inp: int, q_idx: Sequence[int], n_polys: int,
+                       round_mode: int = ROUND_FLOOR, stream: int = 0):
+        """Rescale with the library's built-in scratch (no device allocation anywhere; n_polys <= 2)."""
+        self.lib.check(self.lib.dll.cerium_rescale_static(self.h, round_mode, out, inp, _u32(q_idx), len(q_idx),
+                                                          n_polys, stream))
 
 
 class BaseConverter:

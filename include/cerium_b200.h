@@ -213,6 +213,25 @@ CERIUM_API int cerium_hmult(cerium_keyswitch *ks, void *out0, void *out1, const 
 CERIUM_API int cerium_rescale(cerium_context *ctx, int round_mode, void *out, const void *in,
                    const uint32_t *q_idx, int L, int n_polys, void *scratch, void *stream);
 
+/*
+ * cerium_rescale for callers that cannot allocate (no counterpart in the reference, whose runtime
+ * always owns its buffers).  Same result as cerium_rescale, but the n_polys * N words of scratch
+ * live in a fixed 1 MiB device array inside the library instead of being passed in: meant for
+ * hosts that have no device memory left to hand out, or that must not call cudaMalloc where they
+ * evaluate (an arena-only runtime, a plug-in without an allocation budget, a latency-critical
+ * section, since cudaMalloc synchronises the device).  Limits and rules:
+ *   - n_polys <= 2 (one ciphertext); more is refused with CERIUM_ERR_UNSUPPORTED;
+ *   - the first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress); make that first call before any stream capture begins;
+ *   - neither this call nor anything under it calls cudaMalloc / cudaFree;
+ *   - all calls on one device share the array.  It needs no clearing between calls (each call
+ *     overwrites what it later reads), but two calls whose kernels overlap on the GPU - on
+ *     different streams - race on it: keep them on one stream or order them with events;
+ *   - the array costs 1 MiB on every GPU that loads the library, used or not.
+ */
+CERIUM_API int cerium_rescale_static(cerium_context *ctx, int round_mode, void *out, const void *in,
+                                     const uint32_t *q_idx, int L, int n_polys, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
