@@ -150,16 +150,28 @@ class HRotWorkload(Workload):
         self.prm = params.config_hrot(LOGN, 35, 5, 7)
         self.n_cts = n_cts  # rotating set of ciphertexts so consecutive ops do not reuse inputs
 
-    def setup(self, lib, torch, rank):
+    def setup(self, lib, torch, rank, world=1, sharded=False):
         from cerium_b200 import _capi
         self.torch = torch
         prm = self.prm
+        self.sharded = sharded and world > 1
         self.ctx = _capi.Context(lib, prm.moduli, 64, device=torch.cuda.current_device())
-        self.ks = _capi.KeySwitch(self.ctx, prm.q_idx, prm.p_idx, prm.dnum, _capi.BCONV_LAZY, _capi.ROUND_FLOOR)
         gen = torch.Generator(device="cuda").manual_seed(0xCE210003 + rank)
-        all_idx = prm.q_idx + prm.p_idx
-        self.evk = _rand_limbs_gpu(torch, prm.moduli, all_idx, (prm.dnum, 2), gen)
-        self.cts = [_rand_limbs_gpu(torch, prm.moduli, prm.q_idx, (2,), gen) for _ in range(self.n_cts)]
+        if self.sharded:
+            # every rank holds its own limbs of the SAME ciphertexts and key (round-robin by limb)
+            from cerium_b200 import sharded as sh
+            dev = torch.device("cuda", torch.cuda.current_device())
+            self.sk = sh.ShardedKeySwitch(lib, self.ctx, prm, rank, world, _capi.BCONV_LAZY, _capi.ROUND_FLOOR,
+                                          device=dev)
+            q_loc = [prm.q_idx[i] for i in sh.local_limb_indices(prm.L, rank, world)]
+            all_idx = q_loc + prm.p_idx
+            self.evk = _rand_limbs_gpu(torch, prm.moduli, all_idx, (prm.dnum, 2), gen)
+            self.cts = [_rand_limbs_gpu(torch, prm.moduli, q_loc, (2,), gen) for _ in range(self.n_cts)]
+        else:
+            self.ks = _capi.KeySwitch(self.ctx, prm.q_idx, prm.p_idx, prm.dnum, _capi.BCONV_LAZY, _capi.ROUND_FLOOR)
+            all_idx = prm.q_idx + prm.p_idx
+            self.evk = _rand_limbs_gpu(torch, prm.moduli, all_idx, (prm.dnum, 2), gen)
+            self.cts = [_rand_limbs_gpu(torch, prm.moduli, prm.q_idx, (2,), gen) for _ in range(self.n_cts)]
         self.outs = [torch.empty_like(self.cts[0]) for _ in range(self.n_cts)]
         self.elt = hrot_galois_elt()
         self.i = 0
@@ -171,18 +183,22 @@ class HRotWorkload(Workload):
         self.host_out = torch.empty(self.cts[0].shape, dtype=torch.int64).pin_memory()
         self.gpu_launches_per_step = 2 + (2 + 1 + 2 + 1 + 2 + 1 + 4)
 
+    def _hrot(self, ct, out):
+        if self.sharded:
+            self.sk.hrot(out[0], out[1], ct[0], ct[1], self.evk, self.elt)
+        else:
+            self.ks.hrot(out[0].data_ptr(), out[1].data_ptr(), ct[0].data_ptr(), ct[1].data_ptr(),
+                         self.evk.data_ptr(), self.elt, self.torch.cuda.current_stream().cuda_stream)
+
     def step(self):
         k = self.i % self.n_cts
         self.i += 1
-        ct, out = self.cts[k], self.outs[k]
-        self.ks.hrot(out[0].data_ptr(), out[1].data_ptr(), ct[0].data_ptr(), ct[1].data_ptr(), self.evk.data_ptr(),
-                     self.elt, self.torch.cuda.current_stream().cuda_stream)
+        self._hrot(self.cts[k], self.outs[k])
 
     def e2e_step(self):
         ct, out = self.cts[0], self.outs[0]
         ct.copy_(self.host_in, non_blocking=True)
-        self.ks.hrot(out[0].data_ptr(), out[1].data_ptr(), ct[0].data_ptr(), ct[1].data_ptr(), self.evk.data_ptr(),
-                     self.elt, self.torch.cuda.current_stream().cuda_stream)
+        self._hrot(ct, out)
         self.host_out.copy_(out, non_blocking=True)
         return self.ct_bytes, self.ct_bytes
 
@@ -190,10 +206,16 @@ class HRotWorkload(Workload):
     def roofline_setup(self):
         prm = self.prm
         self.rl_idx = []
+        if getattr(self, "sharded", False):
+            from cerium_b200 import sharded as sh
+            mine = sh.local_limb_indices(prm.L, self.sk.rank, self.sk.world)
+        else:
+            mine = list(range(prm.L))
         for d in range(prm.dnum):
-            for i, p in enumerate(prm.q_idx + prm.p_idx):
-                if not (i < prm.L and i % prm.dnum == d):
-                    self.rl_idx.append(p)
+            for i in mine:
+                if i % prm.dnum != d:
+                    self.rl_idx.append(prm.q_idx[i])
+            self.rl_idx.extend(prm.p_idx)
         gen = self.torch.Generator(device="cuda").manual_seed(5)
         self.rl_buf = _rand_limbs_gpu(self.torch, prm.moduli, self.rl_idx, (), gen)
         self.rl_bytes = 2 * len(self.rl_idx) * N * 8  # read once + write once
@@ -235,7 +257,7 @@ class HMultWorkload(Workload):
     def __init__(self):
         self.prm = params.config_hmult(LOGN, 24)
 
-    def setup(self, lib, torch, rank):
+    def setup(self, lib, torch, rank, world=1, sharded=False):
         from cerium_b200 import _capi
         self.torch = torch
         prm = self.prm
@@ -309,7 +331,7 @@ class NttWorkload(Workload):
         self.idx = [l for _ in range(8) for l in range(48)]
         self.ops_per_step = 2 * len(self.idx)  # forward + inverse
 
-    def setup(self, lib, torch, rank):
+    def setup(self, lib, torch, rank, world=1, sharded=False):
         from cerium_b200 import _capi
         self.torch = torch
         self.ctx = _capi.Context(lib, self.moduli, 64, device=torch.cuda.current_device())
@@ -395,6 +417,9 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="hrot")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--parallelism", choices=["limb", "replica"], default="limb",
+                    help="N > 1: 'limb' shards every ciphertext and key by RNS limb over the ranks (one all-gather "
+                         "per key switch, strong scaling); 'replica' runs independent ciphertexts per rank")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]()
     if args.impl == "reference":
@@ -418,8 +443,10 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     lib = _capi.load()
-    wl.setup(lib, torch, rank)
+    sharded = world > 1 and args.parallelism == "limb" and args.workload == "hrot"
+    wl.setup(lib, torch, rank, world, sharded)
     ops = wl.ops_per_step
+    job_ops = 1 if sharded else world   # ops per step of the whole job: one sharded op, or one per replica
 
     def barrier():
         if world > 1:
@@ -479,15 +506,18 @@ def main():
 
     if rank == 0:
         peak, peak_kind = measured_peaks()
-        value = world * ops * args.steps / (ms / 1e3)
+        value = job_ops * ops * args.steps / (ms / 1e3)
         achieved = wl.rl_bytes / (rl_ms / 1e3) / 1e9
         line = {
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong" if sharded else "weak",
             "vs_baseline": None, "dtype": "u64", "data": "synthetic",
             "config": {"workload": wl.name, "l2": "working set larger than L2 (keys + ciphertexts + workspace > 126 MB)",
-                       "parallelism": "independent ciphertexts per GPU" if world > 1 else "single GPU"},
-            "e2e": {"value": world * ops * e2e_steps / e2e_s, "unit": wl.unit, "h2d_bytes_per_step": h2d,
+                       "parallelism": ("single GPU" if world == 1 else
+                                       "limb-sharded ciphertexts and keys, one NCCL all-gather per key switch" if sharded
+                                       else "independent ciphertexts per GPU")},
+            "e2e": {"value": job_ops * ops * e2e_steps / e2e_s, "unit": wl.unit, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h},
             "gpu_launches": wl.gpu_launches_per_step * args.steps,
             "roofline": {"bound": "hbm", "kernel": wl.rl_name, "achieved": achieved, "peak": peak, "unit": "GB/s",

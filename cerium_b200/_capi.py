@@ -46,6 +46,11 @@ SIGNATURES = {
     "cerium_bconv_destroy": (C.c_int, [_vp]),
     "cerium_bconv_apply": (C.c_int, [_vp, _vp, _sz, _vp, _sz, _vp]),
     "cerium_keyswitch_create": (C.c_int, [_vp, C.POINTER(_vp), C.c_int, C.c_int, _u32p, C.c_int, _u32p, C.c_int, C.c_int]),
+    "cerium_keyswitch_create_sharded": (C.c_int, [_vp, C.POINTER(_vp), C.c_int, C.c_int, _u32p, C.c_int, _u32p, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "cerium_keyswitch_local_limbs": (C.c_int, [_vp]),
+    "cerium_keyswitch_gather_limbs": (C.c_int, [_vp]),
+    "cerium_keyswitch_sharded_begin": (C.c_int, [_vp, _vp, _vp, _vp]),
+    "cerium_keyswitch_sharded_finish": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cerium_keyswitch_destroy": (C.c_int, [_vp]),
     "cerium_keyswitch_workspace_bytes": (_sz, [_vp]),
     "cerium_keyswitch_apply": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
@@ -215,13 +220,32 @@ class KeySwitch:
     """Hybrid key-switching plan (handle of ``cerium_keyswitch``)."""
 
     def __init__(self, ctx: Context, q_idx: Sequence[int], p_idx: Sequence[int], dnum: int,
-                 bconv_mode: int = BCONV_LAZY, round_mode: int = ROUND_FLOOR):
+                 bconv_mode: int = BCONV_LAZY, round_mode: int = ROUND_FLOOR, rank: int = 0, world: int = 1):
         self.ctx = ctx
         self.q_idx, self.p_idx, self.dnum = list(q_idx), list(p_idx), dnum
+        self.rank, self.world = rank, world
         h = _vp()
-        ctx.lib.check(ctx.lib.dll.cerium_keyswitch_create(ctx.h, C.byref(h), bconv_mode, round_mode, _u32(q_idx),
-                                                          len(q_idx), _u32(p_idx), len(p_idx), dnum))
+        ctx.lib.check(ctx.lib.dll.cerium_keyswitch_create_sharded(ctx.h, C.byref(h), bconv_mode, round_mode,
+                                                                  _u32(q_idx), len(q_idx), _u32(p_idx), len(p_idx),
+                                                                  dnum, rank, world))
         self.h = h
+
+    @property
+    def local_limbs(self) -> int:
+        return int(self.ctx.lib.dll.cerium_keyswitch_local_limbs(self.h))
+
+    @property
+    def gather_limbs(self) -> int:
+        return int(self.ctx.lib.dll.cerium_keyswitch_gather_limbs(self.h))
+
+    def sharded_begin(self, send: int, cpoly_local: int, stream: int = 0):
+        self.ctx.lib.check(self.ctx.lib.dll.cerium_keyswitch_sharded_begin(self.h, send, cpoly_local or None, stream))
+
+    def sharded_finish(self, out0: int, out1: int, gathered: int, cpoly_local: int, evk_local: int, add0: int = 0,
+                       add1: int = 0, stream: int = 0):
+        self.ctx.lib.check(self.ctx.lib.dll.cerium_keyswitch_sharded_finish(
+            self.h, out0 or None, out1 or None, gathered, cpoly_local or None, evk_local, add0 or None,
+            add1 or None, stream))
 
     @property
     def workspace_bytes(self) -> int:

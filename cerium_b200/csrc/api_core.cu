@@ -177,6 +177,7 @@ int create_bconv(cerium_context* ctx, cerium_bconv** out, int mode, const uint32
   if (mode != CERIUM_BCONV_LAZY && mode != CERIUM_BCONV_EXACT) return fail(CERIUM_ERR_INVALID, "bconv_create: unknown mode");
   if (n_in < 1 || n_in > 64 || n_out < 1 || n_out > 255) return fail(CERIUM_ERR_INVALID, "bconv_create: need 1..64 inputs and 1..255 outputs");
   if (!opt.out_pos.empty() && (int)opt.out_pos.size() != n_out) return fail(CERIUM_ERR_INVALID, "bconv_create: out_pos size");
+  if (!opt.in_pos.empty() && (int)opt.in_pos.size() != n_in) return fail(CERIUM_ERR_INVALID, "bconv_create: in_pos size");
   for (int i = 0; i < n_in; i++)
     if (in_primes[i] >= (uint32_t)ctx->n_primes) return fail(CERIUM_ERR_INVALID, "bconv_create: input prime index out of range");
   for (int j = 0; j < n_out; j++)
@@ -253,6 +254,7 @@ int create_bconv(cerium_context* ctx, cerium_bconv** out, int mode, const uint32
   const size_t o_ip = blob.append(bc->in_primes.data(), bc->in_primes.size() * 4);
   const size_t o_op = blob.append(bc->out_primes.data(), bc->out_primes.size() * 4);
   const size_t o_pos = blob.append(opt.out_pos.data(), opt.out_pos.size() * 4);
+  const size_t o_ipos = blob.append(opt.in_pos.data(), opt.in_pos.size() * 4);
   if (cudaMalloc(&bc->d_block, blob.bytes.size() + 16) != cudaSuccess) {
     delete bc;
     return fail(CERIUM_ERR_CUDA, "bconv_create: cudaMalloc failed");
@@ -271,6 +273,7 @@ int create_bconv(cerium_context* ctx, cerium_bconv** out, int mode, const uint32
   bc->d_in_prime = reinterpret_cast<uint32_t*>(base + o_ip);
   bc->d_out_prime = reinterpret_cast<uint32_t*>(base + o_op);
   bc->d_out_pos = opt.out_pos.empty() ? nullptr : reinterpret_cast<uint32_t*>(base + o_pos);
+  bc->d_in_pos = opt.in_pos.empty() ? nullptr : reinterpret_cast<uint32_t*>(base + o_ipos);
   *out = bc;
   return CERIUM_OK;
 }
@@ -284,6 +287,7 @@ int launch_bconv(cerium_context* ctx, const BconvCall* calls, int count, cudaStr
       const int cnt = std::min(kBconvMaxBatch, count - first);
       BconvBatch<W> batch{};
       size_t smem = 0;
+      int max_o = 1;
       for (int k = 0; k < cnt; k++) {
         const BconvCall& c = calls[first + k];
         const cerium_bconv* bc = c.bc;
@@ -300,9 +304,11 @@ int launch_bconv(cerium_context* ctx, const BconvCall* calls, int count, cudaStr
         d.in_prime = bc->d_in_prime;
         d.out_prime = bc->d_out_prime;
         d.out_pos = bc->d_out_pos;
+        d.in_pos = bc->d_in_pos;
         d.I = bc->I;
         d.O = bc->O;
-        smem = std::max(smem, bconv_smem_bytes<W>(bc->I, bc->O));
+        smem = std::max(smem, bconv_smem_bytes<W>(bc->I, std::min(bc->O, kBconvOutChunk)));
+        max_o = std::max(max_o, bc->O);
       }
       if (smem > 48 * 1024) {
         if (smem > 200 * 1024) return fail(CERIUM_ERR_UNSUPPORTED, "bconv: conversion needs more than 200 KiB of shared memory");
@@ -312,7 +318,7 @@ int launch_bconv(cerium_context* ctx, const BconvCall* calls, int count, cudaStr
           smem_opt_in[slot] = true;
         }
       }
-      { auto kfn = bconv_kernel<W>; CERIUM_LAUNCH(kfn, dim3(kN / kBconvThreads, cnt), kBconvThreads, smem, stream, batch, static_cast<const PrimeConst<W>*>(ctx->d_pcs)); }
+      { auto kfn = bconv_kernel<W>; CERIUM_LAUNCH(kfn, dim3(kN / kBconvThreads, cnt, (max_o + kBconvOutChunk - 1) / kBconvOutChunk), kBconvThreads, smem, stream, batch, static_cast<const PrimeConst<W>*>(ctx->d_pcs)); }
     }
     CERIUM_LAUNCH_CHECK("bconv");
     return CERIUM_OK;

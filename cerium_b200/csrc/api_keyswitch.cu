@@ -18,11 +18,19 @@
 
 using namespace cerium;
 
+// A plan covers the limbs one GPU owns.  With `world` GPUs, Q-limb i lives on rank i % world
+// (cerium/compiler/backend/terms.h:672-685) and the K extension limbs are replicated on every
+// rank (Term::Ext): "local extended limb" e < nloc is global limb loc[e], e >= nloc is extension
+// limb e - nloc.  L and LK below are the LOCAL counts (nloc and nloc + K); world = 1 makes them
+// the global ones.
 struct cerium_keyswitch {
   cerium_context* ctx = nullptr;
   int bconv_mode = 0, round_mode = 0;
   int L = 0, K = 0, dnum = 0, LK = 0;
-  std::vector<uint32_t> q_idx, p_idx, all_idx;
+  int L_global = 0, rank = 0, world = 1, gather_limbs = 0;  // gather_limbs = ceil(L_global / world)
+  std::vector<int> loc;            // global index of local Q-limb e
+  std::vector<int> own_digit;      // [LK] digit of local extended limb e, -1 for extension limbs
+  std::vector<uint32_t> q_idx, p_idx, all_idx;  // prime indices of the LOCAL limbs
   std::vector<cerium_bconv*> up;   // one converter per non-empty digit
   std::vector<int> up_digit;       // digit number of up[k]
   cerium_bconv* down = nullptr;    // P -> Q
@@ -102,29 +110,33 @@ int rescale_impl(cerium_context* ctx, int round_mode, void* out, const void* in,
   return CERIUM_OK;
 }
 
-int keyswitch_impl(cerium_keyswitch* ks, void* out0, void* out1, const void* cpoly, const void* evk,
-                   const void* add0, const void* add1, cudaStream_t stream) {
+// Step 1: inverse transform of the local limbs of the switched polynomial into `dst`
+// ([gather_limbs][N]; exact mode: times [Qhat_i^-1] of the limb's digit).
+int keyswitch_begin(cerium_keyswitch* ks, void* dst, const void* cpoly, cudaStream_t stream) {
+  const size_t n = kN;
+  NttCall c{cpoly, dst, n, n, nullptr, ks->q_idx.data(), ks->L};
+  return launch_ntt_inverse(ks->ctx, c, ks->d_scale_q, ks->d_scale_q_shoup, stream);
+}
+
+// Steps 2-7 from the coefficient-form limbs of ALL ranks (`gathered`: global limb i at slot
+// (i % world) * gather_limbs + i / world).
+int keyswitch_finish(cerium_keyswitch* ks, void* out0, void* out1, const void* gathered, const void* cpoly,
+                     const void* evk, const void* add0, const void* add1, cudaStream_t stream) {
   cerium_context* ctx = ks->ctx;
   const size_t n = kN;
   const int L = ks->L, K = ks->K, LK = ks->LK, dnum = ks->dnum;
   return dispatch_word(ctx->word_bits, [&](auto tag) -> int {
     using W = decltype(tag);
     using V = Vec16<W>;
-    W* coef = ws_at<W>(ks, ks->o_coef);
     W* raised = ws_at<W>(ks, ks->o_raised);
     W* acc = ws_at<W>(ks, ks->o_acc);
     W* conv = ws_at<W>(ks, ks->o_conv);
-    // 1. iNTT of the switched polynomial (exact mode: times [Qhat_i^-1] of its digit)
-    {
-      NttCall c{cpoly, coef, n, n, nullptr, ks->q_idx.data(), L};
-      if (int rc = launch_ntt_inverse(ctx, c, ks->d_scale_q, ks->d_scale_q_shoup, stream)) return rc;
-    }
-    // 2. ModUp base conversion, every digit in one launch.  Digit d reads limbs d, d+dnum, ...
+    // 2. ModUp base conversion, every digit in one launch
     {
       std::vector<BconvCall> calls;
       for (size_t k = 0; k < ks->up.size(); k++) {
         const int d = ks->up_digit[k];
-        calls.push_back(BconvCall{ks->up[k], raised + (size_t)d * LK * n, n, coef + (size_t)d * n, (size_t)dnum * n});
+        calls.push_back(BconvCall{ks->up[k], raised + (size_t)d * LK * n, n, gathered, n});
       }
       if (int rc = launch_bconv(ctx, calls.data(), (int)calls.size(), stream)) return rc;
     }
@@ -147,9 +159,11 @@ int keyswitch_impl(cerium_keyswitch* ks, void* out0, void* out1, const void* cpo
       g.evk_limb_stride = n;
       g.out0 = {acc, n};
       g.out1 = {acc + (size_t)LK * n, n};
-      g.L = L;
       g.dnum = dnum;
-      for (int b = 0; b < LK; b++) g.prime[b] = (uint8_t)ks->all_idx[b];
+      for (int b = 0; b < LK; b++) {
+        g.prime[b] = (uint8_t)ks->all_idx[b];
+        g.own_digit[b] = (int8_t)ks->own_digit[b];
+      }
       { auto kfn = inner_product_kernel<W>; CERIUM_LAUNCH(kfn, dim3(kN / (kEwThreads * V::kLanes), LK), kEwThreads, 0, stream, g, static_cast<const PrimeConst<W>*>(ctx->d_pcs)); }
       CERIUM_LAUNCH_CHECK("inner_product");
     }
@@ -158,7 +172,8 @@ int keyswitch_impl(cerium_keyswitch* ks, void* out0, void* out1, const void* cpo
       NttCall c{acc, acc, n, n, ks->ext_pos.data(), ks->ext_prime.data(), 2 * K};
       if (int rc = launch_ntt_inverse(ctx, c, ks->d_scale_p, ks->d_scale_p_shoup, stream)) return rc;
     }
-    // 6. ModDown base conversion P -> Q
+    if (L == 0) return CERIUM_OK;  // a rank without Q limbs only feeds the gather
+    // 6. ModDown base conversion P -> local Q limbs
     {
       BconvCall calls[2] = {
           {ks->down, conv, n, acc + (size_t)L * n, n},
@@ -188,23 +203,33 @@ int keyswitch_impl(cerium_keyswitch* ks, void* out0, void* out1, const void* cpo
   });
 }
 
+int keyswitch_impl(cerium_keyswitch* ks, void* out0, void* out1, const void* cpoly, const void* evk,
+                   const void* add0, const void* add1, cudaStream_t stream) {
+  if (ks->world != 1) return fail(CERIUM_ERR_INVALID, "keyswitch: a sharded plan needs the begin / finish calls around the all-gather");
+  void* coef = static_cast<char*>(ks->ws) + ks->o_coef * ks->ctx->word_bytes();
+  if (int rc = keyswitch_begin(ks, coef, cpoly, stream)) return rc;
+  return keyswitch_finish(ks, out0, out1, coef, cpoly, evk, add0, add1, stream);
+}
+
 }  // namespace
 
 extern "C" {
 
-int cerium_keyswitch_create(cerium_context* ctx, cerium_keyswitch** out, int bconv_mode, int round_mode,
-                            const uint32_t* q_idx, int L, const uint32_t* p_idx, int K, int dnum) {
+static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, int bconv_mode, int round_mode,
+                                 const uint32_t* q_idx, int Lg, const uint32_t* p_idx, int K, int dnum, int rank,
+                                 int world) {
   if (!ctx || !out || !q_idx || !p_idx) return fail(CERIUM_ERR_INVALID, "keyswitch_create: null argument");
   if (bconv_mode != CERIUM_BCONV_LAZY && bconv_mode != CERIUM_BCONV_EXACT) return fail(CERIUM_ERR_INVALID, "keyswitch_create: unknown bconv mode");
   if (round_mode != CERIUM_ROUND_FLOOR && round_mode != CERIUM_ROUND_HALF) return fail(CERIUM_ERR_INVALID, "keyswitch_create: unknown round mode");
-  if (L < 1 || K < 1 || dnum < 1 || dnum > L) return fail(CERIUM_ERR_INVALID, "keyswitch_create: need L >= 1, K >= 1, 1 <= dnum <= L");
-  if (L + K > kEwMaxLimbs || L > kSudMaxBatch) return fail(CERIUM_ERR_UNSUPPORTED, "keyswitch_create: too many limbs (L <= 64, L + K <= 128)");
-  const int alpha = (L + dnum - 1) / dnum;
+  if (Lg < 1 || K < 1 || dnum < 1 || dnum > Lg) return fail(CERIUM_ERR_INVALID, "keyswitch_create: need L >= 1, K >= 1, 1 <= dnum <= L");
+  if (world < 1 || rank < 0 || rank >= world) return fail(CERIUM_ERR_INVALID, "keyswitch_create: need 0 <= rank < world");
+  if (Lg + K > kEwMaxLimbs || Lg > kSudMaxBatch) return fail(CERIUM_ERR_UNSUPPORTED, "keyswitch_create: too many limbs (L <= 64, L + K <= 128)");
+  const int alpha = (Lg + dnum - 1) / dnum;
   if (alpha > K) return fail(CERIUM_ERR_INVALID, "keyswitch_create: digit size exceeds the number of extension primes");
-  if ((size_t)dnum * (L + K) > 0xffff) return fail(CERIUM_ERR_UNSUPPORTED, "keyswitch_create: dnum * (L + K) too large");
+  if ((size_t)dnum * (Lg + K) > 0xffff) return fail(CERIUM_ERR_UNSUPPORTED, "keyswitch_create: dnum * (L + K) too large");
   std::vector<bool> seen(ctx->n_primes, false);
-  for (int i = 0; i < L + K; i++) {
-    const uint32_t p = i < L ? q_idx[i] : p_idx[i - L];
+  for (int i = 0; i < Lg + K; i++) {
+    const uint32_t p = i < Lg ? q_idx[i] : p_idx[i - Lg];
     if (p >= (uint32_t)ctx->n_primes) return fail(CERIUM_ERR_INVALID, "keyswitch_create: prime index out of range");
     if (seen[p]) return fail(CERIUM_ERR_INVALID, "keyswitch_create: a prime appears twice");
     seen[p] = true;
@@ -215,38 +240,51 @@ int cerium_keyswitch_create(cerium_context* ctx, cerium_keyswitch** out, int bco
   ks->ctx = ctx;
   ks->bconv_mode = bconv_mode;
   ks->round_mode = round_mode;
-  ks->L = L;
   ks->K = K;
   ks->dnum = dnum;
+  ks->L_global = Lg;
+  ks->rank = rank;
+  ks->world = world;
+  ks->gather_limbs = (Lg + world - 1) / world;
+  for (int i = rank; i < Lg; i += world) {
+    ks->loc.push_back(i);
+    ks->q_idx.push_back(q_idx[i]);
+  }
+  const int L = (int)ks->loc.size();
+  ks->L = L;
   ks->LK = L + K;
-  ks->q_idx.assign(q_idx, q_idx + L);
   ks->p_idx.assign(p_idx, p_idx + K);
   ks->all_idx = ks->q_idx;
   ks->all_idx.insert(ks->all_idx.end(), ks->p_idx.begin(), ks->p_idx.end());
   const int LK = ks->LK;
+  for (int e = 0; e < LK; e++) ks->own_digit.push_back(e < L ? ks->loc[e] % dnum : -1);
   const int bits = ctx->word_bits;
   const bool exact = bconv_mode == CERIUM_BCONV_EXACT;
-  std::vector<uint64_t> scale_q(L, 1), scale_p(2 * K, 1);
+  std::vector<uint64_t> scale_q(std::max(L, 1), 1), scale_p(2 * K, 1);
+  auto slot_of = [&](int i) { return (uint32_t)((i % world) * ks->gather_limbs + i / world); };
   int rc = CERIUM_OK;
-  // per-digit converters: inputs {d, d+dnum, ...}, outputs every other extended limb
+  // per-digit converters: inputs = global limbs {d, d+dnum, ...} (read from the gathered buffer),
+  // outputs = every local extended limb outside the digit
   for (int d = 0; d < dnum && rc == CERIUM_OK; d++) {
-    std::vector<uint32_t> in_primes, out_primes, out_pos;
+    std::vector<uint32_t> in_primes, in_pos, out_primes, out_pos;
     std::vector<int> in_limb;
-    for (int i = 0; i < LK; i++) {
-      if (i < L && i % dnum == d) {
-        in_primes.push_back(ks->all_idx[i]);
-        in_limb.push_back(i);
-      } else {
-        out_primes.push_back(ks->all_idx[i]);
-        out_pos.push_back((uint32_t)i);
-        ks->ntt_pos.push_back((uint32_t)(d * LK + i));
-        ks->ntt_prime.push_back(ks->all_idx[i]);
-      }
+    for (int i = d; i < Lg; i += dnum) {
+      in_primes.push_back(q_idx[i]);
+      in_pos.push_back(slot_of(i));
+      in_limb.push_back(i);
     }
-    if (in_primes.empty()) continue;
+    for (int e = 0; e < LK; e++) {
+      if (ks->own_digit[e] == d) continue;
+      out_primes.push_back(ks->all_idx[e]);
+      out_pos.push_back((uint32_t)e);
+      ks->ntt_pos.push_back((uint32_t)(d * LK + e));
+      ks->ntt_prime.push_back(ks->all_idx[e]);
+    }
+    if (in_primes.empty() || out_primes.empty()) continue;
     BconvOptions opt;
     opt.prescaled = exact;
     opt.out_pos = out_pos;
+    opt.in_pos = in_pos;
     cerium_bconv* bc = nullptr;
     rc = create_bconv(ctx, &bc, bconv_mode, in_primes.data(), (int)in_primes.size(), out_primes.data(),
                       (int)out_primes.size(), opt);
@@ -254,15 +292,24 @@ int cerium_keyswitch_create(cerium_context* ctx, cerium_keyswitch** out, int bco
     ks->up.push_back(bc);
     ks->up_digit.push_back(d);
     if (exact)
-      for (size_t k = 0; k < in_limb.size(); k++) scale_q[in_limb[k]] = bc->inv_host[k];
+      for (size_t k = 0; k < in_limb.size(); k++)
+        if (in_limb[k] % world == rank) scale_q[in_limb[k] / world] = bc->inv_host[k];
   }
-  if (rc == CERIUM_OK) {
+  if (rc == CERIUM_OK && L > 0) {
     BconvOptions opt;
     opt.prescaled = exact;
     opt.round_half = round_mode == CERIUM_ROUND_HALF;
     rc = create_bconv(ctx, &ks->down, bconv_mode, ks->p_idx.data(), K, ks->q_idx.data(), L, opt);
-    if (rc == CERIUM_OK && exact)
-      for (int k = 0; k < K; k++) scale_p[k] = scale_p[K + k] = ks->down->inv_host[k];
+  }
+  if (rc == CERIUM_OK && exact) {
+    // [Phat_k^-1]_{p_k} does not depend on the output set
+    for (int k = 0; k < K; k++) {
+      const uint64_t pk = ctx->moduli[ks->p_idx[k]];
+      uint64_t prod = 1 % pk;
+      for (int j = 0; j < K; j++)
+        if (j != k) prod = host::mulmod(prod, ctx->moduli[ks->p_idx[j]] % pk, pk);
+      scale_p[k] = scale_p[K + k] = K > 1 ? host::invmod(prod, pk) : 1;
+    }
   }
   if (rc != CERIUM_OK) {
     cerium_keyswitch_destroy(ks);
@@ -310,12 +357,12 @@ int cerium_keyswitch_create(cerium_context* ctx, cerium_keyswitch** out, int bco
     off += limbs * n;
     return o;
   };
-  ks->o_coef = take(L);
+  ks->o_coef = take(world == 1 ? Lg : 0);
   ks->o_raised = take((size_t)dnum * LK);
   ks->o_acc = take(2 * (size_t)LK);
-  ks->o_conv = take(2 * (size_t)L);
-  ks->o_tmp = take(3 * (size_t)L);
-  ks->o_ksout = take(2 * (size_t)L);
+  ks->o_conv = take(2 * (size_t)std::max(L, 1));
+  ks->o_tmp = take(3 * (size_t)std::max(L, 1));
+  ks->o_ksout = take(2 * (size_t)std::max(L, 1));
   ks->o_scratch = take(2);
   ks->ws_bytes = off * wb;
   if (cudaMalloc(&ks->ws, ks->ws_bytes) != cudaSuccess) {
@@ -326,11 +373,41 @@ int cerium_keyswitch_create(cerium_context* ctx, cerium_keyswitch** out, int bco
   return CERIUM_OK;
 }
 
+int cerium_keyswitch_create(cerium_context* ctx, cerium_keyswitch** out, int bconv_mode, int round_mode,
+                            const uint32_t* q_idx, int L, const uint32_t* p_idx, int K, int dnum) {
+  return keyswitch_create_impl(ctx, out, bconv_mode, round_mode, q_idx, L, p_idx, K, dnum, 0, 1);
+}
+
+int cerium_keyswitch_create_sharded(cerium_context* ctx, cerium_keyswitch** out, int bconv_mode, int round_mode,
+                                    const uint32_t* q_idx, int L, const uint32_t* p_idx, int K, int dnum, int rank,
+                                    int world) {
+  return keyswitch_create_impl(ctx, out, bconv_mode, round_mode, q_idx, L, p_idx, K, dnum, rank, world);
+}
+
+int cerium_keyswitch_local_limbs(const cerium_keyswitch* ks) { return ks ? ks->L : 0; }
+int cerium_keyswitch_gather_limbs(const cerium_keyswitch* ks) { return ks ? ks->gather_limbs : 0; }
+
+int cerium_keyswitch_sharded_begin(cerium_keyswitch* ks, void* send, const void* cpoly_local, void* stream) {
+  if (!ks || !send) return fail(CERIUM_ERR_INVALID, "keyswitch_sharded_begin: null argument");
+  if (ks->L > 0 && !cpoly_local) return fail(CERIUM_ERR_INVALID, "keyswitch_sharded_begin: null polynomial");
+  DeviceGuard guard(ks->ctx->device);
+  return keyswitch_begin(ks, send, cpoly_local, (cudaStream_t)stream);
+}
+
+int cerium_keyswitch_sharded_finish(cerium_keyswitch* ks, void* out0, void* out1, const void* gathered,
+                                    const void* cpoly_local, const void* evk_local, const void* add0,
+                                    const void* add1, void* stream) {
+  if (!ks || !gathered || !evk_local) return fail(CERIUM_ERR_INVALID, "keyswitch_sharded_finish: null argument");
+  if (ks->L > 0 && (!out0 || !out1 || !cpoly_local)) return fail(CERIUM_ERR_INVALID, "keyswitch_sharded_finish: null argument");
+  DeviceGuard guard(ks->ctx->device);
+  return keyswitch_finish(ks, out0, out1, gathered, cpoly_local, evk_local, add0, add1, (cudaStream_t)stream);
+}
+
 int cerium_keyswitch_destroy(cerium_keyswitch* ks) {
   if (!ks) return CERIUM_OK;
   DeviceGuard guard(ks->ctx->device);
   for (cerium_bconv* b : ks->up) cerium_bconv_destroy(b);
-  cerium_bconv_destroy(ks->down);
+  if (ks->down) cerium_bconv_destroy(ks->down);
   cudaFree(ks->d_scale);
   cudaFree(ks->ws);
   delete ks;
@@ -349,6 +426,7 @@ int cerium_keyswitch_apply(cerium_keyswitch* ks, void* out0, void* out1, const v
 int cerium_hrot(cerium_keyswitch* ks, void* out0, void* out1, const void* c0, const void* c1, const void* evk,
                 uint32_t galois_elt, void* stream) {
   if (!ks || !out0 || !out1 || !c0 || !c1 || !evk) return fail(CERIUM_ERR_INVALID, "hrot: null argument");
+  if (ks->world != 1) return fail(CERIUM_ERR_INVALID, "hrot: sharded plans are driven through the begin / finish calls");
   if (!(galois_elt & 1) || galois_elt >= 2u * kN) return fail(CERIUM_ERR_INVALID, "hrot: Galois element is not valid");
   cerium_context* ctx = ks->ctx;
   DeviceGuard guard(ctx->device);
@@ -365,6 +443,7 @@ int cerium_hrot(cerium_keyswitch* ks, void* out0, void* out1, const void* c0, co
 int cerium_hmult(cerium_keyswitch* ks, void* out0, void* out1, const void* a0, const void* a1, const void* b0,
                  const void* b1, const void* evk, int do_rescale, void* stream) {
   if (!ks || !out0 || !out1 || !a0 || !a1 || !b0 || !b1 || !evk) return fail(CERIUM_ERR_INVALID, "hmult: null argument");
+  if (ks->world != 1) return fail(CERIUM_ERR_INVALID, "hmult: sharded plans are driven through the begin / finish calls");
   cerium_context* ctx = ks->ctx;
   if (do_rescale && ks->L < 2) return fail(CERIUM_ERR_INVALID, "hmult: cannot rescale a one-limb ciphertext");
   DeviceGuard guard(ctx->device);

@@ -22,6 +22,7 @@ namespace cerium {
 
 constexpr int kBconvThreads = 256;
 constexpr int kBconvRegInputs = 8;
+constexpr int kBconvOutChunk = 8;  // outputs per CTA: grid.z splits the output primes for load balance
 
 template <typename W>
 struct BconvDesc {
@@ -37,6 +38,7 @@ struct BconvDesc {
   const uint32_t* in_prime;   // [I] prime index of each input limb
   const uint32_t* out_prime;  // [O]
   const uint32_t* out_pos;    // [O] limb slot of output j inside `out`, or null (slot j)
+  const uint32_t* in_pos;     // [I] limb slot of input i inside `in`, or null (slot i)
   int I;
   int O;
 };
@@ -64,7 +66,7 @@ __device__ __forceinline__ uint64_t barrett2_fast(uint64_t hi, uint64_t lo, uint
 template <typename W>
 __device__ __forceinline__ W bconv_input(const BconvDesc<W>& d, const PrimeConst<W>* __restrict__ pcs, int i,
                                          int coeff) {
-  W v = d.in[(size_t)i * d.in_stride + coeff];
+  W v = d.in[(size_t)(d.in_pos != nullptr ? d.in_pos[i] : (uint32_t)i) * d.in_stride + coeff];
   if (d.in_add != nullptr || d.inv != nullptr) {
     const W qi = pcs[d.in_prime[i]].q;
     if (d.in_add != nullptr) v = add_mod<W>(v, d.in_add[i], qi);
@@ -77,31 +79,29 @@ __device__ __forceinline__ W bconv_input(const BconvDesc<W>& d, const PrimeConst
 // partial product is a 32x32->64 multiply-add into one of three column sums (y0*f0,
 // y0*f1 + y1*f0, y1*f1).  With pieces below 2^30 and at most 8 terms no column overflows, so
 // a multiply-accumulate is four IMAD.WIDE and no carry handling.
-template <int kRegI>
+template <int kI>  // exact number of inputs, 1..8
 __device__ __forceinline__ void bconv_body_split64(const BconvDesc<uint64_t>& d,
                                                    const PrimeConst<uint64_t>* __restrict__ pcs,
                                                    const uint2* sfac, const BconvOut<uint64_t>* sout, int coeff) {
-  const int I = d.I, O = d.O;
-  uint32_t y0[kRegI], y1[kRegI];
+  const int O = d.O;
+  uint32_t y0[kI], y1[kI];
 #pragma unroll
-  for (int i = 0; i < kRegI; i++) {
-    const uint64_t v = i < I ? bconv_input<uint64_t>(d, pcs, i, coeff) : 0;
+  for (int i = 0; i < kI; i++) {
+    const uint64_t v = bconv_input<uint64_t>(d, pcs, i, coeff);
     y0[i] = (uint32_t)v & 0x3fffffffu;
     y1[i] = (uint32_t)(v >> 30);
   }
 #pragma unroll 2
   for (int j = 0; j < O; j++) {
-    const uint2* f = sfac + j * I;
+    const uint2* f = sfac + j * kI;
     uint64_t c0 = 0, c1 = 0, c2 = 0;
 #pragma unroll
-    for (int i = 0; i < kRegI; i++) {
-      if (i < I) {
-        const uint2 fi = f[i];
-        c0 += (uint64_t)y0[i] * fi.x;
-        c1 += (uint64_t)y0[i] * fi.y;
-        c1 += (uint64_t)y1[i] * fi.x;
-        c2 += (uint64_t)y1[i] * fi.y;
-      }
+    for (int i = 0; i < kI; i++) {
+      const uint2 fi = f[i];
+      c0 += (uint64_t)y0[i] * fi.x;
+      c1 += (uint64_t)y0[i] * fi.y;
+      c1 += (uint64_t)y1[i] * fi.x;
+      c2 += (uint64_t)y1[i] * fi.y;
     }
     // value = c0 + c1 * 2^30 + c2 * 2^60 as hi:lo
     uint64_t lo = c0, hi = (c1 >> 34) + (c2 >> 4);
@@ -123,11 +123,11 @@ template <typename W, int kRegI>
 __device__ __forceinline__ void bconv_body(const BconvDesc<W>& d, const PrimeConst<W>* __restrict__ pcs,
                                            const W* sfac, const BconvOut<W>* sout, W* scol, int coeff) {
   const int tid = threadIdx.x;
-  const int I = d.I, O = d.O;
+  const int I = kRegI > 0 ? kRegI : d.I, O = d.O;  // kRegI > 0: exact number of inputs
   W y[kRegI > 0 ? kRegI : 1];
   if (kRegI > 0) {
 #pragma unroll
-    for (int i = 0; i < kRegI; i++) y[i] = i < I ? bconv_input<W>(d, pcs, i, coeff) : (W)0;
+    for (int i = 0; i < kRegI; i++) y[i] = bconv_input<W>(d, pcs, i, coeff);
   } else {
     for (int i = 0; i < I; i++) scol[i * kBconvThreads + tid] = bconv_input<W>(d, pcs, i, coeff);
   }
@@ -138,8 +138,7 @@ __device__ __forceinline__ void bconv_body(const BconvDesc<W>& d, const PrimeCon
     acc.clear();
     if (kRegI > 0) {
 #pragma unroll
-      for (int i = 0; i < kRegI; i++)
-        if (i < I) acc.mad(y[i], f[i]);
+      for (int i = 0; i < kRegI; i++) acc.mad(y[i], f[i]);
     } else {
       for (int i = 0; i < I; i++) acc.mad(scol[i * kBconvThreads + tid], f[i]);
     }
@@ -172,13 +171,24 @@ __host__ __device__ inline size_t bconv_smem_bytes(int I, int O) {
   return n;
 }
 
-// grid = (N / 256, conversions), block = 256, dynamic smem = max bconv_smem_bytes over the batch.
+// grid = (N / 256, conversions, ceil(max O / kBconvOutChunk)), block = 256,
+// dynamic smem = max bconv_smem_bytes over the batch.  CTA z handles outputs
+// [z * kBconvOutChunk, min(O, (z + 1) * kBconvOutChunk)) of its conversion.
 template <typename W>
 __global__ void __launch_bounds__(kBconvThreads)
     bconv_kernel(const BconvBatch<W> batch, const PrimeConst<W>* __restrict__ pcs) {
   CERIUM_DYN_SMEM(smem_raw);
-  const BconvDesc<W>& d = batch.d[blockIdx.y];
-  const int I = d.I, O = d.O;
+  BconvDesc<W> d = batch.d[blockIdx.y];
+  const int j_first = blockIdx.z * kBconvOutChunk;
+  if (j_first >= d.O) return;
+  // restrict the descriptor to this CTA's slice of the outputs
+  const int I = d.I, O = (d.O - j_first) < kBconvOutChunk ? (d.O - j_first) : kBconvOutChunk;
+  d.factors += (size_t)j_first * I;
+  d.out_prime += j_first;
+  if (d.out_sub != nullptr) d.out_sub += j_first;
+  if (d.out_pos != nullptr) d.out_pos += j_first;
+  const uint32_t pos_base = d.out_pos != nullptr ? 0u : (uint32_t)j_first;
+  d.O = O;
   W* sfac = reinterpret_cast<W*>(smem_raw);
   const size_t fac_bytes = ((size_t)O * I * sizeof(W) + 15) / 16 * 16;
   BconvOut<W>* sout = reinterpret_cast<BconvOut<W>*>(smem_raw + fac_bytes);
@@ -202,7 +212,7 @@ __global__ void __launch_bounds__(kBconvThreads)
     o.mu_hi = pc.mu_hi;
     o.mu_lo = pc.mu_lo;
     o.sub = d.out_sub != nullptr ? d.out_sub[j] : (W)0;
-    o.pos = d.out_pos != nullptr ? d.out_pos[j] : (uint32_t)j;
+    o.pos = d.out_pos != nullptr ? d.out_pos[j] : pos_base + (uint32_t)j;
     o.pad = 0;
     sout[j] = o;
   }
@@ -213,15 +223,28 @@ __global__ void __launch_bounds__(kBconvThreads)
     const PrimeConst<uint64_t>* p64 = reinterpret_cast<const PrimeConst<uint64_t>*>(pcs);
     const uint2* f2 = reinterpret_cast<const uint2*>(sfac);
     const BconvOut<uint64_t>* so = reinterpret_cast<const BconvOut<uint64_t>*>(sout);
-    if (I <= 2) bconv_body_split64<2>(d64, p64, f2, so, coeff);
-    else if (I <= 5) bconv_body_split64<5>(d64, p64, f2, so, coeff);
-    else bconv_body_split64<kBconvRegInputs>(d64, p64, f2, so, coeff);
-  } else if (I <= 5) {
-    bconv_body<W, 5>(d, pcs, sfac, sout, scol, coeff);
-  } else if (I <= kBconvRegInputs) {
-    bconv_body<W, kBconvRegInputs>(d, pcs, sfac, sout, scol, coeff);
+    switch (I) {
+      case 1: bconv_body_split64<1>(d64, p64, f2, so, coeff); break;
+      case 2: bconv_body_split64<2>(d64, p64, f2, so, coeff); break;
+      case 3: bconv_body_split64<3>(d64, p64, f2, so, coeff); break;
+      case 4: bconv_body_split64<4>(d64, p64, f2, so, coeff); break;
+      case 5: bconv_body_split64<5>(d64, p64, f2, so, coeff); break;
+      case 6: bconv_body_split64<6>(d64, p64, f2, so, coeff); break;
+      case 7: bconv_body_split64<7>(d64, p64, f2, so, coeff); break;
+      default: bconv_body_split64<8>(d64, p64, f2, so, coeff); break;
+    }
   } else {
-    bconv_body<W, 0>(d, pcs, sfac, sout, scol, coeff);
+    switch (I) {
+      case 1: bconv_body<W, 1>(d, pcs, sfac, sout, scol, coeff); break;
+      case 2: bconv_body<W, 2>(d, pcs, sfac, sout, scol, coeff); break;
+      case 3: bconv_body<W, 3>(d, pcs, sfac, sout, scol, coeff); break;
+      case 4: bconv_body<W, 4>(d, pcs, sfac, sout, scol, coeff); break;
+      case 5: bconv_body<W, 5>(d, pcs, sfac, sout, scol, coeff); break;
+      case 6: bconv_body<W, 6>(d, pcs, sfac, sout, scol, coeff); break;
+      case 7: bconv_body<W, 7>(d, pcs, sfac, sout, scol, coeff); break;
+      case 8: bconv_body<W, 8>(d, pcs, sfac, sout, scol, coeff); break;
+      default: bconv_body<W, 0>(d, pcs, sfac, sout, scol, coeff); break;
+    }
   }
 }
 

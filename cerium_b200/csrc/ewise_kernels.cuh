@@ -174,7 +174,7 @@ __global__ void __launch_bounds__(kEwThreads) automorph_kernel(const AutomorphAr
 // Key-switching inner product over the extended basis (L + K limbs):
 //   out0[b] = sum_d a_d[b] * evk[d][0][b],   out1[b] = sum_d a_d[b] * evk[d][1][b]
 // where a_d[b] is the raised digit d at limb b.  For the limbs that belong to digit d itself
-// (b < L and b % dnum == d) the raised value is the NTT-form input limb, which is read in
+// (own_digit[b] == d) the raised value is the NTT-form input limb, which is read in
 // place from `own` instead of from `raised` (cerium/compiler/backend/kernel_instruction.h:
 // 823-838 moves it; here it is never copied).
 // Restates the EVKMUL / EVKMUL_EXT groups of cerium/compiler/backend/compiler_keyswitch.cc:
@@ -191,9 +191,9 @@ struct InnerProductArgs {
   size_t evk_poly_stride;
   size_t evk_limb_stride;
   Limbs<W> out0, out1;    // [LK][N]
-  int L;
   int dnum;
-  uint8_t prime[kEwMaxLimbs];  // prime index of extended limb b
+  uint8_t prime[kEwMaxLimbs];     // prime index of extended limb b
+  int8_t own_digit[kEwMaxLimbs];  // digit that limb b belongs to (-1 for extension limbs)
 };
 
 template <typename W>
@@ -209,8 +209,10 @@ __global__ void __launch_bounds__(kEwThreads)
     acc0[l].clear();
     acc1[l].clear();
   }
+  const int own_digit = g.own_digit[b];
+#pragma unroll 2
   for (int d = 0; d < g.dnum; d++) {
-    const bool is_own = b < g.L && (b % g.dnum) == d;
+    const bool is_own = d == own_digit;
     const W* ap = is_own ? g.own + (size_t)b * g.own_stride + idx
                          : g.raised + (size_t)d * g.raised_digit_stride +
                                (size_t)b * g.raised_limb_stride + idx;

@@ -97,6 +97,7 @@ struct cerium_bconv {
   uint32_t* d_in_prime = nullptr;
   uint32_t* d_out_prime = nullptr;
   uint32_t* d_out_pos = nullptr;  // or null
+  uint32_t* d_in_pos = nullptr;   // or null
   std::vector<uint64_t> inv_host;  // [Qhat_i^-1]_{q_i}
 };
 
@@ -107,6 +108,7 @@ struct BconvOptions {
   bool prescaled = false;            // exact mode, inputs already multiplied by [Qhat_i^-1]
   bool round_half = false;           // add floor(prod_in/2) to inputs, subtract it from outputs
   std::vector<uint32_t> out_pos;     // output limb slots (empty = 0..O-1)
+  std::vector<uint32_t> in_pos;      // input limb slots (empty = 0..I-1)
 };
 
 int create_bconv(cerium_context* ctx, cerium_bconv** out, int mode, const uint32_t* in_primes, int n_in,

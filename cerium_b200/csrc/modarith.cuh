@@ -199,10 +199,27 @@ __device__ __forceinline__ void butterfly_inv_lazy(W& a, W& b, W w, W ws, W nq, 
   a = a + b;
   b = mul_shoup_approx(d, w, ws, nq);
 }
-// any value -> [0, 4q)
-template <typename W>
-__device__ __forceinline__ W reduce_lazy(W x, W one_shoup, W nq) {
-  return mul_shoup_approx(x, (W)1, one_shoup, nq);
+// any value -> [0, 4q): x - floor~(x / q) * q, the multiplication by 1 left out
+__device__ __forceinline__ uint64_t reduce_lazy(uint64_t x, uint64_t one_shoup, uint64_t nq) {
+  const uint64_t h = mulhi_approx64(x, one_shoup);
+#if defined(CERIUM_EMU)
+  return x + h * nq;
+#else
+  uint32_t h0, h1, n0, n1, lo, hi;
+  asm("mov.b64 {%0,%1}, %2;" : "=r"(h0), "=r"(h1) : "l"(h));
+  asm("mov.b64 {%0,%1}, %2;" : "=r"(n0), "=r"(n1) : "l"(nq));
+  uint64_t acc = x;
+  asm("mad.wide.u32 %0, %1, %2, %0;" : "+l"(acc) : "r"(h0), "r"(n0));
+  asm("mov.b64 {%0,%1}, %2;" : "=r"(lo), "=r"(hi) : "l"(acc));
+  asm("mad.lo.u32 %0, %1, %2, %0;" : "+r"(hi) : "r"(h0), "r"(n1));
+  asm("mad.lo.u32 %0, %1, %2, %0;" : "+r"(hi) : "r"(h1), "r"(n0));
+  uint64_t r;
+  asm("mov.b64 %0, {%1,%2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+#endif
+}
+__device__ __forceinline__ uint32_t reduce_lazy(uint32_t x, uint32_t one_shoup, uint32_t nq) {
+  return x + __umulhi(x, one_shoup) * nq;
 }
 
 // Harvey forward butterfly: a, b in [0, 4q) -> [0, 4q).

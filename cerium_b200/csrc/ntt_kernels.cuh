@@ -95,7 +95,7 @@ struct Arith {
   }
   // value at the end of a forward transform -> [0, q)
   __device__ __forceinline__ W finish_fwd(W x, W one_shoup) const {
-    if (kLazy) x = reduce_lazy<W>(x, one_shoup, nq);
+    if (kLazy) x = reduce_lazy(x, one_shoup, nq);
     return csub<W>(csub<W>(x, q2), q);
   }
 };
@@ -512,7 +512,7 @@ __device__ __forceinline__ void ntt_inv_cols_body(const Batch& batch, const InvS
 #pragma unroll
   for (int j = 0; j < 16; j++) {
     x[j] = buf[(u * 16 + j) * 256 + col];
-    if (kLazy) x[j] = reduce_lazy<W>(x[j], pc.one_shoup, ar.nq);  // back below 4q for the second pass
+    if (kLazy) x[j] = reduce_lazy(x[j], pc.one_shoup, ar.nq);  // back below 4q for the second pass
   }
   __syncthreads();
   radix16_inv<W, false, kLazy, 0>(x, stw, 16u + (uint32_t)u, ar);

@@ -179,6 +179,37 @@ CERIUM_API int cerium_keyswitch_destroy(cerium_keyswitch *ks);
 CERIUM_API size_t cerium_keyswitch_workspace_bytes(const cerium_keyswitch *ks);
 
 /*
+ * Limb-sharded plan for rank `rank` of `world` GPUs.  Q-limb i lives on rank i % world
+ * (cerium/compiler/backend/terms.h:672-685), the K extension limbs are replicated on every
+ * rank (Term::Ext), evaluation keys are sharded like the ciphertext
+ * (cerium/compiler/backend/compiler_partition.cc:446-470).  Every stack a sharded call takes
+ * holds the rank's own limbs only, in increasing global index:
+ *   polynomial  [n_local][N]                       n_local = cerium_keyswitch_local_limbs()
+ *   key         [dnum][c0|c1][n_local + K][N]
+ * The one exchange of a key switch is the all-gather of the coefficient-form limbs before base
+ * conversion (the reference's DRM group, cerium/compiler/backend/compiler_keyswitch.cc:323-335,
+ * cerium/runtime/execution/evaluator.cpp:1154-1251); the caller performs it between the two
+ * calls below with whatever transport it owns (NCCL all-gather):
+ *   cerium_keyswitch_sharded_begin   inverse transform of the local limbs into `send`
+ *                                    ([g][N], g = cerium_keyswitch_gather_limbs() = ceil(L / world);
+ *                                    slots past n_local are not written)
+ *   all-gather of `send` over the ranks into `gathered` ([world][g][N], rank-major)
+ *   cerium_keyswitch_sharded_finish  base conversion, NTT, inner product, ModDown on local limbs
+ * world = 1 reproduces cerium_keyswitch_create / cerium_keyswitch_apply.
+ */
+CERIUM_API int cerium_keyswitch_create_sharded(cerium_context *ctx, cerium_keyswitch **out, int bconv_mode,
+                                    int round_mode, const uint32_t *q_idx, int L,
+                                    const uint32_t *p_idx, int K, int dnum, int rank, int world);
+CERIUM_API int cerium_keyswitch_local_limbs(const cerium_keyswitch *ks);
+CERIUM_API int cerium_keyswitch_gather_limbs(const cerium_keyswitch *ks);
+CERIUM_API int cerium_keyswitch_sharded_begin(cerium_keyswitch *ks, void *send, const void *cpoly_local,
+                                   void *stream);
+CERIUM_API int cerium_keyswitch_sharded_finish(cerium_keyswitch *ks, void *out0, void *out1,
+                                    const void *gathered, const void *cpoly_local,
+                                    const void *evk_local, const void *add0, const void *add1,
+                                    void *stream);
+
+/*
  * out0,out1 [L][N] = ModDown( sum_d ModUp(digit d of cpoly) * evk[d] ); if add0 / add1 are
  * non-NULL they are added to out0 / out1 (the P*c0 pre-addition of the reference's PMU
  * group, which commutes with ModDown).  Restates keyswitch_ciphertext_impl

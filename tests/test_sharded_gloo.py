@@ -1,0 +1,107 @@
+"""Multi-rank path on CPU: world_size 2 and 3 `gloo` process groups drive the limb-sharded key
+switch / HRot (cerium_b200/sharded.py).  Compute runs on the emulation build (tests/emu), the
+all-gather on gloo; every rank's output limbs must equal the oracle's single-device result."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, word_bits, L, K, dnum, bconv_mode, round_mode, ret):
+    try:
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        os.environ["OMP_NUM_THREADS"] = "2"
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        import oracle
+        from cerium_b200 import _capi, sharded
+        from tests import parity_cases as pc
+        from tests.backends import EmuBackend
+        be = EmuBackend()
+        prm = pc.small_params(word_bits, L, K, dnum)
+        ctx = _capi.Context(be.lib, prm.moduli, word_bits)
+        rng = np.random.default_rng(21)             # same inputs on every rank
+        c0, c1, evk = pc.make_keyswitch_inputs(rng, prm)
+        octx = oracle.OracleContext(pc.LOGN, prm.moduli)
+        elt = be.lib.galois_elt_from_step(7, pc.LOGN)
+        want_ks = octx.keyswitch(bconv_mode, round_mode, prm.q_idx, prm.p_idx, dnum, c1, evk)
+        want_rot = octx.hrot(bconv_mode, round_mode, prm.q_idx, prm.p_idx, dnum, elt, c0, c1, evk)
+        tdt = torch.int64 if word_bits == 64 else torch.int32
+        ndt = np.int64 if word_bits == 64 else np.int32
+
+        def t(a):
+            return torch.from_numpy(np.ascontiguousarray(a).astype(np.uint64 if word_bits == 64 else np.uint32).view(ndt).copy())
+
+        sk = sharded.ShardedKeySwitch(be.lib, ctx, prm, rank, world, bconv_mode, round_mode)
+        mine = sharded.local_limb_indices(L, rank, world)
+        assert sk.n_local == len(mine) and sk.g == -(-L // world)
+        lc0, lc1 = sharded.shard_poly(t(c0), rank, world), sharded.shard_poly(t(c1), rank, world)
+        levk = sharded.shard_key(t(evk), L, rank, world)
+        o0 = torch.zeros((max(len(mine), 1), pc.N), dtype=tdt)
+        o1 = torch.zeros_like(o0)
+        sk.keyswitch(o0, o1, lc1, levk)
+        u = np.uint64 if word_bits == 64 else np.uint32
+        ok = True
+        if mine:
+            ok &= np.array_equal(o0.numpy().view(u)[:len(mine)].astype(np.uint64), want_ks[0][mine])
+            ok &= np.array_equal(o1.numpy().view(u)[:len(mine)].astype(np.uint64), want_ks[1][mine])
+        sk.hrot(o0, o1, lc0, lc1, levk, elt)
+        if mine:
+            ok &= np.array_equal(o0.numpy().view(u)[:len(mine)].astype(np.uint64), want_rot[0][mine])
+            ok &= np.array_equal(o1.numpy().view(u)[:len(mine)].astype(np.uint64), want_rot[1][mine])
+        flag = torch.tensor([1 if ok else 0])
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        ret[rank] = int(flag.item())
+        dist.destroy_process_group()
+    except Exception as e:  # surfaced by the parent
+        ret[rank] = "rank %d: %r" % (rank, e)
+        raise
+
+
+@pytest.mark.parametrize("world,word_bits,L,K,dnum,bm,rm", [
+    (2, 64, 5, 2, 3, 0, 0),    # ragged: ranks own 3 and 2 limbs, digits of size 2,2,1
+    (2, 64, 4, 1, 4, 1, 1),    # one digit per limb, exact conversion with rounding
+    (3, 32, 4, 2, 2, 0, 0),    # a rank with a single limb
+])
+def test_sharded_keyswitch_matches_single_device(world, word_bits, L, K, dnum, bm, rm):
+    sys.path.insert(0, os.path.join(ROOT, "tests", "emu"))
+    import build_emu
+    build_emu.build()
+    ctx = mp.get_context("spawn")
+    mgr = ctx.Manager()
+    ret = mgr.dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, word_bits, L, K, dnum, bm, rm, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(600)
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+    assert all(p.exitcode == 0 for p in procs), dict(ret)
+    assert all(ret.get(r) == 1 for r in range(world)), dict(ret)
+
+
+def test_local_limb_indices():
+    from cerium_b200 import sharded
+    assert sharded.local_limb_indices(35, 0, 8) == [0, 8, 16, 24, 32]
+    assert sharded.local_limb_indices(35, 7, 8) == [7, 15, 23, 31]
+    assert sorted(sum((sharded.local_limb_indices(35, r, 4) for r in range(4)), [])) == list(range(35))
