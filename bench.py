@@ -487,6 +487,7 @@ def main():
     torch.cuda.synchronize()
     rl_ms = r0.elapsed_time(r1) / rl_iters
     clocks = sampler.stop() if rank == 0 else None
+    probe = lib.probe_int_pipe(local_rank) if rank == 0 else None
 
     # end to end: host buffers in, host buffers out, through the same C ABI calls
     e2e_steps = max(5, min(args.steps, 50))
@@ -523,9 +524,15 @@ def main():
             "roofline": {"bound": "hbm", "kernel": wl.rl_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
                          "ms_per_launch_pair": rl_ms, "algorithmic_bytes": wl.rl_bytes},
+            # the 64-bit transforms are bound by the integer pipe, not by HBM: butterflies per second of the
+            # same launch pair against the register-only butterfly rate measured on this GPU just now
+            "int_roofline": {"achieved_gbutterfly_s": len(wl.rl_idx if hasattr(wl, "rl_idx") else wl.idx) * (N // 2) * 16
+                             / (rl_ms / 1e3) / 1e9,
+                             "peak_gbutterfly_s": probe["butterfly_u64_lazy"], "probe": probe},
             "step_algorithmic_gbs": wl.alg_bytes * args.steps / (ms / 1e3) / 1e9,
             "clocks": clocks,
         }
+        line["int_roofline"]["frac"] = line["int_roofline"]["achieved_gbutterfly_s"] / line["int_roofline"]["peak_gbutterfly_s"]
         if not args.no_cpu_baseline:
             import oracle
             v, sample = wl.cpu_sample(oracle)

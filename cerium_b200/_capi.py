@@ -57,6 +57,7 @@ SIGNATURES = {
     "cerium_hrot": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, C.c_uint32, _vp]),
     "cerium_hmult": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_int, _vp]),
     "cerium_rescale": (C.c_int, [_vp, C.c_int, _vp, _vp, _u32p, C.c_int, C.c_int, _vp, _vp]),
+    "cerium_probe_int_pipe": (C.c_int, [C.c_int, C.POINTER(C.c_double), C.c_int]),
     "cerium_rescale_static": (C.c_int, [_vp, C.c_int, _vp, _vp, _u32p, C.c_int, C.c_int, _vp]),
 }
 
@@ -95,6 +96,15 @@ class Library:
     def check(self, rc: int) -> None:
         if rc != OK:
             raise CeriumError(rc, self.dll.cerium_last_error().decode())
+
+    PROBE_NAMES = ("mad.lo.u32", "mad.wide.u32", "mul.hi.u64", "mul.lo.u64", "add.u64",
+                   "butterfly_u64_strict", "butterfly_u64_lazy", "butterfly_u32")
+
+    def probe_int_pipe(self, device: int = 0) -> dict:
+        """Register-only instruction / butterfly rates in Gop/s (the integer roofline)."""
+        buf = (C.c_double * 8)()
+        self.check(self.dll.cerium_probe_int_pipe(device, buf, 8))
+        return dict(zip(self.PROBE_NAMES, [float(v) for v in buf]))
 
     def galois_elt_from_step(self, step: int, logn: int = 16) -> int:
         return int(self.dll.cerium_galois_elt_from_step(step, logn))

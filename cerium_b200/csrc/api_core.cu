@@ -187,6 +187,7 @@ int create_bconv(cerium_context* ctx, cerium_bconv** out, int mode, const uint32
   auto* bc = new cerium_bconv();
   bc->ctx = ctx;
   bc->mode = mode;
+  bc->lazy_out = opt.lazy_out;
   bc->I = n_in;
   bc->O = n_out;
   bc->in_primes.assign(in_primes, in_primes + n_in);
@@ -305,6 +306,7 @@ int launch_bconv(cerium_context* ctx, const BconvCall* calls, int count, cudaStr
         d.out_prime = bc->d_out_prime;
         d.out_pos = bc->d_out_pos;
         d.in_pos = bc->d_in_pos;
+        d.lazy_out = bc->lazy_out ? 1 : 0;
         d.I = bc->I;
         d.O = bc->O;
         smem = std::max(smem, bconv_smem_bytes<W>(bc->I, std::min(bc->O, kBconvOutChunk)));

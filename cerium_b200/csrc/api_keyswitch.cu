@@ -285,6 +285,7 @@ static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, in
     opt.prescaled = exact;
     opt.out_pos = out_pos;
     opt.in_pos = in_pos;
+    opt.lazy_out = true;  // ModUp outputs go straight into the forward transform
     cerium_bconv* bc = nullptr;
     rc = create_bconv(ctx, &bc, bconv_mode, in_primes.data(), (int)in_primes.size(), out_primes.data(),
                       (int)out_primes.size(), opt);

@@ -39,6 +39,7 @@ struct BconvDesc {
   const uint32_t* out_prime;  // [O]
   const uint32_t* out_pos;    // [O] limb slot of output j inside `out`, or null (slot j)
   const uint32_t* in_pos;     // [I] limb slot of input i inside `in`, or null (slot i)
+  int lazy_out;               // 64-bit split path only: leave outputs in [0, 8q) / [0, 4q) for the forward NTT
   int I;
   int O;
 };
@@ -49,7 +50,8 @@ template <typename W>
 struct BconvOut {
   W q, q2, mu_hi, mu_lo, sub;  // sub = rounding term (0 when unused)
   uint32_t pos;                // limb slot of this output
-  uint32_t pad;
+  uint16_t has_sub;            // rounding term present
+  uint16_t strict;             // prime too wide for the lazy transform (needs inputs below 4q)
 };
 
 // Barrett reduction with the 3-multiply high products: qhat may be up to 7 short, so the
@@ -79,7 +81,7 @@ __device__ __forceinline__ W bconv_input(const BconvDesc<W>& d, const PrimeConst
 // partial product is a 32x32->64 multiply-add into one of three column sums (y0*f0,
 // y0*f1 + y1*f0, y1*f1).  With pieces below 2^30 and at most 8 terms no column overflows, so
 // a multiply-accumulate is four IMAD.WIDE and no carry handling.
-template <int kI>  // exact number of inputs, 1..8
+template <int kI, bool kLazyOut>  // kI = exact number of inputs, 1..8
 __device__ __forceinline__ void bconv_body_split64(const BconvDesc<uint64_t>& d,
                                                    const PrimeConst<uint64_t>* __restrict__ pcs,
                                                    const uint2* sfac, const BconvOut<uint64_t>* sout, int coeff) {
@@ -103,16 +105,29 @@ __device__ __forceinline__ void bconv_body_split64(const BconvDesc<uint64_t>& d,
       c1 += (uint64_t)y1[i] * fi.x;
       c2 += (uint64_t)y1[i] * fi.y;
     }
-    // value = c0 + c1 * 2^30 + c2 * 2^60 as hi:lo
-    uint64_t lo = c0, hi = (c1 >> 34) + (c2 >> 4);
-    const uint64_t t1 = c1 << 30, t2 = c2 << 60;
-    lo += t1;
-    hi += lo < t1 ? 1 : 0;
-    lo += t2;
-    hi += lo < t2 ? 1 : 0;
+    // value = c0 + c1 * 2^30 + c2 * 2^60 as hi:lo (128-bit adds: carry chains, no compares)
+#if defined(CERIUM_EMU)
+    const unsigned __int128 v128 = (unsigned __int128)c0 + ((unsigned __int128)c1 << 30) + ((unsigned __int128)c2 << 60);
+    const uint64_t lo = (uint64_t)v128, hi = (uint64_t)(v128 >> 64);
+#else
+    uint64_t lo, hi;
+    {
+      const uint64_t t1l = c1 << 30, t1h = c1 >> 34, t2l = c2 << 60, t2h = c2 >> 4;
+      asm("add.cc.u64 %0, %2, %3;\n\taddc.u64 %1, %4, 0;" : "=l"(lo), "=l"(hi) : "l"(c0), "l"(t1l), "l"(t1h));
+      asm("add.cc.u64 %0, %0, %2;\n\taddc.u64 %1, %1, %3;" : "+l"(lo), "+l"(hi) : "l"(t2l), "l"(t2h));
+    }
+#endif
     const BconvOut<uint64_t> o = sout[j];
-    uint64_t r = barrett2_fast(hi, lo, o.q, o.q2, o.mu_hi, o.mu_lo);
-    r = sub_mod<uint64_t>(r, o.sub, o.q);
+    uint64_t r;
+    if (kLazyOut) {
+      // consumer is the forward transform: [0, 8q) is fine for lazy primes, [0, 4q) for strict ones
+      const uint64_t qhat = hi * o.mu_hi + mulhi_approx64(lo, o.mu_hi) + mulhi_approx64(hi, o.mu_lo);
+      r = lo - qhat * o.q;
+      if (o.strict) r = csub<uint64_t>(r, o.q2 + o.q2);
+    } else {
+      r = barrett2_fast(hi, lo, o.q, o.q2, o.mu_hi, o.mu_lo);
+      if (o.has_sub) r = sub_mod<uint64_t>(r, o.sub, o.q);
+    }
     d.out[(size_t)o.pos * d.out_stride + coeff] = r;
   }
 }
@@ -149,7 +164,7 @@ __device__ __forceinline__ void bconv_body(const BconvDesc<W>& d, const PrimeCon
     pc.mu_hi = o.mu_hi;
     pc.mu_lo = o.mu_lo;
     W r = barrett2<W>(acc.hi, acc.lo, pc);
-    r = sub_mod<W>(r, o.sub, o.q);
+    if (o.has_sub) r = sub_mod<W>(r, o.sub, o.q);
     d.out[(size_t)o.pos * d.out_stride + coeff] = r;
   }
 }
@@ -213,7 +228,8 @@ __global__ void __launch_bounds__(kBconvThreads)
     o.mu_lo = pc.mu_lo;
     o.sub = d.out_sub != nullptr ? d.out_sub[j] : (W)0;
     o.pos = d.out_pos != nullptr ? d.out_pos[j] : pos_base + (uint32_t)j;
-    o.pad = 0;
+    o.has_sub = d.out_sub != nullptr ? 1 : 0;
+    o.strict = pc.lazy_ok != 0 ? 0 : 1;
     sout[j] = o;
   }
   __syncthreads();
@@ -224,14 +240,14 @@ __global__ void __launch_bounds__(kBconvThreads)
     const uint2* f2 = reinterpret_cast<const uint2*>(sfac);
     const BconvOut<uint64_t>* so = reinterpret_cast<const BconvOut<uint64_t>*>(sout);
     switch (I) {
-      case 1: bconv_body_split64<1>(d64, p64, f2, so, coeff); break;
-      case 2: bconv_body_split64<2>(d64, p64, f2, so, coeff); break;
-      case 3: bconv_body_split64<3>(d64, p64, f2, so, coeff); break;
-      case 4: bconv_body_split64<4>(d64, p64, f2, so, coeff); break;
-      case 5: bconv_body_split64<5>(d64, p64, f2, so, coeff); break;
-      case 6: bconv_body_split64<6>(d64, p64, f2, so, coeff); break;
-      case 7: bconv_body_split64<7>(d64, p64, f2, so, coeff); break;
-      default: bconv_body_split64<8>(d64, p64, f2, so, coeff); break;
+      case 1: if (d.lazy_out) bconv_body_split64<1, true>(d64, p64, f2, so, coeff); else bconv_body_split64<1, false>(d64, p64, f2, so, coeff); break;
+      case 2: if (d.lazy_out) bconv_body_split64<2, true>(d64, p64, f2, so, coeff); else bconv_body_split64<2, false>(d64, p64, f2, so, coeff); break;
+      case 3: if (d.lazy_out) bconv_body_split64<3, true>(d64, p64, f2, so, coeff); else bconv_body_split64<3, false>(d64, p64, f2, so, coeff); break;
+      case 4: if (d.lazy_out) bconv_body_split64<4, true>(d64, p64, f2, so, coeff); else bconv_body_split64<4, false>(d64, p64, f2, so, coeff); break;
+      case 5: if (d.lazy_out) bconv_body_split64<5, true>(d64, p64, f2, so, coeff); else bconv_body_split64<5, false>(d64, p64, f2, so, coeff); break;
+      case 6: if (d.lazy_out) bconv_body_split64<6, true>(d64, p64, f2, so, coeff); else bconv_body_split64<6, false>(d64, p64, f2, so, coeff); break;
+      case 7: if (d.lazy_out) bconv_body_split64<7, true>(d64, p64, f2, so, coeff); else bconv_body_split64<7, false>(d64, p64, f2, so, coeff); break;
+      default: if (d.lazy_out) bconv_body_split64<8, true>(d64, p64, f2, so, coeff); else bconv_body_split64<8, false>(d64, p64, f2, so, coeff); break;
     }
   } else {
     switch (I) {

@@ -98,6 +98,7 @@ struct cerium_bconv {
   uint32_t* d_out_prime = nullptr;
   uint32_t* d_out_pos = nullptr;  // or null
   uint32_t* d_in_pos = nullptr;   // or null
+  bool lazy_out = false;
   std::vector<uint64_t> inv_host;  // [Qhat_i^-1]_{q_i}
 };
 
@@ -109,6 +110,7 @@ struct BconvOptions {
   bool round_half = false;           // add floor(prod_in/2) to inputs, subtract it from outputs
   std::vector<uint32_t> out_pos;     // output limb slots (empty = 0..O-1)
   std::vector<uint32_t> in_pos;      // input limb slots (empty = 0..I-1)
+  bool lazy_out = false;             // outputs feed the forward NTT directly: skip the final corrections
 };
 
 int create_bconv(cerium_context* ctx, cerium_bconv** out, int mode, const uint32_t* in_primes, int n_in,
