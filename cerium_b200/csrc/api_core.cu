@@ -59,6 +59,7 @@ int launch_ntt_forward(cerium_context* ctx, const NttCall& c, cudaStream_t strea
       cols.out = static_cast<W*>(c.out);
       cols.in_stride = c.in_stride;
       cols.out_stride = c.out_stride;
+      cols.split = kMaxBatch;
       if (int rc = fill_batch<W>(ctx, cols, c.pos, c.prime, first, cnt)) return rc;
       StridedBatch<W> rows = cols;
       rows.in = static_cast<const W*>(c.out);
@@ -85,6 +86,7 @@ int launch_ntt_inverse(cerium_context* ctx, const NttCall& c, const void* scale,
       sb.out = static_cast<W*>(c.out);
       sb.in_stride = c.in_stride;
       sb.out_stride = c.out_stride;
+      sb.split = kMaxBatch;
       if (int rc = fill_batch<W>(ctx, sb, c.pos, c.prime, first, cnt)) return rc;
       InvScale<W> sc{};
       if (scale != nullptr) {
@@ -106,6 +108,7 @@ int launch_sud(cerium_context* ctx, const SudCall& c, cudaStream_t stream) {
     using Pair = typename WordTraits<W>::Pair;
     constexpr int kCols = NttCfg<W>::kCols;
     const int bits = ctx->word_bits;
+    if (c.split > 0 && c.count > kSudMaxBatch) return fail(CERIUM_ERR_INVALID, "sud: a two-polynomial launch holds at most 96 limbs");
     for (int first = 0; first < c.count; first += kSudMaxBatch) {
       const int cnt = std::min(kSudMaxBatch, c.count - first);
       StridedBatch<W> cols{};
@@ -113,8 +116,8 @@ int launch_sud(cerium_context* ctx, const SudCall& c, cudaStream_t stream) {
       cols.out = static_cast<W*>(c.work) + (size_t)first * c.work_stride;
       cols.in_stride = c.src_stride;
       cols.out_stride = c.work_stride;
+      cols.split = kMaxBatch;
       if (int rc = fill_batch<W>(ctx, cols, nullptr, c.prime + first, 0, cnt)) return rc;
-      for (int b = 0; b < cnt; b++) cols.pos[b] = (uint16_t)b;
       StridedBatch<W> rows = cols;
       rows.in = cols.out;
       rows.in_stride = c.work_stride;
@@ -125,6 +128,16 @@ int launch_sud(cerium_context* ctx, const SudCall& c, cudaStream_t stream) {
       epi.minuend_stride = c.minuend_stride;
       epi.addend = c.addend ? static_cast<const W*>(c.addend) + (size_t)first * c.addend_stride : nullptr;
       epi.addend_stride = c.addend_stride;
+      epi.split = kSudMaxBatch;
+      if (c.split > 0) {
+        // second polynomial: entry b lands at slot b - split of dst2 (the slot number itself stays b,
+        // it also addresses the work stack), so the base is moved back by split limbs
+        rows.split = c.split;
+        rows.out2 = static_cast<W*>(c.dst2) - (ptrdiff_t)c.split * (ptrdiff_t)c.dst_stride;
+        epi.split = c.split;
+        epi.minuend2 = static_cast<const W*>(c.minuend2);
+        epi.addend2 = static_cast<const W*>(c.addend2);
+      }
       for (int b = 0; b < cnt; b++) {
         const uint64_t q = ctx->moduli[c.prime[first + b]];
         const uint64_t f = c.factor[first + b] % q;
@@ -182,6 +195,13 @@ int create_bconv(cerium_context* ctx, cerium_bconv** out, int mode, const uint32
     if (in_primes[i] >= (uint32_t)ctx->n_primes) return fail(CERIUM_ERR_INVALID, "bconv_create: input prime index out of range");
   for (int j = 0; j < n_out; j++)
     if (out_primes[j] >= (uint32_t)ctx->n_primes) return fail(CERIUM_ERR_INVALID, "bconv_create: output prime index out of range");
+  // the unreduced sum of products must fit the two-word accumulator
+  for (int j = 0; j < n_out; j++) {
+    long double sum = 0;
+    for (int i = 0; i < n_in; i++) sum += (long double)ctx->moduli[in_primes[i]] * (long double)ctx->moduli[out_primes[j]];
+    if (sum >= (ctx->word_bits == 32 ? 1.8e19L : 3.4e38L))
+      return fail(CERIUM_ERR_UNSUPPORTED, "bconv_create: too many inputs for primes this wide (sum of products overflows)");
+  }
   DeviceGuard guard(ctx->device);
   if (!guard.ok) return fail(CERIUM_ERR_CUDA, "bconv_create: cannot select device");
   auto* bc = new cerium_bconv();
@@ -309,7 +329,7 @@ int launch_bconv(cerium_context* ctx, const BconvCall* calls, int count, cudaStr
         d.lazy_out = bc->lazy_out ? 1 : 0;
         d.I = bc->I;
         d.O = bc->O;
-        smem = std::max(smem, bconv_smem_bytes<W>(bc->I, std::min(bc->O, kBconvOutChunk)));
+        smem = std::max(smem, bconv_smem_bytes<W>(bc->I, bc->O));
         max_o = std::max(max_o, bc->O);
       }
       if (smem > 48 * 1024) {
@@ -320,7 +340,7 @@ int launch_bconv(cerium_context* ctx, const BconvCall* calls, int count, cudaStr
           smem_opt_in[slot] = true;
         }
       }
-      { auto kfn = bconv_kernel<W>; CERIUM_LAUNCH(kfn, dim3(kN / kBconvThreads, cnt, (max_o + kBconvOutChunk - 1) / kBconvOutChunk), kBconvThreads, smem, stream, batch, static_cast<const PrimeConst<W>*>(ctx->d_pcs)); }
+      { auto kfn = bconv_kernel<W>; const int nz = std::max(1, std::min((2048 + 256 * cnt - 1) / (256 * cnt), (max_o + 3) / 4)); const int out_chunk = (max_o + nz - 1) / nz; CERIUM_LAUNCH(kfn, dim3(kN / kBconvThreads, cnt, (max_o + out_chunk - 1) / out_chunk), kBconvThreads, smem, stream, batch, out_chunk, static_cast<const PrimeConst<W>*>(ctx->d_pcs)); }
     }
     CERIUM_LAUNCH_CHECK("bconv");
     return CERIUM_OK;

@@ -44,6 +44,10 @@ struct cerium_keyswitch {
   void* d_scale_q_shoup = nullptr;
   void* d_scale_p = nullptr;
   void* d_scale_p_shoup = nullptr;
+  // side stream: the extension limbs' inverse transform and base conversion (integer-bound)
+  // run next to the Q-limb inner product (HBM-bound)
+  cudaStream_t side = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   // workspace
   void* ws = nullptr;
   size_t ws_bytes = 0;
@@ -164,40 +168,85 @@ int keyswitch_finish(cerium_keyswitch* ks, void* out0, void* out1, const void* g
         g.prime[b] = (uint8_t)ks->all_idx[b];
         g.own_digit[b] = (int8_t)ks->own_digit[b];
       }
-      { auto kfn = inner_product_kernel<W>; CERIUM_LAUNCH(kfn, dim3(kN / (kEwThreads * V::kLanes), LK), kEwThreads, 0, stream, g, static_cast<const PrimeConst<W>*>(ctx->d_pcs)); }
+      const PrimeConst<W>* pcs = static_cast<const PrimeConst<W>*>(ctx->d_pcs);
+      const dim3 block(kEwThreads);
+      // extension limbs first: their ModDown preparation then overlaps the Q-limb pass below
+      g.first_limb = L;
+      { auto kfn = inner_product_kernel<W>; CERIUM_LAUNCH(kfn, dim3(kN / (kEwThreads * V::kLanes), K), block, 0, stream, g, pcs); }
+      const bool fork = ks->side != nullptr && L > 0;
+      cudaStream_t prep = fork ? ks->side : stream;
+      if (fork) {
+        CERIUM_CUDA(cudaEventRecord(ks->ev_fork, stream));
+        CERIUM_CUDA(cudaStreamWaitEvent(ks->side, ks->ev_fork, 0));
+      }
+      if (L > 0) {
+        g.first_limb = 0;
+        auto kfn = inner_product_kernel<W>;
+        CERIUM_LAUNCH(kfn, dim3(kN / (kEwThreads * V::kLanes), L), block, 0, stream, g, pcs);
+      }
       CERIUM_LAUNCH_CHECK("inner_product");
+      // 5. iNTT of the extension limbs of both accumulators, in place
+      {
+        NttCall c{acc, acc, n, n, ks->ext_pos.data(), ks->ext_prime.data(), 2 * K};
+        if (int rc = launch_ntt_inverse(ctx, c, ks->d_scale_p, ks->d_scale_p_shoup, prep)) return rc;
+      }
+      if (L == 0) return CERIUM_OK;  // a rank without Q limbs only feeds the gather
+      // 6. ModDown base conversion P -> local Q limbs
+      {
+        BconvCall calls[2] = {
+            {ks->down, conv, n, acc + (size_t)L * n, n},
+            {ks->down, conv + (size_t)L * n, n, acc + (size_t)(LK + L) * n, n},
+        };
+        if (int rc = launch_bconv(ctx, calls, 2, prep)) return rc;
+      }
+      if (fork) {
+        CERIUM_CUDA(cudaEventRecord(ks->ev_join, ks->side));
+        CERIUM_CUDA(cudaStreamWaitEvent(stream, ks->ev_join, 0));
+      }
     }
-    // 5. iNTT of the extension limbs of both accumulators, in place
-    {
-      NttCall c{acc, acc, n, n, ks->ext_pos.data(), ks->ext_prime.data(), 2 * K};
-      if (int rc = launch_ntt_inverse(ctx, c, ks->d_scale_p, ks->d_scale_p_shoup, stream)) return rc;
-    }
-    if (L == 0) return CERIUM_OK;  // a rank without Q limbs only feeds the gather
-    // 6. ModDown base conversion P -> local Q limbs
-    {
-      BconvCall calls[2] = {
-          {ks->down, conv, n, acc + (size_t)L * n, n},
-          {ks->down, conv + (size_t)L * n, n, acc + (size_t)(LK + L) * n, n},
-      };
-      if (int rc = launch_bconv(ctx, calls, 2, stream)) return rc;
-    }
-    // 7. SuD: out = (acc_Q - NTT(conv)) * P^-1 (+ add)
-    for (int p = 0; p < 2; p++) {
+    // 7. SuD: out = (acc_Q - NTT(conv)) * P^-1 (+ add); both polynomials in one launch pair
+    if (2 * L <= kSudMaxBatch) {
+      std::vector<uint32_t> prime2(ks->q_idx);
+      prime2.insert(prime2.end(), ks->q_idx.begin(), ks->q_idx.end());
+      std::vector<uint64_t> factor2(ks->pinv);
+      factor2.insert(factor2.end(), ks->pinv.begin(), ks->pinv.end());
       SudCall s{};
-      s.src = conv + (size_t)p * L * n;
+      s.src = conv;
       s.src_stride = n;
-      s.work = conv + (size_t)p * L * n;
+      s.work = conv;
       s.work_stride = n;
-      s.dst = p == 0 ? out0 : out1;
+      s.dst = out0;
       s.dst_stride = n;
-      s.minuend = acc + (size_t)p * LK * n;
+      s.minuend = acc;
       s.minuend_stride = n;
-      s.addend = p == 0 ? add0 : add1;
+      s.addend = add0;
       s.addend_stride = n;
-      s.prime = ks->q_idx.data();
-      s.factor = ks->pinv.data();
-      s.count = L;
+      s.prime = prime2.data();
+      s.factor = factor2.data();
+      s.count = 2 * L;
+      s.split = L;
+      s.dst2 = out1;
+      s.minuend2 = acc + (size_t)LK * n;
+      s.addend2 = add1;
       if (int rc = launch_sud(ctx, s, stream)) return rc;
+    } else {
+      for (int p = 0; p < 2; p++) {
+        SudCall s{};
+        s.src = conv + (size_t)p * L * n;
+        s.src_stride = n;
+        s.work = conv + (size_t)p * L * n;
+        s.work_stride = n;
+        s.dst = p == 0 ? out0 : out1;
+        s.dst_stride = n;
+        s.minuend = acc + (size_t)p * LK * n;
+        s.minuend_stride = n;
+        s.addend = p == 0 ? add0 : add1;
+        s.addend_stride = n;
+        s.prime = ks->q_idx.data();
+        s.factor = ks->pinv.data();
+        s.count = L;
+        if (int rc = launch_sud(ctx, s, stream)) return rc;
+      }
     }
     return CERIUM_OK;
   });
@@ -223,7 +272,7 @@ static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, in
   if (round_mode != CERIUM_ROUND_FLOOR && round_mode != CERIUM_ROUND_HALF) return fail(CERIUM_ERR_INVALID, "keyswitch_create: unknown round mode");
   if (Lg < 1 || K < 1 || dnum < 1 || dnum > Lg) return fail(CERIUM_ERR_INVALID, "keyswitch_create: need L >= 1, K >= 1, 1 <= dnum <= L");
   if (world < 1 || rank < 0 || rank >= world) return fail(CERIUM_ERR_INVALID, "keyswitch_create: need 0 <= rank < world");
-  if (Lg + K > kEwMaxLimbs || Lg > kSudMaxBatch) return fail(CERIUM_ERR_UNSUPPORTED, "keyswitch_create: too many limbs (L <= 64, L + K <= 128)");
+  if (Lg + K > kEwMaxLimbs || Lg > 64) return fail(CERIUM_ERR_UNSUPPORTED, "keyswitch_create: too many limbs (L <= 64, L + K <= 128)");
   const int alpha = (Lg + dnum - 1) / dnum;
   if (alpha > K) return fail(CERIUM_ERR_INVALID, "keyswitch_create: digit size exceeds the number of extension primes");
   if ((size_t)dnum * (Lg + K) > 0xffff) return fail(CERIUM_ERR_UNSUPPORTED, "keyswitch_create: dnum * (L + K) too large");
@@ -233,6 +282,11 @@ static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, in
     if (p >= (uint32_t)ctx->n_primes) return fail(CERIUM_ERR_INVALID, "keyswitch_create: prime index out of range");
     if (seen[p]) return fail(CERIUM_ERR_INVALID, "keyswitch_create: a prime appears twice");
     seen[p] = true;
+  }
+  for (int i = 0; i < Lg + K; i++) {
+    const long double q = (long double)ctx->moduli[i < Lg ? q_idx[i] : p_idx[i - Lg]];
+    if (q * q * dnum >= (ctx->word_bits == 32 ? 1.8e19L : 3.4e38L))
+      return fail(CERIUM_ERR_UNSUPPORTED, "keyswitch_create: dnum products of primes this wide overflow the accumulator");
   }
   DeviceGuard guard(ctx->device);
   if (!guard.ok) return fail(CERIUM_ERR_CUDA, "keyswitch_create: cannot select device");
@@ -370,6 +424,12 @@ static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, in
     cerium_keyswitch_destroy(ks);
     return fail(CERIUM_ERR_CUDA, "keyswitch_create: cannot allocate the workspace");
   }
+  if (cudaStreamCreateWithFlags(&ks->side, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaEventCreateWithFlags(&ks->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&ks->ev_join, cudaEventDisableTiming) != cudaSuccess) {
+    cerium_keyswitch_destroy(ks);
+    return fail(CERIUM_ERR_CUDA, "keyswitch_create: cannot create the side stream");
+  }
   *out = ks;
   return CERIUM_OK;
 }
@@ -411,6 +471,9 @@ int cerium_keyswitch_destroy(cerium_keyswitch* ks) {
   if (ks->down) cerium_bconv_destroy(ks->down);
   cudaFree(ks->d_scale);
   cudaFree(ks->ws);
+  if (ks->side) cudaStreamDestroy(ks->side);
+  if (ks->ev_fork) cudaEventDestroy(ks->ev_fork);
+  if (ks->ev_join) cudaEventDestroy(ks->ev_join);
   delete ks;
   return CERIUM_OK;
 }
@@ -470,7 +533,7 @@ int cerium_rescale(cerium_context* ctx, int round_mode, void* out, const void* i
                    int n_polys, void* scratch, void* stream) {
   if (!ctx || !out || !in || !q_idx || !scratch) return fail(CERIUM_ERR_INVALID, "rescale: null argument");
   if (round_mode != CERIUM_ROUND_FLOOR && round_mode != CERIUM_ROUND_HALF) return fail(CERIUM_ERR_INVALID, "rescale: unknown round mode");
-  if (L < 2 || L - 1 > kSudMaxBatch) return fail(CERIUM_ERR_INVALID, "rescale: need 2 <= L <= 65");
+  if (L < 2 || L - 1 > 64) return fail(CERIUM_ERR_INVALID, "rescale: need 2 <= L <= 65");
   if (n_polys < 1 || n_polys > 4096) return fail(CERIUM_ERR_INVALID, "rescale: need 1 <= n_polys <= 4096");
   for (int i = 0; i < L; i++)
     if (q_idx[i] >= (uint32_t)ctx->n_primes) return fail(CERIUM_ERR_INVALID, "rescale: prime index out of range");

@@ -47,7 +47,7 @@ extern "C" int cerium_rescale_static(cerium_context* ctx, int round_mode, void* 
   if (!ctx || !out || !in || !q_idx) return fail(CERIUM_ERR_INVALID, "rescale_static: null argument");
   if (round_mode != CERIUM_ROUND_FLOOR && round_mode != CERIUM_ROUND_HALF)
     return fail(CERIUM_ERR_INVALID, "rescale_static: unknown round mode");
-  if (L < 2 || L - 1 > kSudMaxBatch) return fail(CERIUM_ERR_INVALID, "rescale_static: need 2 <= L <= 65");
+  if (L < 2 || L - 1 > 64) return fail(CERIUM_ERR_INVALID, "rescale_static: need 2 <= L <= 65");
   if (n_polys < 1) return fail(CERIUM_ERR_INVALID, "rescale_static: need at least one polynomial");
   if (n_polys > kStaticRescaleMaxPolys)
     return fail(CERIUM_ERR_UNSUPPORTED,

@@ -22,7 +22,7 @@ namespace cerium {
 
 constexpr int kBconvThreads = 256;
 constexpr int kBconvRegInputs = 8;
-constexpr int kBconvOutChunk = 8;  // outputs per CTA: grid.z splits the output primes for load balance
+// grid.z splits the output primes of a conversion when the batch alone gives too few CTAs
 
 template <typename W>
 struct BconvDesc {
@@ -163,7 +163,7 @@ __device__ __forceinline__ void bconv_body(const BconvDesc<W>& d, const PrimeCon
     pc.q2 = o.q2;
     pc.mu_hi = o.mu_hi;
     pc.mu_lo = o.mu_lo;
-    W r = barrett2<W>(acc.hi, acc.lo, pc);
+    W r = barrett2<W>(acc.hi(), acc.lo(), pc);
     if (o.has_sub) r = sub_mod<W>(r, o.sub, o.q);
     d.out[(size_t)o.pos * d.out_stride + coeff] = r;
   }
@@ -186,18 +186,18 @@ __host__ __device__ inline size_t bconv_smem_bytes(int I, int O) {
   return n;
 }
 
-// grid = (N / 256, conversions, ceil(max O / kBconvOutChunk)), block = 256,
+// grid = (N / 256, conversions, ceil(max O / out_chunk)), block = 256,
 // dynamic smem = max bconv_smem_bytes over the batch.  CTA z handles outputs
-// [z * kBconvOutChunk, min(O, (z + 1) * kBconvOutChunk)) of its conversion.
+// [z * out_chunk, min(O, (z + 1) * out_chunk)) of its conversion.
 template <typename W>
 __global__ void __launch_bounds__(kBconvThreads)
-    bconv_kernel(const BconvBatch<W> batch, const PrimeConst<W>* __restrict__ pcs) {
+    bconv_kernel(const BconvBatch<W> batch, const int out_chunk, const PrimeConst<W>* __restrict__ pcs) {
   CERIUM_DYN_SMEM(smem_raw);
   BconvDesc<W> d = batch.d[blockIdx.y];
-  const int j_first = blockIdx.z * kBconvOutChunk;
+  const int j_first = blockIdx.z * out_chunk;
   if (j_first >= d.O) return;
   // restrict the descriptor to this CTA's slice of the outputs
-  const int I = d.I, O = (d.O - j_first) < kBconvOutChunk ? (d.O - j_first) : kBconvOutChunk;
+  const int I = d.I, O = (d.O - j_first) < out_chunk ? (d.O - j_first) : out_chunk;
   d.factors += (size_t)j_first * I;
   d.out_prime += j_first;
   if (d.out_sub != nullptr) d.out_sub += j_first;

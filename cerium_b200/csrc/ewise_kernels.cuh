@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(kEwThreads)
     acc.clear();
     acc.mad(a0.v[l], b1.v[l]);
     acc.mad(a1.v[l], b0.v[l]);
-    d1.v[l] = barrett2<W>(acc.hi, acc.lo, pc);
+    d1.v[l] = barrett2<W>(acc.hi(), acc.lo(), pc);
   }
   d0.store(g.d0.at(b, idx));
   d1.store(g.d1.at(b, idx));
@@ -191,6 +191,7 @@ struct InnerProductArgs {
   size_t evk_poly_stride;
   size_t evk_limb_stride;
   Limbs<W> out0, out1;    // [LK][N]
+  int first_limb;         // grid.y covers extended limbs first_limb, first_limb + 1, ...
   int dnum;
   uint8_t prime[kEwMaxLimbs];     // prime index of extended limb b
   int8_t own_digit[kEwMaxLimbs];  // digit that limb b belongs to (-1 for extension limbs)
@@ -200,7 +201,7 @@ template <typename W>
 __global__ void __launch_bounds__(kEwThreads)
     inner_product_kernel(const InnerProductArgs<W> g, const PrimeConst<W>* __restrict__ pcs) {
   using V = Vec16<W>;
-  const int b = blockIdx.y;
+  const int b = g.first_limb + blockIdx.y;
   const PrimeConst<W> pc = pcs[g.prime[b]];
   const int idx = (blockIdx.x * kEwThreads + threadIdx.x) * V::kLanes;
   Acc2<W> acc0[V::kLanes], acc1[V::kLanes];
@@ -229,8 +230,8 @@ __global__ void __launch_bounds__(kEwThreads)
   V o0, o1;
 #pragma unroll
   for (int l = 0; l < V::kLanes; l++) {
-    o0.v[l] = barrett2<W>(acc0[l].hi, acc0[l].lo, pc);
-    o1.v[l] = barrett2<W>(acc1[l].hi, acc1[l].lo, pc);
+    o0.v[l] = barrett2<W>(acc0[l].hi(), acc0[l].lo(), pc);
+    o1.v[l] = barrett2<W>(acc1[l].hi(), acc1[l].lo(), pc);
   }
   o0.store(g.out0.at(b, idx));
   o1.store(g.out1.at(b, idx));

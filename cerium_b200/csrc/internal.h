@@ -155,6 +155,12 @@ struct SudCall {
   const uint32_t* prime;  // count prime indices
   const uint64_t* factor; // count canonical residues (host)
   int count;
+  // optional second polynomial in the same launch: entries [split, count) write dst2 and read
+  // minuend2 / addend2 at index (b - split); src / work stay one stack of `count` limbs
+  int split = 0;          // 0 = one polynomial
+  void* dst2 = nullptr;
+  const void* minuend2 = nullptr;
+  const void* addend2 = nullptr;
   // source re-reduction (only when reduce_src): residues of modulus src_q, optional rounding
   bool reduce_src = false;
   uint64_t src_q = 0;

@@ -111,18 +111,25 @@ __device__ __forceinline__ W sub_mod(W a, W b, W q) {
 // Two-word accumulator: acc += a * b (no reduction; caller bounds the number of terms).
 template <typename W>
 struct Acc2 {
-  W hi, lo;
-  __device__ __forceinline__ void clear() { hi = 0; lo = 0; }
+  W hi_, lo_;
+  __device__ __forceinline__ void clear() { hi_ = 0; lo_ = 0; }
   __device__ __forceinline__ void mad(W a, W b) {
     W pl = a * b;
     W ph = WordTraits<W>::mulhi(a, b);
-    lo += pl;
-    hi += ph + (lo < pl ? (W)1 : (W)0);
+    lo_ += pl;
+    hi_ += ph + (lo_ < pl ? (W)1 : (W)0);
   }
-  __device__ __forceinline__ void add_word(W a) {
-    lo += a;
-    hi += (lo < a ? (W)1 : (W)0);
-  }
+  __device__ __forceinline__ W hi() const { return hi_; }
+  __device__ __forceinline__ W lo() const { return lo_; }
+};
+// 32-bit words: the two words are one 64-bit register pair and a term is a single IMAD.WIDE.
+template <>
+struct Acc2<uint32_t> {
+  uint64_t v;
+  __device__ __forceinline__ void clear() { v = 0; }
+  __device__ __forceinline__ void mad(uint32_t a, uint32_t b) { v += (uint64_t)a * b; }
+  __device__ __forceinline__ uint32_t hi() const { return (uint32_t)(v >> 32); }
+  __device__ __forceinline__ uint32_t lo() const { return (uint32_t)v; }
 };
 
 // ---------------------------------------------------------------------------------------

@@ -53,10 +53,14 @@ struct StridedBatch {
   W* out;
   size_t in_stride;   // in words
   size_t out_stride;  // in words
+  W* out2;            // entries b >= split write to out2 instead of out (two result stacks, one launch)
+  int split;          // kMaxBatch when unused
   uint16_t pos[kMaxBatch];
   uint8_t prime[kMaxBatch];
   __device__ __forceinline__ const W* in_limb(int b) const { return in + (size_t)pos[b] * in_stride; }
-  __device__ __forceinline__ W* out_limb(int b) const { return out + (size_t)pos[b] * out_stride; }
+  __device__ __forceinline__ W* out_limb(int b) const {
+    return (b >= split ? out2 : out) + (size_t)pos[b] * out_stride;
+  }
   __device__ __forceinline__ uint32_t prime_of(int b) const { return prime[b]; }
 };
 
@@ -239,7 +243,7 @@ struct PlainLoader {
   __device__ __forceinline__ W apply(W x, int /*b*/, const PrimeConst<W>& /*pc*/) const { return x; }
 };
 
-constexpr int kSudMaxBatch = 64;  // limbs per launch when per-limb scalars travel as parameters
+constexpr int kSudMaxBatch = 96;  // limbs per launch when per-limb scalars travel as parameters
 
 // Source residues belong to another (possibly larger) modulus src_q: optionally add pre_add
 // mod src_q (rounding), reduce into [0, q) of the target prime, optionally subtract
@@ -311,21 +315,29 @@ struct StoreEpilogue {
 };
 
 // SuD tail: out = (minuend - NTT(in)) * factor[b] [+ addend]   (all mod q).
-// minuend / addend are stacks of limbs: entry b at base + b * stride.
+// minuend / addend are stacks of limbs: entry b at base + b * stride; entries b >= split belong
+// to a second polynomial and use minuend2 / addend2 at (b - split) * stride.
 template <typename W>
 struct SudEpilogue {
   const W* minuend;
+  const W* minuend2;
   size_t minuend_stride;
-  const W* addend;  // may be null
+  const W* addend;   // may be null
+  const W* addend2;  // may be null
   size_t addend_stride;
+  int split;         // kSudMaxBatch when there is one polynomial
   W factor[kSudMaxBatch];
   W factor_shoup[kSudMaxBatch];
   __device__ __forceinline__ W apply(W x, int b, int idx, uint32_t /*pi*/,
                                      const PrimeConst<W>& pc) const {
-    const W m = minuend[(size_t)b * minuend_stride + idx];
+    const bool second = b >= split;
+    const int e = second ? b - split : b;
+    const W* mp = second ? minuend2 : minuend;
+    const W* ap = second ? addend2 : addend;
+    const W m = mp[(size_t)e * minuend_stride + idx];
     W d = sub_mod<W>(m, x, pc.q);
     d = csub<W>(mul_shoup_lazy<W>(d, factor[b], factor_shoup[b], pc.q), pc.q);
-    if (addend != nullptr) d = add_mod<W>(d, addend[(size_t)b * addend_stride + idx], pc.q);
+    if (ap != nullptr) d = add_mod<W>(d, ap[(size_t)e * addend_stride + idx], pc.q);
     return d;
   }
 };
