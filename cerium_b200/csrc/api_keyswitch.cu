@@ -424,7 +424,11 @@ static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, in
     cerium_keyswitch_destroy(ks);
     return fail(CERIUM_ERR_CUDA, "keyswitch_create: cannot allocate the workspace");
   }
-  if (cudaStreamCreateWithFlags(&ks->side, cudaStreamNonBlocking) != cudaSuccess ||
+  // highest priority: the side stream's few CTAs take SM slots as the bandwidth-bound kernel on the
+  // caller's stream releases them, instead of queueing behind its whole grid
+  int prio_lo = 0, prio_hi = 0;
+  cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi);
+  if (cudaStreamCreateWithPriority(&ks->side, cudaStreamNonBlocking, prio_hi) != cudaSuccess ||
       cudaEventCreateWithFlags(&ks->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
       cudaEventCreateWithFlags(&ks->ev_join, cudaEventDisableTiming) != cudaSuccess) {
     cerium_keyswitch_destroy(ks);
