@@ -46,7 +46,7 @@ static int check_stack(const void* p, size_t stride_words, size_t word_bytes, co
 // NTT launchers
 // ---------------------------------------------------------------------------------------
 
-int launch_ntt_forward(cerium_context* ctx, const NttCall& c, cudaStream_t stream) {
+int launch_ntt_forward(cerium_context* ctx, const NttCall& c, cudaStream_t stream, bool lazy_out) {
   if (c.count == 0) return CERIUM_OK;
   return dispatch_word(ctx->word_bits, [&](auto tag) -> int {
     using W = decltype(tag);
@@ -65,7 +65,13 @@ int launch_ntt_forward(cerium_context* ctx, const NttCall& c, cudaStream_t strea
       rows.in = static_cast<const W*>(c.out);
       rows.in_stride = c.out_stride;
       { auto kfn = ntt_fwd_cols_kernel<W, StridedBatch<W>, PlainLoader<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kCols, cnt), kCols * 16, 0, stream, cols, PlainLoader<W>{}, static_cast<const Pair*>(ctx->d_tw_fwd), static_cast<const PrimeConst<W>*>(ctx->d_pcs)); }
-      { auto kfn = ntt_fwd_rows_kernel<W, StridedBatch<W>, StoreEpilogue<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kRowsPerCta, cnt), kRowsPerCta * 16, 0, stream, rows, StoreEpilogue<W>{}, static_cast<const Pair*>(ctx->d_tw_fwd), static_cast<const Pair*>(ctx->d_twr_fwd), static_cast<const PrimeConst<W>*>(ctx->d_pcs)); }
+      if (lazy_out) {
+        auto kfn = ntt_fwd_rows_kernel<W, StridedBatch<W>, LazyStoreEpilogue<W>>;
+        CERIUM_LAUNCH(kfn, dim3(256 / kRowsPerCta, cnt), kRowsPerCta * 16, 0, stream, rows, LazyStoreEpilogue<W>{}, static_cast<const Pair*>(ctx->d_tw_fwd), static_cast<const Pair*>(ctx->d_twr_fwd), static_cast<const PrimeConst<W>*>(ctx->d_pcs));
+      } else {
+        auto kfn = ntt_fwd_rows_kernel<W, StridedBatch<W>, StoreEpilogue<W>>;
+        CERIUM_LAUNCH(kfn, dim3(256 / kRowsPerCta, cnt), kRowsPerCta * 16, 0, stream, rows, StoreEpilogue<W>{}, static_cast<const Pair*>(ctx->d_tw_fwd), static_cast<const Pair*>(ctx->d_twr_fwd), static_cast<const PrimeConst<W>*>(ctx->d_pcs));
+      }
     }
     CERIUM_LAUNCH_CHECK("ntt_forward");
     return CERIUM_OK;

@@ -147,7 +147,7 @@ int keyswitch_finish(cerium_keyswitch* ks, void* out0, void* out1, const void* g
     // 3. NTT of every converted limb
     {
       NttCall c{raised, raised, n, n, ks->ntt_pos.data(), ks->ntt_prime.data(), (int)ks->ntt_pos.size()};
-      if (int rc = launch_ntt_forward(ctx, c, stream)) return rc;
+      if (int rc = launch_ntt_forward(ctx, c, stream, /*lazy_out=*/true)) return rc;
     }
     // 4. inner product with the key
     {
@@ -285,7 +285,8 @@ static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, in
   }
   for (int i = 0; i < Lg + K; i++) {
     const long double q = (long double)ctx->moduli[i < Lg ? q_idx[i] : p_idx[i - Lg]];
-    if (q * q * dnum >= (ctx->word_bits == 32 ? 1.8e19L : 3.4e38L))
+    // raised digits reach the inner product below 4q, the key below q
+    if (4 * q * q * dnum >= (ctx->word_bits == 32 ? 1.8e19L : 3.4e38L))
       return fail(CERIUM_ERR_UNSUPPORTED, "keyswitch_create: dnum products of primes this wide overflow the accumulator");
   }
   DeviceGuard guard(ctx->device);

@@ -135,7 +135,8 @@ struct NttCall {
   const uint32_t* prime;  // count entries
   int count;
 };
-int launch_ntt_forward(cerium_context* ctx, const NttCall& c, cudaStream_t stream);
+// lazy_out: leave the results below 4q instead of canonical (internal buffers read by the inner product only)
+int launch_ntt_forward(cerium_context* ctx, const NttCall& c, cudaStream_t stream, bool lazy_out = false);
 // scale / scale_shoup: device arrays with one word per batch entry, or null.
 int launch_ntt_inverse(cerium_context* ctx, const NttCall& c, const void* scale, const void* scale_shoup,
                        cudaStream_t stream);

@@ -97,9 +97,12 @@ struct Arith {
     if (kLazy) butterfly_inv_lazy<W>(a, b, w, ws, nq, q4 << k);
     else butterfly_inv<W>(a, b, w, ws, q, q2);
   }
-  // value at the end of a forward transform -> [0, q)
+  // value at the end of a forward transform -> [0, q), or only below 4q when the consumer
+  // takes lazy residues (kCanonical = false)
+  template <bool kCanonical>
   __device__ __forceinline__ W finish_fwd(W x, W one_shoup) const {
     if (kLazy) x = reduce_lazy(x, one_shoup, nq);
+    if (!kCanonical) return x;
     return csub<W>(csub<W>(x, q2), q);
   }
 };
@@ -305,9 +308,22 @@ __global__ void __launch_bounds__(NttCfg<W>::kCols * 16, sizeof(W) == 8 ? 3 : 2)
                        (ntt_fwd_cols_body<W, false>(batch, loader, b, pc, tile, stw)));
 }
 
-// What the row pass does with the finished (canonical) NTT value.
+// What the row pass does with the finished NTT value.  kCanonicalInput says whether the
+// epilogue wants the value reduced to [0, q) first or takes it below 4q.
 template <typename W>
 struct StoreEpilogue {
+  static constexpr bool kCanonicalInput = true;
+  __device__ __forceinline__ W apply(W x, int /*b*/, int /*idx*/, uint32_t /*pi*/,
+                                     const PrimeConst<W>& /*pc*/) const {
+    return x;
+  }
+};
+
+// Stores the transform below 4q.  Only for buffers whose one reader multiplies the values into a
+// wide accumulator (the raised digits of a key switch, read by the inner product).
+template <typename W>
+struct LazyStoreEpilogue {
+  static constexpr bool kCanonicalInput = false;
   __device__ __forceinline__ W apply(W x, int /*b*/, int /*idx*/, uint32_t /*pi*/,
                                      const PrimeConst<W>& /*pc*/) const {
     return x;
@@ -319,6 +335,7 @@ struct StoreEpilogue {
 // to a second polynomial and use minuend2 / addend2 at (b - split) * stride.
 template <typename W>
 struct SudEpilogue {
+  static constexpr bool kCanonicalInput = false;  // takes the transform below 4q
   const W* minuend;
   const W* minuend2;
   size_t minuend_stride;
@@ -335,7 +352,7 @@ struct SudEpilogue {
     const W* mp = second ? minuend2 : minuend;
     const W* ap = second ? addend2 : addend;
     const W m = mp[(size_t)e * minuend_stride + idx];
-    W d = sub_mod<W>(m, x, pc.q);
+    W d = m + (pc.q2 + pc.q2) - x;  // x < 4q: positive, and the Shoup product takes any word
     d = csub<W>(mul_shoup_lazy<W>(d, factor[b], factor_shoup[b], pc.q), pc.q);
     if (ap != nullptr) d = add_mod<W>(d, ap[(size_t)e * addend_stride + idx], pc.q);
     return d;
@@ -406,7 +423,7 @@ __device__ __forceinline__ void ntt_fwd_rows_body(const Batch& batch, const Epil
   // level 3: this thread's 15 twiddles from the lane-interleaved table of row h
   radix16_fwd<W, true, kLazy, true>(x, twr + ((size_t)h * 15 * 16 + u), 0u, ar);
 #pragma unroll
-  for (int j = 0; j < 16; j++) x[j] = ar.finish_fwd(x[j], pc.one_shoup);
+  for (int j = 0; j < 16; j++) x[j] = ar.template finish_fwd<Epilogue::kCanonicalInput>(x[j], pc.one_shoup);
   // own 16 words -> swizzled vectors -> coalesced vectors, then epilogue and store
   __syncthreads();
   Vec* vrow = reinterpret_cast<Vec*>(tile) + r * RV::kPerRow;
