@@ -417,7 +417,7 @@ __device__ __forceinline__ void ntt_fwd_rows_body(const Batch& batch, const Epil
   radix16_fwd<W, true, kLazy>(x, tw, 256u + (uint32_t)h, ar);
 #pragma unroll
   for (int j = 0; j < 16; j++) trow[row_pos(j * 16 + u)] = x[j];
-  __syncthreads();
+  __syncwarp();  // a row's 16 threads share a warp; no other warp touches its staging rows
 #pragma unroll
   for (int j = 0; j < 16; j++) x[j] = trow[row_pos(u * 16 + j)];
   // level 3: this thread's 15 twiddles from the lane-interleaved table of row h
@@ -425,12 +425,12 @@ __device__ __forceinline__ void ntt_fwd_rows_body(const Batch& batch, const Epil
 #pragma unroll
   for (int j = 0; j < 16; j++) x[j] = ar.template finish_fwd<Epilogue::kCanonicalInput>(x[j], pc.one_shoup);
   // own 16 words -> swizzled vectors -> coalesced vectors, then epilogue and store
-  __syncthreads();
-  Vec* vrow = reinterpret_cast<Vec*>(tile) + r * RV::kPerRow;
+  __syncwarp();  // a row's 16 threads share a warp; no other warp touches its staging rows
+  Vec* vrow = reinterpret_cast<Vec*>(tile + r * kRowPitch);  // same private region as the exchange rows
 #pragma unroll
   for (int jj = 0; jj < RV::kPerThread; jj++)
     vrow[row_vec_slot<W>(u * RV::kPerThread + jj)] = vec_pack(&x[jj * RV::kWords]);
-  __syncthreads();
+  __syncwarp();  // a row's 16 threads share a warp; no other warp touches its staging rows
 #pragma unroll
   for (int k = 0; k < RV::kPerThread; k++) {
     const int v = u + 16 * k;
@@ -479,22 +479,22 @@ __device__ __forceinline__ void ntt_inv_rows_body(const Batch& batch, int b, con
   W* dst = batch.out_limb(b) + h * 256;
   W* trow = tile + r * kRowPitch;
   // coalesced vectors -> swizzled staging -> own 16 consecutive words
-  Vec* vrow = reinterpret_cast<Vec*>(tile) + r * RV::kPerRow;
+  Vec* vrow = reinterpret_cast<Vec*>(tile + r * kRowPitch);  // same private region as the exchange rows
 #pragma unroll
   for (int k = 0; k < RV::kPerThread; k++) {
     const int v = u + 16 * k;
     vrow[row_vec_slot<W>(v)] = reinterpret_cast<const Vec*>(src)[v];
   }
-  __syncthreads();
+  __syncwarp();
   W x[16];
 #pragma unroll
   for (int jj = 0; jj < RV::kPerThread; jj++)
     vec_unpack(vrow[row_vec_slot<W>(u * RV::kPerThread + jj)], &x[jj * RV::kWords]);
   radix16_inv<W, true, kLazy, 0, true>(x, twri + ((size_t)h * 15 * 16 + u), 0u, ar);
-  __syncthreads();
+  __syncwarp();
 #pragma unroll
   for (int j = 0; j < 16; j++) trow[row_pos(u * 16 + j)] = x[j];
-  __syncthreads();
+  __syncwarp();
 #pragma unroll
   for (int j = 0; j < 16; j++) x[j] = trow[row_pos(j * 16 + u)];
   radix16_inv<W, true, kLazy, 4>(x, twi, 256u + (uint32_t)h, ar);
