@@ -8,7 +8,9 @@
 // threads); the threads of a block are ucontext fibers on one OS thread, scheduled round
 // robin, and __syncthreads() yields to the next fiber.  Because every fiber runs to its next
 // barrier before any fiber continues, barriers that all threads of a block reach (the only
-// kind the kernels use) behave as on the device.  __shared__ variables become
+// kind the kernels use) behave as on the device.  __syncwarp() holds only the 32 fibers of a warp
+// together; warps otherwise run one after another as far as they can, so code that needs a
+// block barrier where it only has a warp barrier computes wrong results here too.  __shared__ variables become
 // static thread_local, i.e. one copy per OS thread = per running block.
 #pragma once
 #include <cstddef>
@@ -43,6 +45,7 @@ extern thread_local uint3 t_threadIdx, t_blockIdx;
 extern thread_local dim3 t_blockDim, t_gridDim;
 unsigned char* dyn_smem();
 void sync_threads();
+void sync_warp();
 void launch(dim3 grid, dim3 block, size_t smem_bytes, const std::function<void()>& body);
 long launches();  // number of launches so far (tests use it to see that kernels ran)
 }  // namespace cerium_emu
@@ -53,7 +56,7 @@ long launches();  // number of launches so far (tests use it to see that kernels
 #define gridDim (::cerium_emu::t_gridDim)
 
 static inline void __syncthreads() { ::cerium_emu::sync_threads(); }
-static inline void __syncwarp() { ::cerium_emu::sync_threads(); }
+static inline void __syncwarp() { ::cerium_emu::sync_warp(); }
 static inline unsigned __umulhi(unsigned a, unsigned b) { return (unsigned)(((uint64_t)a * b) >> 32); }
 static inline unsigned long long __umul64hi(unsigned long long a, unsigned long long b) {
   return (unsigned long long)(((unsigned __int128)a * b) >> 64);
