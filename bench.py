@@ -40,6 +40,10 @@ from cerium_b200 import params  # noqa: E402
 
 LOGN = 16
 N = 1 << LOGN
+# dram__bytes_read.sum + dram__bytes_write.sum of the forward-NTT launch pair from the ncu capture
+# summarised in profiles/hrot_u64_top_kernels_ncu_full.md: 498.7 MB for 245 u64 limbs (traffic grows
+# in proportion to the limbs transformed)
+NTT_PAIR_DRAM_BYTES_PER_LIMB = 498.7e6 / 245
 
 
 def env_int(name, default):
@@ -181,7 +185,8 @@ class HRotWorkload(Workload):
         self.host_in = torch.empty(self.cts[0].shape, dtype=torch.int64).pin_memory()
         self.host_in.copy_(self.cts[0].cpu())
         self.host_out = torch.empty(self.cts[0].shape, dtype=torch.int64).pin_memory()
-        self.gpu_launches_per_step = 2 + (2 + 1 + 2 + 1 + 2 + 1 + 4)
+        # automorph x2, iNTT pair, BConv, NTT pair, inner product x2, iNTT pair, BConv, SuD pair
+        self.gpu_launches_per_step = 2 + 2 + 1 + 2 + 2 + 2 + 1 + 2
 
     def _hrot(self, ct, out):
         if self.sharded:
@@ -522,7 +527,9 @@ def main():
                     "d2h_bytes_per_step": d2h},
             "gpu_launches": wl.gpu_launches_per_step * args.steps,
             "roofline": {"bound": "hbm", "kernel": wl.rl_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                         "frac": achieved / peak, "traffic": NTT_PAIR_DRAM_BYTES_PER_LIMB * (wl.rl_bytes // (2 * N * 8)),
+                         "traffic_source": "profiles/hrot_u64_top_kernels_ncu_full.md (ncu, 245 limbs, scaled by limbs)",
+                         "peak_kind": peak_kind,
                          "ms_per_launch_pair": rl_ms, "algorithmic_bytes": wl.rl_bytes},
             # the 64-bit transforms are bound by the integer pipe, not by HBM: butterflies per second of the
             # same launch pair against the register-only butterfly rate measured on this GPU just now
