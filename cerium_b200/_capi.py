@@ -42,9 +42,12 @@ SIGNATURES = {
     "cerium_tensor": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _u32p, C.c_int, _vp]),
     "cerium_galois_elt_from_step": (C.c_uint32, [C.c_int, C.c_int]),
     "cerium_automorph": (C.c_int, [_vp, _vp, _sz, _vp, _sz, C.c_uint32, C.c_int, _vp]),
+    "cerium_resolve2": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _sz, C.c_uint32, C.c_uint32, C.c_int, _vp]),
+    "cerium_mod2": (C.c_int, [_vp, _vp, _sz, _vp, _vp, _u32p, C.c_int, _vp]),
     "cerium_bconv_create": (C.c_int, [_vp, C.POINTER(_vp), C.c_int, _u32p, C.c_int, _u32p, C.c_int]),
     "cerium_bconv_destroy": (C.c_int, [_vp]),
     "cerium_bconv_apply": (C.c_int, [_vp, _vp, _sz, _vp, _sz, _vp]),
+    "cerium_bconv_apply_batch": (C.c_int, [C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), C.c_int, _sz, _sz, _vp]),
     "cerium_keyswitch_create": (C.c_int, [_vp, C.POINTER(_vp), C.c_int, C.c_int, _u32p, C.c_int, _u32p, C.c_int, C.c_int]),
     "cerium_keyswitch_create_sharded": (C.c_int, [_vp, C.POINTER(_vp), C.c_int, C.c_int, _u32p, C.c_int, _u32p, C.c_int, C.c_int, C.c_int, C.c_int]),
     "cerium_keyswitch_local_limbs": (C.c_int, [_vp]),
@@ -185,6 +188,12 @@ class Context:
         n = self.n
         self.lib.check(self.lib.dll.cerium_automorph(self.h, out, n, inp, n, galois_elt, count, stream))
 
+    def resolve2(self, lo: int, hi: int, x0: int, x1: int, prime0: int, prime1: int, count: int = 1, stream: int = 0):
+        self.lib.check(self.lib.dll.cerium_resolve2(self.h, lo, hi, x0, x1, self.n, prime0, prime1, count, stream))
+
+    def mod2(self, out: int, lo: int, hi: int, prime_idx: Sequence[int], stream: int = 0):
+        self.lib.check(self.lib.dll.cerium_mod2(self.h, out, self.n, lo, hi, _u32(prime_idx), len(prime_idx), stream))
+
     def rescale(self, out: int, inp: int, q_idx: Sequence[int], n_polys: int, scratch: int,
                 round_mode: int = ROUND_FLOOR, stream: int = 0):
         self.lib.check(self.lib.dll.cerium_rescale(self.h, round_mode, out, inp, _u32(q_idx), len(q_idx), n_polys,
@@ -213,6 +222,17 @@ class BaseConverter:
               stream: int = 0):
         n = self.ctx.n
         self.ctx.lib.check(self.ctx.lib.dll.cerium_bconv_apply(self.h, out, out_stride or n, inp, in_stride or n, stream))
+
+    @staticmethod
+    def apply_batch(converters, outs: Sequence[int], ins: Sequence[int], stream: int = 0):
+        """Several conversions (converters of one context) in one launch."""
+        ctx = converters[0].ctx
+        n = ctx.n
+        k = len(converters)
+        hs = (_vp * k)(*[c.h for c in converters])
+        o = (_vp * k)(*[_vp(int(p)) for p in outs])
+        i = (_vp * k)(*[_vp(int(p)) for p in ins])
+        ctx.lib.check(ctx.lib.dll.cerium_bconv_apply_batch(hs, o, i, k, n, n, stream))
 
     def close(self):
         if getattr(self, "h", None) and self.ctx.h:

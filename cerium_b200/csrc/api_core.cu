@@ -710,6 +710,66 @@ int cerium_automorph(cerium_context* ctx, void* out, size_t out_stride, const vo
   });
 }
 
+int cerium_resolve2(cerium_context* ctx, void* lo, void* hi, const void* x0, const void* x1, size_t stride,
+                    uint32_t prime0, uint32_t prime1, int count, void* stream) {
+  if (!ctx) return fail(CERIUM_ERR_INVALID, "resolve2: null context");
+  if (count < 0 || count > 65535) return fail(CERIUM_ERR_INVALID, "resolve2: bad count");
+  if (count == 0) return CERIUM_OK;
+  if (prime0 >= (uint32_t)ctx->n_primes || prime1 >= (uint32_t)ctx->n_primes || prime0 == prime1)
+    return fail(CERIUM_ERR_INVALID, "resolve2: need two different prime indices of the context");
+  const size_t wb = ctx->word_bytes();
+  const void* ptrs[4] = {lo, hi, x0, x1};
+  for (const void* p : ptrs)
+    if (int rc = check_stack(p, stride, wb, "resolve2: operand")) return rc;
+  const uint64_t m0 = ctx->moduli[prime0], m1 = ctx->moduli[prime1];
+  const uint64_t inv = host::invmod(m0 % m1, m1);
+  DeviceGuard guard(ctx->device);
+  return dispatch_word(ctx->word_bits, [&](auto tag) -> int {
+    using W = decltype(tag);
+    using V = Vec16<W>;
+    auto mk = [&](const void* p) { return Limbs<W>{const_cast<W*>(static_cast<const W*>(p)), stride}; };
+    Rsv2Args<W> g{};
+    g.x0 = mk(x0); g.x1 = mk(x1); g.lo = mk(lo); g.hi = mk(hi);
+    g.m0 = (W)m0;
+    g.inv = (W)inv;
+    g.inv_shoup = (W)host::shoup(inv, m1, ctx->word_bits);
+    g.prime1 = prime1;
+    { auto kfn = rsv2_kernel<W>; CERIUM_LAUNCH(kfn, dim3(kN / (kEwThreads * V::kLanes), count), kEwThreads, 0, (cudaStream_t)stream, g, static_cast<const PrimeConst<W>*>(ctx->d_pcs)); }
+    CERIUM_LAUNCH_CHECK("resolve2");
+    return CERIUM_OK;
+  });
+}
+
+int cerium_mod2(cerium_context* ctx, void* out, size_t out_stride, const void* lo, const void* hi,
+                const uint32_t* prime_idx, int count, void* stream) {
+  if (!ctx) return fail(CERIUM_ERR_INVALID, "mod2: null context");
+  if (count < 0) return fail(CERIUM_ERR_INVALID, "mod2: negative count");
+  if (count == 0) return CERIUM_OK;
+  if (!prime_idx) return fail(CERIUM_ERR_INVALID, "mod2: null prime_idx");
+  const size_t wb = ctx->word_bytes();
+  if (int rc = check_stack(out, out_stride, wb, "mod2: out")) return rc;
+  if (int rc = check_stack(lo, kN, wb, "mod2: lo")) return rc;
+  if (int rc = check_stack(hi, kN, wb, "mod2: hi")) return rc;
+  for (int i = 0; i < count; i++)
+    if (prime_idx[i] >= (uint32_t)ctx->n_primes) return fail(CERIUM_ERR_INVALID, "mod2: prime index out of range");
+  DeviceGuard guard(ctx->device);
+  return dispatch_word(ctx->word_bits, [&](auto tag) -> int {
+    using W = decltype(tag);
+    using V = Vec16<W>;
+    for (int first = 0; first < count; first += kEwMaxLimbs) {
+      const int cnt = std::min(kEwMaxLimbs, count - first);
+      Mod2Args<W> g{};
+      g.lo = static_cast<const W*>(lo);
+      g.hi = static_cast<const W*>(hi);
+      g.out = {static_cast<W*>(out) + (size_t)first * out_stride, out_stride};
+      for (int k = 0; k < cnt; k++) g.prime[k] = (uint8_t)prime_idx[first + k];
+      { auto kfn = mod2_kernel<W>; CERIUM_LAUNCH(kfn, dim3(kN / (kEwThreads * V::kLanes), cnt), kEwThreads, 0, (cudaStream_t)stream, g, static_cast<const PrimeConst<W>*>(ctx->d_pcs)); }
+    }
+    CERIUM_LAUNCH_CHECK("mod2");
+    return CERIUM_OK;
+  });
+}
+
 int cerium_bconv_create(cerium_context* ctx, cerium_bconv** out, int mode, const uint32_t* in_primes, int n_in,
                         const uint32_t* out_primes, int n_out) {
   return create_bconv(ctx, out, mode, in_primes, n_in, out_primes, n_out, BconvOptions{});
@@ -732,6 +792,24 @@ int cerium_bconv_apply(cerium_bconv* bc, void* out, size_t out_stride, const voi
   DeviceGuard guard(bc->ctx->device);
   BconvCall c{bc, out, out_stride, in, in_stride};
   return launch_bconv(bc->ctx, &c, 1, (cudaStream_t)stream);
+}
+
+int cerium_bconv_apply_batch(cerium_bconv* const* bcs, void* const* outs, const void* const* ins, int count,
+                             size_t out_stride, size_t in_stride, void* stream) {
+  if (count < 0) return fail(CERIUM_ERR_INVALID, "bconv_apply_batch: negative count");
+  if (count == 0) return CERIUM_OK;
+  if (!bcs || !outs || !ins) return fail(CERIUM_ERR_INVALID, "bconv_apply_batch: null array");
+  std::vector<BconvCall> calls(count);
+  for (int k = 0; k < count; k++) {
+    if (!bcs[k]) return fail(CERIUM_ERR_INVALID, "bconv_apply_batch: null converter");
+    if (bcs[k]->ctx != bcs[0]->ctx) return fail(CERIUM_ERR_INVALID, "bconv_apply_batch: converters of different contexts");
+    const size_t wb = bcs[k]->ctx->word_bytes();
+    if (int rc = check_stack(outs[k], out_stride, wb, "bconv_apply_batch: out")) return rc;
+    if (int rc = check_stack(ins[k], in_stride, wb, "bconv_apply_batch: in")) return rc;
+    calls[k] = BconvCall{bcs[k], outs[k], out_stride, ins[k], in_stride};
+  }
+  DeviceGuard guard(bcs[0]->ctx->device);
+  return launch_bconv(bcs[0]->ctx, calls.data(), count, (cudaStream_t)stream);
 }
 
 }  // extern "C"

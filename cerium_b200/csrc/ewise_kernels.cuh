@@ -171,6 +171,72 @@ __global__ void __launch_bounds__(kEwThreads) automorph_kernel(const AutomorphAr
   *g.out.at(b, (int)i) = *g.in.at(b, (int)galois_source_index(i, g.elt));
 }
 
+// Exact CRT composition of two limbs into a two-word integer ("resolve") and its reduction
+// modulo other primes ("mod"): the pair bootstrapping's ModRaise and the double rescale are
+// built from (cerium/compiler/backend/compiler_rescale.cc:69-121, 367-521).
+// Replaces rsv_write_2 / mod_read_2 (cerium/compiler/backend/kernels/fhe_bconv.cuh:31-96) and
+// the generated RSV / MOD kernels (cerium/compiler/backend/cuda_kernel.cc:2767-2952) with their
+// factor tables (cerium/runtime/execution/function_execution.cpp:53-99).  The reference sums
+// x_i * (Mhat_i * [Mhat_i^-1]) modulo M = m0*m1 with a 128-bit Barrett step; the same integer -
+// the unique v in [0, M) with v = x0 mod m0 and v = x1 mod m1 - is obtained here by Garner's
+// formula v = x0 + m0 * ((x1 - x0) * m0^-1 mod m1): one modular product and one word multiply.
+template <typename W>
+struct Rsv2Args {
+  Limbs<W> x0, x1, lo, hi;  // `count` polynomials each
+  W m0;                     // first modulus
+  W inv;                    // m0^-1 mod m1
+  W inv_shoup;
+  uint32_t prime1;          // index of m1
+};
+
+// grid = (N / (256 * lanes), count), block = 256
+template <typename W>
+__global__ void __launch_bounds__(kEwThreads) rsv2_kernel(const Rsv2Args<W> g, const PrimeConst<W>* __restrict__ pcs) {
+  using V = Vec16<W>;
+  const int b = blockIdx.y;
+  const PrimeConst<W> pc1 = pcs[g.prime1];
+  const int idx = (blockIdx.x * kEwThreads + threadIdx.x) * V::kLanes;
+  const V x0 = V::load(g.x0.at(b, idx)), x1 = V::load(g.x1.at(b, idx));
+  V lo, hi;
+#pragma unroll
+  for (int l = 0; l < V::kLanes; l++) {
+    const W x0r = reduce_word<W>(x0.v[l], pc1);                    // x0 mod m1
+    const W d = sub_mod<W>(x1.v[l], x0r, pc1.q);
+    const W t = csub<W>(mul_shoup_lazy<W>(d, g.inv, g.inv_shoup, pc1.q), pc1.q);
+    Acc2<W> acc;
+    acc.clear();
+    acc.mad(g.m0, t);
+    // + x0 with carry
+    const W l0 = acc.lo() + x0.v[l];
+    lo.v[l] = l0;
+    hi.v[l] = acc.hi() + (l0 < x0.v[l] ? (W)1 : (W)0);
+  }
+  lo.store(g.lo.at(b, idx));
+  hi.store(g.hi.at(b, idx));
+}
+
+template <typename W>
+struct Mod2Args {
+  const W* lo;  // one two-word polynomial
+  const W* hi;
+  Limbs<W> out; // `count` limbs
+  uint8_t prime[kEwMaxLimbs];
+};
+
+// grid = (N / (256 * lanes), count), block = 256: out[b] = (hi:lo) mod q_{prime[b]}
+template <typename W>
+__global__ void __launch_bounds__(kEwThreads) mod2_kernel(const Mod2Args<W> g, const PrimeConst<W>* __restrict__ pcs) {
+  using V = Vec16<W>;
+  const int b = blockIdx.y;
+  const PrimeConst<W> pc = pcs[g.prime[b]];
+  const int idx = (blockIdx.x * kEwThreads + threadIdx.x) * V::kLanes;
+  const V lo = V::load(g.lo + idx), hi = V::load(g.hi + idx);
+  V o;
+#pragma unroll
+  for (int l = 0; l < V::kLanes; l++) o.v[l] = barrett2<W>(hi.v[l], lo.v[l], pc);
+  o.store(g.out.at(b, idx));
+}
+
 // Key-switching inner product over the extended basis (L + K limbs):
 //   out0[b] = sum_d a_d[b] * evk[d][0][b],   out1[b] = sum_d a_d[b] * evk[d][1][b]
 // where a_d[b] is the raised digit d at limb b.  For the limbs that belong to digit d itself

@@ -153,6 +153,21 @@ CERIUM_API int cerium_automorph(cerium_context *ctx, void *out, size_t out_strid
                      size_t in_stride, uint32_t galois_elt, int count, void *stream);
 
 /*
+ * Resolve: exact CRT composition of the two limbs x0 (mod prime0) and x1 (mod prime1) of `count`
+ * polynomials into the two-word integer v in [0, q0*q1) with v = x0 mod q0, v = x1 mod q1; the low
+ * words go to `lo`, the high words to `hi`.  Mod: out[i] = (hi:lo) mod q_{prime_idx[i]} for one
+ * two-word polynomial.  Together they are the reference's exact ModRaise / double-rescale pair
+ * (rsv_write_2 and mod_read_2, cerium/compiler/backend/kernels/fhe_bconv.cuh:31-96; generated
+ * RSV / MOD kernels, cerium/compiler/backend/cuda_kernel.cc:2767-2952; factors
+ * cerium/runtime/execution/function_execution.cpp:53-99).  All four stacks of cerium_resolve2
+ * share `stride`.
+ */
+CERIUM_API int cerium_resolve2(cerium_context *ctx, void *lo, void *hi, const void *x0, const void *x1,
+                    size_t stride, uint32_t prime0, uint32_t prime1, int count, void *stream);
+CERIUM_API int cerium_mod2(cerium_context *ctx, void *out, size_t out_stride, const void *lo, const void *hi,
+                const uint32_t *prime_idx, int count, void *stream);
+
+/*
  * Base converter from the primes in_primes[0..n_in) to out_primes[0..n_out).
  * Replaces DeviceBaseConverter (cerium/runtime/execution/evaluator.h:30-92,
  * evaluator.cpp:1483-1608) and _function_bco_ (cerium/compiler/backend/kernels/function.cuh:
@@ -163,6 +178,14 @@ CERIUM_API int cerium_bconv_create(cerium_context *ctx, cerium_bconv **out, int 
 CERIUM_API int cerium_bconv_destroy(cerium_bconv *bc);
 CERIUM_API int cerium_bconv_apply(cerium_bconv *bc, void *out, size_t out_stride, const void *in,
                        size_t in_stride, void *stream);
+/*
+ * `count` conversions in one launch (blockIdx.y = conversion, as num_conversions of
+ * _function_bco_, cerium/compiler/backend/kernels/function.cuh:80-99).  bcs / outs / ins are HOST
+ * arrays of `count` converters (of one context) and device pointers; every conversion uses the
+ * same strides.
+ */
+CERIUM_API int cerium_bconv_apply_batch(cerium_bconv *const *bcs, void *const *outs, const void *const *ins,
+                             int count, size_t out_stride, size_t in_stride, void *stream);
 
 /*
  * Hybrid key-switching plan for ciphertexts over q_idx[0..L) with extension primes

@@ -70,6 +70,8 @@ def lib():
         L.orc_galois_table_ntt.argtypes = [C.c_uint32, C.c_int, _u32p]
         L.orc_apply_galois_ntt.argtypes = [C.c_uint32, C.c_int, _u64p, _u64p]
         L.orc_apply_galois_coeff.argtypes = [C.c_uint32, C.c_int, C.c_uint64, _u64p, _u64p]
+        L.orc_resolve2.argtypes = [C.c_uint64, C.c_uint64, C.c_size_t, _u64p, _u64p, _u64p, _u64p]
+        L.orc_mod2.argtypes = [C.c_uint64, C.c_size_t, _u64p, _u64p, _u64p]
         L.orc_bconv.argtypes = [C.c_int, C.c_size_t, C.c_int, _u64p, _u64p, C.c_int, _u64p, _u64p]
         L.orc_sud.argtypes = [C.c_void_p, C.c_int, _u64p, _u64p, C.c_uint64, _u64p]
         L.orc_moddown.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, _u32p, C.c_int, _u32p,
@@ -210,6 +212,21 @@ def bconv(mode, in_mod, x, out_mod) -> np.ndarray:
     n = x.shape[-1]
     out = np.empty((len(om), n), dtype=np.uint64)
     lib().orc_bconv(mode, n, len(im), _p64(im), _p64(x), len(om), _p64(om), _p64(out))
+    return out
+
+
+def resolve2(m0: int, m1: int, x0, x1):
+    """Exact CRT of two limbs -> (lo, hi) 64-bit words of the integer in [0, m0*m1)."""
+    x0, x1 = _c64(x0), _c64(x1)
+    lo, hi = np.empty_like(x0), np.empty_like(x0)
+    lib().orc_resolve2(m0, m1, x0.size, _p64(x0), _p64(x1), _p64(lo), _p64(hi))
+    return lo, hi
+
+
+def mod2(q: int, lo, hi) -> np.ndarray:
+    lo, hi = _c64(lo), _c64(hi)
+    out = np.empty_like(lo)
+    lib().orc_mod2(q, lo.size, _p64(lo), _p64(hi), _p64(out))
     return out
 
 

@@ -363,6 +363,46 @@ ORC_API void orc_apply_galois_coeff(uint32_t elt, int logn, u64 q, const u64 *in
 }
 
 /* ------------------------------------------------------------------------ */
+/* resolve / mod (exact two-limb CRT)                                        */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * v = sum_i x_i * (Mhat_i * [Mhat_i^-1]_{m_i}) mod M, M = m0*m1, as lo/hi 64-bit words.
+ * Restates compute_rsv_factors (cerium/runtime/execution/function_execution.cpp:53-99) and
+ * rsv_write_2 (cerium/compiler/backend/kernels/fhe_bconv.cuh:78-96).
+ */
+ORC_API void orc_resolve2(u64 m0, u64 m1, size_t n, const u64 *x0, const u64 *x1, u64 *lo, u64 *hi) {
+  u128 M = (u128)m0 * m1;
+  u128 f0 = (u128)m1 * orc_invmod(m1 % m0, m0); /* Mhat_0 * [Mhat_0^-1]_{m0} */
+  u128 f1 = (u128)m0 * orc_invmod(m0 % m1, m1);
+  for (size_t i = 0; i < n; i++) {
+    /* x*f may need 3 words: reduce f*x mod M by splitting x into bits is overkill; use x*(f mod M)
+       through two 128-bit steps on the 64-bit halves of f */
+    u128 acc = 0;
+    const u128 fs[2] = {f0, f1};
+    const u64 xs[2] = {x0[i], x1[i]};
+    for (int k = 0; k < 2; k++) {
+      /* (x * f) mod M with f < M < 2^124: double-and-add over the bits of x */
+      u128 term = 0, base = fs[k] % M;
+      u64 x = xs[k];
+      while (x) {
+        if (x & 1) { term += base; if (term >= M) term -= M; }
+        base += base; if (base >= M) base -= M;
+        x >>= 1;
+      }
+      acc += term; if (acc >= M) acc -= M;
+    }
+    lo[i] = (u64)acc;
+    hi[i] = (u64)(acc >> 64);
+  }
+}
+
+/* out = (hi:lo) mod q  (mod_read_2, cerium/compiler/backend/kernels/fhe_bconv.cuh:31-39) */
+ORC_API void orc_mod2(u64 q, size_t n, const u64 *lo, const u64 *hi, u64 *out) {
+  for (size_t i = 0; i < n; i++) out[i] = (u64)((((u128)hi[i] << 64) | lo[i]) % q);
+}
+
+/* ------------------------------------------------------------------------ */
 /* fast base conversion                                                      */
 /* ------------------------------------------------------------------------ */
 

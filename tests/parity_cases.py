@@ -205,6 +205,14 @@ def case_bconv(be, word_bits, n_in, n_out, mode):
     bc.apply(h.p(out), h.p(dx))
     want = oracle.bconv(mode, [mods[i] for i in in_idx], x, [mods[j] for j in out_idx])
     assert np.array_equal(h.down(out), want), "base conversion differs (mode %d, %d -> %d)" % (mode, n_in, n_out)
+    # two conversions in one launch (second on shifted data)
+    x2 = np.roll(x, 3, axis=1)
+    dx2 = h.up(x2)
+    out2 = h.new(n_out, N)
+    out1 = h.new(n_out, N)
+    _capi.BaseConverter.apply_batch([bc, bc], [h.p(out1), h.p(out2)], [h.p(dx), h.p(dx2)])
+    assert np.array_equal(h.down(out1), want)
+    assert np.array_equal(h.down(out2), np.roll(want, 3, axis=1))
     bc.close()
 
 
@@ -247,6 +255,42 @@ def case_rescale(be, word_bits, round_mode, L=4, n_polys=2):
     h.ctx.rescale(h.p(out), h.p(dx), q_idx, n_polys, h.p(scratch), round_mode)
     want = np.stack([h.orc.rescale(round_mode, q_idx, x[p]) for p in range(n_polys)])
     assert np.array_equal(h.down(out), want)
+
+
+def case_resolve_mod(be, word_bits):
+    """Two-limb CRT composition and its reduction modulo other primes (ModRaise building blocks)."""
+    mods = moduli_for(word_bits, 5, 1)
+    h = Harness(be, word_bits, mods)
+    rng = np.random.default_rng(14)
+    p0, p1 = 1, 2
+    x = np.stack([rand_limbs(rng, mods, [p0, p1]) for _ in range(2)])   # 2 polynomials x 2 limbs
+    x[1, 0, :4] = mods[p0] - 1
+    x[1, 1, :4] = mods[p1] - 1
+    d0, d1 = h.up(x[:, 0]), h.up(x[:, 1])
+    lo, hi = h.new(2, N), h.new(2, N)
+    h.ctx.resolve2(h.p(lo), h.p(hi), h.p(d0), h.p(d1), p0, p1, count=2)
+    glo, ghi = h.down(lo), h.down(hi)
+    shift = 64 if word_bits == 64 else 32
+    for k in range(2):
+        wlo, whi = oracle.resolve2(mods[p0], mods[p1], x[k, 0], x[k, 1])
+        if word_bits == 64:
+            assert np.array_equal(glo[k], wlo) and np.array_equal(ghi[k], whi)
+        else:
+            assert np.array_equal(glo[k] | (ghi[k] << np.uint64(32)), wlo) and not whi.any()
+    # big-integer spot check of the CRT property
+    for c in (0, 1, 2, 3, N - 1):
+        v = (int(ghi[1, c]) << shift) | int(glo[1, c])
+        assert v < mods[p0] * mods[p1] and v % mods[p0] == int(x[1, 0, c]) and v % mods[p1] == int(x[1, 1, c])
+    # reduce the first composite modulo every prime of the context
+    idx = list(range(len(mods)))
+    out = h.new(len(idx), N)
+    lo0, hi0 = h.up(glo[0]), h.up(ghi[0])
+    h.ctx.mod2(h.p(out), h.p(lo0), h.p(hi0), idx)
+    got = h.down(out)
+    wlo, whi = oracle.resolve2(mods[p0], mods[p1], x[0, 0], x[0, 1])
+    for i, p in enumerate(idx):
+        assert np.array_equal(got[i], oracle.mod2(mods[p], wlo, whi))
+    assert np.array_equal(got[p0], x[0, 0]) and np.array_equal(got[p1], x[0, 1])
 
 
 def make_keyswitch_inputs(rng, prm: params.CkksParams):

@@ -62,5 +62,10 @@ def test_keyswitch_hrot_hmult(be, word_bits, L, K, dnum, bm, rm):
     pc.case_keyswitch(be, word_bits, L, K, dnum, bm, rm)
 
 
+@pytest.mark.parametrize("word_bits", [32, 64])
+def test_resolve_and_mod(be, word_bits):
+    pc.case_resolve_mod(be, word_bits)
+
+
 def test_error_codes(be):
     pc.case_errors(be)
