@@ -165,14 +165,15 @@ class HRotWorkload(Workload):
             # every rank holds its own limbs of the SAME ciphertexts and key (round-robin by limb)
             from cerium_b200 import sharded as sh
             dev = torch.device("cuda", torch.cuda.current_device())
-            self.sk = sh.ShardedKeySwitch(lib, self.ctx, prm, rank, world, _capi.BCONV_LAZY, _capi.ROUND_FLOOR,
+            self.sk = sh.ShardedKeySwitch(lib, self.ctx, prm, rank, world, _capi.BCONV_EXACT, _capi.ROUND_HALF,
                                           device=dev)
             q_loc = [prm.q_idx[i] for i in sh.local_limb_indices(prm.L, rank, world)]
             all_idx = q_loc + prm.p_idx
             self.evk = _rand_limbs_gpu(torch, prm.moduli, all_idx, (prm.dnum, 2), gen)
             self.cts = [_rand_limbs_gpu(torch, prm.moduli, q_loc, (2,), gen) for _ in range(self.n_cts)]
         else:
-            self.ks = _capi.KeySwitch(self.ctx, prm.q_idx, prm.p_idx, prm.dnum, _capi.BCONV_LAZY, _capi.ROUND_FLOOR)
+            # exact conversion + rounding: the semantics that are low-noise with 50/60-bit primes
+            self.ks = _capi.KeySwitch(self.ctx, prm.q_idx, prm.p_idx, prm.dnum, _capi.BCONV_EXACT, _capi.ROUND_HALF)
             all_idx = prm.q_idx + prm.p_idx
             self.evk = _rand_limbs_gpu(torch, prm.moduli, all_idx, (prm.dnum, 2), gen)
             self.cts = [_rand_limbs_gpu(torch, prm.moduli, prm.q_idx, (2,), gen) for _ in range(self.n_cts)]
@@ -242,7 +243,7 @@ class HRotWorkload(Workload):
         c0, c1 = rl(prm.q_idx), rl(prm.q_idx)
         evk = np.stack([np.stack([rl(all_idx) for _ in range(2)]) for _ in range(prm.dnum)])
         t0 = time.perf_counter()
-        octx.hrot(orc_mod.BCONV_LAZY, orc_mod.ROUND_FLOOR, prm.q_idx, prm.p_idx, prm.dnum, hrot_galois_elt(), c0, c1, evk)
+        octx.hrot(orc_mod.BCONV_EXACT, orc_mod.ROUND_HALF, prm.q_idx, prm.p_idx, prm.dnum, hrot_galois_elt(), c0, c1, evk)
         dt = time.perf_counter() - t0
         return 1.0 / dt, "1 HRot (L=35, K=5, dnum=7), oracle port with OpenMP over limbs"
 

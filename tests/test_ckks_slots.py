@@ -1,0 +1,108 @@
+"""Slot-level checks in the style of the reference's example runners (encrypt, evaluate, decrypt,
+compare with numpy; examples/common.py:134-142, tolerance rtol=1e-5 / atol=1e-4): rotation and
+multiplication must be right as CKKS operations, which pins the key layout, the digit gadget
+and the ModDown direction independently of the oracle-vs-kernel comparison."""
+import numpy as np
+import pytest
+
+import oracle
+from cerium_b200 import _capi, params
+from tests.ckks_ref import CkksRef
+
+LOGN = 16
+N = 1 << LOGN
+
+
+def small_set(L, K, dnum):
+    q = params.ntt_primes_below(60, 1, LOGN) + params.ntt_primes_below(50, L - 1, LOGN)
+    p = params.ntt_primes_below(60, K + 1, LOGN)[1:]
+    return params.CkksParams(LOGN, 64, q + p[::-1], L, K, dnum)
+
+
+def test_oracle_rotation_decrypts_to_rolled_slots():
+    prm = small_set(3, 2, 2)
+    ck = CkksRef(prm, seed=10)
+    rng = np.random.default_rng(3)
+    z = rng.uniform(-1, 1, N // 2)
+    scale = 2.0 ** 40
+    c0, c1 = ck.encrypt(z, scale)
+    assert np.allclose(ck.decrypt(c0, c1, scale).real, z, rtol=1e-5, atol=1e-4)
+    step = 5
+    elt = oracle.galois_elt_from_step(step, LOGN)
+    evk = ck.rotation_key(elt)
+    o0, o1 = ck.octx.hrot(oracle.BCONV_EXACT, oracle.ROUND_HALF, prm.q_idx, prm.p_idx, prm.dnum, elt, c0, c1, evk)
+    assert np.allclose(ck.decrypt(o0, o1, scale).real, np.roll(z, -step), rtol=1e-5, atol=1e-4)
+    o0, o1 = ck.octx.hrot(oracle.BCONV_EXACT, oracle.ROUND_FLOOR, prm.q_idx, prm.p_idx, prm.dnum, elt, c0, c1, evk)
+    assert np.allclose(ck.decrypt(o0, o1, scale).real, np.roll(z, -step), rtol=1e-5, atol=1e-4)
+
+
+def test_oracle_lazy_conversion_on_the_reference_prime_chain():
+    """The reference's lazy base conversion leaves every digit overshooting by up to alpha * q_max
+    multiples of its modulus and ModDown off by up to K * q_max, because inputs are not reduced by
+    q_i first (cerium/compiler/backend/kernels/fhe_bconv.cuh:123-150).  With 28-bit primes and the
+    reference's 2^56 scale (two primes per level, examples/relinearization/program.py:26-38) that
+    ModDown offset (a positive bias of about K * 2^27 in every coefficient, i.e. up to ~2^45 in the slot
+    next to zeta = 1) disappears under the scale the reference's rotation example uses, 2^84 (three
+    primes, examples/rotation/runner.py:22-25), and the result passes the tolerance of
+    examples/common.py:141; at 2^56 it would not, and with 50/60-bit primes the bias is 2^60 * K,
+    which is why the 64-bit configurations use the exact conversion."""
+    prm = params.config_ref28(LOGN, 6, 4, 2, total=10)  # K = alpha + 1: P exceeds the digit modulus by one prime
+    ck = CkksRef(prm, seed=13)
+    rng = np.random.default_rng(6)
+    z = rng.uniform(-1, 1, N // 2)
+    scale = 2.0 ** 84
+    c0, c1 = ck.encrypt(z, scale)
+    assert np.allclose(ck.decrypt(c0, c1, scale, use=4).real, z, rtol=1e-5, atol=1e-4)
+    step = 3
+    elt = oracle.galois_elt_from_step(step, LOGN)
+    evk = ck.rotation_key(elt)
+    o0, o1 = ck.octx.hrot(oracle.BCONV_LAZY, oracle.ROUND_FLOOR, prm.q_idx, prm.p_idx, prm.dnum, elt, c0, c1, evk)
+    assert np.allclose(ck.decrypt(o0, o1, scale, use=4).real, np.roll(z, -step), rtol=1e-5, atol=1e-4)
+
+
+def test_oracle_hmult_relin_rescale_decrypts_to_product():
+    prm = small_set(3, 1, 3)
+    ck = CkksRef(prm, seed=11)
+    rng = np.random.default_rng(4)
+    x, y = rng.uniform(-1, 1, N // 2), rng.uniform(-1, 1, N // 2)
+    scale = 2.0 ** 40
+    a0, a1 = ck.encrypt(x, scale)
+    b0, b1 = ck.encrypt(y, scale)
+    evk = ck.relin_key()
+    o0, o1 = ck.octx.hmult_relin(oracle.BCONV_EXACT, oracle.ROUND_HALF, True, prm.q_idx, prm.p_idx, prm.dnum,
+                                 a0, a1, b0, b1, evk)
+    q_last = prm.moduli[prm.q_idx[-1]]
+    got = ck.decrypt(o0, o1, scale * scale / q_last).real
+    assert np.allclose(got, x * y, rtol=1e-5, atol=1e-4)
+
+
+@pytest.mark.gpu
+def test_gpu_rotation_and_product_decrypt_correctly():
+    import torch
+    from tests.backends import CudaBackend
+    be = CudaBackend()
+    prm = small_set(6, 2, 3)
+    ck = CkksRef(prm, seed=12)
+    rng = np.random.default_rng(5)
+    x, y = rng.uniform(-1, 1, N // 2), rng.uniform(-1, 1, N // 2)
+    scale = 2.0 ** 40
+    a0, a1 = ck.encrypt(x, scale)
+    b0, b1 = ck.encrypt(y, scale)
+    ctx = _capi.Context(be.lib, prm.moduli, 64)
+    ks = _capi.KeySwitch(ctx, prm.q_idx, prm.p_idx, prm.dnum, _capi.BCONV_EXACT, _capi.ROUND_HALF)
+    up = be.to_dev
+    step = -7
+    elt = be.lib.galois_elt_from_step(step, LOGN)
+    d = [up(v) for v in (a0, a1, b0, b1)]
+    o0, o1 = be.empty((prm.L, N), np.uint64), be.empty((prm.L, N), np.uint64)
+    evk = up(ck.rotation_key(elt))
+    ks.hrot(be.ptr(o0), be.ptr(o1), be.ptr(d[0]), be.ptr(d[1]), be.ptr(evk), elt)
+    got = ck.decrypt(be.to_host(o0), be.to_host(o1), scale).real
+    assert np.allclose(got, np.roll(x, -step), rtol=1e-5, atol=1e-4)
+    rk = up(ck.relin_key())
+    r0, r1 = be.empty((prm.L - 1, N), np.uint64), be.empty((prm.L - 1, N), np.uint64)
+    ks.hmult(be.ptr(r0), be.ptr(r1), be.ptr(d[0]), be.ptr(d[1]), be.ptr(d[2]), be.ptr(d[3]), be.ptr(rk), True)
+    q_last = prm.moduli[prm.q_idx[-1]]
+    got = ck.decrypt(be.to_host(r0), be.to_host(r1), scale * scale / q_last).real
+    err = np.max(np.abs(got - x * y))
+    assert np.allclose(got, x * y, rtol=1e-5, atol=1e-4), err
