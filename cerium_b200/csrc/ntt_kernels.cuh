@@ -272,21 +272,24 @@ __device__ __forceinline__ void ntt_fwd_cols_body(const Batch& batch, const Load
   const Arith<W, kLazy> ar(pc.q);
   const int tid = threadIdx.x, c = tid % kCols, u = tid / kCols;
   const int col = blockIdx.x * kCols + c;
-  const W* in = batch.in_limb(b);
-  W* out = batch.out_limb(b);
+  // one base pointer per access pattern; the unrolled accesses are then constant offsets from it
+  const W* in = batch.in_limb(b) + (unsigned)(u * 256 + col);
+  W* out = batch.out_limb(b) + (unsigned)(u * 16 * 256 + col);
+  W* t_strided = tile + (unsigned)(u * kCols + c);
+  W* t_own = tile + (unsigned)(u * 16 * kCols + c);
   W x[16];
 #pragma unroll
-  for (int j = 0; j < 16; j++) x[j] = loader.apply(in[(j * 16 + u) * 256 + col], b, pc);
+  for (int j = 0; j < 16; j++) x[j] = loader.apply(in[j * 16 * 256], b, pc);
   __syncthreads();
   radix16_fwd<W, false, kLazy>(x, stw, 1u, ar);
 #pragma unroll
-  for (int j = 0; j < 16; j++) tile[(j * 16 + u) * kCols + c] = x[j];
+  for (int j = 0; j < 16; j++) t_strided[j * 16 * kCols] = x[j];
   __syncthreads();
 #pragma unroll
-  for (int j = 0; j < 16; j++) x[j] = tile[(u * 16 + j) * kCols + c];
+  for (int j = 0; j < 16; j++) x[j] = t_own[j * kCols];
   radix16_fwd<W, false, kLazy>(x, stw, 16u + (uint32_t)u, ar);
 #pragma unroll
-  for (int j = 0; j < 16; j++) out[(u * 16 + j) * 256 + col] = x[j];
+  for (int j = 0; j < 16; j++) out[j * 256] = x[j];
 }
 
 // Column pass (levels 0 and 1).  grid = (256 / kCols, limbs), block = 16 * kCols.
@@ -408,18 +411,20 @@ __device__ __forceinline__ void ntt_fwd_rows_body(const Batch& batch, const Epil
   const Arith<W, kLazy> ar(pc.q);
   const int tid = threadIdx.x, r = tid >> 4, u = tid & 15;
   const int h = blockIdx.x * kRowsPerCta + r;
-  const W* row = batch.in_limb(b) + h * 256;
-  W* drow = batch.out_limb(b) + h * 256;
-  W* trow = tile + r * kRowPitch;
+  const W* row = batch.in_limb(b) + (unsigned)(h * 256 + u);
+  W* drow = batch.out_limb(b) + (unsigned)(h * 256);
+  W* trow = tile + (unsigned)(r * kRowPitch);
+  W* t_strided = trow + u;             // row_pos(j * 16 + u) = j * 17 + u
+  W* t_own = trow + (unsigned)(u * 17);  // row_pos(u * 16 + j) = u * 17 + j
   W x[16];
 #pragma unroll
-  for (int j = 0; j < 16; j++) x[j] = row[j * 16 + u];
+  for (int j = 0; j < 16; j++) x[j] = row[j * 16];
   radix16_fwd<W, true, kLazy>(x, tw, 256u + (uint32_t)h, ar);
 #pragma unroll
-  for (int j = 0; j < 16; j++) trow[row_pos(j * 16 + u)] = x[j];
+  for (int j = 0; j < 16; j++) t_strided[j * 17] = x[j];
   __syncwarp();  // a row's 16 threads share a warp; no other warp touches its staging rows
 #pragma unroll
-  for (int j = 0; j < 16; j++) x[j] = trow[row_pos(u * 16 + j)];
+  for (int j = 0; j < 16; j++) x[j] = t_own[j];
   // level 3: this thread's 15 twiddles from the lane-interleaved table of row h
   radix16_fwd<W, true, kLazy, true>(x, twr + ((size_t)h * 15 * 16 + u), 0u, ar);
 #pragma unroll
@@ -492,14 +497,17 @@ __device__ __forceinline__ void ntt_inv_rows_body(const Batch& batch, int b, con
     vec_unpack(vrow[row_vec_slot<W>(u * RV::kPerThread + jj)], &x[jj * RV::kWords]);
   radix16_inv<W, true, kLazy, 0, true>(x, twri + ((size_t)h * 15 * 16 + u), 0u, ar);
   __syncwarp();
+  W* t_own = trow + (unsigned)(u * 17);  // row_pos(u * 16 + j) = u * 17 + j
+  W* t_strided = trow + u;             // row_pos(j * 16 + u) = j * 17 + u
 #pragma unroll
-  for (int j = 0; j < 16; j++) trow[row_pos(u * 16 + j)] = x[j];
+  for (int j = 0; j < 16; j++) t_own[j] = x[j];
   __syncwarp();
 #pragma unroll
-  for (int j = 0; j < 16; j++) x[j] = trow[row_pos(j * 16 + u)];
+  for (int j = 0; j < 16; j++) x[j] = t_strided[j * 17];
   radix16_inv<W, true, kLazy, 4>(x, twi, 256u + (uint32_t)h, ar);
+  W* dcol = dst + u;
 #pragma unroll
-  for (int j = 0; j < 16; j++) dst[j * 16 + u] = x[j];
+  for (int j = 0; j < 16; j++) dcol[j * 16] = x[j];
 }
 
 // Row pass (levels 3 and 2): in -> out; values leave in [0, 2q) (strict) or below 2^10 q (lazy).
@@ -536,20 +544,23 @@ __device__ __forceinline__ void ntt_inv_cols_body(const Batch& batch, const InvS
   const W q = pc.q;
   const int tid = threadIdx.x, c = tid % kCols, u = tid / kCols;
   const int col = blockIdx.x * kCols + c;
-  W* buf = batch.out_limb(b);
+  W* buf_own = batch.out_limb(b) + (unsigned)(u * 16 * 256 + col);
+  W* buf_strided = batch.out_limb(b) + (unsigned)(u * 256 + col);
+  W* t_strided = tile + (unsigned)(u * kCols + c);
+  W* t_own = tile + (unsigned)(u * 16 * kCols + c);
   W x[16];
 #pragma unroll
   for (int j = 0; j < 16; j++) {
-    x[j] = buf[(u * 16 + j) * 256 + col];
+    x[j] = buf_own[j * 256];
     if (kLazy) x[j] = reduce_lazy(x[j], pc.one_shoup, ar.nq);  // back below 4q for the second pass
   }
   __syncthreads();
   radix16_inv<W, false, kLazy, 0>(x, stw, 16u + (uint32_t)u, ar);
 #pragma unroll
-  for (int j = 0; j < 16; j++) tile[(u * 16 + j) * kCols + c] = x[j];
+  for (int j = 0; j < 16; j++) t_own[j * kCols] = x[j];
   __syncthreads();
 #pragma unroll
-  for (int j = 0; j < 16; j++) x[j] = tile[(j * 16 + u) * kCols + c];
+  for (int j = 0; j < 16; j++) x[j] = t_strided[j * 16 * kCols];
   radix16_inv_final<W, kLazy>(x, stw, pc, ar);
   if (sc.scale != nullptr) {
     const W s = __ldg(sc.scale + b), ss = __ldg(sc.scale_shoup + b);
@@ -557,7 +568,7 @@ __device__ __forceinline__ void ntt_inv_cols_body(const Batch& batch, const InvS
     for (int j = 0; j < 16; j++) x[j] = csub<W>(mul_shoup_lazy<W>(x[j], s, ss, q), q);
   }
 #pragma unroll
-  for (int j = 0; j < 16; j++) buf[(j * 16 + u) * 256 + col] = x[j];
+  for (int j = 0; j < 16; j++) buf_strided[j * 16 * 256] = x[j];
 }
 
 // Column pass (levels 1 and 0), in place on the output limb of the row pass; scales by
