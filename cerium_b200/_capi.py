@@ -58,6 +58,8 @@ SIGNATURES = {
     "cerium_keyswitch_workspace_bytes": (_sz, [_vp]),
     "cerium_keyswitch_apply": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cerium_hrot": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, C.c_uint32, _vp]),
+    "cerium_hoisted_begin": (C.c_int, [_vp, _vp, _vp]),
+    "cerium_hoisted_rotate": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, C.c_uint32, _vp]),
     "cerium_hmult": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_int, _vp]),
     "cerium_rescale": (C.c_int, [_vp, C.c_int, _vp, _vp, _u32p, C.c_int, C.c_int, _vp, _vp]),
     "cerium_probe_int_pipe": (C.c_int, [C.c_int, C.POINTER(C.c_double), C.c_int]),
@@ -287,6 +289,12 @@ class KeySwitch:
 
     def hrot(self, out0: int, out1: int, c0: int, c1: int, evk: int, galois_elt: int, stream: int = 0):
         self.ctx.lib.check(self.ctx.lib.dll.cerium_hrot(self.h, out0, out1, c0, c1, evk, galois_elt, stream))
+
+    def hoisted_begin(self, c1: int, stream: int = 0):
+        self.ctx.lib.check(self.ctx.lib.dll.cerium_hoisted_begin(self.h, c1, stream))
+
+    def hoisted_rotate(self, out0: int, out1: int, c0: int, c1: int, evk_pre: int, galois_elt: int, stream: int = 0):
+        self.ctx.lib.check(self.ctx.lib.dll.cerium_hoisted_rotate(self.h, out0, out1, c0, c1, evk_pre, galois_elt, stream))
 
     def hmult(self, out0: int, out1: int, a0: int, a1: int, b0: int, b1: int, evk: int, do_rescale: bool,
               stream: int = 0):

@@ -124,17 +124,15 @@ int keyswitch_begin(cerium_keyswitch* ks, void* dst, const void* cpoly, cudaStre
 
 // Steps 2-7 from the coefficient-form limbs of ALL ranks (`gathered`: global limb i at slot
 // (i % world) * gather_limbs + i / world).
-int keyswitch_finish(cerium_keyswitch* ks, void* out0, void* out1, const void* gathered, const void* cpoly,
-                     const void* evk, const void* add0, const void* add1, cudaStream_t stream) {
+// Steps 2-3: base conversion of every digit and forward transform of the converted limbs into
+// the plan's `raised` buffer.
+int keyswitch_raise(cerium_keyswitch* ks, const void* gathered, cudaStream_t stream) {
   cerium_context* ctx = ks->ctx;
   const size_t n = kN;
-  const int L = ks->L, K = ks->K, LK = ks->LK, dnum = ks->dnum;
+  const int LK = ks->LK;
   return dispatch_word(ctx->word_bits, [&](auto tag) -> int {
     using W = decltype(tag);
-    using V = Vec16<W>;
     W* raised = ws_at<W>(ks, ks->o_raised);
-    W* acc = ws_at<W>(ks, ks->o_acc);
-    W* conv = ws_at<W>(ks, ks->o_conv);
     // 2. ModUp base conversion, every digit in one launch
     {
       std::vector<BconvCall> calls;
@@ -149,6 +147,23 @@ int keyswitch_finish(cerium_keyswitch* ks, void* out0, void* out1, const void* g
       NttCall c{raised, raised, n, n, ks->ntt_pos.data(), ks->ntt_prime.data(), (int)ks->ntt_pos.size()};
       if (int rc = launch_ntt_forward(ctx, c, stream, /*lazy_out=*/true)) return rc;
     }
+    return CERIUM_OK;
+  });
+}
+
+// Steps 4-7 on the digits that keyswitch_raise left in the plan: inner product with `evk`,
+// ModDown, optional additions.  Can be repeated with different keys (hoisting).
+int keyswitch_inner_moddown(cerium_keyswitch* ks, void* out0, void* out1, const void* cpoly, const void* evk,
+                            const void* add0, const void* add1, cudaStream_t stream) {
+  cerium_context* ctx = ks->ctx;
+  const size_t n = kN;
+  const int L = ks->L, K = ks->K, LK = ks->LK, dnum = ks->dnum;
+  return dispatch_word(ctx->word_bits, [&](auto tag) -> int {
+    using W = decltype(tag);
+    using V = Vec16<W>;
+    W* raised = ws_at<W>(ks, ks->o_raised);
+    W* acc = ws_at<W>(ks, ks->o_acc);
+    W* conv = ws_at<W>(ks, ks->o_conv);
     // 4. inner product with the key
     {
       InnerProductArgs<W> g{};
@@ -250,6 +265,12 @@ int keyswitch_finish(cerium_keyswitch* ks, void* out0, void* out1, const void* g
     }
     return CERIUM_OK;
   });
+}
+
+int keyswitch_finish(cerium_keyswitch* ks, void* out0, void* out1, const void* gathered, const void* cpoly,
+                     const void* evk, const void* add0, const void* add1, cudaStream_t stream) {
+  if (int rc = keyswitch_raise(ks, gathered, stream)) return rc;
+  return keyswitch_inner_moddown(ks, out0, out1, cpoly, evk, add0, add1, stream);
 }
 
 int keyswitch_impl(cerium_keyswitch* ks, void* out0, void* out1, const void* cpoly, const void* evk,
@@ -507,6 +528,33 @@ int cerium_hrot(cerium_keyswitch* ks, void* out0, void* out1, const void* c0, co
   if (int rc = cerium_automorph(ctx, rot0, n, c0, n, galois_elt, ks->L, stream)) return rc;
   if (int rc = cerium_automorph(ctx, rot1, n, c1, n, galois_elt, ks->L, stream)) return rc;
   return keyswitch_impl(ks, out0, out1, rot1, evk, rot0, nullptr, (cudaStream_t)stream);
+}
+
+int cerium_hoisted_begin(cerium_keyswitch* ks, const void* c1, void* stream) {
+  if (!ks || !c1) return fail(CERIUM_ERR_INVALID, "hoisted_begin: null argument");
+  if (ks->world != 1) return fail(CERIUM_ERR_INVALID, "hoisted_begin: sharded plans are driven through the begin / finish calls");
+  DeviceGuard guard(ks->ctx->device);
+  void* coef = static_cast<char*>(ks->ws) + ks->o_coef * ks->ctx->word_bytes();
+  if (int rc = keyswitch_begin(ks, coef, c1, (cudaStream_t)stream)) return rc;
+  return keyswitch_raise(ks, coef, (cudaStream_t)stream);
+}
+
+int cerium_hoisted_rotate(cerium_keyswitch* ks, void* out0, void* out1, const void* c0, const void* c1,
+                          const void* evk_pre, uint32_t galois_elt, void* stream) {
+  if (!ks || !out0 || !out1 || !c0 || !c1 || !evk_pre) return fail(CERIUM_ERR_INVALID, "hoisted_rotate: null argument");
+  if (!(galois_elt & 1) || galois_elt >= 2u * kN) return fail(CERIUM_ERR_INVALID, "hoisted_rotate: Galois element is not valid");
+  if (ks->world != 1) return fail(CERIUM_ERR_INVALID, "hoisted_rotate: sharded plans are driven through the begin / finish calls");
+  cerium_context* ctx = ks->ctx;
+  DeviceGuard guard(ctx->device);
+  const size_t n = kN;
+  const size_t wb = ctx->word_bytes();
+  char* tmp = static_cast<char*>(ks->ws) + ks->o_tmp * wb;
+  void* t0 = tmp;
+  void* t1 = tmp + (size_t)ks->L * n * wb;
+  // (t0, t1) = KeySwitch(c1) + (c0, 0) on the un-rotated digits, then the automorphism
+  if (int rc = keyswitch_inner_moddown(ks, t0, t1, c1, evk_pre, c0, nullptr, (cudaStream_t)stream)) return rc;
+  if (int rc = cerium_automorph(ctx, out0, n, t0, n, galois_elt, ks->L, stream)) return rc;
+  return cerium_automorph(ctx, out1, n, t1, n, galois_elt, ks->L, stream);
 }
 
 int cerium_hmult(cerium_keyswitch* ks, void* out0, void* out1, const void* a0, const void* a1, const void* b0,

@@ -250,6 +250,22 @@ CERIUM_API int cerium_hrot(cerium_keyswitch *ks, void *out0, void *out1, const v
                 const void *evk, uint32_t galois_elt, void *stream);
 
 /*
+ * Hoisted rotations: several rotations of one ciphertext share the expensive half of the key
+ * switch (inverse transform, base conversion and forward transform of c1's digits).  Restates the
+ * reference's HoistedRotate lowering (cerium/compiler/backend/compiler.cc:958-1153: one
+ * INTT -> BCONV -> NTT of c1, then per rotation an inner product with the RotationInv key,
+ * ModDown, c0' = ks0 + c0, and the automorphism applied AFTER key switching, :1084-1135).
+ *   cerium_hoisted_begin   raises c1 once into the plan's workspace
+ *   cerium_hoisted_rotate  (out0,out1) = phi( KeySwitch(c1; evk_pre) + (c0, 0) ), phi = galois_elt
+ * evk_pre is the rotation key of phi with every limb pre-permuted by phi^-1 (the reference's
+ * "RotationInv" key): phi(sum_d a_d * phi^-1(k_d)) = sum_d phi(a_d) * k_d.  c1 must be the
+ * polynomial given to cerium_hoisted_begin; any number of rotate calls may follow one begin.
+ */
+CERIUM_API int cerium_hoisted_begin(cerium_keyswitch *ks, const void *c1, void *stream);
+CERIUM_API int cerium_hoisted_rotate(cerium_keyswitch *ks, void *out0, void *out1, const void *c0,
+                          const void *c1, const void *evk_pre, uint32_t galois_elt, void *stream);
+
+/*
  * HMult + relinearize (+ rescale by the last limb when do_rescale != 0): tensor product,
  * key switch of d2, addition of d0/d1 (cerium/compiler/backend/compiler.cc:443-467,
  * compiler_keyswitch.cc:360-380) and rescale (compiler_rescale.cc:209-284).  Outputs hold

@@ -329,6 +329,16 @@ def case_keyswitch(be, word_bits, L, K, dnum, bconv_mode, round_mode):
     w0, w1 = h.orc.hrot(bconv_mode, round_mode, prm.q_idx, prm.p_idx, dnum, elt, c0, c1, evk)
     assert np.array_equal(h.down(o0), w0), "HRot c0 differs"
     assert np.array_equal(h.down(o1), w1), "HRot c1 differs"
+    # hoisted rotations: one ModUp, several rotations with pre-permuted keys
+    ks.hoisted_begin(h.p(d_c1))
+    for step in (1, -2):
+        e2 = be.lib.galois_elt_from_step(step, LOGN)
+        k0, k1 = h.orc.keyswitch(bconv_mode, round_mode, prm.q_idx, prm.p_idx, dnum, c1, evk)
+        k0 = np.stack([oracle.ew("add", prm.moduli[p], k0[i], c0[i]) for i, p in enumerate(prm.q_idx)])
+        w0 = np.stack([oracle.apply_galois_ntt(e2, LOGN, k0[i]) for i in range(L)])
+        w1 = np.stack([oracle.apply_galois_ntt(e2, LOGN, k1[i]) for i in range(L)])
+        ks.hoisted_rotate(h.p(o0), h.p(o1), h.p(d_c0), h.p(d_c1), h.p(d_evk), e2)
+        assert np.array_equal(h.down(o0), w0) and np.array_equal(h.down(o1), w1), "hoisted rotation differs"
     # HMult + relinearise, with and without rescale
     b0, b1 = rand_limbs(rng, prm.moduli, prm.q_idx), rand_limbs(rng, prm.moduli, prm.q_idx)
     d_b0, d_b1 = h.up(b0), h.up(b1)

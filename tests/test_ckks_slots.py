@@ -60,6 +60,31 @@ def test_oracle_lazy_conversion_on_the_reference_prime_chain():
     assert np.allclose(ck.decrypt(o0, o1, scale, use=4).real, np.roll(z, -step), rtol=1e-5, atol=1e-4)
 
 
+def prepermuted_key(evk, elt):
+    """phi^-1 applied to every limb of a key: the reference's RotationInv key for hoisting."""
+    inv = pow(int(elt), -1, 2 * N)
+    flat = evk.reshape(-1, N)
+    return np.stack([oracle.apply_galois_ntt(inv, LOGN, row) for row in flat]).reshape(evk.shape)
+
+
+def test_oracle_hoisted_rotation_identity():
+    """phi( KeySwitch(c1; phi^-1(key)) + (c0, 0) ) decrypts to the rotated slots."""
+    prm = small_set(3, 2, 2)
+    ck = CkksRef(prm, seed=14)
+    rng = np.random.default_rng(7)
+    z = rng.uniform(-1, 1, N // 2)
+    scale = 2.0 ** 40
+    c0, c1 = ck.encrypt(z, scale)
+    step = 9
+    elt = oracle.galois_elt_from_step(step, LOGN)
+    pre = prepermuted_key(ck.rotation_key(elt), elt)
+    k0, k1 = ck.octx.keyswitch(oracle.BCONV_EXACT, oracle.ROUND_HALF, prm.q_idx, prm.p_idx, prm.dnum, c1, pre)
+    k0 = np.stack([oracle.ew("add", prm.moduli[p], k0[i], c0[i]) for i, p in enumerate(prm.q_idx)])
+    o0 = np.stack([oracle.apply_galois_ntt(elt, LOGN, k0[i]) for i in range(prm.L)])
+    o1 = np.stack([oracle.apply_galois_ntt(elt, LOGN, k1[i]) for i in range(prm.L)])
+    assert np.allclose(ck.decrypt(o0, o1, scale).real, np.roll(z, -step), rtol=1e-5, atol=1e-4)
+
+
 def test_oracle_hmult_relin_rescale_decrypts_to_product():
     prm = small_set(3, 1, 3)
     ck = CkksRef(prm, seed=11)
@@ -99,6 +124,14 @@ def test_gpu_rotation_and_product_decrypt_correctly():
     ks.hrot(be.ptr(o0), be.ptr(o1), be.ptr(d[0]), be.ptr(d[1]), be.ptr(evk), elt)
     got = ck.decrypt(be.to_host(o0), be.to_host(o1), scale).real
     assert np.allclose(got, np.roll(x, -step), rtol=1e-5, atol=1e-4)
+    # hoisted: one ModUp of c1, two rotations with pre-permuted keys
+    ks.hoisted_begin(be.ptr(d[1]))
+    for st in (1, 64):
+        e2 = be.lib.galois_elt_from_step(st, LOGN)
+        pre = up(prepermuted_key(ck.rotation_key(e2), e2))
+        ks.hoisted_rotate(be.ptr(o0), be.ptr(o1), be.ptr(d[0]), be.ptr(d[1]), be.ptr(pre), e2)
+        got = ck.decrypt(be.to_host(o0), be.to_host(o1), scale).real
+        assert np.allclose(got, np.roll(x, -st), rtol=1e-5, atol=1e-4)
     rk = up(ck.relin_key())
     r0, r1 = be.empty((prm.L - 1, N), np.uint64), be.empty((prm.L - 1, N), np.uint64)
     ks.hmult(be.ptr(r0), be.ptr(r1), be.ptr(d[0]), be.ptr(d[1]), be.ptr(d[2]), be.ptr(d[3]), be.ptr(rk), True)
