@@ -64,7 +64,19 @@ int launch_ntt_forward(cerium_context* ctx, const NttCall& c, cudaStream_t strea
       StridedBatch<W> rows = cols;
       rows.in = static_cast<const W*>(c.out);
       rows.in_stride = c.out_stride;
-      { auto kfn = ntt_fwd_cols_kernel<W, StridedBatch<W>, PlainLoader<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kCols, cnt), kCols * 16, 0, stream, cols, PlainLoader<W>{}, static_cast<const Pair*>(ctx->d_tw_fwd), static_cast<const PrimeConst<W>*>(ctx->d_pcs)); }
+      if (c.src_pos != nullptr) {
+        GatherBatch<W> gb{};
+        static_cast<StridedBatch<W>&>(gb) = cols;
+        for (int b = 0; b < cnt; b++) {
+          if (c.src_pos[first + b] > 0xffffu) return fail(CERIUM_ERR_INVALID, "limb slot exceeds 65535");
+          gb.in_pos[b] = (uint16_t)c.src_pos[first + b];
+        }
+        auto kfn = ntt_fwd_cols_kernel<W, GatherBatch<W>, ModLoader<W>>;
+        CERIUM_LAUNCH(kfn, dim3(256 / kCols, cnt), kCols * 16, 0, stream, gb, ModLoader<W>{}, static_cast<const Pair*>(ctx->d_tw_fwd), static_cast<const PrimeConst<W>*>(ctx->d_pcs));
+      } else {
+        auto kfn = ntt_fwd_cols_kernel<W, StridedBatch<W>, PlainLoader<W>>;
+        CERIUM_LAUNCH(kfn, dim3(256 / kCols, cnt), kCols * 16, 0, stream, cols, PlainLoader<W>{}, static_cast<const Pair*>(ctx->d_tw_fwd), static_cast<const PrimeConst<W>*>(ctx->d_pcs));
+      }
       if (lazy_out) {
         auto kfn = ntt_fwd_rows_kernel<W, StridedBatch<W>, LazyStoreEpilogue<W>>;
         CERIUM_LAUNCH(kfn, dim3(256 / kRowsPerCta, cnt), kRowsPerCta * 16, 0, stream, rows, LazyStoreEpilogue<W>{}, static_cast<const Pair*>(ctx->d_tw_fwd), static_cast<const Pair*>(ctx->d_twr_fwd), static_cast<const PrimeConst<W>*>(ctx->d_pcs));
@@ -157,7 +169,17 @@ int launch_sud(cerium_context* ctx, const SudCall& c, cudaStream_t stream) {
         ld.src_q = (W)c.src_q;
         ld.pre_add = (W)c.pre_add;
         for (int b = 0; b < cnt; b++) ld.post_sub[b] = c.post_sub ? (W)c.post_sub[first + b] : (W)0;
-        { auto kfn = ntt_fwd_cols_kernel<W, StridedBatch<W>, ReduceLoader<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kCols, cnt), kCols * 16, 0, stream, cols, ld, tw, pcs); }
+        if (c.src_pos != nullptr) {
+          GatherBatch<W> gb{};
+          static_cast<StridedBatch<W>&>(gb) = cols;
+          gb.in = static_cast<const W*>(c.src);
+          for (int b = 0; b < cnt; b++) gb.in_pos[b] = (uint16_t)c.src_pos[first + b];
+          auto kfn = ntt_fwd_cols_kernel<W, GatherBatch<W>, ReduceLoader<W>>;
+          CERIUM_LAUNCH(kfn, dim3(256 / kCols, cnt), kCols * 16, 0, stream, gb, ld, tw, pcs);
+        } else {
+          auto kfn = ntt_fwd_cols_kernel<W, StridedBatch<W>, ReduceLoader<W>>;
+          CERIUM_LAUNCH(kfn, dim3(256 / kCols, cnt), kCols * 16, 0, stream, cols, ld, tw, pcs);
+        }
       } else {
         { auto kfn = ntt_fwd_cols_kernel<W, StridedBatch<W>, PlainLoader<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kCols, cnt), kCols * 16, 0, stream, cols, PlainLoader<W>{}, tw, pcs); }
       }

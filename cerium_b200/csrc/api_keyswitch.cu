@@ -37,6 +37,10 @@ struct cerium_keyswitch {
   std::vector<uint64_t> pinv;      // [L] P^-1 mod q_i
   // transform batches
   std::vector<uint32_t> ntt_pos, ntt_prime;  // converted limbs of all digits inside `raised`
+  // one-limb digits: the conversion is a plain reduction, done by the transform as it reads the
+  // digit's limb (slot ntt_src[b] of the gathered buffer); no converters exist then
+  bool direct_raise = false;
+  std::vector<uint32_t> ntt_src;
   std::vector<uint32_t> ext_pos, ext_prime;  // extension limbs of both accumulators
   // exact mode: per-limb scalars folded into the inverse transforms (device, one word per entry)
   void* d_scale = nullptr;  // [L] then [2K]: scale, and at +count their Shoup companions
@@ -61,19 +65,24 @@ W* ws_at(const cerium_keyswitch* ks, size_t off_words) {
   return static_cast<W*>(ks->ws) + off_words;
 }
 
-int rescale_impl(cerium_context* ctx, int round_mode, void* out, const void* in, const uint32_t* q_idx, int L,
-                 int n_polys, void* scratch, cudaStream_t stream) {
+// Drops the last limb of n_polys polynomials stored back to back in `in` ([n_polys][L][N]);
+// polynomial p goes to outs[p] ([L-1][N]).  Two polynomials share a launch pair when their
+// results are adjacent in memory or `pair_work` (a [2(L-1)][N] stack) is given.
+int rescale_impl(cerium_context* ctx, int round_mode, void* const* outs, void* pair_work, const void* in,
+                 const uint32_t* q_idx, int L, int n_polys, void* scratch, cudaStream_t stream) {
   const size_t n = kN;
   const size_t wb = ctx->word_bytes();
+  const size_t limb = n * wb;
   const uint32_t last = q_idx[L - 1];
   const uint64_t ql = ctx->moduli[last];
+  const int R = L - 1;
   // 1. inverse transform of the last limb of every polynomial -> scratch[poly][N]
   std::vector<uint32_t> pos(n_polys), prime(n_polys, last);
   for (int p = 0; p < n_polys; p++) pos[p] = (uint32_t)p;
   {
     // input limb of poly p sits at in + (p*L + L-1)*N: base shifted to the first such limb, stride L*N
     NttCall c{};
-    c.in = static_cast<const char*>(in) + (size_t)(L - 1) * n * wb;
+    c.in = static_cast<const char*>(in) + (size_t)R * limb;
     c.in_stride = (size_t)L * n;
     c.out = scratch;
     c.out_stride = n;
@@ -83,32 +92,46 @@ int rescale_impl(cerium_context* ctx, int round_mode, void* out, const void* in,
     if (int rc = launch_ntt_inverse(ctx, c, nullptr, nullptr, stream)) return rc;
   }
   // 2. SuD of the remaining limbs against the re-reduced last limb
-  std::vector<uint64_t> factor(L - 1), post_sub(L - 1);
+  std::vector<uint64_t> factor(2 * R), post_sub(2 * R);
+  std::vector<uint32_t> prime2(2 * R), src_pos(2 * R);
   const uint64_t half = ql >> 1;
-  for (int i = 0; i < L - 1; i++) {
-    const uint64_t q = ctx->moduli[q_idx[i]];
+  for (int i = 0; i < 2 * R; i++) {
+    const uint64_t q = ctx->moduli[q_idx[i % R]];
+    prime2[i] = q_idx[i % R];
     factor[i] = host::invmod(ql % q, q);
     post_sub[i] = round_mode == CERIUM_ROUND_HALF ? half % q : 0;
+    src_pos[i] = i < R ? 0 : 1;
   }
-  for (int p = 0; p < n_polys; p++) {
+  for (int p = 0; p < n_polys;) {
     SudCall s{};
-    s.src = static_cast<const char*>(scratch) + (size_t)p * n * wb;
-    s.src_stride = 0;
-    s.work = static_cast<char*>(out) + (size_t)p * (L - 1) * n * wb;
+    s.src = static_cast<const char*>(scratch) + (size_t)p * limb;
     s.work_stride = n;
-    s.dst = s.work;
+    s.dst = outs[p];
     s.dst_stride = n;
-    s.minuend = static_cast<const char*>(in) + (size_t)p * L * n * wb;
+    s.minuend = static_cast<const char*>(in) + (size_t)p * L * limb;
     s.minuend_stride = n;
-    s.addend = nullptr;
-    s.addend_stride = 0;
-    s.prime = q_idx;
+    s.prime = prime2.data();
     s.factor = factor.data();
-    s.count = L - 1;
     s.reduce_src = true;
     s.src_q = ql;
     s.pre_add = round_mode == CERIUM_ROUND_HALF ? half : 0;
     s.post_sub = post_sub.data();
+    const bool adjacent = p + 1 < n_polys && outs[p + 1] == static_cast<char*>(outs[p]) + (size_t)R * limb;
+    if (p + 1 < n_polys && 2 * R <= kSudMaxBatch && (adjacent || pair_work != nullptr)) {
+      s.src_stride = n;
+      s.src_pos = src_pos.data();
+      s.work = adjacent ? outs[p] : pair_work;
+      s.count = 2 * R;
+      s.split = R;
+      s.dst2 = outs[p + 1];
+      s.minuend2 = static_cast<const char*>(in) + (size_t)(p + 1) * L * limb;
+      p += 2;
+    } else {
+      s.src_stride = 0;
+      s.work = outs[p];
+      s.count = R;
+      p += 1;
+    }
     if (int rc = launch_sud(ctx, s, stream)) return rc;
   }
   return CERIUM_OK;
@@ -133,6 +156,11 @@ int keyswitch_raise(cerium_keyswitch* ks, const void* gathered, cudaStream_t str
   return dispatch_word(ctx->word_bits, [&](auto tag) -> int {
     using W = decltype(tag);
     W* raised = ws_at<W>(ks, ks->o_raised);
+    if (ks->direct_raise) {
+      NttCall c{gathered, raised, n, n, ks->ntt_pos.data(), ks->ntt_prime.data(), (int)ks->ntt_pos.size()};
+      c.src_pos = ks->ntt_src.data();
+      return launch_ntt_forward(ctx, c, stream, /*lazy_out=*/true);
+    }
     // 2. ModUp base conversion, every digit in one launch
     {
       std::vector<BconvCall> calls;
@@ -337,6 +365,7 @@ static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, in
   const int bits = ctx->word_bits;
   const bool exact = bconv_mode == CERIUM_BCONV_EXACT;
   std::vector<uint64_t> scale_q(std::max(L, 1), 1), scale_p(2 * K, 1);
+  ks->direct_raise = alpha == 1;
   auto slot_of = [&](int i) { return (uint32_t)((i % world) * ks->gather_limbs + i / world); };
   int rc = CERIUM_OK;
   // per-digit converters: inputs = global limbs {d, d+dnum, ...} (read from the gathered buffer),
@@ -355,8 +384,9 @@ static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, in
       out_pos.push_back((uint32_t)e);
       ks->ntt_pos.push_back((uint32_t)(d * LK + e));
       ks->ntt_prime.push_back(ks->all_idx[e]);
+      ks->ntt_src.push_back(slot_of(d));
     }
-    if (in_primes.empty() || out_primes.empty()) continue;
+    if (in_primes.empty() || out_primes.empty() || ks->direct_raise) continue;
     BconvOptions opt;
     opt.prescaled = exact;
     opt.out_pos = out_pos;
@@ -576,10 +606,10 @@ int cerium_hmult(cerium_keyswitch* ks, void* out0, void* out1, const void* a0, c
   char* kso = static_cast<char*>(ks->ws) + ks->o_ksout * wb;  // [2][L][N], contiguous: two polynomials
   if (int rc = keyswitch_impl(ks, kso, kso + (size_t)ks->L * limb, d2, evk, d0, d1, (cudaStream_t)stream)) return rc;
   void* scratch = static_cast<char*>(ks->ws) + ks->o_scratch * wb;
-  // out0 / out1 are separate buffers: rescale each polynomial on its own
-  if (int rc = rescale_impl(ctx, ks->round_mode, out0, kso, ks->q_idx.data(), ks->L, 1, scratch, (cudaStream_t)stream)) return rc;
-  return rescale_impl(ctx, ks->round_mode, out1, kso + (size_t)ks->L * limb, ks->q_idx.data(), ks->L, 1,
-                      static_cast<char*>(scratch) + limb, (cudaStream_t)stream);
+  // out0 / out1 are separate buffers: the shared column pass works in the (now free) ModDown buffer
+  void* outs[2] = {out0, out1};
+  void* pair_work = static_cast<char*>(ks->ws) + ks->o_conv * wb;
+  return rescale_impl(ctx, ks->round_mode, outs, pair_work, kso, ks->q_idx.data(), ks->L, 2, scratch, (cudaStream_t)stream);
 }
 
 int cerium_rescale(cerium_context* ctx, int round_mode, void* out, const void* in, const uint32_t* q_idx, int L,
@@ -592,7 +622,9 @@ int cerium_rescale(cerium_context* ctx, int round_mode, void* out, const void* i
     if (q_idx[i] >= (uint32_t)ctx->n_primes) return fail(CERIUM_ERR_INVALID, "rescale: prime index out of range");
   if (((uintptr_t)out | (uintptr_t)in | (uintptr_t)scratch) & 15u) return fail(CERIUM_ERR_INVALID, "rescale: pointers must be 16-byte aligned");
   DeviceGuard guard(ctx->device);
-  return rescale_impl(ctx, round_mode, out, in, q_idx, L, n_polys, scratch, (cudaStream_t)stream);
+  std::vector<void*> outs(n_polys);
+  for (int p = 0; p < n_polys; p++) outs[p] = static_cast<char*>(out) + (size_t)p * (L - 1) * kN * ctx->word_bytes();
+  return rescale_impl(ctx, round_mode, outs.data(), nullptr, in, q_idx, L, n_polys, scratch, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -134,6 +134,9 @@ struct NttCall {
   const uint32_t* pos;    // count entries, or null for 0..count-1
   const uint32_t* prime;  // count entries
   int count;
+  // forward transform only: entry b reads limb src_pos[b] of `in`, residues of another modulus,
+  // and reduces them to its own prime on the way in (null: reads limb pos[b], already reduced)
+  const uint32_t* src_pos = nullptr;
 };
 // lazy_out: leave the results below 4q instead of canonical (internal buffers read by the inner product only)
 int launch_ntt_forward(cerium_context* ctx, const NttCall& c, cudaStream_t stream, bool lazy_out = false);
@@ -167,6 +170,9 @@ struct SudCall {
   uint64_t src_q = 0;
   uint64_t pre_add = 0;
   const uint64_t* post_sub = nullptr;  // count residues (host) or null
+  // only with reduce_src: entry b reads limb src_pos[b] of src (null: limb b, or the one limb
+  // when src_stride == 0)
+  const uint32_t* src_pos = nullptr;
 };
 int launch_sud(cerium_context* ctx, const SudCall& c, cudaStream_t stream);
 

@@ -64,6 +64,16 @@ struct StridedBatch {
   __device__ __forceinline__ uint32_t prime_of(int b) const { return prime[b]; }
 };
 
+// StridedBatch whose entries read from a slot of their own: entry b reads limb in_pos[b] of `in`
+// and writes limb pos[b] of `out` (one coefficient-form limb transformed under many primes).
+template <typename W>
+struct GatherBatch : StridedBatch<W> {
+  uint16_t in_pos[kMaxBatch];
+  __device__ __forceinline__ const W* in_limb(int b) const {
+    return this->in + (size_t)in_pos[b] * this->in_stride;
+  }
+};
+
 // Addressing through device-resident pointer tables, the layout the reference's launchers
 // take (args_outputs / args_inputs / bases, cerium/compiler/backend/kernels/function.cu:22-39).
 template <typename W>
@@ -244,6 +254,15 @@ __device__ __forceinline__ uint4 vec_pack(const uint32_t* w) { return make_uint4
 template <typename W>
 struct PlainLoader {
   __device__ __forceinline__ W apply(W x, int /*b*/, const PrimeConst<W>& /*pc*/) const { return x; }
+};
+
+// Source residues belong to another modulus: any word -> [0, q) of the entry's prime.  This is
+// the whole base conversion of a one-limb digit (Qhat = 1), fused into the transform's first read.
+template <typename W>
+struct ModLoader {
+  __device__ __forceinline__ W apply(W x, int /*b*/, const PrimeConst<W>& pc) const {
+    return reduce_word<W>(x, pc);
+  }
 };
 
 constexpr int kSudMaxBatch = 96;  // limbs per launch when per-limb scalars travel as parameters

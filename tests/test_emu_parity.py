@@ -49,7 +49,7 @@ def test_sud(be, word_bits):
 
 @pytest.mark.parametrize("word_bits,round_mode", [(64, _capi.ROUND_FLOOR), (64, _capi.ROUND_HALF), (32, _capi.ROUND_FLOOR)])
 def test_rescale(be, word_bits, round_mode):
-    pc.case_rescale(be, word_bits, round_mode, L=3, n_polys=2)
+    pc.case_rescale(be, word_bits, round_mode, L=3, n_polys=3)   # one pair and a single
 
 
 @pytest.mark.parametrize("word_bits,L,K,dnum,bm,rm", [
@@ -57,6 +57,7 @@ def test_rescale(be, word_bits, round_mode):
     (64, 3, 1, 3, _capi.BCONV_EXACT, _capi.ROUND_HALF),
     (64, 5, 2, 3, _capi.BCONV_EXACT, _capi.ROUND_HALF),   # ragged digits: sizes 2, 2, 1
     (32, 4, 2, 2, _capi.BCONV_LAZY, _capi.ROUND_FLOOR),
+    (32, 3, 1, 3, _capi.BCONV_LAZY, _capi.ROUND_FLOOR),   # one-limb digits: raise without converters
 ])
 def test_keyswitch_hrot_hmult(be, word_bits, L, K, dnum, bm, rm):
     pc.case_keyswitch(be, word_bits, L, K, dnum, bm, rm)

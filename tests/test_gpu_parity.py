@@ -52,7 +52,7 @@ def test_sud(be, word_bits):
 @pytest.mark.parametrize("word_bits,round_mode", [
     (64, _capi.ROUND_FLOOR), (64, _capi.ROUND_HALF), (32, _capi.ROUND_FLOOR), (32, _capi.ROUND_HALF)])
 def test_rescale(be, word_bits, round_mode):
-    pc.case_rescale(be, word_bits, round_mode, L=6, n_polys=2)
+    pc.case_rescale(be, word_bits, round_mode, L=6, n_polys=3)   # one pair and a single
 
 
 @pytest.mark.parametrize("word_bits,L,K,dnum,bm,rm", [
@@ -62,6 +62,7 @@ def test_rescale(be, word_bits, round_mode):
     (64, 9, 3, 3, _capi.BCONV_LAZY, _capi.ROUND_HALF),
     (32, 8, 4, 2, _capi.BCONV_LAZY, _capi.ROUND_FLOOR),
     (32, 6, 2, 3, _capi.BCONV_EXACT, _capi.ROUND_FLOOR),
+    (32, 5, 1, 5, _capi.BCONV_LAZY, _capi.ROUND_FLOOR),    # one-limb digits, 32-bit
 ])
 def test_keyswitch_hrot_hmult(be, word_bits, L, K, dnum, bm, rm):
     pc.case_keyswitch(be, word_bits, L, K, dnum, bm, rm)
