@@ -3,6 +3,7 @@
 // arithmetic lives in the *_kernels.cuh headers.  Mirrors the role of
 // cerium/runtime/execution/evaluator.cpp (Evaluator::fn_*) and device_utils.cu (execute_*).
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 
 #include "internal.h"
@@ -73,6 +74,9 @@ int launch_ntt_forward(cerium_context* ctx, const NttCall& c, cudaStream_t strea
         }
         auto kfn = ntt_fwd_cols_kernel<W, GatherBatch<W>, ModLoader<W>>;
         CERIUM_LAUNCH(kfn, dim3(256 / kCols, cnt), kCols * 16, 0, stream, gb, ModLoader<W>{}, static_cast<const Pair*>(ctx->d_tw_fwd), static_cast<const PrimeConst<W>*>(ctx->d_pcs));
+      } else if (c.lazy_in) {
+        auto kfn = ntt_fwd_cols_kernel<W, StridedBatch<W>, LazyLoader<W>>;
+        CERIUM_LAUNCH(kfn, dim3(256 / kCols, cnt), kCols * 16, 0, stream, cols, LazyLoader<W>{}, static_cast<const Pair*>(ctx->d_tw_fwd), static_cast<const PrimeConst<W>*>(ctx->d_pcs));
       } else {
         auto kfn = ntt_fwd_cols_kernel<W, StridedBatch<W>, PlainLoader<W>>;
         CERIUM_LAUNCH(kfn, dim3(256 / kCols, cnt), kCols * 16, 0, stream, cols, PlainLoader<W>{}, static_cast<const Pair*>(ctx->d_tw_fwd), static_cast<const PrimeConst<W>*>(ctx->d_pcs));
@@ -416,6 +420,7 @@ int cerium_context_create(cerium_context** out, int device, int log_n, int word_
   ctx->n_primes = n_moduli;
   ctx->moduli.assign(moduli, moduli + n_moduli);
   ctx->psi.resize(n_moduli);
+  if (const char* arith = std::getenv("CERIUM_B200_NTT_ARITH")) ctx->allow_fp = std::strcmp(arith, "int") != 0;
   const size_t n = kN;
   int rc = dispatch_word(word_bits, [&](auto tag) -> int {
     using W = decltype(tag);
@@ -427,9 +432,25 @@ int cerium_context_create(cerium_context** out, int device, int log_n, int word_
       const uint64_t q = moduli[k];
       host::PrimeTables t = host::build_prime_tables(q, log_n, word_bits);
       ctx->psi[k] = t.psi;
+      // primes below 2^50 run their butterflies on doubles: the tables then hold the centred
+      // twiddle and its correctly rounded quotient by q instead of the twiddle and its Shoup word
+      const bool fp = word_bits == 64 && q < ((uint64_t)1 << 50) && ctx->allow_fp;
+      auto fp_pair = [&](uint64_t w) {
+        const double wd = w > q / 2 ? -(double)(q - w) : (double)w;
+        const double wq = wd / (double)q;
+        uint64_t a, b;
+        std::memcpy(&a, &wd, 8);
+        std::memcpy(&b, &wq, 8);
+        return WordTraits<W>::make((W)a, (W)b);
+      };
       for (size_t i = 0; i < n; i++) {
-        fwd[k * n + i] = WordTraits<W>::make((W)t.w[i], (W)host::shoup(t.w[i], q, word_bits));
-        inv[k * n + i] = WordTraits<W>::make((W)t.wi[i], (W)host::shoup(t.wi[i], q, word_bits));
+        if (fp) {
+          fwd[k * n + i] = fp_pair(t.w[i]);
+          inv[k * n + i] = fp_pair(t.wi[i]);
+        } else {
+          fwd[k * n + i] = WordTraits<W>::make((W)t.w[i], (W)host::shoup(t.w[i], q, word_bits));
+          inv[k * n + i] = WordTraits<W>::make((W)t.wi[i], (W)host::shoup(t.wi[i], q, word_bits));
+        }
       }
       for (int h = 0; h < 256; h++)
         for (int t = 0; t < 4; t++)
@@ -453,6 +474,18 @@ int cerium_context_create(cerium_context** out, int device, int log_n, int word_
       pc.w1ninv = (W)w1;
       pc.w1ninv_shoup = (W)host::shoup(w1, q, word_bits);
       pc.lazy_ok = (W)((word_bits == 64 && q < ((uint64_t)1 << 52)) ? 1 : 0);
+      if (fp) {
+        const double qinv = 1.0 / (double)q;
+        uint64_t bits;
+        std::memcpy(&bits, &qinv, 8);
+        pc.fp_ok = 1;
+        pc.fp_qinv = (W)bits;
+        const auto ni = fp_pair(t.ninv), w1 = fp_pair(host::mulmod(t.wi[1], t.ninv, q));
+        pc.fp_ninv = ni.x;
+        pc.fp_ninv_q = ni.y;
+        pc.fp_w1ninv = w1.x;
+        pc.fp_w1ninv_q = w1.y;
+      }
     }
     CERIUM_CUDA(cudaMalloc(&ctx->d_tw_fwd, fwd.size() * sizeof(Pair)));
     CERIUM_CUDA(cudaMalloc(&ctx->d_tw_inv, inv.size() * sizeof(Pair)));

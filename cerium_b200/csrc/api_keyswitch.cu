@@ -173,6 +173,7 @@ int keyswitch_raise(cerium_keyswitch* ks, const void* gathered, cudaStream_t str
     // 3. NTT of every converted limb
     {
       NttCall c{raised, raised, n, n, ks->ntt_pos.data(), ks->ntt_prime.data(), (int)ks->ntt_pos.size()};
+      c.lazy_in = true;  // the converters of step 2 are created with lazy_out
       if (int rc = launch_ntt_forward(ctx, c, stream, /*lazy_out=*/true)) return rc;
     }
     return CERIUM_OK;

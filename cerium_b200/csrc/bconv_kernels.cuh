@@ -51,7 +51,7 @@ struct BconvOut {
   W q, q2, mu_hi, mu_lo, sub;  // sub = rounding term (0 when unused)
   uint32_t pos;                // limb slot of this output
   uint16_t has_sub;            // rounding term present
-  uint16_t strict;             // prime too wide for the lazy transform (needs inputs below 4q)
+  uint16_t strict;             // the prime's transform needs inputs below 4q (all but the lazy integer butterflies)
 };
 
 // Barrett reduction with the 3-multiply high products: qhat may be up to 7 short, so the
@@ -120,7 +120,7 @@ __device__ __forceinline__ void bconv_body_split64(const BconvDesc<uint64_t>& d,
     const BconvOut<uint64_t> o = sout[j];
     uint64_t r;
     if (kLazyOut) {
-      // consumer is the forward transform: [0, 8q) is fine for lazy primes, [0, 4q) for strict ones
+      // consumer is the forward transform: [0, 8q) is fine for lazy integer butterflies, the others take [0, 4q)
       const uint64_t qhat = hi * o.mu_hi + mulhi_approx64(lo, o.mu_hi) + mulhi_approx64(hi, o.mu_lo);
       r = lo - qhat * o.q;
       if (o.strict) r = csub<uint64_t>(r, o.q2 + o.q2);
@@ -229,7 +229,7 @@ __global__ void __launch_bounds__(kBconvThreads)
     o.sub = d.out_sub != nullptr ? d.out_sub[j] : (W)0;
     o.pos = d.out_pos != nullptr ? d.out_pos[j] : pos_base + (uint32_t)j;
     o.has_sub = d.out_sub != nullptr ? 1 : 0;
-    o.strict = pc.lazy_ok != 0 ? 0 : 1;
+    o.strict = (pc.lazy_ok != 0 && pc.fp_ok == 0) ? 0 : 1;
     sout[j] = o;
   }
   __syncthreads();

@@ -79,6 +79,9 @@ struct cerium_context {
   void* d_twr_fwd = nullptr; // Pair[n_primes][256][15][16], lane-interleaved level-3 twiddles (row pass)
   void* d_twr_inv = nullptr; // same for the inverse transform
   void* d_pcs = nullptr;     // PrimeConst<W>[n_primes]
+  // 64-bit primes below 2^50 transform on the FP64 pipe unless the environment variable
+  // CERIUM_B200_NTT_ARITH is "int" when the context is created (for comparisons)
+  bool allow_fp = true;
   size_t word_bytes() const { return (size_t)word_bits / 8; }
 };
 
@@ -137,6 +140,8 @@ struct NttCall {
   // forward transform only: entry b reads limb src_pos[b] of `in`, residues of another modulus,
   // and reduces them to its own prime on the way in (null: reads limb pos[b], already reduced)
   const uint32_t* src_pos = nullptr;
+  // forward transform only: the input words are below 4q instead of canonical
+  bool lazy_in = false;
 };
 // lazy_out: leave the results below 4q instead of canonical (internal buffers read by the inner product only)
 int launch_ntt_forward(cerium_context* ctx, const NttCall& c, cudaStream_t stream, bool lazy_out = false);

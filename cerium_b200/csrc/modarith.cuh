@@ -1,6 +1,7 @@
 // Word-generic modular arithmetic for RNS limbs (uint32_t with primes below 2^30,
-// uint64_t with primes below 2^62).  Device code only uses integer multiply/add;
-// there is no floating point and no tensor-core use on this path.
+// uint64_t with primes below 2^62).  Integer multiply/add throughout, except the transforms of
+// 64-bit primes below 2^50, whose butterflies run exactly on the FP64 pipe (see "double-precision
+// modular arithmetic" below); there is no tensor-core use on this path.
 //
 // Replaces cerium/compiler/backend/kernels/fhe_arith.cuh:28-193 (32-bit Barrett with
 // k = 58, lazy products below q^2) and the Shoup butterfly helpers of
@@ -62,7 +63,13 @@ struct PrimeConst {
   W w1ninv;      // psi^-(N/2) * N^-1 mod q  (inverse twiddle of index 1 times N^-1)
   W w1ninv_shoup;
   W lazy_ok;     // 1 when q < 2^52 (64-bit words only): butterflies may skip range corrections
-  W pad[6];
+  // 64-bit words, q < 2^50: constants of the double-precision butterflies, as bit patterns of doubles
+  W fp_ok;        // 1 when the transforms of this prime run on the FP64 pipe
+  W fp_qinv;      // RN(1 / q)
+  W fp_ninv;      // N^-1 mod q, centred in (-q/2, q/2)
+  W fp_ninv_q;    // RN(fp_ninv / q)
+  W fp_w1ninv;    // psi^-(N/2) * N^-1 mod q, centred
+  W fp_w1ninv_q;  // RN(fp_w1ninv / q)
 };
 
 // x * w mod q in [0, 2q) for ANY word x, given ws = floor(w * 2^B / q) with w < q.
@@ -227,6 +234,43 @@ __device__ __forceinline__ uint64_t reduce_lazy(uint64_t x, uint64_t one_shoup, 
 }
 __device__ __forceinline__ uint32_t reduce_lazy(uint32_t x, uint32_t one_shoup, uint32_t nq) {
   return x + __umulhi(x, one_shoup) * nq;
+}
+
+// ---------------------------------------------------------------------------------------
+// Double-precision modular arithmetic (primes below 2^50).
+//
+// B200 issues FP64 multiply-adds at the rate of 32-bit integer multiply-adds, on a pipe of their
+// own, and a 64-bit modular product costs 6 of them against 9 integer multiply-adds plus the
+// carries; the butterflies of the transforms therefore run on doubles holding exact integers.
+// Values are signed residues |x| <= B*q with B < 8 (so every sum is an exact integer below 2^53);
+// twiddles are centred, |w| < q/2, and come with wq = RN(w / q).
+//
+//   fp_mulmod(y, w, wq):  h = RN(y*w), l = y*w - h (exact, one FMA), c = RN(y*wq) by the
+//   2^52-magic addition (needs |y*wq| <= 2^51, i.e. |y| <= 4q), r = (h - c*q) + l.  h - c*q is an
+//   integer below 2^53 in magnitude, hence exact, and so is the last sum: r = y*w - c*q exactly,
+//   with |c - y*w/q| <= 1/2 + |y| * 2^-55, i.e.  |r| <= q * (1/2 + B/32)  for |y| <= B*q.
+//   fp_reduce(x) is the same with w = 1: |r| <= q * (1/2 + 2^-50).
+// A host-side plan (ntt_kernels.cuh) tracks B through the layers and places the reductions.
+// ---------------------------------------------------------------------------------------
+constexpr double kFpMagic = 6755399441055744.0;  // 1.5 * 2^52
+constexpr double kFpTwo52 = 4503599627370496.0;  // 2^52
+
+__device__ __forceinline__ double fp_mulmod(double y, double w, double wq, double nq) {
+  const double h = __dmul_rn(y, w);
+  const double l = __fma_rn(y, w, -h);
+  const double c = __dadd_rn(__fma_rn(y, wq, kFpMagic), -kFpMagic);
+  return __dadd_rn(__fma_rn(c, nq, h), l);
+}
+__device__ __forceinline__ double fp_reduce(double x, double qinv, double nq) {
+  const double c = __dadd_rn(__fma_rn(x, qinv, kFpMagic), -kFpMagic);
+  return __fma_rn(c, nq, x);
+}
+// integer in [0, 2^52) <-> double, through the mantissa of 2^52 + x
+__device__ __forceinline__ double fp_from_u64(uint64_t x) {
+  return __dadd_rn(__longlong_as_double((long long)(x | 0x4330000000000000ull)), -kFpTwo52);
+}
+__device__ __forceinline__ uint64_t fp_to_u64(double x) {
+  return (uint64_t)__double_as_longlong(__dadd_rn(x, kFpTwo52)) & 0x000fffffffffffffull;
 }
 
 // Harvey forward butterfly: a, b in [0, 4q) -> [0, 4q).

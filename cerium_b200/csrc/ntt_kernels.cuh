@@ -94,10 +94,19 @@ struct PointerBatch {
 // correction per butterfly; they serve 32-bit words and 64-bit primes of 52 bits or more.
 // Lazy butterflies (64-bit words, primes below 2^52) use the headroom above the prime instead
 // of corrections and the 32-bit-piece products of modarith.cuh.
-template <typename W, bool kLazy>
+// Fp butterflies (64-bit words, primes below 2^50) run on the FP64 pipe: the registers hold the
+// bit patterns of doubles, signed residues whose bound a compile-time plan tracks.
+enum : int { kArithStrict = 0, kArithLazy = 1, kArithFp = 2 };
+
+template <typename W, int kMode>
 struct Arith {
+  static constexpr bool kLazy = kMode == kArithLazy;
   W q, q2, q4, nq;
-  __device__ __forceinline__ explicit Arith(W q_) : q(q_), q2(q_ + q_), q4(q_ * 4), nq((W)0 - q_) {}
+  __device__ __forceinline__ explicit Arith(const PrimeConst<W>& pc)
+      : q(pc.q), q2(pc.q + pc.q), q4(pc.q * 4), nq((W)0 - pc.q) {}
+  // canonical residue -> the form the butterflies work on
+  __device__ __forceinline__ W enter(W x) const { return x; }
+  __device__ __forceinline__ W reduce(W x) const { return x; }
   __device__ __forceinline__ void fwd(W& a, W& b, W w, W ws) const {
     if (kLazy) butterfly_fwd_lazy<W>(a, b, w, ws, nq, q4);
     else butterfly_fwd<W>(a, b, w, ws, q, q2);
@@ -115,7 +124,165 @@ struct Arith {
     if (!kCanonical) return x;
     return csub<W>(csub<W>(x, q2), q);
   }
+  // last inverse layer: (a + b) * N^-1 and (a - b) * w1 * N^-1, reduced to [0, q)
+  __device__ __forceinline__ void inv_last(W& a, W& b, const PrimeConst<W>& pc) const {
+    const W s = a + b;
+    const W d = a + (kLazy ? (q4 << 7) : q2) - b;
+    if (kLazy) {
+      a = csub<W>(csub<W>(mul_shoup_approx(s, pc.ninv, pc.ninv_shoup, nq), q2), q);
+      b = csub<W>(csub<W>(mul_shoup_approx(d, pc.w1ninv, pc.w1ninv_shoup, nq), q2), q);
+    } else {
+      a = csub<W>(mul_shoup_lazy<W>(s, pc.ninv, pc.ninv_shoup, q), q);
+      b = csub<W>(mul_shoup_lazy<W>(d, pc.w1ninv, pc.w1ninv_shoup, q), q);
+    }
+  }
 };
+
+template <>
+struct Arith<uint64_t, kArithFp> {
+  using W = uint64_t;
+  double q, nq, qinv;
+  __device__ __forceinline__ explicit Arith(const PrimeConst<W>& pc) {
+    q = fp_from_u64(pc.q);
+    nq = -q;
+    qinv = d(pc.fp_qinv);
+  }
+  static __device__ __forceinline__ double d(W x) { return __longlong_as_double((long long)x); }
+  static __device__ __forceinline__ W u(double x) { return (W)__double_as_longlong(x); }
+  __device__ __forceinline__ W enter(W x) const { return u(fp_from_u64(x)); }
+  __device__ __forceinline__ W reduce(W x) const { return u(fp_reduce(d(x), qinv, nq)); }
+  __device__ __forceinline__ void fwd(W& a, W& b, W w, W wq) const {
+    const double r = fp_mulmod(d(b), d(w), d(wq), nq);
+    const double x = d(a);
+    a = u(__dadd_rn(x, r));
+    b = u(__dadd_rn(x, -r));
+  }
+  __device__ __forceinline__ void inv(W& a, W& b, W w, W wq, int /*k*/) const {
+    const double x = d(a), y = d(b);
+    a = u(__dadd_rn(x, y));
+    b = u(fp_mulmod(__dadd_rn(x, -y), d(w), d(wq), nq));
+  }
+  // |x| <= 0.63 q -> [0, q) as an integer word
+  __device__ __forceinline__ W canonical(double x) const {
+    return fp_to_u64(x < 0.0 ? __dadd_rn(x, q) : x);
+  }
+  template <bool kCanonical>
+  __device__ __forceinline__ W finish_fwd(W x, W /*one_shoup*/) const {
+    const double r = fp_reduce(d(x), qinv, nq);
+    if (kCanonical) return canonical(r);
+    return fp_to_u64(__dadd_rn(r, q));  // (0.49 q, 1.51 q): a lazy residue
+  }
+  __device__ __forceinline__ void inv_last(W& a, W& b, const PrimeConst<W>& pc) const {
+    const double x = d(a), y = d(b);
+    a = canonical(fp_mulmod(__dadd_rn(x, y), d(pc.fp_ninv), d(pc.fp_ninv_q), nq));
+    b = canonical(fp_mulmod(__dadd_rn(x, -y), d(pc.fp_w1ninv), d(pc.fp_w1ninv_q), nq));
+  }
+};
+
+// ---------------------------------------------------------------------------------------
+// Compile-time plan of the Fp butterflies: bounds in units of q / 1024, rounded up.
+// A product's operand may reach 4q and comes back within q * (1/2 + operand / 32q); sums stay
+// below 8q.  The plan walks the layers of a radix-16 group and reduces, just in time, the
+// values whose bound would break the operand limit.
+// ---------------------------------------------------------------------------------------
+constexpr int kFpCanon = 1024;       // canonical input, [0, q)
+constexpr int kFpReduced = 513;      // after fp_reduce
+constexpr int kFpOperandMax = 4096;  // operand of a product
+__host__ __device__ constexpr int fp_product_bound(int operand) { return 512 + (operand + 31) / 32; }
+
+// forward (Cooley-Tukey): a' = a + w*b, b' = a - w*b; all 16 values share one bound
+struct FpFwdPlan {
+  bool before[4];  // reduce every value before layer t
+  int out;
+};
+__host__ __device__ constexpr FpFwdPlan fp_plan_fwd(int bin) {
+  FpFwdPlan p{};
+  int b = bin;
+  for (int t = 0; t < 4; t++) {
+    p.before[t] = b > kFpOperandMax;
+    if (p.before[t]) b = kFpReduced;
+    b += fp_product_bound(b);
+  }
+  p.out = b;
+  return p;
+}
+
+// inverse (Gentleman-Sande): a' = a + b, b' = w * (a - b); the operand a - b needs
+// bound(a) + bound(b) <= 4q.  before[t] is the mask of registers to reduce before layer t.
+struct FpInvPlan {
+  unsigned before[4];
+  int bound[16];
+  int max_out;
+};
+__host__ __device__ constexpr FpInvPlan fp_plan_inv(int bin) {
+  FpInvPlan p{};
+  for (int j = 0; j < 16; j++) p.bound[j] = bin;
+  for (int t = 3; t >= 0; t--) {
+    const int half = 8 >> t;
+    unsigned mask = 0;
+    for (int g = 0; g < (1 << t); g++)
+      for (int k = 0; k < half; k++) {
+        const int j = g * 2 * half + k, i = j + half;
+        if (p.bound[j] + p.bound[i] > kFpOperandMax) {
+          const int big = p.bound[j] >= p.bound[i] ? j : i;
+          p.bound[big] = kFpReduced;
+          mask |= 1u << big;
+          if (p.bound[j] + p.bound[i] > kFpOperandMax) {
+            const int other = big == j ? i : j;
+            p.bound[other] = kFpReduced;
+            mask |= 1u << other;
+          }
+        }
+        const int sum = p.bound[j] + p.bound[i];
+        p.bound[j] = sum;
+        p.bound[i] = fp_product_bound(sum);
+      }
+    p.before[t] = mask;
+  }
+  p.max_out = 0;
+  for (int j = 0; j < 16; j++) p.max_out = p.bound[j] > p.max_out ? p.bound[j] : p.max_out;
+  return p;
+}
+// Registers above `threshold` are reduced before they are exchanged (the next group mixes the
+// registers of 16 threads, so it starts from the largest bound).
+struct FpExchange {
+  unsigned mask;
+  int out;
+};
+__host__ __device__ constexpr FpExchange fp_plan_exchange(const FpInvPlan& p, int threshold) {
+  FpExchange e{};
+  for (int j = 0; j < 16; j++) {
+    int b = p.bound[j];
+    if (b > threshold) {
+      e.mask |= 1u << j;
+      b = kFpReduced;
+    }
+    e.out = b > e.out ? b : e.out;
+  }
+  return e;
+}
+constexpr int kFpInvExchangeMax = 2048;
+
+// bounds along the forward transform: the column pass starts from its loader's bound (canonical
+// words, or lazy ones below 4q) and stores at most kFpFwdMid, from which the row pass starts
+constexpr int kFpLazyIn = 4096;
+constexpr int kFpFwdMid = fp_plan_fwd(fp_plan_fwd(kFpLazyIn).out).out;
+static_assert(fp_plan_fwd(fp_plan_fwd(kFpCanon).out).out <= kFpFwdMid, "the lazy loader is the worst case");
+constexpr int kFpFwdL3 = fp_plan_fwd(kFpFwdMid).out;
+// bounds along the inverse transform: row pass (levels 3, 2) stores kFpInvMid
+constexpr int kFpInvL3 = fp_plan_exchange(fp_plan_inv(kFpCanon), kFpInvExchangeMax).out;
+constexpr int kFpInvMid = fp_plan_inv(kFpInvL3).max_out;
+constexpr int kFpInvL1 = fp_plan_exchange(fp_plan_inv(kFpInvMid), kFpInvExchangeMax).out;
+constexpr unsigned kFpInvRowsExMask = fp_plan_exchange(fp_plan_inv(kFpCanon), kFpInvExchangeMax).mask;
+constexpr unsigned kFpInvColsExMask = fp_plan_exchange(fp_plan_inv(kFpInvMid), kFpInvExchangeMax).mask;
+static_assert(kFpFwdMid < 8192 && kFpInvMid < 8192, "stored intermediates must stay exact integers");
+
+template <typename W, int kMode>
+__device__ __forceinline__ void fp_reduce_masked(W (&x)[16], unsigned mask, const Arith<W, kMode>& ar) {
+#pragma unroll
+  for (int j = 0; j < 16; j++)
+    if (mask >> j & 1u) x[j] = ar.reduce(x[j]);
+}
 
 // ---------------------------------------------------------------------------------------
 // radix-16 register kernels
@@ -136,13 +303,16 @@ __device__ __forceinline__ uint32_t tw_index(uint32_t S, int t, int g) {
   return kLaneTable ? (uint32_t)(((1 << t) - 1 + g) * 16) : (S << t) + (uint32_t)g;
 }
 
-// Four forward layers on x[0..15]; layer t pairs (j, j + (8 >> t)).
-template <typename W, bool kGlobalTw, bool kLazy, bool kLaneTable = false>
+// Four forward layers on x[0..15]; layer t pairs (j, j + (8 >> t)).  kBin: bound of the inputs
+// (Fp arithmetic only).
+template <typename W, bool kGlobalTw, int kMode, bool kLaneTable = false, int kBin = 0>
 __device__ __forceinline__ void radix16_fwd(W (&x)[16], const typename WordTraits<W>::Pair* tw,
-                                            uint32_t S, const Arith<W, kLazy>& ar) {
+                                            uint32_t S, const Arith<W, kMode>& ar) {
+  constexpr FpFwdPlan plan = fp_plan_fwd(kBin);
 #pragma unroll
   for (int t = 0; t < 4; t++) {
     const int half = 8 >> t;
+    if (kMode == kArithFp && plan.before[t]) fp_reduce_masked<W, kMode>(x, 0xffffu, ar);
 #pragma unroll
     for (int g = 0; g < (1 << t); g++) {
       const auto w = load_tw<W, kGlobalTw>(tw, tw_index<kLaneTable>(S, t, g));
@@ -157,12 +327,14 @@ __device__ __forceinline__ void radix16_fwd(W (&x)[16], const typename WordTrait
 
 // The four inverse layers of the same group, in reverse order; kLayer0 is the pass-local
 // number of the first layer executed (0 for the first level of a pass, 4 for the second).
-template <typename W, bool kGlobalTw, bool kLazy, int kLayer0, bool kLaneTable = false>
+template <typename W, bool kGlobalTw, int kMode, int kLayer0, bool kLaneTable = false, int kBin = 0>
 __device__ __forceinline__ void radix16_inv(W (&x)[16], const typename WordTraits<W>::Pair* twi,
-                                            uint32_t S, const Arith<W, kLazy>& ar) {
+                                            uint32_t S, const Arith<W, kMode>& ar) {
+  constexpr FpInvPlan plan = fp_plan_inv(kBin);
 #pragma unroll
   for (int t = 3; t >= 0; t--) {
     const int half = 8 >> t;
+    if (kMode == kArithFp) fp_reduce_masked<W, kMode>(x, plan.before[t], ar);
 #pragma unroll
     for (int g = 0; g < (1 << t); g++) {
       const auto w = load_tw<W, kGlobalTw>(twi, tw_index<kLaneTable>(S, t, g));
@@ -177,12 +349,14 @@ __device__ __forceinline__ void radix16_inv(W (&x)[16], const typename WordTrait
 
 // Level 0 of the inverse transform (S = 1, layers 4..7 of the column pass): the last layer
 // also multiplies by N^-1 and reduces to [0, q).
-template <typename W, bool kLazy>
+template <typename W, int kMode, int kBin = 0>
 __device__ __forceinline__ void radix16_inv_final(W (&x)[16], const typename WordTraits<W>::Pair* twi,
-                                                  const PrimeConst<W>& pc, const Arith<W, kLazy>& ar) {
+                                                  const PrimeConst<W>& pc, const Arith<W, kMode>& ar) {
+  constexpr FpInvPlan plan = fp_plan_inv(kBin);
 #pragma unroll
   for (int t = 3; t >= 1; t--) {
     const int half = 8 >> t;
+    if (kMode == kArithFp) fp_reduce_masked<W, kMode>(x, plan.before[t], ar);
 #pragma unroll
     for (int g = 0; g < (1 << t); g++) {
       const auto w = twi[(1u << t) + g];
@@ -193,18 +367,9 @@ __device__ __forceinline__ void radix16_inv_final(W (&x)[16], const typename Wor
       }
     }
   }
+  if (kMode == kArithFp) fp_reduce_masked<W, kMode>(x, plan.before[0], ar);
 #pragma unroll
-  for (int j = 0; j < 8; j++) {
-    const W s = x[j] + x[j + 8];
-    const W d = x[j] + (kLazy ? (ar.q4 << 7) : ar.q2) - x[j + 8];
-    if (kLazy) {
-      x[j] = csub<W>(csub<W>(mul_shoup_approx(s, pc.ninv, pc.ninv_shoup, ar.nq), ar.q2), ar.q);
-      x[j + 8] = csub<W>(csub<W>(mul_shoup_approx(d, pc.w1ninv, pc.w1ninv_shoup, ar.nq), ar.q2), ar.q);
-    } else {
-      x[j] = csub<W>(mul_shoup_lazy<W>(s, pc.ninv, pc.ninv_shoup, ar.q), ar.q);
-      x[j + 8] = csub<W>(mul_shoup_lazy<W>(d, pc.w1ninv, pc.w1ninv_shoup, ar.q), ar.q);
-    }
-  }
+  for (int j = 0; j < 8; j++) ar.inv_last(x[j], x[j + 8], pc);
 }
 
 // Row-pass exchange buffer: one pad word after every 16 keeps both the strided and the
@@ -239,11 +404,16 @@ __device__ __forceinline__ void vec_unpack(const uint4& v, uint32_t* w) { w[0] =
 __device__ __forceinline__ ulonglong2 vec_pack(const uint64_t* w) { return make_ulonglong2(w[0], w[1]); }
 __device__ __forceinline__ uint4 vec_pack(const uint32_t* w) { return make_uint4(w[0], w[1], w[2], w[3]); }
 
-// Runs body(bool_constant<lazy>) with the arithmetic policy of this CTA's prime.
-#define CERIUM_DISPATCH_LAZY(W, pc, CALL_LAZY, CALL_STRICT) \
-  do {                                                       \
-    if (sizeof(W) == 8 && (pc).lazy_ok != 0) { CALL_LAZY; }  \
-    else { CALL_STRICT; }                                    \
+// Runs one of the instantiations of a kernel body: the arithmetic policy of this CTA's prime
+// (BODY is a template name taking <W, mode, ...>; ARGS its call arguments in parentheses).
+#define CERIUM_TARGS(...) __VA_ARGS__
+#define CERIUM_DISPATCH_ARITH(W, pc, BODY, TARGS, ARGS)                   \
+  do {                                                                   \
+    if constexpr (sizeof(W) == 8) {                                      \
+      if ((pc).fp_ok != 0) { BODY<W, kArithFp, TARGS> ARGS; break; }     \
+      if ((pc).lazy_ok != 0) { BODY<W, kArithLazy, TARGS> ARGS; break; } \
+    }                                                                    \
+    BODY<W, kArithStrict, TARGS> ARGS;                                   \
   } while (0)
 
 // ---------------------------------------------------------------------------------------
@@ -253,6 +423,7 @@ __device__ __forceinline__ uint4 vec_pack(const uint32_t* w) { return make_uint4
 // What the column pass does with a word it has just read.
 template <typename W>
 struct PlainLoader {
+  static constexpr int kFpBound = kFpCanon;
   __device__ __forceinline__ W apply(W x, int /*b*/, const PrimeConst<W>& /*pc*/) const { return x; }
 };
 
@@ -260,9 +431,17 @@ struct PlainLoader {
 // the whole base conversion of a one-limb digit (Qhat = 1), fused into the transform's first read.
 template <typename W>
 struct ModLoader {
+  static constexpr int kFpBound = kFpCanon;
   __device__ __forceinline__ W apply(W x, int /*b*/, const PrimeConst<W>& pc) const {
     return reduce_word<W>(x, pc);
   }
+};
+
+// Words below 4q, as the ModUp base conversion leaves them for the transform.
+template <typename W>
+struct LazyLoader {
+  static constexpr int kFpBound = kFpLazyIn;
+  __device__ __forceinline__ W apply(W x, int /*b*/, const PrimeConst<W>& /*pc*/) const { return x; }
 };
 
 constexpr int kSudMaxBatch = 96;  // limbs per launch when per-limb scalars travel as parameters
@@ -273,6 +452,7 @@ constexpr int kSudMaxBatch = 96;  // limbs per launch when per-limb scalars trav
 // (rescale, cerium/compiler/backend/compiler_rescale.cc:262-284).
 template <typename W>
 struct ReduceLoader {
+  static constexpr int kFpBound = kFpCanon;
   W src_q;
   W pre_add;
   W post_sub[kSudMaxBatch];
@@ -283,12 +463,12 @@ struct ReduceLoader {
   }
 };
 
-template <typename W, bool kLazy, typename Batch, typename Loader>
+template <typename W, int kMode, typename Batch, typename Loader>
 __device__ __forceinline__ void ntt_fwd_cols_body(const Batch& batch, const Loader& loader, int b,
                                                   const PrimeConst<W>& pc, W* tile,
                                                   const typename WordTraits<W>::Pair* stw) {
   constexpr int kCols = NttCfg<W>::kCols;
-  const Arith<W, kLazy> ar(pc.q);
+  const Arith<W, kMode> ar(pc);
   const int tid = threadIdx.x, c = tid % kCols, u = tid / kCols;
   const int col = blockIdx.x * kCols + c;
   // one base pointer per access pattern; the unrolled accesses are then constant offsets from it
@@ -298,15 +478,15 @@ __device__ __forceinline__ void ntt_fwd_cols_body(const Batch& batch, const Load
   W* t_own = tile + (unsigned)(u * 16 * kCols + c);
   W x[16];
 #pragma unroll
-  for (int j = 0; j < 16; j++) x[j] = loader.apply(in[j * 16 * 256], b, pc);
+  for (int j = 0; j < 16; j++) x[j] = ar.enter(loader.apply(in[j * 16 * 256], b, pc));
   __syncthreads();
-  radix16_fwd<W, false, kLazy>(x, stw, 1u, ar);
+  radix16_fwd<W, false, kMode, false, Loader::kFpBound>(x, stw, 1u, ar);
 #pragma unroll
   for (int j = 0; j < 16; j++) t_strided[j * 16 * kCols] = x[j];
   __syncthreads();
 #pragma unroll
   for (int j = 0; j < 16; j++) x[j] = t_own[j * kCols];
-  radix16_fwd<W, false, kLazy>(x, stw, 16u + (uint32_t)u, ar);
+  radix16_fwd<W, false, kMode, false, fp_plan_fwd(Loader::kFpBound).out>(x, stw, 16u + (uint32_t)u, ar);
 #pragma unroll
   for (int j = 0; j < 16; j++) out[j * 256] = x[j];
 }
@@ -326,8 +506,7 @@ __global__ void __launch_bounds__(NttCfg<W>::kCols * 16, sizeof(W) == 8 ? 3 : 2)
   const uint32_t pi = batch.prime_of(b);
   const PrimeConst<W> pc = pcs[pi];
   if (threadIdx.x < 256) stw[threadIdx.x] = __ldg(tw_all + (size_t)pi * kN + threadIdx.x);
-  CERIUM_DISPATCH_LAZY(W, pc, (ntt_fwd_cols_body<W, true>(batch, loader, b, pc, tile, stw)),
-                       (ntt_fwd_cols_body<W, false>(batch, loader, b, pc, tile, stw)));
+  CERIUM_DISPATCH_ARITH(W, pc, ntt_fwd_cols_body, CERIUM_TARGS(Batch, Loader), (batch, loader, b, pc, tile, stw));
 }
 
 // What the row pass does with the finished NTT value.  kCanonicalInput says whether the
@@ -420,14 +599,14 @@ __device__ __forceinline__ void load16<uint32_t>(const uint32_t* src, uint32_t (
   }
 }
 
-template <typename W, bool kLazy, typename Batch, typename Epilogue>
+template <typename W, int kMode, typename Batch, typename Epilogue>
 __device__ __forceinline__ void ntt_fwd_rows_body(const Batch& batch, const Epilogue& epi, int b, uint32_t pi,
                                                   const PrimeConst<W>& pc, W* tile,
                                                   const typename WordTraits<W>::Pair* tw,
                                                   const typename WordTraits<W>::Pair* twr) {
   using RV = RowVec<W>;
   using Vec = typename RV::Vec;
-  const Arith<W, kLazy> ar(pc.q);
+  const Arith<W, kMode> ar(pc);
   const int tid = threadIdx.x, r = tid >> 4, u = tid & 15;
   const int h = blockIdx.x * kRowsPerCta + r;
   const W* row = batch.in_limb(b) + (unsigned)(h * 256 + u);
@@ -438,14 +617,14 @@ __device__ __forceinline__ void ntt_fwd_rows_body(const Batch& batch, const Epil
   W x[16];
 #pragma unroll
   for (int j = 0; j < 16; j++) x[j] = row[j * 16];
-  radix16_fwd<W, true, kLazy>(x, tw, 256u + (uint32_t)h, ar);
+  radix16_fwd<W, true, kMode, false, kFpFwdMid>(x, tw, 256u + (uint32_t)h, ar);
 #pragma unroll
   for (int j = 0; j < 16; j++) t_strided[j * 17] = x[j];
   __syncwarp();  // a row's 16 threads share a warp; no other warp touches its staging rows
 #pragma unroll
   for (int j = 0; j < 16; j++) x[j] = t_own[j];
   // level 3: this thread's 15 twiddles from the lane-interleaved table of row h
-  radix16_fwd<W, true, kLazy, true>(x, twr + ((size_t)h * 15 * 16 + u), 0u, ar);
+  radix16_fwd<W, true, kMode, true, kFpFwdL3>(x, twr + ((size_t)h * 15 * 16 + u), 0u, ar);
 #pragma unroll
   for (int j = 0; j < 16; j++) x[j] = ar.template finish_fwd<Epilogue::kCanonicalInput>(x[j], pc.one_shoup);
   // own 16 words -> swizzled vectors -> coalesced vectors, then epilogue and store
@@ -482,21 +661,20 @@ __global__ void __launch_bounds__(kRowsPerCta * 16, 3)
   const PrimeConst<W> pc = pcs[pi];
   const Pair* tw = tw_all + (size_t)pi * kN;
   const Pair* twr = twr_all + (size_t)pi * kRowTwPerPrime;
-  CERIUM_DISPATCH_LAZY(W, pc, (ntt_fwd_rows_body<W, true>(batch, epi, b, pi, pc, tile, tw, twr)),
-                       (ntt_fwd_rows_body<W, false>(batch, epi, b, pi, pc, tile, tw, twr)));
+  CERIUM_DISPATCH_ARITH(W, pc, ntt_fwd_rows_body, CERIUM_TARGS(Batch, Epilogue), (batch, epi, b, pi, pc, tile, tw, twr));
 }
 
 // ---------------------------------------------------------------------------------------
 // inverse transform
 // ---------------------------------------------------------------------------------------
 
-template <typename W, bool kLazy, typename Batch>
+template <typename W, int kMode, typename Batch>
 __device__ __forceinline__ void ntt_inv_rows_body(const Batch& batch, int b, const PrimeConst<W>& pc, W* tile,
                                                   const typename WordTraits<W>::Pair* twi,
                                                   const typename WordTraits<W>::Pair* twri) {
   using RV = RowVec<W>;
   using Vec = typename RV::Vec;
-  const Arith<W, kLazy> ar(pc.q);
+  const Arith<W, kMode> ar(pc);
   const int tid = threadIdx.x, r = tid >> 4, u = tid & 15;
   const int h = blockIdx.x * kRowsPerCta + r;
   const W* src = batch.in_limb(b) + h * 256;
@@ -514,7 +692,10 @@ __device__ __forceinline__ void ntt_inv_rows_body(const Batch& batch, int b, con
 #pragma unroll
   for (int jj = 0; jj < RV::kPerThread; jj++)
     vec_unpack(vrow[row_vec_slot<W>(u * RV::kPerThread + jj)], &x[jj * RV::kWords]);
-  radix16_inv<W, true, kLazy, 0, true>(x, twri + ((size_t)h * 15 * 16 + u), 0u, ar);
+#pragma unroll
+  for (int j = 0; j < 16; j++) x[j] = ar.enter(x[j]);
+  radix16_inv<W, true, kMode, 0, true, kFpCanon>(x, twri + ((size_t)h * 15 * 16 + u), 0u, ar);
+  if (kMode == kArithFp) fp_reduce_masked<W, kMode>(x, kFpInvRowsExMask, ar);
   __syncwarp();
   W* t_own = trow + (unsigned)(u * 17);  // row_pos(u * 16 + j) = u * 17 + j
   W* t_strided = trow + u;             // row_pos(j * 16 + u) = j * 17 + u
@@ -523,7 +704,7 @@ __device__ __forceinline__ void ntt_inv_rows_body(const Batch& batch, int b, con
   __syncwarp();
 #pragma unroll
   for (int j = 0; j < 16; j++) x[j] = t_strided[j * 17];
-  radix16_inv<W, true, kLazy, 4>(x, twi, 256u + (uint32_t)h, ar);
+  radix16_inv<W, true, kMode, 4, false, kFpInvL3>(x, twi, 256u + (uint32_t)h, ar);
   W* dcol = dst + u;
 #pragma unroll
   for (int j = 0; j < 16; j++) dcol[j * 16] = x[j];
@@ -542,8 +723,7 @@ __global__ void __launch_bounds__(kRowsPerCta * 16, 3)
   const PrimeConst<W> pc = pcs[pi];
   const Pair* twi = twi_all + (size_t)pi * kN;
   const Pair* twri = twri_all + (size_t)pi * kRowTwPerPrime;
-  CERIUM_DISPATCH_LAZY(W, pc, (ntt_inv_rows_body<W, true>(batch, b, pc, tile, twi, twri)),
-                       (ntt_inv_rows_body<W, false>(batch, b, pc, tile, twi, twri)));
+  CERIUM_DISPATCH_ARITH(W, pc, ntt_inv_rows_body, Batch, (batch, b, pc, tile, twi, twri));
 }
 
 // Optional per-limb scalar applied to the finished inverse transform (exact base
@@ -554,12 +734,12 @@ struct InvScale {
   const W* scale_shoup;  // per batch entry
 };
 
-template <typename W, bool kLazy, typename Batch>
+template <typename W, int kMode, typename Batch>
 __device__ __forceinline__ void ntt_inv_cols_body(const Batch& batch, const InvScale<W>& sc, int b,
                                                   const PrimeConst<W>& pc, W* tile,
                                                   const typename WordTraits<W>::Pair* stw) {
   constexpr int kCols = NttCfg<W>::kCols;
-  const Arith<W, kLazy> ar(pc.q);
+  const Arith<W, kMode> ar(pc);
   const W q = pc.q;
   const int tid = threadIdx.x, c = tid % kCols, u = tid / kCols;
   const int col = blockIdx.x * kCols + c;
@@ -571,16 +751,17 @@ __device__ __forceinline__ void ntt_inv_cols_body(const Batch& batch, const InvS
 #pragma unroll
   for (int j = 0; j < 16; j++) {
     x[j] = buf_own[j * 256];
-    if (kLazy) x[j] = reduce_lazy(x[j], pc.one_shoup, ar.nq);  // back below 4q for the second pass
+    if (kMode == kArithLazy) x[j] = reduce_lazy(x[j], pc.one_shoup, (W)0 - pc.q);  // back below 4q for the second pass
   }
   __syncthreads();
-  radix16_inv<W, false, kLazy, 0>(x, stw, 16u + (uint32_t)u, ar);
+  radix16_inv<W, false, kMode, 0, false, kFpInvMid>(x, stw, 16u + (uint32_t)u, ar);
+  if (kMode == kArithFp) fp_reduce_masked<W, kMode>(x, kFpInvColsExMask, ar);
 #pragma unroll
   for (int j = 0; j < 16; j++) t_own[j * kCols] = x[j];
   __syncthreads();
 #pragma unroll
   for (int j = 0; j < 16; j++) x[j] = t_strided[j * 16 * kCols];
-  radix16_inv_final<W, kLazy>(x, stw, pc, ar);
+  radix16_inv_final<W, kMode, kFpInvL1>(x, stw, pc, ar);
   if (sc.scale != nullptr) {
     const W s = __ldg(sc.scale + b), ss = __ldg(sc.scale_shoup + b);
 #pragma unroll
@@ -605,8 +786,7 @@ __global__ void __launch_bounds__(NttCfg<W>::kCols * 16, sizeof(W) == 8 ? 3 : 2)
   const uint32_t pi = batch.prime_of(b);
   const PrimeConst<W> pc = pcs[pi];
   if (threadIdx.x < 256) stw[threadIdx.x] = __ldg(twi_all + (size_t)pi * kN + threadIdx.x);
-  CERIUM_DISPATCH_LAZY(W, pc, (ntt_inv_cols_body<W, true>(batch, sc, b, pc, tile, stw)),
-                       (ntt_inv_cols_body<W, false>(batch, sc, b, pc, tile, stw)));
+  CERIUM_DISPATCH_ARITH(W, pc, ntt_inv_cols_body, Batch, (batch, sc, b, pc, tile, stw));
 }
 
 }  // namespace cerium

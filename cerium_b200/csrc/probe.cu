@@ -3,6 +3,8 @@
 // roofline" the 64-bit kernels are judged against (their HBM roofline is not the binding one):
 // a transform cannot run its butterflies faster than these loops, which touch no memory.
 // Diagnostic entry point; not on any evaluation path.
+#include <cstring>
+
 #include "internal.h"
 
 using namespace cerium;
@@ -11,14 +13,16 @@ namespace {
 
 constexpr int kProbeThreads = 256;
 
-// OP: 0 mad.lo.u32, 1 mad.wide.u32, 2 mul.hi.u64, 3 mul.lo.u64, 4 add.u64 -- 8 chains per thread
+// OP: 0 mad.lo.u32, 1 mad.wide.u32, 2 mul.hi.u64, 3 mul.lo.u64, 4 add.u64, 5 fma.rn.f64 -- 8 chains per thread
 template <int OP>
 __global__ void __launch_bounds__(kProbeThreads) probe_raw_kernel(uint64_t* out, uint32_t a, uint32_t b, int iters) {
   uint32_t r[8];
   uint64_t R[8];
+  double D[8];
   for (int j = 0; j < 8; j++) {
     r[j] = threadIdx.x + j;
     R[j] = threadIdx.x * 3 + j;
+    D[j] = (double)(threadIdx.x + j);
   }
 #if !defined(CERIUM_EMU)
   const uint64_t ab = (uint64_t)a << 32 | b;
@@ -32,24 +36,33 @@ __global__ void __launch_bounds__(kProbeThreads) probe_raw_kernel(uint64_t* out,
         if (OP == 2) asm volatile("mul.hi.u64 %0, %0, %1;" : "+l"(R[j]) : "l"(ab));
         if (OP == 3) asm volatile("mul.lo.u64 %0, %0, %1;" : "+l"(R[j]) : "l"(ab));
         if (OP == 4) asm volatile("add.u64 %0, %0, %1;" : "+l"(R[j]) : "l"(ab));
+        if (OP == 5) asm volatile("fma.rn.f64 %0, %0, %1, %2;" : "+d"(D[j]) : "d"(0.999999 + a * 1e-9), "d"(0.5 + b));
       }
   }
 #endif
   uint64_t s = 0;
-  for (int j = 0; j < 8; j++) s ^= R[j] ^ r[j];
+  for (int j = 0; j < 8; j++) s ^= R[j] ^ r[j] ^ (uint64_t)__double_as_longlong(D[j]);
   out[blockIdx.x * blockDim.x + threadIdx.x] = s + iters;
 }
 
 // `iters` radix-16 groups (32 butterflies each) on 16 register-resident words per thread, with the
 // library's own butterfly code; twiddles are loop-invariant registers.
-template <typename W, bool kLazy>
-__global__ void __launch_bounds__(kProbeThreads) probe_butterfly_kernel(W* out, W q, W w0, W ws0, int iters) {
-  const Arith<W, kLazy> ar(q);
+template <typename W, int kMode>
+__global__ void __launch_bounds__(kProbeThreads) probe_butterfly_kernel(W* out, PrimeConst<W> pc, W w0, W ws0, int iters) {
+  constexpr bool kLazy = kMode == kArithLazy;
+  const Arith<W, kMode> ar(pc);
+  const W q = pc.q;
   W x[16], w[4], ws[4];
-  for (int j = 0; j < 16; j++) x[j] = (W)(threadIdx.x * 977u + j * 131u + blockIdx.x) % q;
+  for (int j = 0; j < 16; j++) x[j] = ar.enter((W)(threadIdx.x * 977u + j * 131u + blockIdx.x) % q);
   for (int t = 0; t < 4; t++) {
     w[t] = (w0 + (W)(t * 12345u + threadIdx.x)) % q;
     ws[t] = ws0 + (W)(t * 777u + threadIdx.x);
+    if (kMode == kArithFp) {
+      // centred twiddle and its quotient by q, as the bit patterns of doubles
+      const double wd = (double)(long long)w[t] - (w[t] > q / 2 ? (double)(long long)q : 0.0);
+      w[t] = (W)__double_as_longlong(wd);
+      ws[t] = (W)__double_as_longlong(wd / (double)(long long)q);
+    }
   }
   for (int it = 0; it < iters; it++) {
 #pragma unroll
@@ -67,6 +80,11 @@ __global__ void __launch_bounds__(kProbeThreads) probe_butterfly_kernel(W* out, 
       // a transform reduces once per 16 layers; here a mask keeps the lazy values in range
 #pragma unroll
       for (int j = 0; j < 16; j++) x[j] &= (W)(~(W)0 >> 8);
+    }
+    if (kMode == kArithFp) {
+      // the transforms reduce once per six layers at most; once per four here
+#pragma unroll
+      for (int j = 0; j < 16; j++) x[j] = ar.reduce(x[j]);
     }
   }
   W s = 0;
@@ -103,6 +121,7 @@ float time_ms(F launch) {
 // results (giga-operations per second, whole GPU):
 //  [0] mad.lo.u32   [1] mad.wide.u32   [2] mul.hi.u64   [3] mul.lo.u64   [4] add.u64
 //  [5] 64-bit strict (Harvey) butterfly   [6] 64-bit lazy butterfly   [7] 32-bit strict butterfly
+//  and, when n_results >= 10:   [8] fma.rn.f64   [9] 64-bit double-precision butterfly
 extern "C" int cerium_probe_int_pipe(int device, double* gops, int n_results) {
   if (!gops || n_results < 8) return fail(CERIUM_ERR_INVALID, "probe_int_pipe: need room for 8 results");
   int ndev = 0;
@@ -129,9 +148,21 @@ extern "C" int cerium_probe_int_pipe(int device, double* gops, int n_results) {
   gops[2] = rate(time_ms([&] { auto k = probe_raw_kernel<2>; CERIUM_LAUNCH(k, g, b, 0, 0, out, 3u, 5u, iters); }), 32);
   gops[3] = rate(time_ms([&] { auto k = probe_raw_kernel<3>; CERIUM_LAUNCH(k, g, b, 0, 0, out, 3u, 5u, iters); }), 32);
   gops[4] = rate(time_ms([&] { auto k = probe_raw_kernel<4>; CERIUM_LAUNCH(k, g, b, 0, 0, out, 3u, 5u, iters); }), 32);
-  gops[5] = rate(time_ms([&] { auto k = probe_butterfly_kernel<uint64_t, false>; CERIUM_LAUNCH(k, g, b, 0, 0, out, q64, (uint64_t)12345, (uint64_t)67890, iters); }), 32);
-  gops[6] = rate(time_ms([&] { auto k = probe_butterfly_kernel<uint64_t, true>; CERIUM_LAUNCH(k, g, b, 0, 0, out, q64, (uint64_t)12345, (uint64_t)67890, iters); }), 32);
-  gops[7] = rate(time_ms([&] { auto k = probe_butterfly_kernel<uint32_t, false>; CERIUM_LAUNCH(k, g, b, 0, 0, reinterpret_cast<uint32_t*>(out), q32, 12345u, 67890u, iters); }), 32);
+  PrimeConst<uint64_t> pc64{};
+  pc64.q = q64;
+  {
+    const double qinv = 1.0 / (double)q64;
+    std::memcpy(&pc64.fp_qinv, &qinv, sizeof(double));
+  }
+  PrimeConst<uint32_t> pc32{};
+  pc32.q = q32;
+  gops[5] = rate(time_ms([&] { auto k = probe_butterfly_kernel<uint64_t, kArithStrict>; CERIUM_LAUNCH(k, g, b, 0, 0, out, pc64, (uint64_t)12345, (uint64_t)67890, iters); }), 32);
+  gops[6] = rate(time_ms([&] { auto k = probe_butterfly_kernel<uint64_t, kArithLazy>; CERIUM_LAUNCH(k, g, b, 0, 0, out, pc64, (uint64_t)12345, (uint64_t)67890, iters); }), 32);
+  gops[7] = rate(time_ms([&] { auto k = probe_butterfly_kernel<uint32_t, kArithStrict>; CERIUM_LAUNCH(k, g, b, 0, 0, reinterpret_cast<uint32_t*>(out), pc32, 12345u, 67890u, iters); }), 32);
+  if (n_results >= 10) {
+    gops[8] = rate(time_ms([&] { auto k = probe_raw_kernel<5>; CERIUM_LAUNCH(k, g, b, 0, 0, out, 3u, 5u, iters); }), 32);
+    gops[9] = rate(time_ms([&] { auto k = probe_butterfly_kernel<uint64_t, kArithFp>; CERIUM_LAUNCH(k, g, b, 0, 0, out, pc64, (uint64_t)12345, (uint64_t)67890, iters); }), 32);
+  }
   cudaFree(out);
   CERIUM_LAUNCH_CHECK("probe_int_pipe");
   return CERIUM_OK;

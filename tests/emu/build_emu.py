@@ -16,7 +16,7 @@ def build(force: bool = False) -> str:
              os.path.join(ROOT, "include", "cerium_b200.h")]
     if not force and os.path.exists(LIB) and all(os.path.getmtime(d) <= os.path.getmtime(LIB) for d in deps):
         return LIB
-    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-fopenmp", "-DCERIUM_EMU", "-I" + HERE,
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-fopenmp", "-ffp-contract=off", "-DCERIUM_EMU", "-I" + HERE,
            "-Wno-unused-variable", "-o", LIB, os.path.join(HERE, "emu_runtime.cpp")]
     for s in srcs:
         cmd += ["-x", "c++", s]

@@ -13,6 +13,7 @@
 // block barrier where it only has a warp barrier computes wrong results here too.  __shared__ variables become
 // static thread_local, i.e. one copy per OS thread = per running block.
 #pragma once
+#include <cmath>
 #include <cstddef>
 #include <cstdint>
 #include <cstdlib>
@@ -61,6 +62,11 @@ static inline unsigned __umulhi(unsigned a, unsigned b) { return (unsigned)(((ui
 static inline unsigned long long __umul64hi(unsigned long long a, unsigned long long b) {
   return (unsigned long long)(((unsigned __int128)a * b) >> 64);
 }
+static inline double __dmul_rn(double a, double b) { return a * b; }
+static inline double __dadd_rn(double a, double b) { return a + b; }
+static inline double __fma_rn(double a, double b, double c) { return std::fma(a, b, c); }
+static inline double __longlong_as_double(long long x) { double d; std::memcpy(&d, &x, 8); return d; }
+static inline long long __double_as_longlong(double d) { long long x; std::memcpy(&x, &d, 8); return x; }
 static inline unsigned __brev(unsigned x) {
   unsigned r = 0;
   for (int i = 0; i < 32; i++) { r = (r << 1) | (x & 1); x >>= 1; }
