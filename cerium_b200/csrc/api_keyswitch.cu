@@ -214,15 +214,16 @@ int keyswitch_inner_moddown(cerium_keyswitch* ks, void* out0, void* out1, const 
       }
       const PrimeConst<W>* pcs = static_cast<const PrimeConst<W>*>(ctx->d_pcs);
       const dim3 block(kEwThreads);
-      // extension limbs first: their ModDown preparation then overlaps the Q-limb pass below
-      g.first_limb = L;
-      { auto kfn = inner_product_kernel<W>; CERIUM_LAUNCH(kfn, dim3(kN / (kEwThreads * V::kLanes), K), block, 0, stream, g, pcs); }
+      // The extension limbs and their ModDown preparation (inverse transform, conversion to the Q
+      // limbs) run on the side stream next to the Q-limb pass of the main stream.
       const bool fork = ks->side != nullptr && L > 0;
       cudaStream_t prep = fork ? ks->side : stream;
       if (fork) {
         CERIUM_CUDA(cudaEventRecord(ks->ev_fork, stream));
         CERIUM_CUDA(cudaStreamWaitEvent(ks->side, ks->ev_fork, 0));
       }
+      g.first_limb = L;
+      { auto kfn = inner_product_kernel<W>; CERIUM_LAUNCH(kfn, dim3(kN / (kEwThreads * V::kLanes), K), block, 0, prep, g, pcs); }
       if (L > 0) {
         g.first_limb = 0;
         auto kfn = inner_product_kernel<W>;

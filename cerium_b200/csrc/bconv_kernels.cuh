@@ -193,6 +193,7 @@ template <typename W>
 __global__ void __launch_bounds__(kBconvThreads)
     bconv_kernel(const BconvBatch<W> batch, const int out_chunk, const PrimeConst<W>* __restrict__ pcs) {
   CERIUM_DYN_SMEM(smem_raw);
+  grid_dependency_launch();
   BconvDesc<W> d = batch.d[blockIdx.y];
   const int j_first = blockIdx.z * out_chunk;
   if (j_first >= d.O) return;
@@ -232,6 +233,7 @@ __global__ void __launch_bounds__(kBconvThreads)
     o.strict = (pc.lazy_ok != 0 && pc.fp_ok == 0) ? 0 : 1;
     sout[j] = o;
   }
+  grid_dependency_wait();  // the tables above never change; the input limbs below come from the previous kernel
   __syncthreads();
   const int coeff = blockIdx.x * kBconvThreads + threadIdx.x;
   if (sizeof(W) == 8 && I <= kBconvRegInputs) {

@@ -82,6 +82,8 @@ struct EwArgs {
 template <typename W, int kOp>
 __global__ void __launch_bounds__(kEwThreads)
     ewise_kernel(const EwArgs<W> g, const PrimeConst<W>* __restrict__ pcs) {
+  grid_dependency_launch();
+  grid_dependency_wait();
   using V = Vec16<W>;
   const int b = blockIdx.y;
   const uint32_t pi = g.prime[b];
@@ -122,6 +124,8 @@ struct TensorArgs {
 template <typename W>
 __global__ void __launch_bounds__(kEwThreads)
     tensor_kernel(const TensorArgs<W> g, const PrimeConst<W>* __restrict__ pcs) {
+  grid_dependency_launch();
+  grid_dependency_wait();
   using V = Vec16<W>;
   const int b = blockIdx.y;
   const PrimeConst<W> pc = pcs[g.prime[b]];
@@ -166,6 +170,8 @@ struct AutomorphArgs {
 // grid = (N / 256, limbs), block = 256; in and out must not overlap.
 template <typename W>
 __global__ void __launch_bounds__(kEwThreads) automorph_kernel(const AutomorphArgs<W> g) {
+  grid_dependency_launch();
+  grid_dependency_wait();
   const int b = blockIdx.y;
   const uint32_t i = blockIdx.x * kEwThreads + threadIdx.x;
   *g.out.at(b, (int)i) = *g.in.at(b, (int)galois_source_index(i, g.elt));
@@ -192,6 +198,8 @@ struct Rsv2Args {
 // grid = (N / (256 * lanes), count), block = 256
 template <typename W>
 __global__ void __launch_bounds__(kEwThreads) rsv2_kernel(const Rsv2Args<W> g, const PrimeConst<W>* __restrict__ pcs) {
+  grid_dependency_launch();
+  grid_dependency_wait();
   using V = Vec16<W>;
   const int b = blockIdx.y;
   const PrimeConst<W> pc1 = pcs[g.prime1];
@@ -226,6 +234,8 @@ struct Mod2Args {
 // grid = (N / (256 * lanes), count), block = 256: out[b] = (hi:lo) mod q_{prime[b]}
 template <typename W>
 __global__ void __launch_bounds__(kEwThreads) mod2_kernel(const Mod2Args<W> g, const PrimeConst<W>* __restrict__ pcs) {
+  grid_dependency_launch();
+  grid_dependency_wait();
   using V = Vec16<W>;
   const int b = blockIdx.y;
   const PrimeConst<W> pc = pcs[g.prime[b]];
@@ -266,6 +276,8 @@ struct InnerProductArgs {
 template <typename W>
 __global__ void __launch_bounds__(kEwThreads)
     inner_product_kernel(const InnerProductArgs<W> g, const PrimeConst<W>* __restrict__ pcs) {
+  grid_dependency_launch();
+  grid_dependency_wait();
   using V = Vec16<W>;
   const int b = g.first_limb + blockIdx.y;
   const PrimeConst<W> pc = pcs[g.prime[b]];

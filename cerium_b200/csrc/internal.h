@@ -9,6 +9,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "../../include/cerium_b200.h"
@@ -41,7 +42,25 @@ int fail(int code, const std::string& msg);
 #define CERIUM_LAUNCH(kfn, grid, block, smem, stream, ...) \
   ::cerium_emu::launch((grid), (block), (smem), [=]() { kfn(__VA_ARGS__); })
 #else
-#define CERIUM_LAUNCH(kfn, grid, block, smem, stream, ...) kfn<<<(grid), (block), (smem), (stream)>>>(__VA_ARGS__)
+// Every kernel is launched with programmatic stream serialisation (see grid_dependency_wait in
+// modarith.cuh): its CTAs may be placed while the previous kernel of the stream drains.
+template <typename... KArgs, typename... Args>
+inline void launch_dependent(void (*kfn)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kfn, std::forward<Args>(args)...);  // errors surface in CERIUM_LAUNCH_CHECK
+}
+#define CERIUM_LAUNCH(kfn, grid, block, smem, stream, ...) \
+  ::cerium::launch_dependent(kfn, dim3(grid), dim3(block), (size_t)(smem), (stream), __VA_ARGS__)
 #endif
 
 // Runs fn(W{}) with W = uint32_t or uint64_t according to the context's word size.

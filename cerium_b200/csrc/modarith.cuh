@@ -25,6 +25,23 @@
 
 namespace cerium {
 
+// Programmatic dependent launch: every kernel of this library is launched with stream
+// serialisation relaxed, so the next kernel's CTAs are placed (and read their constant tables)
+// while the last CTAs of this one drain.  grid_dependency_launch() lets the next kernel start
+// being placed; grid_dependency_wait() returns once every earlier kernel of the stream has
+// completed and its writes are visible.  EVERY kernel must call the wait before it touches a
+// buffer another kernel may have written or may still read.
+__device__ __forceinline__ void grid_dependency_launch() {
+#if !defined(CERIUM_EMU)
+  asm volatile("griddepcontrol.launch_dependents;");
+#endif
+}
+__device__ __forceinline__ void grid_dependency_wait() {
+#if !defined(CERIUM_EMU)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+#endif
+}
+
 constexpr int kLogN = 16;
 constexpr int kN = 1 << kLogN;
 

@@ -502,10 +502,12 @@ __global__ void __launch_bounds__(NttCfg<W>::kCols * 16, sizeof(W) == 8 ? 3 : 2)
   constexpr int kCols = NttCfg<W>::kCols;
   __shared__ W tile[256 * kCols];
   __shared__ Pair stw[256];
+  grid_dependency_launch();
   const int b = blockIdx.y;
   const uint32_t pi = batch.prime_of(b);
   const PrimeConst<W> pc = pcs[pi];
   if (threadIdx.x < 256) stw[threadIdx.x] = __ldg(tw_all + (size_t)pi * kN + threadIdx.x);
+  grid_dependency_wait();
   CERIUM_DISPATCH_ARITH(W, pc, ntt_fwd_cols_body, CERIUM_TARGS(Batch, Loader), (batch, loader, b, pc, tile, stw));
 }
 
@@ -656,11 +658,13 @@ __global__ void __launch_bounds__(kRowsPerCta * 16, 3)
                         const PrimeConst<W>* __restrict__ pcs) {
   using Pair = typename WordTraits<W>::Pair;
   __shared__ __align__(16) W tile[kRowsPerCta * kRowPitch];
+  grid_dependency_launch();
   const int b = blockIdx.y;
   const uint32_t pi = batch.prime_of(b);
   const PrimeConst<W> pc = pcs[pi];
   const Pair* tw = tw_all + (size_t)pi * kN;
   const Pair* twr = twr_all + (size_t)pi * kRowTwPerPrime;
+  grid_dependency_wait();
   CERIUM_DISPATCH_ARITH(W, pc, ntt_fwd_rows_body, CERIUM_TARGS(Batch, Epilogue), (batch, epi, b, pi, pc, tile, tw, twr));
 }
 
@@ -718,11 +722,13 @@ __global__ void __launch_bounds__(kRowsPerCta * 16, 3)
                         const PrimeConst<W>* __restrict__ pcs) {
   using Pair = typename WordTraits<W>::Pair;
   __shared__ __align__(16) W tile[kRowsPerCta * kRowPitch];
+  grid_dependency_launch();
   const int b = blockIdx.y;
   const uint32_t pi = batch.prime_of(b);
   const PrimeConst<W> pc = pcs[pi];
   const Pair* twi = twi_all + (size_t)pi * kN;
   const Pair* twri = twri_all + (size_t)pi * kRowTwPerPrime;
+  grid_dependency_wait();
   CERIUM_DISPATCH_ARITH(W, pc, ntt_inv_rows_body, Batch, (batch, b, pc, tile, twi, twri));
 }
 
@@ -782,10 +788,12 @@ __global__ void __launch_bounds__(NttCfg<W>::kCols * 16, sizeof(W) == 8 ? 3 : 2)
   constexpr int kCols = NttCfg<W>::kCols;
   __shared__ W tile[256 * kCols];
   __shared__ Pair stw[256];
+  grid_dependency_launch();
   const int b = blockIdx.y;
   const uint32_t pi = batch.prime_of(b);
   const PrimeConst<W> pc = pcs[pi];
   if (threadIdx.x < 256) stw[threadIdx.x] = __ldg(twi_all + (size_t)pi * kN + threadIdx.x);
+  grid_dependency_wait();
   CERIUM_DISPATCH_ARITH(W, pc, ntt_inv_cols_body, Batch, (batch, sc, b, pc, tile, stw));
 }
 

@@ -16,6 +16,8 @@ constexpr int kProbeThreads = 256;
 // OP: 0 mad.lo.u32, 1 mad.wide.u32, 2 mul.hi.u64, 3 mul.lo.u64, 4 add.u64, 5 fma.rn.f64 -- 8 chains per thread
 template <int OP>
 __global__ void __launch_bounds__(kProbeThreads) probe_raw_kernel(uint64_t* out, uint32_t a, uint32_t b, int iters) {
+  grid_dependency_launch();
+  grid_dependency_wait();
   uint32_t r[8];
   uint64_t R[8];
   double D[8];
@@ -49,6 +51,8 @@ __global__ void __launch_bounds__(kProbeThreads) probe_raw_kernel(uint64_t* out,
 // library's own butterfly code; twiddles are loop-invariant registers.
 template <typename W, int kMode>
 __global__ void __launch_bounds__(kProbeThreads) probe_butterfly_kernel(W* out, PrimeConst<W> pc, W w0, W ws0, int iters) {
+  grid_dependency_launch();
+  grid_dependency_wait();
   constexpr bool kLazy = kMode == kArithLazy;
   const Arith<W, kMode> ar(pc);
   const W q = pc.q;
