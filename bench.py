@@ -12,7 +12,10 @@ already resident in HBM:
   ntt    forward + inverse NTT of 48 limbs x 8 polynomials of 50-bit primes
 With N > 1 ranks (torchrun) every rank runs the same workload on its own ciphertexts
 (independent ciphertexts, no data-path collective): weak scaling, value = all ranks' ops / max
-time over ranks.
+time over ranks.  For hrot the same operation is also timed limb-sharded over all ranks
+(ciphertext and key split by RNS limb, one NCCL all-gather per key switch: the latency of one
+operation, strong scaling) and reported under `limb_sharded`; `--parallelism limb` makes that
+the headline instead.
 
 Prints one JSON line.  `value` is device-resident throughput timed with CUDA events; `e2e` is the
 same metric through the C ABI with host buffers (pinned), host->device and device->host copies
@@ -41,9 +44,9 @@ from cerium_b200 import params  # noqa: E402
 LOGN = 16
 N = 1 << LOGN
 # dram__bytes_read.sum + dram__bytes_write.sum of the forward-NTT launch pair from the ncu capture
-# summarised in profiles/hrot_u64_top_kernels_ncu_full.md: 498.7 MB for 245 u64 limbs (traffic grows
+# summarised in profiles/hrot_u64_top_kernels_ncu_full.md: 496.5 MB for 245 u64 limbs (traffic grows
 # in proportion to the limbs transformed)
-NTT_PAIR_DRAM_BYTES_PER_LIMB = 498.7e6 / 245
+NTT_PAIR_DRAM_BYTES_PER_LIMB = 496.5e6 / 245
 
 
 def env_int(name, default):
@@ -423,9 +426,11 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="hrot")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--parallelism", choices=["limb", "replica"], default="limb",
-                    help="N > 1: 'limb' shards every ciphertext and key by RNS limb over the ranks (one all-gather "
-                         "per key switch, strong scaling); 'replica' runs independent ciphertexts per rank")
+    ap.add_argument("--parallelism", choices=["auto", "limb", "replica"], default="auto",
+                    help="N > 1: 'replica' runs independent ciphertexts per rank (throughput, weak scaling); 'limb' "
+                         "shards every ciphertext and key by RNS limb over the ranks (one all-gather per key switch, "
+                         "latency of one operation, strong scaling); 'auto' reports the replica throughput as the "
+                         "headline and times the limb-sharded operation beside it (key 'limb_sharded')")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]()
     if args.impl == "reference":
@@ -496,6 +501,30 @@ def main():
     probe = lib.probe_int_pipe(local_rank) if rank == 0 else None
 
     # end to end: host buffers in, host buffers out, through the same C ABI calls
+    # N > 1, auto: the same operation limb-sharded over all ranks (its latency, not its throughput)
+    limb_line = None
+    if world > 1 and args.parallelism == "auto" and args.workload == "hrot":
+        wl2 = WORKLOADS["hrot"]()
+        wl2.setup(lib, torch, rank, world, True)
+        steps2 = max(5, min(args.steps, 200))
+        for _ in range(5):
+            wl2.step()
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(steps2):
+            wl2.step()
+        s1.record()
+        barrier()
+        t = torch.tensor([s0.elapsed_time(s1)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms2 = float(t.item()) / steps2
+        limb_line = {"ms_per_op": ms2, "value": wl2.ops_per_step / (ms2 / 1e3), "unit": wl2.unit, "steps": steps2,
+                     "scaling": "strong",
+                     "parallelism": "one operation, ciphertext and key limb-sharded over %d ranks, one NCCL "
+                                    "all-gather per key switch" % world}
+        del wl2
+
     e2e_steps = max(5, min(args.steps, 50))
     for _ in range(3):
         wl.e2e_step()
@@ -532,16 +561,20 @@ def main():
                          "traffic_source": "profiles/hrot_u64_top_kernels_ncu_full.md (ncu, 245 limbs, scaled by limbs)",
                          "peak_kind": peak_kind,
                          "ms_per_launch_pair": rl_ms, "algorithmic_bytes": wl.rl_bytes},
-            # the 64-bit transforms are bound by the integer pipe, not by HBM: butterflies per second of the
-            # same launch pair against the register-only butterfly rate measured on this GPU just now
-            "int_roofline": {"achieved_gbutterfly_s": len(wl.rl_idx if hasattr(wl, "rl_idx") else wl.idx) * (N // 2) * 16
-                             / (rl_ms / 1e3) / 1e9,
-                             "peak_gbutterfly_s": probe["butterfly_u64_lazy"], "probe": probe},
-            "step_algorithmic_gbs": wl.alg_bytes * args.steps / (ms / 1e3) / 1e9,
+            # the 64-bit transforms are also bound by arithmetic: butterflies per second of the same launch
+            # pair against the register-only rate of the butterfly these primes use (FP64 pipe for primes
+            # below 2^50), measured on this GPU just now
+            "arith_roofline": {"pipe": "fp64", "achieved_gbutterfly_s": len(wl.rl_idx if hasattr(wl, "rl_idx") else wl.idx)
+                               * (N // 2) * 16 / (rl_ms / 1e3) / 1e9,
+                               "peak_gbutterfly_s": probe["butterfly_u64_fp64"], "probe": probe},
+            "step_algorithmic_gbs": job_ops * wl.alg_bytes * args.steps / (ms / 1e3) / 1e9,
             "clocks": clocks,
         }
-        line["int_roofline"]["frac"] = line["int_roofline"]["achieved_gbutterfly_s"] / line["int_roofline"]["peak_gbutterfly_s"]
-        if not args.no_cpu_baseline:
+        line["arith_roofline"]["frac"] = (line["arith_roofline"]["achieved_gbutterfly_s"]
+                                          / line["arith_roofline"]["peak_gbutterfly_s"])
+        if limb_line is not None:
+            line["limb_sharded"] = limb_line
+        if not args.no_cpu_baseline and world == 1:
             import oracle
             v, sample = wl.cpu_sample(oracle)
             line["cpu_baseline"] = {"value": v, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",

@@ -103,12 +103,13 @@ class Library:
             raise CeriumError(rc, self.dll.cerium_last_error().decode())
 
     PROBE_NAMES = ("mad.lo.u32", "mad.wide.u32", "mul.hi.u64", "mul.lo.u64", "add.u64",
-                   "butterfly_u64_strict", "butterfly_u64_lazy", "butterfly_u32")
+                   "butterfly_u64_strict", "butterfly_u64_lazy", "butterfly_u32",
+                   "fma.rn.f64", "butterfly_u64_fp64")
 
     def probe_int_pipe(self, device: int = 0) -> dict:
-        """Register-only instruction / butterfly rates in Gop/s (the integer roofline)."""
-        buf = (C.c_double * 8)()
-        self.check(self.dll.cerium_probe_int_pipe(device, buf, 8))
+        """Register-only instruction / butterfly rates in Gop/s (the arithmetic roofline)."""
+        buf = (C.c_double * 10)()
+        self.check(self.dll.cerium_probe_int_pipe(device, buf, 10))
         return dict(zip(self.PROBE_NAMES, [float(v) for v in buf]))
 
     def galois_elt_from_step(self, step: int, logn: int = 16) -> int:

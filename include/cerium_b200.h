@@ -284,11 +284,13 @@ CERIUM_API int cerium_rescale(cerium_context *ctx, int round_mode, void *out, co
                    const uint32_t *q_idx, int L, int n_polys, void *scratch, void *stream);
 
 /*
- * Diagnostic: register-only rates of the integer instructions and butterflies the transforms are
- * made of, in giga-operations per second on `device` (the integer-multiply roofline of the
- * 64-bit kernels).  gops[0..7] = mad.lo.u32, mad.wide.u32, mul.hi.u64, mul.lo.u64, add.u64,
- * 64-bit strict butterfly, 64-bit lazy butterfly, 32-bit butterfly.  Allocates a small scratch
- * buffer and synchronises the device; no counterpart in the reference.
+ * Diagnostic: register-only rates of the instructions and butterflies the transforms are made
+ * of, in giga-operations per second on `device` (the arithmetic roofline of the 64-bit kernels).
+ * gops[0..7] = mad.lo.u32, mad.wide.u32, mul.hi.u64, mul.lo.u64, add.u64, 64-bit strict
+ * butterfly, 64-bit lazy butterfly, 32-bit butterfly; with n_results >= 10 also gops[8] =
+ * fma.rn.f64 and gops[9] = the double-precision butterfly that primes below 2^50 use.
+ * n_results must be at least 8.  Allocates a small scratch buffer and synchronises the device;
+ * no counterpart in the reference.
  */
 CERIUM_API int cerium_probe_int_pipe(int device, double *gops, int n_results);
 
