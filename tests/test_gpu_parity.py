@@ -102,3 +102,37 @@ def test_ntt_full_batch_properties(be):
     sample = [0, 47, 48 * 3 + 17, 48 * 7 + 47]
     want = h.orc.ntt_forward(be.to_host(x[sample].contiguous()), [idx[i] for i in sample])
     assert np.array_equal(be.to_host(fx[sample].contiguous()), want)
+
+
+def test_host_pipeline_matches_direct_calls(be):
+    """The three-stream host pipeline returns, per submitted operation, what the direct call returns
+    (ring of 3 slots, 7 operations, so every slot is reused)."""
+    import numpy as np
+    from cerium_b200.host_pipeline import HostPipeline
+    torch = be.torch
+    import oracle
+    mods = pc.moduli_for(64, 4, 1)
+    ctx = _capi.Context(be.lib, mods, 64)
+    idx = [0, 1, 2, 3]
+    rng = np.random.default_rng(7)
+
+    def op(ins, outs, stream):
+        ctx.ntt_forward(outs[0].data_ptr(), ins[0].data_ptr(), idx, stream=stream)
+
+    pipe = HostPipeline(torch, [(4, pc.N)], [(4, pc.N)], op)
+    hosts, slots = [], []
+    for k in range(7):
+        x = np.stack([rng.integers(0, mods[i], size=pc.N, dtype=np.uint64) for i in idx])
+        h = torch.from_numpy(x.view(np.int64)).pin_memory()
+        hosts.append((x, h))
+        slot = pipe.submit([h])
+        if k >= 2:
+            # read the result of operation k - 2 while k and k - 1 are in flight
+            got = pipe.wait((k - 2) % 3)[0].numpy().view(np.uint64).copy()
+            slots.append((k - 2, got))
+    pipe.drain()
+    for k in (5, 6):
+        slots.append((k, pipe.host_out[k % 3][0].numpy().view(np.uint64).copy()))
+    orc = oracle.OracleContext(pc.LOGN, mods)
+    for k, got in slots:
+        assert np.array_equal(got, orc.ntt_forward(hosts[k][0], idx)), "operation %d" % k

@@ -84,3 +84,54 @@ def test_sud_three_way(env):
                      for i, b in enumerate(d["bases"])]).astype(np.uint32)
     assert np.array_equal(_canon(r, mods), want), "oracle differs from the reference CUDA kernel"
     assert np.array_equal(o.cpu().numpy().view(np.uint32), want), "product differs from the oracle"
+
+
+def test_timing_against_reference_kernels(env, capsys):
+    """Times the reference's kernels and the product's 32-bit kernels on identical inputs (384 limb
+    transforms, the seven 5 -> 35 conversions of one key switch) and prints one JSON object; run
+    with `-s` to see it.  Only the agreement of the outputs is asserted."""
+    import json
+    be, G, ref, ctx, octx = env
+    torch = be.torch
+
+    def timed(fn, iters=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / iters
+
+    P = G.PRIMES
+    idx = [l for _ in range(8) for l in range(48)]
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    q = torch.tensor([P[i] for i in idx], dtype=torch.int64, device="cuda").view(-1, 1)
+    x = (torch.randint(0, 1 << 40, (len(idx), N), dtype=torch.int64, device="cuda", generator=gen) % q).to(torch.int32)
+    y, z = torch.empty_like(x), torch.empty_like(x)
+    res = {}
+    res["ours_ntt_fwd_384_ms"] = timed(lambda: ctx.ntt_forward(y.data_ptr(), x.data_ptr(), idx))
+    res["ours_ntt_inv_384_ms"] = timed(lambda: ctx.ntt_inverse(y.data_ptr(), x.data_ptr(), idx))
+    ref.ntt(z.data_ptr(), x.data_ptr(), idx, False, 3)
+    res["ref_ntt_fwd_384_ms"] = ref.ntt(z.data_ptr(), x.data_ptr(), idx, False, 20) / 20
+    ref.ntt(z.data_ptr(), x.data_ptr(), idx, True, 3)
+    res["ref_ntt_inv_384_ms"] = ref.ntt(z.data_ptr(), x.data_ptr(), idx, True, 20) / 20
+    in_idx = [0, 7, 14, 21, 28]
+    out_idx = [i for i in range(35) if i % 7] + [63, 62, 61, 60, 59]
+    xin = x[:35].contiguous()
+    o_ref = torch.empty((7 * 35, N), dtype=torch.int32, device="cuda")
+    o_ours = torch.empty_like(o_ref)
+    ref.bconv(o_ref.data_ptr(), xin.data_ptr(), in_idx, out_idx, 7, 3)
+    res["ref_bconv_5_35_x7_ms"] = ref.bconv(o_ref.data_ptr(), xin.data_ptr(), in_idx, out_idx, 7, 20) / 20
+    bc = _capi.BaseConverter(ctx, in_idx, out_idx, _capi.BCONV_LAZY)
+    outs = [o_ours.data_ptr() + d * 35 * N * 4 for d in range(7)]
+    ins = [xin.data_ptr() + d * 5 * N * 4 for d in range(7)]
+    res["ours_bconv_5_35_x7_one_launch_ms"] = timed(lambda: _capi.BaseConverter.apply_batch([bc] * 7, outs, ins))
+    torch.cuda.synchronize()
+    mods = np.array([P[j] for j in out_idx] * 7, dtype=np.uint32)[:, None]
+    assert np.array_equal(o_ref.cpu().numpy().view(np.uint32) % mods, o_ours.cpu().numpy().view(np.uint32))
+    with capsys.disabled():
+        print("\nREF_CUDA_TIMING " + json.dumps(res))
