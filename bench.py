@@ -417,6 +417,8 @@ def run_reference_arm(args, wl):
     if rank != 0:
         return
     import oracle
+    # all the host threads there are, also under torchrun (which exports OMP_NUM_THREADS=1)
+    oracle.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     vals = []
     sample = ""
     for _ in range(max(1, min(args.warmup, 1))):

@@ -85,6 +85,7 @@ def lib():
                                       C.c_int, _u32p, C.c_int, _u64p, _u64p, _u64p, _u64p, _u64p,
                                       _u64p, _u64p]
         L.orc_num_threads.restype = C.c_int
+        L.orc_set_num_threads.argtypes = [C.c_int]
         for name in ("orc_ew_add", "orc_ew_sub", "orc_ew_mul"):
             getattr(L, name).argtypes = [C.c_uint64, C.c_size_t, _u64p, _u64p, _u64p]
         L.orc_ew_neg.argtypes = [C.c_uint64, C.c_size_t, _u64p, _u64p]
@@ -276,3 +277,9 @@ def ew(op: str, q: int, *arrays, scalar: int | None = None) -> np.ndarray:
 
 def num_threads() -> int:
     return int(lib().orc_num_threads())
+
+
+def set_num_threads(n: int) -> None:
+    """Number of OpenMP threads of the following calls (launchers such as torchrun export
+    OMP_NUM_THREADS=1 to their children)."""
+    lib().orc_set_num_threads(int(n))

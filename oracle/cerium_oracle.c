@@ -704,6 +704,15 @@ ORC_API void orc_hmult_relin(const orc_ctx *c, int bconv_mode, int round_mode, i
   free(d0); free(d1); free(d2); free(k0); free(k1);
 }
 
+/* n <= 0 leaves the OpenMP default alone */
+ORC_API void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 ORC_API int orc_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();
