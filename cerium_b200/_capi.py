@@ -62,6 +62,8 @@ SIGNATURES = {
     "cerium_hoisted_rotate": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, C.c_uint32, _vp]),
     "cerium_hmult": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_int, _vp]),
     "cerium_rescale": (C.c_int, [_vp, C.c_int, _vp, _vp, _u32p, C.c_int, C.c_int, _vp, _vp]),
+    "cerium_double_rescale": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32), C.c_int, C.c_int,
+                                        C.c_void_p, C.c_void_p]),
     "cerium_probe_int_pipe": (C.c_int, [C.c_int, C.POINTER(C.c_double), C.c_int]),
     "cerium_rescale_static": (C.c_int, [_vp, C.c_int, _vp, _vp, _u32p, C.c_int, C.c_int, _vp]),
 }
@@ -202,6 +204,11 @@ class Context:
         self.lib.check(self.lib.dll.cerium_rescale(self.h, round_mode, out, inp, _u32(q_idx), len(q_idx), n_polys,
                                                    scratch, stream))
 
+
+    def double_rescale(self, out: int, inp: int, q_idx: Sequence[int], n_polys: int, scratch: int, stream: int = 0):
+        """Drops the last two limbs at once; scratch holds 4 * n_polys limbs."""
+        self.lib.check(self.lib.dll.cerium_double_rescale(self.h, out, inp, _u32(q_idx), len(q_idx), n_polys,
+                                                          scratch, stream))
 
     def rescale_static(self, out: int, inp: int, q_idx: Sequence[int], n_polys: int,
                        round_mode: int = ROUND_FLOOR, stream: int = 0):

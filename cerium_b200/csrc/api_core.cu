@@ -292,6 +292,10 @@ int create_bconv(cerium_context* ctx, cerium_bconv** out, int mode, const uint32
     }
     for (int j = 0; j < n_out; j++) out_sub[j] = half_mod(m[out_primes[j]]);
   }
+  // every input prime runs double-precision arithmetic and no rounding term is added: the kernel may
+  // compute the outputs of such primes on the FP64 pipe
+  bc->fp_in = bits == 64 && n_in <= kBconvRegInputs && ctx->allow_fp && in_add.empty();
+  for (int i = 0; i < n_in; i++) bc->fp_in = bc->fp_in && m[in_primes[i]] < ((uint64_t)1 << 50);
   const bool use_inv = mode == CERIUM_BCONV_EXACT && !opt.prescaled && n_in > 1;
   Blob blob;
   size_t o_fac = 0, o_inv = 0, o_invs = 0, o_add = 0, o_sub = 0;
@@ -304,6 +308,45 @@ int create_bconv(cerium_context* ctx, cerium_bconv** out, int mode, const uint32
     o_sub = blob.append_words<W>(out_sub);
     return 0;
   });
+  size_t o_outc = 0, o_split = 0, o_fpfac = 0;
+  const bool split = bits == 64 && n_in <= kBconvRegInputs;
+  dispatch_word(bits, [&](auto tag) -> int {
+    using W = decltype(tag);
+    std::vector<BconvOut<W>> outc(n_out);
+    for (int j = 0; j < n_out; j++) {
+      const uint32_t pj = out_primes[j];
+      BconvOut<W>& o = outc[j];
+      std::memset(&o, 0, sizeof(o));
+      o.q = (W)m[pj];
+      o.q2 = (W)(2 * m[pj]);
+      o.mu_hi = (W)ctx->mu_hi[pj];
+      o.mu_lo = (W)ctx->mu_lo[pj];
+      o.sub = out_sub.empty() ? (W)0 : (W)out_sub[j];
+      o.pos = opt.out_pos.empty() ? (uint32_t)j : opt.out_pos[j];
+      o.has_sub = out_sub.empty() ? 0 : 1;
+      o.strict = (ctx->lazy_ok[pj] && !ctx->fp_ok[pj]) ? 0 : 1;
+      o.fp = (split && bc->fp_in && ctx->fp_ok[pj] && out_sub.empty()) ? 1 : 0;
+      const double qinv = 1.0 / (double)m[pj];
+      uint64_t qinv_bits;
+      std::memcpy(&qinv_bits, &qinv, 8);
+      o.fp_qinv = (W)qinv_bits;
+    }
+    o_outc = blob.append(outc.data(), outc.size() * sizeof(BconvOut<W>));
+    return 0;
+  });
+  if (split) {
+    std::vector<uint2> sf(factors.size());
+    std::vector<double2> ff(factors.size());
+    for (size_t k = 0; k < factors.size(); k++) {
+      const uint64_t f = factors[k], q = m[out_primes[k / n_in]];
+      sf[k] = make_uint2((uint32_t)f & 0x3fffffffu, (uint32_t)(f >> 30));
+      // centred factor and its correctly rounded quotient by q (IEEE division)
+      const double fd = f > q / 2 ? -(double)(q - f) : (double)f;
+      ff[k] = make_double2(fd, fd / (double)q);
+    }
+    o_split = blob.append(sf.data(), sf.size() * sizeof(uint2));
+    o_fpfac = blob.append(ff.data(), ff.size() * sizeof(double2));
+  }
   const size_t o_ip = blob.append(bc->in_primes.data(), bc->in_primes.size() * 4);
   const size_t o_op = blob.append(bc->out_primes.data(), bc->out_primes.size() * 4);
   const size_t o_pos = blob.append(opt.out_pos.data(), opt.out_pos.size() * 4);
@@ -319,6 +362,9 @@ int create_bconv(cerium_context* ctx, cerium_bconv** out, int mode, const uint32
   }
   char* base = static_cast<char*>(bc->d_block);
   bc->d_factors = base + o_fac;
+  bc->d_outc = base + o_outc;
+  bc->d_split_fac = split ? base + o_split : nullptr;
+  bc->d_fp_fac = (split && bc->fp_in) ? base + o_fpfac : nullptr;
   bc->d_inv = use_inv ? base + o_inv : nullptr;
   bc->d_inv_shoup = use_inv ? base + o_invs : nullptr;
   bc->d_in_add = in_add.empty() ? nullptr : base + o_add;
@@ -358,7 +404,11 @@ int launch_bconv(cerium_context* ctx, const BconvCall* calls, int count, cudaStr
         d.out_prime = bc->d_out_prime;
         d.out_pos = bc->d_out_pos;
         d.in_pos = bc->d_in_pos;
+        d.outc = static_cast<const BconvOut<W>*>(bc->d_outc);
+        d.split_fac = static_cast<const uint2*>(bc->d_split_fac);
+        d.fp_fac = static_cast<const double2*>(bc->d_fp_fac);
         d.lazy_out = bc->lazy_out ? 1 : 0;
+        d.fp_in = bc->fp_in ? 1 : 0;
         d.I = bc->I;
         d.O = bc->O;
         smem = std::max(smem, bconv_smem_bytes<W>(bc->I, bc->O));
@@ -474,6 +524,10 @@ int cerium_context_create(cerium_context** out, int device, int log_n, int word_
       pc.w1ninv = (W)w1;
       pc.w1ninv_shoup = (W)host::shoup(w1, q, word_bits);
       pc.lazy_ok = (W)((word_bits == 64 && q < ((uint64_t)1 << 52)) ? 1 : 0);
+      ctx->mu_hi.push_back(t.mu_hi);
+      ctx->mu_lo.push_back(t.mu_lo);
+      ctx->lazy_ok.push_back(pc.lazy_ok != 0 ? 1 : 0);
+      ctx->fp_ok.push_back(fp ? 1 : 0);
       if (fp) {
         const double qinv = 1.0 / (double)q;
         uint64_t bits;

@@ -629,4 +629,79 @@ int cerium_rescale(cerium_context* ctx, int round_mode, void* out, const void* i
   return rescale_impl(ctx, round_mode, outs.data(), nullptr, in, q_idx, L, n_polys, scratch, (cudaStream_t)stream);
 }
 
+int cerium_double_rescale(cerium_context* ctx, void* out, const void* in, const uint32_t* q_idx, int L, int n_polys,
+                          void* scratch, void* stream) {
+  if (!ctx || !out || !in || !q_idx || !scratch) return fail(CERIUM_ERR_INVALID, "double_rescale: null argument");
+  if (L < 3 || L - 2 > 64) return fail(CERIUM_ERR_INVALID, "double_rescale: need 3 <= L <= 66");
+  if (n_polys < 1 || n_polys > 128) return fail(CERIUM_ERR_INVALID, "double_rescale: need 1 <= n_polys <= 128");
+  for (int i = 0; i < L; i++)
+    if (q_idx[i] >= (uint32_t)ctx->n_primes) return fail(CERIUM_ERR_INVALID, "double_rescale: prime index out of range");
+  if (q_idx[L - 1] == q_idx[L - 2]) return fail(CERIUM_ERR_INVALID, "double_rescale: the two dropped primes are the same");
+  if (((uintptr_t)out | (uintptr_t)in | (uintptr_t)scratch) & 15u) return fail(CERIUM_ERR_INVALID, "double_rescale: pointers must be 16-byte aligned");
+  DeviceGuard guard(ctx->device);
+  const size_t n = kN, wb = ctx->word_bytes(), limb = n * wb;
+  const int R = L - 2;
+  const uint32_t pa = q_idx[L - 2], pb = q_idx[L - 1];
+  cudaStream_t st = (cudaStream_t)stream;
+  char* sc = static_cast<char*>(scratch);  // per polynomial: [x_a | x_b | lo | hi]
+  // 1. inverse transform of the two dropped limbs of every polynomial
+  {
+    // entry (p, k) reads limb p*L + L-2+k of `in`: one call per k with the input base shifted
+    for (int k = 0; k < 2; k++) {
+      std::vector<uint32_t> po(n_polys), pr(n_polys, k == 0 ? pa : pb);
+      for (int p = 0; p < n_polys; p++) po[p] = (uint32_t)p;
+      NttCall c{};
+      c.in = static_cast<const char*>(in) + (size_t)(L - 2 + k) * limb;
+      c.in_stride = (size_t)L * n;
+      c.out = sc + (size_t)k * limb;
+      c.out_stride = 4 * n;
+      c.pos = po.data();
+      c.prime = pr.data();
+      c.count = n_polys;
+      if (int rc = launch_ntt_inverse(ctx, c, nullptr, nullptr, st)) return rc;
+    }
+  }
+  // 2. exact CRT composition of the pair, every polynomial in one launch
+  if (int rc = cerium_resolve2(ctx, sc + 2 * limb, sc + 3 * limb, sc, sc + limb, 4 * n, pa, pb, n_polys, stream)) return rc;
+  // 3. its residues modulo the remaining primes, written where the results will be
+  for (int p = 0; p < n_polys; p++) {
+    char* o = static_cast<char*>(out) + (size_t)p * R * limb;
+    if (int rc = cerium_mod2(ctx, o, n, sc + (size_t)(4 * p + 2) * limb, sc + (size_t)(4 * p + 3) * limb, q_idx, R, stream)) return rc;
+  }
+  // 4. SuD in place: out = (in - NTT(out)) * (q_a q_b)^-1, two polynomials per launch pair
+  std::vector<uint64_t> factor(2 * R);
+  std::vector<uint32_t> prime2(2 * R);
+  for (int i = 0; i < 2 * R; i++) {
+    const uint64_t q = ctx->moduli[q_idx[i % R]];
+    prime2[i] = q_idx[i % R];
+    factor[i] = host::invmod(host::mulmod(ctx->moduli[pa] % q, ctx->moduli[pb] % q, q), q);
+  }
+  for (int p = 0; p < n_polys;) {
+    char* o = static_cast<char*>(out) + (size_t)p * R * limb;
+    SudCall s{};
+    s.src = o;
+    s.src_stride = n;
+    s.work = o;
+    s.work_stride = n;
+    s.dst = o;
+    s.dst_stride = n;
+    s.minuend = static_cast<const char*>(in) + (size_t)p * L * limb;
+    s.minuend_stride = n;
+    s.prime = prime2.data();
+    s.factor = factor.data();
+    if (p + 1 < n_polys && 2 * R <= kSudMaxBatch) {
+      s.count = 2 * R;
+      s.split = R;
+      s.dst2 = o + (size_t)R * limb;
+      s.minuend2 = static_cast<const char*>(in) + (size_t)(p + 1) * L * limb;
+      p += 2;
+    } else {
+      s.count = R;
+      p += 1;
+    }
+    if (int rc = launch_sud(ctx, s, st)) return rc;
+  }
+  return CERIUM_OK;
+}
+
 }  // extern "C"

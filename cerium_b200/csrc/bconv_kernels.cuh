@@ -25,6 +25,9 @@ constexpr int kBconvRegInputs = 8;
 // grid.z splits the output primes of a conversion when the batch alone gives too few CTAs
 
 template <typename W>
+struct BconvOut;
+
+template <typename W>
 struct BconvDesc {
   const W* in;             // I limbs, coefficient form
   W* out;                  // O limbs
@@ -39,7 +42,14 @@ struct BconvDesc {
   const uint32_t* out_prime;  // [O]
   const uint32_t* out_pos;    // [O] limb slot of output j inside `out`, or null (slot j)
   const uint32_t* in_pos;     // [I] limb slot of input i inside `in`, or null (slot i)
+  // tables built when the converter is created (device memory, never change): per-output constants,
+  // and for the 64-bit split path the factors as 30-bit pieces and as double-precision pairs
+  const BconvOut<W>* outc;    // [O]
+  const uint2* split_fac;     // [O][I] or null
+  const double2* fp_fac;      // [O][I] {factor centred, RN(factor / q)} or null
   int lazy_out;               // 64-bit split path only: leave outputs in [0, 8q) / [0, 4q) for the forward NTT
+  int fp_in;                  // 64-bit split path only: every input prime is below 2^50 and no rounding term is
+                              // added, so outputs whose prime is below 2^50 too are computed on the FP64 pipe
   int I;
   int O;
 };
@@ -49,9 +59,11 @@ struct BconvDesc {
 template <typename W>
 struct BconvOut {
   W q, q2, mu_hi, mu_lo, sub;  // sub = rounding term (0 when unused)
+  W fp_qinv;                   // bit pattern of RN(1 / q) when fp is set
   uint32_t pos;                // limb slot of this output
   uint16_t has_sub;            // rounding term present
-  uint16_t strict;             // the prime's transform needs inputs below 4q (all but the lazy integer butterflies)
+  uint8_t strict;              // the prime's transform needs inputs below 4q (all but the lazy integer butterflies)
+  uint8_t fp;                  // this output is computed in double precision (see bconv_body_split64)
 };
 
 // Barrett reduction with the 3-multiply high products: qhat may be up to 7 short, so the
@@ -81,20 +93,43 @@ __device__ __forceinline__ W bconv_input(const BconvDesc<W>& d, const PrimeConst
 // partial product is a 32x32->64 multiply-add into one of three column sums (y0*f0,
 // y0*f1 + y1*f0, y1*f1).  With pieces below 2^30 and at most 8 terms no column overflows, so
 // a multiply-accumulate is four IMAD.WIDE and no carry handling.
+//
+// Outputs flagged `fp` (input and output primes below 2^50, no rounding terms) take the FP64 pipe
+// instead: each term is an exact double-precision modular product (fp_mulmod, modarith.cuh) of the
+// input, held as a double, with the centred factor; the sum of at most 8 terms of magnitude below
+// 0.6 q is exact, one fp_reduce brings it within q/2.  41 FP64 operations per output of 5 terms
+// against ~120 integer instructions, and the remaining integer outputs (60-bit primes) overlap
+// with them on the other pipe.  sfp holds {factor centred, RN(factor / q)} per (output, input).
 template <int kI, bool kLazyOut>  // kI = exact number of inputs, 1..8
 __device__ __forceinline__ void bconv_body_split64(const BconvDesc<uint64_t>& d,
                                                    const PrimeConst<uint64_t>* __restrict__ pcs,
-                                                   const uint2* sfac, const BconvOut<uint64_t>* sout, int coeff) {
+                                                   const uint2* sfac, const BconvOut<uint64_t>* sout,
+                                                   const double2* sfp, int coeff) {
   const int O = d.O;
   uint32_t y0[kI], y1[kI];
+  double yd[kI];
 #pragma unroll
   for (int i = 0; i < kI; i++) {
     const uint64_t v = bconv_input<uint64_t>(d, pcs, i, coeff);
     y0[i] = (uint32_t)v & 0x3fffffffu;
     y1[i] = (uint32_t)(v >> 30);
+    yd[i] = d.fp_in ? fp_from_u64(v) : 0.0;
   }
 #pragma unroll 2
   for (int j = 0; j < O; j++) {
+    if (sout[j].fp) {
+      const BconvOut<uint64_t> o = sout[j];
+      const double2* f = sfp + j * kI;
+      const double q = fp_from_u64(o.q), nq = -q;
+      double acc = 0.0;
+#pragma unroll
+      for (int i = 0; i < kI; i++) acc = __dadd_rn(acc, fp_mulmod(yd[i], f[i].x, f[i].y, nq));
+      double r = fp_reduce(acc, __longlong_as_double((long long)o.fp_qinv), nq);
+      // lazy: (q/2, 3q/2) is as good as [0, q) for the forward transform that follows
+      if (kLazyOut || r < 0.0) r = __dadd_rn(r, q);
+      d.out[(size_t)o.pos * d.out_stride + coeff] = fp_to_u64(r);
+      continue;
+    }
     const uint2* f = sfac + j * kI;
     uint64_t c0 = 0, c1 = 0, c2 = 0;
 #pragma unroll
@@ -181,8 +216,9 @@ struct BconvBatch {
 template <typename W>
 __host__ __device__ inline size_t bconv_smem_bytes(int I, int O) {
   size_t n = (size_t)O * I * sizeof(W);
-  n = (n + 15) / 16 * 16 + (size_t)O * sizeof(BconvOut<W>);
+  n = (n + 15) / 16 * 16 + ((size_t)O * sizeof(BconvOut<W>) + 15) / 16 * 16;
   if (I > kBconvRegInputs) n += (size_t)I * kBconvThreads * sizeof(W);
+  else if (sizeof(W) == 8) n += (size_t)O * I * 16;  // double-precision factor pairs
   return n;
 }
 
@@ -200,39 +236,24 @@ __global__ void __launch_bounds__(kBconvThreads)
   // restrict the descriptor to this CTA's slice of the outputs
   const int I = d.I, O = (d.O - j_first) < out_chunk ? (d.O - j_first) : out_chunk;
   d.factors += (size_t)j_first * I;
-  d.out_prime += j_first;
-  if (d.out_sub != nullptr) d.out_sub += j_first;
-  if (d.out_pos != nullptr) d.out_pos += j_first;
-  const uint32_t pos_base = d.out_pos != nullptr ? 0u : (uint32_t)j_first;
   d.O = O;
   W* sfac = reinterpret_cast<W*>(smem_raw);
   const size_t fac_bytes = ((size_t)O * I * sizeof(W) + 15) / 16 * 16;
   BconvOut<W>* sout = reinterpret_cast<BconvOut<W>*>(smem_raw + fac_bytes);
-  W* scol = reinterpret_cast<W*>(smem_raw + fac_bytes + (size_t)O * sizeof(BconvOut<W>));
+  const size_t out_bytes = ((size_t)O * sizeof(BconvOut<W>) + 15) / 16 * 16;
+  W* scol = reinterpret_cast<W*>(smem_raw + fac_bytes + out_bytes);
+  double2* sfp = reinterpret_cast<double2*>(smem_raw + fac_bytes + out_bytes);  // split path only (no scol then)
   const bool split = sizeof(W) == 8 && I <= kBconvRegInputs;
+  // stage this CTA's slice of the converter's tables
   for (int k = threadIdx.x; k < O * I; k += kBconvThreads) {
-    const W f = d.factors[k];
     if (split) {
-      // the split path reads the factor as two 30-bit pieces
-      const uint64_t f64 = (uint64_t)f;
-      reinterpret_cast<uint2*>(sfac)[k] = make_uint2((uint32_t)f64 & 0x3fffffffu, (uint32_t)(f64 >> 30));
+      reinterpret_cast<uint2*>(sfac)[k] = d.split_fac[(size_t)j_first * I + k];
+      if (d.fp_in != 0) sfp[k] = d.fp_fac[(size_t)j_first * I + k];
     } else {
-      sfac[k] = f;
+      sfac[k] = d.factors[k];
     }
   }
-  for (int j = threadIdx.x; j < O; j += kBconvThreads) {
-    const PrimeConst<W> pc = pcs[d.out_prime[j]];
-    BconvOut<W> o;
-    o.q = pc.q;
-    o.q2 = pc.q2;
-    o.mu_hi = pc.mu_hi;
-    o.mu_lo = pc.mu_lo;
-    o.sub = d.out_sub != nullptr ? d.out_sub[j] : (W)0;
-    o.pos = d.out_pos != nullptr ? d.out_pos[j] : pos_base + (uint32_t)j;
-    o.has_sub = d.out_sub != nullptr ? 1 : 0;
-    o.strict = (pc.lazy_ok != 0 && pc.fp_ok == 0) ? 0 : 1;
-    sout[j] = o;
-  }
+  for (int j = threadIdx.x; j < O; j += kBconvThreads) sout[j] = d.outc[j_first + j];
   grid_dependency_wait();  // the tables above never change; the input limbs below come from the previous kernel
   __syncthreads();
   const int coeff = blockIdx.x * kBconvThreads + threadIdx.x;
@@ -242,14 +263,14 @@ __global__ void __launch_bounds__(kBconvThreads)
     const uint2* f2 = reinterpret_cast<const uint2*>(sfac);
     const BconvOut<uint64_t>* so = reinterpret_cast<const BconvOut<uint64_t>*>(sout);
     switch (I) {
-      case 1: if (d.lazy_out) bconv_body_split64<1, true>(d64, p64, f2, so, coeff); else bconv_body_split64<1, false>(d64, p64, f2, so, coeff); break;
-      case 2: if (d.lazy_out) bconv_body_split64<2, true>(d64, p64, f2, so, coeff); else bconv_body_split64<2, false>(d64, p64, f2, so, coeff); break;
-      case 3: if (d.lazy_out) bconv_body_split64<3, true>(d64, p64, f2, so, coeff); else bconv_body_split64<3, false>(d64, p64, f2, so, coeff); break;
-      case 4: if (d.lazy_out) bconv_body_split64<4, true>(d64, p64, f2, so, coeff); else bconv_body_split64<4, false>(d64, p64, f2, so, coeff); break;
-      case 5: if (d.lazy_out) bconv_body_split64<5, true>(d64, p64, f2, so, coeff); else bconv_body_split64<5, false>(d64, p64, f2, so, coeff); break;
-      case 6: if (d.lazy_out) bconv_body_split64<6, true>(d64, p64, f2, so, coeff); else bconv_body_split64<6, false>(d64, p64, f2, so, coeff); break;
-      case 7: if (d.lazy_out) bconv_body_split64<7, true>(d64, p64, f2, so, coeff); else bconv_body_split64<7, false>(d64, p64, f2, so, coeff); break;
-      default: if (d.lazy_out) bconv_body_split64<8, true>(d64, p64, f2, so, coeff); else bconv_body_split64<8, false>(d64, p64, f2, so, coeff); break;
+      case 1: if (d.lazy_out) bconv_body_split64<1, true>(d64, p64, f2, so, sfp, coeff); else bconv_body_split64<1, false>(d64, p64, f2, so, sfp, coeff); break;
+      case 2: if (d.lazy_out) bconv_body_split64<2, true>(d64, p64, f2, so, sfp, coeff); else bconv_body_split64<2, false>(d64, p64, f2, so, sfp, coeff); break;
+      case 3: if (d.lazy_out) bconv_body_split64<3, true>(d64, p64, f2, so, sfp, coeff); else bconv_body_split64<3, false>(d64, p64, f2, so, sfp, coeff); break;
+      case 4: if (d.lazy_out) bconv_body_split64<4, true>(d64, p64, f2, so, sfp, coeff); else bconv_body_split64<4, false>(d64, p64, f2, so, sfp, coeff); break;
+      case 5: if (d.lazy_out) bconv_body_split64<5, true>(d64, p64, f2, so, sfp, coeff); else bconv_body_split64<5, false>(d64, p64, f2, so, sfp, coeff); break;
+      case 6: if (d.lazy_out) bconv_body_split64<6, true>(d64, p64, f2, so, sfp, coeff); else bconv_body_split64<6, false>(d64, p64, f2, so, sfp, coeff); break;
+      case 7: if (d.lazy_out) bconv_body_split64<7, true>(d64, p64, f2, so, sfp, coeff); else bconv_body_split64<7, false>(d64, p64, f2, so, sfp, coeff); break;
+      default: if (d.lazy_out) bconv_body_split64<8, true>(d64, p64, f2, so, sfp, coeff); else bconv_body_split64<8, false>(d64, p64, f2, so, sfp, coeff); break;
     }
   } else {
     switch (I) {

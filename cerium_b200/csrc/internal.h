@@ -101,6 +101,8 @@ struct cerium_context {
   // 64-bit primes below 2^50 transform on the FP64 pipe unless the environment variable
   // CERIUM_B200_NTT_ARITH is "int" when the context is created (for comparisons)
   bool allow_fp = true;
+  std::vector<uint64_t> mu_hi, mu_lo;  // Barrett constants per prime (host copy)
+  std::vector<uint8_t> fp_ok, lazy_ok; // arithmetic of each prime's transforms (host copy)
   size_t word_bytes() const { return (size_t)word_bits / 8; }
 };
 
@@ -112,6 +114,9 @@ struct cerium_bconv {
   // one device allocation holding every table below
   void* d_block = nullptr;
   void* d_factors = nullptr;    // W[O][I]
+  void* d_outc = nullptr;       // BconvOut<W>[O]
+  void* d_split_fac = nullptr;  // uint2[O][I] (64-bit words, at most 8 inputs)
+  void* d_fp_fac = nullptr;     // double2[O][I] (when fp_in)
   void* d_inv = nullptr;        // W[I] (exact mode, unless the caller pre-scales)
   void* d_inv_shoup = nullptr;  // W[I]
   void* d_in_add = nullptr;     // W[I]  rounding term, or null
@@ -122,6 +127,7 @@ struct cerium_bconv {
   uint32_t* d_in_pos = nullptr;   // or null
   bool lazy_out = false;
   std::vector<uint64_t> inv_host;  // [Qhat_i^-1]_{q_i}
+  bool fp_in = false;              // inputs qualify for the double-precision outputs of the kernel
 };
 
 namespace cerium {

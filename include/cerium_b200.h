@@ -284,6 +284,16 @@ CERIUM_API int cerium_rescale(cerium_context *ctx, int round_mode, void *out, co
                    const uint32_t *q_idx, int L, int n_polys, void *scratch, void *stream);
 
 /*
+ * Double rescale: drops the last TWO limbs of n_polys polynomials at once (floor division by
+ * q_{L-2} * q_{L-1}); in is [n_polys][L][N] in NTT form, out is [n_polys][L-2][N], scratch holds
+ * 4 * n_polys limbs.  Restates double_rescale (cerium/compiler/backend/compiler_rescale.cc:
+ * 367-521): INTT of the two limbs, Resolve (exact CRT of the pair), Mod (its residues modulo the
+ * remaining primes), SuD with both primes as divide bases.  out must not overlap in.
+ */
+CERIUM_API int cerium_double_rescale(cerium_context *ctx, void *out, const void *in, const uint32_t *q_idx,
+                          int L, int n_polys, void *scratch, void *stream);
+
+/*
  * Diagnostic: register-only rates of the instructions and butterflies the transforms are made
  * of, in giga-operations per second on `device` (the arithmetic roofline of the 64-bit kernels).
  * gops[0..7] = mad.lo.u32, mad.wide.u32, mul.hi.u64, mul.lo.u64, add.u64, 64-bit strict

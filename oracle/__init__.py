@@ -79,6 +79,7 @@ def lib():
         L.orc_keyswitch.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, _u32p, C.c_int, _u32p,
                                     C.c_int, _u64p, _u64p, _u64p, _u64p]
         L.orc_rescale.argtypes = [C.c_void_p, C.c_int, C.c_int, _u32p, _u64p, _u64p]
+        L.orc_double_rescale.argtypes = [C.c_void_p, C.c_int, _u32p, _u64p, _u64p]
         L.orc_hrot.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, _u32p, C.c_int, _u32p,
                                C.c_int, C.c_uint32, _u64p, _u64p, _u64p, _u64p, _u64p]
         L.orc_hmult_relin.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, _u32p,
@@ -181,6 +182,14 @@ class OracleContext:
         cpoly = _c64(cpoly)
         out = np.empty((len(qi) - 1, self.n), dtype=np.uint64)
         lib().orc_rescale(self._h, round_mode, len(qi), _p32(qi), _p64(cpoly), _p64(out))
+        return out
+
+    def double_rescale(self, q_idx, cpoly) -> np.ndarray:
+        """Drops the last two limbs at once (floor division by their product)."""
+        qi = _idx(q_idx)
+        cpoly = _c64(cpoly)
+        out = np.empty((len(qi) - 2, self.n), dtype=np.uint64)
+        lib().orc_double_rescale(self._h, len(qi), _p32(qi), _p64(cpoly), _p64(out))
         return out
 
     def hrot(self, bconv_mode, round_mode, q_idx, p_idx, dnum, elt, c0, c1, evk):

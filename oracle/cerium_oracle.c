@@ -642,6 +642,36 @@ ORC_API void orc_rescale(const orc_ctx *c, int round_mode, int L, const uint32_t
 }
 
 /*
+ * Double rescale: drops the last TWO limbs at once.  With a = q_idx[L-2], b = q_idx[L-1]:
+ * v = the integer in [0, q_a q_b) with the coefficient-form residues of limbs a and b (exact CRT,
+ * orc_resolve2), out[i] = (c[i] - NTT_i(v mod q_i)) * (q_a q_b)^-1 for i < L-2: floor division by
+ * q_a q_b.  Restates double_rescale (cerium/compiler/backend/compiler_rescale.cc:367-521: INTT of
+ * the two limbs, Resolve, Mod, SuD with both primes as divide bases).
+ */
+ORC_API void orc_double_rescale(const orc_ctx *c, int L, const uint32_t *q_idx, const u64 *cpoly, u64 *out) {
+  size_t n = c->n;
+  int ia = (int)q_idx[L - 2], ib = (int)q_idx[L - 1];
+  u64 qa = c->p[ia].q, qb = c->p[ib].q;
+  u64 *xa = (u64 *)malloc(n * sizeof(u64)), *xb = (u64 *)malloc(n * sizeof(u64));
+  u64 *lo = (u64 *)malloc(n * sizeof(u64)), *hi = (u64 *)malloc(n * sizeof(u64));
+  memcpy(xa, cpoly + (size_t)(L - 2) * n, n * sizeof(u64));
+  memcpy(xb, cpoly + (size_t)(L - 1) * n, n * sizeof(u64));
+  orc_ntt_inverse(c, ia, xa);
+  orc_ntt_inverse(c, ib, xb);
+  orc_resolve2(qa, qb, n, xa, xb, lo, hi);
+#pragma omp parallel for schedule(dynamic)
+  for (int i = 0; i < L - 2; i++) {
+    u64 q = c->p[q_idx[i]].q;
+    u64 *t = (u64 *)malloc(n * sizeof(u64));
+    orc_mod2(q, n, lo, hi, t);
+    u64 f = orc_invmod(orc_mulmod(qa % q, qb % q, q), q);
+    orc_sud(c, (int)q_idx[i], cpoly + (size_t)i * n, t, f, out + (size_t)i * n);
+    free(t);
+  }
+  free(xa); free(xb); free(lo); free(hi);
+}
+
+/*
  * HRot: rotate (c0,c1) by Galois element elt and key-switch back.
  * Restates rotate_internal (cerium/compiler/backend/compiler.cc:701-726):
  * automorphism of both polynomials in NTT form, key switch of the rotated c1,

@@ -24,6 +24,8 @@ struct uint2 { unsigned x, y; };
 struct uint3 { unsigned x, y, z; };
 struct alignas(16) uint4 { unsigned x, y, z, w; };
 struct alignas(16) ulonglong2 { unsigned long long x, y; };
+struct alignas(16) double2 { double x, y; };
+static inline double2 make_double2(double a, double b) { return double2{a, b}; }
 struct dim3 {
   unsigned x, y, z;
   dim3(unsigned x_ = 1, unsigned y_ = 1, unsigned z_ = 1) : x(x_), y(y_), z(z_) {}

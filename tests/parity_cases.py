@@ -257,6 +257,23 @@ def case_rescale(be, word_bits, round_mode, L=4, n_polys=2):
     assert np.array_equal(h.down(out), want)
 
 
+def case_double_rescale(be, word_bits, L=5, n_polys=3):
+    """Two limbs dropped at once (INTT x2, Resolve, Mod, SuD); one pair of polynomials and a single."""
+    mods = moduli_for(word_bits, L, 1)
+    if word_bits == 64:
+        mods = mods[1:] + mods[:1]   # the 60-bit prime is one of the two dropped ones
+    h = Harness(be, word_bits, mods)
+    rng = np.random.default_rng(21)
+    q_idx = list(range(L))
+    x = np.stack([rand_limbs(rng, mods, q_idx) for _ in range(n_polys)])
+    dx = h.up(x)
+    out = h.new(n_polys, L - 2, N)
+    scratch = h.new(4 * n_polys, N)
+    h.ctx.double_rescale(h.p(out), h.p(dx), q_idx, n_polys, h.p(scratch))
+    want = np.stack([h.orc.double_rescale(q_idx, x[p]) for p in range(n_polys)])
+    assert np.array_equal(h.down(out), want)
+
+
 def case_resolve_mod(be, word_bits):
     """Two-limb CRT composition and its reduction modulo other primes (ModRaise building blocks)."""
     mods = moduli_for(word_bits, 5, 1)

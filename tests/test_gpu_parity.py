@@ -69,6 +69,11 @@ def test_keyswitch_hrot_hmult(be, word_bits, L, K, dnum, bm, rm):
 
 
 @pytest.mark.parametrize("word_bits", [32, 64])
+def test_double_rescale(be, word_bits):
+    pc.case_double_rescale(be, word_bits)
+
+
+@pytest.mark.parametrize("word_bits", [32, 64])
 def test_resolve_and_mod(be, word_bits):
     pc.case_resolve_mod(be, word_bits)
 

@@ -149,3 +149,21 @@ def test_rescale_vs_bigint_division():
         for c in range(n):
             want = (T[c] + q[2] // 2) // q[2] if mode == oracle.ROUND_HALF else T[c] // q[2]
             assert [int(v) for v in got[:, c]] == [want % q[0], want % q[1]]
+
+
+def test_double_rescale_vs_bigint_division():
+    logn = 4
+    n = 1 << logn
+    q = params.ntt_primes_below(50, 4, logn)
+    ctx = oracle.OracleContext(logn, q)
+    rng = np.random.default_rng(9)
+    Q = q[0] * q[1] * q[2] * q[3]
+    T = [int(rng.integers(0, 2**62)) * int(rng.integers(0, 2**62)) * int(rng.integers(0, 2**62))
+         * int(rng.integers(0, 2**14)) % Q for _ in range(n)]
+    T[0], T[1] = Q - 1, q[2] * q[3] - 1       # extremes: largest value, largest dropped part
+    coeffs = np.array([[t % m for t in T] for m in q], dtype=np.uint64)
+    ntt = ctx.ntt_forward(coeffs, [0, 1, 2, 3])
+    got = ctx.ntt_inverse(ctx.double_rescale([0, 1, 2, 3], ntt), [0, 1])
+    for c in range(n):
+        want = T[c] // (q[2] * q[3])
+        assert [int(v) for v in got[:, c]] == [want % q[0], want % q[1]]
