@@ -62,6 +62,10 @@ SIGNATURES = {
     "cerium_hoisted_rotate": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, C.c_uint32, _vp]),
     "cerium_hmult": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_int, _vp]),
     "cerium_rescale": (C.c_int, [_vp, C.c_int, _vp, _vp, _u32p, C.c_int, C.c_int, _vp, _vp]),
+    "cerium_keyswitch_create_lifted": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int,
+                                                 C.POINTER(C.c_uint32), C.c_int, C.POINTER(C.c_uint32), C.c_int]),
+    "cerium_mod_raise": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32,
+                                   C.c_void_p, C.c_void_p]),
     "cerium_double_rescale": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32), C.c_int, C.c_int,
                                         C.c_void_p, C.c_void_p]),
     "cerium_probe_int_pipe": (C.c_int, [C.c_int, C.POINTER(C.c_double), C.c_int]),
@@ -260,15 +264,24 @@ class KeySwitch:
     """Hybrid key-switching plan (handle of ``cerium_keyswitch``)."""
 
     def __init__(self, ctx: Context, q_idx: Sequence[int], p_idx: Sequence[int], dnum: int,
-                 bconv_mode: int = BCONV_LAZY, round_mode: int = ROUND_FLOOR, rank: int = 0, world: int = 1):
+                 bconv_mode: int = BCONV_LAZY, round_mode: int = ROUND_FLOOR, rank: int = 0, world: int = 1,
+                 lifted: bool = False):
         self.ctx = ctx
         self.q_idx, self.p_idx, self.dnum = list(q_idx), list(p_idx), dnum
         self.rank, self.world = rank, world
         h = _vp()
-        ctx.lib.check(ctx.lib.dll.cerium_keyswitch_create_sharded(ctx.h, C.byref(h), bconv_mode, round_mode,
-                                                                  _u32(q_idx), len(q_idx), _u32(p_idx), len(p_idx),
-                                                                  dnum, rank, world))
+        if lifted:
+            # ModRaise plan: q_idx = target primes + the prime the final rescale drops; one lifted digit
+            ctx.lib.check(ctx.lib.dll.cerium_keyswitch_create_lifted(ctx.h, C.byref(h), bconv_mode, round_mode,
+                                                                     _u32(q_idx), len(q_idx), _u32(p_idx), len(p_idx)))
+        else:
+            ctx.lib.check(ctx.lib.dll.cerium_keyswitch_create_sharded(ctx.h, C.byref(h), bconv_mode, round_mode,
+                                                                      _u32(q_idx), len(q_idx), _u32(p_idx), len(p_idx),
+                                                                      dnum, rank, world))
         self.h = h
+
+    def mod_raise(self, out0: int, out1: int, c0: int, c1: int, base0: int, base1: int, evk: int, stream: int = 0):
+        self.ctx.lib.check(self.ctx.lib.dll.cerium_mod_raise(self.h, out0, out1, c0, c1, base0, base1, evk, stream))
 
     @property
     def local_limbs(self) -> int:

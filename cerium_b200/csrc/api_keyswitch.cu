@@ -41,6 +41,9 @@ struct cerium_keyswitch {
   // digit's limb (slot ntt_src[b] of the gathered buffer); no converters exist then
   bool direct_raise = false;
   std::vector<uint32_t> ntt_src;
+  // lifted plan (ModRaise): one digit whose value arrives as an exact integer and is reduced modulo
+  // every prime of the plan by the caller of keyswitch_inner_moddown; no converters, no own limbs
+  bool lifted = false;
   std::vector<uint32_t> ext_pos, ext_prime;  // extension limbs of both accumulators
   // exact mode: per-limb scalars folded into the inverse transforms (device, one word per entry)
   void* d_scale = nullptr;  // [L] then [2K]: scale, and at +count their Shoup companions
@@ -68,8 +71,10 @@ W* ws_at(const cerium_keyswitch* ks, size_t off_words) {
 // Drops the last limb of n_polys polynomials stored back to back in `in` ([n_polys][L][N]);
 // polynomial p goes to outs[p] ([L-1][N]).  Two polynomials share a launch pair when their
 // results are adjacent in memory or `pair_work` (a [2(L-1)][N] stack) is given.
+// addend0 (optional, [L-1][N]) is added to polynomial 0.
 int rescale_impl(cerium_context* ctx, int round_mode, void* const* outs, void* pair_work, const void* in,
-                 const uint32_t* q_idx, int L, int n_polys, void* scratch, cudaStream_t stream) {
+                 const uint32_t* q_idx, int L, int n_polys, void* scratch, cudaStream_t stream,
+                 const void* addend0 = nullptr) {
   const size_t n = kN;
   const size_t wb = ctx->word_bytes();
   const size_t limb = n * wb;
@@ -110,6 +115,10 @@ int rescale_impl(cerium_context* ctx, int round_mode, void* const* outs, void* p
     s.dst_stride = n;
     s.minuend = static_cast<const char*>(in) + (size_t)p * L * limb;
     s.minuend_stride = n;
+    if (p == 0 && addend0 != nullptr) {
+      s.addend = addend0;
+      s.addend_stride = n;
+    }
     s.prime = prime2.data();
     s.factor = factor.data();
     s.reduce_src = true;
@@ -306,6 +315,7 @@ int keyswitch_finish(cerium_keyswitch* ks, void* out0, void* out1, const void* g
 int keyswitch_impl(cerium_keyswitch* ks, void* out0, void* out1, const void* cpoly, const void* evk,
                    const void* add0, const void* add1, cudaStream_t stream) {
   if (ks->world != 1) return fail(CERIUM_ERR_INVALID, "keyswitch: a sharded plan needs the begin / finish calls around the all-gather");
+  if (ks->lifted) return fail(CERIUM_ERR_INVALID, "keyswitch: a lifted plan only serves cerium_mod_raise");
   void* coef = static_cast<char*>(ks->ws) + ks->o_coef * ks->ctx->word_bytes();
   if (int rc = keyswitch_begin(ks, coef, cpoly, stream)) return rc;
   return keyswitch_finish(ks, out0, out1, coef, cpoly, evk, add0, add1, stream);
@@ -317,7 +327,7 @@ extern "C" {
 
 static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, int bconv_mode, int round_mode,
                                  const uint32_t* q_idx, int Lg, const uint32_t* p_idx, int K, int dnum, int rank,
-                                 int world) {
+                                 int world, bool lifted = false) {
   if (!ctx || !out || !q_idx || !p_idx) return fail(CERIUM_ERR_INVALID, "keyswitch_create: null argument");
   if (bconv_mode != CERIUM_BCONV_LAZY && bconv_mode != CERIUM_BCONV_EXACT) return fail(CERIUM_ERR_INVALID, "keyswitch_create: unknown bconv mode");
   if (round_mode != CERIUM_ROUND_FLOOR && round_mode != CERIUM_ROUND_HALF) return fail(CERIUM_ERR_INVALID, "keyswitch_create: unknown round mode");
@@ -325,7 +335,7 @@ static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, in
   if (world < 1 || rank < 0 || rank >= world) return fail(CERIUM_ERR_INVALID, "keyswitch_create: need 0 <= rank < world");
   if (Lg + K > kEwMaxLimbs || Lg > 64) return fail(CERIUM_ERR_UNSUPPORTED, "keyswitch_create: too many limbs (L <= 64, L + K <= 128)");
   const int alpha = (Lg + dnum - 1) / dnum;
-  if (alpha > K) return fail(CERIUM_ERR_INVALID, "keyswitch_create: digit size exceeds the number of extension primes");
+  if (alpha > K && !lifted) return fail(CERIUM_ERR_INVALID, "keyswitch_create: digit size exceeds the number of extension primes");
   if ((size_t)dnum * (Lg + K) > 0xffff) return fail(CERIUM_ERR_UNSUPPORTED, "keyswitch_create: dnum * (L + K) too large");
   std::vector<bool> seen(ctx->n_primes, false);
   for (int i = 0; i < Lg + K; i++) {
@@ -363,7 +373,8 @@ static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, in
   ks->all_idx = ks->q_idx;
   ks->all_idx.insert(ks->all_idx.end(), ks->p_idx.begin(), ks->p_idx.end());
   const int LK = ks->LK;
-  for (int e = 0; e < LK; e++) ks->own_digit.push_back(e < L ? ks->loc[e] % dnum : -1);
+  ks->lifted = lifted;
+  for (int e = 0; e < LK; e++) ks->own_digit.push_back((e < L && !lifted) ? ks->loc[e] % dnum : -1);
   const int bits = ctx->word_bits;
   const bool exact = bconv_mode == CERIUM_BCONV_EXACT;
   std::vector<uint64_t> scale_q(std::max(L, 1), 1), scale_p(2 * K, 1);
@@ -372,7 +383,7 @@ static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, in
   int rc = CERIUM_OK;
   // per-digit converters: inputs = global limbs {d, d+dnum, ...} (read from the gathered buffer),
   // outputs = every local extended limb outside the digit
-  for (int d = 0; d < dnum && rc == CERIUM_OK; d++) {
+  for (int d = 0; d < dnum && rc == CERIUM_OK && !lifted; d++) {
     std::vector<uint32_t> in_primes, in_pos, out_primes, out_pos;
     std::vector<int> in_limb;
     for (int i = d; i < Lg; i += dnum) {
@@ -503,6 +514,56 @@ int cerium_keyswitch_create_sharded(cerium_context* ctx, cerium_keyswitch** out,
   return keyswitch_create_impl(ctx, out, bconv_mode, round_mode, q_idx, L, p_idx, K, dnum, rank, world);
 }
 
+int cerium_keyswitch_create_lifted(cerium_context* ctx, cerium_keyswitch** out, int bconv_mode, int round_mode,
+                                   const uint32_t* q_idx, int L, const uint32_t* p_idx, int K) {
+  if (L < 4) return fail(CERIUM_ERR_INVALID, "keyswitch_create_lifted: need L >= 4");
+  return keyswitch_create_impl(ctx, out, bconv_mode, round_mode, q_idx, L, p_idx, K, 1, 0, 1, /*lifted=*/true);
+}
+
+int cerium_mod_raise(cerium_keyswitch* ks, void* out0, void* out1, const void* c0, const void* c1, uint32_t base0,
+                     uint32_t base1, const void* evk, void* stream) {
+  if (!ks || !out0 || !out1 || !c0 || !c1 || !evk) return fail(CERIUM_ERR_INVALID, "mod_raise: null argument");
+  if (!ks->lifted) return fail(CERIUM_ERR_INVALID, "mod_raise: the plan was not made by cerium_keyswitch_create_lifted");
+  cerium_context* ctx = ks->ctx;
+  if (base0 >= (uint32_t)ctx->n_primes || base1 >= (uint32_t)ctx->n_primes || base0 == base1)
+    return fail(CERIUM_ERR_INVALID, "mod_raise: need two different base primes of the context");
+  DeviceGuard guard(ctx->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t n = kN, wb = ctx->word_bytes(), limb = n * wb;
+  const int L = ks->L, LK = ks->LK, Lt = L - 1;
+  char* ws = static_cast<char*>(ks->ws);
+  char* tmp = ws + ks->o_conv * wb;     // 8 limbs, free until the ModDown: [c0b0 c0b1 c1b0 c1b1 | lo0 hi0 lo1 hi1]
+  char* t6 = ws + ks->o_tmp * wb;       // [Lt] the lifted c0
+  char* raised = ws + ks->o_raised * wb;
+  char* kso = ws + ks->o_ksout * wb;
+  // 1. the four input limbs to coefficient form
+  for (int k = 0; k < 2; k++) {
+    const uint32_t prime[2] = {base0, base1};
+    NttCall c{k == 0 ? c0 : c1, tmp + (size_t)2 * k * limb, n, n, nullptr, prime, 2};
+    if (int rc = launch_ntt_inverse(ctx, c, nullptr, nullptr, st)) return rc;
+  }
+  // 2. exact CRT of each polynomial's pair of limbs: integers in [0, q_base0 * q_base1)
+  if (int rc = cerium_resolve2(ctx, tmp + 4 * limb, tmp + 5 * limb, tmp, tmp + limb, 2 * n, base0, base1, 2, stream)) return rc;
+  // 3. c0 lifted to the target primes
+  if (int rc = cerium_mod2(ctx, t6, n, tmp + 4 * limb, tmp + 5 * limb, ks->q_idx.data(), Lt, stream)) return rc;
+  {
+    NttCall c{t6, t6, n, n, nullptr, ks->q_idx.data(), Lt};
+    if (int rc = launch_ntt_forward(ctx, c, st)) return rc;
+  }
+  // 4. c1 lifted to every prime of the plan: the one digit of the key switch
+  if (int rc = cerium_mod2(ctx, raised, n, tmp + 6 * limb, tmp + 7 * limb, ks->all_idx.data(), LK, stream)) return rc;
+  {
+    NttCall c{raised, raised, n, n, nullptr, ks->all_idx.data(), LK};
+    if (int rc = launch_ntt_forward(ctx, c, st, /*lazy_out=*/true)) return rc;
+  }
+  // 5-6. product with the key, ModDown
+  if (int rc = keyswitch_inner_moddown(ks, kso, kso + (size_t)L * limb, nullptr, evk, nullptr, nullptr, st)) return rc;
+  // 7-8. drop the plan's last Q limb; add the lifted c0
+  void* outs[2] = {out0, out1};
+  void* scratch = ws + ks->o_scratch * wb;
+  return rescale_impl(ctx, ks->round_mode, outs, tmp, kso, ks->q_idx.data(), L, 2, scratch, st, t6);
+}
+
 int cerium_keyswitch_local_limbs(const cerium_keyswitch* ks) { return ks ? ks->L : 0; }
 int cerium_keyswitch_gather_limbs(const cerium_keyswitch* ks) { return ks ? ks->gather_limbs : 0; }
 
@@ -565,6 +626,7 @@ int cerium_hrot(cerium_keyswitch* ks, void* out0, void* out1, const void* c0, co
 int cerium_hoisted_begin(cerium_keyswitch* ks, const void* c1, void* stream) {
   if (!ks || !c1) return fail(CERIUM_ERR_INVALID, "hoisted_begin: null argument");
   if (ks->world != 1) return fail(CERIUM_ERR_INVALID, "hoisted_begin: sharded plans are driven through the begin / finish calls");
+  if (ks->lifted) return fail(CERIUM_ERR_INVALID, "hoisted_begin: a lifted plan only serves cerium_mod_raise");
   DeviceGuard guard(ks->ctx->device);
   void* coef = static_cast<char*>(ks->ws) + ks->o_coef * ks->ctx->word_bytes();
   if (int rc = keyswitch_begin(ks, coef, c1, (cudaStream_t)stream)) return rc;

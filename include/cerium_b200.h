@@ -284,6 +284,24 @@ CERIUM_API int cerium_rescale(cerium_context *ctx, int round_mode, void *out, co
                    const uint32_t *q_idx, int L, int n_polys, void *scratch, void *stream);
 
 /*
+ * Bootstrap ModRaise (cerium/compiler/backend/compiler_rescale.cc:32-207): a ciphertext with the
+ * two limbs base0, base1 is lifted to the primes of a larger basis.  Each polynomial's pair of
+ * limbs is composed to the exact integer in [0, q_base0 * q_base1) (INTT, Resolve); c0's integer
+ * is reduced modulo the target primes (Mod, NTT); c1's integer is reduced modulo EVERY prime of
+ * the plan (Q and P), multiplied with the bootstrap key (one digit), taken through ModDown by P
+ * and rescaled by the plan's last Q prime; out0 = that + lifted c0, out1 = the other half.
+ *   plan: cerium_keyswitch_create_lifted over q_idx[0..L) (the L-1 target primes followed by the
+ *         prime the final rescale drops) and the K extension primes; no other call accepts it;
+ *   c0, c1: [2][N] (limb base0, limb base1), NTT form;  evk: [1][2][L+K][N];
+ *   out0, out1: [L-1][N].
+ */
+CERIUM_API int cerium_keyswitch_create_lifted(cerium_context *ctx, cerium_keyswitch **out, int bconv_mode,
+                                   int round_mode, const uint32_t *q_idx, int L,
+                                   const uint32_t *p_idx, int K);
+CERIUM_API int cerium_mod_raise(cerium_keyswitch *ks, void *out0, void *out1, const void *c0, const void *c1,
+                     uint32_t base0, uint32_t base1, const void *evk, void *stream);
+
+/*
  * Double rescale: drops the last TWO limbs of n_polys polynomials at once (floor division by
  * q_{L-2} * q_{L-1}); in is [n_polys][L][N] in NTT form, out is [n_polys][L-2][N], scratch holds
  * 4 * n_polys limbs.  Restates double_rescale (cerium/compiler/backend/compiler_rescale.cc:

@@ -80,6 +80,8 @@ def lib():
                                     C.c_int, _u64p, _u64p, _u64p, _u64p]
         L.orc_rescale.argtypes = [C.c_void_p, C.c_int, C.c_int, _u32p, _u64p, _u64p]
         L.orc_double_rescale.argtypes = [C.c_void_p, C.c_int, _u32p, _u64p, _u64p]
+        L.orc_mod_raise.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, _u32p, C.c_int, _u32p, C.c_uint32,
+                                    C.c_uint32, _u64p, _u64p, _u64p, _u64p, _u64p]
         L.orc_hrot.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, _u32p, C.c_int, _u32p,
                                C.c_int, C.c_uint32, _u64p, _u64p, _u64p, _u64p, _u64p]
         L.orc_hmult_relin.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, _u32p,
@@ -183,6 +185,16 @@ class OracleContext:
         out = np.empty((len(qi) - 1, self.n), dtype=np.uint64)
         lib().orc_rescale(self._h, round_mode, len(qi), _p32(qi), _p64(cpoly), _p64(out))
         return out
+
+    def mod_raise(self, bconv_mode, round_mode, q_idx, p_idx, base0, base1, c0, c1, evk):
+        """Bootstrap ModRaise: (c0, c1) with limbs (base0, base1) -> two polynomials of len(q_idx) - 1 limbs."""
+        qi, pi = _idx(q_idx), _idx(p_idx)
+        c0, c1, evk = _c64(c0), _c64(c1), _c64(evk)
+        o0 = np.empty((len(qi) - 1, self.n), dtype=np.uint64)
+        o1 = np.empty((len(qi) - 1, self.n), dtype=np.uint64)
+        lib().orc_mod_raise(self._h, bconv_mode, round_mode, len(qi), _p32(qi), len(pi), _p32(pi), int(base0),
+                            int(base1), _p64(c0), _p64(c1), _p64(evk), _p64(o0), _p64(o1))
+        return o0, o1
 
     def double_rescale(self, q_idx, cpoly) -> np.ndarray:
         """Drops the last two limbs at once (floor division by their product)."""

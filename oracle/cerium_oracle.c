@@ -672,6 +672,60 @@ ORC_API void orc_double_rescale(const orc_ctx *c, int L, const uint32_t *q_idx, 
 }
 
 /*
+ * Bootstrap ModRaise (cerium/compiler/backend/compiler_rescale.cc:32-207).  (c0, c1): two limbs
+ * each (primes b0, b1), NTT form.  q_idx[0..L): L-1 target primes and the prime the final
+ * rescale drops; p_idx[0..K): extension primes; evk: [2][L+K][N] (one digit).
+ *   v0, v1 = exact CRT lifts of c0, c1 (INTT + Resolve);  t = NTT(v0 mod q_i), i < L-1;
+ *   r_j = NTT(v1 mod m_j) for every prime m_j of Q and P;  (a0, a1) = (r * evk0, r * evk1);
+ *   ModDown by P;  rescale by q_{L-1};  out0 = rescaled0 + t,  out1 = rescaled1.
+ */
+ORC_API void orc_mod_raise(const orc_ctx *c, int bconv_mode, int round_mode, int L, const uint32_t *q_idx,
+                           int K, const uint32_t *p_idx, uint32_t b0, uint32_t b1, const u64 *c0, const u64 *c1,
+                           const u64 *evk, u64 *out0, u64 *out1) {
+  size_t n = c->n;
+  int LK = L + K, Lt = L - 1;
+  u64 m0 = c->p[b0].q, m1 = c->p[b1].q;
+  u64 *x = (u64 *)malloc(4 * n * sizeof(u64));
+  u64 *lohi = (u64 *)malloc(4 * n * sizeof(u64));
+  memcpy(x, c0, 2 * n * sizeof(u64));
+  memcpy(x + 2 * n, c1, 2 * n * sizeof(u64));
+  orc_ntt_inverse(c, (int)b0, x);
+  orc_ntt_inverse(c, (int)b1, x + n);
+  orc_ntt_inverse(c, (int)b0, x + 2 * n);
+  orc_ntt_inverse(c, (int)b1, x + 3 * n);
+  orc_resolve2(m0, m1, n, x, x + n, lohi, lohi + n);
+  orc_resolve2(m0, m1, n, x + 2 * n, x + 3 * n, lohi + 2 * n, lohi + 3 * n);
+  u64 *t = (u64 *)malloc((size_t)Lt * n * sizeof(u64));
+  for (int i = 0; i < Lt; i++) {
+    orc_mod2(c->p[q_idx[i]].q, n, lohi, lohi + n, t + (size_t)i * n);
+    orc_ntt_forward(c, (int)q_idx[i], t + (size_t)i * n);
+  }
+  u64 *acc0 = (u64 *)malloc((size_t)LK * n * sizeof(u64)), *acc1 = (u64 *)malloc((size_t)LK * n * sizeof(u64));
+  u64 *r = (u64 *)malloc(n * sizeof(u64));
+  for (int j = 0; j < LK; j++) {
+    int pj = (int)(j < L ? q_idx[j] : p_idx[j - L]);
+    u64 q = c->p[pj].q;
+    orc_mod2(q, n, lohi + 2 * n, lohi + 3 * n, r);
+    orc_ntt_forward(c, pj, r);
+    const u64 *k0 = evk + (size_t)j * n, *k1 = evk + (size_t)(LK + j) * n;
+    for (size_t i = 0; i < n; i++) {
+      acc0[(size_t)j * n + i] = orc_mulmod(r[i], k0[i], q);
+      acc1[(size_t)j * n + i] = orc_mulmod(r[i], k1[i], q);
+    }
+  }
+  u64 *d0 = (u64 *)malloc((size_t)L * n * sizeof(u64)), *d1 = (u64 *)malloc((size_t)L * n * sizeof(u64));
+  orc_moddown(c, bconv_mode, round_mode, L, q_idx, K, p_idx, acc0, acc0 + (size_t)L * n, d0);
+  orc_moddown(c, bconv_mode, round_mode, L, q_idx, K, p_idx, acc1, acc1 + (size_t)L * n, d1);
+  orc_rescale(c, round_mode, L, q_idx, d0, out0);
+  orc_rescale(c, round_mode, L, q_idx, d1, out1);
+  for (int i = 0; i < Lt; i++) {
+    u64 q = c->p[q_idx[i]].q;
+    for (size_t k = 0; k < n; k++) out0[(size_t)i * n + k] = addmod(out0[(size_t)i * n + k], t[(size_t)i * n + k], q);
+  }
+  free(x); free(lohi); free(t); free(acc0); free(acc1); free(r); free(d0); free(d1);
+}
+
+/*
  * HRot: rotate (c0,c1) by Galois element elt and key-switch back.
  * Restates rotate_internal (cerium/compiler/backend/compiler.cc:701-726):
  * automorphism of both polynomials in NTT form, key switch of the rotated c1,

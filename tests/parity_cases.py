@@ -257,6 +257,36 @@ def case_rescale(be, word_bits, round_mode, L=4, n_polys=2):
     assert np.array_equal(h.down(out), want)
 
 
+def case_mod_raise(be, word_bits, bconv_mode, round_mode, Lt=4, K=2):
+    """Bootstrap ModRaise: two base limbs -> Lt target limbs through an exact lift, a one-digit key
+    switch over Lt + 1 + K limbs, ModDown and a rescale."""
+    if word_bits == 32:
+        mods = moduli_for(32, Lt + 1 + K)
+        q_idx, p_idx = list(range(Lt + 1)), list(range(Lt + 1, Lt + 1 + K))
+    else:
+        mods = moduli_for(64, Lt + 1 + K, K)          # the K 60-bit primes first
+        q_idx, p_idx = list(range(K, K + Lt + 1)), list(range(K))
+    h = Harness(be, word_bits, mods)
+    rng = np.random.default_rng(33)
+    base = [q_idx[0], q_idx[1]]                        # the level-2 ciphertext lives on the first two primes
+    c0, c1 = rand_limbs(rng, mods, base), rand_limbs(rng, mods, base)
+    evk = np.stack([rand_limbs(rng, mods, q_idx + p_idx) for _ in range(2)])
+    ks = _capi.KeySwitch(h.ctx, q_idx, p_idx, 1, bconv_mode, round_mode, lifted=True)
+    o0, o1 = h.new(Lt, N), h.new(Lt, N)
+    d0, d1, dk = h.up(c0), h.up(c1), h.up(evk)
+    ks.mod_raise(h.p(o0), h.p(o1), h.p(d0), h.p(d1), base[0], base[1], h.p(dk))
+    w0, w1 = h.orc.mod_raise(bconv_mode, round_mode, q_idx, p_idx, base[0], base[1], c0, c1, evk)
+    assert np.array_equal(h.down(o0), w0), "ModRaise c0 differs"
+    assert np.array_equal(h.down(o1), w1), "ModRaise c1 differs"
+    # a lifted plan serves nothing else
+    try:
+        ks.apply(h.p(o0), h.p(o1), h.p(o0), h.p(dk))
+    except _capi.CeriumError:
+        pass
+    else:
+        raise AssertionError("a lifted plan accepted an ordinary key switch")
+
+
 def case_double_rescale(be, word_bits, L=5, n_polys=3):
     """Two limbs dropped at once (INTT x2, Resolve, Mod, SuD); one pair of polynomials and a single."""
     mods = moduli_for(word_bits, L, 1)

@@ -63,6 +63,11 @@ def test_keyswitch_hrot_hmult(be, word_bits, L, K, dnum, bm, rm):
     pc.case_keyswitch(be, word_bits, L, K, dnum, bm, rm)
 
 
+@pytest.mark.parametrize("word_bits,bm,rm", [(64, _capi.BCONV_EXACT, _capi.ROUND_HALF), (32, _capi.BCONV_LAZY, _capi.ROUND_FLOOR)])
+def test_mod_raise(be, word_bits, bm, rm):
+    pc.case_mod_raise(be, word_bits, bm, rm)
+
+
 @pytest.mark.parametrize("word_bits", [32, 64])
 def test_double_rescale(be, word_bits):
     pc.case_double_rescale(be, word_bits)

@@ -167,3 +167,40 @@ def test_double_rescale_vs_bigint_division():
     for c in range(n):
         want = T[c] // (q[2] * q[3])
         assert [int(v) for v in got[:, c]] == [want % q[0], want % q[1]]
+
+
+def test_mod_raise_with_a_noiseless_key_is_exact():
+    """ModRaise pinned on integers: with the key (P * q_drop * s', 0) and no noise every step is an
+    exact division, so out0 = NTT(v0 + v1 (*) s') and out1 = 0, where v0, v1 are the integers the two
+    base limbs compose to and (*) is the negacyclic product over the integers."""
+    logn = 4
+    n = 1 << logn
+    q = params.ntt_primes_below(50, 4, logn)          # base = q[0], q[1]; targets q[0..2]; q[3] is dropped
+    p = params.ntt_primes_below(60, 2, logn)
+    mods = q + p
+    ctx = oracle.OracleContext(logn, mods)
+    q_idx, p_idx = [0, 1, 2, 3], [4, 5]
+    rng = np.random.default_rng(11)
+    B01 = q[0] * q[1]
+    V0 = [int(rng.integers(0, 2**62)) * int(rng.integers(0, 2**40)) % B01 for _ in range(n)]
+    V1 = [int(rng.integers(0, 2**62)) * int(rng.integers(0, 2**40)) % B01 for _ in range(n)]
+    V1[0] = B01 - 1
+    s = [int(v) for v in rng.integers(-1, 2, size=n)]
+    # negacyclic product over the integers
+    Z = [0] * n
+    for i in range(n):
+        for j in range(n):
+            k = i + j
+            Z[k % n] += V1[i] * s[j] * (1 if k < n else -1)
+
+    def limbs(poly, idx):
+        return ctx.ntt_forward(np.array([[c % mods[i] for c in poly] for i in idx], dtype=np.uint64), idx)
+
+    c0, c1 = limbs(V0, [0, 1]), limbs(V1, [0, 1])
+    P = p[0] * p[1]
+    key = [P * q[3] * c for c in s]
+    evk = np.stack([limbs(key, q_idx + p_idx), np.zeros((6, n), dtype=np.uint64)])
+    o0, o1 = ctx.mod_raise(oracle.BCONV_EXACT, oracle.ROUND_FLOOR, q_idx, p_idx, 0, 1, c0, c1, evk)
+    want = limbs([a + b for a, b in zip(V0, Z)], [0, 1, 2])
+    assert np.array_equal(o0, want)
+    assert not o1.any()
