@@ -66,6 +66,8 @@ SIGNATURES = {
                                                  C.POINTER(C.c_uint32), C.c_int, C.POINTER(C.c_uint32), C.c_int]),
     "cerium_mod_raise": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32,
                                    C.c_void_p, C.c_void_p]),
+    "cerium_rescale_local": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32), C.c_int,
+                                       C.c_uint32, C.c_void_p, C.c_int, C.c_void_p]),
     "cerium_double_rescale": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32), C.c_int, C.c_int,
                                         C.c_void_p, C.c_void_p]),
     "cerium_probe_int_pipe": (C.c_int, [C.c_int, C.POINTER(C.c_double), C.c_int]),
@@ -208,6 +210,12 @@ class Context:
         self.lib.check(self.lib.dll.cerium_rescale(self.h, round_mode, out, inp, _u32(q_idx), len(q_idx), n_polys,
                                                    scratch, stream))
 
+
+    def rescale_local(self, out: int, inp: int, local_idx: Sequence[int], last_prime: int, last_coef: int,
+                      n_polys: int, round_mode: int = ROUND_FLOOR, stream: int = 0):
+        """Rescale of one rank's remaining limbs against the broadcast coefficient-form last limb."""
+        self.lib.check(self.lib.dll.cerium_rescale_local(self.h, round_mode, out, inp, _u32(local_idx), len(local_idx),
+                                                         last_prime, last_coef, n_polys, stream))
 
     def double_rescale(self, out: int, inp: int, q_idx: Sequence[int], n_polys: int, scratch: int, stream: int = 0):
         """Drops the last two limbs at once; scratch holds 4 * n_polys limbs."""

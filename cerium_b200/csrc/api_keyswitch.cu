@@ -72,19 +72,22 @@ W* ws_at(const cerium_keyswitch* ks, size_t off_words) {
 // polynomial p goes to outs[p] ([L-1][N]).  Two polynomials share a launch pair when their
 // results are adjacent in memory or `pair_work` (a [2(L-1)][N] stack) is given.
 // addend0 (optional, [L-1][N]) is added to polynomial 0.
+// have_last: `scratch` already holds the coefficient-form last limbs (another rank produced them)
+// and `in` is [n_polys][L-1][N], the remaining limbs only.
 int rescale_impl(cerium_context* ctx, int round_mode, void* const* outs, void* pair_work, const void* in,
                  const uint32_t* q_idx, int L, int n_polys, void* scratch, cudaStream_t stream,
-                 const void* addend0 = nullptr) {
+                 const void* addend0 = nullptr, bool have_last = false) {
   const size_t n = kN;
   const size_t wb = ctx->word_bytes();
   const size_t limb = n * wb;
   const uint32_t last = q_idx[L - 1];
   const uint64_t ql = ctx->moduli[last];
   const int R = L - 1;
+  const int in_limbs = have_last ? R : L;  // limbs per polynomial in `in`
   // 1. inverse transform of the last limb of every polynomial -> scratch[poly][N]
   std::vector<uint32_t> pos(n_polys), prime(n_polys, last);
   for (int p = 0; p < n_polys; p++) pos[p] = (uint32_t)p;
-  {
+  if (!have_last) {
     // input limb of poly p sits at in + (p*L + L-1)*N: base shifted to the first such limb, stride L*N
     NttCall c{};
     c.in = static_cast<const char*>(in) + (size_t)R * limb;
@@ -113,7 +116,7 @@ int rescale_impl(cerium_context* ctx, int round_mode, void* const* outs, void* p
     s.work_stride = n;
     s.dst = outs[p];
     s.dst_stride = n;
-    s.minuend = static_cast<const char*>(in) + (size_t)p * L * limb;
+    s.minuend = static_cast<const char*>(in) + (size_t)p * in_limbs * limb;
     s.minuend_stride = n;
     if (p == 0 && addend0 != nullptr) {
       s.addend = addend0;
@@ -133,7 +136,7 @@ int rescale_impl(cerium_context* ctx, int round_mode, void* const* outs, void* p
       s.count = 2 * R;
       s.split = R;
       s.dst2 = outs[p + 1];
-      s.minuend2 = static_cast<const char*>(in) + (size_t)(p + 1) * L * limb;
+      s.minuend2 = static_cast<const char*>(in) + (size_t)(p + 1) * in_limbs * limb;
       p += 2;
     } else {
       s.src_stride = 0;
@@ -689,6 +692,25 @@ int cerium_rescale(cerium_context* ctx, int round_mode, void* out, const void* i
   std::vector<void*> outs(n_polys);
   for (int p = 0; p < n_polys; p++) outs[p] = static_cast<char*>(out) + (size_t)p * (L - 1) * kN * ctx->word_bytes();
   return rescale_impl(ctx, round_mode, outs.data(), nullptr, in, q_idx, L, n_polys, scratch, (cudaStream_t)stream);
+}
+
+int cerium_rescale_local(cerium_context* ctx, int round_mode, void* out, const void* in, const uint32_t* local_idx,
+                         int n_local, uint32_t last_prime, const void* last_coef, int n_polys, void* stream) {
+  if (!ctx || !out || !in || !local_idx || !last_coef) return fail(CERIUM_ERR_INVALID, "rescale_local: null argument");
+  if (round_mode != CERIUM_ROUND_FLOOR && round_mode != CERIUM_ROUND_HALF) return fail(CERIUM_ERR_INVALID, "rescale_local: unknown round mode");
+  if (n_local < 1 || n_local > 64) return fail(CERIUM_ERR_INVALID, "rescale_local: need 1 <= n_local <= 64");
+  if (n_polys < 1 || n_polys > 4096) return fail(CERIUM_ERR_INVALID, "rescale_local: need 1 <= n_polys <= 4096");
+  if (last_prime >= (uint32_t)ctx->n_primes) return fail(CERIUM_ERR_INVALID, "rescale_local: prime index out of range");
+  std::vector<uint32_t> idx(local_idx, local_idx + n_local);
+  for (uint32_t i : idx)
+    if (i >= (uint32_t)ctx->n_primes || i == last_prime) return fail(CERIUM_ERR_INVALID, "rescale_local: bad local prime index");
+  if (((uintptr_t)out | (uintptr_t)in | (uintptr_t)last_coef) & 15u) return fail(CERIUM_ERR_INVALID, "rescale_local: pointers must be 16-byte aligned");
+  idx.push_back(last_prime);
+  DeviceGuard guard(ctx->device);
+  std::vector<void*> outs(n_polys);
+  for (int p = 0; p < n_polys; p++) outs[p] = static_cast<char*>(out) + (size_t)p * n_local * kN * ctx->word_bytes();
+  return rescale_impl(ctx, round_mode, outs.data(), nullptr, in, idx.data(), n_local + 1, n_polys,
+                      const_cast<void*>(last_coef), (cudaStream_t)stream, nullptr, /*have_last=*/true);
 }
 
 int cerium_double_rescale(cerium_context* ctx, void* out, const void* in, const uint32_t* q_idx, int L, int n_polys,

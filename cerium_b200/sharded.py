@@ -88,3 +88,33 @@ class ShardedKeySwitch:
             self.keyswitch(out0, out1, r1, evk, add0=r0)
         else:
             self.keyswitch(out0, out1, c1, evk)
+
+
+def sharded_rescale(ctx: _capi.Context, q_idx: List[int], local: torch.Tensor, rank: int, world: int,
+                    round_mode: int = _capi.ROUND_FLOOR, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """Rescale of a limb-sharded ciphertext (cerium/compiler/backend/compiler_rescale.cc:209-284 with
+    ``current_partition_size > 1``): the owner of the last limb inverse-transforms it and broadcasts
+    the coefficient-form residues, every rank divides its remaining limbs.
+
+    local: [n_polys, n_local, N], this rank's limbs of every polynomial (round robin over q_idx).
+    Returns [n_polys, n_local', N] with the last limb gone (n_local' = n_local - 1 on its owner).
+    """
+    L = len(q_idx)
+    n_polys = local.shape[0]
+    owner = (L - 1) % world
+    mine = local_limb_indices(L, rank, world)
+    stream = torch.cuda.current_stream().cuda_stream if local.device.type == "cuda" else 0
+    last = torch.empty((n_polys, ctx.n), dtype=local.dtype, device=local.device)
+    if rank == owner:
+        src = local[:, -1].contiguous()                      # limb L-1 is the owner's last local limb
+        ctx.ntt_inverse(last.data_ptr(), src.data_ptr(), [q_idx[L - 1]] * n_polys, stream=stream)
+    if world > 1:
+        dist.broadcast(last, src=owner, group=group)
+    keep = [i for i in mine if i != L - 1]
+    if not keep:
+        return local[:, :0].contiguous()
+    rest = local[:, :len(keep)].contiguous()
+    out = torch.empty_like(rest)
+    ctx.rescale_local(out.data_ptr(), rest.data_ptr(), [q_idx[i] for i in keep], q_idx[L - 1], last.data_ptr(),
+                      n_polys, round_mode, stream)
+    return out

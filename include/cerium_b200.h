@@ -284,6 +284,18 @@ CERIUM_API int cerium_rescale(cerium_context *ctx, int round_mode, void *out, co
                    const uint32_t *q_idx, int L, int n_polys, void *scratch, void *stream);
 
 /*
+ * Rescale of the limbs ONE rank owns when a ciphertext is sharded by limb: the rank that owns the
+ * dropped limb inverse-transforms it (cerium_ntt_inverse) and broadcasts the coefficient-form
+ * residues ([n_polys][N], last_coef here); every rank then calls this on its remaining limbs
+ * (in, out: [n_polys][n_local][N], primes local_idx[0..n_local), none equal to last_prime).
+ * Same arithmetic as cerium_rescale; the exchange is the reference's DRM of the last limb
+ * (cerium/compiler/backend/compiler_rescale.cc:262-273).
+ */
+CERIUM_API int cerium_rescale_local(cerium_context *ctx, int round_mode, void *out, const void *in,
+                         const uint32_t *local_idx, int n_local, uint32_t last_prime,
+                         const void *last_coef, int n_polys, void *stream);
+
+/*
  * Bootstrap ModRaise (cerium/compiler/backend/compiler_rescale.cc:32-207): a ciphertext with the
  * two limbs base0, base1 is lifted to the primes of a larger basis.  Each polynomial's pair of
  * limbs is composed to the exact integer in [0, q_base0 * q_base1) (INTT, Resolve); c0's integer

@@ -48,6 +48,16 @@ def _worker(rank, world, port, ret):
                 sharded.shard_key(tevk, L, rank, world), elt)
     torch.cuda.synchronize()
     ok = bool(torch.equal(o0, f0[mine]) and torch.equal(o1, f1[mine]))
+    # sharded rescale (broadcast of the last limb) against the one-GPU rescale
+    full = torch.stack([f0, f1])
+    one = torch.empty((2, L - 1, pc.N), dtype=torch.int64, device=dev)
+    scratch = torch.empty((2, pc.N), dtype=torch.int64, device=dev)
+    ctx.rescale(one.data_ptr(), full.data_ptr(), prm.q_idx, 2, scratch.data_ptr(), _capi.ROUND_FLOOR,
+                torch.cuda.current_stream().cuda_stream)
+    res = sharded.sharded_rescale(ctx, prm.q_idx, torch.stack([o0, o1]), rank, world)
+    torch.cuda.synchronize()
+    keep = [i for i in mine if i != L - 1]
+    ok = ok and bool(torch.equal(res, one[:, keep]))
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     ret[rank] = int(flag.item())

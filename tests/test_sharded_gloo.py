@@ -66,6 +66,14 @@ def _worker(rank, world, port, word_bits, L, K, dnum, bconv_mode, round_mode, re
         if mine:
             ok &= np.array_equal(o0.numpy().view(u)[:len(mine)].astype(np.uint64), want_rot[0][mine])
             ok &= np.array_equal(o1.numpy().view(u)[:len(mine)].astype(np.uint64), want_rot[1][mine])
+        # rescale of the sharded rotation result against the one-device oracle
+        rot = torch.stack([o0[:len(mine)], o1[:len(mine)]]) if mine else torch.zeros((2, 0, pc.N), dtype=tdt)
+        res = sharded.sharded_rescale(ctx, prm.q_idx, rot, rank, world, round_mode)
+        keep = [i for i in mine if i != L - 1]
+        for p_ in range(2):
+            want_rs = octx.rescale(round_mode, prm.q_idx, want_rot[p_])
+            if keep:
+                ok &= np.array_equal(res[p_].numpy().view(u).astype(np.uint64), want_rs[keep])
         flag = torch.tensor([1 if ok else 0])
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         ret[rank] = int(flag.item())
