@@ -10,6 +10,7 @@ already resident in HBM:
          metric: key-switch ops/s                                            [default]
   hmult  one HMult + relinearise + rescale, L=24 (60-bit first prime, 50-bit rest), K=1, dnum=24
   ntt    forward + inverse NTT of 48 limbs x 8 polynomials of 50-bit primes
+  hoisted  eight rotations of one ciphertext sharing one ModUp (HRot parameters); rotations/s
 With N > 1 ranks (torchrun) every rank runs the same workload on its own ciphertexts
 (independent ciphertexts, no data-path collective): weak scaling, value = all ranks' ops / max
 time over ranks.  For hrot the same operation is also timed limb-sharded over all ranks
@@ -405,7 +406,55 @@ class NttWorkload(Workload):
         return self.ops_per_step / dt, "forward+inverse NTT of 384 limbs, oracle port (Harvey lazy butterflies), OpenMP over limbs"
 
 
-WORKLOADS = {"hrot": HRotWorkload, "hmult": HMultWorkload, "ntt": NttWorkload}
+class HoistedWorkload(HRotWorkload):
+    """Eight rotations of one ciphertext that share the ModUp (hoisting, the baby steps of a BSGS
+    matrix-vector product: cerium/compiler/backend/compiler.cc:958-1153): one cerium_hoisted_begin,
+    then per rotation inner product + ModDown + automorphism with a pre-permuted key."""
+    name = "hoisted_8_rotations_N65536_L35_K5_dnum7_u64"
+    metric = "hoisted_rotations_per_s"
+    unit = "rotations/s"
+    ops_per_step = 8
+
+    def setup(self, lib, torch, rank, world=1, sharded=False):
+        super().setup(lib, torch, rank, world, False)
+        prm = self.prm
+        gen = torch.Generator(device="cuda").manual_seed(0xCE210013 + rank)
+        all_idx = prm.q_idx + prm.p_idx
+        self.evks = [self.evk] + [_rand_limbs_gpu(torch, prm.moduli, all_idx, (prm.dnum, 2), gen)
+                                  for _ in range(self.ops_per_step - 1)]
+        self.elts = [lib.galois_elt_from_step(1 << k, LOGN) for k in range(self.ops_per_step)]
+        self.houts = [torch.empty_like(self.cts[0]) for _ in range(self.ops_per_step)]
+        self.alg_bytes = (2 * prm.L + self.ops_per_step * (prm.dnum * 2 * (prm.L + prm.K) + 2 * prm.L)) * N * 8
+        self.gpu_launches_per_step = 5 + self.ops_per_step * 10
+
+    def _run(self, ct, outs, stream):
+        self.ks.hoisted_begin(ct[1].data_ptr(), stream)
+        for k in range(self.ops_per_step):
+            o = outs[k]
+            self.ks.hoisted_rotate(o[0].data_ptr(), o[1].data_ptr(), ct[0].data_ptr(), ct[1].data_ptr(),
+                                   self.evks[k].data_ptr(), self.elts[k], stream)
+
+    def step(self):
+        k = self.i % self.n_cts
+        self.i += 1
+        self._run(self.cts[k], self.houts, self.torch.cuda.current_stream().cuda_stream)
+
+    def e2e_step(self):
+        if getattr(self, "pipe", None) is None:
+            from cerium_b200.host_pipeline import HostPipeline
+
+            def op(ins, outs, stream):
+                self._run(ins[0], outs, stream)
+            self.pipe = HostPipeline(self.torch, [self.cts[0].shape], [self.cts[0].shape] * self.ops_per_step, op)
+        self.pipe.submit([self.host_in])
+        return self.pipe.in_bytes, self.pipe.out_bytes
+
+    def cpu_sample(self, orc_mod):
+        v, sample = super().cpu_sample(orc_mod)
+        return v, sample + " (one plain rotation; the CPU port does not hoist)"
+
+
+WORKLOADS = {"hrot": HRotWorkload, "hmult": HMultWorkload, "ntt": NttWorkload, "hoisted": HoistedWorkload}
 
 
 # ---------------------------------------------------------------------------------------
