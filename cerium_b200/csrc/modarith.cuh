@@ -290,20 +290,11 @@ __device__ __forceinline__ uint64_t fp_to_u64(double x) {
   return (uint64_t)__double_as_longlong(__dadd_rn(x, kFpTwo52)) & 0x000fffffffffffffull;
 }
 
-// Shoup product for the strict butterflies, in [0, 2q) for any word x.  64-bit words take the
-// 32-bit-piece product (below 4q) and one conditional subtraction: 9 multiply-pipe instructions
-// and a compare/select instead of the ~17 of mul.hi.u64 + two mul.lo.u64.
-template <typename W>
-__device__ __forceinline__ W mul_shoup_strict(W x, W w, W ws, W q, W q2) {
-  if (sizeof(W) == 8) return csub<W>(mul_shoup_approx(x, w, ws, (W)0 - q), q2);
-  return mul_shoup_lazy<W>(x, w, ws, q);
-}
-
 // Harvey forward butterfly: a, b in [0, 4q) -> [0, 4q).
 template <typename W>
 __device__ __forceinline__ void butterfly_fwd(W& a, W& b, W w, W ws, W q, W q2) {
   W u = csub<W>(a, q2);
-  W v = mul_shoup_strict<W>(b, w, ws, q, q2);
+  W v = mul_shoup_lazy<W>(b, w, ws, q);
   a = u + v;
   b = u + q2 - v;
 }
@@ -314,7 +305,7 @@ __device__ __forceinline__ void butterfly_inv(W& a, W& b, W w, W ws, W q, W q2) 
   W s = csub<W>(a + b, q2);
   W d = a + q2 - b;
   a = s;
-  b = mul_shoup_strict<W>(d, w, ws, q, q2);
+  b = mul_shoup_lazy<W>(d, w, ws, q);
 }
 
 }  // namespace cerium

@@ -132,8 +132,8 @@ struct Arith {
       a = csub<W>(csub<W>(mul_shoup_approx(s, pc.ninv, pc.ninv_shoup, nq), q2), q);
       b = csub<W>(csub<W>(mul_shoup_approx(d, pc.w1ninv, pc.w1ninv_shoup, nq), q2), q);
     } else {
-      a = csub<W>(mul_shoup_strict<W>(s, pc.ninv, pc.ninv_shoup, q, q2), q);
-      b = csub<W>(mul_shoup_strict<W>(d, pc.w1ninv, pc.w1ninv_shoup, q, q2), q);
+      a = csub<W>(mul_shoup_lazy<W>(s, pc.ninv, pc.ninv_shoup, q), q);
+      b = csub<W>(mul_shoup_lazy<W>(d, pc.w1ninv, pc.w1ninv_shoup, q), q);
     }
   }
 };
