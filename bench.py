@@ -191,8 +191,8 @@ class HRotWorkload(Workload):
         self.host_in = torch.empty(self.cts[0].shape, dtype=torch.int64).pin_memory()
         self.host_in.copy_(self.cts[0].cpu())
         self.host_out = torch.empty(self.cts[0].shape, dtype=torch.int64).pin_memory()
-        # automorph x2, iNTT pair, BConv, NTT pair, inner product x2, iNTT pair, BConv, SuD pair
-        self.gpu_launches_per_step = 2 + 2 + 1 + 2 + 2 + 2 + 1 + 2
+        # automorphism (both polynomials), iNTT pair, BConv, NTT pair, inner product, iNTT pair, BConv, SuD pair
+        self.gpu_launches_per_step = 1 + 2 + 1 + 2 + 1 + 2 + 1 + 2
 
     def _hrot(self, ct, out):
         if self.sharded:
@@ -296,7 +296,9 @@ class HMultWorkload(Workload):
         self.host_in[0].copy_(self.a.cpu())
         self.host_in[1].copy_(self.b.cpu())
         self.host_out = torch.empty(self.out.shape, dtype=torch.int64).pin_memory()
-        self.gpu_launches_per_step = 1 + 13 + 2 * 4
+        # tensor; key switch: iNTT pair, NTT pair x2 (576 limbs in two batches), inner product, iNTT pair,
+        # BConv, SuD pair; rescale of both polynomials: iNTT pair, SuD pair
+        self.gpu_launches_per_step = 1 + (2 + 4 + 1 + 2 + 1 + 2) + 4
 
     def step(self):
         s = self.torch.cuda.current_stream().cuda_stream
@@ -425,7 +427,8 @@ class HoistedWorkload(HRotWorkload):
         self.elts = [lib.galois_elt_from_step(1 << k, LOGN) for k in range(self.ops_per_step)]
         self.houts = [torch.empty_like(self.cts[0]) for _ in range(self.ops_per_step)]
         self.alg_bytes = (2 * prm.L + self.ops_per_step * (prm.dnum * 2 * (prm.L + prm.K) + 2 * prm.L)) * N * 8
-        self.gpu_launches_per_step = 5 + self.ops_per_step * 10
+        # begin: iNTT pair, BConv, NTT pair; per rotation: inner product, iNTT pair, BConv, SuD pair, automorphism
+        self.gpu_launches_per_step = 5 + self.ops_per_step * 7
 
     def _run(self, ct, outs, stream):
         self.ks.hoisted_begin(ct[1].data_ptr(), stream)

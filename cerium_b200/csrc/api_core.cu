@@ -812,12 +812,37 @@ int cerium_automorph(cerium_context* ctx, void* out, size_t out_stride, const vo
     AutomorphArgs<W> g{};
     g.out = {static_cast<W*>(out), out_stride};
     g.in = {const_cast<W*>(static_cast<const W*>(in)), in_stride};
+    g.split = count;
     g.elt = galois_elt;
     { auto kfn = automorph_kernel<W>; CERIUM_LAUNCH(kfn, dim3(kN / kEwThreads, count), kEwThreads, 0, (cudaStream_t)stream, g); }
     CERIUM_LAUNCH_CHECK("automorph");
     return CERIUM_OK;
   });
 }
+
+}  // extern "C"
+
+namespace cerium {
+// Automorphism of two polynomials of `count` limbs each (stride N) in one launch.
+int launch_automorph_pair(cerium_context* ctx, void* out_a, const void* in_a, void* out_b, const void* in_b,
+                          uint32_t galois_elt, int count, cudaStream_t stream) {
+  return dispatch_word(ctx->word_bits, [&](auto tag) -> int {
+    using W = decltype(tag);
+    AutomorphArgs<W> g{};
+    g.out = {static_cast<W*>(out_a), (size_t)kN};
+    g.in = {const_cast<W*>(static_cast<const W*>(in_a)), (size_t)kN};
+    g.out2 = {static_cast<W*>(out_b), (size_t)kN};
+    g.in2 = {const_cast<W*>(static_cast<const W*>(in_b)), (size_t)kN};
+    g.split = count;
+    g.elt = galois_elt;
+    { auto kfn = automorph_kernel<W>; CERIUM_LAUNCH(kfn, dim3(kN / kEwThreads, 2 * count), kEwThreads, 0, stream, g); }
+    CERIUM_LAUNCH_CHECK("automorph");
+    return CERIUM_OK;
+  });
+}
+}  // namespace cerium
+
+extern "C" {
 
 int cerium_resolve2(cerium_context* ctx, void* lo, void* hi, const void* x0, const void* x1, size_t stride,
                     uint32_t prime0, uint32_t prime1, int count, void* stream) {

@@ -51,10 +51,6 @@ struct cerium_keyswitch {
   void* d_scale_q_shoup = nullptr;
   void* d_scale_p = nullptr;
   void* d_scale_p_shoup = nullptr;
-  // side stream: the extension limbs' inverse transform and base conversion (integer-bound)
-  // run next to the Q-limb inner product (HBM-bound)
-  cudaStream_t side = nullptr;
-  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   // workspace
   void* ws = nullptr;
   size_t ws_bytes = 0;
@@ -226,26 +222,14 @@ int keyswitch_inner_moddown(cerium_keyswitch* ks, void* out0, void* out1, const 
       }
       const PrimeConst<W>* pcs = static_cast<const PrimeConst<W>*>(ctx->d_pcs);
       const dim3 block(kEwThreads);
-      // The extension limbs and their ModDown preparation (inverse transform, conversion to the Q
-      // limbs) run on the side stream next to the Q-limb pass of the main stream.
-      const bool fork = ks->side != nullptr && L > 0;
-      cudaStream_t prep = fork ? ks->side : stream;
-      if (fork) {
-        CERIUM_CUDA(cudaEventRecord(ks->ev_fork, stream));
-        CERIUM_CUDA(cudaStreamWaitEvent(ks->side, ks->ev_fork, 0));
-      }
-      g.first_limb = L;
-      { auto kfn = inner_product_kernel<W>; CERIUM_LAUNCH(kfn, dim3(kN / (kEwThreads * V::kLanes), K), block, 0, prep, g, pcs); }
-      if (L > 0) {
-        g.first_limb = 0;
-        auto kfn = inner_product_kernel<W>;
-        CERIUM_LAUNCH(kfn, dim3(kN / (kEwThreads * V::kLanes), L), block, 0, stream, g, pcs);
-      }
+      // every local extended limb (Q and extension) in one launch
+      g.first_limb = 0;
+      { auto kfn = inner_product_kernel<W>; CERIUM_LAUNCH(kfn, dim3(kN / (kEwThreads * V::kLanes), LK), block, 0, stream, g, pcs); }
       CERIUM_LAUNCH_CHECK("inner_product");
       // 5. iNTT of the extension limbs of both accumulators, in place
       {
         NttCall c{acc, acc, n, n, ks->ext_pos.data(), ks->ext_prime.data(), 2 * K};
-        if (int rc = launch_ntt_inverse(ctx, c, ks->d_scale_p, ks->d_scale_p_shoup, prep)) return rc;
+        if (int rc = launch_ntt_inverse(ctx, c, ks->d_scale_p, ks->d_scale_p_shoup, stream)) return rc;
       }
       if (L == 0) return CERIUM_OK;  // a rank without Q limbs only feeds the gather
       // 6. ModDown base conversion P -> local Q limbs
@@ -254,11 +238,7 @@ int keyswitch_inner_moddown(cerium_keyswitch* ks, void* out0, void* out1, const 
             {ks->down, conv, n, acc + (size_t)L * n, n},
             {ks->down, conv + (size_t)L * n, n, acc + (size_t)(LK + L) * n, n},
         };
-        if (int rc = launch_bconv(ctx, calls, 2, prep)) return rc;
-      }
-      if (fork) {
-        CERIUM_CUDA(cudaEventRecord(ks->ev_join, ks->side));
-        CERIUM_CUDA(cudaStreamWaitEvent(stream, ks->ev_join, 0));
+        if (int rc = launch_bconv(ctx, calls, 2, stream)) return rc;
       }
     }
     // 7. SuD: out = (acc_Q - NTT(conv)) * P^-1 (+ add); both polynomials in one launch pair
@@ -492,16 +472,6 @@ static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, in
     cerium_keyswitch_destroy(ks);
     return fail(CERIUM_ERR_CUDA, "keyswitch_create: cannot allocate the workspace");
   }
-  // highest priority: the side stream's few CTAs take SM slots as the bandwidth-bound kernel on the
-  // caller's stream releases them, instead of queueing behind its whole grid
-  int prio_lo = 0, prio_hi = 0;
-  cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi);
-  if (cudaStreamCreateWithPriority(&ks->side, cudaStreamNonBlocking, prio_hi) != cudaSuccess ||
-      cudaEventCreateWithFlags(&ks->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
-      cudaEventCreateWithFlags(&ks->ev_join, cudaEventDisableTiming) != cudaSuccess) {
-    cerium_keyswitch_destroy(ks);
-    return fail(CERIUM_ERR_CUDA, "keyswitch_create: cannot create the side stream");
-  }
   *out = ks;
   return CERIUM_OK;
 }
@@ -593,9 +563,6 @@ int cerium_keyswitch_destroy(cerium_keyswitch* ks) {
   if (ks->down) cerium_bconv_destroy(ks->down);
   cudaFree(ks->d_scale);
   cudaFree(ks->ws);
-  if (ks->side) cudaStreamDestroy(ks->side);
-  if (ks->ev_fork) cudaEventDestroy(ks->ev_fork);
-  if (ks->ev_join) cudaEventDestroy(ks->ev_join);
   delete ks;
   return CERIUM_OK;
 }
@@ -621,8 +588,8 @@ int cerium_hrot(cerium_keyswitch* ks, void* out0, void* out1, const void* c0, co
   char* tmp = static_cast<char*>(ks->ws) + ks->o_tmp * wb;
   void* rot0 = tmp;
   void* rot1 = tmp + (size_t)ks->L * n * wb;
-  if (int rc = cerium_automorph(ctx, rot0, n, c0, n, galois_elt, ks->L, stream)) return rc;
-  if (int rc = cerium_automorph(ctx, rot1, n, c1, n, galois_elt, ks->L, stream)) return rc;
+  if (((uintptr_t)c0 | (uintptr_t)c1) & 15u) return fail(CERIUM_ERR_INVALID, "hrot: pointers must be 16-byte aligned");
+  if (int rc = launch_automorph_pair(ctx, rot0, c0, rot1, c1, galois_elt, ks->L, (cudaStream_t)stream)) return rc;
   return keyswitch_impl(ks, out0, out1, rot1, evk, rot0, nullptr, (cudaStream_t)stream);
 }
 
@@ -650,8 +617,8 @@ int cerium_hoisted_rotate(cerium_keyswitch* ks, void* out0, void* out1, const vo
   void* t1 = tmp + (size_t)ks->L * n * wb;
   // (t0, t1) = KeySwitch(c1) + (c0, 0) on the un-rotated digits, then the automorphism
   if (int rc = keyswitch_inner_moddown(ks, t0, t1, c1, evk_pre, c0, nullptr, (cudaStream_t)stream)) return rc;
-  if (int rc = cerium_automorph(ctx, out0, n, t0, n, galois_elt, ks->L, stream)) return rc;
-  return cerium_automorph(ctx, out1, n, t1, n, galois_elt, ks->L, stream);
+  if (((uintptr_t)out0 | (uintptr_t)out1) & 15u) return fail(CERIUM_ERR_INVALID, "hoisted_rotate: pointers must be 16-byte aligned");
+  return launch_automorph_pair(ctx, out0, t0, out1, t1, galois_elt, ks->L, (cudaStream_t)stream);
 }
 
 int cerium_hmult(cerium_keyswitch* ks, void* out0, void* out1, const void* a0, const void* a1, const void* b0,

@@ -164,6 +164,8 @@ __device__ __forceinline__ uint32_t galois_source_index(uint32_t i, uint32_t elt
 template <typename W>
 struct AutomorphArgs {
   Limbs<W> out, in;
+  Limbs<W> out2, in2;  // entries b >= split: limb b - split of a second polynomial (same launch)
+  int split;
   uint32_t elt;
 };
 
@@ -174,7 +176,9 @@ __global__ void __launch_bounds__(kEwThreads) automorph_kernel(const AutomorphAr
   grid_dependency_wait();
   const int b = blockIdx.y;
   const uint32_t i = blockIdx.x * kEwThreads + threadIdx.x;
-  *g.out.at(b, (int)i) = *g.in.at(b, (int)galois_source_index(i, g.elt));
+  const uint32_t src = galois_source_index(i, g.elt);
+  if (b < g.split) *g.out.at(b, (int)i) = *g.in.at(b, (int)src);
+  else *g.out2.at(b - g.split, (int)i) = *g.in2.at(b - g.split, (int)src);
 }
 
 // Exact CRT composition of two limbs into a two-word integer ("resolve") and its reduction

@@ -205,5 +205,7 @@ struct SudCall {
   const uint32_t* src_pos = nullptr;
 };
 int launch_sud(cerium_context* ctx, const SudCall& c, cudaStream_t stream);
+int launch_automorph_pair(cerium_context* ctx, void* out_a, const void* in_a, void* out_b, const void* in_b,
+                          uint32_t galois_elt, int count, cudaStream_t stream);
 
 }  // namespace cerium
