@@ -102,6 +102,36 @@ def case_ntt(be, word_bits, n_limbs=3, sixty=1):
     h.ctx.ntt_forward(h.p(d_y), h.p(d_y), [])
 
 
+def case_ntt_fp_extremes(be):
+    """Primes just below 2^50 (the least headroom of the double-precision butterflies) on inputs
+    made of extreme residues; forward and inverse against the oracle, and the round trip."""
+    mods = params.ntt_primes_below(50, 3, LOGN)
+    assert all((1 << 49) < q < (1 << 50) for q in mods)
+    h = Harness(be, 64, mods)
+    rng = np.random.default_rng(77)
+    rows, idx = [], []
+    for p, q in enumerate(mods):
+        a = np.full(N, q - 1, dtype=np.uint64)
+        b = np.full(N, (q - 1) // 2, dtype=np.uint64)
+        c = np.where(np.arange(N) % 2 == 0, q - 1, 0).astype(np.uint64)
+        d = np.where(rng.integers(0, 2, size=N) == 0, q - 1, 1).astype(np.uint64)
+        e = np.zeros(N, dtype=np.uint64)
+        e[0] = q - 1
+        for r in (a, b, c, d, e):
+            rows.append(r)
+            idx.append(p)
+    x = np.stack(rows)
+    dx = h.up(x)
+    out = h.new(len(idx), N)
+    h.ctx.ntt_forward(h.p(out), h.p(dx), idx)
+    f = h.down(out)
+    assert np.array_equal(f, h.orc.ntt_forward(x, idx)), "forward NTT of extreme inputs differs"
+    h.ctx.ntt_inverse(h.p(out), h.p(out), idx)
+    assert np.array_equal(h.down(out), x), "round trip of extreme inputs differs"
+    h.ctx.ntt_inverse(h.p(out), h.p(dx), idx)
+    assert np.array_equal(h.down(out), h.orc.ntt_inverse(x, idx)), "inverse NTT of extreme inputs differs"
+
+
 def case_ntt_ptrs(be, word_bits):
     """Pointer-table entry points (the reference launchers' layout), ragged limb placement."""
     mods = moduli_for(word_bits, 2, 0)
@@ -428,3 +458,12 @@ def case_errors(be, word_bits=64):
         _capi.KeySwitch(h.ctx, [0, 1], [1], 1)                    # prime used twice
     with pytest.raises(_capi.CeriumError):
         _capi.KeySwitch(h.ctx, [0], [1], 2)                       # dnum > L
+    with pytest.raises(_capi.CeriumError):
+        h.ctx.double_rescale(h.p(buf), h.p(buf), [0, 1], 1, h.p(buf))            # fewer than 3 limbs
+    with pytest.raises(_capi.CeriumError):
+        h.ctx.rescale_local(h.p(buf), h.p(buf), [0], 0, h.p(buf), 1)             # local prime = dropped prime
+    with pytest.raises(_capi.CeriumError):
+        _capi.KeySwitch(h.ctx, [0], [1], 1, lifted=True)                         # a lifted plan needs L >= 4
+    ks = _capi.KeySwitch(h.ctx, [0], [1], 1)
+    with pytest.raises(_capi.CeriumError):
+        ks.mod_raise(h.p(buf), h.p(buf), h.p(buf), h.p(buf), 0, 1, h.p(buf))     # not a lifted plan

@@ -18,6 +18,10 @@ def test_ntt(be, word_bits):
     pc.case_ntt(be, word_bits, n_limbs=2)
 
 
+def test_ntt_fp_extremes(be):
+    pc.case_ntt_fp_extremes(be)
+
+
 @pytest.mark.parametrize("word_bits", [32, 64])
 def test_ntt_pointer_tables(be, word_bits):
     pc.case_ntt_ptrs(be, word_bits)
