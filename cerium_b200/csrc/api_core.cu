@@ -72,8 +72,11 @@ int launch_ntt_forward(cerium_context* ctx, const NttCall& c, cudaStream_t strea
           if (c.src_pos[first + b] > 0xffffu) return fail(CERIUM_ERR_INVALID, "limb slot exceeds 65535");
           gb.in_pos[b] = (uint16_t)c.src_pos[first + b];
         }
+        ModLoader<W> ml{};
+        for (int b = 0; b < cnt; b++)
+          ml.small[b] = (c.src_prime != nullptr && ctx->moduli[c.src_prime[first + b]] < ((uint64_t)1 << 50)) ? 1 : 0;
         auto kfn = ntt_fwd_cols_kernel<W, GatherBatch<W>, ModLoader<W>>;
-        CERIUM_LAUNCH(kfn, dim3(256 / kCols, cnt), kCols * 16, 0, stream, gb, ModLoader<W>{}, static_cast<const Pair*>(ctx->d_tw_fwd), static_cast<const PrimeConst<W>*>(ctx->d_pcs));
+        CERIUM_LAUNCH(kfn, dim3(256 / kCols, cnt), kCols * 16, 0, stream, gb, ml, static_cast<const Pair*>(ctx->d_tw_fwd), static_cast<const PrimeConst<W>*>(ctx->d_pcs));
       } else if (c.lazy_in) {
         auto kfn = ntt_fwd_cols_kernel<W, StridedBatch<W>, LazyLoader<W>>;
         CERIUM_LAUNCH(kfn, dim3(256 / kCols, cnt), kCols * 16, 0, stream, cols, LazyLoader<W>{}, static_cast<const Pair*>(ctx->d_tw_fwd), static_cast<const PrimeConst<W>*>(ctx->d_pcs));

@@ -40,7 +40,7 @@ struct cerium_keyswitch {
   // one-limb digits: the conversion is a plain reduction, done by the transform as it reads the
   // digit's limb (slot ntt_src[b] of the gathered buffer); no converters exist then
   bool direct_raise = false;
-  std::vector<uint32_t> ntt_src;
+  std::vector<uint32_t> ntt_src, ntt_src_prime;
   // lifted plan (ModRaise): one digit whose value arrives as an exact integer and is reduced modulo
   // every prime of the plan by the caller of keyswitch_inner_moddown; no converters, no own limbs
   bool lifted = false;
@@ -167,6 +167,7 @@ int keyswitch_raise(cerium_keyswitch* ks, const void* gathered, cudaStream_t str
     if (ks->direct_raise) {
       NttCall c{gathered, raised, n, n, ks->ntt_pos.data(), ks->ntt_prime.data(), (int)ks->ntt_pos.size()};
       c.src_pos = ks->ntt_src.data();
+      c.src_prime = ks->ntt_src_prime.data();
       return launch_ntt_forward(ctx, c, stream, /*lazy_out=*/true);
     }
     // 2. ModUp base conversion, every digit in one launch
@@ -381,6 +382,7 @@ static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, in
       ks->ntt_pos.push_back((uint32_t)(d * LK + e));
       ks->ntt_prime.push_back(ks->all_idx[e]);
       ks->ntt_src.push_back(slot_of(d));
+      ks->ntt_src_prime.push_back(q_idx[d]);
     }
     if (in_primes.empty() || out_primes.empty() || ks->direct_raise) continue;
     BconvOptions opt;

@@ -165,6 +165,8 @@ struct NttCall {
   // forward transform only: entry b reads limb src_pos[b] of `in`, residues of another modulus,
   // and reduces them to its own prime on the way in (null: reads limb pos[b], already reduced)
   const uint32_t* src_pos = nullptr;
+  // with src_pos: prime index of the modulus the words of entry b are residues of (null: unknown)
+  const uint32_t* src_prime = nullptr;
   // forward transform only: the input words are below 4q instead of canonical
   bool lazy_in = false;
 };

@@ -423,6 +423,7 @@ __device__ __forceinline__ uint4 vec_pack(const uint32_t* w) { return make_uint4
 // What the column pass does with a word it has just read.
 template <typename W>
 struct PlainLoader {
+  static constexpr bool kHasSmall = false;
   static constexpr int kFpBound = kFpCanon;
   __device__ __forceinline__ W apply(W x, int /*b*/, const PrimeConst<W>& /*pc*/) const { return x; }
 };
@@ -432,6 +433,11 @@ struct PlainLoader {
 template <typename W>
 struct ModLoader {
   static constexpr int kFpBound = kFpCanon;
+  static constexpr bool kHasSmall = true;
+  // small[b] != 0: the words of entry b are below 2^50 (their source prime is), so a prime with
+  // double-precision butterflies converts and reduces them on the FP64 pipe (5 operations)
+  // instead of the integer Shoup reduction
+  uint8_t small[kMaxBatch];
   __device__ __forceinline__ W apply(W x, int /*b*/, const PrimeConst<W>& pc) const {
     return reduce_word<W>(x, pc);
   }
@@ -440,6 +446,7 @@ struct ModLoader {
 // Words below 4q, as the ModUp base conversion leaves them for the transform.
 template <typename W>
 struct LazyLoader {
+  static constexpr bool kHasSmall = false;
   static constexpr int kFpBound = kFpLazyIn;
   __device__ __forceinline__ W apply(W x, int /*b*/, const PrimeConst<W>& /*pc*/) const { return x; }
 };
@@ -452,6 +459,7 @@ constexpr int kSudMaxBatch = 96;  // limbs per launch when per-limb scalars trav
 // (rescale, cerium/compiler/backend/compiler_rescale.cc:262-284).
 template <typename W>
 struct ReduceLoader {
+  static constexpr bool kHasSmall = false;
   static constexpr int kFpBound = kFpCanon;
   W src_q;
   W pre_add;
@@ -478,7 +486,19 @@ __device__ __forceinline__ void ntt_fwd_cols_body(const Batch& batch, const Load
   W* t_own = tile + (unsigned)(u * 16 * kCols + c);
   W x[16];
 #pragma unroll
-  for (int j = 0; j < 16; j++) x[j] = ar.enter(loader.apply(in[j * 16 * 256], b, pc));
+  for (int j = 0; j < 16; j++) x[j] = in[j * 16 * 256];
+  bool entered = false;
+  if constexpr (Loader::kHasSmall && kMode == kArithFp) {
+    if (loader.small[b] != 0) {
+#pragma unroll
+      for (int j = 0; j < 16; j++) x[j] = ar.reduce(ar.enter(x[j]));
+      entered = true;
+    }
+  }
+  if (!entered) {
+#pragma unroll
+    for (int j = 0; j < 16; j++) x[j] = ar.enter(loader.apply(x[j], b, pc));
+  }
   __syncthreads();
   radix16_fwd<W, false, kMode, false, Loader::kFpBound>(x, stw, 1u, ar);
 #pragma unroll
