@@ -139,3 +139,74 @@ def test_gpu_rotation_and_product_decrypt_correctly():
     got = ck.decrypt(be.to_host(r0), be.to_host(r1), scale * scale / q_last).real
     err = np.max(np.abs(got - x * y))
     assert np.allclose(got, x * y, rtol=1e-5, atol=1e-4), err
+
+
+def test_oracle_conjugation_decrypts_to_conjugated_slots():
+    """Step 0 is the conjugation (Galois element 2N - 1, cerium/runtime/math/galois.cpp:79-113):
+    the same rotate + key-switch path with the key for that element."""
+    prm = small_set(3, 2, 2)
+    ck = CkksRef(prm, seed=12)
+    rng = np.random.default_rng(5)
+    z = rng.uniform(-1, 1, N // 2) + 1j * rng.uniform(-1, 1, N // 2)
+    scale = 2.0 ** 40
+    c0, c1 = ck.encrypt(z, scale)
+    elt = oracle.galois_elt_from_step(0, LOGN)
+    assert elt == 2 * N - 1
+    evk = ck.rotation_key(elt)
+    o0, o1 = ck.octx.hrot(oracle.BCONV_EXACT, oracle.ROUND_HALF, prm.q_idx, prm.p_idx, prm.dnum, elt, c0, c1, evk)
+    assert np.allclose(ck.decrypt(o0, o1, scale), np.conj(z), rtol=1e-5, atol=1e-4)
+
+
+def _bsgs_case(be):
+    """Four generalised diagonals (steps 0..3) as baby steps {0, 1} x giant steps {0, 2}: the hoisted
+    baby rotation, the plaintext products, the giant rotation and the accumulation decrypt to
+    sum_k diag_k * roll(z, -k)."""
+    from cerium_b200 import _capi
+    from cerium_b200.bsgs import BsgsMultiplyAccumulate
+    prm = small_set(3, 2, 2)
+    ck = CkksRef(prm, seed=14)
+    rng = np.random.default_rng(9)
+    n_slots = N // 2
+    z = rng.uniform(-1, 1, n_slots)
+    diags = [rng.uniform(-1, 1, n_slots) for _ in range(4)]
+    scale = 2.0 ** 40
+    c0, c1 = ck.encrypt(z, scale)
+    g = 2
+    idx = list(prm.q_idx)
+
+    def plaintext(v):
+        m = ck.encode(v, scale)
+        return np.stack([ck.octx.ntt_forward(ck._signed_to_limb(m, p), [p])[0] for p in idx])
+
+    pts = [[plaintext(np.roll(diags[g * j + i], g * j)) for i in range(g)] for j in range(2)]
+    e1 = oracle.galois_elt_from_step(1, LOGN)
+    e2 = oracle.galois_elt_from_step(2, LOGN)
+    ctx = _capi.Context(be.lib, prm.moduli, 64)
+    ks = _capi.KeySwitch(ctx, prm.q_idx, prm.p_idx, prm.dnum, _capi.BCONV_EXACT, _capi.ROUND_HALF)
+    keep = []
+
+    def up(a):
+        b = be.to_dev(np.ascontiguousarray(a).astype(np.uint64))
+        keep.append(b)
+        return b
+
+    op = BsgsMultiplyAccumulate(ctx, ks, g, 2, lambda shape: be.empty(tuple(shape), np.uint64), be.ptr)
+    ct = up(np.stack([c0, c1]))
+    out = be.empty((2, prm.L, N), np.uint64)
+    op.run(out, ct, [[up(p) for p in row] for row in pts], [up(prepermuted_key(ck.rotation_key(e1), e1))],
+           [up(ck.rotation_key(e2))], [e1], [e2])
+    res = be.to_host(out)
+    want = sum(diags[k] * np.roll(z, -k) for k in range(4))
+    got = ck.decrypt(res[0], res[1], scale * scale).real
+    assert np.allclose(got, want, rtol=1e-5, atol=1e-4)
+
+
+def test_bsgs_multiply_accumulate_is_a_matrix_vector_product():
+    from tests.backends import EmuBackend
+    _bsgs_case(EmuBackend())
+
+
+@pytest.mark.gpu
+def test_gpu_bsgs_multiply_accumulate():
+    from tests.backends import CudaBackend
+    _bsgs_case(CudaBackend())
