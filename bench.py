@@ -11,6 +11,7 @@ already resident in HBM:
   hmult  one HMult + relinearise + rescale, L=24 (60-bit first prime, 50-bit rest), K=1, dnum=24
   ntt    forward + inverse NTT of 48 limbs x 8 polynomials of 50-bit primes
   hoisted  eight rotations of one ciphertext sharing one ModUp (HRot parameters); rotations/s
+  bsgs   one 8 x 8 baby-step / giant-step multiply-accumulate (64 diagonals, HRot parameters)
 With N > 1 ranks (torchrun) every rank runs the same workload on its own ciphertexts
 (independent ciphertexts, no data-path collective): weak scaling, value = all ranks' ops / max
 time over ranks.  For hrot the same operation is also timed limb-sharded over all ranks
@@ -457,7 +458,64 @@ class HoistedWorkload(HRotWorkload):
         return v, sample + " (one plain rotation; the CPU port does not hoist)"
 
 
-WORKLOADS = {"hrot": HRotWorkload, "hmult": HMultWorkload, "ntt": NttWorkload, "hoisted": HoistedWorkload}
+class BsgsWorkload(HRotWorkload):
+    """One BSGS multiply-accumulate with 8 baby x 8 giant steps (64 diagonals) on the HRot parameter
+    set: the linear-transform stage of bootstrapping (CoeffToSlot / SlotToCoeff,
+    cerium/compiler/backend/compiler.cc:2457-2822) through cerium_b200/bsgs.py: 7 hoisted baby
+    rotations, 64 plaintext multiply-accumulates on both polynomials, 7 giant-step rotations."""
+    name = "bsgs_8x8_N65536_L35_K5_dnum7_u64"
+    metric = "bsgs_linear_transforms_per_s"
+    unit = "transforms/s"
+    ops_per_step = 1
+    G = 8
+
+    def setup(self, lib, torch, rank, world=1, sharded=False):
+        super().setup(lib, torch, rank, world, False)
+        from cerium_b200.bsgs import BsgsMultiplyAccumulate
+        prm, G = self.prm, self.G
+        gen = torch.Generator(device="cuda").manual_seed(0xCE210023 + rank)
+        all_idx = prm.q_idx + prm.p_idx
+        key = lambda: _rand_limbs_gpu(torch, prm.moduli, all_idx, (prm.dnum, 2), gen)  # noqa: E731
+        self.baby_keys = [key() for _ in range(G - 1)]
+        self.giant_keys = [key() for _ in range(G - 1)]
+        self.baby_elts = [lib.galois_elt_from_step(i, LOGN) for i in range(1, G)]
+        self.giant_elts = [lib.galois_elt_from_step(G * j, LOGN) for j in range(1, G)]
+        self.pts = [[_rand_limbs_gpu(torch, prm.moduli, prm.q_idx, (), gen) for _ in range(G)] for _ in range(G)]
+        self.op = BsgsMultiplyAccumulate(self.ctx, self.ks, G, G,
+                                         lambda shape: torch.empty(tuple(shape), dtype=torch.int64, device="cuda"),
+                                         lambda t: t.data_ptr())
+        self.bout = torch.empty_like(self.cts[0])
+        limb = N * 8
+        # ciphertext in and out, 14 keys, 64 plaintexts
+        self.alg_bytes = (4 * prm.L + 2 * (G - 1) * prm.dnum * 2 * (prm.L + prm.K) + G * G * prm.L) * limb
+        self.gpu_launches_per_step = 5 + (G - 1) * 7 + G * G * 2 + (G - 1) * (12 + 2)
+
+    def _run(self, ct, out, stream):
+        self.op.run(out, ct, self.pts, self.baby_keys, self.giant_keys, self.baby_elts, self.giant_elts, stream)
+
+    def step(self):
+        k = self.i % self.n_cts
+        self.i += 1
+        self._run(self.cts[k], self.bout, self.torch.cuda.current_stream().cuda_stream)
+
+    def e2e_step(self):
+        if getattr(self, "pipe", None) is None:
+            from cerium_b200.host_pipeline import HostPipeline
+
+            def op(ins, outs, stream):
+                self._run(ins[0], outs[0], stream)
+            self.pipe = HostPipeline(self.torch, [self.cts[0].shape], [self.cts[0].shape], op)
+        self.pipe.submit([self.host_in])
+        return self.pipe.in_bytes, self.pipe.out_bytes
+
+    def cpu_sample(self, orc_mod):
+        v, sample = super().cpu_sample(orc_mod)
+        # 14 key switches dominate one transform on the CPU as well
+        return v / (2 * (self.G - 1)), sample + " (one rotation timed; a transform is counted as its 14 rotations)"
+
+
+WORKLOADS = {"hrot": HRotWorkload, "hmult": HMultWorkload, "ntt": NttWorkload, "hoisted": HoistedWorkload,
+             "bsgs": BsgsWorkload}
 
 
 # ---------------------------------------------------------------------------------------
