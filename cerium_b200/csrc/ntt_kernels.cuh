@@ -531,11 +531,20 @@ __global__ void __launch_bounds__(NttCfg<W>::kCols * 16, sizeof(W) == 8 ? 3 : 2)
   CERIUM_DISPATCH_ARITH(W, pc, ntt_fwd_cols_body, CERIUM_TARGS(Batch, Loader), (batch, loader, b, pc, tile, stw));
 }
 
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+#if !defined(CERIUM_EMU)
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+#else
+  (void)p;
+#endif
+}
+
 // What the row pass does with the finished NTT value.  kCanonicalInput says whether the
 // epilogue wants the value reduced to [0, q) first or takes it below 4q.
 template <typename W>
 struct StoreEpilogue {
   static constexpr bool kCanonicalInput = true;
+  __device__ __forceinline__ void prefetch(int /*b*/, int /*idx*/) const {}
   __device__ __forceinline__ W apply(W x, int /*b*/, int /*idx*/, uint32_t /*pi*/,
                                      const PrimeConst<W>& /*pc*/) const {
     return x;
@@ -547,6 +556,7 @@ struct StoreEpilogue {
 template <typename W>
 struct LazyStoreEpilogue {
   static constexpr bool kCanonicalInput = false;
+  __device__ __forceinline__ void prefetch(int /*b*/, int /*idx*/) const {}
   __device__ __forceinline__ W apply(W x, int /*b*/, int /*idx*/, uint32_t /*pi*/,
                                      const PrimeConst<W>& /*pc*/) const {
     return x;
@@ -568,6 +578,15 @@ struct SudEpilogue {
   int split;         // kSudMaxBatch when there is one polynomial
   W factor[kSudMaxBatch];
   W factor_shoup[kSudMaxBatch];
+  // starts the 16 bytes at word idx of the operands towards L2 (called before the transform, whose
+  // arithmetic then hides their latency)
+  __device__ __forceinline__ void prefetch(int b, int idx) const {
+    const bool second = b >= split;
+    const int e = second ? b - split : b;
+    prefetch_l2((second ? minuend2 : minuend) + (size_t)e * minuend_stride + idx);
+    const W* ap = second ? addend2 : addend;
+    if (ap != nullptr) prefetch_l2(ap + (size_t)e * addend_stride + idx);
+  }
   __device__ __forceinline__ W apply(W x, int b, int idx, uint32_t /*pi*/,
                                      const PrimeConst<W>& pc) const {
     const bool second = b >= split;
@@ -639,6 +658,8 @@ __device__ __forceinline__ void ntt_fwd_rows_body(const Batch& batch, const Epil
   W x[16];
 #pragma unroll
   for (int j = 0; j < 16; j++) x[j] = row[j * 16];
+#pragma unroll
+  for (int k = 0; k < RV::kPerThread; k++) epi.prefetch(b, h * 256 + (u + 16 * k) * RV::kWords);
   radix16_fwd<W, true, kMode, false, kFpFwdMid>(x, tw, 256u + (uint32_t)h, ar);
 #pragma unroll
   for (int j = 0; j < 16; j++) t_strided[j * 17] = x[j];
