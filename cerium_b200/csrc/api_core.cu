@@ -510,9 +510,23 @@ int cerium_context_create(cerium_context** out, int device, int log_n, int word_
           for (int g = 0; g < (1 << t); g++)
             for (int u = 0; u < 16; u++) {
               const size_t src = k * n + (((size_t)(4096 + 16 * h + u)) << t) + g;
-              const size_t dst = (size_t)k * kRowTwPerPrime + ((size_t)h * 15 + ((1 << t) - 1 + g)) * 16 + u;
-              rfwd[dst] = fwd[src];
-              rinv[dst] = inv[src];
+              if (fp) {
+                // twiddles only (the kernel computes their quotients), two per entry: double number
+                // 2^t + g of the group's 16 (see lane_tw_fp)
+                const int slot = (1 << t) + g;
+                const size_t dst = (size_t)k * kRowTwPerPrime + ((size_t)h * 8 + (slot >> 1)) * 16 + u;
+                if (slot & 1) {
+                  rfwd[dst].y = fwd[src].x;
+                  rinv[dst].y = inv[src].x;
+                } else {
+                  rfwd[dst].x = fwd[src].x;
+                  rinv[dst].x = inv[src].x;
+                }
+              } else {
+                const size_t dst = (size_t)k * kRowTwPerPrime + ((size_t)h * 15 + ((1 << t) - 1 + g)) * 16 + u;
+                rfwd[dst] = fwd[src];
+                rinv[dst] = inv[src];
+              }
             }
       PrimeConst<W>& pc = pcs[k];
       std::memset(&pc, 0, sizeof(pc));

@@ -151,6 +151,8 @@ struct Arith<uint64_t, kArithFp> {
   static __device__ __forceinline__ W u(double x) { return (W)__double_as_longlong(x); }
   __device__ __forceinline__ W enter(W x) const { return u(fp_from_u64(x)); }
   __device__ __forceinline__ W reduce(W x) const { return u(fp_reduce(d(x), qinv, nq)); }
+  // quotient of a twiddle by q when the table holds the twiddle alone
+  __device__ __forceinline__ W quotient(W w) const { return u(__dmul_rn(d(w), qinv)); }
   __device__ __forceinline__ void fwd(W& a, W& b, W w, W wq) const {
     const double r = fp_mulmod(d(b), d(w), d(wq), nq);
     const double x = d(a);
@@ -188,20 +190,25 @@ struct Arith<uint64_t, kArithFp> {
 constexpr int kFpCanon = 1024;       // canonical input, [0, q)
 constexpr int kFpReduced = 513;      // after fp_reduce
 constexpr int kFpOperandMax = 4096;  // operand of a product
-__host__ __device__ constexpr int fp_product_bound(int operand) { return 512 + (operand + 31) / 32; }
+// k32 = 1: the twiddle comes with its tabulated quotient RN(w / q); k32 = 3: the quotient is
+// computed as RN(w * RN(1 / q)) (last level of the row pass, whose table then holds w only), three
+// times the error: |r| <= q * (1/2 + 3 * operand / 32q)
+__host__ __device__ constexpr int fp_product_bound(int operand, int k32 = 1) {
+  return 512 + (k32 * operand + 31) / 32;
+}
 
 // forward (Cooley-Tukey): a' = a + w*b, b' = a - w*b; all 16 values share one bound
 struct FpFwdPlan {
   bool before[4];  // reduce every value before layer t
   int out;
 };
-__host__ __device__ constexpr FpFwdPlan fp_plan_fwd(int bin) {
+__host__ __device__ constexpr FpFwdPlan fp_plan_fwd(int bin, int k32 = 1) {
   FpFwdPlan p{};
   int b = bin;
   for (int t = 0; t < 4; t++) {
     p.before[t] = b > kFpOperandMax;
     if (p.before[t]) b = kFpReduced;
-    b += fp_product_bound(b);
+    b += fp_product_bound(b, k32);
   }
   p.out = b;
   return p;
@@ -214,7 +221,7 @@ struct FpInvPlan {
   int bound[16];
   int max_out;
 };
-__host__ __device__ constexpr FpInvPlan fp_plan_inv(int bin) {
+__host__ __device__ constexpr FpInvPlan fp_plan_inv(int bin, int k32 = 1) {
   FpInvPlan p{};
   for (int j = 0; j < 16; j++) p.bound[j] = bin;
   for (int t = 3; t >= 0; t--) {
@@ -235,7 +242,7 @@ __host__ __device__ constexpr FpInvPlan fp_plan_inv(int bin) {
         }
         const int sum = p.bound[j] + p.bound[i];
         p.bound[j] = sum;
-        p.bound[i] = fp_product_bound(sum);
+        p.bound[i] = fp_product_bound(sum, k32);
       }
     p.before[t] = mask;
   }
@@ -269,11 +276,13 @@ constexpr int kFpLazyIn = 4096;
 constexpr int kFpFwdMid = fp_plan_fwd(fp_plan_fwd(kFpLazyIn).out).out;
 static_assert(fp_plan_fwd(fp_plan_fwd(kFpCanon).out).out <= kFpFwdMid, "the lazy loader is the worst case");
 constexpr int kFpFwdL3 = fp_plan_fwd(kFpFwdMid).out;
+constexpr int kFpLaneK32 = 3;  // level 3 (lane table) computes its quotients
+static_assert(fp_plan_fwd(kFpFwdL3, kFpLaneK32).out < 8192, "the transform's last values must stay exact integers");
 // bounds along the inverse transform: row pass (levels 3, 2) stores kFpInvMid
-constexpr int kFpInvL3 = fp_plan_exchange(fp_plan_inv(kFpCanon), kFpInvExchangeMax).out;
+constexpr int kFpInvL3 = fp_plan_exchange(fp_plan_inv(kFpCanon, kFpLaneK32), kFpInvExchangeMax).out;
 constexpr int kFpInvMid = fp_plan_inv(kFpInvL3).max_out;
 constexpr int kFpInvL1 = fp_plan_exchange(fp_plan_inv(kFpInvMid), kFpInvExchangeMax).out;
-constexpr unsigned kFpInvRowsExMask = fp_plan_exchange(fp_plan_inv(kFpCanon), kFpInvExchangeMax).mask;
+constexpr unsigned kFpInvRowsExMask = fp_plan_exchange(fp_plan_inv(kFpCanon, kFpLaneK32), kFpInvExchangeMax).mask;
 constexpr unsigned kFpInvColsExMask = fp_plan_exchange(fp_plan_inv(kFpInvMid), kFpInvExchangeMax).mask;
 static_assert(kFpFwdMid < 8192 && kFpInvMid < 8192, "stored intermediates must stay exact integers");
 
@@ -303,23 +312,42 @@ __device__ __forceinline__ uint32_t tw_index(uint32_t S, int t, int g) {
   return kLaneTable ? (uint32_t)(((1 << t) - 1 + g) * 16) : (S << t) + (uint32_t)g;
 }
 
+// Lane-interleaved table of a prime with double-precision butterflies: twiddles only, two per
+// 16-byte entry; twiddle e = 2^t - 1 + g sits in double number e + 1 of the group's 16 (number 0
+// is padding, so that every layer starts on an entry boundary), entry v of thread u at (v * 16).
+template <typename W>
+__device__ __forceinline__ W lane_tw_fp(const typename WordTraits<W>::Pair* tw, int t, int g) {
+  const int slot = (1 << t) + g;
+  const auto pv = __ldg(tw + (slot >> 1) * 16);
+  return (slot & 1) ? pv.y : pv.x;
+}
+
 // Four forward layers on x[0..15]; layer t pairs (j, j + (8 >> t)).  kBin: bound of the inputs
 // (Fp arithmetic only).
 template <typename W, bool kGlobalTw, int kMode, bool kLaneTable = false, int kBin = 0>
 __device__ __forceinline__ void radix16_fwd(W (&x)[16], const typename WordTraits<W>::Pair* tw,
                                             uint32_t S, const Arith<W, kMode>& ar) {
-  constexpr FpFwdPlan plan = fp_plan_fwd(kBin);
+  constexpr bool kPacked = kLaneTable && kMode == kArithFp;
+  constexpr FpFwdPlan plan = fp_plan_fwd(kBin, kPacked ? kFpLaneK32 : 1);
 #pragma unroll
   for (int t = 0; t < 4; t++) {
     const int half = 8 >> t;
     if (kMode == kArithFp && plan.before[t]) fp_reduce_masked<W, kMode>(x, 0xffffu, ar);
 #pragma unroll
     for (int g = 0; g < (1 << t); g++) {
-      const auto w = load_tw<W, kGlobalTw>(tw, tw_index<kLaneTable>(S, t, g));
+      W w0, w1;
+      if constexpr (kPacked) {
+        w0 = lane_tw_fp<W>(tw, t, g);
+        w1 = ar.quotient(w0);
+      } else {
+        const auto w = load_tw<W, kGlobalTw>(tw, tw_index<kLaneTable>(S, t, g));
+        w0 = w.x;
+        w1 = w.y;
+      }
 #pragma unroll
       for (int k = 0; k < half; k++) {
         const int j = g * 2 * half + k;
-        ar.fwd(x[j], x[j + half], w.x, w.y);
+        ar.fwd(x[j], x[j + half], w0, w1);
       }
     }
   }
@@ -330,18 +358,27 @@ __device__ __forceinline__ void radix16_fwd(W (&x)[16], const typename WordTrait
 template <typename W, bool kGlobalTw, int kMode, int kLayer0, bool kLaneTable = false, int kBin = 0>
 __device__ __forceinline__ void radix16_inv(W (&x)[16], const typename WordTraits<W>::Pair* twi,
                                             uint32_t S, const Arith<W, kMode>& ar) {
-  constexpr FpInvPlan plan = fp_plan_inv(kBin);
+  constexpr bool kPacked = kLaneTable && kMode == kArithFp;
+  constexpr FpInvPlan plan = fp_plan_inv(kBin, kPacked ? kFpLaneK32 : 1);
 #pragma unroll
   for (int t = 3; t >= 0; t--) {
     const int half = 8 >> t;
     if (kMode == kArithFp) fp_reduce_masked<W, kMode>(x, plan.before[t], ar);
 #pragma unroll
     for (int g = 0; g < (1 << t); g++) {
-      const auto w = load_tw<W, kGlobalTw>(twi, tw_index<kLaneTable>(S, t, g));
+      W w0, w1;
+      if constexpr (kPacked) {
+        w0 = lane_tw_fp<W>(twi, t, g);
+        w1 = ar.quotient(w0);
+      } else {
+        const auto w = load_tw<W, kGlobalTw>(twi, tw_index<kLaneTable>(S, t, g));
+        w0 = w.x;
+        w1 = w.y;
+      }
 #pragma unroll
       for (int k = 0; k < half; k++) {
         const int j = g * 2 * half + k;
-        ar.inv(x[j], x[j + half], w.x, w.y, kLayer0 + 3 - t);
+        ar.inv(x[j], x[j + half], w0, w1, kLayer0 + 3 - t);
       }
     }
   }
@@ -667,7 +704,7 @@ __device__ __forceinline__ void ntt_fwd_rows_body(const Batch& batch, const Epil
 #pragma unroll
   for (int j = 0; j < 16; j++) x[j] = t_own[j];
   // level 3: this thread's 15 twiddles from the lane-interleaved table of row h
-  radix16_fwd<W, true, kMode, true, kFpFwdL3>(x, twr + ((size_t)h * 15 * 16 + u), 0u, ar);
+  radix16_fwd<W, true, kMode, true, kFpFwdL3>(x, twr + ((size_t)h * (kMode == kArithFp ? 8 : 15) * 16 + u), 0u, ar);
 #pragma unroll
   for (int j = 0; j < 16; j++) x[j] = ar.template finish_fwd<Epilogue::kCanonicalInput>(x[j], pc.one_shoup);
   // own 16 words -> swizzled vectors -> coalesced vectors, then epilogue and store
@@ -739,7 +776,7 @@ __device__ __forceinline__ void ntt_inv_rows_body(const Batch& batch, int b, con
     vec_unpack(vrow[row_vec_slot<W>(u * RV::kPerThread + jj)], &x[jj * RV::kWords]);
 #pragma unroll
   for (int j = 0; j < 16; j++) x[j] = ar.enter(x[j]);
-  radix16_inv<W, true, kMode, 0, true, kFpCanon>(x, twri + ((size_t)h * 15 * 16 + u), 0u, ar);
+  radix16_inv<W, true, kMode, 0, true, kFpCanon>(x, twri + ((size_t)h * (kMode == kArithFp ? 8 : 15) * 16 + u), 0u, ar);
   if (kMode == kArithFp) fp_reduce_masked<W, kMode>(x, kFpInvRowsExMask, ar);
   __syncwarp();
   W* t_own = trow + (unsigned)(u * 17);  // row_pos(u * 16 + j) = u * 17 + j
