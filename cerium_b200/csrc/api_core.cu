@@ -425,7 +425,25 @@ int launch_bconv(cerium_context* ctx, const BconvCall* calls, int count, cudaStr
           smem_opt_in[slot] = true;
         }
       }
-      { auto kfn = bconv_kernel<W>; /* grid.z splits the outputs until the launch has about 1000 CTAs (measured: 1024 beats 2048 and 4096) */ const int nz = std::max(1, std::min((1024 + 256 * cnt - 1) / (256 * cnt), (max_o + 3) / 4)); const int out_chunk = (max_o + nz - 1) / nz; CERIUM_LAUNCH(kfn, dim3(kN / kBconvThreads, cnt, (max_o + out_chunk - 1) / out_chunk), kBconvThreads, smem, stream, batch, out_chunk, static_cast<const PrimeConst<W>*>(ctx->d_pcs)); }
+      {
+        // grid.z splits the outputs of a conversion over nz CTAs (each reloads the inputs and restages its
+        // tables): take the nz in 1..4 with the best waves x per-CTA-work estimate on this GPU
+        auto kfn = bconv_kernel<W>;
+        const int slots = 5 * ctx->sm_count;
+        int nz = 1;
+        double best = 1e30;
+        for (int cand = 1; cand <= std::min(4, (max_o + 3) / 4); cand++) {
+          const int ctas = kBconvBlocks * cnt * cand;
+          const double cost = (double)((ctas + slots - 1) / slots) * (1.0 / cand + 0.15);
+          if (cost < best - 1e-9) {
+            best = cost;
+            nz = cand;
+          }
+        }
+        const int out_chunk = (max_o + nz - 1) / nz;
+        CERIUM_LAUNCH(kfn, dim3(kBconvBlocks, cnt, (max_o + out_chunk - 1) / out_chunk), kBconvThreads, smem, stream,
+                      batch, out_chunk, static_cast<const PrimeConst<W>*>(ctx->d_pcs));
+      }
     }
     CERIUM_LAUNCH_CHECK("bconv");
     return CERIUM_OK;
@@ -473,6 +491,10 @@ int cerium_context_create(cerium_context** out, int device, int log_n, int word_
   ctx->n_primes = n_moduli;
   ctx->moduli.assign(moduli, moduli + n_moduli);
   ctx->psi.resize(n_moduli);
+  if (cudaDeviceGetAttribute(&ctx->sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || ctx->sm_count < 1) {
+    delete ctx;
+    return fail(CERIUM_ERR_CUDA, "context_create: cannot read the number of SMs");
+  }
   if (const char* arith = std::getenv("CERIUM_B200_NTT_ARITH")) ctx->allow_fp = std::strcmp(arith, "int") != 0;
   const size_t n = kN;
   int rc = dispatch_word(word_bits, [&](auto tag) -> int {

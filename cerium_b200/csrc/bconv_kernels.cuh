@@ -20,7 +20,11 @@
 
 namespace cerium {
 
-constexpr int kBconvThreads = 256;
+// 160 threads: with the kernel's ~70 registers five CTAs fit an SM (740 slots on 148 SMs), and the
+// 7 x 410 CTAs of a ModUp over seven digits are 3.9 waves; 256-thread CTAs gave 4.04 waves of 444,
+// i.e. a fifth wave of 16 CTAs
+constexpr int kBconvThreads = 160;
+constexpr int kBconvBlocks = (kN + kBconvThreads - 1) / kBconvThreads;  // the last block is partial
 constexpr int kBconvRegInputs = 8;
 // grid.z splits the output primes of a conversion when the batch alone gives too few CTAs
 
@@ -226,7 +230,7 @@ __host__ __device__ inline size_t bconv_smem_bytes(int I, int O) {
 // dynamic smem = max bconv_smem_bytes over the batch.  CTA z handles outputs
 // [z * out_chunk, min(O, (z + 1) * out_chunk)) of its conversion.
 template <typename W>
-__global__ void __launch_bounds__(kBconvThreads)
+__global__ void __launch_bounds__(kBconvThreads, 5)
     bconv_kernel(const BconvBatch<W> batch, const int out_chunk, const PrimeConst<W>* __restrict__ pcs) {
   CERIUM_DYN_SMEM(smem_raw);
   grid_dependency_launch();
@@ -257,6 +261,7 @@ __global__ void __launch_bounds__(kBconvThreads)
   grid_dependency_wait();  // the tables above never change; the input limbs below come from the previous kernel
   __syncthreads();
   const int coeff = blockIdx.x * kBconvThreads + threadIdx.x;
+  if (coeff >= kN) return;  // partial last block (after the only barrier)
   if (sizeof(W) == 8 && I <= kBconvRegInputs) {
     const BconvDesc<uint64_t>& d64 = reinterpret_cast<const BconvDesc<uint64_t>&>(d);
     const PrimeConst<uint64_t>* p64 = reinterpret_cast<const PrimeConst<uint64_t>*>(pcs);

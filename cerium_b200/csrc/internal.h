@@ -101,6 +101,7 @@ struct cerium_context {
   // 64-bit primes below 2^50 transform on the FP64 pipe unless the environment variable
   // CERIUM_B200_NTT_ARITH is "int" when the context is created (for comparisons)
   bool allow_fp = true;
+  int sm_count = 1;  // SMs of the device (launch shapes are sized in multiples of it)
   std::vector<uint64_t> mu_hi, mu_lo;  // Barrett constants per prime (host copy)
   std::vector<uint8_t> fp_ok, lazy_ok; // arithmetic of each prime's transforms (host copy)
   size_t word_bytes() const { return (size_t)word_bits / 8; }
