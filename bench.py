@@ -192,8 +192,9 @@ class HRotWorkload(Workload):
         self.host_in = torch.empty(self.cts[0].shape, dtype=torch.int64).pin_memory()
         self.host_in.copy_(self.cts[0].cpu())
         self.host_out = torch.empty(self.cts[0].shape, dtype=torch.int64).pin_memory()
-        # automorphism (both polynomials), iNTT pair, BConv, NTT pair, inner product, iNTT pair, BConv, SuD pair
-        self.gpu_launches_per_step = 1 + 2 + 1 + 2 + 1 + 2 + 1 + 2
+        # iNTT pair, BConv, NTT pair, inner product, iNTT pair, BConv, SuD pair (the rotation itself is
+        # folded into the reads of the iNTT, the inner product and the SuD tail: no launch of its own)
+        self.gpu_launches_per_step = 2 + 1 + 2 + 1 + 2 + 1 + 2
 
     def _hrot(self, ct, out):
         if self.sharded:
@@ -488,7 +489,7 @@ class BsgsWorkload(HRotWorkload):
         limb = N * 8
         # ciphertext in and out, 14 keys, 64 plaintexts
         self.alg_bytes = (4 * prm.L + 2 * (G - 1) * prm.dnum * 2 * (prm.L + prm.K) + G * G * prm.L) * limb
-        self.gpu_launches_per_step = 5 + (G - 1) * 7 + G * G * 2 + (G - 1) * (12 + 2)
+        self.gpu_launches_per_step = 5 + (G - 1) * 7 + G * G * 2 + (G - 1) * (11 + 2)
 
     def _run(self, ct, out, stream):
         self.op.run(out, ct, self.pts, self.baby_keys, self.giant_keys, self.baby_elts, self.giant_elts, stream)

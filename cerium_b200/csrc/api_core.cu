@@ -112,6 +112,7 @@ int launch_ntt_inverse(cerium_context* ctx, const NttCall& c, const void* scale,
       sb.in_stride = c.in_stride;
       sb.out_stride = c.out_stride;
       sb.split = kMaxBatch;
+      sb.in_elt = c.in_galois;
       if (int rc = fill_batch<W>(ctx, sb, c.pos, c.prime, first, cnt)) return rc;
       InvScale<W> sc{};
       if (scale != nullptr) {
@@ -153,6 +154,7 @@ int launch_sud(cerium_context* ctx, const SudCall& c, cudaStream_t stream) {
       epi.minuend_stride = c.minuend_stride;
       epi.addend = c.addend ? static_cast<const W*>(c.addend) + (size_t)first * c.addend_stride : nullptr;
       epi.addend_stride = c.addend_stride;
+      epi.addend_elt = c.addend_galois;
       epi.split = kSudMaxBatch;
       if (c.split > 0) {
         // second polynomial: entry b lands at slot b - split of dst2 (the slot number itself stays b,

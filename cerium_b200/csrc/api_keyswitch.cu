@@ -147,9 +147,13 @@ int rescale_impl(cerium_context* ctx, int round_mode, void* const* outs, void* p
 
 // Step 1: inverse transform of the local limbs of the switched polynomial into `dst`
 // ([gather_limbs][N]; exact mode: times [Qhat_i^-1] of the limb's digit).
-int keyswitch_begin(cerium_keyswitch* ks, void* dst, const void* cpoly, cudaStream_t stream) {
+// pre_elt (here and below), not 0: the key switch runs on the Galois automorphism of this element
+// applied to cpoly and to add0 / add1, which are read through the index map wherever they are used
+// (a rotation then needs no pass and no copy of its own).
+int keyswitch_begin(cerium_keyswitch* ks, void* dst, const void* cpoly, cudaStream_t stream, uint32_t pre_elt = 0) {
   const size_t n = kN;
   NttCall c{cpoly, dst, n, n, nullptr, ks->q_idx.data(), ks->L};
+  c.in_galois = pre_elt;
   return launch_ntt_inverse(ks->ctx, c, ks->d_scale_q, ks->d_scale_q_shoup, stream);
 }
 
@@ -192,7 +196,7 @@ int keyswitch_raise(cerium_keyswitch* ks, const void* gathered, cudaStream_t str
 // Steps 4-7 on the digits that keyswitch_raise left in the plan: inner product with `evk`,
 // ModDown, optional additions.  Can be repeated with different keys (hoisting).
 int keyswitch_inner_moddown(cerium_keyswitch* ks, void* out0, void* out1, const void* cpoly, const void* evk,
-                            const void* add0, const void* add1, cudaStream_t stream) {
+                            const void* add0, const void* add1, cudaStream_t stream, uint32_t pre_elt = 0) {
   cerium_context* ctx = ks->ctx;
   const size_t n = kN;
   const int L = ks->L, K = ks->K, LK = ks->LK, dnum = ks->dnum;
@@ -210,6 +214,7 @@ int keyswitch_inner_moddown(cerium_keyswitch* ks, void* out0, void* out1, const 
       g.raised_limb_stride = n;
       g.own = static_cast<const W*>(cpoly);
       g.own_stride = n;
+      g.own_elt = pre_elt;
       g.evk = static_cast<const W*>(evk);
       g.evk_digit_stride = (size_t)2 * LK * n;
       g.evk_poly_stride = (size_t)LK * n;
@@ -266,6 +271,7 @@ int keyswitch_inner_moddown(cerium_keyswitch* ks, void* out0, void* out1, const 
       s.dst2 = out1;
       s.minuend2 = acc + (size_t)LK * n;
       s.addend2 = add1;
+      s.addend_galois = pre_elt;
       if (int rc = launch_sud(ctx, s, stream)) return rc;
     } else {
       for (int p = 0; p < 2; p++) {
@@ -283,6 +289,7 @@ int keyswitch_inner_moddown(cerium_keyswitch* ks, void* out0, void* out1, const 
         s.prime = ks->q_idx.data();
         s.factor = ks->pinv.data();
         s.count = L;
+        s.addend_galois = pre_elt;
         if (int rc = launch_sud(ctx, s, stream)) return rc;
       }
     }
@@ -291,18 +298,18 @@ int keyswitch_inner_moddown(cerium_keyswitch* ks, void* out0, void* out1, const 
 }
 
 int keyswitch_finish(cerium_keyswitch* ks, void* out0, void* out1, const void* gathered, const void* cpoly,
-                     const void* evk, const void* add0, const void* add1, cudaStream_t stream) {
+                     const void* evk, const void* add0, const void* add1, cudaStream_t stream, uint32_t pre_elt = 0) {
   if (int rc = keyswitch_raise(ks, gathered, stream)) return rc;
-  return keyswitch_inner_moddown(ks, out0, out1, cpoly, evk, add0, add1, stream);
+  return keyswitch_inner_moddown(ks, out0, out1, cpoly, evk, add0, add1, stream, pre_elt);
 }
 
 int keyswitch_impl(cerium_keyswitch* ks, void* out0, void* out1, const void* cpoly, const void* evk,
-                   const void* add0, const void* add1, cudaStream_t stream) {
+                   const void* add0, const void* add1, cudaStream_t stream, uint32_t pre_elt = 0) {
   if (ks->world != 1) return fail(CERIUM_ERR_INVALID, "keyswitch: a sharded plan needs the begin / finish calls around the all-gather");
   if (ks->lifted) return fail(CERIUM_ERR_INVALID, "keyswitch: a lifted plan only serves cerium_mod_raise");
   void* coef = static_cast<char*>(ks->ws) + ks->o_coef * ks->ctx->word_bytes();
-  if (int rc = keyswitch_begin(ks, coef, cpoly, stream)) return rc;
-  return keyswitch_finish(ks, out0, out1, coef, cpoly, evk, add0, add1, stream);
+  if (int rc = keyswitch_begin(ks, coef, cpoly, stream, pre_elt)) return rc;
+  return keyswitch_finish(ks, out0, out1, coef, cpoly, evk, add0, add1, stream, pre_elt);
 }
 
 }  // namespace
@@ -591,6 +598,16 @@ int cerium_hrot(cerium_keyswitch* ks, void* out0, void* out1, const void* c0, co
   void* rot0 = tmp;
   void* rot1 = tmp + (size_t)ks->L * n * wb;
   if (((uintptr_t)c0 | (uintptr_t)c1) & 15u) return fail(CERIUM_ERR_INVALID, "hrot: pointers must be 16-byte aligned");
+  // The rotation is folded into the key switch's own reads of c0 and c1 (inverse transform, the
+  // digits' own limbs in the inner product, the final addition) unless an output overlaps an input:
+  // the last kernel writes out0 / out1 while it still gathers from c0, and the inner product reads c1.
+  const size_t poly_bytes = (size_t)ks->L * n * wb;
+  auto overlaps = [&](const void* a, const void* b) {
+    const uintptr_t x = (uintptr_t)a, y = (uintptr_t)b;
+    return x < y + poly_bytes && y < x + poly_bytes;
+  };
+  if (!overlaps(out0, c0) && !overlaps(out1, c0) && !overlaps(out0, c1) && !overlaps(out1, c1))
+    return keyswitch_impl(ks, out0, out1, c1, evk, c0, nullptr, (cudaStream_t)stream, galois_elt);
   if (int rc = launch_automorph_pair(ctx, rot0, c0, rot1, c1, galois_elt, ks->L, (cudaStream_t)stream)) return rc;
   return keyswitch_impl(ks, out0, out1, rot1, evk, rot0, nullptr, (cudaStream_t)stream);
 }

@@ -148,19 +148,6 @@ __global__ void __launch_bounds__(kEwThreads)
   d2.store(g.d2.at(b, idx));
 }
 
-// NTT-domain Galois automorphism out[i] = in[pi(i)] with
-//   pi(i) = brev16( ((elt * (2*brev16(i) + 1)) >> 1) & (N-1) )
-// (cerium/runtime/math/galois.cpp:30-62 builds this as a table; the reference kernels scatter
-// through its inverse, cerium/compiler/backend/cuda_kernel.cc:228-300).  The map sends every
-// aligned block of 2^k indices onto an aligned block of 2^k indices, so a warp's 32 gathered
-// words always come from one aligned 32-word segment: the gather is sector-exact without a
-// table and without staging.
-__device__ __forceinline__ uint32_t galois_source_index(uint32_t i, uint32_t elt) {
-  const uint32_t r = (__brev(i) >> (32 - kLogN)) * 2u + 1u;
-  const uint32_t raw = ((elt * r) >> 1) & (uint32_t)(kN - 1);
-  return __brev(raw) >> (32 - kLogN);
-}
-
 template <typename W>
 struct AutomorphArgs {
   Limbs<W> out, in;
@@ -273,6 +260,8 @@ struct InnerProductArgs {
   Limbs<W> out0, out1;    // [LK][N]
   int first_limb;         // grid.y covers extended limbs first_limb, first_limb + 1, ...
   int dnum;
+  uint32_t own_elt;       // not 0: `own` is read through the Galois automorphism of this element
+                          // (word i of a limb is own[pi(i)]), i.e. the rotation of the input is folded in
   uint8_t prime[kEwMaxLimbs];     // prime index of extended limb b
   int8_t own_digit[kEwMaxLimbs];  // digit that limb b belongs to (-1 for extension limbs)
 };
@@ -300,7 +289,14 @@ __global__ void __launch_bounds__(kEwThreads)
                          : g.raised + (size_t)d * g.raised_digit_stride +
                                (size_t)b * g.raised_limb_stride + idx;
     const W* kp = g.evk + (size_t)d * g.evk_digit_stride + (size_t)b * g.evk_limb_stride + idx;
-    const V a = V::load(ap);
+    V a;
+    if (is_own && g.own_elt != 0) {
+      const W* limb = g.own + (size_t)b * g.own_stride;
+#pragma unroll
+      for (int l = 0; l < V::kLanes; l++) a.v[l] = limb[galois_source_index((uint32_t)(idx + l), g.own_elt)];
+    } else {
+      a = V::load(ap);
+    }
     const V k0 = V::load(kp);
     const V k1 = V::load(kp + g.evk_poly_stride);
 #pragma unroll

@@ -170,6 +170,8 @@ struct NttCall {
   const uint32_t* src_prime = nullptr;
   // forward transform only: the input words are below 4q instead of canonical
   bool lazy_in = false;
+  // inverse transform only, not 0: the input limbs are read through the Galois automorphism of this element
+  uint32_t in_galois = 0;
 };
 // lazy_out: leave the results below 4q instead of canonical (internal buffers read by the inner product only)
 int launch_ntt_forward(cerium_context* ctx, const NttCall& c, cudaStream_t stream, bool lazy_out = false);
@@ -206,6 +208,8 @@ struct SudCall {
   // only with reduce_src: entry b reads limb src_pos[b] of src (null: limb b, or the one limb
   // when src_stride == 0)
   const uint32_t* src_pos = nullptr;
+  // not 0: addend / addend2 are read through the Galois automorphism of this element
+  uint32_t addend_galois = 0;
 };
 int launch_sud(cerium_context* ctx, const SudCall& c, cudaStream_t stream);
 int launch_automorph_pair(cerium_context* ctx, void* out_a, const void* in_a, void* out_b, const void* in_b,

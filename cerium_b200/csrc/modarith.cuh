@@ -308,4 +308,18 @@ __device__ __forceinline__ void butterfly_inv(W& a, W& b, W w, W ws, W q, W q2) 
   b = mul_shoup_lazy<W>(d, w, ws, q);
 }
 
+// NTT-domain Galois automorphism out[i] = in[pi(i)] with
+//   pi(i) = brev16( ((elt * (2*brev16(i) + 1)) >> 1) & (N-1) )
+// (cerium/runtime/math/galois.cpp:30-62 builds this as a table; the reference kernels scatter
+// through its inverse, cerium/compiler/backend/cuda_kernel.cc:228-300).  The map sends every
+// aligned block of 2^k indices onto an aligned block of 2^k indices, so a warp's 32 gathered
+// words always come from one aligned 32-word segment: the gather is sector-exact without a
+// table and without staging.
+__device__ __forceinline__ uint32_t galois_source_index(uint32_t i, uint32_t elt) {
+  const uint32_t r = (__brev(i) >> (32 - kLogN)) * 2u + 1u;
+  const uint32_t raw = ((elt * r) >> 1) & (uint32_t)(kN - 1);
+  return __brev(raw) >> (32 - kLogN);
+}
+
+
 }  // namespace cerium

@@ -55,6 +55,8 @@ struct StridedBatch {
   size_t out_stride;  // in words
   W* out2;            // entries b >= split write to out2 instead of out (two result stacks, one launch)
   int split;          // kMaxBatch when unused
+  uint32_t in_elt;    // inverse transform only, not 0: word i of an input limb is read at pi(i), the Galois
+                      // automorphism of this element (modarith.cuh), so a rotation costs no pass of its own
   uint16_t pos[kMaxBatch];
   uint8_t prime[kMaxBatch];
   __device__ __forceinline__ const W* in_limb(int b) const { return in + (size_t)pos[b] * in_stride; }
@@ -62,6 +64,7 @@ struct StridedBatch {
     return (b >= split ? out2 : out) + (size_t)pos[b] * out_stride;
   }
   __device__ __forceinline__ uint32_t prime_of(int b) const { return prime[b]; }
+  __device__ __forceinline__ uint32_t gather_elt() const { return in_elt; }
 };
 
 // StridedBatch whose entries read from a slot of their own: entry b reads limb in_pos[b] of `in`
@@ -84,6 +87,7 @@ struct PointerBatch {
   __device__ __forceinline__ const W* in_limb(int b) const { return ins[b]; }
   __device__ __forceinline__ W* out_limb(int b) const { return outs[b]; }
   __device__ __forceinline__ uint32_t prime_of(int b) const { return bases[b]; }
+  __device__ __forceinline__ uint32_t gather_elt() const { return 0u; }
 };
 
 // ---------------------------------------------------------------------------------------
@@ -613,6 +617,7 @@ struct SudEpilogue {
   const W* addend2;  // may be null
   size_t addend_stride;
   int split;         // kSudMaxBatch when there is one polynomial
+  uint32_t addend_elt;  // not 0: the addends are read through the Galois automorphism of this element
   W factor[kSudMaxBatch];
   W factor_shoup[kSudMaxBatch];
   // starts the 16 bytes at word idx of the operands towards L2 (called before the transform, whose
@@ -622,7 +627,7 @@ struct SudEpilogue {
     const int e = second ? b - split : b;
     prefetch_l2((second ? minuend2 : minuend) + (size_t)e * minuend_stride + idx);
     const W* ap = second ? addend2 : addend;
-    if (ap != nullptr) prefetch_l2(ap + (size_t)e * addend_stride + idx);
+    if (ap != nullptr && addend_elt == 0) prefetch_l2(ap + (size_t)e * addend_stride + idx);
   }
   __device__ __forceinline__ W apply(W x, int b, int idx, uint32_t /*pi*/,
                                      const PrimeConst<W>& pc) const {
@@ -633,7 +638,10 @@ struct SudEpilogue {
     const W m = mp[(size_t)e * minuend_stride + idx];
     W d = m + (pc.q2 + pc.q2) - x;  // x < 4q: positive, and the Shoup product takes any word
     d = csub<W>(mul_shoup_lazy<W>(d, factor[b], factor_shoup[b], pc.q), pc.q);
-    if (ap != nullptr) d = add_mod<W>(d, ap[(size_t)e * addend_stride + idx], pc.q);
+    if (ap != nullptr) {
+      const uint32_t at = addend_elt != 0 ? galois_source_index((uint32_t)idx, addend_elt) : (uint32_t)idx;
+      d = add_mod<W>(d, ap[(size_t)e * addend_stride + at], pc.q);
+    }
     return d;
   }
 };
@@ -759,7 +767,9 @@ __device__ __forceinline__ void ntt_inv_rows_body(const Batch& batch, int b, con
   const Arith<W, kMode> ar(pc);
   const int tid = threadIdx.x, r = tid >> 4, u = tid & 15;
   const int h = blockIdx.x * kRowsPerCta + r;
-  const W* src = batch.in_limb(b) + h * 256;
+  const W* limb_in = batch.in_limb(b);
+  const W* src = limb_in + h * 256;
+  const uint32_t elt = batch.gather_elt();
   W* dst = batch.out_limb(b) + h * 256;
   W* trow = tile + r * kRowPitch;
   // coalesced vectors -> swizzled staging -> own 16 consecutive words
@@ -767,7 +777,17 @@ __device__ __forceinline__ void ntt_inv_rows_body(const Batch& batch, int b, con
 #pragma unroll
   for (int k = 0; k < RV::kPerThread; k++) {
     const int v = u + 16 * k;
-    vrow[row_vec_slot<W>(v)] = reinterpret_cast<const Vec*>(src)[v];
+    if (elt != 0) {
+      // the automorphism maps the aligned 256-word block of this row onto one aligned block:
+      // the gathered words use whole sectors
+      W w[RV::kWords];
+#pragma unroll
+      for (int e = 0; e < RV::kWords; e++)
+        w[e] = limb_in[galois_source_index((uint32_t)(h * 256 + v * RV::kWords + e), elt)];
+      vrow[row_vec_slot<W>(v)] = vec_pack(w);
+    } else {
+      vrow[row_vec_slot<W>(v)] = reinterpret_cast<const Vec*>(src)[v];
+    }
   }
   __syncwarp();
   W x[16];

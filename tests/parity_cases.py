@@ -406,6 +406,11 @@ def case_keyswitch(be, word_bits, L, K, dnum, bconv_mode, round_mode):
     w0, w1 = h.orc.hrot(bconv_mode, round_mode, prm.q_idx, prm.p_idx, dnum, elt, c0, c1, evk)
     assert np.array_equal(h.down(o0), w0), "HRot c0 differs"
     assert np.array_equal(h.down(o1), w1), "HRot c1 differs"
+    # in place (outputs = inputs): the library rotates into its workspace first instead of folding the
+    # rotation into the key switch's reads
+    i0, i1 = h.up(c0), h.up(c1)
+    ks.hrot(h.p(i0), h.p(i1), h.p(i0), h.p(i1), h.p(d_evk), elt)
+    assert np.array_equal(h.down(i0), w0) and np.array_equal(h.down(i1), w1), "in-place HRot differs"
     # hoisted rotations: one ModUp, several rotations with pre-permuted keys
     ks.hoisted_begin(h.p(d_c1))
     for step in (1, -2):
