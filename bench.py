@@ -429,8 +429,8 @@ class HoistedWorkload(HRotWorkload):
         self.elts = [lib.galois_elt_from_step(1 << k, LOGN) for k in range(self.ops_per_step)]
         self.houts = [torch.empty_like(self.cts[0]) for _ in range(self.ops_per_step)]
         self.alg_bytes = (2 * prm.L + self.ops_per_step * (prm.dnum * 2 * (prm.L + prm.K) + 2 * prm.L)) * N * 8
-        # begin: iNTT pair, BConv, NTT pair; per rotation: inner product, iNTT pair, BConv, SuD pair, automorphism
-        self.gpu_launches_per_step = 5 + self.ops_per_step * 7
+        # begin: iNTT pair, BConv, NTT pair; per rotation: inner product, iNTT pair, BConv, SuD pair (the automorphism is the SuD tail's store pattern)
+        self.gpu_launches_per_step = 5 + self.ops_per_step * 6
 
     def _run(self, ct, outs, stream):
         self.ks.hoisted_begin(ct[1].data_ptr(), stream)
@@ -489,7 +489,7 @@ class BsgsWorkload(HRotWorkload):
         limb = N * 8
         # ciphertext in and out, 14 keys, 64 plaintexts
         self.alg_bytes = (4 * prm.L + 2 * (G - 1) * prm.dnum * 2 * (prm.L + prm.K) + G * G * prm.L) * limb
-        self.gpu_launches_per_step = 5 + (G - 1) * 7 + G * G * 2 + (G - 1) * (11 + 2)
+        self.gpu_launches_per_step = 5 + (G - 1) * 6 + G * G * 2 + (G - 1) * (11 + 2)
 
     def _run(self, ct, out, stream):
         self.op.run(out, ct, self.pts, self.baby_keys, self.giant_keys, self.baby_elts, self.giant_elts, stream)

@@ -155,6 +155,7 @@ int launch_sud(cerium_context* ctx, const SudCall& c, cudaStream_t stream) {
       epi.addend = c.addend ? static_cast<const W*>(c.addend) + (size_t)first * c.addend_stride : nullptr;
       epi.addend_stride = c.addend_stride;
       epi.addend_elt = c.addend_galois;
+      epi.store_elt = c.store_galois;
       epi.split = kSudMaxBatch;
       if (c.split > 0) {
         // second polynomial: entry b lands at slot b - split of dst2 (the slot number itself stays b,

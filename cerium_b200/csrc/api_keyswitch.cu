@@ -196,7 +196,8 @@ int keyswitch_raise(cerium_keyswitch* ks, const void* gathered, cudaStream_t str
 // Steps 4-7 on the digits that keyswitch_raise left in the plan: inner product with `evk`,
 // ModDown, optional additions.  Can be repeated with different keys (hoisting).
 int keyswitch_inner_moddown(cerium_keyswitch* ks, void* out0, void* out1, const void* cpoly, const void* evk,
-                            const void* add0, const void* add1, cudaStream_t stream, uint32_t pre_elt = 0) {
+                            const void* add0, const void* add1, cudaStream_t stream, uint32_t pre_elt = 0,
+                            uint32_t store_elt = 0) {
   cerium_context* ctx = ks->ctx;
   const size_t n = kN;
   const int L = ks->L, K = ks->K, LK = ks->LK, dnum = ks->dnum;
@@ -272,6 +273,7 @@ int keyswitch_inner_moddown(cerium_keyswitch* ks, void* out0, void* out1, const 
       s.minuend2 = acc + (size_t)LK * n;
       s.addend2 = add1;
       s.addend_galois = pre_elt;
+      s.store_galois = store_elt;
       if (int rc = launch_sud(ctx, s, stream)) return rc;
     } else {
       for (int p = 0; p < 2; p++) {
@@ -290,6 +292,7 @@ int keyswitch_inner_moddown(cerium_keyswitch* ks, void* out0, void* out1, const 
         s.factor = ks->pinv.data();
         s.count = L;
         s.addend_galois = pre_elt;
+        s.store_galois = store_elt;
         if (int rc = launch_sud(ctx, s, stream)) return rc;
       }
     }
@@ -634,7 +637,23 @@ int cerium_hoisted_rotate(cerium_keyswitch* ks, void* out0, void* out1, const vo
   char* tmp = static_cast<char*>(ks->ws) + ks->o_tmp * wb;
   void* t0 = tmp;
   void* t1 = tmp + (size_t)ks->L * n * wb;
-  // (t0, t1) = KeySwitch(c1) + (c0, 0) on the un-rotated digits, then the automorphism
+  // (t0, t1) = KeySwitch(c1) + (c0, 0) on the un-rotated digits, then the automorphism: as the store
+  // pattern of the last kernel (out[i] = t[pi_g(i)] is t[i] -> out[pi_{1/g}(i)]), unless an output
+  // overlaps an input that kernel still reads
+  {
+    const size_t poly_bytes = (size_t)ks->L * n * wb;
+    auto overlaps = [&](const void* a, const void* b) {
+      const uintptr_t x = (uintptr_t)a, y = (uintptr_t)b;
+      return x < y + poly_bytes && y < x + poly_bytes;
+    };
+    if (!overlaps(out0, c0) && !overlaps(out1, c0) && !overlaps(out0, c1) && !overlaps(out1, c1)) {
+      // inverse of the element modulo 2N (odd, so it exists): Newton steps double the valid bits
+      uint32_t inv = galois_elt;
+      for (int k = 0; k < 5; k++) inv *= 2u - galois_elt * inv;
+      inv &= 2u * (uint32_t)kN - 1u;
+      return keyswitch_inner_moddown(ks, out0, out1, c1, evk_pre, c0, nullptr, (cudaStream_t)stream, 0, inv);
+    }
+  }
   if (int rc = keyswitch_inner_moddown(ks, t0, t1, c1, evk_pre, c0, nullptr, (cudaStream_t)stream)) return rc;
   if (((uintptr_t)out0 | (uintptr_t)out1) & 15u) return fail(CERIUM_ERR_INVALID, "hoisted_rotate: pointers must be 16-byte aligned");
   return launch_automorph_pair(ctx, out0, t0, out1, t1, galois_elt, ks->L, (cudaStream_t)stream);

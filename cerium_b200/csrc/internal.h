@@ -210,6 +210,9 @@ struct SudCall {
   const uint32_t* src_pos = nullptr;
   // not 0: addend / addend2 are read through the Galois automorphism of this element
   uint32_t addend_galois = 0;
+  // not 0: word i of every result limb is stored at pi(i) (index map of this element); dst / dst2 must
+  // then not overlap minuend, addend or work
+  uint32_t store_galois = 0;
 };
 int launch_sud(cerium_context* ctx, const SudCall& c, cudaStream_t stream);
 int launch_automorph_pair(cerium_context* ctx, void* out_a, const void* in_a, void* out_b, const void* in_b,

@@ -585,6 +585,7 @@ __device__ __forceinline__ void prefetch_l2(const void* p) {
 template <typename W>
 struct StoreEpilogue {
   static constexpr bool kCanonicalInput = true;
+  __device__ __forceinline__ uint32_t scatter_elt() const { return 0u; }
   __device__ __forceinline__ void prefetch(int /*b*/, int /*idx*/) const {}
   __device__ __forceinline__ W apply(W x, int /*b*/, int /*idx*/, uint32_t /*pi*/,
                                      const PrimeConst<W>& /*pc*/) const {
@@ -597,6 +598,7 @@ struct StoreEpilogue {
 template <typename W>
 struct LazyStoreEpilogue {
   static constexpr bool kCanonicalInput = false;
+  __device__ __forceinline__ uint32_t scatter_elt() const { return 0u; }
   __device__ __forceinline__ void prefetch(int /*b*/, int /*idx*/) const {}
   __device__ __forceinline__ W apply(W x, int /*b*/, int /*idx*/, uint32_t /*pi*/,
                                      const PrimeConst<W>& /*pc*/) const {
@@ -618,6 +620,9 @@ struct SudEpilogue {
   size_t addend_stride;
   int split;         // kSudMaxBatch when there is one polynomial
   uint32_t addend_elt;  // not 0: the addends are read through the Galois automorphism of this element
+  uint32_t store_elt;   // not 0: word i of the result is stored at pi(i), the index map of this element, so
+                        // the output is the automorphism of the INVERSE element applied to the result
+  __device__ __forceinline__ uint32_t scatter_elt() const { return store_elt; }
   W factor[kSudMaxBatch];
   W factor_shoup[kSudMaxBatch];
   // starts the 16 bytes at word idx of the operands towards L2 (called before the transform, whose
@@ -696,7 +701,9 @@ __device__ __forceinline__ void ntt_fwd_rows_body(const Batch& batch, const Epil
   const int tid = threadIdx.x, r = tid >> 4, u = tid & 15;
   const int h = blockIdx.x * kRowsPerCta + r;
   const W* row = batch.in_limb(b) + (unsigned)(h * 256 + u);
-  W* drow = batch.out_limb(b) + (unsigned)(h * 256);
+  W* limb_out = batch.out_limb(b);
+  W* drow = limb_out + (unsigned)(h * 256);
+  const uint32_t selt = epi.scatter_elt();
   W* trow = tile + (unsigned)(r * kRowPitch);
   W* t_strided = trow + u;             // row_pos(j * 16 + u) = j * 17 + u
   W* t_own = trow + (unsigned)(u * 17);  // row_pos(u * 16 + j) = u * 17 + j
@@ -729,7 +736,14 @@ __device__ __forceinline__ void ntt_fwd_rows_body(const Batch& batch, const Epil
     vec_unpack(vrow[row_vec_slot<W>(v)], w);
 #pragma unroll
     for (int e = 0; e < RV::kWords; e++) w[e] = epi.apply(w[e], b, h * 256 + v * RV::kWords + e, pi, pc);
-    reinterpret_cast<Vec*>(drow)[v] = vec_pack(w);
+    if (selt != 0) {
+      // the row's aligned 256-word block lands on one aligned block of the output limb
+#pragma unroll
+      for (int e = 0; e < RV::kWords; e++)
+        limb_out[galois_source_index((uint32_t)(h * 256 + v * RV::kWords + e), selt)] = w[e];
+    } else {
+      reinterpret_cast<Vec*>(drow)[v] = vec_pack(w);
+    }
   }
 }
 

@@ -421,6 +421,10 @@ def case_keyswitch(be, word_bits, L, K, dnum, bconv_mode, round_mode):
         w1 = np.stack([oracle.apply_galois_ntt(e2, LOGN, k1[i]) for i in range(L)])
         ks.hoisted_rotate(h.p(o0), h.p(o1), h.p(d_c0), h.p(d_c1), h.p(d_evk), e2)
         assert np.array_equal(h.down(o0), w0) and np.array_equal(h.down(o1), w1), "hoisted rotation differs"
+    # the last one again with the outputs on top of the inputs (separate automorphism pass)
+    i0, i1 = h.up(c0), h.up(c1)
+    ks.hoisted_rotate(h.p(i0), h.p(i1), h.p(i0), h.p(i1), h.p(d_evk), e2)
+    assert np.array_equal(h.down(i0), w0) and np.array_equal(h.down(i1), w1), "in-place hoisted rotation differs"
     # HMult + relinearise, with and without rescale
     b0, b1 = rand_limbs(rng, prm.moduli, prm.q_idx), rand_limbs(rng, prm.moduli, prm.q_idx)
     d_b0, d_b1 = h.up(b0), h.up(b1)
