@@ -641,7 +641,13 @@ struct SudEpilogue {
     const W* mp = second ? minuend2 : minuend;
     const W* ap = second ? addend2 : addend;
     const W m = mp[(size_t)e * minuend_stride + idx];
-    W d = m + (pc.q2 + pc.q2) - x;  // x < 4q: positive, and the Shoup product takes any word
+    W d;
+    if (sizeof(W) == 4) {
+      // 32-bit words hold primes up to 2^30: m + 4q would pass 2^32, so x comes below 2q first
+      d = m + pc.q2 - csub<W>(x, pc.q2);
+    } else {
+      d = m + (pc.q2 + pc.q2) - x;  // x < 4q: positive, and the Shoup product takes any word
+    }
     d = csub<W>(mul_shoup_lazy<W>(d, factor[b], factor_shoup[b], pc.q), pc.q);
     if (ap != nullptr) {
       const uint32_t at = addend_elt != 0 ? galois_source_index((uint32_t)idx, addend_elt) : (uint32_t)idx;

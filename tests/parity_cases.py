@@ -19,9 +19,14 @@ def wdtype(word_bits):
     return np.uint64 if word_bits == 64 else np.uint32
 
 
+_U32_BITS = 28   # case_u32_widest_primes switches the 32-bit cases to primes just below 2^30
+
+
 def moduli_for(word_bits, count, sixty=0):
     """`count` primes for the word size; for 64-bit the first `sixty` are 60-bit, the rest 50-bit."""
     if word_bits == 32:
+        if _U32_BITS != 28:
+            return params.ntt_primes_below(_U32_BITS, count, LOGN)
         return params.reference_primes_28bit(count, LOGN)
     return params.ntt_primes_below(60, sixty, LOGN) + params.ntt_primes_below(50, count - sixty, LOGN)
 
@@ -269,6 +274,21 @@ def case_sud(be, word_bits):
     h.ctx.sud(h.p(dm), h.p(dm), h.p(dc), idx, div, addend=h.p(da))  # in place on the minuend, with addend
     want2 = np.stack([oracle.ew("add", mods[p], want[i], addend[i]) for i, p in enumerate(idx)])
     assert np.array_equal(h.down(dm), want2)
+
+
+def case_u32_widest_primes(be):
+    """32-bit words with primes just below 2^30, the widest the library accepts: sums such as
+    minuend + 4q pass 2^32 there, which the 28-bit reference chain never shows."""
+    global _U32_BITS
+    _U32_BITS = 30
+    try:
+        assert min(moduli_for(32, 6)) > 0.99 * 2**30
+        case_sud(be, 32)
+        case_rescale(be, 32, 0)
+        case_rescale(be, 32, 1, L=3, n_polys=1)
+        case_double_rescale(be, 32)
+    finally:
+        _U32_BITS = 28
 
 
 def case_rescale(be, word_bits, round_mode, L=4, n_polys=2):

@@ -51,6 +51,10 @@ def test_sud(be, word_bits):
     pc.case_sud(be, word_bits)
 
 
+def test_u32_widest_primes(be):
+    pc.case_u32_widest_primes(be)
+
+
 @pytest.mark.parametrize("word_bits,round_mode", [(64, _capi.ROUND_FLOOR), (64, _capi.ROUND_HALF), (32, _capi.ROUND_FLOOR)])
 def test_rescale(be, word_bits, round_mode):
     pc.case_rescale(be, word_bits, round_mode, L=3, n_polys=3)   # one pair and a single

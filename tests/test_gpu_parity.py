@@ -53,6 +53,10 @@ def test_sud(be, word_bits):
     pc.case_sud(be, word_bits)
 
 
+def test_u32_widest_primes(be):
+    pc.case_u32_widest_primes(be)
+
+
 @pytest.mark.parametrize("word_bits,round_mode", [
     (64, _capi.ROUND_FLOOR), (64, _capi.ROUND_HALF), (32, _capi.ROUND_FLOOR), (32, _capi.ROUND_HALF)])
 def test_rescale(be, word_bits, round_mode):
