@@ -37,6 +37,8 @@ SIGNATURES = {
     "cerium_ntt_inverse": (C.c_int, [_vp, _vp, _sz, _vp, _sz, _u32p, C.c_int, _vp]),
     "cerium_ntt_forward_ptrs": (C.c_int, [_vp, _vp, _vp, _vp, _sz, _vp]),
     "cerium_ntt_inverse_ptrs": (C.c_int, [_vp, _vp, _vp, _vp, _sz, _vp]),
+    "cerium_sud_ptrs": (C.c_int, [_vp, _vp, _vp, _vp, _sz, _vp, _vp]),
+    "cerium_bconv_ptrs": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _vp]),
     "cerium_sud": (C.c_int, [_vp, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _u32p, C.c_int, _u32p, C.c_int, _vp]),
     "cerium_ewise": (C.c_int, [_vp, C.c_int, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _u64p, _u32p, C.c_int, _vp]),
     "cerium_tensor": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _u32p, C.c_int, _vp]),
@@ -174,6 +176,16 @@ class Context:
 
     def ntt_inverse_ptrs(self, outs: int, ins: int, bases: int, num_bases: int, stream: int = 0):
         self.lib.check(self.lib.dll.cerium_ntt_inverse_ptrs(self.h, outs, ins, bases, num_bases, stream))
+
+    def sud_ptrs(self, outs: int, ins: int, bases: int, num_bases: int, factors: int, stream: int = 0):
+        """SuD on device pointer tables (two inputs per entry), the reference launcher's layout."""
+        self.lib.check(self.lib.dll.cerium_sud_ptrs(self.h, outs, ins, bases, num_bases, factors, stream))
+
+    def bconv_ptrs(self, outs: int, n_out: int, ins: int, n_in: int, factors: int, out_moduli: int,
+                   max_in: int, max_out: int, num_conversions: int, stream: int = 0):
+        """Base conversion driven by device tables only, the reference launcher's layout."""
+        self.lib.check(self.lib.dll.cerium_bconv_ptrs(self.h, outs, n_out, ins, n_in, factors, out_moduli,
+                                                      max_in, max_out, num_conversions, stream))
 
     def sud(self, out: int, minuend: int, in_coeff: int, prime_idx: Sequence[int], divide_primes: Sequence[int],
             addend: int = 0, stream: int = 0):

@@ -662,8 +662,8 @@ static int ntt_ptrs_common(cerium_context* ctx, bool forward, void* const* outs,
     using Pair = typename WordTraits<W>::Pair;
     constexpr int kCols = NttCfg<W>::kCols;
     const PrimeConst<W>* pcs = static_cast<const PrimeConst<W>*>(ctx->d_pcs);
-    PointerBatch<W> pb{reinterpret_cast<W* const*>(outs), reinterpret_cast<const W* const*>(ins), bases};
-    PointerBatch<W> inplace{reinterpret_cast<W* const*>(outs), reinterpret_cast<const W* const*>(outs), bases};
+    PointerBatch<W> pb{reinterpret_cast<W* const*>(outs), reinterpret_cast<const W* const*>(ins), bases, 1, 0};
+    PointerBatch<W> inplace{reinterpret_cast<W* const*>(outs), reinterpret_cast<const W* const*>(outs), bases, 1, 0};
     const int cnt = (int)num_bases;
     if (forward) {
       const Pair* tw = static_cast<const Pair*>(ctx->d_tw_fwd);
@@ -687,6 +687,65 @@ int cerium_ntt_forward_ptrs(cerium_context* ctx, void* const* outs, const void* 
 int cerium_ntt_inverse_ptrs(cerium_context* ctx, void* const* outs, const void* const* ins, const uint32_t* bases,
                             size_t num_bases, void* stream) {
   return ntt_ptrs_common(ctx, false, outs, ins, bases, num_bases, stream);
+}
+
+int cerium_sud_ptrs(cerium_context* ctx, void* const* outs, const void* const* ins, const uint32_t* bases,
+                    size_t num_bases, const void* factors, void* stream) {
+  if (!ctx) return fail(CERIUM_ERR_INVALID, "sud_ptrs: null context");
+  if (num_bases == 0) return CERIUM_OK;
+  if (!outs || !ins || !bases || !factors) return fail(CERIUM_ERR_INVALID, "sud_ptrs: null table");
+  if (num_bases > 65535) return fail(CERIUM_ERR_INVALID, "sud_ptrs: more than 65535 limbs in one call");
+  DeviceGuard guard(ctx->device);
+  cudaStream_t s = (cudaStream_t)stream;
+  return dispatch_word(ctx->word_bits, [&](auto tag) -> int {
+    using W = decltype(tag);
+    using Pair = typename WordTraits<W>::Pair;
+    constexpr int kCols = NttCfg<W>::kCols;
+    const PrimeConst<W>* pcs = static_cast<const PrimeConst<W>*>(ctx->d_pcs);
+    const Pair* tw = static_cast<const Pair*>(ctx->d_tw_fwd);
+    const int cnt = (int)num_bases;
+    // column pass: second input of every entry -> output limb; row pass in place on the output
+    PointerBatch<W> cols{reinterpret_cast<W* const*>(outs), reinterpret_cast<const W* const*>(ins), bases, 2, 1};
+    PointerBatch<W> rows{reinterpret_cast<W* const*>(outs), reinterpret_cast<const W* const*>(outs), bases, 1, 0};
+    PtrSudEpilogue<W> epi{reinterpret_cast<const W* const*>(ins), static_cast<const W*>(factors)};
+    { auto kfn = ntt_fwd_cols_kernel<W, PointerBatch<W>, PlainLoader<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kCols, cnt), kCols * 16, 0, s, cols, PlainLoader<W>{}, tw, pcs); }
+    { auto kfn = ntt_fwd_rows_kernel<W, PointerBatch<W>, PtrSudEpilogue<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kRowsPerCta, cnt), kRowsPerCta * 16, 0, s, rows, epi, tw, static_cast<const Pair*>(ctx->d_twr_fwd), pcs); }
+    CERIUM_LAUNCH_CHECK("sud_ptrs");
+    return CERIUM_OK;
+  });
+}
+
+int cerium_bconv_ptrs(cerium_context* ctx, void* const* outs, const size_t* n_out, const void* const* ins,
+                      const size_t* n_in, const void* const* factors, const void* const* out_moduli,
+                      size_t max_in, size_t max_out, size_t num_conversions, void* stream) {
+  if (!ctx) return fail(CERIUM_ERR_INVALID, "bconv_ptrs: null context");
+  if (num_conversions == 0) return CERIUM_OK;
+  if (!outs || !n_out || !ins || !n_in || !factors || !out_moduli) return fail(CERIUM_ERR_INVALID, "bconv_ptrs: null table");
+  if (max_in < 1 || max_out < 1 || max_in > 64 || max_out > 128) return fail(CERIUM_ERR_INVALID, "bconv_ptrs: bad shape bound");
+  if (num_conversions > 65535) return fail(CERIUM_ERR_INVALID, "bconv_ptrs: more than 65535 conversions in one call");
+  DeviceGuard guard(ctx->device);
+  cudaStream_t s = (cudaStream_t)stream;
+  return dispatch_word(ctx->word_bits, [&](auto tag) -> int {
+    using W = decltype(tag);
+    static bool smem_opt_in[2] = {false, false};
+    // the shapes live on the device: size the shared memory for the caller's bounds (inputs staged per
+    // thread when there are more than kBconvRegInputs of them)
+    const size_t smem = bconv_smem_bytes<W>((int)max_in, (int)max_out);
+    if (smem > 200 * 1024) return fail(CERIUM_ERR_UNSUPPORTED, "bconv_ptrs: conversion needs more than 200 KiB of shared memory");
+    if (smem > 48 * 1024) {
+      const int slot = sizeof(W) == 4 ? 0 : 1;
+      if (!smem_opt_in[slot]) {
+        CERIUM_CUDA(cudaFuncSetAttribute(bconv_ptrs_kernel<W>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        smem_opt_in[slot] = true;
+      }
+    }
+    auto kfn = bconv_ptrs_kernel<W>;
+    CERIUM_LAUNCH(kfn, dim3(kBconvBlocks, (unsigned)num_conversions), kBconvThreads, smem, s,
+                  reinterpret_cast<W* const*>(outs), n_out, reinterpret_cast<const W* const*>(ins), n_in,
+                  reinterpret_cast<const W* const*>(factors), reinterpret_cast<const W* const*>(out_moduli));
+    CERIUM_LAUNCH_CHECK("bconv_ptrs");
+    return CERIUM_OK;
+  });
 }
 
 int cerium_sud(cerium_context* ctx, void* out, size_t out_stride, const void* minuend, size_t minuend_stride,

@@ -226,7 +226,7 @@ __host__ __device__ inline size_t bconv_smem_bytes(int I, int O) {
   return n;
 }
 
-// grid = (N / 256, conversions, ceil(max O / out_chunk)), block = 256,
+// grid = (ceil(N / kBconvThreads), conversions, ceil(max O / out_chunk)), block = kBconvThreads,
 // dynamic smem = max bconv_smem_bytes over the batch.  CTA z handles outputs
 // [z * out_chunk, min(O, (z + 1) * out_chunk)) of its conversion.
 template <typename W>
@@ -289,6 +289,84 @@ __global__ void __launch_bounds__(kBconvThreads, 5)
       case 8: bconv_body<W, 8>(d, pcs, sfac, sout, scol, coeff); break;
       default: bconv_body<W, 0>(d, pcs, sfac, sout, scol, coeff); break;
     }
+  }
+}
+
+// The same conversion driven entirely by device-resident tables, the argument layout of the
+// reference's launcher (_kernel_bco, cerium/compiler/backend/kernels/function.cuh:61-78, filled by
+// Evaluator::fn_bco, cerium/runtime/execution/evaluator.cpp:861-940): conversion j reads
+// ins[j] = [n_in[j]][N], writes outs[j] = [n_out[j]][N], with factors[j] = [O][I] residues and
+// out_moduli[j] = [O] primes.  The host knows neither shapes nor primes, so the Barrett constants
+// are derived here from the moduli (one division per output and CTA).  Lazy conversion only
+// (the reference's), canonical outputs.
+// grid = (ceil(N / kBconvThreads), conversions), block = kBconvThreads, dynamic smem >= bconv_smem_bytes(I, O).
+template <typename W>
+__global__ void __launch_bounds__(kBconvThreads, 5)
+    bconv_ptrs_kernel(W* const* __restrict__ outs, const size_t* __restrict__ n_out, const W* const* __restrict__ ins,
+                      const size_t* __restrict__ n_in, const W* const* __restrict__ factors,
+                      const W* const* __restrict__ out_moduli) {
+  CERIUM_DYN_SMEM(smem_raw);
+  grid_dependency_launch();
+  grid_dependency_wait();  // the tables may have been written by the stream's previous work
+  const int j = blockIdx.y;
+  const int I = (int)n_in[j], O = (int)n_out[j];
+  BconvDesc<W> d{};
+  d.in = ins[j];
+  d.out = outs[j];
+  d.in_stride = kN;
+  d.out_stride = kN;
+  d.I = I;
+  d.O = O;
+  W* sfac = reinterpret_cast<W*>(smem_raw);
+  const size_t fac_bytes = ((size_t)O * I * sizeof(W) + 15) / 16 * 16;
+  BconvOut<W>* sout = reinterpret_cast<BconvOut<W>*>(smem_raw + fac_bytes);
+  const size_t out_bytes = ((size_t)O * sizeof(BconvOut<W>) + 15) / 16 * 16;
+  W* scol = reinterpret_cast<W*>(smem_raw + fac_bytes + out_bytes);
+  const W* fac = factors[j];
+  const W* omod = out_moduli[j];
+  for (int k = threadIdx.x; k < O * I; k += kBconvThreads) sfac[k] = fac[k];
+  for (int o = threadIdx.x; o < O; o += kBconvThreads) {
+    const W q = omod[o];
+    BconvOut<W> c{};
+    c.q = q;
+    c.q2 = q + q;
+    if (sizeof(W) == 4) {
+      // floor(2^64 / q) = floor((2^64 - 1) / q) for a q that is not a power of two
+      const uint64_t mu = ~(uint64_t)0 / (uint64_t)q;
+      c.mu_hi = (W)(mu >> 32);
+      c.mu_lo = (W)(mu & 0xffffffffu);
+    } else {
+      // floor(2^128 / q) by two divisions: 2^64 = a q + r, then 2^128 / q = a 2^64 + floor(r 2^64 / q)
+      const uint64_t a = ~(uint64_t)0 / (uint64_t)q;
+      uint64_t r = ~(uint64_t)0 - a * (uint64_t)q + 1;  // 2^64 mod q (or q itself, fixed below)
+      uint64_t hi = a;
+      if (r >= (uint64_t)q) { r -= (uint64_t)q; hi += 1; }
+      // long division of r * 2^64 by q, one bit at a time (r < q < 2^60, so 2r never overflows)
+      uint64_t lo = 0;
+      for (int bit = 0; bit < 64; bit++) {
+        r <<= 1;
+        lo <<= 1;
+        if (r >= (uint64_t)q) { r -= (uint64_t)q; lo |= 1; }
+      }
+      c.mu_hi = (W)hi;
+      c.mu_lo = (W)lo;
+    }
+    c.pos = (uint32_t)o;
+    sout[o] = c;
+  }
+  __syncthreads();
+  const int coeff = blockIdx.x * kBconvThreads + threadIdx.x;
+  if (coeff >= kN) return;
+  switch (I) {
+    case 1: bconv_body<W, 1>(d, nullptr, sfac, sout, scol, coeff); break;
+    case 2: bconv_body<W, 2>(d, nullptr, sfac, sout, scol, coeff); break;
+    case 3: bconv_body<W, 3>(d, nullptr, sfac, sout, scol, coeff); break;
+    case 4: bconv_body<W, 4>(d, nullptr, sfac, sout, scol, coeff); break;
+    case 5: bconv_body<W, 5>(d, nullptr, sfac, sout, scol, coeff); break;
+    case 6: bconv_body<W, 6>(d, nullptr, sfac, sout, scol, coeff); break;
+    case 7: bconv_body<W, 7>(d, nullptr, sfac, sout, scol, coeff); break;
+    case 8: bconv_body<W, 8>(d, nullptr, sfac, sout, scol, coeff); break;
+    default: bconv_body<W, 0>(d, nullptr, sfac, sout, scol, coeff); break;
   }
 }
 

@@ -84,7 +84,9 @@ struct PointerBatch {
   W* const* outs;
   const W* const* ins;
   const uint32_t* bases;
-  __device__ __forceinline__ const W* in_limb(int b) const { return ins[b]; }
+  int in_step;  // entry b reads ins[b * in_step + in_off] (the SuD launcher passes two inputs per entry)
+  int in_off;
+  __device__ __forceinline__ const W* in_limb(int b) const { return ins[b * in_step + in_off]; }
   __device__ __forceinline__ W* out_limb(int b) const { return outs[b]; }
   __device__ __forceinline__ uint32_t prime_of(int b) const { return bases[b]; }
   __device__ __forceinline__ uint32_t gather_elt() const { return 0u; }
@@ -654,6 +656,26 @@ struct SudEpilogue {
       d = add_mod<W>(d, ap[(size_t)e * addend_stride + at], pc.q);
     }
     return d;
+  }
+};
+
+// SuD tail with the argument tables of the reference's launcher (_kernel_sud_1,
+// cerium/compiler/backend/kernels/function.cu:123-149): entry b has two inputs, ins[2b] the minuend
+// and ins[2b + 1] the coefficient-form limb whose transform is subtracted; factors holds one
+// residue per prime of the context, indexed by the entry's prime.
+template <typename W>
+struct PtrSudEpilogue {
+  static constexpr bool kCanonicalInput = false;
+  const W* const* ins;
+  const W* factors;
+  __device__ __forceinline__ uint32_t scatter_elt() const { return 0u; }
+  __device__ __forceinline__ void prefetch(int b, int idx) const { prefetch_l2(ins[2 * b] + idx); }
+  __device__ __forceinline__ W apply(W x, int b, int idx, uint32_t pi, const PrimeConst<W>& pc) const {
+    const W m = ins[2 * b][idx];
+    // x < 4q and m < q: bring the difference to [0, q) before the Barrett product
+    W d = m + pc.q2 - csub<W>(x, pc.q2);  // (m, m + 2q]
+    d = csub<W>(csub<W>(d, pc.q2), pc.q);
+    return mul_mod<W>(d, csub<W>(factors[pi], pc.q), pc);
   }
 };
 

@@ -108,6 +108,33 @@ CERIUM_API int cerium_ntt_inverse_ptrs(cerium_context *ctx, void *const *outs, c
                             const uint32_t *bases, size_t num_bases, void *stream);
 
 /*
+ * SuD with the argument tables of the reference's launcher (_function_sud_,
+ * cerium/compiler/backend/kernels/function.cu:101-174; cerium/runtime/execution/device_utils.h:54-62):
+ * all arrays are DEVICE resident.  Entry b has two inputs: ins[2b] is the minuend (NTT form),
+ * ins[2b+1] the coefficient-form limb; outs[b] = (ins[2b] - NTT(ins[2b+1])) * factors[bases[b]] mod q.
+ * `factors` has one word per prime of the context (compute_sud_factors layout,
+ * cerium/runtime/execution/function.cpp:685-732).  outs[b] may alias either input.  Results are
+ * canonical.
+ */
+CERIUM_API int cerium_sud_ptrs(cerium_context *ctx, void *const *outs, const void *const *ins,
+                               const uint32_t *bases, size_t num_bases, const void *factors, void *stream);
+
+/*
+ * Base conversion with the argument tables of the reference's launcher (_function_bco_<I, O>,
+ * cerium/compiler/backend/kernels/function.cuh:80-98, marshalled by Evaluator::fn_bco,
+ * cerium/runtime/execution/evaluator.cpp:861-940): all arrays are DEVICE resident.  Conversion j
+ * reads ins[j] = [n_in[j]][N] and writes outs[j] = [n_out[j]][N] with the factor matrix
+ * factors[j] = [n_out[j]][n_in[j]] (DeviceBaseConverter, evaluator.cpp:1539-1578) and the output
+ * primes out_moduli[j] = [n_out[j]]; no converter object and no prime index is involved.  max_in /
+ * max_out are HOST upper bounds of the shapes (they size the shared memory).  The reference's lazy
+ * conversion; results are canonical.
+ */
+CERIUM_API int cerium_bconv_ptrs(cerium_context *ctx, void *const *outs, const size_t *n_out,
+                                 const void *const *ins, const size_t *n_in, const void *const *factors,
+                                 const void *const *out_moduli, size_t max_in, size_t max_out,
+                                 size_t num_conversions, void *stream);
+
+/*
  * SuD: out[i] = (minuend[i] - NTT(in_coeff[i])) * [(prod divide primes)^-1] mod q_i,
  * optionally + addend[i] (addend may be NULL).  in_coeff holds coefficient-form residues
  * already reduced mod q_i.  out may alias minuend; in_coeff is overwritten (it is the

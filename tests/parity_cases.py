@@ -167,6 +167,67 @@ def case_ntt_ptrs(be, word_bits):
         assert np.array_equal(got[s], row)
 
 
+def case_sud_ptrs(be, word_bits):
+    """SuD with the reference launcher's tables: two device pointers per entry, factors per prime."""
+    mods = moduli_for(word_bits, 4, 1)
+    h = Harness(be, word_bits, mods)
+    rng = np.random.default_rng(71)
+    idx = [2, 0, 1, 2]
+    minuend, coeff = rand_limbs(rng, mods, idx), rand_limbs(rng, mods, idx)
+    fac = [int(rng.integers(1, m)) for m in mods]          # one residue per prime of the context
+    want = np.stack([h.orc.sud(p, minuend[i], coeff[i], fac[p]) for i, p in enumerate(idx)])
+    dm, dc, out = h.up(minuend), h.up(coeff), h.new(len(idx), N)
+    lb = N * h.ctx.word_bytes
+    ins = np.empty(2 * len(idx), dtype=np.uint64)
+    ins[0::2] = [h.p(dm) + i * lb for i in range(len(idx))]
+    ins[1::2] = [h.p(dc) + i * lb for i in range(len(idx))]
+    d_ins = be.to_dev(ins)
+    d_outs = be.to_dev(np.array([h.p(out) + i * lb for i in range(len(idx))], dtype=np.uint64))
+    d_bases = be.to_dev(np.array(idx, dtype=np.uint32))
+    wdt = np.uint32 if word_bits == 32 else np.uint64
+    d_fac = be.to_dev(np.array(fac, dtype=wdt))
+    h.ctx.sud_ptrs(be.ptr(d_outs), be.ptr(d_ins), be.ptr(d_bases), len(idx), be.ptr(d_fac))
+    assert np.array_equal(h.down(out), want)
+    # in place on the coefficient-form input, as the reference's stage 0 / stage 1 pair allows
+    d_outs2 = be.to_dev(ins[1::2].copy())
+    h.ctx.sud_ptrs(be.ptr(d_outs2), be.ptr(d_ins), be.ptr(d_bases), len(idx), be.ptr(d_fac))
+    assert np.array_equal(h.down(dc), want)
+
+
+def case_bconv_ptrs(be, word_bits):
+    """Base conversion from device tables only (shapes, factor matrices and output primes), two
+    conversions of different shape in one launch, one of them with more than eight inputs."""
+    n_mod = 14
+    mods = moduli_for(word_bits, n_mod, 0)
+    h = Harness(be, word_bits, mods)
+    rng = np.random.default_rng(72)
+    wdt = np.uint32 if word_bits == 32 else np.uint64
+    shapes = [([0, 1, 2], [3, 4, 5, 6, 7]), (list(range(9)), [9, 10, 11, 12, 13])]
+    keep, outs, ins, facs, omods, wants, d_out = [], [], [], [], [], [], []
+    for in_idx, out_idx in shapes:
+        x = rand_limbs(rng, mods, in_idx)
+        # F[j][i] = [Qhat_i^-1]_{q_i} * (Qhat_i mod p_j) mod p_j  (cerium/runtime/execution/evaluator.cpp:1539-1578)
+        qs, ps = [mods[i] for i in in_idx], [mods[j] for j in out_idx]
+        Q = 1
+        for q in qs:
+            Q *= q
+        fac = [[pow(Q // q % q, -1, q) % pj * (Q // q % pj) % pj for q in qs] for pj in ps]
+        wants.append(oracle.bconv(oracle.BCONV_LAZY, qs, x, ps))
+        dx, do = h.up(x), h.new(len(out_idx), N)
+        dfac = be.to_dev(np.asarray(fac, dtype=wdt).reshape(-1))
+        dmod = be.to_dev(np.array([mods[j] for j in out_idx], dtype=wdt))
+        keep += [dx, dfac, dmod]
+        d_out.append(do)
+        outs.append(h.p(do)); ins.append(h.p(dx)); facs.append(be.ptr(dfac)); omods.append(be.ptr(dmod))
+    t = lambda v: be.to_dev(np.array(v, dtype=np.uint64))
+    d_outs, d_ins, d_facs, d_omods = t(outs), t(ins), t(facs), t(omods)
+    d_nin, d_nout = t([len(a) for a, _ in shapes]), t([len(b) for _, b in shapes])
+    h.ctx.bconv_ptrs(be.ptr(d_outs), be.ptr(d_nout), be.ptr(d_ins), be.ptr(d_nin), be.ptr(d_facs), be.ptr(d_omods),
+                     9, 5, len(shapes))
+    for do, want in zip(d_out, wants):
+        assert np.array_equal(h.down(do), want)
+
+
 def case_ewise(be, word_bits):
     mods = moduli_for(word_bits, 3, 1)
     h = Harness(be, word_bits, mods)

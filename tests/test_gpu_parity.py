@@ -53,6 +53,12 @@ def test_sud(be, word_bits):
     pc.case_sud(be, word_bits)
 
 
+@pytest.mark.parametrize("word_bits", [32, 64])
+def test_reference_launcher_tables(be, word_bits):
+    pc.case_sud_ptrs(be, word_bits)
+    pc.case_bconv_ptrs(be, word_bits)
+
+
 def test_u32_widest_primes(be):
     pc.case_u32_widest_primes(be)
 
