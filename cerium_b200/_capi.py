@@ -37,6 +37,11 @@ SIGNATURES = {
     "cerium_ntt_inverse": (C.c_int, [_vp, _vp, _sz, _vp, _sz, _u32p, C.c_int, _vp]),
     "cerium_ntt_forward_ptrs": (C.c_int, [_vp, _vp, _vp, _vp, _sz, _vp]),
     "cerium_ntt_inverse_ptrs": (C.c_int, [_vp, _vp, _vp, _vp, _sz, _vp]),
+    "cerium_function_map_bind": (C.c_int, [_vp, C.c_int]),
+    "cerium_function_map_load": (C.c_int, [C.c_char_p, C.c_char_p]),
+    "cerium_function_map_size": (C.c_int, [C.c_int]),
+    "cerium_function_map_lookup": (_vp, [C.c_int, C.c_uint32]),
+    "cerium_function_map_launcher": (_vp, [C.c_char_p, C.c_int]),
     "cerium_sud_ptrs": (C.c_int, [_vp, _vp, _vp, _vp, _sz, _vp, _vp]),
     "cerium_bconv_ptrs": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _vp]),
     "cerium_sud": (C.c_int, [_vp, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _u32p, C.c_int, _u32p, C.c_int, _vp]),

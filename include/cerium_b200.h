@@ -380,6 +380,29 @@ CERIUM_API int cerium_probe_int_pipe(int device, double *gops, int n_results);
 CERIUM_API int cerium_rescale_static(cerium_context *ctx, int round_mode, void *out, const void *in,
                                      const uint32_t *q_idx, int L, int n_polys, void *stream);
 
+/*
+ * The reference runtime's plugin contract.  libcerium_b200.so also exports the two C++ getters the
+ * Cerium runtime resolves in a function_map_<p>.so, __GET_FUNCTION_MAP__ and
+ * __GET_FUNCTION_MAP_CUGRAPH__ (cerium/runtime/execution/function.cpp:144-177): installed under that
+ * name it maps the ids of the program's ntt / int / sud / bco records (read from the `functions<p>`
+ * file beside it) to launchers with the signatures of cerium/runtime/execution/device_utils.cu:33-113,
+ * stream and graph variants, backed by cerium_ntt_*_ptrs, cerium_sud_ptrs and cerium_bconv_ptrs.
+ * Launchers of other record types are taken from function_map_<p>.orig.so when it is present.
+ *
+ * cerium_function_map_bind     names the context whose tables the launchers use on `device`
+ *                              (NULL unbinds).  Bind before the first launch.
+ * cerium_function_map_load     fills the maps from an explicit functions file (and generated plugin,
+ *                              may be NULL) instead of the paths derived from the plugin's own name.
+ * cerium_function_map_size / _lookup / _launcher   inspect the maps (tests, diagnostics): number of
+ *                              entries, launcher of a kernel id, launcher of a record type
+ *                              ("ntt", "int", "sud", "bco").
+ */
+CERIUM_API int cerium_function_map_bind(cerium_context *ctx, int device);
+CERIUM_API int cerium_function_map_load(const char *functions_path, const char *generated_plugin_path);
+CERIUM_API int cerium_function_map_size(int cugraph);
+CERIUM_API void *cerium_function_map_lookup(int cugraph, uint32_t kernel_id);
+CERIUM_API void *cerium_function_map_launcher(const char *type, int cugraph);
+
 #ifdef __cplusplus
 }
 #endif
