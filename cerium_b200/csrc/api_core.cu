@@ -298,10 +298,29 @@ int create_bconv(cerium_context* ctx, cerium_bconv** out, int mode, const uint32
     }
     for (int j = 0; j < n_out; j++) out_sub[j] = half_mod(m[out_primes[j]]);
   }
-  // every input prime runs double-precision arithmetic and no rounding term is added: the kernel may
-  // compute the outputs of such primes on the FP64 pipe
-  bc->fp_in = bits == 64 && n_in <= kBconvRegInputs && ctx->allow_fp && in_add.empty();
-  for (int i = 0; i < n_in; i++) bc->fp_in = bc->fp_in && m[in_primes[i]] < ((uint64_t)1 << 50);
+  // 64-bit words, at most 8 inputs: outputs may take their quotient from the FP64 pipe.  The estimate
+  // c ~ sum_i y_i f_i / p_j (f_i centred) is off by at most e = (I + 2) 2^-53 sum_i q_i |f_i| / p_j + 1/2
+  // (rounding of RN(f_i / p_j), of y_i as a double, of every partial sum; then rounding to an integer),
+  // so |sum - c p_j| <= e p_j: class 1 when that is below 3 p_j, class 2 when it is below 2^62.
+  bc->fp_in = bits == 64 && n_in <= kBconvRegInputs && ctx->allow_fp;
+  std::vector<uint8_t> fp_class(n_out, 0);
+  if (bc->fp_in) {
+    bool any = false;
+    for (int j = 0; j < n_out; j++) {
+      const uint64_t pj = m[out_primes[j]];
+      long double b = 0.0L;
+      for (int i = 0; i < n_in; i++) {
+        const uint64_t f = factors[(size_t)j * n_in + i];
+        const uint64_t mag = f > pj / 2 ? pj - f : f;
+        b += (long double)m[in_primes[i]] * (long double)mag / (long double)pj;
+      }
+      const long double e = (long double)(n_in + 2) * b * 0x1p-53L + 0.5L;
+      if (e < 2.9L) fp_class[j] = 1;
+      else if ((e + 1.0L) * (long double)pj < 0x1p62L) fp_class[j] = 2;
+      any = any || fp_class[j] != 0;
+    }
+    bc->fp_in = any;
+  }
   const bool use_inv = mode == CERIUM_BCONV_EXACT && !opt.prescaled && n_in > 1;
   Blob blob;
   size_t o_fac = 0, o_inv = 0, o_invs = 0, o_add = 0, o_sub = 0;
@@ -331,7 +350,7 @@ int create_bconv(cerium_context* ctx, cerium_bconv** out, int mode, const uint32
       o.pos = opt.out_pos.empty() ? (uint32_t)j : opt.out_pos[j];
       o.has_sub = out_sub.empty() ? 0 : 1;
       o.strict = (ctx->lazy_ok[pj] && !ctx->fp_ok[pj]) ? 0 : 1;
-      o.fp = (split && bc->fp_in && ctx->fp_ok[pj] && out_sub.empty()) ? 1 : 0;
+      o.fp = (split && bc->fp_in) ? fp_class[j] : 0;
       const double qinv = 1.0 / (double)m[pj];
       uint64_t qinv_bits;
       std::memcpy(&qinv_bits, &qinv, 8);
@@ -346,9 +365,11 @@ int create_bconv(cerium_context* ctx, cerium_bconv** out, int mode, const uint32
     for (size_t k = 0; k < factors.size(); k++) {
       const uint64_t f = factors[k], q = m[out_primes[k / n_in]];
       sf[k] = make_uint2((uint32_t)f & 0x3fffffffu, (uint32_t)(f >> 30));
-      // centred factor and its correctly rounded quotient by q (IEEE division)
-      const double fd = f > q / 2 ? -(double)(q - f) : (double)f;
-      ff[k] = make_double2(fd, fd / (double)q);
+      // centred factor (as the bit pattern of an int64) and its quotient by q rounded to a double
+      const long long fc = f > q / 2 ? -(long long)(q - f) : (long long)f;
+      double fbits;
+      std::memcpy(&fbits, &fc, 8);
+      ff[k] = make_double2(fbits, (double)((long double)fc / (long double)q));
     }
     o_split = blob.append(sf.data(), sf.size() * sizeof(uint2));
     o_fpfac = blob.append(ff.data(), ff.size() * sizeof(double2));

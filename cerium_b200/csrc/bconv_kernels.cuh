@@ -50,10 +50,10 @@ struct BconvDesc {
   // and for the 64-bit split path the factors as 30-bit pieces and as double-precision pairs
   const BconvOut<W>* outc;    // [O]
   const uint2* split_fac;     // [O][I] or null
-  const double2* fp_fac;      // [O][I] {factor centred, RN(factor / q)} or null
+  const double2* fp_fac;      // [O][I] {bit pattern of the centred factor as int64, RN(centred factor / q)} or null
   int lazy_out;               // 64-bit split path only: leave outputs in [0, 8q) / [0, 4q) for the forward NTT
-  int fp_in;                  // 64-bit split path only: every input prime is below 2^50 and no rounding term is
-                              // added, so outputs whose prime is below 2^50 too are computed on the FP64 pipe
+  int fp_in;                  // 64-bit split path only: fp_fac is present and some outputs take their quotient
+                              // from the FP64 pipe (see bconv_body_split64)
   int I;
   int O;
 };
@@ -67,7 +67,8 @@ struct BconvOut {
   uint32_t pos;                // limb slot of this output
   uint16_t has_sub;            // rounding term present
   uint8_t strict;              // the prime's transform needs inputs below 4q (all but the lazy integer butterflies)
-  uint8_t fp;                  // this output is computed in double precision (see bconv_body_split64)
+  uint8_t fp;                  // 1 / 2: quotient estimated in double precision, without / with a second step
+                               // (see bconv_body_split64); 0: integer Barrett path
 };
 
 // Barrett reduction with the 3-multiply high products: qhat may be up to 7 short, so the
@@ -93,45 +94,61 @@ __device__ __forceinline__ W bconv_input(const BconvDesc<W>& d, const PrimeConst
   return v;
 }
 
-// 64-bit words, at most 8 inputs: residues and factors are split at bit 30 so that every
-// partial product is a 32x32->64 multiply-add into one of three column sums (y0*f0,
-// y0*f1 + y1*f0, y1*f1).  With pieces below 2^30 and at most 8 terms no column overflows, so
-// a multiply-accumulate is four IMAD.WIDE and no carry handling.
+// 64-bit words, at most 8 inputs.
 //
-// Outputs flagged `fp` (input and output primes below 2^50, no rounding terms) take the FP64 pipe
-// instead: each term is an exact double-precision modular product (fp_mulmod, modarith.cuh) of the
-// input, held as a double, with the centred factor; the sum of at most 8 terms of magnitude below
-// 0.6 q is exact, one fp_reduce brings it within q/2.  41 FP64 operations per output of 5 terms
-// against ~120 integer instructions, and the remaining integer outputs (60-bit primes) overlap
-// with them on the other pipe.  sfp holds {factor centred, RN(factor / q)} per (output, input).
+// Outputs flagged `fp` take the quotient from the FP64 pipe and the remainder from wrapping 64-bit
+// integer arithmetic: with S = sum_i y_i * f_i (f_i the factor centred in (-q/2, q/2]) the kernel
+// estimates c ~ S / q as the double-precision sum of y_i * RN(f_i / q), one FMA per term, rounds it to
+// an integer and forms r = S - c q modulo 2^64 (three IMAD per 64-bit product, no high words, no
+// carries).  r is the exact value of S - c q whenever |S - c q| < 2^63, i.e. whenever the estimate's
+// error e satisfies (e + 1) q < 2^63; the host bounds e per output when the converter is created
+// ((I + 2) 2^-53 sum_i q_i |f_i| / q) and sets fp = 1 when |r| < 3q is guaranteed (50-bit inputs:
+// e < 2.5), fp = 2 when a second quotient step is needed (60-bit inputs into 50-bit outputs:
+// |r| < 2^62; c2 = rint(r / q) in double precision, r -= c2 q), fp = 0 when neither holds (60-bit
+// inputs into 60-bit outputs).  5 FMA + 18 IMAD + two conversions per 5-term output instead of 41
+// FP64 operations (exact products on the FP64 pipe) or ~120 integer instructions (Barrett on a
+// 128-bit sum).  sfp holds {bit pattern of the centred factor as int64, RN(factor / q)} per (output, input).
+//
+// Outputs with fp = 0: residues and factors are split at bit 30 so that every partial product is a
+// 32x32->64 multiply-add into one of three column sums (y0*f0, y0*f1 + y1*f0, y1*f1).  With pieces
+// below 2^30 and at most 8 terms no column overflows, so a multiply-accumulate is four IMAD.WIDE and
+// no carry handling; one Barrett reduction of the 128-bit sum follows.
 template <int kI, bool kLazyOut>  // kI = exact number of inputs, 1..8
 __device__ __forceinline__ void bconv_body_split64(const BconvDesc<uint64_t>& d,
                                                    const PrimeConst<uint64_t>* __restrict__ pcs,
                                                    const uint2* sfac, const BconvOut<uint64_t>* sout,
                                                    const double2* sfp, int coeff) {
   const int O = d.O;
-  uint32_t y0[kI], y1[kI];
+  uint64_t y[kI];
   double yd[kI];
 #pragma unroll
   for (int i = 0; i < kI; i++) {
-    const uint64_t v = bconv_input<uint64_t>(d, pcs, i, coeff);
-    y0[i] = (uint32_t)v & 0x3fffffffu;
-    y1[i] = (uint32_t)(v >> 30);
-    yd[i] = d.fp_in ? fp_from_u64(v) : 0.0;
+    y[i] = bconv_input<uint64_t>(d, pcs, i, coeff);
+    yd[i] = d.fp_in ? __ull2double_rn(y[i]) : 0.0;
   }
 #pragma unroll 2
   for (int j = 0; j < O; j++) {
     if (sout[j].fp) {
       const BconvOut<uint64_t> o = sout[j];
       const double2* f = sfp + j * kI;
-      const double q = fp_from_u64(o.q), nq = -q;
-      double acc = 0.0;
+      double cf = __dmul_rn(yd[0], f[0].y);
+      uint64_t s = y[0] * (uint64_t)__double_as_longlong(f[0].x);
 #pragma unroll
-      for (int i = 0; i < kI; i++) acc = __dadd_rn(acc, fp_mulmod(yd[i], f[i].x, f[i].y, nq));
-      double r = fp_reduce(acc, __longlong_as_double((long long)o.fp_qinv), nq);
-      // lazy: (q/2, 3q/2) is as good as [0, q) for the forward transform that follows
-      if (kLazyOut || r < 0.0) r = __dadd_rn(r, q);
-      d.out[(size_t)o.pos * d.out_stride + coeff] = fp_to_u64(r);
+      for (int i = 1; i < kI; i++) {
+        cf = __fma_rn(yd[i], f[i].y, cf);
+        s += y[i] * (uint64_t)__double_as_longlong(f[i].x);
+      }
+      long long r = (long long)(s - (uint64_t)__double2ll_rn(cf) * o.q);
+      if (kLazyOut && o.fp == 1) {
+        // |r| < 3q: [0, 3q) is as good as [0, q) for the forward transform that follows
+        if (r < 0) r += (long long)(o.q2 + o.q);
+      } else {
+        const long long c2 = __double2ll_rn(__dmul_rn(__ll2double_rn(r), __longlong_as_double((long long)o.fp_qinv)));
+        r -= c2 * (long long)o.q;  // within q/2 of zero (and a rounding sliver)
+        if (r < 0) r += (long long)o.q;
+        if (o.has_sub) r = (long long)sub_mod<uint64_t>((uint64_t)r, o.sub, o.q);
+      }
+      d.out[(size_t)o.pos * d.out_stride + coeff] = (uint64_t)r;
       continue;
     }
     const uint2* f = sfac + j * kI;
@@ -139,10 +156,11 @@ __device__ __forceinline__ void bconv_body_split64(const BconvDesc<uint64_t>& d,
 #pragma unroll
     for (int i = 0; i < kI; i++) {
       const uint2 fi = f[i];
-      c0 += (uint64_t)y0[i] * fi.x;
-      c1 += (uint64_t)y0[i] * fi.y;
-      c1 += (uint64_t)y1[i] * fi.x;
-      c2 += (uint64_t)y1[i] * fi.y;
+      const uint32_t y0 = (uint32_t)y[i] & 0x3fffffffu, y1 = (uint32_t)(y[i] >> 30);
+      c0 += (uint64_t)y0 * fi.x;
+      c1 += (uint64_t)y0 * fi.y;
+      c1 += (uint64_t)y1 * fi.x;
+      c2 += (uint64_t)y1 * fi.y;
     }
     // value = c0 + c1 * 2^30 + c2 * 2^60 as hi:lo (128-bit adds: carry chains, no compares)
 #if defined(CERIUM_EMU)

@@ -67,6 +67,9 @@ static inline unsigned long long __umul64hi(unsigned long long a, unsigned long 
 static inline double __dmul_rn(double a, double b) { return a * b; }
 static inline double __dadd_rn(double a, double b) { return a + b; }
 static inline double __fma_rn(double a, double b, double c) { return std::fma(a, b, c); }
+static inline long long __double2ll_rn(double x) { return std::llrint(x); }  // default rounding mode: to nearest even
+static inline double __ll2double_rn(long long x) { return (double)x; }
+static inline double __ull2double_rn(unsigned long long x) { return (double)x; }
 static inline double __longlong_as_double(long long x) { double d; std::memcpy(&d, &x, 8); return d; }
 static inline long long __double_as_longlong(double d) { long long x; std::memcpy(&x, &d, 8); return x; }
 static inline unsigned __brev(unsigned x) {
