@@ -47,9 +47,9 @@ from cerium_b200 import params  # noqa: E402
 LOGN = 16
 N = 1 << LOGN
 # dram__bytes_read.sum + dram__bytes_write.sum of the forward-NTT launch pair from the ncu capture
-# summarised in profiles/hrot_u64_top_kernels_ncu_full.md: 495.7 MB for 245 u64 limbs (traffic grows
+# summarised in profiles/hrot_u64_top_kernels_ncu_full.md: 443.2 MB for 245 u64 limbs (traffic grows
 # in proportion to the limbs transformed)
-NTT_PAIR_DRAM_BYTES_PER_LIMB = 495.7e6 / 245
+NTT_PAIR_DRAM_BYTES_PER_LIMB = 443.2e6 / 245
 
 
 def env_int(name, default):
