@@ -414,6 +414,7 @@ int launch_bconv(cerium_context* ctx, const BconvCall* calls, int count, cudaStr
       BconvBatch<W> batch{};
       size_t smem = 0;
       int max_o = 1;
+      bool pair = sizeof(W) == 4;  // two coefficients per thread (see bconv_body_pair32)
       for (int k = 0; k < cnt; k++) {
         const BconvCall& c = calls[first + k];
         const cerium_bconv* bc = c.bc;
@@ -440,24 +441,28 @@ int launch_bconv(cerium_context* ctx, const BconvCall* calls, int count, cudaStr
         d.O = bc->O;
         smem = std::max(smem, bconv_smem_bytes<W>(bc->I, bc->O));
         max_o = std::max(max_o, bc->O);
+        pair = pair && bc->I <= kBconvRegInputs && ((uintptr_t)c.in | (uintptr_t)c.out) % 8 == 0 &&
+               (c.in_stride * sizeof(W)) % 8 == 0 && (c.out_stride * sizeof(W)) % 8 == 0;
       }
       if (smem > 48 * 1024) {
         if (smem > 200 * 1024) return fail(CERIUM_ERR_UNSUPPORTED, "bconv: conversion needs more than 200 KiB of shared memory");
         const int slot = sizeof(W) == 4 ? 0 : 1;
         if (!smem_opt_in[slot]) {
-          CERIUM_CUDA(cudaFuncSetAttribute(bconv_kernel<W>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+          CERIUM_CUDA(cudaFuncSetAttribute(bconv_kernel<W, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+          CERIUM_CUDA(cudaFuncSetAttribute(bconv_kernel<W, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
           smem_opt_in[slot] = true;
         }
       }
       {
         // grid.z splits the outputs of a conversion over nz CTAs (each reloads the inputs and restages its
         // tables): take the nz in 1..4 with the best waves x per-CTA-work estimate on this GPU
-        auto kfn = bconv_kernel<W>;
+        auto kfn = pair ? bconv_kernel<W, true> : bconv_kernel<W, false>;
+        const int blocks = pair ? (kBconvBlocks + 1) / 2 : kBconvBlocks;
         const int slots = 5 * ctx->sm_count;
         int nz = 1;
         double best = 1e30;
         for (int cand = 1; cand <= std::min(4, (max_o + 3) / 4); cand++) {
-          const int ctas = kBconvBlocks * cnt * cand;
+          const int ctas = blocks * cnt * cand;
           const double cost = (double)((ctas + slots - 1) / slots) * (1.0 / cand + 0.15);
           if (cost < best - 1e-9) {
             best = cost;
@@ -465,7 +470,7 @@ int launch_bconv(cerium_context* ctx, const BconvCall* calls, int count, cudaStr
           }
         }
         const int out_chunk = (max_o + nz - 1) / nz;
-        CERIUM_LAUNCH(kfn, dim3(kBconvBlocks, cnt, (max_o + out_chunk - 1) / out_chunk), kBconvThreads, smem, stream,
+        CERIUM_LAUNCH(kfn, dim3(blocks, cnt, (max_o + out_chunk - 1) / out_chunk), kBconvThreads, smem, stream,
                       batch, out_chunk, static_cast<const PrimeConst<W>*>(ctx->d_pcs));
       }
     }

@@ -82,16 +82,22 @@ __device__ __forceinline__ uint64_t barrett2_fast(uint64_t hi, uint64_t lo, uint
   return csub<uint64_t>(r, q);
 }
 
+// rounding term and [Qhat_i^-1] applied to a residue of input i as it is read
 template <typename W>
-__device__ __forceinline__ W bconv_input(const BconvDesc<W>& d, const PrimeConst<W>* __restrict__ pcs, int i,
-                                         int coeff) {
-  W v = d.in[(size_t)(d.in_pos != nullptr ? d.in_pos[i] : (uint32_t)i) * d.in_stride + coeff];
+__device__ __forceinline__ W bconv_prepare(const BconvDesc<W>& d, const PrimeConst<W>* __restrict__ pcs, int i, W v) {
   if (d.in_add != nullptr || d.inv != nullptr) {
     const W qi = pcs[d.in_prime[i]].q;
     if (d.in_add != nullptr) v = add_mod<W>(v, d.in_add[i], qi);
     if (d.inv != nullptr) v = csub<W>(mul_shoup_lazy<W>(v, d.inv[i], d.inv_shoup[i], qi), qi);
   }
   return v;
+}
+
+template <typename W>
+__device__ __forceinline__ W bconv_input(const BconvDesc<W>& d, const PrimeConst<W>* __restrict__ pcs, int i,
+                                         int coeff) {
+  return bconv_prepare<W>(d, pcs, i,
+                          d.in[(size_t)(d.in_pos != nullptr ? d.in_pos[i] : (uint32_t)i) * d.in_stride + coeff]);
 }
 
 // 64-bit words, at most 8 inputs.
@@ -206,13 +212,26 @@ __device__ __forceinline__ void bconv_body(const BconvDesc<W>& d, const PrimeCon
 #pragma unroll 2
   for (int j = 0; j < O; j++) {
     const W* f = sfac + j * I;
-    Acc2<W> acc;
-    acc.clear();
-    if (kRegI > 0) {
+    W acc_hi, acc_lo;
+    if (sizeof(W) == 4 && kRegI > 0) {
+      // 32-bit words, at most 8 terms below 2^60 each: the sum fits one 64-bit register, so a
+      // multiply-accumulate is a single wide multiply-add
+      uint64_t a64 = 0;
 #pragma unroll
-      for (int i = 0; i < kRegI; i++) acc.mad(y[i], f[i]);
+      for (int i = 0; i < kRegI; i++) a64 += (uint64_t)y[i] * (uint64_t)f[i];
+      acc_hi = (W)(a64 >> 32);
+      acc_lo = (W)a64;
     } else {
-      for (int i = 0; i < I; i++) acc.mad(scol[i * kBconvThreads + tid], f[i]);
+      Acc2<W> acc;
+      acc.clear();
+      if (kRegI > 0) {
+#pragma unroll
+        for (int i = 0; i < kRegI; i++) acc.mad(y[i], f[i]);
+      } else {
+        for (int i = 0; i < I; i++) acc.mad(scol[i * kBconvThreads + tid], f[i]);
+      }
+      acc_hi = acc.hi();
+      acc_lo = acc.lo();
     }
     const BconvOut<W> o = sout[j];
     PrimeConst<W> pc;
@@ -220,9 +239,52 @@ __device__ __forceinline__ void bconv_body(const BconvDesc<W>& d, const PrimeCon
     pc.q2 = o.q2;
     pc.mu_hi = o.mu_hi;
     pc.mu_lo = o.mu_lo;
-    W r = barrett2<W>(acc.hi(), acc.lo(), pc);
+    W r = barrett2<W>(acc_hi, acc_lo, pc);
     if (o.has_sub) r = sub_mod<W>(r, o.sub, o.q);
     d.out[(size_t)o.pos * d.out_stride + coeff] = r;
+  }
+}
+
+// 32-bit words, at most 8 inputs, every limb 8-byte aligned: a thread converts the two coefficients
+// coeff, coeff + 1 (coeff even) with 8-byte loads and stores, so the factor row and the output's
+// constants are fetched from shared memory once per pair; the sum of at most 8 products below 2^60
+// fits one 64-bit register (a multiply-accumulate is one wide multiply-add).
+template <int kRegI>
+__device__ __forceinline__ void bconv_body_pair32(const BconvDesc<uint32_t>& d,
+                                                  const PrimeConst<uint32_t>* __restrict__ pcs, const uint32_t* sfac,
+                                                  const BconvOut<uint32_t>* sout, int coeff) {
+  uint32_t ya[kRegI], yb[kRegI];
+#pragma unroll
+  for (int i = 0; i < kRegI; i++) {
+    const uint2 v = *reinterpret_cast<const uint2*>(
+        d.in + (size_t)(d.in_pos != nullptr ? d.in_pos[i] : (uint32_t)i) * d.in_stride + coeff);
+    ya[i] = bconv_prepare<uint32_t>(d, pcs, i, v.x);
+    yb[i] = bconv_prepare<uint32_t>(d, pcs, i, v.y);
+  }
+  const int O = d.O;
+#pragma unroll 2
+  for (int j = 0; j < O; j++) {
+    const uint32_t* f = sfac + j * kRegI;
+    uint64_t a = 0, b = 0;
+#pragma unroll
+    for (int i = 0; i < kRegI; i++) {
+      const uint64_t fi = f[i];
+      a += (uint64_t)ya[i] * fi;
+      b += (uint64_t)yb[i] * fi;
+    }
+    const BconvOut<uint32_t> o = sout[j];
+    PrimeConst<uint32_t> pc;
+    pc.q = o.q;
+    pc.q2 = o.q2;
+    pc.mu_hi = o.mu_hi;
+    pc.mu_lo = o.mu_lo;
+    uint32_t ra = barrett2<uint32_t>((uint32_t)(a >> 32), (uint32_t)a, pc);
+    uint32_t rb = barrett2<uint32_t>((uint32_t)(b >> 32), (uint32_t)b, pc);
+    if (o.has_sub) {
+      ra = sub_mod<uint32_t>(ra, o.sub, o.q);
+      rb = sub_mod<uint32_t>(rb, o.sub, o.q);
+    }
+    *reinterpret_cast<uint2*>(d.out + (size_t)o.pos * d.out_stride + coeff) = make_uint2(ra, rb);
   }
 }
 
@@ -247,7 +309,9 @@ __host__ __device__ inline size_t bconv_smem_bytes(int I, int O) {
 // grid = (ceil(N / kBconvThreads), conversions, ceil(max O / out_chunk)), block = kBconvThreads,
 // dynamic smem = max bconv_smem_bytes over the batch.  CTA z handles outputs
 // [z * out_chunk, min(O, (z + 1) * out_chunk)) of its conversion.
-template <typename W>
+// kPair (32-bit words only, every conversion of the batch with at most 8 inputs and 8-byte aligned
+// limbs): two coefficients per thread, grid.x = ceil(N / (2 kBconvThreads)).
+template <typename W, bool kPair>
 __global__ void __launch_bounds__(kBconvThreads, 5)
     bconv_kernel(const BconvBatch<W> batch, const int out_chunk, const PrimeConst<W>* __restrict__ pcs) {
   CERIUM_DYN_SMEM(smem_raw);
@@ -278,6 +342,25 @@ __global__ void __launch_bounds__(kBconvThreads, 5)
   for (int j = threadIdx.x; j < O; j += kBconvThreads) sout[j] = d.outc[j_first + j];
   grid_dependency_wait();  // the tables above never change; the input limbs below come from the previous kernel
   __syncthreads();
+  if (kPair && sizeof(W) == 4) {
+    const int coeff = (blockIdx.x * kBconvThreads + threadIdx.x) * 2;
+    if (coeff >= kN) return;  // partial last block (after the only barrier)
+    const BconvDesc<uint32_t>& d32 = reinterpret_cast<const BconvDesc<uint32_t>&>(d);
+    const PrimeConst<uint32_t>* p32 = reinterpret_cast<const PrimeConst<uint32_t>*>(pcs);
+    const uint32_t* f32 = reinterpret_cast<const uint32_t*>(sfac);
+    const BconvOut<uint32_t>* so = reinterpret_cast<const BconvOut<uint32_t>*>(sout);
+    switch (I) {
+      case 1: bconv_body_pair32<1>(d32, p32, f32, so, coeff); break;
+      case 2: bconv_body_pair32<2>(d32, p32, f32, so, coeff); break;
+      case 3: bconv_body_pair32<3>(d32, p32, f32, so, coeff); break;
+      case 4: bconv_body_pair32<4>(d32, p32, f32, so, coeff); break;
+      case 5: bconv_body_pair32<5>(d32, p32, f32, so, coeff); break;
+      case 6: bconv_body_pair32<6>(d32, p32, f32, so, coeff); break;
+      case 7: bconv_body_pair32<7>(d32, p32, f32, so, coeff); break;
+      default: bconv_body_pair32<8>(d32, p32, f32, so, coeff); break;
+    }
+    return;
+  }
   const int coeff = blockIdx.x * kBconvThreads + threadIdx.x;
   if (coeff >= kN) return;  // partial last block (after the only barrier)
   if (sizeof(W) == 8 && I <= kBconvRegInputs) {
