@@ -133,5 +133,27 @@ def test_timing_against_reference_kernels(env, capsys):
     torch.cuda.synchronize()
     mods = np.array([P[j] for j in out_idx] * 7, dtype=np.uint32)[:, None]
     assert np.array_equal(o_ref.cpu().numpy().view(np.uint32) % mods, o_ours.cpu().numpy().view(np.uint32))
+    # SuD tail over 70 limbs (two polynomials of 35), the reference launcher's tables on both sides
+    sidx = [l for _ in range(2) for l in range(35)]
+    fac = [(i * 2654435761 + 12345) % P[i] for i in range(len(P))]           # one residue per prime
+    m1, c2 = x[:70].contiguous(), x[70:140].contiguous()
+    for r_, l in enumerate(sidx):                                            # residues of the right primes
+        m1[r_] = (x[r_ + 140].to(torch.int64) % P[l]).to(torch.int32)
+        c2[r_] = (x[r_ + 210].to(torch.int64) % P[l]).to(torch.int32)
+    s_ref, s_ours = torch.empty_like(m1), torch.empty_like(m1)
+    ref.sud(s_ref.data_ptr(), m1.data_ptr(), c2.data_ptr(), sidx, fac, 3)
+    res["ref_sud_70_ms"] = ref.sud(s_ref.data_ptr(), m1.data_ptr(), c2.data_ptr(), sidx, fac, 20) / 20
+    lb = N * 4
+    pair = np.empty(140, dtype=np.uint64)
+    pair[0::2] = [m1.data_ptr() + i * lb for i in range(70)]
+    pair[1::2] = [c2.data_ptr() + i * lb for i in range(70)]
+    d_pair = be.to_dev(pair)
+    d_outs = be.to_dev(np.array([s_ours.data_ptr() + i * lb for i in range(70)], dtype=np.uint64))
+    d_bases = be.to_dev(np.array(sidx, dtype=np.uint32))
+    d_fac = be.to_dev(np.array(fac, dtype=np.uint32))
+    res["ours_sud_70_ms"] = timed(lambda: ctx.sud_ptrs(be.ptr(d_outs), be.ptr(d_pair), be.ptr(d_bases), 70, be.ptr(d_fac)))
+    torch.cuda.synchronize()
+    smods = np.array([P[l] for l in sidx], dtype=np.uint32)[:, None]
+    assert np.array_equal(s_ref.cpu().numpy().view(np.uint32) % smods, s_ours.cpu().numpy().view(np.uint32))
     with capsys.disabled():
         print("\nREF_CUDA_TIMING " + json.dumps(res))
