@@ -128,7 +128,7 @@ struct cerium_bconv {
   uint32_t* d_in_pos = nullptr;   // or null
   bool lazy_out = false;
   std::vector<uint64_t> inv_host;  // [Qhat_i^-1]_{q_i}
-  bool fp_in = false;              // inputs qualify for the double-precision outputs of the kernel
+  bool fp_in = false;              // some outputs take their quotient from the FP64 pipe (d_fp_fac is present)
 };
 
 namespace cerium {

@@ -271,7 +271,10 @@ CERIUM_API int cerium_keyswitch_apply(cerium_keyswitch *ks, void *out0, void *ou
 
 /*
  * HRot: (out0,out1) = KeySwitch(phi(c1)) + (phi(c0), 0), phi the automorphism galois_elt.
- * Restates rotate_internal (cerium/compiler/backend/compiler.cc:701-726).
+ * Restates rotate_internal (cerium/compiler/backend/compiler.cc:701-726).  The rotated
+ * polynomials are never materialised: the kernels of the key switch read c0 and c1 through the
+ * automorphism's index map.  When an output overlaps an input (in-place rotation) the library
+ * rotates into its workspace first, one more launch; both give the same result.
  */
 CERIUM_API int cerium_hrot(cerium_keyswitch *ks, void *out0, void *out1, const void *c0, const void *c1,
                 const void *evk, uint32_t galois_elt, void *stream);
@@ -287,6 +290,7 @@ CERIUM_API int cerium_hrot(cerium_keyswitch *ks, void *out0, void *out1, const v
  * evk_pre is the rotation key of phi with every limb pre-permuted by phi^-1 (the reference's
  * "RotationInv" key): phi(sum_d a_d * phi^-1(k_d)) = sum_d phi(a_d) * k_d.  c1 must be the
  * polynomial given to cerium_hoisted_begin; any number of rotate calls may follow one begin.
+ * The automorphism is the store pattern of the last kernel unless an output overlaps an input.
  */
 CERIUM_API int cerium_hoisted_begin(cerium_keyswitch *ks, const void *c1, void *stream);
 CERIUM_API int cerium_hoisted_rotate(cerium_keyswitch *ks, void *out0, void *out1, const void *c0,
