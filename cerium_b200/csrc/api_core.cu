@@ -135,6 +135,13 @@ int launch_sud(cerium_context* ctx, const SudCall& c, cudaStream_t stream) {
     constexpr int kCols = NttCfg<W>::kCols;
     const int bits = ctx->word_bits;
     if (c.split > 0 && c.count > kSudMaxBatch) return fail(CERIUM_ERR_INVALID, "sud: a two-polynomial launch holds at most 96 limbs");
+    {
+      // the tail reads minuend and addend as 16-byte vectors
+      const size_t wb = sizeof(W);
+      const uintptr_t ptrs = (uintptr_t)c.minuend | (uintptr_t)c.minuend2 | (uintptr_t)c.addend | (uintptr_t)c.addend2;
+      if (ptrs % 16 != 0 || (c.minuend_stride * wb) % 16 != 0 || (c.addend != nullptr && (c.addend_stride * wb) % 16 != 0))
+        return fail(CERIUM_ERR_INVALID, "sud: minuend and addend limbs must be 16-byte aligned");
+    }
     for (int first = 0; first < c.count; first += kSudMaxBatch) {
       const int cnt = std::min(kSudMaxBatch, c.count - first);
       StridedBatch<W> cols{};

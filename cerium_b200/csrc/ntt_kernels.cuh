@@ -588,11 +588,9 @@ template <typename W>
 struct StoreEpilogue {
   static constexpr bool kCanonicalInput = true;
   __device__ __forceinline__ uint32_t scatter_elt() const { return 0u; }
+  template <int kWords>
+  __device__ __forceinline__ void apply_vec(W (&)[kWords], int, int, uint32_t, const PrimeConst<W>&) const {}
   __device__ __forceinline__ void prefetch(int /*b*/, int /*idx*/) const {}
-  __device__ __forceinline__ W apply(W x, int /*b*/, int /*idx*/, uint32_t /*pi*/,
-                                     const PrimeConst<W>& /*pc*/) const {
-    return x;
-  }
 };
 
 // Stores the transform below 4q.  Only for buffers whose one reader multiplies the values into a
@@ -601,11 +599,9 @@ template <typename W>
 struct LazyStoreEpilogue {
   static constexpr bool kCanonicalInput = false;
   __device__ __forceinline__ uint32_t scatter_elt() const { return 0u; }
+  template <int kWords>
+  __device__ __forceinline__ void apply_vec(W (&)[kWords], int, int, uint32_t, const PrimeConst<W>&) const {}
   __device__ __forceinline__ void prefetch(int /*b*/, int /*idx*/) const {}
-  __device__ __forceinline__ W apply(W x, int /*b*/, int /*idx*/, uint32_t /*pi*/,
-                                     const PrimeConst<W>& /*pc*/) const {
-    return x;
-  }
 };
 
 // SuD tail: out = (minuend - NTT(in)) * factor[b] [+ addend]   (all mod q).
@@ -636,26 +632,52 @@ struct SudEpilogue {
     const W* ap = second ? addend2 : addend;
     if (ap != nullptr && addend_elt == 0) prefetch_l2(ap + (size_t)e * addend_stride + idx);
   }
-  __device__ __forceinline__ W apply(W x, int b, int idx, uint32_t /*pi*/,
-                                     const PrimeConst<W>& pc) const {
+  // The kWords results of one 16-byte vector (idx0 a multiple of kWords): minuend and addend come in
+  // as one 16-byte load each.  With an automorphism the aligned group idx0 .. idx0 + kWords - 1 is the
+  // image of ONE aligned group of the addend (the index map sends aligned 2^k blocks onto aligned 2^k
+  // blocks), so that is one load as well and the words are picked from it.
+  template <int kWords>
+  __device__ __forceinline__ void apply_vec(W (&w)[kWords], int b, int idx0, uint32_t /*pi*/,
+                                            const PrimeConst<W>& pc) const {
+    using Vec = typename RowVec<W>::Vec;
     const bool second = b >= split;
-    const int e = second ? b - split : b;
-    const W* mp = second ? minuend2 : minuend;
+    const int e_ = second ? b - split : b;
+    const W* mp = (second ? minuend2 : minuend) + (size_t)e_ * minuend_stride;
     const W* ap = second ? addend2 : addend;
-    const W m = mp[(size_t)e * minuend_stride + idx];
-    W d;
-    if (sizeof(W) == 4) {
-      // 32-bit words hold primes up to 2^30: m + 4q would pass 2^32, so x comes below 2q first
-      d = m + pc.q2 - csub<W>(x, pc.q2);
-    } else {
-      d = m + (pc.q2 + pc.q2) - x;  // x < 4q: positive, and the Shoup product takes any word
-    }
-    d = csub<W>(mul_shoup_lazy<W>(d, factor[b], factor_shoup[b], pc.q), pc.q);
+    W m[kWords], a[kWords] = {};
+    vec_unpack(*reinterpret_cast<const Vec*>(mp + idx0), m);
     if (ap != nullptr) {
-      const uint32_t at = addend_elt != 0 ? galois_source_index((uint32_t)idx, addend_elt) : (uint32_t)idx;
-      d = add_mod<W>(d, ap[(size_t)e * addend_stride + at], pc.q);
+      ap += (size_t)e_ * addend_stride;
+      if (addend_elt != 0) {
+        uint32_t src[kWords];
+#pragma unroll
+        for (int e = 0; e < kWords; e++) src[e] = galois_source_index((uint32_t)(idx0 + e), addend_elt);
+        W t[kWords];
+        vec_unpack(*reinterpret_cast<const Vec*>(ap + (src[0] & ~(uint32_t)(kWords - 1))), t);
+#pragma unroll
+        for (int e = 0; e < kWords; e++) {
+          a[e] = t[0];
+#pragma unroll
+          for (int k = 1; k < kWords; k++)
+            if ((src[e] & (uint32_t)(kWords - 1)) == (uint32_t)k) a[e] = t[k];
+        }
+      } else {
+        vec_unpack(*reinterpret_cast<const Vec*>(ap + idx0), a);
+      }
     }
-    return d;
+#pragma unroll
+    for (int e = 0; e < kWords; e++) {
+      W d;
+      if (sizeof(W) == 4) {
+        // 32-bit words hold primes up to 2^30: m + 4q would pass 2^32, so the transform comes below 2q first
+        d = m[e] + pc.q2 - csub<W>(w[e], pc.q2);
+      } else {
+        d = m[e] + (pc.q2 + pc.q2) - w[e];  // w < 4q: positive, and the Shoup product takes any word
+      }
+      d = csub<W>(mul_shoup_lazy<W>(d, factor[b], factor_shoup[b], pc.q), pc.q);
+      if (ap != nullptr) d = add_mod<W>(d, a[e], pc.q);
+      w[e] = d;
+    }
   }
 };
 
@@ -670,6 +692,12 @@ struct PtrSudEpilogue {
   const W* factors;
   __device__ __forceinline__ uint32_t scatter_elt() const { return 0u; }
   __device__ __forceinline__ void prefetch(int b, int idx) const { prefetch_l2(ins[2 * b] + idx); }
+  template <int kWords>
+  __device__ __forceinline__ void apply_vec(W (&w)[kWords], int b, int idx0, uint32_t pi,
+                                            const PrimeConst<W>& pc) const {
+#pragma unroll
+    for (int e = 0; e < kWords; e++) w[e] = apply(w[e], b, idx0 + e, pi, pc);  // caller's limbs may be unaligned
+  }
   __device__ __forceinline__ W apply(W x, int b, int idx, uint32_t pi, const PrimeConst<W>& pc) const {
     const W m = ins[2 * b][idx];
     // x < 4q and m < q: bring the difference to [0, q) before the Barrett product
@@ -763,7 +791,7 @@ __device__ __forceinline__ void ntt_fwd_rows_body(const Batch& batch, const Epil
     W w[RV::kWords];
     vec_unpack(vrow[row_vec_slot<W>(v)], w);
 #pragma unroll
-    for (int e = 0; e < RV::kWords; e++) w[e] = epi.apply(w[e], b, h * 256 + v * RV::kWords + e, pi, pc);
+    epi.apply_vec(w, b, h * 256 + v * RV::kWords, pi, pc);
     if (selt != 0) {
       // the row's aligned 256-word block lands on one aligned block of the output limb
 #pragma unroll
