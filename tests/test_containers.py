@@ -93,3 +93,35 @@ def test_malformed_files_are_refused(tmp_path):
         ct.read(str(tmp_path / "bad.bin"))
     with pytest.raises(ValueError, match="polynomials"):
         ct.write(str(tmp_path / "w.bin"), ct.Container("plaintexts", 16, [97], {"x": c.entries["x"]}))
+
+
+def test_key_from_a_container_drives_a_rotation(tmp_path):
+    """A rotation key written digit by digit in the reference's file layout, read back and stacked by
+    evalkey_tensor, gives the oracle's HRot when handed to the library (CPU build of the library sources)."""
+    from cerium_b200 import _capi
+    from tests import parity_cases as pc
+    from tests.backends import EmuBackend
+    be = EmuBackend()
+    L, K, dnum = 4, 2, 2
+    prm = pc.small_params(32, L, K, dnum)
+    order = prm.q_idx + prm.p_idx
+    h = pc.Harness(be, 32, prm.moduli)
+    rng = np.random.default_rng(44)
+    c0, c1, evk = pc.make_keyswitch_inputs(rng, prm)
+    ks = _capi.KeySwitch(h.ctx, prm.q_idx, prm.p_idx, dnum, _capi.BCONV_LAZY, _capi.ROUND_FLOOR)
+    # digit d owns the Q limbs d, d + dnum, ... (the reference's strided split)
+    c = ct.Container("evalkeys", pc.N, [int(m) for m in prm.moduli])
+    for d in reversed(range(dnum)):
+        name = "1:%d:%d:5:[%s]" % (L, K, ",".join(str(prm.q_idx[i]) for i in range(d, L, dnum)))
+        c.entries[name] = ct.Entry(name, [[(order[k], evk[d, p, k].astype(np.uint32)) for k in range(len(order))]
+                                          for p in range(2)])
+    path = str(tmp_path / "evk.bin")
+    ct.write(path, c)
+    key = ct.evalkey_tensor(ct.read(path), 1, L, K, 5, order)
+    assert key.shape == (dnum, 2, L + K, pc.N) and np.array_equal(key, evk.astype(np.uint32))
+    elt = be.lib.galois_elt_from_step(5, pc.LOGN)
+    d_c0, d_c1, d_evk = h.up(c0), h.up(c1), h.up(key.astype(np.uint64))
+    o0, o1 = h.new(L, pc.N), h.new(L, pc.N)
+    ks.hrot(h.p(o0), h.p(o1), h.p(d_c0), h.p(d_c1), h.p(d_evk), elt)
+    w0, w1 = h.orc.hrot(_capi.BCONV_LAZY, _capi.ROUND_FLOOR, prm.q_idx, prm.p_idx, dnum, elt, c0, c1, evk)
+    assert np.array_equal(h.down(o0), w0) and np.array_equal(h.down(o1), w1)
