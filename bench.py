@@ -50,6 +50,9 @@ N = 1 << LOGN
 # summarised in profiles/hrot_u64_top_kernels_ncu_full.md: 443.2 MB for 245 u64 limbs (traffic grows
 # in proportion to the limbs transformed)
 NTT_PAIR_DRAM_BYTES_PER_LIMB = 443.2e6 / 245
+# what the CPU figure is: the checker, not a tuned evaluator
+PORT_QUALITY = ("unoptimised checker: plain-C restatement with a 128-bit remainder in every modular product outside "
+                "the transforms; a Barrett/Shoup CPU evaluator would be several times faster")
 
 
 def env_int(name, default):
@@ -65,6 +68,25 @@ def measured_peaks():
         with open(p) as f:
             return float(json.load(f)["hbm_gbs"]), "measured"
     return 6650.0, "fallback"
+
+
+PROBE_NAMES = ("mad.lo.u32", "mad.wide.u32", "mul.hi.u64", "mul.lo.u64", "add.u64", "butterfly_u64_strict",
+               "butterfly_u64_lazy", "butterfly_u32", "fma.rn.f64", "butterfly_u64_fp64")
+
+
+def probe_int_pipe(device):
+    """Register-only instruction / butterfly rates in Gop/s on `device` (the arithmetic roofline of
+    the 64-bit kernels), from the bench-side probe library built next to the evaluation library."""
+    import ctypes
+    from cerium_b200 import build as cbuild
+    dll = ctypes.CDLL(cbuild.PROBE_LIB)
+    dll.cerium_probe_int_pipe.restype = ctypes.c_int
+    dll.cerium_probe_int_pipe.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_double), ctypes.c_int]
+    dll.cerium_probe_last_error.restype = ctypes.c_char_p
+    buf = (ctypes.c_double * 10)()
+    if dll.cerium_probe_int_pipe(device, buf, 10) != 0:
+        raise RuntimeError("probe: " + dll.cerium_probe_last_error().decode())
+    return dict(zip(PROBE_NAMES, [float(v) for v in buf]))
 
 
 class ClockSampler:
@@ -208,6 +230,22 @@ class HRotWorkload(Workload):
         self.i += 1
         self._hrot(self.cts[k], self.outs[k])
 
+    def verify(self, orc_mod):
+        """One operation on the benchmark's own inputs against the oracle, every limb bit for bit
+        (outside the timed region).  Sharded: every rank checks its own limbs."""
+        torch, prm = self.torch, self.prm
+        if self.sharded:
+            return None   # the sharded leg is compared with the one-GPU result by its caller
+        ct, out = self.cts[0], self.outs[0]
+        self._hrot(ct, out)
+        torch.cuda.synchronize()
+        u = lambda t: t.cpu().numpy().view(np.uint64)  # noqa: E731
+        octx = orc_mod.OracleContext(LOGN, prm.moduli)
+        w0, w1 = octx.hrot(orc_mod.BCONV_EXACT, orc_mod.ROUND_HALF, prm.q_idx, prm.p_idx, prm.dnum, self.elt,
+                           u(ct[0]), u(ct[1]), u(self.evk))
+        got = u(out)
+        return bool(np.array_equal(got[0], w0) and np.array_equal(got[1], w1))
+
     def e2e_step(self):
         if self.sharded:
             ct, out = self.cts[0], self.outs[0]
@@ -308,6 +346,17 @@ class HMultWorkload(Workload):
         self.ks.hmult(o[0].data_ptr(), o[1].data_ptr(), a[0].data_ptr(), a[1].data_ptr(), b[0].data_ptr(),
                       b[1].data_ptr(), self.evk.data_ptr(), True, s)
 
+    def verify(self, orc_mod):
+        torch, prm = self.torch, self.prm
+        self.step()
+        torch.cuda.synchronize()
+        u = lambda t: t.cpu().numpy().view(np.uint64)  # noqa: E731
+        octx = orc_mod.OracleContext(LOGN, prm.moduli)
+        w0, w1 = octx.hmult_relin(orc_mod.BCONV_EXACT, orc_mod.ROUND_HALF, True, prm.q_idx, prm.p_idx, prm.dnum,
+                                  u(self.a[0]), u(self.a[1]), u(self.b[0]), u(self.b[1]), u(self.evk))
+        got = u(self.out)
+        return bool(np.array_equal(got[0], w0) and np.array_equal(got[1], w1))
+
     def e2e_step(self):
         if getattr(self, "pipe", None) is None:
             from cerium_b200.host_pipeline import HostPipeline
@@ -379,6 +428,19 @@ class NttWorkload(Workload):
         s = self.torch.cuda.current_stream().cuda_stream
         self.ctx.ntt_forward(self.y.data_ptr(), self.x.data_ptr(), self.idx, stream=s)
         self.ctx.ntt_inverse(self.y.data_ptr(), self.y.data_ptr(), self.idx, stream=s)
+
+    def verify(self, orc_mod):
+        """Forward transform of every limb against the oracle, then the round trip on the device."""
+        torch = self.torch
+        s = torch.cuda.current_stream().cuda_stream
+        self.ctx.ntt_forward(self.y.data_ptr(), self.x.data_ptr(), self.idx, stream=s)
+        torch.cuda.synchronize()
+        octx = orc_mod.OracleContext(LOGN, self.moduli)
+        want = octx.ntt_forward(self.x.cpu().numpy().view(np.uint64), self.idx)
+        ok = bool(np.array_equal(self.y.cpu().numpy().view(np.uint64), want))
+        self.ctx.ntt_inverse(self.y.data_ptr(), self.y.data_ptr(), self.idx, stream=s)
+        torch.cuda.synchronize()
+        return ok and bool(torch.equal(self.y, self.x))
 
     def e2e_step(self):
         if getattr(self, "pipe", None) is None:
@@ -545,8 +607,10 @@ def run_reference_arm(args, wl):
         "impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * ops / value,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
-        "config": {"workload": wl.name, "note": "CPU port of the reference algorithm (SEAL-based reference runtime not buildable here)"},
-        "cpu_baseline": {"value": value, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port", "sample": sample},
+        "config": {"workload": wl.name},
+        "note": "CPU port of the reference algorithm (SEAL-based reference runtime not buildable here)",
+        "cpu_baseline": {"value": value, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",
+                         "port_quality": PORT_QUALITY, "sample": sample},
         "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_s": wall,
     }
@@ -561,6 +625,7 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="hrot")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-verify", action="store_true", help="skip the oracle comparison before timing")
     ap.add_argument("--parallelism", choices=["auto", "limb", "replica"], default="auto",
                     help="N > 1: 'replica' runs independent ciphertexts per rank (throughput, weak scaling); 'limb' "
                          "shards every ciphertext and key by RNS limb over the ranks (one all-gather per key switch, "
@@ -599,6 +664,20 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # parity first: one operation on the benchmark's own inputs against the oracle (the checker),
+    # outside every timed region; no value is printed for a path whose result is wrong
+    verified = None
+    if not args.no_verify:
+        import oracle
+        oracle.set_num_threads(max(1, (os.cpu_count() or 1) // max(1, world)))
+        verified = wl.verify(oracle)
+        if world > 1 and verified is not None:
+            t = torch.tensor([1 if verified else 0], dtype=torch.int32, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+            verified = bool(t.item())
+        if verified is False:
+            raise SystemExit("bench.py: %s does not match the oracle on the benchmark inputs; nothing is timed" % wl.name)
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -633,7 +712,7 @@ def main():
     torch.cuda.synchronize()
     rl_ms = r0.elapsed_time(r1) / rl_iters
     clocks = sampler.stop() if rank == 0 else None
-    probe = lib.probe_int_pipe(local_rank) if rank == 0 else None
+    probe = probe_int_pipe(local_rank) if rank == 0 else None
 
     # end to end: host buffers in, host buffers out, through the same C ABI calls
     # N > 1, auto: the same operation limb-sharded over all ranks (its latency, not its throughput)
@@ -684,10 +763,12 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong" if sharded else "weak",
             "vs_baseline": None, "dtype": "u64", "data": "synthetic",
-            "config": {"workload": wl.name, "l2": "working set larger than L2 (keys + ciphertexts + workspace > 126 MB)",
-                       "parallelism": ("single GPU" if world == 1 else
-                                       "limb-sharded ciphertexts and keys, one NCCL all-gather per key switch" if sharded
-                                       else "independent ciphertexts per GPU")},
+            "config": {"workload": wl.name},
+            "verified": verified,
+            "l2": "working set larger than L2 (keys + ciphertexts + workspace > 126 MB)",
+            "parallelism": ("single GPU" if world == 1 else
+                            "limb-sharded ciphertexts and keys, one NCCL all-gather per key switch" if sharded
+                            else "independent ciphertexts per GPU"),
             "e2e": {"value": job_ops * ops * e2e_steps / e2e_s, "unit": wl.unit, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h},
             "gpu_launches": wl.gpu_launches_per_step * args.steps,
@@ -711,9 +792,10 @@ def main():
             line["limb_sharded"] = limb_line
         if not args.no_cpu_baseline and world == 1:
             import oracle
+            oracle.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
             v, sample = wl.cpu_sample(oracle)
             line["cpu_baseline"] = {"value": v, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",
-                                    "sample": sample}
+                                    "port_quality": PORT_QUALITY, "sample": sample}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

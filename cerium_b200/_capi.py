@@ -29,6 +29,7 @@ SIGNATURES = {
     "cerium_last_error": (C.c_char_p, []),
     "cerium_context_create": (C.c_int, [C.POINTER(_vp), C.c_int, C.c_int, C.c_int, _u64p, C.c_int]),
     "cerium_context_destroy": (C.c_int, [_vp]),
+    "cerium_context_check": (C.c_int, [_vp]),
     "cerium_context_word_bits": (C.c_int, [_vp]),
     "cerium_context_num_moduli": (C.c_int, [_vp]),
     "cerium_context_modulus": (C.c_uint64, [_vp, C.c_int]),
@@ -38,9 +39,10 @@ SIGNATURES = {
     "cerium_ntt_forward_ptrs": (C.c_int, [_vp, _vp, _vp, _vp, _sz, _vp]),
     "cerium_ntt_inverse_ptrs": (C.c_int, [_vp, _vp, _vp, _vp, _sz, _vp]),
     "cerium_function_map_bind": (C.c_int, [_vp, C.c_int]),
-    "cerium_function_map_load": (C.c_int, [C.c_char_p, C.c_char_p]),
-    "cerium_function_map_size": (C.c_int, [C.c_int]),
-    "cerium_function_map_lookup": (_vp, [C.c_int, C.c_uint32]),
+    "cerium_function_map_get": (_vp, [C.c_char_p, C.c_char_p, C.c_int]),
+    "cerium_function_map_error": (C.c_char_p, []),
+    "cerium_function_map_size": (C.c_int, [C.c_char_p, C.c_int]),
+    "cerium_function_map_lookup": (_vp, [C.c_char_p, C.c_int, C.c_uint32]),
     "cerium_function_map_launcher": (_vp, [C.c_char_p, C.c_int]),
     "cerium_sud_ptrs": (C.c_int, [_vp, _vp, _vp, _vp, _sz, _vp, _vp]),
     "cerium_bconv_ptrs": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _vp]),
@@ -77,7 +79,6 @@ SIGNATURES = {
                                        C.c_uint32, C.c_void_p, C.c_int, C.c_void_p]),
     "cerium_double_rescale": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32), C.c_int, C.c_int,
                                         C.c_void_p, C.c_void_p]),
-    "cerium_probe_int_pipe": (C.c_int, [C.c_int, C.POINTER(C.c_double), C.c_int]),
     "cerium_rescale_static": (C.c_int, [_vp, C.c_int, _vp, _vp, _u32p, C.c_int, C.c_int, _vp]),
 }
 
@@ -117,16 +118,6 @@ class Library:
         if rc != OK:
             raise CeriumError(rc, self.dll.cerium_last_error().decode())
 
-    PROBE_NAMES = ("mad.lo.u32", "mad.wide.u32", "mul.hi.u64", "mul.lo.u64", "add.u64",
-                   "butterfly_u64_strict", "butterfly_u64_lazy", "butterfly_u32",
-                   "fma.rn.f64", "butterfly_u64_fp64")
-
-    def probe_int_pipe(self, device: int = 0) -> dict:
-        """Register-only instruction / butterfly rates in Gop/s (the arithmetic roofline)."""
-        buf = (C.c_double * 10)()
-        self.check(self.dll.cerium_probe_int_pipe(device, buf, 10))
-        return dict(zip(self.PROBE_NAMES, [float(v) for v in buf]))
-
     def galois_elt_from_step(self, step: int, logn: int = 16) -> int:
         return int(self.dll.cerium_galois_elt_from_step(step, logn))
 
@@ -162,6 +153,10 @@ class Context:
 
     def root(self, k: int) -> int:
         return int(self.lib.dll.cerium_context_root(self.h, k))
+
+    def check(self):
+        """Waits for the device and raises if a kernel skipped a malformed work item since the last check."""
+        self.lib.check(self.lib.dll.cerium_context_check(self.h))
 
     # -- transforms ------------------------------------------------------------------
     def ntt_forward(self, out: int, inp: int, prime_idx: Sequence[int], out_stride: Optional[int] = None,

@@ -2,12 +2,24 @@
 // instructions and butterflies the transforms are made of.  It is the "integer-multiply
 // roofline" the 64-bit kernels are judged against (their HBM roofline is not the binding one):
 // a transform cannot run its butterflies faster than these loops, which touch no memory.
-// Diagnostic entry point; not on any evaluation path.
+// Benchmark infrastructure: built into its own shared object (libcerium_b200_probe.so), which only
+// bench.py loads; the evaluation library does not contain it.  It allocates a small scratch buffer
+// and synchronises the device.
 #include <cstring>
 
-#include "internal.h"
+#include "../csrc/internal.h"
 
 using namespace cerium;
+
+// the error plumbing of the evaluation library, restated for this stand-alone object
+namespace cerium {
+static thread_local std::string g_probe_error;
+void set_error(const std::string& msg) { g_probe_error = msg; }
+int fail(int code, const std::string& msg) {
+  g_probe_error = msg;
+  return code;
+}
+}  // namespace cerium
 
 namespace {
 
@@ -126,7 +138,11 @@ float time_ms(F launch) {
 //  [0] mad.lo.u32   [1] mad.wide.u32   [2] mul.hi.u64   [3] mul.lo.u64   [4] add.u64
 //  [5] 64-bit strict (Harvey) butterfly   [6] 64-bit lazy butterfly   [7] 32-bit strict butterfly
 //  and, when n_results >= 10:   [8] fma.rn.f64   [9] 64-bit double-precision butterfly
-extern "C" int cerium_probe_int_pipe(int device, double* gops, int n_results) {
+extern "C" __attribute__((visibility("default"))) const char* cerium_probe_last_error(void) {
+  return cerium::g_probe_error.c_str();
+}
+
+extern "C" __attribute__((visibility("default"))) int cerium_probe_int_pipe(int device, double* gops, int n_results) {
   if (!gops || n_results < 8) return fail(CERIUM_ERR_INVALID, "probe_int_pipe: need room for 8 results");
   int ndev = 0;
   if (cudaGetDeviceCount(&ndev) != cudaSuccess || device < 0 || device >= ndev)

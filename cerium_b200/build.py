@@ -3,6 +3,10 @@
 ``python -m cerium_b200.build`` compiles every ``csrc/*.cu`` into an object file next to it
 and links ``cerium_b200/libcerium_b200.so``.  The shared object is git-ignored but travels
 with the tree, so a GPU host without the sources' build step can still load it.
+``bench_probe/probe.cu`` (the register-only arithmetic-rate probe that bench.py reports its
+arithmetic roofline against) becomes a library of its own, ``libcerium_b200_probe.so``: it is
+benchmark infrastructure and stays out of the evaluation library.  ``function_map_shim.so`` is the
+per-partition plugin of the reference runtime (see ``cerium_b200/plugin.py``).
 """
 from __future__ import annotations
 
@@ -15,6 +19,10 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcerium_b200.so")
+SHIM_SRC = os.path.join(CSRC, "plugin_shim", "function_map_shim.cpp")
+SHIM_LIB = os.path.join(HERE, "function_map_shim.so")
+PROBE_SRC = os.path.join(HERE, "bench_probe", "probe.cu")
+PROBE_LIB = os.path.join(HERE, "libcerium_b200_probe.so")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden",
               "--expt-relaxed-constexpr", "-Xptxas", "-v"]
@@ -63,10 +71,23 @@ def build(force: bool = False, verbose: bool = False) -> str:
             if verbose:
                 print("== ptxas %s ==\n%s" % (os.path.basename(src), log))
     if jobs or force or _stale(LIB, objs):
-        cmd = [nvcc] + ARCH + ["-shared", "-Xcompiler", "-fPIC", "-o", LIB] + objs + ["-lcudart_static"]
+        cmd = [nvcc] + ARCH + ["-shared", "-Xcompiler", "-fPIC", "-o", LIB] + objs + ["-lcudart_static", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n%s" % r.stderr)
+    if force or _stale(SHIM_LIB, [SHIM_SRC, LIB]):
+        # the per-partition plugin of the reference runtime: links the library by absolute run path,
+        # because copies of it are installed into program directories
+        cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-o", SHIM_LIB, SHIM_SRC,
+               "-L" + HERE, "-lcerium_b200", "-Wl,-rpath," + HERE, "-ldl"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("g++ failed for %s:\n%s" % (SHIM_SRC, r.stderr))
+    if force or _stale(PROBE_LIB, [PROBE_SRC] + headers):
+        cmd = [nvcc] + ARCH + NVCC_FLAGS + ["-shared", "-o", PROBE_LIB, PROBE_SRC, "-lcudart_static"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("nvcc failed for %s:\n%s" % (PROBE_SRC, r.stderr))
     return LIB
 
 

@@ -415,7 +415,7 @@ int launch_bconv(cerium_context* ctx, const BconvCall* calls, int count, cudaStr
   if (count == 0) return CERIUM_OK;
   return dispatch_word(ctx->word_bits, [&](auto tag) -> int {
     using W = decltype(tag);
-    static bool smem_opt_in[2] = {false, false};
+    static bool smem_opt_in[kMaxDevices][2] = {};  // the attribute is per device
     for (int first = 0; first < count; first += kBconvMaxBatch) {
       const int cnt = std::min(kBconvMaxBatch, count - first);
       BconvBatch<W> batch{};
@@ -454,10 +454,11 @@ int launch_bconv(cerium_context* ctx, const BconvCall* calls, int count, cudaStr
       if (smem > 48 * 1024) {
         if (smem > 200 * 1024) return fail(CERIUM_ERR_UNSUPPORTED, "bconv: conversion needs more than 200 KiB of shared memory");
         const int slot = sizeof(W) == 4 ? 0 : 1;
-        if (!smem_opt_in[slot]) {
+        const int dev = ctx->device;
+        if (dev < 0 || dev >= kMaxDevices || !smem_opt_in[dev][slot]) {
           CERIUM_CUDA(cudaFuncSetAttribute(bconv_kernel<W, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
           CERIUM_CUDA(cudaFuncSetAttribute(bconv_kernel<W, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-          smem_opt_in[slot] = true;
+          if (dev >= 0 && dev < kMaxDevices) smem_opt_in[dev][slot] = true;
         }
       }
       {
@@ -621,6 +622,8 @@ int cerium_context_create(cerium_context** out, int device, int log_n, int word_
     CERIUM_CUDA(cudaMalloc(&ctx->d_pcs, pcs.size() * sizeof(PrimeConst<W>)));
     CERIUM_CUDA(cudaMalloc(&ctx->d_twr_fwd, rfwd.size() * sizeof(Pair)));
     CERIUM_CUDA(cudaMalloc(&ctx->d_twr_inv, rinv.size() * sizeof(Pair)));
+    CERIUM_CUDA(cudaMalloc(reinterpret_cast<void**>(&ctx->d_status), 16));
+    CERIUM_CUDA(cudaMemset(ctx->d_status, 0, 16));
     CERIUM_CUDA(cudaMemcpy(ctx->d_twr_fwd, rfwd.data(), rfwd.size() * sizeof(Pair), cudaMemcpyHostToDevice));
     CERIUM_CUDA(cudaMemcpy(ctx->d_twr_inv, rinv.data(), rinv.size() * sizeof(Pair), cudaMemcpyHostToDevice));
     CERIUM_CUDA(cudaMemcpy(ctx->d_tw_fwd, fwd.data(), fwd.size() * sizeof(Pair), cudaMemcpyHostToDevice));
@@ -644,8 +647,22 @@ int cerium_context_destroy(cerium_context* ctx) {
   cudaFree(ctx->d_pcs);
   cudaFree(ctx->d_twr_fwd);
   cudaFree(ctx->d_twr_inv);
+  cudaFree(ctx->d_status);
   delete ctx;
   return CERIUM_OK;
+}
+
+int cerium_context_check(cerium_context* ctx) {
+  if (!ctx) return fail(CERIUM_ERR_INVALID, "context_check: null context");
+  DeviceGuard guard(ctx->device);
+  uint32_t st = 0;
+  CERIUM_CUDA(cudaMemcpy(&st, ctx->d_status, sizeof(st), cudaMemcpyDeviceToHost));  // waits for the device's work
+  if (st == 0) return CERIUM_OK;
+  CERIUM_CUDA(cudaMemset(ctx->d_status, 0, sizeof(st)));
+  std::string msg = "context_check:";
+  if (st & kStatusBconvShape) msg += " a base-conversion table entry exceeded the shape bounds of its launch (that conversion was skipped);";
+  if (st & ~kStatusBconvShape) msg += " unknown status bits;";
+  return fail(CERIUM_ERR_INVALID, msg);
 }
 
 int cerium_context_word_bits(const cerium_context* ctx) { return ctx ? ctx->word_bits : 0; }
@@ -760,22 +777,26 @@ int cerium_bconv_ptrs(cerium_context* ctx, void* const* outs, const size_t* n_ou
   cudaStream_t s = (cudaStream_t)stream;
   return dispatch_word(ctx->word_bits, [&](auto tag) -> int {
     using W = decltype(tag);
-    static bool smem_opt_in[2] = {false, false};
+    static bool smem_opt_in[kMaxDevices][2] = {};  // the attribute is per device
     // the shapes live on the device: size the shared memory for the caller's bounds (inputs staged per
-    // thread when there are more than kBconvRegInputs of them)
-    const size_t smem = bconv_smem_bytes<W>((int)max_in, (int)max_out);
+    // thread when there are more than kBconvRegInputs of them); smaller shapes inside the bounds may need
+    // more than the bound shape itself (the double-precision factor pairs of up to 8 inputs)
+    size_t smem = bconv_smem_bytes<W>((int)max_in, (int)max_out);
+    smem = std::max(smem, bconv_smem_bytes<W>((int)std::min<size_t>(max_in, kBconvRegInputs), (int)max_out));
     if (smem > 200 * 1024) return fail(CERIUM_ERR_UNSUPPORTED, "bconv_ptrs: conversion needs more than 200 KiB of shared memory");
     if (smem > 48 * 1024) {
       const int slot = sizeof(W) == 4 ? 0 : 1;
-      if (!smem_opt_in[slot]) {
+      const int dev = ctx->device;
+      if (dev < 0 || dev >= kMaxDevices || !smem_opt_in[dev][slot]) {
         CERIUM_CUDA(cudaFuncSetAttribute(bconv_ptrs_kernel<W>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        smem_opt_in[slot] = true;
+        if (dev >= 0 && dev < kMaxDevices) smem_opt_in[dev][slot] = true;
       }
     }
     auto kfn = bconv_ptrs_kernel<W>;
     CERIUM_LAUNCH(kfn, dim3(kBconvBlocks, (unsigned)num_conversions), kBconvThreads, smem, s,
                   reinterpret_cast<W* const*>(outs), n_out, reinterpret_cast<const W* const*>(ins), n_in,
-                  reinterpret_cast<const W* const*>(factors), reinterpret_cast<const W* const*>(out_moduli));
+                  reinterpret_cast<const W* const*>(factors), reinterpret_cast<const W* const*>(out_moduli),
+                  max_in, max_out, smem, ctx->d_status);
     CERIUM_LAUNCH_CHECK("bconv_ptrs");
     return CERIUM_OK;
   });

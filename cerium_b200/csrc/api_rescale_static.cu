@@ -7,6 +7,8 @@
 // such a caller for a scratch buffer of n_polys * N words; the variant here carries that scratch
 // inside the library image instead, as a fixed device array of 1 MiB that every GPU which loads
 // the library holds from load until the process exits.
+#include <atomic>
+
 #include "internal.h"
 
 using namespace cerium;
@@ -16,25 +18,28 @@ namespace {
 constexpr int kStaticRescaleMaxPolys = 2;  // one ciphertext: c0 and c1
 constexpr int kStaticMaxDevices = 64;
 
-// N 64-bit words per polynomial; a 32-bit context uses the first half of each slot.
+// Room for two polynomials of N 64-bit words.  Polynomial p sits at byte p * N * word size, so a
+// 32-bit context packs its two polynomials into the first half of the array.
 static __device__ __align__(256) unsigned char g_rescale_scratch[kStaticRescaleMaxPolys * kN * 8];
 
 // In host code the name `g_rescale_scratch` only identifies the symbol; it is not an address a
 // kernel may be given.  The device address is looked up once per device, with that device
 // current, and cached here.
+// Two host threads may make the first call on one device at the same time: both look the address
+// up and store the same value; the flag is published with release order after the pointer.
 void* g_scratch_ptr[kStaticMaxDevices] = {};
-bool g_scratch_ready[kStaticMaxDevices] = {};
+std::atomic<bool> g_scratch_ready[kStaticMaxDevices] = {};
 
 int static_rescale_scratch(int device, void** out) {
   if (device < 0 || device >= kStaticMaxDevices)
     return fail(CERIUM_ERR_UNSUPPORTED, "rescale_static: device index above 63");
-  if (!g_scratch_ready[device]) {
+  if (!g_scratch_ready[device].load(std::memory_order_acquire)) {
     void* p = nullptr;
     const cudaError_t e = cudaGetSymbolAddress(&p, g_rescale_scratch);
     if (e != cudaSuccess || p == nullptr)
       return fail(CERIUM_ERR_CUDA, std::string("rescale_static: cudaGetSymbolAddress: ") + cudaGetErrorString(e));
     g_scratch_ptr[device] = p;
-    g_scratch_ready[device] = true;
+    g_scratch_ready[device].store(true, std::memory_order_release);
   }
   *out = g_scratch_ptr[device];
   return CERIUM_OK;

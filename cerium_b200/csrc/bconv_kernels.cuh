@@ -400,17 +400,27 @@ __global__ void __launch_bounds__(kBconvThreads, 5)
 // out_moduli[j] = [O] primes.  The host knows neither shapes nor primes, so the Barrett constants
 // are derived here from the moduli (one division per output and CTA).  Lazy conversion only
 // (the reference's), canonical outputs.
+// The shared memory was sized on the host from the caller's shape bounds; a table entry above them
+// (or above the smem_limit bytes the launch has) must not be staged: such a CTA touches no memory,
+// records kStatusBconvShape in *status and returns.
 // grid = (ceil(N / kBconvThreads), conversions), block = kBconvThreads, dynamic smem >= bconv_smem_bytes(I, O).
+constexpr uint32_t kStatusBconvShape = 1u;  // bit of the context's status word
 template <typename W>
 __global__ void __launch_bounds__(kBconvThreads, 5)
     bconv_ptrs_kernel(W* const* __restrict__ outs, const size_t* __restrict__ n_out, const W* const* __restrict__ ins,
                       const size_t* __restrict__ n_in, const W* const* __restrict__ factors,
-                      const W* const* __restrict__ out_moduli) {
+                      const W* const* __restrict__ out_moduli, const size_t max_in, const size_t max_out,
+                      const size_t smem_limit, uint32_t* __restrict__ status) {
   CERIUM_DYN_SMEM(smem_raw);
   grid_dependency_launch();
   grid_dependency_wait();  // the tables may have been written by the stream's previous work
   const int j = blockIdx.y;
-  const int I = (int)n_in[j], O = (int)n_out[j];
+  const size_t In = n_in[j], On = n_out[j];
+  if (In < 1 || On < 1 || In > max_in || On > max_out || bconv_smem_bytes<W>((int)In, (int)On) > smem_limit) {
+    if (threadIdx.x == 0 && status != nullptr) atomicOr(status, kStatusBconvShape);
+    return;
+  }
+  const int I = (int)In, O = (int)On;
   BconvDesc<W> d{};
   d.in = ins[j];
   d.out = outs[j];

@@ -20,6 +20,8 @@
 
 namespace cerium {
 
+constexpr int kMaxDevices = 64;  // per-device host-side caches are indexed by the CUDA device ordinal
+
 void set_error(const std::string& msg);
 int fail(int code, const std::string& msg);
 
@@ -98,6 +100,7 @@ struct cerium_context {
   void* d_twr_fwd = nullptr; // Pair[n_primes][256][15][16], lane-interleaved level-3 twiddles (row pass)
   void* d_twr_inv = nullptr; // same for the inverse transform
   void* d_pcs = nullptr;     // PrimeConst<W>[n_primes]
+  uint32_t* d_status = nullptr;  // device status word: kernels that skip a malformed work item set a bit here
   // 64-bit primes below 2^50 transform on the FP64 pipe unless the environment variable
   // CERIUM_B200_NTT_ARITH is "int" when the context is created (for comparisons)
   bool allow_fp = true;

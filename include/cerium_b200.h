@@ -81,6 +81,13 @@ CERIUM_API const char *cerium_last_error(void);
 CERIUM_API int cerium_context_create(cerium_context **out, int device, int log_n, int word_bits,
                           const uint64_t *moduli, int n_moduli);
 CERIUM_API int cerium_context_destroy(cerium_context *ctx);
+/*
+ * Kernels never trap on a malformed work item (the reference's do no bounds checking at all,
+ * cerium/compiler/backend/kernels/function.cuh:61-78): the affected CTAs skip it and set a bit in
+ * a status word of the context.  cerium_context_check waits for the device, reads and clears that
+ * word; it returns CERIUM_ERR_INVALID (and a message) when a bit was set since the last check.
+ */
+CERIUM_API int cerium_context_check(cerium_context *ctx);
 CERIUM_API int cerium_context_word_bits(const cerium_context *ctx);
 CERIUM_API int cerium_context_num_moduli(const cerium_context *ctx);
 CERIUM_API uint64_t cerium_context_modulus(const cerium_context *ctx, int k);
@@ -126,7 +133,8 @@ CERIUM_API int cerium_sud_ptrs(cerium_context *ctx, void *const *outs, const voi
  * reads ins[j] = [n_in[j]][N] and writes outs[j] = [n_out[j]][N] with the factor matrix
  * factors[j] = [n_out[j]][n_in[j]] (DeviceBaseConverter, evaluator.cpp:1539-1578) and the output
  * primes out_moduli[j] = [n_out[j]]; no converter object and no prime index is involved.  max_in /
- * max_out are HOST upper bounds of the shapes (they size the shared memory).  The reference's lazy
+ * max_out are HOST upper bounds of the shapes (they size the shared memory); a table entry above
+ * them is skipped on the device and reported by cerium_context_check.  The reference's lazy
  * conversion; results are canonical.
  */
 CERIUM_API int cerium_bconv_ptrs(cerium_context *ctx, void *const *outs, const size_t *n_out,
@@ -355,17 +363,6 @@ CERIUM_API int cerium_double_rescale(cerium_context *ctx, void *out, const void 
                           int L, int n_polys, void *scratch, void *stream);
 
 /*
- * Diagnostic: register-only rates of the instructions and butterflies the transforms are made
- * of, in giga-operations per second on `device` (the arithmetic roofline of the 64-bit kernels).
- * gops[0..7] = mad.lo.u32, mad.wide.u32, mul.hi.u64, mul.lo.u64, add.u64, 64-bit strict
- * butterfly, 64-bit lazy butterfly, 32-bit butterfly; with n_results >= 10 also gops[8] =
- * fma.rn.f64 and gops[9] = the double-precision butterfly that primes below 2^50 use.
- * n_results must be at least 8.  Allocates a small scratch buffer and synchronises the device;
- * no counterpart in the reference.
- */
-CERIUM_API int cerium_probe_int_pipe(int device, double *gops, int n_results);
-
-/*
  * cerium_rescale for callers that cannot allocate (no counterpart in the reference, whose runtime
  * always owns its buffers).  Same result as cerium_rescale, but the n_polys * N words of scratch
  * live in a fixed 1 MiB device array inside the library instead of being passed in: meant for
@@ -385,26 +382,33 @@ CERIUM_API int cerium_rescale_static(cerium_context *ctx, int round_mode, void *
                                      const uint32_t *q_idx, int L, int n_polys, void *stream);
 
 /*
- * The reference runtime's plugin contract.  libcerium_b200.so also exports the two C++ getters the
- * Cerium runtime resolves in a function_map_<p>.so, __GET_FUNCTION_MAP__ and
- * __GET_FUNCTION_MAP_CUGRAPH__ (cerium/runtime/execution/function.cpp:144-177): installed under that
- * name it maps the ids of the program's ntt / int / sud / bco records (read from the `functions<p>`
- * file beside it) to launchers with the signatures of cerium/runtime/execution/device_utils.cu:33-113,
- * stream and graph variants, backed by cerium_ntt_*_ptrs, cerium_sud_ptrs and cerium_bconv_ptrs.
- * Launchers of other record types are taken from function_map_<p>.orig.so when it is present.
+ * The reference runtime's plugin contract.  The Cerium runtime resolves two C++ getters in every
+ * function_map_<p>.so it loads, __GET_FUNCTION_MAP__ and __GET_FUNCTION_MAP_CUGRAPH__
+ * (cerium/runtime/execution/function.cpp:144-177).  Here they live in a small shim
+ * (cerium_b200/function_map_shim.so, source csrc/plugin_shim/function_map_shim.cpp) of which one
+ * copy per partition is installed under that name; the shim asks this library for the maps of its
+ * partition's records file `functions<p>`: the ids of the ntt / int / sud / bco records mapped to
+ * launchers with the signatures of cerium/runtime/execution/device_utils.cu:33-113, stream and
+ * graph variants, backed by cerium_ntt_*_ptrs, cerium_sud_ptrs and cerium_bconv_ptrs.  Launchers of
+ * other record types are taken from the generated plugin when its path is given.
  *
  * cerium_function_map_bind     names the context whose tables the launchers use on `device`
  *                              (NULL unbinds).  Bind before the first launch.
- * cerium_function_map_load     fills the maps from an explicit functions file (and generated plugin,
- *                              may be NULL) instead of the paths derived from the plugin's own name.
+ * cerium_function_map_get      the stream (cugraph = 0) or graph map of one records file, as a
+ *                              `const std::unordered_map<uint32_t, void*> *`; built on first request
+ *                              and kept for the life of the process, one pair per records file (so
+ *                              per function and partition).  generated_plugin_path may be NULL.
+ *                              Returns NULL on failure; cerium_function_map_error() says why.
  * cerium_function_map_size / _lookup / _launcher   inspect the maps (tests, diagnostics): number of
- *                              entries, launcher of a kernel id, launcher of a record type
- *                              ("ntt", "int", "sud", "bco").
+ *                              entries (-1 on failure), launcher of a kernel id, launcher of a
+ *                              record type ("ntt", "int", "sud", "bco").
  */
 CERIUM_API int cerium_function_map_bind(cerium_context *ctx, int device);
-CERIUM_API int cerium_function_map_load(const char *functions_path, const char *generated_plugin_path);
-CERIUM_API int cerium_function_map_size(int cugraph);
-CERIUM_API void *cerium_function_map_lookup(int cugraph, uint32_t kernel_id);
+CERIUM_API const void *cerium_function_map_get(const char *functions_path, const char *generated_plugin_path,
+                                               int cugraph);
+CERIUM_API const char *cerium_function_map_error(void);
+CERIUM_API int cerium_function_map_size(const char *functions_path, int cugraph);
+CERIUM_API void *cerium_function_map_lookup(const char *functions_path, int cugraph, uint32_t kernel_id);
 CERIUM_API void *cerium_function_map_launcher(const char *type, int cugraph);
 
 #ifdef __cplusplus

@@ -226,6 +226,21 @@ def case_bconv_ptrs(be, word_bits):
                      9, 5, len(shapes))
     for do, want in zip(d_out, wants):
         assert np.array_equal(h.down(do), want)
+    # a table entry above the launch's shape bounds (9 inputs against max_in = 8) is skipped on the
+    # device, not staged past the shared memory: its outputs stay untouched, the other conversion
+    # runs, and the context reports it once
+    import pytest
+    h.ctx.check()
+    for do in d_out:
+        do[...] = 0 if isinstance(do, np.ndarray) else do.zero_()
+    h.ctx.bconv_ptrs(be.ptr(d_outs), be.ptr(d_nout), be.ptr(d_ins), be.ptr(d_nin), be.ptr(d_facs), be.ptr(d_omods),
+                     8, 5, len(shapes))
+    with pytest.raises(_capi.CeriumError) as e:
+        h.ctx.check()
+    assert e.value.code == _capi.ERR_INVALID and "shape bounds" in e.value.message
+    h.ctx.check()                                            # reading the status cleared it
+    assert np.array_equal(h.down(d_out[0]), wants[0])
+    assert not h.down(d_out[1]).any(), "the over-bound conversion wrote its outputs"
 
 
 def case_ewise(be, word_bits):

@@ -1,7 +1,7 @@
-"""The reference runtime's plugin contract served by libcerium_b200.so: installed under the name
-function_map_<p>.so it answers __GET_FUNCTION_MAP__ / __GET_FUNCTION_MAP_CUGRAPH__ with launchers of the
+"""The reference runtime's plugin contract: a copy of function_map_shim.so installed as function_map_<p>.so
+answers __GET_FUNCTION_MAP__ / __GET_FUNCTION_MAP_CUGRAPH__ with libcerium_b200.so's launchers of the
 reference's signatures (cerium/runtime/execution/device_utils.cu:33-113) for the ntt / int / sud / bco
-records of the program's functions<p> file (cerium/compiler/backend/cuda_kernel.cc:1707-1916).
+records of the partition's functions<p> file (cerium/compiler/backend/cuda_kernel.cc:1707-1916).
 
 CPU tests: the maps, through a driver that loads the plugin as the reference does.  GPU tests: the
 launchers themselves, stream and graph variants, against the oracle."""
@@ -68,61 +68,110 @@ const M& b() { graph_map[9] = (void*)&generated_9; return graph_map; }
 
 
 def _ensure_lib():
-    if not os.path.exists(_capi.LIB_PATH):
-        from cerium_b200 import build
+    from cerium_b200 import build
+    if not os.path.exists(_capi.LIB_PATH) or not os.path.exists(build.SHIM_LIB):
         build.build()
 
 
-def _run_driver(tmp_path, with_generated):
+# a second partition whose record 3 is a base conversion, not an inverse transform
+FUNCTIONS_P1 = """function3 {
+  .id: 3
+  .type: bco
+  .outputs: b0(3)
+  .inputs: b0(0)
+}
+function7 {
+  .id: 7
+  .type: sud
+  .outputs: r4
+  .inputs: r3 r2
+}
+"""
+
+
+def _run_driver(tmp_path, with_generated=False, two_partitions=False, preload=False, drop_functions=False):
     _ensure_lib()
+    from cerium_b200 import plugin
     drv = str(tmp_path / "driver")
     subprocess.run(["g++", "-O1", "-std=c++17", os.path.join(ROOT, "tests", "function_map_driver.cpp"), "-o", drv, "-ldl"],
                    check=True)
     d = tmp_path / "prog" / "main"
     d.mkdir(parents=True)
     (d / "functions0").write_text(FUNCTIONS)
-    os.symlink(_capi.LIB_PATH, d / "function_map_0.so")
+    if two_partitions:
+        (d / "functions1").write_text(FUNCTIONS_P1)
     if with_generated:
         (tmp_path / "gen.cpp").write_text(FAKE_PLUGIN)
         subprocess.run(["g++", "-shared", "-fPIC", "-std=c++17", str(tmp_path / "gen.cpp"), "-o",
-                        str(d / "function_map_0.orig.so")], check=True)
-    env = {k: v for k, v in os.environ.items() if not k.startswith("CERIUM_B200_FUNCTION")}
-    r = subprocess.run([drv, str(d / "function_map_0.so")], capture_output=True, text=True, env=env)
+                        str(d / "function_map_0.so")], check=True)
+    written = plugin.install(str(d))
+    assert [os.path.basename(w) for w in written] == ["function_map_%d.so" % p for p in range(2 if two_partitions else 1)]
+    assert os.path.exists(d / "function_map_0.orig.so") == with_generated
+    assert plugin.install(str(d)) == written                   # installing twice changes nothing
+    assert os.path.exists(d / "function_map_0.orig.so") == with_generated
+    if drop_functions:
+        os.remove(d / "functions0")
+    cmd = [drv] + (["--preload", _capi.LIB_PATH] if preload else []) + written
+    r = subprocess.run(cmd, capture_output=True, text=True)
     assert r.returncode == 0, r.stdout + r.stderr
-    maps = {"stream": {}, "graph": {}}
-    launchers = {}
+    maps = [{"stream": {}, "graph": {}} for _ in written]
+    launchers, errors = {}, []
     for line in r.stdout.split("\n"):
         f = line.split()
-        if len(f) == 3 and f[0] in maps:
-            maps[f[0]][int(f[1])] = f[2]
+        if len(f) == 4 and f[0].isdigit():
+            maps[int(f[0])][f[1]][int(f[2])] = f[3]
         elif len(f) == 4 and f[0] == "launcher":
             launchers[(f[1], f[2])] = f[3]
-    return maps, launchers
+        elif f and f[0] == "error":
+            errors.append(line)
+    return maps, launchers, errors
 
 
 def test_plugin_maps_transform_records(tmp_path):
-    maps, launchers = _run_driver(tmp_path, with_generated=False)
+    maps, launchers, errors = _run_driver(tmp_path)
+    assert not errors
     for kind in ("stream", "graph"):
-        assert sorted(maps[kind]) == [3, 4, 5, 11]          # the generic record has no launcher here
-        assert maps[kind][3] == launchers[(kind, "int")]
-        assert maps[kind][4] == launchers[(kind, "bco")]
-        assert maps[kind][5] == launchers[(kind, "ntt")]
-        assert maps[kind][11] == launchers[(kind, "sud")]
+        m = maps[0][kind]
+        assert sorted(m) == [3, 4, 5, 11]          # the generic record has no launcher here
+        assert m[3] == launchers[(kind, "int")]
+        assert m[4] == launchers[(kind, "bco")]
+        assert m[5] == launchers[(kind, "ntt")]
+        assert m[11] == launchers[(kind, "sud")]
     assert len(set(launchers.values())) == 8 and "(nil)" not in launchers.values()
 
 
 def test_plugin_keeps_generated_launchers_of_other_records(tmp_path):
-    maps, launchers = _run_driver(tmp_path, with_generated=True)
-    assert sorted(maps["stream"]) == [3, 4, 5, 9, 11] and sorted(maps["graph"]) == [3, 4, 5, 9, 11]
-    assert maps["stream"][9] not in launchers.values()       # record 9 (generic) is the generated plugin's
-    assert maps["stream"][5] == launchers[("stream", "ntt")]  # record 5 (ntt) is overridden
+    maps, launchers, errors = _run_driver(tmp_path, with_generated=True)
+    assert not errors
+    m = maps[0]
+    assert sorted(m["stream"]) == [3, 4, 5, 9, 11] and sorted(m["graph"]) == [3, 4, 5, 9, 11]
+    assert m["stream"][9] not in launchers.values()       # record 9 (generic) is the generated plugin's
+    assert m["stream"][5] == launchers[("stream", "ntt")]  # record 5 (ntt) is overridden
+
+
+@pytest.mark.parametrize("preload", [False, True])
+def test_partitions_loaded_into_one_process_keep_their_own_maps(tmp_path, preload):
+    """The runtime loads function_map_0.so, function_map_1.so, ... into one process
+    (cerium/runtime/execution/function.cpp:171-177): id 3 is an inverse transform in partition 0 and a
+    base conversion in partition 1, and each plugin must answer with its own record's launcher - also
+    when the host program already holds the library under its real name."""
+    maps, launchers, errors = _run_driver(tmp_path, two_partitions=True, preload=preload)
+    assert not errors
+    for kind in ("stream", "graph"):
+        assert sorted(maps[0][kind]) == [3, 4, 5, 11]
+        assert sorted(maps[1][kind]) == [3, 7]
+        assert maps[0][kind][3] == launchers[(kind, "int")]
+        assert maps[1][kind][3] == launchers[(kind, "bco")]
+        assert maps[1][kind][7] == launchers[(kind, "sud")]
 
 
 def test_plugin_reports_a_missing_functions_file(tmp_path):
-    _ensure_lib()
+    maps, launchers, errors = _run_driver(tmp_path, drop_functions=True)
+    assert len(errors) == 2 and all("cannot open" in e and "functions0" in e for e in errors)
     lib = _capi.load()
-    rc = lib.dll.cerium_function_map_load(str(tmp_path / "nope").encode(), None)
-    assert rc == _capi.ERR_INVALID
+    assert lib.dll.cerium_function_map_get(str(tmp_path / "nope").encode(), None, 0) is None
+    assert b"cannot open" in lib.dll.cerium_function_map_error()
+    assert lib.dll.cerium_function_map_size(str(tmp_path / "nope").encode(), 0) == -1
 
 
 # ---------------------------------------------------------------------------------------------
@@ -173,11 +222,11 @@ def test_launchers_match_the_oracle(tmp_path, graph):
     lib = h.ctx.lib
     fpath = tmp_path / "functions0"
     fpath.write_text(FUNCTIONS)
-    assert lib.dll.cerium_function_map_load(str(fpath).encode(), None) == 0
-    assert lib.dll.cerium_function_map_size(0) == 4
+    fp = str(fpath).encode()
+    assert lib.dll.cerium_function_map_size(fp, 0) == 4
     assert lib.dll.cerium_function_map_bind(h.ctx.h, torch.cuda.current_device()) == 0
     try:
-        look = lambda kid: lib.dll.cerium_function_map_lookup(1 if graph else 0, kid)
+        look = lambda kid: lib.dll.cerium_function_map_lookup(fp, 1 if graph else 0, kid)
         rng = np.random.default_rng(91)
         N = pc.N
         lb = N * 4

@@ -2,7 +2,8 @@
 (arena-only runtimes, plug-ins without an allocation budget, latency-critical sections).  Its
 scratch is a fixed array inside the library, so the test drives it through the C ABI twice in a
 row - the second call finds the first call's leftovers in the array - and expects both results
-to equal cerium_rescale with a caller-provided scratch, bit for bit (integer work)."""
+to equal cerium_rescale with a caller-provided scratch and the CPU oracle's rescale, bit for bit
+(integer work)."""
 import numpy as np
 import pytest
 
@@ -32,6 +33,8 @@ def test_rescale_static_matches_rescale_twice(word_bits, round_mode):
         got = h.new(n_polys, L - 1, pc.N)
         h.ctx.rescale_static(h.p(got), h.p(dx), q_idx, n_polys, round_mode)
         assert np.array_equal(h.down(got), h.down(want)), "call %d differs from cerium_rescale" % call
+        orc = np.stack([h.orc.rescale(round_mode, q_idx, x[p]) for p in range(n_polys)])
+        assert np.array_equal(h.down(got), orc), "call %d differs from the oracle" % call
         # a single polynomial uses only the first slot of the built-in scratch
         got1 = h.new(1, L - 1, pc.N)
         h.ctx.rescale_static(h.p(got1), h.p(dx), q_idx, 1, round_mode)
