@@ -163,6 +163,16 @@ class Workload:
     def step(self):
         raise NotImplementedError
 
+    def fork(self):
+        pass
+
+    def join(self):
+        pass
+
+    def e2e_drain(self):
+        if getattr(self, "pipe", None) is not None:
+            self.pipe.drain()
+
 
 def _rand_limbs_gpu(torch, moduli, prime_idx, lead, gen):
     """[lead..., len(prime_idx), N] int64 uniform residues on the GPU (seeded)."""
@@ -182,64 +192,113 @@ class HRotWorkload(Workload):
         self.prm = params.config_hrot(LOGN, 35, 5, 7)
         self.n_cts = n_cts  # rotating set of ciphertexts so consecutive ops do not reuse inputs
 
-    def setup(self, lib, torch, rank, world=1, sharded=False):
+    def setup(self, lib, torch, rank, world=1, sharded=False, comm=None, ext_split=True, inflight=4):
         from cerium_b200 import _capi
         self.torch = torch
         prm = self.prm
         self.sharded = sharded and world > 1
+        self.rank, self.world = rank, world
         self.ctx = _capi.Context(lib, prm.moduli, 64, device=torch.cuda.current_device())
-        gen = torch.Generator(device="cuda").manual_seed(0xCE210003 + rank)
+        all_idx = prm.q_idx + prm.p_idx
         if self.sharded:
-            # every rank holds its own limbs of the SAME ciphertexts and key (round-robin by limb)
+            # every rank generates the SAME ciphertexts and key and keeps its own limbs (round robin by
+            # limb); `inflight` operations are in flight at a time, each on a plan and a stream of its own,
+            # so that one operation's exchange runs under another's arithmetic
             from cerium_b200 import sharded as sh
-            dev = torch.device("cuda", torch.cuda.current_device())
-            self.sk = sh.ShardedKeySwitch(lib, self.ctx, prm, rank, world, _capi.BCONV_EXACT, _capi.ROUND_HALF,
-                                          device=dev)
-            q_loc = [prm.q_idx[i] for i in sh.local_limb_indices(prm.L, rank, world)]
-            all_idx = q_loc + prm.p_idx
-            self.evk = _rand_limbs_gpu(torch, prm.moduli, all_idx, (prm.dnum, 2), gen)
-            self.cts = [_rand_limbs_gpu(torch, prm.moduli, q_loc, (2,), gen) for _ in range(self.n_cts)]
+            self.sh = sh
+            self.comm, self.ext_split, self.inflight = comm, ext_split, inflight
+            gen = torch.Generator(device="cuda").manual_seed(0xCE210003)
+            full_evk = _rand_limbs_gpu(torch, prm.moduli, all_idx, (prm.dnum, 2), gen)
+            full_cts = [_rand_limbs_gpu(torch, prm.moduli, prm.q_idx, (2,), gen) for _ in range(self.n_cts)]
+            self.mine = sh.local_limb_indices(prm.L, rank, world)
+            self.evk = sh.shard_key(full_evk, prm.L, rank, world, ext_split)
+            self.cts = [torch.stack([sh.shard_poly(c[0], rank, world), sh.shard_poly(c[1], rank, world)])
+                        for c in full_cts]
+            self.full_evk, self.full_ct0 = full_evk, full_cts[0]     # kept for verify(), dropped afterwards
+            self.sks = [sh.ShardedKeySwitch(self.ctx, prm, comm, _capi.BCONV_EXACT, _capi.ROUND_HALF, ext_split=ext_split)
+                        for _ in range(inflight)]
+            self.streams = [torch.cuda.Stream() for _ in range(inflight)]
+            self.outs = [torch.empty_like(self.cts[0]) for _ in range(max(self.n_cts, inflight))]
+            k_loc = self.sks[0].k_local
+            # iNTT pair, [gather], BConv, NTT pair, inner product, iNTT pair, [gather], BConv, SuD pair
+            self.gpu_launches_per_step = 2 + 1 + 2 + 1 + (2 if k_loc else 0) + 1 + 2
         else:
+            gen = torch.Generator(device="cuda").manual_seed(0xCE210003 + rank)
             # exact conversion + rounding: the semantics that are low-noise with 50/60-bit primes
             self.ks = _capi.KeySwitch(self.ctx, prm.q_idx, prm.p_idx, prm.dnum, _capi.BCONV_EXACT, _capi.ROUND_HALF)
-            all_idx = prm.q_idx + prm.p_idx
             self.evk = _rand_limbs_gpu(torch, prm.moduli, all_idx, (prm.dnum, 2), gen)
             self.cts = [_rand_limbs_gpu(torch, prm.moduli, prm.q_idx, (2,), gen) for _ in range(self.n_cts)]
-        self.outs = [torch.empty_like(self.cts[0]) for _ in range(self.n_cts)]
+            self.outs = [torch.empty_like(self.cts[0]) for _ in range(self.n_cts)]
+            # iNTT pair, BConv, NTT pair, inner product, iNTT pair, BConv, SuD pair (the rotation itself is
+            # folded into the reads of the iNTT, the inner product and the SuD tail: no launch of its own)
+            self.gpu_launches_per_step = 2 + 1 + 2 + 1 + 2 + 1 + 2
         self.elt = hrot_galois_elt()
         self.i = 0
         self.ct_bytes = self.cts[0].numel() * 8
         # algorithmic (compulsory) bytes of one HRot: ciphertext in + key + ciphertext out
         self.alg_bytes = (2 * prm.L + prm.dnum * 2 * (prm.L + prm.K) + 2 * prm.L) * N * 8
-        self.host_in = torch.empty(self.cts[0].shape, dtype=torch.int64).pin_memory()
-        self.host_in.copy_(self.cts[0].cpu())
-        self.host_out = torch.empty(self.cts[0].shape, dtype=torch.int64).pin_memory()
-        # iNTT pair, BConv, NTT pair, inner product, iNTT pair, BConv, SuD pair (the rotation itself is
-        # folded into the reads of the iNTT, the inner product and the SuD tail: no launch of its own)
-        self.gpu_launches_per_step = 2 + 1 + 2 + 1 + 2 + 1 + 2
+        self.host_ins = [torch.empty(self.cts[0].shape, dtype=torch.int64).pin_memory() for _ in range(3)]
+        for h in self.host_ins:
+            h.copy_(self.cts[0].cpu())
 
-    def _hrot(self, ct, out):
+    def _hrot(self, ct, out, stream=None, slot=0):
+        s = self.torch.cuda.current_stream().cuda_stream if stream is None else stream
         if self.sharded:
-            self.sk.hrot(out[0], out[1], ct[0], ct[1], self.evk, self.elt)
+            self.sks[slot].hrot(out[0], out[1], ct[0], ct[1], self.evk, self.elt, s)
         else:
             self.ks.hrot(out[0].data_ptr(), out[1].data_ptr(), ct[0].data_ptr(), ct[1].data_ptr(),
-                         self.evk.data_ptr(), self.elt, self.torch.cuda.current_stream().cuda_stream)
+                         self.evk.data_ptr(), self.elt, s)
 
     def step(self):
         k = self.i % self.n_cts
+        if self.sharded:
+            slot = self.i % self.inflight
+            self._hrot(self.cts[k], self.outs[slot], self.streams[slot].cuda_stream, slot)
+        else:
+            self._hrot(self.cts[k], self.outs[k])
         self.i += 1
-        self._hrot(self.cts[k], self.outs[k])
+
+    # the timed region is bracketed by events on the current stream: the side streams start after its
+    # first event and are joined before its second
+    def fork(self):
+        if self.sharded:
+            cur = self.torch.cuda.current_stream()
+            for st in self.streams:
+                st.wait_stream(cur)
+
+    def join(self):
+        if self.sharded:
+            cur = self.torch.cuda.current_stream()
+            for st in self.streams:
+                cur.wait_stream(st)
 
     def verify(self, orc_mod):
-        """One operation on the benchmark's own inputs against the oracle, every limb bit for bit
-        (outside the timed region).  Sharded: every rank checks its own limbs."""
+        """One operation on the benchmark's own inputs, every limb bit for bit, outside the timed region.
+        One GPU: against the oracle.  Sharded: every rank runs the whole one-GPU operation on the same
+        ciphertext (the path the oracle pins at this shape) and compares its own limbs with it, for
+        every plan in flight."""
         torch, prm = self.torch, self.prm
+        u = lambda t: t.cpu().numpy().view(np.uint64)  # noqa: E731
         if self.sharded:
-            return None   # the sharded leg is compared with the one-GPU result by its caller
+            from cerium_b200 import _capi
+            ks = _capi.KeySwitch(self.ctx, prm.q_idx, prm.p_idx, prm.dnum, _capi.BCONV_EXACT, _capi.ROUND_HALF)
+            full = torch.empty_like(self.full_ct0)
+            ks.hrot(full[0].data_ptr(), full[1].data_ptr(), self.full_ct0[0].data_ptr(), self.full_ct0[1].data_ptr(),
+                    self.full_evk.data_ptr(), self.elt, torch.cuda.current_stream().cuda_stream)
+            ok = True
+            for slot in range(self.inflight):
+                out = self.outs[slot]
+                out.zero_()
+                self._hrot(self.cts[0], out, None, slot)
+                torch.cuda.synchronize()
+                ok = ok and bool(torch.equal(out, full[:, self.mine]))
+            ks.close()
+            del self.full_evk, self.full_ct0, full
+            torch.cuda.empty_cache()
+            return ok
         ct, out = self.cts[0], self.outs[0]
         self._hrot(ct, out)
         torch.cuda.synchronize()
-        u = lambda t: t.cpu().numpy().view(np.uint64)  # noqa: E731
         octx = orc_mod.OracleContext(LOGN, prm.moduli)
         w0, w1 = octx.hrot(orc_mod.BCONV_EXACT, orc_mod.ROUND_HALF, prm.q_idx, prm.p_idx, prm.dnum, self.elt,
                            u(ct[0]), u(ct[1]), u(self.evk))
@@ -247,37 +306,52 @@ class HRotWorkload(Workload):
         return bool(np.array_equal(got[0], w0) and np.array_equal(got[1], w1))
 
     def e2e_step(self):
-        if self.sharded:
-            ct, out = self.cts[0], self.outs[0]
-            ct.copy_(self.host_in, non_blocking=True)
-            self._hrot(ct, out)
-            self.host_out.copy_(out, non_blocking=True)
-            return self.ct_bytes, self.ct_bytes
         if getattr(self, "pipe", None) is None:
             from cerium_b200.host_pipeline import HostPipeline
 
             def op(ins, outs, stream):
-                ct, out = ins[0], outs[0]
-                self.ks.hrot(out[0].data_ptr(), out[1].data_ptr(), ct[0].data_ptr(), ct[1].data_ptr(),
-                             self.evk.data_ptr(), self.elt, stream)
+                self._hrot(ins[0], outs[0], stream, 0)
             self.pipe = HostPipeline(self.torch, [self.cts[0].shape], [self.cts[0].shape], op)
-        self.pipe.submit([self.host_in])
+            self.e2e_i = 0
+        self.pipe.submit([self.host_ins[self.e2e_i % len(self.host_ins)]])
+        self.e2e_i += 1
         return self.pipe.in_bytes, self.pipe.out_bytes
+
+    def e2e_drain(self):
+        if getattr(self, "pipe", None) is not None:
+            self.pipe.drain()
+
+    # the collective(s) of one sharded operation alone, on buffers of the same size
+    def collective_step(self):
+        sk = self.sks[0]
+        if not hasattr(self, "cbuf"):
+            n_q = self.world * sk.g
+            n_p = self.world * 2 * (-(-self.prm.K // self.world)) if self.ext_split else 0
+            self.cbuf = self.torch.zeros((n_q + n_p, N), dtype=self.torch.int64, device="cuda")
+            self.c_nq = n_q
+        s = self.torch.cuda.current_stream().cuda_stream
+        base = self.cbuf.data_ptr()
+        self.comm.allgather_limbs(self.ctx, base, base + self.rank * sk.g * N * 8, sk.g, s)
+        if self.ext_split:
+            kg = 2 * (-(-self.prm.K // self.world))
+            pb = base + self.c_nq * N * 8
+            self.comm.allgather_limbs(self.ctx, pb, pb + self.rank * kg * N * 8, kg, s)
 
     # dominant kernel pair: forward NTT over the raised limbs (dnum*(L+K) - L limb transforms)
     def roofline_setup(self):
         prm = self.prm
         self.rl_idx = []
         if getattr(self, "sharded", False):
-            from cerium_b200 import sharded as sh
-            mine = sh.local_limb_indices(prm.L, self.sk.rank, self.sk.world)
+            mine = self.mine
+            ext = [prm.p_idx[k] for k in self.sh.local_ext_indices(prm.L, prm.K, self.rank, self.world, self.ext_split)]
         else:
             mine = list(range(prm.L))
+            ext = prm.p_idx
         for d in range(prm.dnum):
             for i in mine:
                 if i % prm.dnum != d:
                     self.rl_idx.append(prm.q_idx[i])
-            self.rl_idx.extend(prm.p_idx)
+            self.rl_idx.extend(ext)
         gen = self.torch.Generator(device="cuda").manual_seed(5)
         self.rl_buf = _rand_limbs_gpu(self.torch, prm.moduli, self.rl_idx, (), gen)
         self.rl_bytes = 2 * len(self.rl_idx) * N * 8  # read once + write once
@@ -513,7 +587,7 @@ class HoistedWorkload(HRotWorkload):
             def op(ins, outs, stream):
                 self._run(ins[0], outs, stream)
             self.pipe = HostPipeline(self.torch, [self.cts[0].shape], [self.cts[0].shape] * self.ops_per_step, op)
-        self.pipe.submit([self.host_in])
+        self.pipe.submit([self.host_ins[0]])
         return self.pipe.in_bytes, self.pipe.out_bytes
 
     def cpu_sample(self, orc_mod):
@@ -568,7 +642,7 @@ class BsgsWorkload(HRotWorkload):
             def op(ins, outs, stream):
                 self._run(ins[0], outs[0], stream)
             self.pipe = HostPipeline(self.torch, [self.cts[0].shape], [self.cts[0].shape], op)
-        self.pipe.submit([self.host_in])
+        self.pipe.submit([self.host_ins[0]])
         return self.pipe.in_bytes, self.pipe.out_bytes
 
     def cpu_sample(self, orc_mod):
@@ -617,6 +691,97 @@ def run_reference_arm(args, wl):
     print(json.dumps(line), flush=True)
 
 
+def bind_to_gpu_numa(torch, local_rank):
+    """Best effort: run this process (and so first-touch its pinned buffers) on the NUMA node of its GPU."""
+    try:
+        bus = torch.cuda.get_device_properties(local_rank).pci_bus_id
+        dom = torch.cuda.get_device_properties(local_rank).pci_domain_id
+        dev = torch.cuda.get_device_properties(local_rank).pci_device_id
+        path = "/sys/bus/pci/devices/%04x:%02x:%02x.0/numa_node" % (dom, bus, dev)
+        node = int(open(path).read().strip())
+        if node < 0:
+            return None
+        cpus = []
+        for part in open("/sys/devices/system/node/node%d/cpulist" % node).read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.extend(range(int(lo), int(hi or lo) + 1))
+        allowed = sorted(set(cpus) & os.sched_getaffinity(0))
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+        return node
+    except Exception:
+        return None
+
+
+def time_blocks(torch, dist, world, wl, steps, blocks, barrier):
+    """`blocks` timed regions of `steps` steps each (CUDA events on the current stream, side streams
+    forked and joined inside, max over ranks); returns the list of milliseconds."""
+    out = []
+    for _ in range(blocks):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        wl.fork()
+        for _ in range(steps):
+            wl.step()
+        wl.join()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        out.append(ms)
+    return out
+
+
+def roofline_of(torch, wl, peak, peak_kind, iters=20):
+    wl.roofline_setup()
+    for _ in range(3):
+        wl.roofline_step()
+    torch.cuda.synchronize()
+    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    r0.record()
+    for _ in range(iters):
+        wl.roofline_step()
+    r1.record()
+    torch.cuda.synchronize()
+    rl_ms = r0.elapsed_time(r1) / iters
+    achieved = wl.rl_bytes / (rl_ms / 1e3) / 1e9
+    limbs = wl.rl_bytes // (2 * N * 8)
+    return {"bound": "hbm", "kernel": wl.rl_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "frac": achieved / peak, "traffic": NTT_PAIR_DRAM_BYTES_PER_LIMB * limbs,
+            "traffic_source": "profiles/ (ncu capture of the forward NTT pair, scaled by limbs)",
+            "peak_kind": peak_kind, "ms_per_launch_pair": rl_ms, "algorithmic_bytes": wl.rl_bytes}, rl_ms, limbs
+
+
+def sub_measurement(torch, lib, name, steps, peak, peak_kind, verify_with):
+    """A short run of another workload (its own inputs, verification, timing and roofline) for the default line."""
+    wl = WORKLOADS[name]()
+    wl.setup(lib, torch, 0, 1, False)
+    verified = wl.verify(verify_with) if verify_with is not None else None
+    if verified is False:
+        return {"workload": wl.name, "verified": False}
+    for _ in range(10):
+        wl.step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        wl.step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    rl, _, _ = roofline_of(torch, wl, peak, peak_kind, iters=10)
+    out = {"workload": wl.name, "metric": wl.metric, "value": wl.ops_per_step / (ms / 1e3), "unit": wl.unit,
+           "ms_per_step": ms, "steps": steps, "verified": verified, "roofline": rl,
+           "step_algorithmic_gbs": wl.alg_bytes / (ms / 1e3) / 1e9}
+    del wl
+    torch.cuda.empty_cache()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -626,11 +791,15 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-verify", action="store_true", help="skip the oracle comparison before timing")
+    ap.add_argument("--no-sub", action="store_true", help="skip the short hmult / ntt measurements of the default line")
+    ap.add_argument("--blocks", type=int, default=5, help="timed blocks of --steps steps (the first is the headline)")
     ap.add_argument("--parallelism", choices=["auto", "limb", "replica"], default="auto",
-                    help="N > 1: 'replica' runs independent ciphertexts per rank (throughput, weak scaling); 'limb' "
-                         "shards every ciphertext and key by RNS limb over the ranks (one all-gather per key switch, "
-                         "latency of one operation, strong scaling); 'auto' reports the replica throughput as the "
-                         "headline and times the limb-sharded operation beside it (key 'limb_sharded')")
+                    help="N > 1, hrot: 'limb' (what 'auto' picks) shards every ciphertext and key by RNS limb over the "
+                         "ranks, NCCL all-gathers where limbs must meet, several operations in flight; 'replica' runs "
+                         "independent ciphertexts per rank with no collective")
+    ap.add_argument("--inflight", type=int, default=4, help="limb-sharded operations in flight per rank")
+    ap.add_argument("--ext", choices=["split", "replicated"], default="split",
+                    help="limb-sharded: extension limbs split over the ranks, or replicated on every rank")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]()
     if args.impl == "reference":
@@ -651,11 +820,18 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
     torch.cuda.set_device(local_rank)
+    numa = bind_to_gpu_numa(torch, local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     lib = _capi.load()
-    sharded = world > 1 and args.parallelism == "limb" and args.workload == "hrot"
-    wl.setup(lib, torch, rank, world, sharded)
+    sharded = world > 1 and args.parallelism in ("auto", "limb") and args.workload == "hrot"
+    comm = None
+    if sharded:
+        from cerium_b200 import sharded as sh
+        comm = sh.nccl_comm(lib, rank, world, local_rank)
+        wl.setup(lib, torch, rank, world, True, comm=comm, ext_split=args.ext == "split", inflight=max(1, args.inflight))
+    else:
+        wl.setup(lib, torch, rank, world, False)
     ops = wl.ops_per_step
     job_ops = 1 if sharded else world   # ops per step of the whole job: one sharded op, or one per replica
 
@@ -664,12 +840,14 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    # parity first: one operation on the benchmark's own inputs against the oracle (the checker),
-    # outside every timed region; no value is printed for a path whose result is wrong
+    # parity first: one operation on the benchmark's own inputs against the oracle (the checker; sharded:
+    # against the one-GPU operation the oracle pins), outside every timed region; no value is printed for
+    # a path whose result is wrong
     verified = None
+    oracle = None
     if not args.no_verify:
         import oracle
-        oracle.set_num_threads(max(1, (os.cpu_count() or 1) // max(1, world)))
+        oracle.set_num_threads(max(1, len(os.sched_getaffinity(0)) // max(1, world)))
         verified = wl.verify(oracle)
         if world > 1 and verified is not None:
             t = torch.tensor([1 if verified else 0], dtype=torch.int32, device="cuda")
@@ -681,83 +859,89 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    wl.fork()
     for _ in range(args.warmup):
         wl.step()
+    wl.join()
     barrier()
     sampler.mark_start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        wl.step()
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    block_ms = time_blocks(torch, dist, world, wl, args.steps, max(1, args.blocks), barrier)
+    ms = block_ms[0]
 
-    # dominant kernel pair, timed live with CUDA events on the launching stream
-    wl.roofline_setup()
-    for _ in range(3):
-        wl.roofline_step()
-    torch.cuda.synchronize()
-    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    rl_iters = 20
-    r0.record()
-    for _ in range(rl_iters):
-        wl.roofline_step()
-    r1.record()
-    torch.cuda.synchronize()
-    rl_ms = r0.elapsed_time(r1) / rl_iters
+    peak, peak_kind = measured_peaks()
+    roofline, rl_ms, rl_limbs = roofline_of(torch, wl, peak, peak_kind)
     clocks = sampler.stop() if rank == 0 else None
     probe = probe_int_pipe(local_rank) if rank == 0 else None
 
-    # end to end: host buffers in, host buffers out, through the same C ABI calls
-    # N > 1, auto: the same operation limb-sharded over all ranks (its latency, not its throughput)
-    limb_line = None
-    if world > 1 and args.parallelism == "auto" and args.workload == "hrot":
-        wl2 = WORKLOADS["hrot"]()
-        wl2.setup(lib, torch, rank, world, True)
-        steps2 = max(5, min(args.steps, 200))
+    # N > 1: the other parallelism beside the headline, and the collectives of one sharded operation alone
+    side = {}
+    if sharded:
         for _ in range(5):
-            wl2.step()
+            wl.collective_step()
         barrier()
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s0.record()
-        for _ in range(steps2):
-            wl2.step()
-        s1.record()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for _ in range(50):
+            wl.collective_step()
+        c1.record()
         barrier()
-        t = torch.tensor([s0.elapsed_time(s1)], dtype=torch.float64, device="cuda")
+        t = torch.tensor([c0.elapsed_time(c1) / 50], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms2 = float(t.item()) / steps2
-        limb_line = {"ms_per_op": ms2, "value": wl2.ops_per_step / (ms2 / 1e3), "unit": wl2.unit, "steps": steps2,
-                     "scaling": "strong",
-                     "parallelism": "one operation, ciphertext and key limb-sharded over %d ranks, one NCCL "
-                                    "all-gather per key switch" % world}
-        del wl2
+        side["collective_ms_per_op"] = float(t.item())
+        # latency of ONE operation (nothing else in flight)
+        wl1 = wl
+        keep = wl1.inflight
+        wl1.inflight = 1
+        lat = time_blocks(torch, dist, world, wl1, max(5, min(args.steps, 200)), 1, barrier)[0] / max(5, min(args.steps, 200))
+        wl1.inflight = keep
+        side["latency_ms_one_op_in_flight"] = lat
+        # replicas: independent ciphertexts per GPU, no collective (weak scaling by construction)
+        wr = WORKLOADS["hrot"]()
+        wr.setup(lib, torch, rank, world, False)
+        for _ in range(10):
+            wr.step()
+        rsteps = max(5, min(args.steps, 400))
+        rms = time_blocks(torch, dist, world, wr, rsteps, 1, barrier)[0]
+        side["replicas"] = {"value": world * rsteps / (rms / 1e3), "unit": wl.unit, "scaling": "weak",
+                            "parallelism": "independent ciphertexts per GPU, no collective"}
+        del wr
+        torch.cuda.empty_cache()
 
+    # end to end: pinned host buffers in and out through the same C ABI calls, three streams
     e2e_steps = max(5, min(args.steps, 200))
     for _ in range(3):
         wl.e2e_step()
+    wl.e2e_drain()
     barrier()
     t0 = time.perf_counter()
     h2d = d2h = 0
     for _ in range(e2e_steps):
         h2d, d2h = wl.e2e_step()
+    wl.e2e_drain()
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
+    # the copies alone: the same bytes up and down per step on two streams, nothing computed
+    pipe = wl.pipe
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        slot = i % pipe.depth
+        with torch.cuda.stream(pipe.s_in):
+            for d, h in zip(pipe.dev_in[slot], pipe.last_host_ins):
+                d.copy_(h, non_blocking=True)
+        with torch.cuda.stream(pipe.s_out):
+            for h, d in zip(pipe.host_out[slot], pipe.dev_out[slot]):
+                h.copy_(d, non_blocking=True)
+    torch.cuda.synchronize()
+    copy_s = time.perf_counter() - t0
     if world > 1:
-        t = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
+        t = torch.tensor([e2e_s, copy_s], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
+        e2e_s, copy_s = float(t[0].item()), float(t[1].item())
 
     if rank == 0:
-        peak, peak_kind = measured_peaks()
         value = job_ops * ops * args.steps / (ms / 1e3)
-        achieved = wl.rl_bytes / (rl_ms / 1e3) / 1e9
+        per_step = sorted(b / args.steps for b in block_ms)
         line = {
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
@@ -767,29 +951,30 @@ def main():
             "verified": verified,
             "l2": "working set larger than L2 (keys + ciphertexts + workspace > 126 MB)",
             "parallelism": ("single GPU" if world == 1 else
-                            "limb-sharded ciphertexts and keys, one NCCL all-gather per key switch" if sharded
+                            "every ciphertext and key limb-sharded over %d ranks (%s extension limbs), NCCL all-gather "
+                            "where limbs must meet, %d operations in flight" % (world, args.ext, wl.inflight) if sharded
                             else "independent ciphertexts per GPU"),
+            "repeat": {"blocks": len(block_ms), "steps_per_block": args.steps, "ms_per_step_median": per_step[len(per_step) // 2],
+                       "ms_per_step_min": per_step[0], "ms_per_step_max": per_step[-1]},
             "e2e": {"value": job_ops * ops * e2e_steps / e2e_s, "unit": wl.unit, "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h},
+                    "d2h_bytes_per_step": d2h, "copy_ceiling": job_ops * ops * e2e_steps / copy_s,
+                    "copy_ceiling_note": "the same bytes up and down per step with nothing computed, same streams and buffers",
+                    "numa_node": numa},
             "gpu_launches": wl.gpu_launches_per_step * args.steps,
-            "roofline": {"bound": "hbm", "kernel": wl.rl_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": NTT_PAIR_DRAM_BYTES_PER_LIMB * (wl.rl_bytes // (2 * N * 8)),
-                         "traffic_source": "profiles/hrot_u64_top_kernels_ncu_full.md (ncu, 245 limbs, scaled by limbs)",
-                         "peak_kind": peak_kind,
-                         "ms_per_launch_pair": rl_ms, "algorithmic_bytes": wl.rl_bytes},
+            "roofline": roofline,
             # the 64-bit transforms are also bound by arithmetic: butterflies per second of the same launch
             # pair against the register-only rate of the butterfly these primes use (FP64 pipe for primes
             # below 2^50), measured on this GPU just now
-            "arith_roofline": {"pipe": "fp64", "achieved_gbutterfly_s": len(wl.rl_idx if hasattr(wl, "rl_idx") else wl.idx)
-                               * (N // 2) * 16 / (rl_ms / 1e3) / 1e9,
+            "arith_roofline": {"pipe": "fp64", "achieved_gbutterfly_s": rl_limbs * (N // 2) * 16 / (rl_ms / 1e3) / 1e9,
                                "peak_gbutterfly_s": probe["butterfly_u64_fp64"], "probe": probe},
             "step_algorithmic_gbs": job_ops * wl.alg_bytes * args.steps / (ms / 1e3) / 1e9,
             "clocks": clocks,
         }
         line["arith_roofline"]["frac"] = (line["arith_roofline"]["achieved_gbutterfly_s"]
                                           / line["arith_roofline"]["peak_gbutterfly_s"])
-        if limb_line is not None:
-            line["limb_sharded"] = limb_line
+        line.update(side)
+        if world == 1 and args.workload == "hrot" and not args.no_sub:
+            line["sub"] = {name: sub_measurement(torch, lib, name, 200, peak, peak_kind, oracle) for name in ("hmult", "ntt")}
         if not args.no_cpu_baseline and world == 1:
             import oracle
             oracle.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
@@ -797,6 +982,8 @@ def main():
             line["cpu_baseline"] = {"value": v, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",
                                     "port_quality": PORT_QUALITY, "sample": sample}
         print(json.dumps(line), flush=True)
+    if comm is not None:
+        comm.close()
     if world > 1:
         dist.destroy_process_group()
 

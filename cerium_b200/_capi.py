@@ -16,7 +16,8 @@ LIB_PATH = os.path.join(HERE, "libcerium_b200.so")
 OK, ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED = 0, 1, 2, 3
 BCONV_LAZY, BCONV_EXACT = 0, 1
 ROUND_FLOOR, ROUND_HALF = 0, 1
-EW_ADD, EW_SUB, EW_NEG, EW_MUL, EW_MAD, EW_PMU, EW_MUL_SCALAR = range(7)
+EW_ADD, EW_SUB, EW_NEG, EW_MUL, EW_MAD, EW_PMU, EW_MUL_SCALAR, EW_REDUCE = range(8)
+COMM_ID_BYTES = 128
 
 _vp = C.c_void_p
 _u32p = C.POINTER(C.c_uint32)
@@ -58,8 +59,22 @@ SIGNATURES = {
     "cerium_bconv_apply": (C.c_int, [_vp, _vp, _sz, _vp, _sz, _vp]),
     "cerium_bconv_apply_batch": (C.c_int, [C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), C.c_int, _sz, _sz, _vp]),
     "cerium_keyswitch_create": (C.c_int, [_vp, C.POINTER(_vp), C.c_int, C.c_int, _u32p, C.c_int, _u32p, C.c_int, C.c_int]),
-    "cerium_keyswitch_create_sharded": (C.c_int, [_vp, C.POINTER(_vp), C.c_int, C.c_int, _u32p, C.c_int, _u32p, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "cerium_keyswitch_create_sharded": (C.c_int, [_vp, C.POINTER(_vp), C.c_int, C.c_int, _u32p, C.c_int, _u32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "cerium_keyswitch_local_limbs": (C.c_int, [_vp]),
+    "cerium_keyswitch_local_ext_limbs": (C.c_int, [_vp]),
+    "cerium_keyswitch_sharded_apply": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "cerium_hrot_sharded": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_uint32, _vp]),
+    "cerium_rescale_sharded": (C.c_int, [_vp, _vp, C.c_int, _vp, _vp, _u32p, C.c_int, C.c_int, _vp, _vp]),
+    "cerium_comm_unique_id": (C.c_int, [_vp, _sz]),
+    "cerium_comm_init": (C.c_int, [C.POINTER(_vp), _vp, _sz, C.c_int, C.c_int, C.c_int]),
+    "cerium_comm_init_callbacks": (C.c_int, [C.POINTER(_vp), C.c_int, C.c_int, C.c_int, _vp]),
+    "cerium_comm_destroy": (C.c_int, [_vp]),
+    "cerium_comm_rank": (C.c_int, [_vp]),
+    "cerium_comm_world": (C.c_int, [_vp]),
+    "cerium_allgather_limbs": (C.c_int, [_vp, _vp, _vp, _vp, _sz, _vp]),
+    "cerium_reducescatter_limbs": (C.c_int, [_vp, _vp, _vp, _vp, _u32p, C.c_int, _vp]),
+    "cerium_allreduce_limbs": (C.c_int, [_vp, _vp, _vp, _vp, _u32p, C.c_int, _vp]),
+    "cerium_broadcast_limbs": (C.c_int, [_vp, _vp, _vp, _sz, C.c_int, _vp]),
     "cerium_keyswitch_gather_limbs": (C.c_int, [_vp]),
     "cerium_keyswitch_sharded_begin": (C.c_int, [_vp, _vp, _vp, _vp]),
     "cerium_keyswitch_sharded_finish": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
@@ -229,6 +244,13 @@ class Context:
         self.lib.check(self.lib.dll.cerium_rescale_local(self.h, round_mode, out, inp, _u32(local_idx), len(local_idx),
                                                          last_prime, last_coef, n_polys, stream))
 
+    def rescale_sharded(self, comm: "Comm", out: int, inp: int, q_idx: Sequence[int], n_polys: int, last_coef: int,
+                        round_mode: int = ROUND_FLOOR, stream: int = 0):
+        """Rescale of this rank's limbs of a limb-sharded ciphertext (owner's inverse transform of the
+        last limb, broadcast, division of the remaining local limbs)."""
+        self.lib.check(self.lib.dll.cerium_rescale_sharded(self.h, comm.h, round_mode, out or None, inp or None,
+                                                           _u32(q_idx), len(q_idx), n_polys, last_coef, stream))
+
     def double_rescale(self, out: int, inp: int, q_idx: Sequence[int], n_polys: int, scratch: int, stream: int = 0):
         """Drops the last two limbs at once; scratch holds 4 * n_polys limbs."""
         self.lib.check(self.lib.dll.cerium_double_rescale(self.h, out, inp, _u32(q_idx), len(q_idx), n_polys,
@@ -239,6 +261,89 @@ class Context:
         """Rescale with the library's built-in scratch (no device allocation anywhere; n_polys <= 2)."""
         self.lib.check(self.lib.dll.cerium_rescale_static(self.h, round_mode, out, inp, _u32(q_idx), len(q_idx),
                                                           n_polys, stream))
+
+
+ALLGATHER_FN = C.CFUNCTYPE(C.c_int, _vp, _vp, _vp, _sz, _vp)
+REDUCESCATTER_FN = C.CFUNCTYPE(C.c_int, _vp, _vp, _vp, _sz, C.c_int, _vp)
+ALLREDUCE_FN = C.CFUNCTYPE(C.c_int, _vp, _vp, _vp, _sz, C.c_int, _vp)
+BROADCAST_FN = C.CFUNCTYPE(C.c_int, _vp, _vp, _sz, C.c_int, _vp)
+
+
+class CommCallbacks(C.Structure):
+    """``cerium_comm_callbacks``: the caller's own collectives."""
+    _fields_ = [("user", _vp), ("allgather", ALLGATHER_FN), ("reducescatter", REDUCESCATTER_FN),
+                ("allreduce", ALLREDUCE_FN), ("broadcast", BROADCAST_FN)]
+
+
+class Comm:
+    """Communicator of the limb collectives (handle of ``cerium_comm``).
+
+    ``Comm(lib, rank, world, device, nccl_id=...)`` joins an NCCL communicator (``Comm.unique_id(lib)``
+    on rank 0, handed to every rank by the caller); ``Comm(lib, rank, world, device, transport=obj)``
+    uses the caller's collectives: ``obj`` has methods ``allgather(recv, send, bytes_per_rank,
+    stream)``, ``reducescatter(recv, send, words_per_rank, word_bits, stream)``, ``allreduce(recv,
+    send, words, word_bits, stream)``, ``broadcast(buf, bytes, root, stream)`` over raw addresses
+    (missing methods leave that collective unsupported)."""
+
+    def __init__(self, lib: Library, rank: int, world: int, device: int = 0, nccl_id: Optional[bytes] = None,
+                 transport=None):
+        self.lib, self.rank, self.world = lib, rank, world
+        h = _vp()
+        if transport is not None:
+            def wrap(fn_type, method):
+                m = getattr(transport, method, None)
+                if m is None:
+                    return fn_type()
+
+                def call(user, *args):
+                    try:
+                        m(*[0 if a is None else a for a in args])
+                        return 0
+                    except Exception:       # an exception cannot cross the C boundary
+                        import traceback
+                        traceback.print_exc()
+                        return 1
+                return fn_type(call)
+            self._cb = CommCallbacks(None, wrap(ALLGATHER_FN, "allgather"), wrap(REDUCESCATTER_FN, "reducescatter"),
+                                     wrap(ALLREDUCE_FN, "allreduce"), wrap(BROADCAST_FN, "broadcast"))
+            lib.check(lib.dll.cerium_comm_init_callbacks(C.byref(h), rank, world, device, C.byref(self._cb)))
+        else:
+            if nccl_id is None or len(nccl_id) < COMM_ID_BYTES:
+                raise ValueError("an NCCL communicator needs the %d-byte id made by Comm.unique_id" % COMM_ID_BYTES)
+            buf = C.create_string_buffer(bytes(nccl_id), COMM_ID_BYTES)
+            lib.check(lib.dll.cerium_comm_init(C.byref(h), buf, COMM_ID_BYTES, rank, world, device))
+        self.h = h
+
+    @staticmethod
+    def unique_id(lib: Library) -> bytes:
+        buf = C.create_string_buffer(COMM_ID_BYTES)
+        lib.check(lib.dll.cerium_comm_unique_id(buf, COMM_ID_BYTES))
+        return buf.raw
+
+    def allgather_limbs(self, ctx: "Context", gathered: int, send: int, limbs_per_rank: int, stream: int = 0):
+        self.lib.check(self.lib.dll.cerium_allgather_limbs(self.h, ctx.h, gathered, send, limbs_per_rank, stream))
+
+    def reducescatter_limbs(self, ctx: "Context", out: int, inp: int, prime_idx: Sequence[int], stream: int = 0):
+        self.lib.check(self.lib.dll.cerium_reducescatter_limbs(self.h, ctx.h, out, inp, _u32(prime_idx),
+                                                               len(prime_idx), stream))
+
+    def allreduce_limbs(self, ctx: "Context", out: int, inp: int, prime_idx: Sequence[int], stream: int = 0):
+        self.lib.check(self.lib.dll.cerium_allreduce_limbs(self.h, ctx.h, out, inp, _u32(prime_idx), len(prime_idx),
+                                                           stream))
+
+    def broadcast_limbs(self, ctx: "Context", buf: int, limbs: int, root: int, stream: int = 0):
+        self.lib.check(self.lib.dll.cerium_broadcast_limbs(self.h, ctx.h, buf, limbs, root, stream))
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.dll.cerium_comm_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class BaseConverter:
@@ -285,10 +390,10 @@ class KeySwitch:
 
     def __init__(self, ctx: Context, q_idx: Sequence[int], p_idx: Sequence[int], dnum: int,
                  bconv_mode: int = BCONV_LAZY, round_mode: int = ROUND_FLOOR, rank: int = 0, world: int = 1,
-                 lifted: bool = False):
+                 lifted: bool = False, ext_split: bool = False):
         self.ctx = ctx
         self.q_idx, self.p_idx, self.dnum = list(q_idx), list(p_idx), dnum
-        self.rank, self.world = rank, world
+        self.rank, self.world, self.ext_split = rank, world, bool(ext_split) and world > 1
         h = _vp()
         if lifted:
             # ModRaise plan: q_idx = target primes + the prime the final rescale drops; one lifted digit
@@ -297,7 +402,7 @@ class KeySwitch:
         else:
             ctx.lib.check(ctx.lib.dll.cerium_keyswitch_create_sharded(ctx.h, C.byref(h), bconv_mode, round_mode,
                                                                       _u32(q_idx), len(q_idx), _u32(p_idx), len(p_idx),
-                                                                      dnum, rank, world))
+                                                                      dnum, rank, world, 1 if ext_split else 0))
         self.h = h
 
     def mod_raise(self, out0: int, out1: int, c0: int, c1: int, base0: int, base1: int, evk: int, stream: int = 0):
@@ -310,6 +415,22 @@ class KeySwitch:
     @property
     def gather_limbs(self) -> int:
         return int(self.ctx.lib.dll.cerium_keyswitch_gather_limbs(self.h))
+
+    @property
+    def local_ext_limbs(self) -> int:
+        return int(self.ctx.lib.dll.cerium_keyswitch_local_ext_limbs(self.h))
+
+    def sharded_apply(self, comm: "Comm", out0: int, out1: int, cpoly_local: int, evk_local: int, add0: int = 0,
+                      add1: int = 0, stream: int = 0):
+        self.ctx.lib.check(self.ctx.lib.dll.cerium_keyswitch_sharded_apply(
+            self.h, comm.h, out0 or None, out1 or None, cpoly_local or None, evk_local, add0 or None, add1 or None,
+            stream))
+
+    def hrot_sharded(self, comm: "Comm", out0: int, out1: int, c0_local: int, c1_local: int, evk_local: int,
+                     galois_elt: int, stream: int = 0):
+        self.ctx.lib.check(self.ctx.lib.dll.cerium_hrot_sharded(
+            self.h, comm.h, out0 or None, out1 or None, c0_local or None, c1_local or None, evk_local, galois_elt,
+            stream))
 
     def sharded_begin(self, send: int, cpoly_local: int, stream: int = 0):
         self.ctx.lib.check(self.ctx.lib.dll.cerium_keyswitch_sharded_begin(self.h, send, cpoly_local or None, stream))

@@ -119,7 +119,20 @@ int launch_ntt_inverse(cerium_context* ctx, const NttCall& c, const void* scale,
         sc.scale = static_cast<const W*>(scale) + first;
         sc.scale_shoup = static_cast<const W*>(scale_shoup) + first;
       }
-      { auto kfn = ntt_inv_rows_kernel<W, StridedBatch<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kRowsPerCta, cnt), kRowsPerCta * 16, 0, stream, sb, static_cast<const Pair*>(ctx->d_tw_inv), static_cast<const Pair*>(ctx->d_twr_inv), static_cast<const PrimeConst<W>*>(ctx->d_pcs)); }
+      if (c.src_pos != nullptr) {
+        // entry b reads limb src_pos[b] of `in` and writes limb pos[b] of `out`
+        GatherBatch<W> gb{};
+        static_cast<StridedBatch<W>&>(gb) = sb;
+        for (int b = 0; b < cnt; b++) {
+          if (c.src_pos[first + b] > 0xffffu) return fail(CERIUM_ERR_INVALID, "limb slot exceeds 65535");
+          gb.in_pos[b] = (uint16_t)c.src_pos[first + b];
+        }
+        auto kfn = ntt_inv_rows_kernel<W, GatherBatch<W>>;
+        CERIUM_LAUNCH(kfn, dim3(256 / kRowsPerCta, cnt), kRowsPerCta * 16, 0, stream, gb, static_cast<const Pair*>(ctx->d_tw_inv), static_cast<const Pair*>(ctx->d_twr_inv), static_cast<const PrimeConst<W>*>(ctx->d_pcs));
+      } else {
+        auto kfn = ntt_inv_rows_kernel<W, StridedBatch<W>>;
+        CERIUM_LAUNCH(kfn, dim3(256 / kRowsPerCta, cnt), kRowsPerCta * 16, 0, stream, sb, static_cast<const Pair*>(ctx->d_tw_inv), static_cast<const Pair*>(ctx->d_twr_inv), static_cast<const PrimeConst<W>*>(ctx->d_pcs));
+      }
       { auto kfn = ntt_inv_cols_kernel<W, StridedBatch<W>>; CERIUM_LAUNCH(kfn, dim3(256 / kCols, cnt), kCols * 16, 0, stream, sb, sc, static_cast<const Pair*>(ctx->d_tw_inv), static_cast<const PrimeConst<W>*>(ctx->d_pcs)); }
     }
     CERIUM_LAUNCH_CHECK("ntt_inverse");
@@ -847,7 +860,7 @@ int cerium_ewise(cerium_context* ctx, int op, void* out, size_t out_stride, cons
                  const void* b, size_t b_stride, const void* c, size_t c_stride, const uint64_t* scalars,
                  const uint32_t* prime_idx, int count, void* stream) {
   if (!ctx) return fail(CERIUM_ERR_INVALID, "ewise: null context");
-  if (op < CERIUM_EW_ADD || op > CERIUM_EW_MUL_SCALAR) return fail(CERIUM_ERR_INVALID, "ewise: unknown op");
+  if (op < CERIUM_EW_ADD || op > CERIUM_EW_REDUCE) return fail(CERIUM_ERR_INVALID, "ewise: unknown op");
   if (count < 0) return fail(CERIUM_ERR_INVALID, "ewise: negative count");
   if (count == 0) return CERIUM_OK;
   if (!prime_idx) return fail(CERIUM_ERR_INVALID, "ewise: null prime_idx");
@@ -895,6 +908,7 @@ int cerium_ewise(cerium_context* ctx, int op, void* out, size_t out_stride, cons
         case CERIUM_EW_MUL: { auto kfn = ewise_kernel<W, kEwMul>; CERIUM_LAUNCH(kfn, grid, kEwThreads, 0, s, g, pcs); } break;
         case CERIUM_EW_MAD: { auto kfn = ewise_kernel<W, kEwMad>; CERIUM_LAUNCH(kfn, grid, kEwThreads, 0, s, g, pcs); } break;
         case CERIUM_EW_PMU: { auto kfn = ewise_kernel<W, kEwPmu>; CERIUM_LAUNCH(kfn, grid, kEwThreads, 0, s, g, pcs); } break;
+        case CERIUM_EW_REDUCE: { auto kfn = ewise_kernel<W, kEwReduce>; CERIUM_LAUNCH(kfn, grid, kEwThreads, 0, s, g, pcs); } break;
         default: { auto kfn = ewise_kernel<W, kEwMulScalar>; CERIUM_LAUNCH(kfn, grid, kEwThreads, 0, s, g, pcs); } break;
       }
     }

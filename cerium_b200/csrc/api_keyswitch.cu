@@ -28,6 +28,13 @@ struct cerium_keyswitch {
   int bconv_mode = 0, round_mode = 0;
   int L = 0, K = 0, dnum = 0, LK = 0;
   int L_global = 0, rank = 0, world = 1, gather_limbs = 0;  // gather_limbs = ceil(L_global / world)
+  // extension limbs: replicated on every rank (K == K_global), or split over the ranks like the Q limbs
+  // (extension limb k lives on rank (L_global + k) % world; K is then the LOCAL count and the coefficient-
+  // form extension limbs of the accumulators are all-gathered before the ModDown conversion)
+  bool ext_split = false;
+  int K_global = 0, pgather_limbs = 0;  // pgather_limbs = ceil(K_global / world), per polynomial and rank
+  std::vector<int> ploc;           // global index of local extension limb
+  std::vector<uint32_t> ext_dst;   // ext_split: slot of each entry of ext_pos inside this rank's block of `pgather`
   std::vector<int> loc;            // global index of local Q-limb e
   std::vector<int> own_digit;      // [LK] digit of local extended limb e, -1 for extension limbs
   std::vector<uint32_t> q_idx, p_idx, all_idx;  // prime indices of the LOCAL limbs
@@ -55,6 +62,10 @@ struct cerium_keyswitch {
   void* ws = nullptr;
   size_t ws_bytes = 0;
   size_t o_coef = 0, o_raised = 0, o_acc = 0, o_conv = 0, o_tmp = 0, o_ksout = 0, o_scratch = 0;  // words
+  // sharded plans: [world][gather_limbs] coefficient-form limbs of the switched polynomial, and with
+  // ext_split [world][2][pgather_limbs] coefficient-form extension limbs of the two accumulators; a rank
+  // writes its own block in place and the all-gather fills the others
+  size_t o_gathered = 0, o_pgather = 0;
 };
 
 namespace {
@@ -195,9 +206,13 @@ int keyswitch_raise(cerium_keyswitch* ks, const void* gathered, cudaStream_t str
 
 // Steps 4-7 on the digits that keyswitch_raise left in the plan: inner product with `evk`,
 // ModDown, optional additions.  Can be repeated with different keys (hoisting).
+// comm: needed by plans with split extension limbs, whose accumulators' extension limbs are
+// all-gathered (coefficient form) between steps 5 and 6.
 int keyswitch_inner_moddown(cerium_keyswitch* ks, void* out0, void* out1, const void* cpoly, const void* evk,
                             const void* add0, const void* add1, cudaStream_t stream, uint32_t pre_elt = 0,
-                            uint32_t store_elt = 0) {
+                            uint32_t store_elt = 0, cerium_comm* comm = nullptr) {
+  if (ks->ext_split && comm == nullptr)
+    return fail(CERIUM_ERR_INVALID, "keyswitch: a plan with split extension limbs needs a communicator");
   cerium_context* ctx = ks->ctx;
   const size_t n = kN;
   const int L = ks->L, K = ks->K, LK = ks->LK, dnum = ks->dnum;
@@ -233,17 +248,31 @@ int keyswitch_inner_moddown(cerium_keyswitch* ks, void* out0, void* out1, const 
       g.first_limb = 0;
       { auto kfn = inner_product_kernel<W>; CERIUM_LAUNCH(kfn, dim3(kN / (kEwThreads * V::kLanes), LK), block, 0, stream, g, pcs); }
       CERIUM_LAUNCH_CHECK("inner_product");
-      // 5. iNTT of the extension limbs of both accumulators, in place
-      {
+      const W* p0 = acc + (size_t)L * n;          // coefficient-form extension limbs of accumulator 0 ...
+      const W* p1 = acc + (size_t)(LK + L) * n;   // ... and 1, as the ModDown conversion reads them
+      if (!ks->ext_split) {
+        // 5. iNTT of the extension limbs of both accumulators, in place
         NttCall c{acc, acc, n, n, ks->ext_pos.data(), ks->ext_prime.data(), 2 * K};
         if (int rc = launch_ntt_inverse(ctx, c, ks->d_scale_p, ks->d_scale_p_shoup, stream)) return rc;
+      } else {
+        // 5. iNTT of the LOCAL extension limbs into this rank's block of the gather buffer
+        //    ([world][2][pgather_limbs]), then the all-gather: every rank needs all K limbs to convert
+        W* pg = ws_at<W>(ks, ks->o_pgather);
+        const size_t block = (size_t)2 * ks->pgather_limbs * n;
+        W* mine = pg + (size_t)ks->rank * block;
+        NttCall c{acc, mine, n, n, ks->ext_dst.data(), ks->ext_prime.data(), 2 * K};
+        c.src_pos = ks->ext_pos.data();
+        if (int rc = launch_ntt_inverse(ctx, c, ks->d_scale_p, ks->d_scale_p_shoup, stream)) return rc;
+        if (int rc = comm_allgather(comm, pg, mine, block * sizeof(W), stream)) return rc;
+        p0 = pg;
+        p1 = pg + (size_t)ks->pgather_limbs * n;
       }
-      if (L == 0) return CERIUM_OK;  // a rank without Q limbs only feeds the gather
+      if (L == 0) return CERIUM_OK;  // a rank without Q limbs only feeds the gathers
       // 6. ModDown base conversion P -> local Q limbs
       {
         BconvCall calls[2] = {
-            {ks->down, conv, n, acc + (size_t)L * n, n},
-            {ks->down, conv + (size_t)L * n, n, acc + (size_t)(LK + L) * n, n},
+            {ks->down, conv, n, p0, n},
+            {ks->down, conv + (size_t)L * n, n, p1, n},
         };
         if (int rc = launch_bconv(ctx, calls, 2, stream)) return rc;
       }
@@ -301,9 +330,27 @@ int keyswitch_inner_moddown(cerium_keyswitch* ks, void* out0, void* out1, const 
 }
 
 int keyswitch_finish(cerium_keyswitch* ks, void* out0, void* out1, const void* gathered, const void* cpoly,
-                     const void* evk, const void* add0, const void* add1, cudaStream_t stream, uint32_t pre_elt = 0) {
+                     const void* evk, const void* add0, const void* add1, cudaStream_t stream, uint32_t pre_elt = 0,
+                     cerium_comm* comm = nullptr) {
   if (int rc = keyswitch_raise(ks, gathered, stream)) return rc;
-  return keyswitch_inner_moddown(ks, out0, out1, cpoly, evk, add0, add1, stream, pre_elt);
+  return keyswitch_inner_moddown(ks, out0, out1, cpoly, evk, add0, add1, stream, pre_elt, 0, comm);
+}
+
+// The whole key switch of a limb-sharded plan: inverse transform of the local limbs straight into
+// this rank's block of the gather buffer, all-gather (in place), steps 2-7 on the local limbs.
+int keyswitch_sharded_impl(cerium_keyswitch* ks, cerium_comm* comm, void* out0, void* out1, const void* cpoly,
+                           const void* evk, const void* add0, const void* add1, cudaStream_t stream,
+                           uint32_t pre_elt = 0) {
+  if (ks->world == 1) return fail(CERIUM_ERR_INVALID, "keyswitch_sharded: the plan is not sharded");
+  if (!comm || comm->world != ks->world || comm->rank != ks->rank)
+    return fail(CERIUM_ERR_INVALID, "keyswitch_sharded: the communicator does not match the plan's rank and world");
+  const size_t wb = ks->ctx->word_bytes();
+  char* gathered = static_cast<char*>(ks->ws) + ks->o_gathered * wb;
+  const size_t block = (size_t)ks->gather_limbs * kN * wb;
+  char* mine = gathered + (size_t)ks->rank * block;
+  if (int rc = keyswitch_begin(ks, mine, cpoly, stream, pre_elt)) return rc;
+  if (int rc = comm_allgather(comm, gathered, mine, block, stream)) return rc;
+  return keyswitch_finish(ks, out0, out1, gathered, cpoly, evk, add0, add1, stream, pre_elt, comm);
 }
 
 int keyswitch_impl(cerium_keyswitch* ks, void* out0, void* out1, const void* cpoly, const void* evk,
@@ -320,8 +367,9 @@ int keyswitch_impl(cerium_keyswitch* ks, void* out0, void* out1, const void* cpo
 extern "C" {
 
 static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, int bconv_mode, int round_mode,
-                                 const uint32_t* q_idx, int Lg, const uint32_t* p_idx, int K, int dnum, int rank,
-                                 int world, bool lifted = false) {
+                                 const uint32_t* q_idx, int Lg, const uint32_t* p_idx, int Kg, int dnum, int rank,
+                                 int world, bool lifted = false, bool ext_split = false) {
+  const int K = Kg;  // the checks below are on the global shape
   if (!ctx || !out || !q_idx || !p_idx) return fail(CERIUM_ERR_INVALID, "keyswitch_create: null argument");
   if (bconv_mode != CERIUM_BCONV_LAZY && bconv_mode != CERIUM_BCONV_EXACT) return fail(CERIUM_ERR_INVALID, "keyswitch_create: unknown bconv mode");
   if (round_mode != CERIUM_ROUND_FLOOR && round_mode != CERIUM_ROUND_HALF) return fail(CERIUM_ERR_INVALID, "keyswitch_create: unknown round mode");
@@ -350,28 +398,37 @@ static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, in
   ks->ctx = ctx;
   ks->bconv_mode = bconv_mode;
   ks->round_mode = round_mode;
-  ks->K = K;
   ks->dnum = dnum;
   ks->L_global = Lg;
+  ks->K_global = Kg;
   ks->rank = rank;
   ks->world = world;
   ks->gather_limbs = (Lg + world - 1) / world;
+  ks->ext_split = ext_split && world > 1;
+  ks->pgather_limbs = (Kg + world - 1) / world;
   for (int i = rank; i < Lg; i += world) {
     ks->loc.push_back(i);
     ks->q_idx.push_back(q_idx[i]);
   }
   const int L = (int)ks->loc.size();
   ks->L = L;
-  ks->LK = L + K;
-  ks->p_idx.assign(p_idx, p_idx + K);
+  // the extension limbs this rank computes: all of them, or (split) those that continue the round robin
+  for (int k = 0; k < Kg; k++)
+    if (!ks->ext_split || (Lg + k) % world == rank) {
+      ks->ploc.push_back(k);
+      ks->p_idx.push_back(p_idx[k]);
+    }
+  ks->K = (int)ks->ploc.size();
+  ks->LK = L + ks->K;
   ks->all_idx = ks->q_idx;
   ks->all_idx.insert(ks->all_idx.end(), ks->p_idx.begin(), ks->p_idx.end());
   const int LK = ks->LK;
+  const int Kl = ks->K;  // local extension limbs
   ks->lifted = lifted;
   for (int e = 0; e < LK; e++) ks->own_digit.push_back((e < L && !lifted) ? ks->loc[e] % dnum : -1);
   const int bits = ctx->word_bits;
   const bool exact = bconv_mode == CERIUM_BCONV_EXACT;
-  std::vector<uint64_t> scale_q(std::max(L, 1), 1), scale_p(2 * K, 1);
+  std::vector<uint64_t> scale_q(std::max(L, 1), 1), scale_p(2 * std::max(Kl, 1), 1);
   ks->direct_raise = alpha == 1;
   auto slot_of = [&](int i) { return (uint32_t)((i % world) * ks->gather_limbs + i / world); };
   int rc = CERIUM_OK;
@@ -406,24 +463,43 @@ static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, in
     if (rc != CERIUM_OK) break;
     ks->up.push_back(bc);
     ks->up_digit.push_back(d);
-    if (exact)
-      for (size_t k = 0; k < in_limb.size(); k++)
-        if (in_limb[k] % world == rank) scale_q[in_limb[k] / world] = bc->inv_host[k];
+  }
+  if (exact && !lifted && !ks->direct_raise) {
+    // exact conversion: the inverse transform of local limb i leaves x_i * [Qhat_i^-1]_{q_i}, Qhat_i the
+    // product of the other limbs of its digit (every rank scales its own limbs, whoever converts them)
+    for (int e = 0; e < L; e++) {
+      const int i = ks->loc[e];
+      const uint64_t qi = ctx->moduli[q_idx[i]];
+      uint64_t prod = 1 % qi;
+      for (int j = i % dnum; j < Lg; j += dnum)
+        if (j != i) prod = host::mulmod(prod, ctx->moduli[q_idx[j]] % qi, qi);
+      scale_q[e] = host::invmod(prod, qi);
+    }
   }
   if (rc == CERIUM_OK && L > 0) {
+    // P -> Q over ALL extension primes; with split extension limbs the inputs are read from the gathered
+    // buffer: limb k of a polynomial sits at slot owner(k) * 2 * pgather_limbs + (its index on the owner)
     BconvOptions opt;
     opt.prescaled = exact;
     opt.round_half = round_mode == CERIUM_ROUND_HALF;
-    rc = create_bconv(ctx, &ks->down, bconv_mode, ks->p_idx.data(), K, ks->q_idx.data(), L, opt);
+    if (ks->ext_split) {
+      std::vector<int> seen(world, 0);
+      for (int k = 0; k < Kg; k++) {
+        const int owner = (Lg + k) % world;
+        opt.in_pos.push_back((uint32_t)(owner * 2 * ks->pgather_limbs + seen[owner]++));
+      }
+    }
+    rc = create_bconv(ctx, &ks->down, bconv_mode, p_idx, Kg, ks->q_idx.data(), L, opt);
   }
   if (rc == CERIUM_OK && exact) {
     // [Phat_k^-1]_{p_k} does not depend on the output set
-    for (int k = 0; k < K; k++) {
-      const uint64_t pk = ctx->moduli[ks->p_idx[k]];
+    for (int j = 0; j < Kl; j++) {
+      const int k = ks->ploc[j];
+      const uint64_t pk = ctx->moduli[p_idx[k]];
       uint64_t prod = 1 % pk;
-      for (int j = 0; j < K; j++)
-        if (j != k) prod = host::mulmod(prod, ctx->moduli[ks->p_idx[j]] % pk, pk);
-      scale_p[k] = scale_p[K + k] = K > 1 ? host::invmod(prod, pk) : 1;
+      for (int i = 0; i < Kg; i++)
+        if (i != k) prod = host::mulmod(prod, ctx->moduli[p_idx[i]] % pk, pk);
+      scale_p[j] = scale_p[Kl + j] = Kg > 1 ? host::invmod(prod, pk) : 1;
     }
   }
   if (rc != CERIUM_OK) {
@@ -431,14 +507,18 @@ static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, in
     return rc;
   }
   ks->pinv.resize(L);
-  for (int i = 0; i < L; i++) {
-    const uint64_t q = ctx->moduli[ks->q_idx[i]];
-    ks->pinv[i] = host::invmod(host::product_mod(ctx->moduli, ks->p_idx, q), q);
+  {
+    const std::vector<uint32_t> p_all(p_idx, p_idx + Kg);
+    for (int i = 0; i < L; i++) {
+      const uint64_t q = ctx->moduli[ks->q_idx[i]];
+      ks->pinv[i] = host::invmod(host::product_mod(ctx->moduli, p_all, q), q);
+    }
   }
   for (int p = 0; p < 2; p++)
-    for (int k = 0; k < K; k++) {
+    for (int k = 0; k < Kl; k++) {
       ks->ext_pos.push_back((uint32_t)(p * LK + L + k));
       ks->ext_prime.push_back(ks->p_idx[k]);
+      ks->ext_dst.push_back((uint32_t)(p * ks->pgather_limbs + k));
     }
   const size_t wb = ctx->word_bytes();
   const size_t n = kN;
@@ -447,8 +527,9 @@ static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, in
     std::vector<uint64_t> all;
     for (int i = 0; i < L; i++) all.push_back(scale_q[i]);
     for (int i = 0; i < L; i++) all.push_back(host::shoup(scale_q[i], ctx->moduli[ks->q_idx[i]], bits));
-    for (int i = 0; i < 2 * K; i++) all.push_back(scale_p[i]);
-    for (int i = 0; i < 2 * K; i++) all.push_back(host::shoup(scale_p[i], ctx->moduli[ks->p_idx[i % K]], bits));
+    for (int i = 0; i < 2 * Kl; i++) all.push_back(scale_p[i]);
+    for (int i = 0; i < 2 * Kl; i++) all.push_back(host::shoup(scale_p[i], ctx->moduli[ks->p_idx[i % Kl]], bits));
+    if (all.empty()) all.push_back(0);
     std::vector<char> bytes(all.size() * wb);
     for (size_t i = 0; i < all.size(); i++) {
       if (bits == 32) reinterpret_cast<uint32_t*>(bytes.data())[i] = (uint32_t)all[i];
@@ -463,7 +544,7 @@ static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, in
     ks->d_scale_q = b;
     ks->d_scale_q_shoup = b + (size_t)L * wb;
     ks->d_scale_p = b + (size_t)2 * L * wb;
-    ks->d_scale_p_shoup = b + (size_t)(2 * L + 2 * K) * wb;
+    ks->d_scale_p_shoup = b + (size_t)(2 * L + 2 * Kl) * wb;
   }
   // workspace layout (in words)
   size_t off = 0;
@@ -473,6 +554,8 @@ static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, in
     return o;
   };
   ks->o_coef = take(world == 1 ? Lg : 0);
+  ks->o_gathered = take(world == 1 ? 0 : (size_t)world * ks->gather_limbs);
+  ks->o_pgather = take(ks->ext_split ? (size_t)world * 2 * ks->pgather_limbs : 0);
   ks->o_raised = take((size_t)dnum * LK);
   ks->o_acc = take(2 * (size_t)LK);
   ks->o_conv = take(2 * (size_t)std::max(L, 1));
@@ -495,8 +578,9 @@ int cerium_keyswitch_create(cerium_context* ctx, cerium_keyswitch** out, int bco
 
 int cerium_keyswitch_create_sharded(cerium_context* ctx, cerium_keyswitch** out, int bconv_mode, int round_mode,
                                     const uint32_t* q_idx, int L, const uint32_t* p_idx, int K, int dnum, int rank,
-                                    int world) {
-  return keyswitch_create_impl(ctx, out, bconv_mode, round_mode, q_idx, L, p_idx, K, dnum, rank, world);
+                                    int world, int ext_split) {
+  return keyswitch_create_impl(ctx, out, bconv_mode, round_mode, q_idx, L, p_idx, K, dnum, rank, world, false,
+                               ext_split != 0);
 }
 
 int cerium_keyswitch_create_lifted(cerium_context* ctx, cerium_keyswitch** out, int bconv_mode, int round_mode,
@@ -555,6 +639,7 @@ int cerium_keyswitch_gather_limbs(const cerium_keyswitch* ks) { return ks ? ks->
 int cerium_keyswitch_sharded_begin(cerium_keyswitch* ks, void* send, const void* cpoly_local, void* stream) {
   if (!ks || !send) return fail(CERIUM_ERR_INVALID, "keyswitch_sharded_begin: null argument");
   if (ks->L > 0 && !cpoly_local) return fail(CERIUM_ERR_INVALID, "keyswitch_sharded_begin: null polynomial");
+  if (ks->ext_split) return fail(CERIUM_ERR_INVALID, "keyswitch_sharded_begin: plans with split extension limbs exchange twice; use cerium_keyswitch_sharded_apply");
   DeviceGuard guard(ks->ctx->device);
   return keyswitch_begin(ks, send, cpoly_local, (cudaStream_t)stream);
 }
@@ -564,8 +649,99 @@ int cerium_keyswitch_sharded_finish(cerium_keyswitch* ks, void* out0, void* out1
                                     const void* add1, void* stream) {
   if (!ks || !gathered || !evk_local) return fail(CERIUM_ERR_INVALID, "keyswitch_sharded_finish: null argument");
   if (ks->L > 0 && (!out0 || !out1 || !cpoly_local)) return fail(CERIUM_ERR_INVALID, "keyswitch_sharded_finish: null argument");
+  if (ks->ext_split) return fail(CERIUM_ERR_INVALID, "keyswitch_sharded_finish: plans with split extension limbs exchange twice; use cerium_keyswitch_sharded_apply");
   DeviceGuard guard(ks->ctx->device);
   return keyswitch_finish(ks, out0, out1, gathered, cpoly_local, evk_local, add0, add1, (cudaStream_t)stream);
+}
+
+int cerium_keyswitch_local_ext_limbs(const cerium_keyswitch* ks) { return ks ? ks->K : 0; }
+
+int cerium_keyswitch_sharded_apply(cerium_keyswitch* ks, cerium_comm* comm, void* out0, void* out1,
+                                   const void* cpoly_local, const void* evk_local, const void* add0, const void* add1,
+                                   void* stream) {
+  if (!ks || !comm || !evk_local) return fail(CERIUM_ERR_INVALID, "keyswitch_sharded_apply: null argument");
+  if (ks->L > 0 && (!out0 || !out1 || !cpoly_local)) return fail(CERIUM_ERR_INVALID, "keyswitch_sharded_apply: null argument");
+  DeviceGuard guard(ks->ctx->device);
+  return keyswitch_sharded_impl(ks, comm, out0, out1, cpoly_local, evk_local, add0, add1, (cudaStream_t)stream);
+}
+
+int cerium_hrot_sharded(cerium_keyswitch* ks, cerium_comm* comm, void* out0, void* out1, const void* c0_local,
+                        const void* c1_local, const void* evk_local, uint32_t galois_elt, void* stream) {
+  if (!ks || !comm || !evk_local) return fail(CERIUM_ERR_INVALID, "hrot_sharded: null argument");
+  if (ks->L > 0 && (!out0 || !out1 || !c0_local || !c1_local)) return fail(CERIUM_ERR_INVALID, "hrot_sharded: null argument");
+  if (!(galois_elt & 1) || galois_elt >= 2u * kN) return fail(CERIUM_ERR_INVALID, "hrot_sharded: Galois element is not valid");
+  cerium_context* ctx = ks->ctx;
+  DeviceGuard guard(ctx->device);
+  const size_t wb = ctx->word_bytes();
+  if (((uintptr_t)c0_local | (uintptr_t)c1_local) & 15u) return fail(CERIUM_ERR_INVALID, "hrot_sharded: pointers must be 16-byte aligned");
+  // as in cerium_hrot: the rotation is folded into the key switch's reads of the local limbs unless an
+  // output overlaps an input
+  const size_t poly_bytes = (size_t)ks->L * kN * wb;
+  auto overlaps = [&](const void* a, const void* b) {
+    const uintptr_t x = (uintptr_t)a, y = (uintptr_t)b;
+    return x < y + poly_bytes && y < x + poly_bytes;
+  };
+  if (ks->L == 0 || (!overlaps(out0, c0_local) && !overlaps(out1, c0_local) && !overlaps(out0, c1_local) && !overlaps(out1, c1_local)))
+    return keyswitch_sharded_impl(ks, comm, out0, out1, c1_local, evk_local, c0_local, nullptr, (cudaStream_t)stream, galois_elt);
+  char* tmp = static_cast<char*>(ks->ws) + ks->o_tmp * wb;
+  void* rot0 = tmp;
+  void* rot1 = tmp + poly_bytes;
+  if (int rc = launch_automorph_pair(ctx, rot0, c0_local, rot1, c1_local, galois_elt, ks->L, (cudaStream_t)stream)) return rc;
+  return keyswitch_sharded_impl(ks, comm, out0, out1, rot1, evk_local, rot0, nullptr, (cudaStream_t)stream);
+}
+
+int cerium_rescale_sharded(cerium_context* ctx, cerium_comm* comm, int round_mode, void* out, const void* in,
+                           const uint32_t* q_idx, int L, int n_polys, void* last_coef, void* stream) {
+  if (!ctx || !comm || !q_idx || !last_coef) return fail(CERIUM_ERR_INVALID, "rescale_sharded: null argument");
+  if (round_mode != CERIUM_ROUND_FLOOR && round_mode != CERIUM_ROUND_HALF) return fail(CERIUM_ERR_INVALID, "rescale_sharded: unknown round mode");
+  if (L < 2 || L - 1 > 64 * comm->world) return fail(CERIUM_ERR_INVALID, "rescale_sharded: bad L");
+  if (n_polys < 1 || n_polys > 4096) return fail(CERIUM_ERR_INVALID, "rescale_sharded: need 1 <= n_polys <= 4096");
+  for (int i = 0; i < L; i++)
+    if (q_idx[i] >= (uint32_t)ctx->n_primes) return fail(CERIUM_ERR_INVALID, "rescale_sharded: prime index out of range");
+  const int rank = comm->rank, world = comm->world;
+  const int owner = (L - 1) % world;
+  std::vector<uint32_t> mine, keep;
+  for (int i = rank; i < L; i += world) {
+    mine.push_back(q_idx[i]);
+    if (i != L - 1) keep.push_back(q_idx[i]);
+  }
+  const int n_local = (int)mine.size();
+  if ((n_local > 0 && !in) || (!keep.empty() && !out)) return fail(CERIUM_ERR_INVALID, "rescale_sharded: null argument");
+  DeviceGuard guard(ctx->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t n = kN, wb = ctx->word_bytes();
+  if (rank == owner) {
+    // the dropped limb is the owner's last local limb of every polynomial
+    std::vector<uint32_t> pos(n_polys), prime(n_polys, q_idx[L - 1]);
+    for (int p = 0; p < n_polys; p++) pos[p] = (uint32_t)p;
+    NttCall c{};
+    c.in = static_cast<const char*>(in) + (size_t)(n_local - 1) * n * wb;
+    c.in_stride = (size_t)n_local * n;
+    c.out = last_coef;
+    c.out_stride = n;
+    c.pos = pos.data();
+    c.prime = prime.data();
+    c.count = n_polys;
+    if (int rc = launch_ntt_inverse(ctx, c, nullptr, nullptr, st)) return rc;
+  }
+  if (int rc = comm_broadcast(comm, last_coef, (size_t)n_polys * n * wb, owner, st)) return rc;
+  if (keep.empty()) return CERIUM_OK;
+  // divide the remaining local limbs; on the owner they are strided by n_local inside `in`
+  keep.push_back(q_idx[L - 1]);
+  const int R = (int)keep.size() - 1;
+  if (rank != owner) {
+    std::vector<void*> outs(n_polys);
+    for (int p = 0; p < n_polys; p++) outs[p] = static_cast<char*>(out) + (size_t)p * R * n * wb;
+    return rescale_impl(ctx, round_mode, outs.data(), nullptr, in, keep.data(), R + 1, n_polys, last_coef, st, nullptr, true);
+  }
+  // owner: polynomial p's remaining limbs start at in + p * n_local limbs: one polynomial per call
+  for (int p = 0; p < n_polys; p++) {
+    void* o = static_cast<char*>(out) + (size_t)p * R * n * wb;
+    const void* i = static_cast<const char*>(in) + (size_t)p * n_local * n * wb;
+    void* lc = static_cast<char*>(last_coef) + (size_t)p * n * wb;
+    if (int rc = rescale_impl(ctx, round_mode, &o, nullptr, i, keep.data(), R + 1, 1, lc, st, nullptr, true)) return rc;
+  }
+  return CERIUM_OK;
 }
 
 int cerium_keyswitch_destroy(cerium_keyswitch* ks) {

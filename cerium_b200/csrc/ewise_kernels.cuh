@@ -68,6 +68,7 @@ enum EwOp : int {
   kEwMad = 4,   // out = a * b + c
   kEwPmu = 5,   // out = a + b * s[limb]
   kEwMulScalar = 6,  // out = a * s[limb]
+  kEwReduce = 7,     // out = a mod q for ANY word a (sums of residues after a reduce-scatter / all-reduce)
 };
 
 template <typename W>
@@ -109,6 +110,7 @@ __global__ void __launch_bounds__(kEwThreads)
     if (kOp == kEwPmu)
       o.v[l] = add_mod<W>(a.v[l], csub<W>(mul_shoup_lazy<W>(bb.v[l], s, ss, pc.q), pc.q), pc.q);
     if (kOp == kEwMulScalar) o.v[l] = csub<W>(mul_shoup_lazy<W>(a.v[l], s, ss, pc.q), pc.q);
+    if (kOp == kEwReduce) o.v[l] = reduce_word<W>(a.v[l], pc);
   }
   o.store(g.out.at(b, idx));
 }

@@ -134,7 +134,24 @@ struct cerium_bconv {
   bool fp_in = false;              // some outputs take their quotient from the FP64 pipe (d_fp_fac is present)
 };
 
+// Communicator of the limb collectives: the ranks of one job, one GPU each.  The transport is NCCL
+// (loaded at run time) or a set of caller-provided functions.
+struct cerium_comm {
+  int rank = 0, world = 1, device = 0;
+  void* nccl = nullptr;  // ncclComm_t when the transport is NCCL
+  cerium_comm_callbacks cb = {};
+  bool has_cb = false;
+};
+
 namespace cerium {
+
+// Collectives on raw device buffers, enqueued on `stream`.  `send` of the all-gather may be the
+// rank's own block of `recv` (in place).  Sums are plain word additions (no modular reduction).
+int comm_allgather(cerium_comm* comm, void* recv, const void* send, size_t bytes_per_rank, cudaStream_t stream);
+int comm_reducescatter_sum(cerium_comm* comm, void* recv, const void* send, size_t words_per_rank, int word_bits,
+                           cudaStream_t stream);
+int comm_allreduce_sum(cerium_comm* comm, void* recv, const void* send, size_t words, int word_bits, cudaStream_t stream);
+int comm_broadcast(cerium_comm* comm, void* buf, size_t bytes, int root, cudaStream_t stream);
 
 // Options of create_bconv beyond the public entry point.
 struct BconvOptions {
@@ -166,8 +183,9 @@ struct NttCall {
   const uint32_t* pos;    // count entries, or null for 0..count-1
   const uint32_t* prime;  // count entries
   int count;
-  // forward transform only: entry b reads limb src_pos[b] of `in`, residues of another modulus,
-  // and reduces them to its own prime on the way in (null: reads limb pos[b], already reduced)
+  // forward transform: entry b reads limb src_pos[b] of `in`, residues of another modulus, and
+  // reduces them to its own prime on the way in (null: reads limb pos[b], already reduced).
+  // inverse transform: entry b reads limb src_pos[b] of `in` (same modulus) instead of limb pos[b]
   const uint32_t* src_pos = nullptr;
   // with src_pos: prime index of the modulus the words of entry b are residues of (null: unknown)
   const uint32_t* src_prime = nullptr;

@@ -40,6 +40,7 @@ class HostPipeline:
         slot = self.count % self.depth
         first_use = self.count < self.depth
         self.count += 1
+        self.last_host_ins = host_ins
         with torch.cuda.stream(self.s_in):
             if not first_use:
                 self.s_in.wait_event(self.ev_op[slot])   # the slot's previous inputs have been consumed

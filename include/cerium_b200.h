@@ -60,10 +60,12 @@ extern "C" {
 #define CERIUM_EW_MAD 4        /* out = a * b + c        */
 #define CERIUM_EW_PMU 5        /* out = a + b * s[i]     */
 #define CERIUM_EW_MUL_SCALAR 6 /* out = a * s[i]         */
+#define CERIUM_EW_REDUCE 7     /* out = a mod q, a any word (sums of residues after a collective) */
 
 typedef struct cerium_context cerium_context;
 typedef struct cerium_bconv cerium_bconv;
 typedef struct cerium_keyswitch cerium_keyswitch;
+typedef struct cerium_comm cerium_comm;
 
 /* Library version (major * 10000 + minor * 100 + patch). */
 CERIUM_API int cerium_version(void);
@@ -237,13 +239,75 @@ CERIUM_API int cerium_keyswitch_destroy(cerium_keyswitch *ks);
 CERIUM_API size_t cerium_keyswitch_workspace_bytes(const cerium_keyswitch *ks);
 
 /*
+ * Communicator of the limb collectives: the `world` ranks of one job, one process and one GPU each.
+ * Replaces the NCCL layer of the reference runtime (CUDA::NCCL::*, cerium/runtime/cuda/nccl_ops.cu:
+ * 241-440, one host thread per GPU there) for the three exchange records of a compiled program:
+ *   DRM  all-gather of coefficient-form limbs      Evaluator::drm  evaluator.cpp:1154-1251
+ *   AGS  reduce-scatter of partial sums + mod      Evaluator::ags  evaluator.cpp:1253-1367
+ *   ARD  all-reduce of partial sums + mod          Evaluator::ard  evaluator.cpp:1369-1481
+ * Limb stacks are contiguous, so there is no pack / unpack pass around a collective (the reference's
+ * copy_to_nccl_buffer / copy_from_nccl_buffer[_with_mod], device_utils.cu:290-413): the producer
+ * writes the send block, the consumer reads the receive buffer, and the sums are reduced in place.
+ * Two transports:
+ *   cerium_comm_unique_id + cerium_comm_init   NCCL (libnccl.so.2, opened at run time).  Rank 0 makes
+ *       the 128-byte id, the caller hands it to every rank (a file, a store, MPI, torch.distributed).
+ *   cerium_comm_init_callbacks                 the caller's own collectives (a runtime that owns its
+ *       communicators; a host-memory transport in tests).  A callback enqueues on `stream`, or
+ *       completes before it returns, and returns 0 on success.  Unused entries may be NULL.
+ * Every collective is enqueued on the given stream and lands in this GPU's own memory.  The ranks
+ * must issue their collectives on one communicator in the same order.
+ */
+#define CERIUM_COMM_ID_BYTES 128
+typedef struct cerium_comm_callbacks {
+  void *user;
+  /* recv [world][bytes_per_rank]; send is this rank's block, possibly recv + rank * bytes_per_rank */
+  int (*allgather)(void *user, void *recv, const void *send, size_t bytes_per_rank, void *stream);
+  /* send [world][words_per_rank]; recv [words_per_rank] = sum over the ranks of their block `rank` (plain
+   * word sums, word_bits = 32 or 64) */
+  int (*reducescatter)(void *user, void *recv, const void *send, size_t words_per_rank, int word_bits, void *stream);
+  int (*allreduce)(void *user, void *recv, const void *send, size_t words, int word_bits, void *stream);
+  int (*broadcast)(void *user, void *buf, size_t bytes, int root, void *stream);
+} cerium_comm_callbacks;
+CERIUM_API int cerium_comm_unique_id(void *id, size_t id_bytes);
+CERIUM_API int cerium_comm_init(cerium_comm **out, const void *id, size_t id_bytes, int rank, int world, int device);
+CERIUM_API int cerium_comm_init_callbacks(cerium_comm **out, int rank, int world, int device,
+                                          const cerium_comm_callbacks *cb);
+CERIUM_API int cerium_comm_destroy(cerium_comm *comm);
+CERIUM_API int cerium_comm_rank(const cerium_comm *comm);
+CERIUM_API int cerium_comm_world(const cerium_comm *comm);
+/*
+ * cerium_allgather_limbs      gathered [world][limbs_per_rank][N] <- every rank's send [limbs_per_rank][N]
+ *                             (send may be the rank's own block of gathered)
+ * cerium_reducescatter_limbs  in [world][limbs_per_rank][N] partial sums of canonical residues;
+ *                             out [limbs_per_rank][N] = (sum over the ranks of their block `rank`) mod
+ *                             q_{prime_idx[i]}, canonical.  out may be the rank's block of in.
+ * cerium_allreduce_limbs      out [limbs][N] = (sum over the ranks of in) mod q_{prime_idx[i]}; in place allowed
+ * cerium_broadcast_limbs      buf [limbs][N] of rank `root` to every rank
+ * The sums are word additions on the wire: world * q must fit a word (refused otherwise).
+ */
+CERIUM_API int cerium_allgather_limbs(cerium_comm *comm, cerium_context *ctx, void *gathered, const void *send,
+                                      size_t limbs_per_rank, void *stream);
+CERIUM_API int cerium_reducescatter_limbs(cerium_comm *comm, cerium_context *ctx, void *out, const void *in,
+                                          const uint32_t *prime_idx, int limbs_per_rank, void *stream);
+CERIUM_API int cerium_allreduce_limbs(cerium_comm *comm, cerium_context *ctx, void *out, const void *in,
+                                      const uint32_t *prime_idx, int limbs, void *stream);
+CERIUM_API int cerium_broadcast_limbs(cerium_comm *comm, cerium_context *ctx, void *buf, size_t limbs, int root,
+                                      void *stream);
+
+/*
  * Limb-sharded plan for rank `rank` of `world` GPUs.  Q-limb i lives on rank i % world
- * (cerium/compiler/backend/terms.h:672-685), the K extension limbs are replicated on every
- * rank (Term::Ext), evaluation keys are sharded like the ciphertext
- * (cerium/compiler/backend/compiler_partition.cc:446-470).  Every stack a sharded call takes
- * holds the rank's own limbs only, in increasing global index:
+ * (cerium/compiler/backend/terms.h:672-685); evaluation keys are sharded like the ciphertext
+ * (cerium/compiler/backend/compiler_partition.cc:446-470).  The K extension limbs are
+ *   ext_split = 0  replicated on every rank (the reference's Term::Ext): no second exchange, but every
+ *                  rank repeats the extension limbs' share of the conversions, transforms and products;
+ *   ext_split = 1  split over the ranks like the Q limbs (the reference's Ext_Split / PaE_Split terms,
+ *                  cerium/compiler/backend/terms.h:623-790): extension limb k lives on rank
+ *                  (L + k) % world, and the coefficient-form extension limbs of the two accumulators are
+ *                  all-gathered (2 K limbs) before the ModDown conversion.
+ * Every stack a sharded call takes holds the rank's own limbs only, in increasing global index:
  *   polynomial  [n_local][N]                       n_local = cerium_keyswitch_local_limbs()
- *   key         [dnum][c0|c1][n_local + K][N]
+ *   key         [dnum][c0|c1][n_local + k_local][N]   k_local = cerium_keyswitch_local_ext_limbs()
+ *                                                  (= K when the extension limbs are replicated)
  * The one exchange of a key switch is the all-gather of the coefficient-form limbs before base
  * conversion (the reference's DRM group, cerium/compiler/backend/compiler_keyswitch.cc:323-335,
  * cerium/runtime/execution/evaluator.cpp:1154-1251); the caller performs it between the two
@@ -253,12 +317,38 @@ CERIUM_API size_t cerium_keyswitch_workspace_bytes(const cerium_keyswitch *ks);
  *                                    slots past n_local are not written)
  *   all-gather of `send` over the ranks into `gathered` ([world][g][N], rank-major)
  *   cerium_keyswitch_sharded_finish  base conversion, NTT, inner product, ModDown on local limbs
- * world = 1 reproduces cerium_keyswitch_create / cerium_keyswitch_apply.
+ * world = 1 reproduces cerium_keyswitch_create / cerium_keyswitch_apply.  The begin / finish pair
+ * serves plans with replicated extension limbs only.
+ *
+ * With a communicator the library runs the exchanges itself, into buffers of the plan's workspace
+ * (the inverse transform writes this rank's block of the gather buffer in place):
+ *   cerium_keyswitch_sharded_apply   the whole key switch on the local limbs (either ext_split mode)
+ *   cerium_hrot_sharded              HRot of a sharded ciphertext; the rotation is folded into the
+ *                                    key switch's reads of the local limbs, as in cerium_hrot
+ *   cerium_rescale_sharded           rescale of a sharded ciphertext (cerium/compiler/backend/
+ *                                    compiler_rescale.cc:209-284 with several partitions): the owner of
+ *                                    limb L-1 inverse-transforms it into last_coef ([n_polys][N], a
+ *                                    caller-owned buffer on every rank), broadcast, every rank divides
+ *                                    its remaining limbs.  in: [n_polys][n_local][N] (limbs i = rank,
+ *                                    rank + world, ... of q_idx[0..L)); out: [n_polys][n_local'][N],
+ *                                    n_local' = n_local - 1 on the owner of the dropped limb.
+ * Every rank makes the same call in the same order.  Results equal the one-GPU plan's bit for bit.
  */
 CERIUM_API int cerium_keyswitch_create_sharded(cerium_context *ctx, cerium_keyswitch **out, int bconv_mode,
                                     int round_mode, const uint32_t *q_idx, int L,
-                                    const uint32_t *p_idx, int K, int dnum, int rank, int world);
+                                    const uint32_t *p_idx, int K, int dnum, int rank, int world,
+                                    int ext_split);
 CERIUM_API int cerium_keyswitch_local_limbs(const cerium_keyswitch *ks);
+CERIUM_API int cerium_keyswitch_local_ext_limbs(const cerium_keyswitch *ks);
+CERIUM_API int cerium_keyswitch_sharded_apply(cerium_keyswitch *ks, cerium_comm *comm, void *out0, void *out1,
+                                              const void *cpoly_local, const void *evk_local, const void *add0,
+                                              const void *add1, void *stream);
+CERIUM_API int cerium_hrot_sharded(cerium_keyswitch *ks, cerium_comm *comm, void *out0, void *out1,
+                                   const void *c0_local, const void *c1_local, const void *evk_local,
+                                   uint32_t galois_elt, void *stream);
+CERIUM_API int cerium_rescale_sharded(cerium_context *ctx, cerium_comm *comm, int round_mode, void *out,
+                                      const void *in, const uint32_t *q_idx, int L, int n_polys, void *last_coef,
+                                      void *stream);
 CERIUM_API int cerium_keyswitch_gather_limbs(const cerium_keyswitch *ks);
 CERIUM_API int cerium_keyswitch_sharded_begin(cerium_keyswitch *ks, void *send, const void *cpoly_local,
                                    void *stream);
