@@ -192,7 +192,7 @@ class HRotWorkload(Workload):
         self.prm = params.config_hrot(LOGN, 35, 5, 7)
         self.n_cts = n_cts  # rotating set of ciphertexts so consecutive ops do not reuse inputs
 
-    def setup(self, lib, torch, rank, world=1, sharded=False, comm=None, ext_split=True, inflight=4):
+    def setup(self, lib, torch, rank, world=1, sharded=False, comm=None, ext_split=True, inflight=1):
         from cerium_b200 import _capi
         self.torch = torch
         prm = self.prm
@@ -215,8 +215,11 @@ class HRotWorkload(Workload):
             self.cts = [torch.stack([sh.shard_poly(c[0], rank, world), sh.shard_poly(c[1], rank, world)])
                         for c in full_cts]
             self.full_evk, self.full_ct0 = full_evk, full_cts[0]     # kept for verify(), dropped afterwards
-            self.sks = [sh.ShardedKeySwitch(self.ctx, prm, comm, _capi.BCONV_EXACT, _capi.ROUND_HALF, ext_split=ext_split)
-                        for _ in range(inflight)]
+            # a communicator per operation in flight: collectives of one communicator run in issue order,
+            # so with one communicator an operation's second exchange would hold back the next operation's first
+            self.comms = [comm] + [sh.nccl_comm(lib, rank, world, torch.cuda.current_device()) for _ in range(inflight - 1)]
+            self.sks = [sh.ShardedKeySwitch(self.ctx, prm, c, _capi.BCONV_EXACT, _capi.ROUND_HALF, ext_split=ext_split)
+                        for c in self.comms]
             self.streams = [torch.cuda.Stream() for _ in range(inflight)]
             self.outs = [torch.empty_like(self.cts[0]) for _ in range(max(self.n_cts, inflight))]
             k_loc = self.sks[0].k_local
@@ -224,9 +227,16 @@ class HRotWorkload(Workload):
             self.gpu_launches_per_step = 2 + 1 + 2 + 1 + (2 if k_loc else 0) + 1 + 2
         else:
             gen = torch.Generator(device="cuda").manual_seed(0xCE210003 + rank)
-            # exact conversion + rounding: the semantics that are low-noise with 50/60-bit primes
-            self.ks = _capi.KeySwitch(self.ctx, prm.q_idx, prm.p_idx, prm.dnum, _capi.BCONV_EXACT, _capi.ROUND_HALF)
+            # exact conversion + rounding: the semantics that are low-noise with 50/60-bit primes.
+            # `inflight` independent operations may be in flight, each on a plan (workspace) and a stream
+            # of its own: the latency-bound small launches of one then run beside the other's large ones
+            self.inflight = max(1, inflight)
+            self.kss = [_capi.KeySwitch(self.ctx, prm.q_idx, prm.p_idx, prm.dnum, _capi.BCONV_EXACT, _capi.ROUND_HALF)
+                        for _ in range(self.inflight)]
+            self.ks = self.kss[0]
+            self.streams = [torch.cuda.Stream() for _ in range(self.inflight)] if self.inflight > 1 else []
             self.evk = _rand_limbs_gpu(torch, prm.moduli, all_idx, (prm.dnum, 2), gen)
+            self.n_cts = self.inflight * -(-self.n_cts // self.inflight)   # a buffer is only ever used by one stream
             self.cts = [_rand_limbs_gpu(torch, prm.moduli, prm.q_idx, (2,), gen) for _ in range(self.n_cts)]
             self.outs = [torch.empty_like(self.cts[0]) for _ in range(self.n_cts)]
             # iNTT pair, BConv, NTT pair, inner product, iNTT pair, BConv, SuD pair (the rotation itself is
@@ -246,14 +256,14 @@ class HRotWorkload(Workload):
         if self.sharded:
             self.sks[slot].hrot(out[0], out[1], ct[0], ct[1], self.evk, self.elt, s)
         else:
-            self.ks.hrot(out[0].data_ptr(), out[1].data_ptr(), ct[0].data_ptr(), ct[1].data_ptr(),
-                         self.evk.data_ptr(), self.elt, s)
+            self.kss[slot].hrot(out[0].data_ptr(), out[1].data_ptr(), ct[0].data_ptr(), ct[1].data_ptr(),
+                                self.evk.data_ptr(), self.elt, s)
 
     def step(self):
         k = self.i % self.n_cts
-        if self.sharded:
+        if self.streams:
             slot = self.i % self.inflight
-            self._hrot(self.cts[k], self.outs[slot], self.streams[slot].cuda_stream, slot)
+            self._hrot(self.cts[k], self.outs[k if not self.sharded else slot], self.streams[slot].cuda_stream, slot)
         else:
             self._hrot(self.cts[k], self.outs[k])
         self.i += 1
@@ -261,16 +271,14 @@ class HRotWorkload(Workload):
     # the timed region is bracketed by events on the current stream: the side streams start after its
     # first event and are joined before its second
     def fork(self):
-        if self.sharded:
-            cur = self.torch.cuda.current_stream()
-            for st in self.streams:
-                st.wait_stream(cur)
+        cur = self.torch.cuda.current_stream()
+        for st in self.streams:
+            st.wait_stream(cur)
 
     def join(self):
-        if self.sharded:
-            cur = self.torch.cuda.current_stream()
-            for st in self.streams:
-                cur.wait_stream(st)
+        cur = self.torch.cuda.current_stream()
+        for st in self.streams:
+            cur.wait_stream(st)
 
     def verify(self, orc_mod):
         """One operation on the benchmark's own inputs, every limb bit for bit, outside the timed region.
@@ -390,8 +398,13 @@ class HMultWorkload(Workload):
     unit = "ops/s"
     ops_per_step = 1
 
+    # 2: the rescale is folded into the relinearisation's ModDown (one division by P * q_last, the way the
+    # reference lowers a key switch with rescale levels); 1: ModDown, then rescale
+    rescale_mode = 2
+
     def __init__(self):
         self.prm = params.config_hmult(LOGN, 24)
+        self.rescale_mode = int(os.environ.get("CERIUM_BENCH_HMULT_RESCALE", self.rescale_mode))
 
     def setup(self, lib, torch, rank, world=1, sharded=False):
         from cerium_b200 import _capi
@@ -411,14 +424,15 @@ class HMultWorkload(Workload):
         self.host_in[1].copy_(self.b.cpu())
         self.host_out = torch.empty(self.out.shape, dtype=torch.int64).pin_memory()
         # tensor; key switch: iNTT pair, NTT pair x2 (576 limbs in two batches), inner product, iNTT pair,
-        # BConv, SuD pair; rescale of both polynomials: iNTT pair, SuD pair
-        self.gpu_launches_per_step = 1 + (2 + 4 + 1 + 2 + 1 + 2) + 4
+        # BConv, SuD pair; then either the rescale of both polynomials (iNTT pair, SuD pair) or, folded
+        # into the ModDown, two PMU launches
+        self.gpu_launches_per_step = 1 + (2 + 4 + 1 + 2 + 1 + 2) + (2 if self.rescale_mode == 2 else 4)
 
     def step(self):
         s = self.torch.cuda.current_stream().cuda_stream
         a, b, o = self.a, self.b, self.out
         self.ks.hmult(o[0].data_ptr(), o[1].data_ptr(), a[0].data_ptr(), a[1].data_ptr(), b[0].data_ptr(),
-                      b[1].data_ptr(), self.evk.data_ptr(), True, s)
+                      b[1].data_ptr(), self.evk.data_ptr(), self.rescale_mode, s)
 
     def verify(self, orc_mod):
         torch, prm = self.torch, self.prm
@@ -426,8 +440,11 @@ class HMultWorkload(Workload):
         torch.cuda.synchronize()
         u = lambda t: t.cpu().numpy().view(np.uint64)  # noqa: E731
         octx = orc_mod.OracleContext(LOGN, prm.moduli)
-        w0, w1 = octx.hmult_relin(orc_mod.BCONV_EXACT, orc_mod.ROUND_HALF, True, prm.q_idx, prm.p_idx, prm.dnum,
-                                  u(self.a[0]), u(self.a[1]), u(self.b[0]), u(self.b[1]), u(self.evk))
+        args = (u(self.a[0]), u(self.a[1]), u(self.b[0]), u(self.b[1]), u(self.evk))
+        if self.rescale_mode == 2:
+            w0, w1 = octx.hmult_relin_fused(orc_mod.BCONV_EXACT, orc_mod.ROUND_HALF, prm.q_idx, prm.p_idx, prm.dnum, *args)
+        else:
+            w0, w1 = octx.hmult_relin(orc_mod.BCONV_EXACT, orc_mod.ROUND_HALF, True, prm.q_idx, prm.p_idx, prm.dnum, *args)
         got = u(self.out)
         return bool(np.array_equal(got[0], w0) and np.array_equal(got[1], w1))
 
@@ -438,7 +455,7 @@ class HMultWorkload(Workload):
             def op(ins, outs, stream):
                 a, b, o = ins[0], ins[1], outs[0]
                 self.ks.hmult(o[0].data_ptr(), o[1].data_ptr(), a[0].data_ptr(), a[1].data_ptr(), b[0].data_ptr(),
-                              b[1].data_ptr(), self.evk.data_ptr(), True, stream)
+                              b[1].data_ptr(), self.evk.data_ptr(), self.rescale_mode, stream)
             self.pipe = HostPipeline(self.torch, [self.a.shape, self.b.shape], [self.out.shape], op)
         self.pipe.submit([self.host_in[0], self.host_in[1]])
         return self.pipe.in_bytes, self.pipe.out_bytes
@@ -598,8 +615,9 @@ class HoistedWorkload(HRotWorkload):
 class BsgsWorkload(HRotWorkload):
     """One BSGS multiply-accumulate with 8 baby x 8 giant steps (64 diagonals) on the HRot parameter
     set: the linear-transform stage of bootstrapping (CoeffToSlot / SlotToCoeff,
-    cerium/compiler/backend/compiler.cc:2457-2822) through cerium_b200/bsgs.py: 7 hoisted baby
-    rotations, 64 plaintext multiply-accumulates on both polynomials, 7 giant-step rotations."""
+    cerium/compiler/backend/compiler.cc:2457-2822) through cerium_bsgs_apply: 7 hoisted baby
+    rotations, the plaintext multiply-accumulate of all giant steps in two passes over the rotated
+    copies, 7 giant-step key switches accumulated in the extended basis, one ModDown."""
     name = "bsgs_8x8_N65536_L35_K5_dnum7_u64"
     metric = "bsgs_linear_transforms_per_s"
     unit = "transforms/s"
@@ -625,7 +643,9 @@ class BsgsWorkload(HRotWorkload):
         limb = N * 8
         # ciphertext in and out, 14 keys, 64 plaintexts
         self.alg_bytes = (4 * prm.L + 2 * (G - 1) * prm.dnum * 2 * (prm.L + prm.K) + G * G * prm.L) * limb
-        self.gpu_launches_per_step = 5 + (G - 1) * 6 + G * G * 2 + (G - 1) * (11 + 2)
+        # hoisted begin 5, baby rotation 6 each, 2 plaintext passes, 2 rotation sums, per giant step
+        # iNTT pair + BConv + NTT pair + inner product, final ModDown 5
+        self.gpu_launches_per_step = 5 + (G - 1) * 6 + 2 + 2 + (G - 1) * 6 + 5
 
     def _run(self, ct, out, stream):
         self.op.run(out, ct, self.pts, self.baby_keys, self.giant_keys, self.baby_elts, self.giant_elts, stream)
@@ -634,6 +654,30 @@ class BsgsWorkload(HRotWorkload):
         k = self.i % self.n_cts
         self.i += 1
         self._run(self.cts[k], self.bout, self.torch.cuda.current_stream().cuda_stream)
+
+    def verify(self, orc_mod):
+        """The whole transform against the oracle's restatement of the reference lowering (baby steps
+        as hoisted rotations, extended-basis accumulation, one ModDown)."""
+        torch, prm, G = self.torch, self.prm, self.G
+        u = lambda t: t.cpu().numpy().view(np.uint64)  # noqa: E731
+        ct = self.cts[0]
+        self._run(ct, self.bout, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        octx = orc_mod.OracleContext(LOGN, prm.moduli)
+        c0, c1 = u(ct[0]), u(ct[1])
+        baby = [np.stack([c0, c1])]
+        for j in range(1, G):
+            k0, k1 = octx.keyswitch(orc_mod.BCONV_EXACT, orc_mod.ROUND_HALF, prm.q_idx, prm.p_idx, prm.dnum, c1,
+                                    u(self.baby_keys[j - 1]))
+            k0 = np.stack([orc_mod.ew("add", prm.moduli[p], k0[i], c0[i]) for i, p in enumerate(prm.q_idx)])
+            e = self.baby_elts[j - 1]
+            baby.append(np.stack([np.stack([orc_mod.apply_galois_ntt(e, LOGN, k[i]) for i in range(prm.L)]) for k in (k0, k1)]))
+        pts = np.stack([np.stack([u(t) for t in row]) for row in self.pts])
+        keys = np.stack([np.zeros_like(u(self.giant_keys[0]))] + [u(k) for k in self.giant_keys])
+        w0, w1 = octx.bsgs(orc_mod.BCONV_EXACT, orc_mod.ROUND_HALF, prm.q_idx, prm.p_idx, prm.dnum, 0, np.stack(baby), pts,
+                           np.ones((G, G), dtype=np.uint8), [1] + list(self.giant_elts), keys)
+        got = u(self.bout)
+        return bool(np.array_equal(got[0], w0) and np.array_equal(got[1], w1))
 
     def e2e_step(self):
         if getattr(self, "pipe", None) is None:
@@ -797,7 +841,9 @@ def main():
                     help="N > 1, hrot: 'limb' (what 'auto' picks) shards every ciphertext and key by RNS limb over the "
                          "ranks, NCCL all-gathers where limbs must meet, several operations in flight; 'replica' runs "
                          "independent ciphertexts per rank with no collective")
-    ap.add_argument("--inflight", type=int, default=4, help="limb-sharded operations in flight per rank")
+    ap.add_argument("--inflight", type=int, default=None,
+                    help="independent operations in flight per rank, each on its own plan and stream (hrot; default 1 "
+                         "on one GPU, 4 limb-sharded)")
     ap.add_argument("--ext", choices=["split", "replicated"], default="split",
                     help="limb-sharded: extension limbs split over the ranks, or replicated on every rank")
     args = ap.parse_args()
@@ -829,9 +875,13 @@ def main():
     if sharded:
         from cerium_b200 import sharded as sh
         comm = sh.nccl_comm(lib, rank, world, local_rank)
-        wl.setup(lib, torch, rank, world, True, comm=comm, ext_split=args.ext == "split", inflight=max(1, args.inflight))
+        wl.setup(lib, torch, rank, world, True, comm=comm, ext_split=args.ext == "split",
+                 inflight=max(1, args.inflight if args.inflight is not None else 4))
     else:
-        wl.setup(lib, torch, rank, world, False)
+        if args.workload == "hrot":
+            wl.setup(lib, torch, rank, world, False, inflight=max(1, args.inflight if args.inflight is not None else 1))
+        else:
+            wl.setup(lib, torch, rank, world, False)
     ops = wl.ops_per_step
     job_ops = 1 if sharded else world   # ops per step of the whole job: one sharded op, or one per replica
 
@@ -950,6 +1000,7 @@ def main():
             "config": {"workload": wl.name},
             "verified": verified,
             "l2": "working set larger than L2 (keys + ciphertexts + workspace > 126 MB)",
+            "inflight": getattr(wl, "inflight", 1),
             "parallelism": ("single GPU" if world == 1 else
                             "every ciphertext and key limb-sharded over %d ranks (%s extension limbs), NCCL all-gather "
                             "where limbs must meet, %d operations in flight" % (world, args.ext, wl.inflight) if sharded

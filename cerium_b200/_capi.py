@@ -81,6 +81,10 @@ SIGNATURES = {
     "cerium_keyswitch_destroy": (C.c_int, [_vp]),
     "cerium_keyswitch_workspace_bytes": (_sz, [_vp]),
     "cerium_keyswitch_apply": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "cerium_keyswitch_apply_rescale": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_int, _vp]),
+    "cerium_bsgs_work_limbs": (_sz, [_vp, C.c_int, C.c_int]),
+    "cerium_bsgs_apply": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.POINTER(_vp), C.POINTER(_vp), _u32p,
+                                    C.POINTER(_vp), _u32p, C.c_int, _vp, _vp]),
     "cerium_hrot": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, C.c_uint32, _vp]),
     "cerium_hoisted_begin": (C.c_int, [_vp, _vp, _vp]),
     "cerium_hoisted_rotate": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, C.c_uint32, _vp]),
@@ -449,6 +453,25 @@ class KeySwitch:
         self.ctx.lib.check(self.ctx.lib.dll.cerium_keyswitch_apply(self.h, out0, out1, cpoly, evk, add0 or None,
                                                                    add1 or None, stream))
 
+    def apply_rescale(self, out0: int, out1: int, cpoly: int, evk: int, rescale_levels: int, add0: int = 0,
+                      add1: int = 0, stream: int = 0):
+        """Key switch with the PMU pre-additions and the rescale folded into the ModDown (one division)."""
+        self.ctx.lib.check(self.ctx.lib.dll.cerium_keyswitch_apply_rescale(self.h, out0, out1, cpoly, evk, add0 or None,
+                                                                           add1 or None, rescale_levels, stream))
+
+    def bsgs_work_limbs(self, g: int, n_giant: int) -> int:
+        return int(self.ctx.lib.dll.cerium_bsgs_work_limbs(self.h, g, n_giant))
+
+    def bsgs_apply(self, out0: int, out1: int, c0: int, c1: int, g: int, n_giant: int, plaintexts: Sequence[int],
+                   baby_keys_pre: Sequence[int], baby_elts: Sequence[int], giant_keys: Sequence[int],
+                   giant_elts: Sequence[int], rescale_levels: int, work: int, stream: int = 0):
+        """plaintexts: n_giant * g device addresses (0 = absent diagonal), entry i * g + j; baby_* have g
+        entries (entry 0 unused), giant_* have n_giant entries (element 1 = no rotation, key 0)."""
+        vp = lambda seq: (_vp * len(seq))(*[_vp(int(p)) if p else _vp() for p in seq])  # noqa: E731
+        self.ctx.lib.check(self.ctx.lib.dll.cerium_bsgs_apply(
+            self.h, out0, out1, c0, c1, g, n_giant, vp(plaintexts), vp(baby_keys_pre), _u32(baby_elts), vp(giant_keys),
+            _u32(giant_elts), rescale_levels, work, stream))
+
     def hrot(self, out0: int, out1: int, c0: int, c1: int, evk: int, galois_elt: int, stream: int = 0):
         self.ctx.lib.check(self.ctx.lib.dll.cerium_hrot(self.h, out0, out1, c0, c1, evk, galois_elt, stream))
 
@@ -458,10 +481,11 @@ class KeySwitch:
     def hoisted_rotate(self, out0: int, out1: int, c0: int, c1: int, evk_pre: int, galois_elt: int, stream: int = 0):
         self.ctx.lib.check(self.ctx.lib.dll.cerium_hoisted_rotate(self.h, out0, out1, c0, c1, evk_pre, galois_elt, stream))
 
-    def hmult(self, out0: int, out1: int, a0: int, a1: int, b0: int, b1: int, evk: int, do_rescale: bool,
+    def hmult(self, out0: int, out1: int, a0: int, a1: int, b0: int, b1: int, evk: int, do_rescale,
               stream: int = 0):
+        """do_rescale: False / 0 none, True / 1 ModDown then rescale, 2 the rescale folded into the ModDown."""
         self.ctx.lib.check(self.ctx.lib.dll.cerium_hmult(self.h, out0, out1, a0, a1, b0, b1, evk,
-                                                         1 if do_rescale else 0, stream))
+                                                         int(do_rescale), stream))
 
     def close(self):
         if getattr(self, "h", None) and self.ctx.h:

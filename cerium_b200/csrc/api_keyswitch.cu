@@ -42,6 +42,17 @@ struct cerium_keyswitch {
   std::vector<int> up_digit;       // digit number of up[k]
   cerium_bconv* down = nullptr;    // P -> Q
   std::vector<uint64_t> pinv;      // [L] P^-1 mod q_i
+  std::vector<uint64_t> pmod;      // [L] P mod q_i (the PMU factor, cerium/runtime/execution/function.cpp:733-755)
+  // ModDown with r = 1, 2 rescale levels in the same division (one-GPU plans): converter
+  // (dropped Q limbs, P) -> remaining Q limbs, (P * dropped primes)^-1, the limbs to inverse-transform
+  struct FusedDown {
+    cerium_bconv* down = nullptr;
+    std::vector<uint64_t> pinv;              // [L - r]
+    std::vector<uint32_t> ext_pos, ext_prime;  // both accumulators: slots [L - r, LK) of each
+    void* d_scale = nullptr;                 // exact mode: per entry of ext_pos, then the Shoup companions
+    void* d_scale_shoup = nullptr;
+  };
+  std::vector<FusedDown> fused;
   // transform batches
   std::vector<uint32_t> ntt_pos, ntt_prime;  // converted limbs of all digits inside `raised`
   // one-limb digits: the conversion is a plain reduction, done by the transform as it reads the
@@ -204,50 +215,122 @@ int keyswitch_raise(cerium_keyswitch* ks, const void* gathered, cudaStream_t str
   });
 }
 
-// Steps 4-7 on the digits that keyswitch_raise left in the plan: inner product with `evk`,
-// ModDown, optional additions.  Can be repeated with different keys (hoisting).
+// Step 4 on the digits that keyswitch_raise left in the plan: inner product with `evk` into the
+// plan's accumulators (both polynomials, every local extended limb).  accumulate: add to what the
+// accumulators hold (the giant steps of a BSGS multiply-accumulate sum up in the extended basis).
+int keyswitch_inner(cerium_keyswitch* ks, const void* cpoly, const void* evk, cudaStream_t stream, uint32_t pre_elt = 0,
+                    bool accumulate = false) {
+  cerium_context* ctx = ks->ctx;
+  const size_t n = kN;
+  const int LK = ks->LK, dnum = ks->dnum;
+  return dispatch_word(ctx->word_bits, [&](auto tag) -> int {
+    using W = decltype(tag);
+    using V = Vec16<W>;
+    W* acc = ws_at<W>(ks, ks->o_acc);
+    InnerProductArgs<W> g{};
+    g.raised = ws_at<W>(ks, ks->o_raised);
+    g.raised_digit_stride = (size_t)LK * n;
+    g.raised_limb_stride = n;
+    g.own = static_cast<const W*>(cpoly);
+    g.own_stride = n;
+    g.own_elt = pre_elt;
+    g.accumulate = accumulate ? 1 : 0;
+    g.evk = static_cast<const W*>(evk);
+    g.evk_digit_stride = (size_t)2 * LK * n;
+    g.evk_poly_stride = (size_t)LK * n;
+    g.evk_limb_stride = n;
+    g.out0 = {acc, n};
+    g.out1 = {acc + (size_t)LK * n, n};
+    g.dnum = dnum;
+    for (int b = 0; b < LK; b++) {
+      g.prime[b] = (uint8_t)ks->all_idx[b];
+      g.own_digit[b] = (int8_t)ks->own_digit[b];
+    }
+    const PrimeConst<W>* pcs = static_cast<const PrimeConst<W>*>(ctx->d_pcs);
+    // every local extended limb (Q and extension) in one launch
+    g.first_limb = 0;
+    { auto kfn = inner_product_kernel<W>; CERIUM_LAUNCH(kfn, dim3(kN / (kEwThreads * V::kLanes), LK), dim3(kEwThreads), 0, stream, g, pcs); }
+    CERIUM_LAUNCH_CHECK("inner_product");
+    return CERIUM_OK;
+  });
+}
+
+// Steps 5-7: ModDown of the plan's accumulators, optional additions.
 // comm: needed by plans with split extension limbs, whose accumulators' extension limbs are
 // all-gathered (coefficient form) between steps 5 and 6.
-int keyswitch_inner_moddown(cerium_keyswitch* ks, void* out0, void* out1, const void* cpoly, const void* evk,
-                            const void* add0, const void* add1, cudaStream_t stream, uint32_t pre_elt = 0,
-                            uint32_t store_elt = 0, cerium_comm* comm = nullptr) {
+// r > 0: the last r Q limbs are divided away in the same step (they join the extension limbs:
+// cerium/compiler/backend/compiler_keyswitch.cc:26-39, 402-412); add0 / add1 then enter as the
+// reference's PMU group does, acc += [P] * add on the Q limbs, and the outputs hold L - r limbs.
+int keyswitch_moddown(cerium_keyswitch* ks, void* out0, void* out1, const void* add0, const void* add1,
+                      cudaStream_t stream, uint32_t pre_elt = 0, uint32_t store_elt = 0, cerium_comm* comm = nullptr,
+                      int r = 0) {
   if (ks->ext_split && comm == nullptr)
     return fail(CERIUM_ERR_INVALID, "keyswitch: a plan with split extension limbs needs a communicator");
   cerium_context* ctx = ks->ctx;
   const size_t n = kN;
-  const int L = ks->L, K = ks->K, LK = ks->LK, dnum = ks->dnum;
+  const int L = ks->L, K = ks->K, LK = ks->LK;
+  if (r > 0) {
+    if (r > 2 || (size_t)r > ks->fused.size() || ks->fused[r - 1].down == nullptr)
+      return fail(CERIUM_ERR_UNSUPPORTED, "keyswitch: this plan has no ModDown with that many rescale levels (1 or 2, one GPU, L - r >= 1)");
+    if (pre_elt != 0 || store_elt != 0) return fail(CERIUM_ERR_UNSUPPORTED, "keyswitch: a rotation cannot be folded into a ModDown with rescale levels");
+  }
   return dispatch_word(ctx->word_bits, [&](auto tag) -> int {
     using W = decltype(tag);
-    using V = Vec16<W>;
-    W* raised = ws_at<W>(ks, ks->o_raised);
     W* acc = ws_at<W>(ks, ks->o_acc);
     W* conv = ws_at<W>(ks, ks->o_conv);
-    // 4. inner product with the key
-    {
-      InnerProductArgs<W> g{};
-      g.raised = raised;
-      g.raised_digit_stride = (size_t)LK * n;
-      g.raised_limb_stride = n;
-      g.own = static_cast<const W*>(cpoly);
-      g.own_stride = n;
-      g.own_elt = pre_elt;
-      g.evk = static_cast<const W*>(evk);
-      g.evk_digit_stride = (size_t)2 * LK * n;
-      g.evk_poly_stride = (size_t)LK * n;
-      g.evk_limb_stride = n;
-      g.out0 = {acc, n};
-      g.out1 = {acc + (size_t)LK * n, n};
-      g.dnum = dnum;
-      for (int b = 0; b < LK; b++) {
-        g.prime[b] = (uint8_t)ks->all_idx[b];
-        g.own_digit[b] = (int8_t)ks->own_digit[b];
+    if (r > 0) {
+      const cerium_keyswitch::FusedDown& fd = ks->fused[r - 1];
+      const int Lr = L - r;
+      // PMU: acc_p += [P] * add_p on all Q limbs (the dropped ones as well: they are divided away below)
+      for (int p = 0; p < 2; p++) {
+        const void* add = p == 0 ? add0 : add1;
+        if (add == nullptr) continue;
+        W* ap = acc + (size_t)p * LK * n;
+        if (int rc = cerium_ewise(ctx, CERIUM_EW_PMU, ap, n, ap, n, add, n, nullptr, 0, ks->pmod.data(), ks->q_idx.data(), L, stream)) return rc;
       }
-      const PrimeConst<W>* pcs = static_cast<const PrimeConst<W>*>(ctx->d_pcs);
-      const dim3 block(kEwThreads);
-      // every local extended limb (Q and extension) in one launch
-      g.first_limb = 0;
-      { auto kfn = inner_product_kernel<W>; CERIUM_LAUNCH(kfn, dim3(kN / (kEwThreads * V::kLanes), LK), block, 0, stream, g, pcs); }
-      CERIUM_LAUNCH_CHECK("inner_product");
+      // 5. iNTT of the extension limbs and the dropped Q limbs of both accumulators, in place
+      {
+        NttCall c{acc, acc, n, n, fd.ext_pos.data(), fd.ext_prime.data(), (int)fd.ext_pos.size()};
+        if (int rc = launch_ntt_inverse(ctx, c, fd.d_scale, fd.d_scale_shoup, stream)) return rc;
+      }
+      // 6. base conversion (dropped Q limbs, P) -> remaining Q limbs
+      {
+        BconvCall calls[2] = {
+            {fd.down, conv, n, acc + (size_t)Lr * n, n},
+            {fd.down, conv + (size_t)Lr * n, n, acc + (size_t)(LK + Lr) * n, n},
+        };
+        if (int rc = launch_bconv(ctx, calls, 2, stream)) return rc;
+      }
+      // 7. SuD: out = (acc - NTT(conv)) * (P * dropped primes)^-1
+      std::vector<uint32_t> prime2(ks->q_idx.begin(), ks->q_idx.begin() + Lr);
+      prime2.insert(prime2.end(), ks->q_idx.begin(), ks->q_idx.begin() + Lr);
+      std::vector<uint64_t> factor2(fd.pinv);
+      factor2.insert(factor2.end(), fd.pinv.begin(), fd.pinv.end());
+      for (int p = 0; p < 2; p++) {
+        const bool both = 2 * Lr <= kSudMaxBatch;
+        if (p == 1 && both) break;
+        SudCall s{};
+        s.src = conv + (size_t)p * Lr * n;
+        s.src_stride = n;
+        s.work = conv + (size_t)p * Lr * n;
+        s.work_stride = n;
+        s.dst = p == 0 ? out0 : out1;
+        s.dst_stride = n;
+        s.minuend = acc + (size_t)p * LK * n;
+        s.minuend_stride = n;
+        s.prime = prime2.data();
+        s.factor = factor2.data();
+        s.count = both ? 2 * Lr : Lr;
+        if (both) {
+          s.split = Lr;
+          s.dst2 = out1;
+          s.minuend2 = acc + (size_t)LK * n;
+        }
+        if (int rc = launch_sud(ctx, s, stream)) return rc;
+      }
+      return CERIUM_OK;
+    }
+    {
       const W* p0 = acc + (size_t)L * n;          // coefficient-form extension limbs of accumulator 0 ...
       const W* p1 = acc + (size_t)(LK + L) * n;   // ... and 1, as the ModDown conversion reads them
       if (!ks->ext_split) {
@@ -329,6 +412,16 @@ int keyswitch_inner_moddown(cerium_keyswitch* ks, void* out0, void* out1, const 
   });
 }
 
+// Steps 4-7.  Can be repeated with different keys on the same raised digits (hoisting).
+int keyswitch_inner_moddown(cerium_keyswitch* ks, void* out0, void* out1, const void* cpoly, const void* evk,
+                            const void* add0, const void* add1, cudaStream_t stream, uint32_t pre_elt = 0,
+                            uint32_t store_elt = 0, cerium_comm* comm = nullptr, int r = 0) {
+  if (ks->ext_split && comm == nullptr)
+    return fail(CERIUM_ERR_INVALID, "keyswitch: a plan with split extension limbs needs a communicator");
+  if (int rc = keyswitch_inner(ks, cpoly, evk, stream, pre_elt)) return rc;
+  return keyswitch_moddown(ks, out0, out1, add0, add1, stream, pre_elt, store_elt, comm, r);
+}
+
 int keyswitch_finish(cerium_keyswitch* ks, void* out0, void* out1, const void* gathered, const void* cpoly,
                      const void* evk, const void* add0, const void* add1, cudaStream_t stream, uint32_t pre_elt = 0,
                      cerium_comm* comm = nullptr) {
@@ -354,12 +447,13 @@ int keyswitch_sharded_impl(cerium_keyswitch* ks, cerium_comm* comm, void* out0, 
 }
 
 int keyswitch_impl(cerium_keyswitch* ks, void* out0, void* out1, const void* cpoly, const void* evk,
-                   const void* add0, const void* add1, cudaStream_t stream, uint32_t pre_elt = 0) {
+                   const void* add0, const void* add1, cudaStream_t stream, uint32_t pre_elt = 0, int r = 0) {
   if (ks->world != 1) return fail(CERIUM_ERR_INVALID, "keyswitch: a sharded plan needs the begin / finish calls around the all-gather");
   if (ks->lifted) return fail(CERIUM_ERR_INVALID, "keyswitch: a lifted plan only serves cerium_mod_raise");
   void* coef = static_cast<char*>(ks->ws) + ks->o_coef * ks->ctx->word_bytes();
   if (int rc = keyswitch_begin(ks, coef, cpoly, stream, pre_elt)) return rc;
-  return keyswitch_finish(ks, out0, out1, coef, cpoly, evk, add0, add1, stream, pre_elt);
+  if (int rc = keyswitch_raise(ks, coef, stream)) return rc;
+  return keyswitch_inner_moddown(ks, out0, out1, cpoly, evk, add0, add1, stream, pre_elt, 0, nullptr, r);
 }
 
 }  // namespace
@@ -520,8 +614,60 @@ static int keyswitch_create_impl(cerium_context* ctx, cerium_keyswitch** out, in
       ks->ext_prime.push_back(ks->p_idx[k]);
       ks->ext_dst.push_back((uint32_t)(p * ks->pgather_limbs + k));
     }
+  ks->pmod.resize(L);
+  {
+    const std::vector<uint32_t> p_all(p_idx, p_idx + Kg);
+    for (int i = 0; i < L; i++) ks->pmod[i] = host::product_mod(ctx->moduli, p_all, ctx->moduli[ks->q_idx[i]]);
+  }
   const size_t wb = ctx->word_bytes();
   const size_t n = kN;
+  // ModDown with rescale levels folded in (one-GPU plans only)
+  for (int r = 1; r <= 2 && world == 1 && !lifted && L - r >= 1; r++) {
+    cerium_keyswitch::FusedDown fd;
+    const int Lr = L - r, E = Kg + r;
+    std::vector<uint32_t> e_idx;
+    for (int k = 0; k < r; k++) e_idx.push_back(q_idx[Lr + k]);
+    for (int k = 0; k < Kg; k++) e_idx.push_back(p_idx[k]);
+    BconvOptions opt;
+    opt.prescaled = exact;
+    opt.round_half = round_mode == CERIUM_ROUND_HALF;
+    if (create_bconv(ctx, &fd.down, bconv_mode, e_idx.data(), E, ks->q_idx.data(), Lr, opt) != CERIUM_OK) {
+      // a shape the converter cannot take (sum of products too wide): the plan simply has no fused variant
+      fd.down = nullptr;
+      ks->fused.push_back(fd);
+      continue;
+    }
+    fd.pinv.resize(Lr);
+    for (int i = 0; i < Lr; i++) {
+      const uint64_t q = ctx->moduli[ks->q_idx[i]];
+      fd.pinv[i] = host::invmod(host::product_mod(ctx->moduli, e_idx, q), q);
+    }
+    std::vector<uint64_t> sc, scs;
+    for (int p = 0; p < 2; p++)
+      for (int k = 0; k < E; k++) {
+        fd.ext_pos.push_back((uint32_t)(p * LK + Lr + k));
+        fd.ext_prime.push_back(e_idx[k]);
+        const uint64_t ek = ctx->moduli[e_idx[k]];
+        sc.push_back(exact ? fd.down->inv_host[k] : 1);
+        scs.push_back(host::shoup(sc.back(), ek, bits));
+      }
+    if (exact) {
+      std::vector<char> bytes(2 * sc.size() * wb);
+      for (size_t i = 0; i < 2 * sc.size(); i++) {
+        const uint64_t v = i < sc.size() ? sc[i] : scs[i - sc.size()];
+        if (bits == 32) reinterpret_cast<uint32_t*>(bytes.data())[i] = (uint32_t)v;
+        else reinterpret_cast<uint64_t*>(bytes.data())[i] = v;
+      }
+      if (cudaMalloc(&fd.d_scale, bytes.size()) != cudaSuccess ||
+          cudaMemcpy(fd.d_scale, bytes.data(), bytes.size(), cudaMemcpyHostToDevice) != cudaSuccess) {
+        cerium_bconv_destroy(fd.down);
+        cerium_keyswitch_destroy(ks);
+        return fail(CERIUM_ERR_CUDA, "keyswitch_create: scale upload failed");
+      }
+      fd.d_scale_shoup = static_cast<char*>(fd.d_scale) + sc.size() * wb;
+    }
+    ks->fused.push_back(fd);
+  }
   if (exact) {
     // [scale_q | scale_q_shoup | scale_p | scale_p_shoup]
     std::vector<uint64_t> all;
@@ -749,6 +895,10 @@ int cerium_keyswitch_destroy(cerium_keyswitch* ks) {
   DeviceGuard guard(ks->ctx->device);
   for (cerium_bconv* b : ks->up) cerium_bconv_destroy(b);
   if (ks->down) cerium_bconv_destroy(ks->down);
+  for (auto& fd : ks->fused) {
+    if (fd.down) cerium_bconv_destroy(fd.down);
+    cudaFree(fd.d_scale);
+  }
   cudaFree(ks->d_scale);
   cudaFree(ks->ws);
   delete ks;
@@ -762,6 +912,14 @@ int cerium_keyswitch_apply(cerium_keyswitch* ks, void* out0, void* out1, const v
   if (!ks || !out0 || !out1 || !cpoly || !evk) return fail(CERIUM_ERR_INVALID, "keyswitch_apply: null argument");
   DeviceGuard guard(ks->ctx->device);
   return keyswitch_impl(ks, out0, out1, cpoly, evk, add0, add1, (cudaStream_t)stream);
+}
+
+int cerium_keyswitch_apply_rescale(cerium_keyswitch* ks, void* out0, void* out1, const void* cpoly, const void* evk,
+                                   const void* add0, const void* add1, int rescale_levels, void* stream) {
+  if (!ks || !out0 || !out1 || !cpoly || !evk) return fail(CERIUM_ERR_INVALID, "keyswitch_apply_rescale: null argument");
+  if (rescale_levels < 0 || rescale_levels > 2) return fail(CERIUM_ERR_INVALID, "keyswitch_apply_rescale: 0, 1 or 2 rescale levels");
+  DeviceGuard guard(ks->ctx->device);
+  return keyswitch_impl(ks, out0, out1, cpoly, evk, add0, add1, (cudaStream_t)stream, 0, rescale_levels);
 }
 
 int cerium_hrot(cerium_keyswitch* ks, void* out0, void* out1, const void* c0, const void* c1, const void* evk,
@@ -849,8 +1007,11 @@ int cerium_hmult(cerium_keyswitch* ks, void* out0, void* out1, const void* a0, c
   void* d0 = tmp;
   void* d1 = tmp + (size_t)ks->L * limb;
   void* d2 = tmp + (size_t)2 * ks->L * limb;
+  if (do_rescale < 0 || do_rescale > 2) return fail(CERIUM_ERR_INVALID, "hmult: do_rescale is 0, 1 or 2");
   if (int rc = cerium_tensor(ctx, d0, d1, d2, a0, a1, b0, b1, n, ks->q_idx.data(), ks->L, stream)) return rc;
   if (!do_rescale) return keyswitch_impl(ks, out0, out1, d2, evk, d0, d1, (cudaStream_t)stream);
+  // one division by P * q_last: the last limb joins the extension limbs of the ModDown
+  if (do_rescale == 2) return keyswitch_impl(ks, out0, out1, d2, evk, d0, d1, (cudaStream_t)stream, 0, 1);
   char* kso = static_cast<char*>(ks->ws) + ks->o_ksout * wb;  // [2][L][N], contiguous: two polynomials
   if (int rc = keyswitch_impl(ks, kso, kso + (size_t)ks->L * limb, d2, evk, d0, d1, (cudaStream_t)stream)) return rc;
   void* scratch = static_cast<char*>(ks->ws) + ks->o_scratch * wb;
@@ -858,6 +1019,136 @@ int cerium_hmult(cerium_keyswitch* ks, void* out0, void* out1, const void* a0, c
   void* outs[2] = {out0, out1};
   void* pair_work = static_cast<char*>(ks->ws) + ks->o_conv * wb;
   return rescale_impl(ctx, ks->round_mode, outs, pair_work, kso, ks->q_idx.data(), ks->L, 2, scratch, (cudaStream_t)stream);
+}
+
+size_t cerium_bsgs_work_limbs(const cerium_keyswitch* ks, int g, int n_giant) {
+  if (!ks || g < 1 || n_giant < 1) return 0;
+  // rotated copies of the input, the giant steps' inner sums, the two pre-addition sums
+  return ((size_t)(g - 1) * 2 + (size_t)n_giant * 2 + 2) * (size_t)ks->L;
+}
+
+int cerium_bsgs_apply(cerium_keyswitch* ks, void* out0, void* out1, const void* c0, const void* c1, int g, int n_giant,
+                      const void* const* plaintexts, const void* const* baby_keys_pre, const uint32_t* baby_elts,
+                      const void* const* giant_keys, const uint32_t* giant_elts, int rescale_levels, void* work,
+                      void* stream) {
+  if (!ks || !out0 || !out1 || !c0 || !c1 || !plaintexts || !giant_elts || !work)
+    return fail(CERIUM_ERR_INVALID, "bsgs_apply: null argument");
+  if (ks->world != 1 || ks->lifted) return fail(CERIUM_ERR_INVALID, "bsgs_apply: needs a one-GPU key-switching plan");
+  if (g < 1 || g > kBsgsMaxBaby || n_giant < 1 || n_giant > kBsgsMaxGiant)
+    return fail(CERIUM_ERR_UNSUPPORTED, "bsgs_apply: at most 16 baby steps and 32 giant steps");
+  if (g > 1 && (!baby_keys_pre || !baby_elts)) return fail(CERIUM_ERR_INVALID, "bsgs_apply: baby steps need keys and elements");
+  if (rescale_levels < 0 || rescale_levels > 2) return fail(CERIUM_ERR_INVALID, "bsgs_apply: 0, 1 or 2 rescale levels");
+  cerium_context* ctx = ks->ctx;
+  const int L = ks->L;
+  if (((uintptr_t)work | (uintptr_t)c0 | (uintptr_t)c1 | (uintptr_t)out0 | (uintptr_t)out1) & 15u)
+    return fail(CERIUM_ERR_INVALID, "bsgs_apply: pointers must be 16-byte aligned");
+  for (int i = 0; i < L; i++) {
+    // g products of two residues per accumulator
+    const long double q = (long double)ctx->moduli[ks->q_idx[i]];
+    if (q * q * g >= (ctx->word_bits == 32 ? 1.8e19L : 3.4e38L))
+      return fail(CERIUM_ERR_UNSUPPORTED, "bsgs_apply: that many baby steps overflow the accumulator for primes this wide");
+  }
+  int n_rot = 0;
+  for (int i = 0; i < n_giant; i++) {
+    if (!(giant_elts[i] & 1) || giant_elts[i] >= 2u * kN) return fail(CERIUM_ERR_INVALID, "bsgs_apply: Galois element is not valid");
+    if (giant_elts[i] != 1) {
+      if (!giant_keys || !giant_keys[i]) return fail(CERIUM_ERR_INVALID, "bsgs_apply: a rotated giant step has no key");
+      n_rot++;
+    }
+  }
+  if (n_rot == 0 && rescale_levels != 0) return fail(CERIUM_ERR_UNSUPPORTED, "bsgs_apply: rescale levels need at least one rotated giant step");
+  DeviceGuard guard(ctx->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t n = kN, wb = ctx->word_bytes(), poly = (size_t)L * n * wb;
+  char* w = static_cast<char*>(work);
+  char* baby = w;                                        // [g-1][2][L]
+  char* inner = baby + (size_t)(g - 1) * 2 * poly;       // [n_giant][2][L]
+  char* sum0 = inner + (size_t)n_giant * 2 * poly;       // [L]  sum of the rotated first polynomials
+  char* sum1 = sum0 + poly;                              // [L]  sum of the un-rotated second polynomials
+  // 1. baby steps: g - 1 hoisted rotations of the input (one ModUp)
+  if (g > 1) {
+    if (int rc = cerium_hoisted_begin(ks, c1, stream)) return rc;
+    for (int j = 1; j < g; j++) {
+      if (!baby_keys_pre[j]) return fail(CERIUM_ERR_INVALID, "bsgs_apply: a baby step has no key");
+      char* bj = baby + (size_t)(j - 1) * 2 * poly;
+      if (int rc = cerium_hoisted_rotate(ks, bj, bj + poly, c0, c1, baby_keys_pre[j], baby_elts[j], stream)) return rc;
+    }
+  }
+  // 2. inner sums s_i = sum_j pt[i][j] * baby_j, kBsgsGroup giant steps per pass over the baby steps
+  std::vector<char> have(n_giant, 0);
+  int rc = dispatch_word(ctx->word_bits, [&](auto tag) -> int {
+    using W = decltype(tag);
+    using V = Vec16<W>;
+    const PrimeConst<W>* pcs = static_cast<const PrimeConst<W>*>(ctx->d_pcs);
+    for (int first = 0; first < n_giant; first += kBsgsGroup) {
+      const int cnt = std::min(kBsgsGroup, n_giant - first);
+      PtMacArgs<W> a{};
+      a.g = g;
+      for (int j = 0; j < g; j++) {
+        const char* b = j == 0 ? nullptr : baby + (size_t)(j - 1) * 2 * poly;
+        a.src0[j] = reinterpret_cast<const W*>(j == 0 ? static_cast<const char*>(c0) : b);
+        a.src1[j] = reinterpret_cast<const W*>(j == 0 ? static_cast<const char*>(c1) : b + poly);
+      }
+      for (int i = 0; i < kBsgsGroup; i++) {
+        const int gi = first + std::min(i, cnt - 1);   // unused slots of the last group repeat its last giant step
+        a.out0[i] = reinterpret_cast<W*>(inner + (size_t)gi * 2 * poly);
+        a.out1[i] = reinterpret_cast<W*>(inner + (size_t)gi * 2 * poly + poly);
+        for (int j = 0; j < g; j++) {
+          const void* p = i < cnt ? plaintexts[(size_t)(first + i) * g + j] : nullptr;
+          if (p != nullptr && ((uintptr_t)p & 15u)) return fail(CERIUM_ERR_INVALID, "bsgs_apply: pointers must be 16-byte aligned");
+          a.pt[i][j] = static_cast<const W*>(p);
+          if (p != nullptr) have[first + i] = 1;
+        }
+      }
+      for (int b = 0; b < L; b++) a.prime[b] = (uint8_t)ks->q_idx[b];
+      const dim3 grid(kN / (kEwThreads * V::kLanes), L);
+      switch (cnt) {
+        case 1: { auto kfn = pt_mac_kernel<W, 1>; CERIUM_LAUNCH(kfn, grid, kEwThreads, 0, st, a, pcs); } break;
+        case 2: { auto kfn = pt_mac_kernel<W, 2>; CERIUM_LAUNCH(kfn, grid, kEwThreads, 0, st, a, pcs); } break;
+        case 3: { auto kfn = pt_mac_kernel<W, 3>; CERIUM_LAUNCH(kfn, grid, kEwThreads, 0, st, a, pcs); } break;
+        default: { auto kfn = pt_mac_kernel<W, 4>; CERIUM_LAUNCH(kfn, grid, kEwThreads, 0, st, a, pcs); } break;
+      }
+    }
+    CERIUM_LAUNCH_CHECK("bsgs plaintext multiply-accumulate");
+    // 3. sum0 = sum_i phi_i(s_i.c0) over every giant step, sum1 = sum of s_i.c1 over the un-rotated ones
+    for (int which = 0; which < 2; which++) {
+      AutoSumArgs<W> s{};
+      for (int i = 0; i < n_giant; i++) {
+        if (!have[i] || (which == 1 && giant_elts[i] != 1)) continue;
+        s.in[s.count] = reinterpret_cast<const W*>(inner + (size_t)i * 2 * poly + (which ? poly : 0));
+        s.elt[s.count] = giant_elts[i];
+        s.count++;
+      }
+      s.out = reinterpret_cast<W*>(which ? sum1 : sum0);
+      for (int b = 0; b < L; b++) s.prime[b] = (uint8_t)ks->q_idx[b];
+      { auto kfn = automorph_sum_kernel<W>; CERIUM_LAUNCH(kfn, dim3(kN / kEwThreads, L), kEwThreads, 0, st, s, pcs); }
+    }
+    CERIUM_LAUNCH_CHECK("bsgs rotation sums");
+    return CERIUM_OK;
+  });
+  if (rc != CERIUM_OK) return rc;
+  if (!have[0] && n_rot == 0) return fail(CERIUM_ERR_INVALID, "bsgs_apply: no diagonal at all");
+  // 4. every rotated giant step: ModUp of phi_i(s_i.c1) (the rotation is the read pattern of the inverse
+  //    transform and of the digits' own limbs) and its product with the key, summed in the extended basis
+  void* coef = static_cast<char*>(ks->ws) + ks->o_coef * wb;
+  bool first = true;
+  for (int i = 0; i < n_giant; i++) {
+    if (!have[i] || giant_elts[i] == 1) continue;
+    const char* s1 = inner + (size_t)i * 2 * poly + poly;
+    if (int r2 = keyswitch_begin(ks, coef, s1, st, giant_elts[i])) return r2;
+    if (int r2 = keyswitch_raise(ks, coef, st)) return r2;
+    if (int r2 = keyswitch_inner(ks, s1, giant_keys[i], st, giant_elts[i], !first)) return r2;
+    first = false;
+  }
+  if (first) {
+    // no rotated giant step: the sums are the result
+    CERIUM_CUDA(cudaMemcpyAsync(out0, sum0, poly, cudaMemcpyDeviceToDevice, st));
+    CERIUM_CUDA(cudaMemcpyAsync(out1, sum1, poly, cudaMemcpyDeviceToDevice, st));
+    return CERIUM_OK;
+  }
+  // 5. ONE ModDown (with the rescale levels in the same division); the sums enter as the PMU
+  //    pre-addition: as addends of the last kernel when nothing else is divided away
+  return keyswitch_moddown(ks, out0, out1, sum0, sum1, st, 0, 0, nullptr, rescale_levels);
 }
 
 int cerium_rescale(cerium_context* ctx, int round_mode, void* out, const void* in, const uint32_t* q_idx, int L,

@@ -264,6 +264,7 @@ struct InnerProductArgs {
   int dnum;
   uint32_t own_elt;       // not 0: `own` is read through the Galois automorphism of this element
                           // (word i of a limb is own[pi(i)]), i.e. the rotation of the input is folded in
+  int accumulate;         // not 0: the products are added to the (canonical) values out0 / out1 already hold
   uint8_t prime[kEwMaxLimbs];     // prime index of extended limb b
   int8_t own_digit[kEwMaxLimbs];  // digit that limb b belongs to (-1 for extension limbs)
 };
@@ -312,6 +313,14 @@ __global__ void __launch_bounds__(kEwThreads)
   for (int l = 0; l < V::kLanes; l++) {
     o0.v[l] = barrett2<W>(acc0[l].hi(), acc0[l].lo(), pc);
     o1.v[l] = barrett2<W>(acc1[l].hi(), acc1[l].lo(), pc);
+  }
+  if (g.accumulate != 0) {
+    const V p0 = V::load(g.out0.at(b, idx)), p1 = V::load(g.out1.at(b, idx));
+#pragma unroll
+    for (int l = 0; l < V::kLanes; l++) {
+      o0.v[l] = add_mod<W>(o0.v[l], p0.v[l], pc.q);
+      o1.v[l] = add_mod<W>(o1.v[l], p1.v[l], pc.q);
+    }
   }
   o0.store(g.out0.at(b, idx));
   o1.store(g.out1.at(b, idx));

@@ -14,6 +14,7 @@
 
 #include "../../include/cerium_b200.h"
 #include "bconv_kernels.cuh"
+#include "bsgs_kernels.cuh"
 #include "ewise_kernels.cuh"
 #include "host_math.h"
 #include "ntt_kernels.cuh"

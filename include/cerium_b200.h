@@ -368,6 +368,19 @@ CERIUM_API int cerium_keyswitch_apply(cerium_keyswitch *ks, void *out0, void *ou
                            const void *evk, const void *add0, const void *add1, void *stream);
 
 /*
+ * The key switch with the reference's PMU pre-addition and `rescale_levels` (0, 1 or 2) of the last Q
+ * limbs divided away in the SAME division as P: the dropped limbs join the extension limbs of the
+ * ModDown - inverse transform, base conversion (dropped limbs, P) -> remaining limbs, one SuD with
+ * (P * dropped primes)^-1 - as keyswitch_ciphertext_impl does with rescale_levels > 0
+ * (cerium/compiler/backend/compiler_keyswitch.cc:26-39, 360-417).  out0 / out1 hold L - rescale_levels
+ * limbs.  One rounding, where cerium_keyswitch_apply followed by cerium_rescale rounds twice: the two
+ * results may differ in the last unit.  One-GPU plans; rescale_levels = 0 is cerium_keyswitch_apply.
+ */
+CERIUM_API int cerium_keyswitch_apply_rescale(cerium_keyswitch *ks, void *out0, void *out1, const void *cpoly,
+                                              const void *evk, const void *add0, const void *add1,
+                                              int rescale_levels, void *stream);
+
+/*
  * HRot: (out0,out1) = KeySwitch(phi(c1)) + (phi(c0), 0), phi the automorphism galois_elt.
  * Restates rotate_internal (cerium/compiler/backend/compiler.cc:701-726).  The rotated
  * polynomials are never materialised: the kernels of the key switch read c0 and c1 through the
@@ -398,10 +411,41 @@ CERIUM_API int cerium_hoisted_rotate(cerium_keyswitch *ks, void *out0, void *out
  * HMult + relinearize (+ rescale by the last limb when do_rescale != 0): tensor product,
  * key switch of d2, addition of d0/d1 (cerium/compiler/backend/compiler.cc:443-467,
  * compiler_keyswitch.cc:360-380) and rescale (compiler_rescale.cc:209-284).  Outputs hold
- * L limbs, or L-1 with rescale.
+ * L limbs, or L-1 with rescale.  do_rescale = 1: ModDown, then rescale (two divisions, two
+ * roundings); do_rescale = 2: the rescale folded into the ModDown (one division by P * q_last,
+ * cerium_keyswitch_apply_rescale with one level: fewer kernels, one rounding).
  */
 CERIUM_API int cerium_hmult(cerium_keyswitch *ks, void *out0, void *out1, const void *a0, const void *a1,
                  const void *b0, const void *b1, const void *evk, int do_rescale, void *stream);
+
+/*
+ * Baby-step / giant-step multiply-accumulate, out = sum_i phi_{G_i}( sum_j pt[i][j] (.) phi_{B_j}(ct) ):
+ * the linear-transform building block of bootstrapping (CoeffToSlot / SlotToCoeff) and of matrix-vector
+ * products.  Restates the reference's BsgsMultiplyAccumulate lowering
+ * (cerium/compiler/backend/compiler.cc:2457-2822, entry :3001-3069): the baby steps are hoisted
+ * rotations of the input (one ModUp); per giant step the plaintext products are summed (MuP, Add),
+ * the sum is rotated, raised (INTT, BCONV, NTT) and multiplied with the giant step's key, and these
+ * products are ACCUMULATED IN THE EXTENDED BASIS over all giant steps; the un-rotated parts enter as the
+ * PMU pre-addition; ONE ModDown ends the operation, with `rescale_levels` (0, 1, 2) extra Q limbs
+ * divided away in the same step.
+ *   c0, c1            the input ciphertext, [L][N] each
+ *   g, n_giant        baby steps (1..16, baby step 0 is the input itself) and giant steps (1..32)
+ *   plaintexts        HOST array [n_giant * g] of device pointers to NTT-form diagonals [L][N], entry
+ *                     i * g + j; NULL = that diagonal is absent
+ *   baby_keys_pre     HOST array [g]: pre-permuted ("RotationInv") key of baby step j (entry 0 unused), as
+ *   baby_elts         cerium_hoisted_rotate takes them; HOST array [g] of Galois elements (entry 0 unused)
+ *   giant_keys        HOST array [n_giant]: ordinary rotation key of giant step i, as cerium_hrot takes it
+ *   giant_elts        HOST array [n_giant] of Galois elements; 1 = this giant step is not rotated (no key)
+ *   work              caller-owned device scratch of cerium_bsgs_work_limbs() limbs
+ *   out0, out1        [L - rescale_levels][N]; must not overlap the inputs
+ * Every diagonal and every key is read exactly once; the rotated copies once per four giant steps.
+ */
+CERIUM_API size_t cerium_bsgs_work_limbs(const cerium_keyswitch *ks, int g, int n_giant);
+CERIUM_API int cerium_bsgs_apply(cerium_keyswitch *ks, void *out0, void *out1, const void *c0, const void *c1,
+                                 int g, int n_giant, const void *const *plaintexts,
+                                 const void *const *baby_keys_pre, const uint32_t *baby_elts,
+                                 const void *const *giant_keys, const uint32_t *giant_elts, int rescale_levels,
+                                 void *work, void *stream);
 
 /*
  * Rescale `n_polys` polynomials of L limbs each ([poly][limb][N] contiguous) by their last

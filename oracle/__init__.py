@@ -78,6 +78,16 @@ def lib():
                                   _u64p, _u64p, _u64p]
         L.orc_keyswitch.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, _u32p, C.c_int, _u32p,
                                     C.c_int, _u64p, _u64p, _u64p, _u64p]
+        L.orc_keyswitch_acc.argtypes = [C.c_void_p, C.c_int, C.c_int, _u32p, C.c_int, _u32p, C.c_int, _u64p, _u64p,
+                                        _u64p, _u64p]
+        L.orc_moddown_rescale.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, _u32p, C.c_int, _u32p, C.c_int,
+                                          _u64p, _u64p]
+        L.orc_keyswitch_rescale.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, _u32p, C.c_int, _u32p, C.c_int,
+                                            C.c_int, _u64p, _u64p, _u64p, _u64p, _u64p, _u64p]
+        L.orc_hmult_relin_fused.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, _u32p, C.c_int, _u32p, C.c_int,
+                                            _u64p, _u64p, _u64p, _u64p, _u64p, _u64p, _u64p]
+        L.orc_bsgs.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, _u32p, C.c_int, _u32p, C.c_int, C.c_int, C.c_int,
+                               C.c_int, _u64p, _u64p, C.POINTER(C.c_uint8), _u32p, _u64p, _u64p, _u64p]
         L.orc_rescale.argtypes = [C.c_void_p, C.c_int, C.c_int, _u32p, _u64p, _u64p]
         L.orc_double_rescale.argtypes = [C.c_void_p, C.c_int, _u32p, _u64p, _u64p]
         L.orc_mod_raise.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, _u32p, C.c_int, _u32p, C.c_uint32,
@@ -177,6 +187,54 @@ class OracleContext:
         o1 = np.empty((L, self.n), dtype=np.uint64)
         lib().orc_keyswitch(self._h, bconv_mode, round_mode, L, _p32(qi), K, _p32(pi), dnum,
                             _p64(cpoly), _p64(evk), _p64(o0), _p64(o1))
+        return o0, o1
+
+    def moddown_rescale(self, bconv_mode, round_mode, q_idx, p_idx, r, t) -> np.ndarray:
+        """ModDown of t ([L+K][N], extended basis) with r rescale levels in the same division: [L-r][N]."""
+        qi, pi = _idx(q_idx), _idx(p_idx)
+        t = _c64(t)
+        out = np.empty((len(qi) - r, self.n), dtype=np.uint64)
+        lib().orc_moddown_rescale(self._h, bconv_mode, round_mode, len(qi), _p32(qi), len(pi), _p32(pi), int(r),
+                                  _p64(t), _p64(out))
+        return out
+
+    def keyswitch_rescale(self, bconv_mode, round_mode, q_idx, p_idx, dnum, r, cpoly, evk, add0=None, add1=None):
+        """Key switch with the PMU pre-additions and r rescale levels inside the ModDown: two [L-r][N]."""
+        qi, pi = _idx(q_idx), _idx(p_idx)
+        cpoly, evk = _c64(cpoly), _c64(evk)
+        a0 = _c64(add0) if add0 is not None else None
+        a1 = _c64(add1) if add1 is not None else None
+        o0 = np.empty((len(qi) - r, self.n), dtype=np.uint64)
+        o1 = np.empty((len(qi) - r, self.n), dtype=np.uint64)
+        lib().orc_keyswitch_rescale(self._h, bconv_mode, round_mode, len(qi), _p32(qi), len(pi), _p32(pi), dnum,
+                                    int(r), _p64(cpoly), _p64(evk), _p64(a0) if a0 is not None else None,
+                                    _p64(a1) if a1 is not None else None, _p64(o0), _p64(o1))
+        return o0, o1
+
+    def hmult_relin_fused(self, bconv_mode, round_mode, q_idx, p_idx, dnum, a0, a1, b0, b1, evk):
+        """HMult + relinearize + rescale with one division (the rescale folded into the ModDown)."""
+        qi, pi = _idx(q_idx), _idx(p_idx)
+        a0, a1, b0, b1, evk = map(_c64, (a0, a1, b0, b1, evk))
+        o0 = np.empty((len(qi) - 1, self.n), dtype=np.uint64)
+        o1 = np.empty((len(qi) - 1, self.n), dtype=np.uint64)
+        lib().orc_hmult_relin_fused(self._h, bconv_mode, round_mode, len(qi), _p32(qi), len(pi), _p32(pi), dnum,
+                                    _p64(a0), _p64(a1), _p64(b0), _p64(b1), _p64(evk), _p64(o0), _p64(o1))
+        return o0, o1
+
+    def bsgs(self, bconv_mode, round_mode, q_idx, p_idx, dnum, r, baby, pts, present, elts, keys):
+        """Baby-step / giant-step multiply-accumulate with the giant-step key switches accumulated in the
+        extended basis and one ModDown (r rescale levels).  baby [g][2][L][N], pts [n_giant][g][L][N],
+        present [n_giant][g], elts [n_giant] (1 = no rotation), keys [n_giant][dnum][2][L+K][N]."""
+        qi, pi = _idx(q_idx), _idx(p_idx)
+        baby, pts, keys = _c64(baby), _c64(pts), _c64(keys)
+        g, n_giant = baby.shape[0], pts.shape[0]
+        pres = np.ascontiguousarray(np.asarray(present, dtype=np.uint8).reshape(n_giant * g))
+        el = _idx(elts)
+        o0 = np.empty((len(qi) - r, self.n), dtype=np.uint64)
+        o1 = np.empty((len(qi) - r, self.n), dtype=np.uint64)
+        lib().orc_bsgs(self._h, bconv_mode, round_mode, len(qi), _p32(qi), len(pi), _p32(pi), dnum, g, n_giant, int(r),
+                       _p64(baby), _p64(pts), pres.ctypes.data_as(C.POINTER(C.c_uint8)), _p32(el), _p64(keys),
+                       _p64(o0), _p64(o1))
         return o0, o1
 
     def rescale(self, round_mode, q_idx, cpoly) -> np.ndarray:

@@ -541,23 +541,22 @@ ORC_API void orc_moddown(const orc_ctx *c, int bconv_mode, int round_mode, int L
 }
 
 /*
- * Hybrid key switch of one polynomial.
+ * Front half of the hybrid key switch of one polynomial: acc0, acc1 ([L+K][n], the extended basis
+ * q_idx u p_idx, NTT form) += sum_d ModUp(c restricted to digit d) * evk_d.
  *   cpoly : [L][n], NTT form, limb i over prime q_idx[i]
  *   evk   : [dnum][2][L+K][n]; limb order inside a key polynomial is
  *           q_idx[0..L-1] then p_idx[0..K-1]
  *   digit of limb i = i % dnum (stride split,
  *           cerium/compiler/backend/compiler_keyswitch.cc:68-99)
- *   out0,out1 : [L][n] = ModDown( sum_d ModUp(c restricted to digit d) * evk_d )
- * Restates keyswitch_ciphertext_impl
- * (cerium/compiler/backend/compiler_keyswitch.cc:253-432) without the P*c0
- * pre-addition (PMU), which the caller performs as an ordinary modular add
- * after ModDown: (t + P*c0 - b)/P = (t - b)/P + c0 exactly mod q.
- * The digit's own limbs are copied from the NTT-form input instead of being
- * converted (kernel_instruction.h:823-838).
+ * Restates the INTT / BCONV / NTT / EVKMUL groups of keyswitch_ciphertext_impl
+ * (cerium/compiler/backend/compiler_keyswitch.cc:253-358).  The digit's own limbs are copied from
+ * the NTT-form input instead of being converted (kernel_instruction.h:823-838).  Accumulating into
+ * given sums is what the BSGS lowering does across giant steps
+ * (cerium/compiler/backend/compiler.cc:2630-2665, kg_acc).
  */
-ORC_API void orc_keyswitch(const orc_ctx *c, int bconv_mode, int round_mode, int L,
-                           const uint32_t *q_idx, int K, const uint32_t *p_idx, int dnum,
-                           const u64 *cpoly, const u64 *evk, u64 *out0, u64 *out1) {
+ORC_API void orc_keyswitch_acc(const orc_ctx *c, int bconv_mode, int L, const uint32_t *q_idx, int K,
+                               const uint32_t *p_idx, int dnum, const u64 *cpoly, const u64 *evk, u64 *acc0,
+                               u64 *acc1) {
   size_t n = c->n;
   int LK = L + K;
   uint32_t *all_idx = (uint32_t *)malloc((size_t)LK * sizeof(uint32_t));
@@ -566,8 +565,6 @@ ORC_API void orc_keyswitch(const orc_ctx *c, int bconv_mode, int round_mode, int
   u64 *coef = (u64 *)malloc((size_t)L * n * sizeof(u64));
   memcpy(coef, cpoly, (size_t)L * n * sizeof(u64));
   orc_ntt_inverse_batch(c, coef, q_idx, L);
-  u64 *acc0 = (u64 *)calloc((size_t)LK * n, sizeof(u64));
-  u64 *acc1 = (u64 *)calloc((size_t)LK * n, sizeof(u64));
   u64 *raised = (u64 *)malloc((size_t)LK * n * sizeof(u64));
   u64 *din = (u64 *)malloc((size_t)L * n * sizeof(u64));
   u64 *dmod = (u64 *)malloc((size_t)LK * sizeof(u64));
@@ -603,10 +600,65 @@ ORC_API void orc_keyswitch(const orc_ctx *c, int bconv_mode, int round_mode, int
       orc_ew_mad(q, n, r, k1 + (size_t)i * n, acc1 + (size_t)i * n, acc1 + (size_t)i * n);
     }
   }
-  orc_moddown(c, bconv_mode, round_mode, L, q_idx, K, p_idx, acc0, acc0 + (size_t)L * n, out0);
-  orc_moddown(c, bconv_mode, round_mode, L, q_idx, K, p_idx, acc1, acc1 + (size_t)L * n, out1);
-  free(all_idx); free(coef); free(acc0); free(acc1); free(raised); free(din);
+  free(all_idx); free(coef); free(raised); free(din);
   free(dmod); free(omod); free(oidx); free(opos); free(obuf);
+}
+
+/*
+ * ModDown with `r` rescale levels in the same division: t ([L+K][n], extended basis, NTT form) ->
+ * out ([L-r][n]) = (t - NTT(BConv_{E->Q'}(iNTT(t_E)))) * (prod E)^-1, E = the last r primes of
+ * q_idx and all of p_idx, Q' = q_idx[0..L-r).  "The dropped Q limbs are treated as extra extension
+ * limbs": the reference's key switch with rescale_levels
+ * (cerium/compiler/backend/compiler_keyswitch.cc:26-39, 382-417; the Usp / Ext adjustment sizes of
+ * cerium/compiler/backend/compiler.cc:2538-2561, 2706-2760).  r = 0 is orc_moddown.  One rounding
+ * (floor, or to nearest with ORC_ROUND_HALF) of the division by P * q_{L-r} ... q_{L-1}, where ModDown
+ * followed by rescale rounds twice.
+ */
+ORC_API void orc_moddown_rescale(const orc_ctx *c, int bconv_mode, int round_mode, int L, const uint32_t *q_idx,
+                                 int K, const uint32_t *p_idx, int r, const u64 *t, u64 *out) {
+  size_t n = c->n;
+  int Lr = L - r, E = K + r;
+  uint32_t *e_idx = (uint32_t *)malloc((size_t)E * sizeof(uint32_t));
+  for (int k = 0; k < r; k++) e_idx[k] = q_idx[Lr + k];
+  for (int k = 0; k < K; k++) e_idx[r + k] = p_idx[k];
+  /* the limbs of E are contiguous in t: [Lr, L + K) */
+  orc_moddown(c, bconv_mode, round_mode, Lr, q_idx, E, e_idx, t, t + (size_t)Lr * n, out);
+  free(e_idx);
+}
+
+/*
+ * Key switch of one polynomial with the reference's PMU pre-addition and `r` rescale levels:
+ *   acc = sum_d ModUp(cpoly_d) * evk_d;  acc0 += [P] * add0, acc1 += [P] * add1 on the Q limbs (add may
+ *   be NULL; PMU, cerium/compiler/backend/compiler_keyswitch.cc:360-380);  out = ModDown_r(acc).
+ * With r = 0 this equals orc_keyswitch followed by the additions; with r > 0 the division by
+ * P * (dropped primes) is rounded once.
+ */
+ORC_API void orc_keyswitch_rescale(const orc_ctx *c, int bconv_mode, int round_mode, int L, const uint32_t *q_idx,
+                                   int K, const uint32_t *p_idx, int dnum, int r, const u64 *cpoly, const u64 *evk,
+                                   const u64 *add0, const u64 *add1, u64 *out0, u64 *out1) {
+  size_t n = c->n;
+  int LK = L + K;
+  u64 *acc0 = (u64 *)calloc((size_t)LK * n, sizeof(u64));
+  u64 *acc1 = (u64 *)calloc((size_t)LK * n, sizeof(u64));
+  orc_keyswitch_acc(c, bconv_mode, L, q_idx, K, p_idx, dnum, cpoly, evk, acc0, acc1);
+  for (int i = 0; i < L; i++) {
+    u64 q = c->p[q_idx[i]].q;
+    u64 pq = prod_mod(c, p_idx, K, q);
+    if (add0) orc_ew_pmu(q, n, acc0 + (size_t)i * n, add0 + (size_t)i * n, pq, acc0 + (size_t)i * n);
+    if (add1) orc_ew_pmu(q, n, acc1 + (size_t)i * n, add1 + (size_t)i * n, pq, acc1 + (size_t)i * n);
+  }
+  orc_moddown_rescale(c, bconv_mode, round_mode, L, q_idx, K, p_idx, r, acc0, out0);
+  orc_moddown_rescale(c, bconv_mode, round_mode, L, q_idx, K, p_idx, r, acc1, out1);
+  free(acc0); free(acc1);
+}
+
+/* Hybrid key switch of one polynomial: out0, out1 [L][n] = ModDown(sum_d ModUp(c_d) * evk_d), without
+ * the P*c0 pre-addition (the caller adds after ModDown: (t + P*c0 - b)/P = (t - b)/P + c0 exactly mod q).
+ * Restates keyswitch_ciphertext_impl (cerium/compiler/backend/compiler_keyswitch.cc:253-432). */
+ORC_API void orc_keyswitch(const orc_ctx *c, int bconv_mode, int round_mode, int L,
+                           const uint32_t *q_idx, int K, const uint32_t *p_idx, int dnum,
+                           const u64 *cpoly, const u64 *evk, u64 *out0, u64 *out1) {
+  orc_keyswitch_rescale(c, bconv_mode, round_mode, L, q_idx, K, p_idx, dnum, 0, cpoly, evk, NULL, NULL, out0, out1);
 }
 
 /*
@@ -786,6 +838,93 @@ ORC_API void orc_hmult_relin(const orc_ctx *c, int bconv_mode, int round_mode, i
     memcpy(out1, k1, sz * sizeof(u64));
   }
   free(d0); free(d1); free(d2); free(k0); free(k1);
+}
+
+/*
+ * HMult + relinearize + rescale with ONE division: tensor product, key switch of d2 with the PMU
+ * pre-additions of d0, d1 and one rescale level inside the ModDown (the reference's relinearize2
+ * followed by rescale when the compiler folds the rescale into the key switch,
+ * cerium/compiler/backend/compiler_keyswitch.cc:26-39, 360-417).  out0 / out1: [L-1][n].
+ */
+ORC_API void orc_hmult_relin_fused(const orc_ctx *c, int bconv_mode, int round_mode, int L, const uint32_t *q_idx,
+                                   int K, const uint32_t *p_idx, int dnum, const u64 *a0, const u64 *a1,
+                                   const u64 *b0, const u64 *b1, const u64 *evk, u64 *out0, u64 *out1) {
+  size_t n = c->n, sz = (size_t)L * n;
+  u64 *d0 = (u64 *)malloc(sz * sizeof(u64)), *d1 = (u64 *)malloc(sz * sizeof(u64));
+  u64 *d2 = (u64 *)malloc(sz * sizeof(u64));
+#pragma omp parallel for schedule(static)
+  for (int i = 0; i < L; i++) {
+    u64 q = c->p[q_idx[i]].q;
+    size_t o = (size_t)i * n;
+    orc_ew_mul(q, n, a0 + o, b0 + o, d0 + o);
+    orc_ew_mul(q, n, a0 + o, b1 + o, d1 + o);
+    orc_ew_mad(q, n, a1 + o, b0 + o, d1 + o, d1 + o);
+    orc_ew_mul(q, n, a1 + o, b1 + o, d2 + o);
+  }
+  orc_keyswitch_rescale(c, bconv_mode, round_mode, L, q_idx, K, p_idx, dnum, 1, d2, evk, d0, d1, out0, out1);
+  free(d0); free(d1); free(d2);
+}
+
+/*
+ * Baby-step / giant-step multiply-accumulate, from the baby-step ciphertexts on
+ * (cerium/compiler/backend/compiler.cc:2457-2822, bsgs_giantstep_accumulate_keyswitch_iterations):
+ *   baby   : [g][2][L][n]  the g rotated copies of the input (both polynomials), NTT form
+ *   pts    : [n_giant][g][L][n] plaintext diagonals; present[i * g + j] = 0 skips a diagonal
+ *   elts   : [n_giant] Galois element of every giant step (1 = no rotation)
+ *   keys   : [n_giant][dnum][2][L+K][n] rotation key of every giant step (ignored where elts[i] = 1)
+ * per giant step i: s_i = sum_j pt[i][j] * baby_j (MuP + Add); rot_i = phi_{elts[i]}(s_i);
+ * ct0_sum += rot_i.c0; for elts[i] = 1: ct1_zero += rot_i.c1, otherwise (k0, k1) += ModUp(rot_i.c1) * key_i,
+ * ACCUMULATED in the extended basis; then k0 += [P] ct0_sum, k1 += [P] ct1_zero (PMU) and ONE ModDown
+ * with r rescale levels.  out0 / out1: [L-r][n].
+ */
+ORC_API void orc_bsgs(const orc_ctx *c, int bconv_mode, int round_mode, int L, const uint32_t *q_idx, int K,
+                      const uint32_t *p_idx, int dnum, int g, int n_giant, int r, const u64 *baby, const u64 *pts,
+                      const uint8_t *present, const uint32_t *elts, const u64 *keys, u64 *out0, u64 *out1) {
+  size_t n = c->n, sz = (size_t)L * n;
+  int LK = L + K;
+  u64 *acc0 = (u64 *)calloc((size_t)LK * n, sizeof(u64));
+  u64 *acc1 = (u64 *)calloc((size_t)LK * n, sizeof(u64));
+  u64 *ct0_sum = (u64 *)calloc(sz, sizeof(u64)), *ct1_zero = (u64 *)calloc(sz, sizeof(u64));
+  u64 *s0 = (u64 *)malloc(sz * sizeof(u64)), *s1 = (u64 *)malloc(sz * sizeof(u64));
+  u64 *r0 = (u64 *)malloc(sz * sizeof(u64)), *r1 = (u64 *)malloc(sz * sizeof(u64));
+  for (int i = 0; i < n_giant; i++) {
+    memset(s0, 0, sz * sizeof(u64));
+    memset(s1, 0, sz * sizeof(u64));
+    int any = 0;
+    for (int j = 0; j < g; j++) {
+      if (!present[i * g + j]) continue;
+      any = 1;
+      const u64 *pt = pts + ((size_t)i * g + j) * sz;
+      const u64 *b0 = baby + ((size_t)j * 2 + 0) * sz, *b1 = baby + ((size_t)j * 2 + 1) * sz;
+      for (int l = 0; l < L; l++) {
+        u64 q = c->p[q_idx[l]].q;
+        size_t o = (size_t)l * n;
+        orc_ew_mad(q, n, b0 + o, pt + o, s0 + o, s0 + o);
+        orc_ew_mad(q, n, b1 + o, pt + o, s1 + o, s1 + o);
+      }
+    }
+    if (!any) continue;
+    for (int l = 0; l < L; l++) {
+      size_t o = (size_t)l * n;
+      orc_apply_galois_ntt(elts[i], c->logn, s0 + o, r0 + o);
+      orc_apply_galois_ntt(elts[i], c->logn, s1 + o, r1 + o);
+      u64 q = c->p[q_idx[l]].q;
+      orc_ew_add(q, n, ct0_sum + o, r0 + o, ct0_sum + o);
+      if (elts[i] == 1) orc_ew_add(q, n, ct1_zero + o, r1 + o, ct1_zero + o);
+    }
+    if (elts[i] != 1)
+      orc_keyswitch_acc(c, bconv_mode, L, q_idx, K, p_idx, dnum, r1, keys + (size_t)i * dnum * 2 * LK * n, acc0, acc1);
+  }
+  for (int l = 0; l < L; l++) {
+    u64 q = c->p[q_idx[l]].q;
+    u64 pq = prod_mod(c, p_idx, K, q);
+    size_t o = (size_t)l * n;
+    orc_ew_pmu(q, n, acc0 + o, ct0_sum + o, pq, acc0 + o);
+    orc_ew_pmu(q, n, acc1 + o, ct1_zero + o, pq, acc1 + o);
+  }
+  orc_moddown_rescale(c, bconv_mode, round_mode, L, q_idx, K, p_idx, r, acc0, out0);
+  orc_moddown_rescale(c, bconv_mode, round_mode, L, q_idx, K, p_idx, r, acc1, out1);
+  free(acc0); free(acc1); free(ct0_sum); free(ct1_zero); free(s0); free(s1); free(r0); free(r1);
 }
 
 /* n <= 0 leaves the OpenMP default alone */

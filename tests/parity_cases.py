@@ -535,6 +535,84 @@ def case_keyswitch(be, word_bits, L, K, dnum, bconv_mode, round_mode):
     ks.close()
 
 
+def case_keyswitch_rescale(be, word_bits, L, K, dnum, bconv_mode, round_mode):
+    """Key switch with the PMU pre-additions and 1 / 2 rescale levels inside the ModDown, and the
+    HMult that folds its rescale into the relinearisation's ModDown."""
+    prm = small_params(word_bits, L, K, dnum)
+    h = Harness(be, word_bits, prm.moduli)
+    rng = np.random.default_rng(17)
+    c0, c1, evk = make_keyswitch_inputs(rng, prm)
+    a0, a1 = rand_limbs(rng, prm.moduli, prm.q_idx), rand_limbs(rng, prm.moduli, prm.q_idx)
+    ks = _capi.KeySwitch(h.ctx, prm.q_idx, prm.p_idx, dnum, bconv_mode, round_mode)
+    d_c1, d_evk, d_a0, d_a1 = h.up(c1), h.up(evk), h.up(a0), h.up(a1)
+    for r in (0, 1, 2):
+        if L - r < 1:
+            continue
+        o0, o1 = h.new(L - r, N), h.new(L - r, N)
+        ks.apply_rescale(h.p(o0), h.p(o1), h.p(d_c1), h.p(d_evk), r, h.p(d_a0), h.p(d_a1))
+        w0, w1 = h.orc.keyswitch_rescale(bconv_mode, round_mode, prm.q_idx, prm.p_idx, dnum, r, c1, evk, a0, a1)
+        assert np.array_equal(h.down(o0), w0) and np.array_equal(h.down(o1), w1), "key switch with %d rescale levels differs" % r
+        ks.apply_rescale(h.p(o0), h.p(o1), h.p(d_c1), h.p(d_evk), r)          # without pre-additions
+        w0, w1 = h.orc.keyswitch_rescale(bconv_mode, round_mode, prm.q_idx, prm.p_idx, dnum, r, c1, evk)
+        assert np.array_equal(h.down(o0), w0) and np.array_equal(h.down(o1), w1)
+    if L >= 2:
+        d_c0 = h.up(c0)
+        r0, r1 = h.new(L - 1, N), h.new(L - 1, N)
+        ks.hmult(h.p(r0), h.p(r1), h.p(d_c0), h.p(d_c1), h.p(d_a0), h.p(d_a1), h.p(d_evk), 2)
+        w0, w1 = h.orc.hmult_relin_fused(bconv_mode, round_mode, prm.q_idx, prm.p_idx, dnum, c0, c1, a0, a1, evk)
+        assert np.array_equal(h.down(r0), w0) and np.array_equal(h.down(r1), w1), "HMult with the fused rescale differs"
+    ks.close()
+
+
+def case_bsgs(be, word_bits, L, K, dnum, bconv_mode, round_mode, g=3, n_giant=3, r=0, missing=((1, 2),),
+              prm=None, zero_first=True):
+    """cerium_bsgs_apply against the oracle's restatement of the reference lowering: hoisted baby steps,
+    plaintext products summed per giant step, giant-step key switches accumulated in the extended basis,
+    one ModDown (with r rescale levels).  `missing` lists absent diagonals (giant, baby)."""
+    prm = prm or small_params(word_bits, L, K, dnum)
+    L, K, dnum = prm.L, prm.K, prm.dnum
+    h = Harness(be, word_bits, prm.moduli)
+    rng = np.random.default_rng(19)
+    c0, c1, _ = make_keyswitch_inputs(rng, prm)
+    all_idx = prm.q_idx + prm.p_idx
+    key = lambda: np.stack([np.stack([rand_limbs(rng, prm.moduli, all_idx) for _ in range(2)]) for _ in range(dnum)])  # noqa: E731
+    baby_elts = [1] + [be.lib.galois_elt_from_step(j, LOGN) for j in range(1, g)]
+    giant_elts = [1 if (i == 0 and zero_first) else be.lib.galois_elt_from_step(g * i + (0 if zero_first else g), LOGN)
+                  for i in range(n_giant)]
+    baby_keys = [None] + [key() for _ in range(1, g)]
+    giant_keys = [None if e == 1 else key() for e in giant_elts]
+    present = np.ones((n_giant, g), dtype=np.uint8)
+    for (i, j) in missing:
+        if i < n_giant and j < g:
+            present[i, j] = 0
+    pts = np.stack([np.stack([rand_limbs(rng, prm.moduli, prm.q_idx) for _ in range(g)]) for _ in range(n_giant)])
+    # oracle: baby steps as the hoisted rotations define them, then the lowering
+    baby = [np.stack([c0, c1])]
+    for j in range(1, g):
+        k0, k1 = h.orc.keyswitch(bconv_mode, round_mode, prm.q_idx, prm.p_idx, dnum, c1, baby_keys[j])
+        k0 = np.stack([oracle.ew("add", prm.moduli[p], k0[i], c0[i]) for i, p in enumerate(prm.q_idx)])
+        baby.append(np.stack([np.stack([oracle.apply_galois_ntt(baby_elts[j], LOGN, k[i]) for i in range(L)]) for k in (k0, k1)]))
+    zero_key = np.zeros_like(key())
+    w0, w1 = h.orc.bsgs(bconv_mode, round_mode, prm.q_idx, prm.p_idx, dnum, r, np.stack(baby), pts, present, giant_elts,
+                        np.stack([zero_key if k is None else k for k in giant_keys]))
+    # device
+    ks = _capi.KeySwitch(h.ctx, prm.q_idx, prm.p_idx, dnum, bconv_mode, round_mode)
+    d_c0, d_c1 = h.up(c0), h.up(c1)
+    d_pts = [[h.up(pts[i, j]) if present[i, j] else None for j in range(g)] for i in range(n_giant)]
+    d_bk = [None] + [h.up(baby_keys[j]) for j in range(1, g)]    # taken as the pre-permuted keys, as the oracle does above
+    d_gk = [None if k is None else h.up(k) for k in giant_keys]
+    work = h.new(ks.bsgs_work_limbs(g, n_giant), N)
+    o0, o1 = h.new(L - r, N), h.new(L - r, N)
+    for _ in range(2):                                          # twice: the plan's accumulators are reused
+        ks.bsgs_apply(h.p(o0), h.p(o1), h.p(d_c0), h.p(d_c1), g, n_giant,
+                      [h.p(t) if t is not None else 0 for row in d_pts for t in row],
+                      [h.p(t) if t is not None else 0 for t in d_bk], baby_elts,
+                      [h.p(t) if t is not None else 0 for t in d_gk], giant_elts, r, h.p(work))
+        assert np.array_equal(h.down(o0), w0), "BSGS c0 differs"
+        assert np.array_equal(h.down(o1), w1), "BSGS c1 differs"
+    ks.close()
+
+
 def case_errors(be, word_bits=64):
     """Error behaviour of the boundary: status codes and messages instead of exceptions or faults."""
     import pytest

@@ -77,6 +77,22 @@ def test_keyswitch_hrot_hmult(be, word_bits, L, K, dnum, bm, rm):
     pc.case_keyswitch(be, word_bits, L, K, dnum, bm, rm)
 
 
+@pytest.mark.parametrize("word_bits,L,K,dnum,bm,rm", [
+    (64, 4, 2, 2, _capi.BCONV_EXACT, _capi.ROUND_HALF),
+    (32, 3, 1, 3, _capi.BCONV_LAZY, _capi.ROUND_FLOOR),
+])
+def test_keyswitch_with_fused_rescale(be, word_bits, L, K, dnum, bm, rm):
+    pc.case_keyswitch_rescale(be, word_bits, L, K, dnum, bm, rm)
+
+
+@pytest.mark.parametrize("word_bits,L,K,dnum,bm,rm,g,n_giant,r", [
+    (64, 3, 2, 2, _capi.BCONV_EXACT, _capi.ROUND_HALF, 2, 2, 0),
+    (32, 3, 1, 3, _capi.BCONV_LAZY, _capi.ROUND_FLOOR, 2, 3, 1),
+])
+def test_bsgs(be, word_bits, L, K, dnum, bm, rm, g, n_giant, r):
+    pc.case_bsgs(be, word_bits, L, K, dnum, bm, rm, g=g, n_giant=n_giant, r=r, missing=((1, 1),))
+
+
 @pytest.mark.parametrize("word_bits,bm,rm", [(64, _capi.BCONV_EXACT, _capi.ROUND_HALF), (32, _capi.BCONV_LAZY, _capi.ROUND_FLOOR)])
 def test_mod_raise(be, word_bits, bm, rm):
     pc.case_mod_raise(be, word_bits, bm, rm)

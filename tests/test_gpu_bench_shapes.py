@@ -82,8 +82,20 @@ def test_hmult_bench_shape(be):
     w0, w1 = h.orc.hmult_relin(BM, RM, True, prm.q_idx, prm.p_idx, prm.dnum, a0, a1, b0, b1, evk)
     assert np.array_equal(h.down(r0), w0), "HMult+relin+rescale c0 differs at L=24, dnum=24"
     assert np.array_equal(h.down(r1), w1), "HMult+relin+rescale c1 differs at L=24, dnum=24"
+    # the rescale folded into the relinearisation's ModDown: one division by P * q_last
+    ks.hmult(h.p(r0), h.p(r1), h.p(da0), h.p(da1), h.p(db0), h.p(db1), h.p(dk), 2)
+    w0, w1 = h.orc.hmult_relin_fused(BM, RM, prm.q_idx, prm.p_idx, prm.dnum, a0, a1, b0, b1, evk)
+    assert np.array_equal(h.down(r0), w0) and np.array_equal(h.down(r1), w1), "HMult with the fused rescale differs at L=24"
     o0, o1 = h.new(prm.L, pc.N), h.new(prm.L, pc.N)
     ks.hmult(h.p(o0), h.p(o1), h.p(da0), h.p(da1), h.p(db0), h.p(db1), h.p(dk), False)
     w0, w1 = h.orc.hmult_relin(BM, RM, False, prm.q_idx, prm.p_idx, prm.dnum, a0, a1, b0, b1, evk)
     assert np.array_equal(h.down(o0), w0) and np.array_equal(h.down(o1), w1), "HMult+relin differs at L=24"
     ks.close()
+
+
+def test_bsgs_bench_shape(be):
+    """A 3 x 3 multiply-accumulate (one absent diagonal) and a 2 x 5 one with two rescale levels at the
+    HRot parameter set."""
+    prm = params.config_hrot(pc.LOGN, 35, 5, 7)
+    pc.case_bsgs(be, 64, 35, 5, 7, BM, RM, g=3, n_giant=3, r=0, prm=prm)
+    pc.case_bsgs(be, 64, 35, 5, 7, BM, RM, g=2, n_giant=5, r=2, missing=(), prm=prm)

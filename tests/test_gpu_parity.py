@@ -82,6 +82,31 @@ def test_keyswitch_hrot_hmult(be, word_bits, L, K, dnum, bm, rm):
     pc.case_keyswitch(be, word_bits, L, K, dnum, bm, rm)
 
 
+@pytest.mark.parametrize("word_bits,L,K,dnum,bm,rm", [
+    (64, 7, 3, 3, _capi.BCONV_EXACT, _capi.ROUND_HALF),
+    (64, 6, 1, 6, _capi.BCONV_EXACT, _capi.ROUND_HALF),
+    (64, 9, 3, 3, _capi.BCONV_LAZY, _capi.ROUND_FLOOR),
+    (32, 8, 4, 2, _capi.BCONV_LAZY, _capi.ROUND_FLOOR),
+    (32, 6, 2, 3, _capi.BCONV_EXACT, _capi.ROUND_HALF),
+])
+def test_keyswitch_with_fused_rescale(be, word_bits, L, K, dnum, bm, rm):
+    pc.case_keyswitch_rescale(be, word_bits, L, K, dnum, bm, rm)
+
+
+@pytest.mark.parametrize("word_bits,L,K,dnum,bm,rm,g,n_giant,r", [
+    (64, 7, 3, 3, _capi.BCONV_EXACT, _capi.ROUND_HALF, 3, 3, 0),
+    (64, 7, 3, 3, _capi.BCONV_EXACT, _capi.ROUND_HALF, 4, 6, 2),     # two groups of giant steps, double rescale level
+    (64, 5, 2, 3, _capi.BCONV_LAZY, _capi.ROUND_FLOOR, 1, 3, 1),     # no baby rotation at all
+    (32, 8, 4, 2, _capi.BCONV_LAZY, _capi.ROUND_FLOOR, 3, 5, 1),
+])
+def test_bsgs(be, word_bits, L, K, dnum, bm, rm, g, n_giant, r):
+    pc.case_bsgs(be, word_bits, L, K, dnum, bm, rm, g=g, n_giant=n_giant, r=r)
+
+
+def test_bsgs_every_giant_step_rotated(be):
+    pc.case_bsgs(be, 64, 5, 2, 3, _capi.BCONV_EXACT, _capi.ROUND_HALF, g=2, n_giant=2, r=0, missing=(), zero_first=False)
+
+
 @pytest.mark.parametrize("word_bits,bm,rm", [(64, _capi.BCONV_EXACT, _capi.ROUND_HALF), (64, _capi.BCONV_LAZY, _capi.ROUND_FLOOR), (32, _capi.BCONV_LAZY, _capi.ROUND_FLOOR)])
 def test_mod_raise(be, word_bits, bm, rm):
     pc.case_mod_raise(be, word_bits, bm, rm)

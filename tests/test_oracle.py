@@ -133,6 +133,81 @@ def test_moddown_vs_bigint_division(round_mode):
         assert [int(v) for v in got[:, c]] in cands
 
 
+@pytest.mark.parametrize("round_mode", [oracle.ROUND_FLOOR, oracle.ROUND_HALF])
+@pytest.mark.parametrize("r", [1, 2])
+def test_moddown_with_fused_rescale_vs_bigint_division(round_mode, r):
+    """ModDown with r rescale levels is ONE division by P * q_{L-r} ... q_{L-1}: the dropped Q limbs join
+    the extension limbs (cerium/compiler/backend/compiler_keyswitch.cc:26-39, 402-412)."""
+    logn = 4
+    n = 1 << logn
+    q = params.ntt_primes_below(50, 4, logn)
+    p = params.ntt_primes_below(60, 2, logn)
+    ctx = oracle.OracleContext(logn, q + p)
+    rng = np.random.default_rng(70 + r)
+    QP = 1
+    for m in q + p:
+        QP *= m
+    D = p[0] * p[1]
+    for m in q[4 - r:]:
+        D *= m
+    T = [int.from_bytes(rng.bytes(40), "little") % QP for _ in range(n)]
+    coeffs = np.array([[t % m for t in T] for m in q + p], dtype=np.uint64)
+    ntt = ctx.ntt_forward(coeffs, list(range(6)))
+    keep = list(range(4 - r))
+    out = ctx.moddown_rescale(oracle.BCONV_EXACT, round_mode, [0, 1, 2, 3], [4, 5], r, ntt)
+    got = ctx.ntt_inverse(out, keep)
+    for c in range(n):
+        want = (T[c] + D // 2) // D if round_mode == oracle.ROUND_HALF else T[c] // D
+        cands = [[(want - u) % q[i] for i in keep] for u in range(2 + r + 1)]
+        assert [int(v) for v in got[:, c]] in cands
+    # r = 0 is the plain ModDown
+    assert np.array_equal(ctx.moddown_rescale(oracle.BCONV_EXACT, round_mode, [0, 1, 2, 3], [4, 5], 0, ntt),
+                          ctx.moddown(oracle.BCONV_EXACT, round_mode, [0, 1, 2, 3], [4, 5], ntt[:4], ntt[4:]))
+
+
+def test_keyswitch_rescale_and_bsgs_compose_from_pinned_parts():
+    """The fused entries are compositions of pinned parts: with r = 0 the key switch with PMU additions
+    equals key switch + additions; the BSGS accumulation equals, before its single ModDown, the sum
+    of the giant steps' extended-basis key switches (linearity), so with r = 0 and exact division it
+    differs from the sum of separately divided rotations by at most the rounding of each division."""
+    logn = 4
+    n = 1 << logn
+    L, K, dnum = 4, 2, 2
+    q = params.ntt_primes_below(50, L, logn)
+    p = params.ntt_primes_below(60, K, logn)
+    mods = q + p
+    ctx = oracle.OracleContext(logn, mods)
+    rng = np.random.default_rng(81)
+    q_idx, p_idx = list(range(L)), list(range(L, L + K))
+    rl = lambda idx: np.stack([rng.integers(0, mods[i], size=n, dtype=np.uint64) for i in idx])  # noqa: E731
+    c, a0, a1 = rl(q_idx), rl(q_idx), rl(q_idx)
+    evk = np.stack([np.stack([rl(q_idx + p_idx) for _ in range(2)]) for _ in range(dnum)])
+    k0, k1 = ctx.keyswitch(1, 1, q_idx, p_idx, dnum, c, evk)
+    f0, f1 = ctx.keyswitch_rescale(1, 1, q_idx, p_idx, dnum, 0, c, evk, a0, a1)
+    for i in range(L):
+        assert np.array_equal(f0[i], oracle.ew("add", mods[i], k0[i], a0[i]))
+        assert np.array_equal(f1[i], oracle.ew("add", mods[i], k1[i], a1[i]))
+    # one giant step without rotation and one with: compare with the explicit composition
+    g, n_giant = 2, 2
+    baby = np.stack([np.stack([rl(q_idx), rl(q_idx)]) for _ in range(g)])
+    pts = np.stack([np.stack([rl(q_idx) for _ in range(g)]) for _ in range(n_giant)])
+    elt = oracle.galois_elt_from_step(2, logn)
+    keys = np.stack([evk, np.stack([np.stack([rl(q_idx + p_idx) for _ in range(2)]) for _ in range(dnum)])])
+    o0, o1 = ctx.bsgs(1, 0, q_idx, p_idx, dnum, 0, baby, pts, np.ones((n_giant, g)), [1, elt], keys)
+
+    def inner(i, poly):
+        s = np.zeros((L, n), dtype=np.uint64)
+        for j in range(g):
+            s = np.stack([oracle.ew("mad", mods[l], baby[j, poly, l], pts[i, j, l], s[l]) for l in range(L)])
+        return s
+    s00, s01, s10, s11 = inner(0, 0), inner(0, 1), inner(1, 0), inner(1, 1)
+    r10 = np.stack([oracle.apply_galois_ntt(elt, logn, s10[l]) for l in range(L)])
+    r11 = np.stack([oracle.apply_galois_ntt(elt, logn, s11[l]) for l in range(L)])
+    add0 = np.stack([oracle.ew("add", mods[l], s00[l], r10[l]) for l in range(L)])
+    w0, w1 = ctx.keyswitch_rescale(1, 0, q_idx, p_idx, dnum, 0, r11, keys[1], add0, s01)
+    assert np.array_equal(o0, w0) and np.array_equal(o1, w1)
+
+
 def test_rescale_vs_bigint_division():
     logn = 4
     n = 1 << logn
