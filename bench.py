@@ -842,7 +842,7 @@ def main():
                          "ranks, NCCL all-gathers where limbs must meet, several operations in flight; 'replica' runs "
                          "independent ciphertexts per rank with no collective")
     ap.add_argument("--inflight", type=int, default=None,
-                    help="independent operations in flight per rank, each on its own plan and stream (hrot; default 1 "
+                    help="independent operations in flight per rank, each on its own plan and stream (hrot; default 2 "
                          "on one GPU, 4 limb-sharded)")
     ap.add_argument("--ext", choices=["split", "replicated"], default="split",
                     help="limb-sharded: extension limbs split over the ranks, or replicated on every rank")
@@ -879,7 +879,9 @@ def main():
                  inflight=max(1, args.inflight if args.inflight is not None else 4))
     else:
         if args.workload == "hrot":
-            wl.setup(lib, torch, rank, world, False, inflight=max(1, args.inflight if args.inflight is not None else 1))
+            # replicas (N > 1, --parallelism replica) run one operation at a time; one GPU runs two
+            wl.setup(lib, torch, rank, world, False,
+                     inflight=max(1, args.inflight if args.inflight is not None else (2 if world == 1 else 1)))
         else:
             wl.setup(lib, torch, rank, world, False)
     ops = wl.ops_per_step
@@ -923,8 +925,15 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
     probe = probe_int_pipe(local_rank) if rank == 0 else None
 
-    # N > 1: the other parallelism beside the headline, and the collectives of one sharded operation alone
+    # latency of ONE operation (nothing else in flight) beside the throughput of several
     side = {}
+    if getattr(wl, "inflight", 1) > 1 and args.workload == "hrot":
+        keep = wl.inflight
+        wl.inflight = 1
+        lsteps = max(5, min(args.steps, 200))
+        side["latency_ms_one_op_in_flight"] = time_blocks(torch, dist, world, wl, lsteps, 1, barrier)[0] / lsteps
+        wl.inflight = keep
+    # N > 1: the other parallelism beside the headline, and the collectives of one sharded operation alone
     if sharded:
         for _ in range(5):
             wl.collective_step()
@@ -938,13 +947,6 @@ def main():
         t = torch.tensor([c0.elapsed_time(c1) / 50], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         side["collective_ms_per_op"] = float(t.item())
-        # latency of ONE operation (nothing else in flight)
-        wl1 = wl
-        keep = wl1.inflight
-        wl1.inflight = 1
-        lat = time_blocks(torch, dist, world, wl1, max(5, min(args.steps, 200)), 1, barrier)[0] / max(5, min(args.steps, 200))
-        wl1.inflight = keep
-        side["latency_ms_one_op_in_flight"] = lat
         # replicas: independent ciphertexts per GPU, no collective (weak scaling by construction)
         wr = WORKLOADS["hrot"]()
         wr.setup(lib, torch, rank, world, False)

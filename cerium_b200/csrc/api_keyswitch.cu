@@ -1101,7 +1101,7 @@ int cerium_bsgs_apply(cerium_keyswitch* ks, void* out0, void* out1, const void* 
         }
       }
       for (int b = 0; b < L; b++) a.prime[b] = (uint8_t)ks->q_idx[b];
-      const dim3 grid(kN / (kEwThreads * V::kLanes), L);
+      const dim3 grid(kN / (kEwThreads * PtMacLanes<W>::kWords), L);
       switch (cnt) {
         case 1: { auto kfn = pt_mac_kernel<W, 1>; CERIUM_LAUNCH(kfn, grid, kEwThreads, 0, st, a, pcs); } break;
         case 2: { auto kfn = pt_mac_kernel<W, 2>; CERIUM_LAUNCH(kfn, grid, kEwThreads, 0, st, a, pcs); } break;

@@ -27,47 +27,79 @@ struct PtMacArgs {
   uint8_t prime[kEwMaxLimbs];
 };
 
-// out[i][p] = sum_j pt[i][j] * src_p[j] for the GI giant steps of a group.  grid = (N / (256 * lanes), limbs).
+// One thread owns kPtMacWords consecutive words of a limb: one 8-byte access per operand for both word
+// sizes (a warp still moves whole 256-byte runs).  Wider accesses would double the accumulator
+// registers: with four giant steps, two polynomials and two-word sums that costs the occupancy a
+// streaming kernel lives on (136 registers and one CTA per SM when measured with 16-byte accesses).
+template <typename W>
+struct PtMacLanes {
+  static constexpr int kWords = 8 / sizeof(W);
+};
+template <typename W>
+__device__ __forceinline__ void ptmac_load(const W* p, W (&v)[PtMacLanes<W>::kWords]) {
+  if constexpr (sizeof(W) == 8) {
+    v[0] = __ldg(p);
+  } else {
+    const uint2 t = __ldg(reinterpret_cast<const uint2*>(p));
+    v[0] = t.x;
+    v[1] = t.y;
+  }
+}
+template <typename W>
+__device__ __forceinline__ void ptmac_store(W* p, const W (&v)[PtMacLanes<W>::kWords]) {
+  if constexpr (sizeof(W) == 8) {
+    *p = v[0];
+  } else {
+    *reinterpret_cast<uint2*>(p) = make_uint2(v[0], v[1]);
+  }
+}
+
+// out[i][p] = sum_j pt[i][j] * src_p[j] for the GI giant steps of a group.
+// grid = (N / (256 * kWords), limbs).
 template <typename W, int GI>
-__global__ void __launch_bounds__(kEwThreads) pt_mac_kernel(const PtMacArgs<W> a, const PrimeConst<W>* __restrict__ pcs) {
+__global__ void __launch_bounds__(kEwThreads, 3) pt_mac_kernel(const PtMacArgs<W> a, const PrimeConst<W>* __restrict__ pcs) {
   grid_dependency_launch();
   grid_dependency_wait();
-  using V = Vec16<W>;
+  constexpr int kWords = PtMacLanes<W>::kWords;
   const int b = blockIdx.y;
   const PrimeConst<W> pc = pcs[a.prime[b]];
-  const size_t off = (size_t)b * kN + (size_t)(blockIdx.x * kEwThreads + threadIdx.x) * V::kLanes;
-  Acc2<W> acc[GI][2][V::kLanes];
+  const size_t off = (size_t)b * kN + (size_t)(blockIdx.x * kEwThreads + threadIdx.x) * kWords;
+  Acc2<W> acc[GI][2][kWords];
 #pragma unroll
   for (int i = 0; i < GI; i++)
 #pragma unroll
-    for (int l = 0; l < V::kLanes; l++) {
+    for (int l = 0; l < kWords; l++) {
       acc[i][0][l].clear();
       acc[i][1][l].clear();
     }
+#pragma unroll 2
   for (int j = 0; j < a.g; j++) {
-    const V s0 = V::load(a.src0[j] + off), s1 = V::load(a.src1[j] + off);
+    W s0[kWords], s1[kWords];
+    ptmac_load<W>(a.src0[j] + off, s0);
+    ptmac_load<W>(a.src1[j] + off, s1);
 #pragma unroll
     for (int i = 0; i < GI; i++) {
       const W* pp = a.pt[i][j];
       if (pp == nullptr) continue;
-      const V p = V::load(pp + off);
+      W p[kWords];
+      ptmac_load<W>(pp + off, p);
 #pragma unroll
-      for (int l = 0; l < V::kLanes; l++) {
-        acc[i][0][l].mad(s0.v[l], p.v[l]);
-        acc[i][1][l].mad(s1.v[l], p.v[l]);
+      for (int l = 0; l < kWords; l++) {
+        acc[i][0][l].mad(s0[l], p[l]);
+        acc[i][1][l].mad(s1[l], p[l]);
       }
     }
   }
 #pragma unroll
   for (int i = 0; i < GI; i++) {
-    V o0, o1;
+    W o0[kWords], o1[kWords];
 #pragma unroll
-    for (int l = 0; l < V::kLanes; l++) {
-      o0.v[l] = barrett2<W>(acc[i][0][l].hi(), acc[i][0][l].lo(), pc);
-      o1.v[l] = barrett2<W>(acc[i][1][l].hi(), acc[i][1][l].lo(), pc);
+    for (int l = 0; l < kWords; l++) {
+      o0[l] = barrett2<W>(acc[i][0][l].hi(), acc[i][0][l].lo(), pc);
+      o1[l] = barrett2<W>(acc[i][1][l].hi(), acc[i][1][l].lo(), pc);
     }
-    o0.store(a.out0[i] + off);
-    o1.store(a.out1[i] + off);
+    ptmac_store<W>(a.out0[i] + off, o0);
+    ptmac_store<W>(a.out1[i] + off, o1);
   }
 }
 
