@@ -99,6 +99,12 @@ SIGNATURES = {
     "cerium_double_rescale": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32), C.c_int, C.c_int,
                                         C.c_void_p, C.c_void_p]),
     "cerium_rescale_static": (C.c_int, [_vp, C.c_int, _vp, _vp, _u32p, C.c_int, C.c_int, _vp]),
+    "cerium_program_load": (C.c_int, [_vp, C.POINTER(_vp), C.c_char_p, C.c_char_p, C.POINTER(C.c_char_p), _u64p, C.c_int, _vp]),
+    "cerium_program_destroy": (C.c_int, [_vp]),
+    "cerium_program_num_steps": (C.c_int, [_vp]),
+    "cerium_program_memory": (C.c_int, [_vp, C.c_char_p, C.POINTER(_vp)]),
+    "cerium_program_run": (C.c_int, [_vp, _vp]),
+    "cerium_program_inspect": (C.c_int, [C.c_char_p, C.c_char_p, _sz, C.POINTER(C.c_int)]),
 }
 
 
@@ -342,6 +348,59 @@ class Comm:
         if getattr(self, "h", None):
             self.lib.dll.cerium_comm_destroy(self.h)
             self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def inspect_program(lib: Library, functions_path: str):
+    """Parses a compiled function's kernel stream (no device): list of dicts, one per record."""
+    n = C.c_int()
+    buf = C.create_string_buffer(1 << 20)
+    lib.check(lib.dll.cerium_program_inspect(functions_path.encode(), buf, len(buf), C.byref(n)))
+    keys = ("id", "type", "outputs", "inputs", "bases", "rots", "units", "sud", "pmu")
+    out = []
+    for line in buf.value.decode().splitlines():
+        f = line.split()
+        out.append({k: (v if k == "type" else int(v)) for k, v in zip(keys, f)})
+    assert len(out) == n.value
+    return out
+
+
+class Program:
+    """One partition of a compiled Cerium function, loaded for replay (handle of ``cerium_program``)."""
+
+    def __init__(self, ctx: Context, functions_path: str, plugin_path: str, scalars: Optional[dict] = None,
+                 comm: Optional["Comm"] = None):
+        self.ctx, self.comm = ctx, comm
+        scalars = scalars or {}
+        names = (C.c_char_p * max(1, len(scalars)))(*[k.encode() for k in scalars])
+        vals = _u64(list(scalars.values()) or [0])
+        h = _vp()
+        ctx.lib.check(ctx.lib.dll.cerium_program_load(ctx.h, C.byref(h), functions_path.encode(), plugin_path.encode(),
+                                                      names, vals, len(scalars), comm.h if comm is not None else None))
+        self.h = h
+
+    @property
+    def num_steps(self) -> int:
+        return int(self.ctx.lib.dll.cerium_program_num_steps(self.h))
+
+    def memory(self, term: str) -> int:
+        """Device address of a named memory term such as "i1(0)" (one limb)."""
+        p = _vp()
+        self.ctx.lib.check(self.ctx.lib.dll.cerium_program_memory(self.h, term.encode(), C.byref(p)))
+        return int(p.value)
+
+    def run(self, stream: int = 0):
+        self.ctx.lib.check(self.ctx.lib.dll.cerium_program_run(self.h, stream))
+
+    def close(self):
+        if getattr(self, "h", None) and self.ctx.h:
+            self.ctx.lib.dll.cerium_program_destroy(self.h)
+        self.h = None
 
     def __del__(self):
         try:

@@ -1,0 +1,684 @@
+// Executor of a compiled Cerium function: reads the compiler's kernel stream (the `ll.functions` /
+// `functions<p>` records written by FusedKernel::write_instruction,
+// cerium/compiler/backend/cuda_kernel.cc:1707-1916), builds the argument tables of every record once
+// and replays the records in order on a CUDA stream, calling the launchers of the function's kernel
+// plugin by kernel id - the stream mode of the reference runtime:
+//   record parser                 FunctionMetaData          cerium/runtime/execution/function.h:269-347
+//   term resolution               get_pointer_from_term     cerium/runtime/execution/function.cpp:464-503
+//   base-conversion units         DeviceBaseConverter       cerium/runtime/execution/evaluator.cpp:1483-1608
+//   SuD / PMU factors             compute_{sud,pmu}_factors cerium/runtime/execution/function.cpp:685-755
+//   argument tables per record    make_program's build loop cerium/runtime/execution/function_execution.cpp:124-360
+//   replay                        run_program_multithread_threadfn  function_execution.cpp:437-611
+// With the plugin shim of this library installed as function_map_<p>.so the ntt / int / sud / bco
+// records run on this library's kernels and the generic / pmu records on the launchers the compiler
+// generated for the program (kept as function_map_<p>.orig.so): a compiled program runs unchanged.
+// One process drives one partition (the reference runs one host thread per partition).
+//
+// Differences from the reference: records are addressed by field name, not by line number; register
+// file and base-conversion buffers are sized from what the records use; mov records (no-ops in the
+// reference's runtime too) are dropped; the modulus / Barrett / rotation tables the generated
+// element-wise launchers expect are built here in the reference's layout (EvaluatorContext,
+// evaluator.cpp:58-92, 233-260), since they are part of that launcher contract.  A drm record (the
+// all-gather of limbs between partitions, Evaluator::drm, evaluator.cpp:1154-1251) runs on the
+// communicator given at load: its sources are packed into this rank's block of a staging buffer,
+// gathered in place, and unpacked to the record's destinations.  Not served: rsv, call, ags and ard
+// records - a function that holds one is refused at load.
+#include <cstring>
+#include <fstream>
+#include <map>
+#include <sstream>
+#include <stdexcept>
+#include <unordered_map>
+
+#include "internal.h"
+
+#if !defined(CERIUM_EMU)
+#include <dlfcn.h>
+#endif
+
+using namespace cerium;
+
+namespace {
+
+struct Term {
+  enum Type { Reg, Bcu, Mem, Arg, Zero } type = Mem;
+  std::string s;  // without the "[X]" (dead after this use) mark
+};
+
+struct Record {
+  uint32_t id = 0;
+  std::string type;
+  std::vector<Term> outputs, inputs, scalars, remapables, comm_srcs, comm_dests;
+  size_t comm_size = 0, comm_num_limbs = 0;
+  std::string base_conv;
+  std::vector<int32_t> rots;
+  std::vector<uint32_t> sud, pmu, rsv, bases;
+};
+
+std::string strip(const std::string& v) {
+  std::string o;
+  for (char c : v)
+    if (c != ' ' && c != '\t' && c != '\r' && c != '\n') o += c;
+  return o;
+}
+
+std::vector<std::string> csv(const std::string& v) {
+  std::vector<std::string> out;
+  std::string cur;
+  for (char c : strip(v)) {
+    if (c == ',') {
+      if (!cur.empty()) out.push_back(cur);
+      cur.clear();
+    } else {
+      cur += c;
+    }
+  }
+  if (!cur.empty()) out.push_back(cur);
+  return out;
+}
+
+Term make_term(std::string s) {
+  Term t;
+  const size_t dead = s.find("[X]");
+  if (dead != std::string::npos) s.erase(dead);
+  t.s = s;
+  // the first character decides (function.cpp:236-255)
+  switch (s.empty() ? ' ' : s[0]) {
+    case 'b': t.type = Term::Bcu; break;
+    case 'r': t.type = Term::Reg; break;
+    case 'f': t.type = Term::Arg; break;
+    case 'Z': t.type = Term::Zero; break;
+    default: t.type = Term::Mem; break;
+  }
+  return t;
+}
+
+std::vector<Term> terms(const std::string& v) {
+  std::vector<Term> out;
+  for (const std::string& s : csv(v)) out.push_back(make_term(s));
+  return out;
+}
+
+template <typename T>
+std::vector<T> numbers(const std::string& v) {
+  std::vector<T> out;
+  for (const std::string& s : csv(v)) out.push_back((T)std::stol(s));
+  return out;
+}
+
+// Records are '}'-delimited; every field is a ".name: value" line.
+bool parse_records(const std::string& path, std::vector<Record>& out, std::string& err) {
+  std::ifstream f(path);
+  if (!f.is_open()) {
+    err = "cannot open " + path;
+    return false;
+  }
+  std::string text;
+  while (std::getline(f, text, '}')) {
+    std::istringstream lines(text);
+    std::string line;
+    Record r;
+    bool any = false;
+    std::map<std::string, std::string> field;
+    while (std::getline(lines, line)) {
+      const size_t a = line.find_first_not_of(" \t");
+      if (a == std::string::npos || line[a] != '.') continue;
+      const size_t colon = line.find(':', a);
+      if (colon == std::string::npos) continue;
+      field[line.substr(a + 1, colon - a - 1)] = line.substr(colon + 1);
+      any = true;
+    }
+    if (!any) continue;
+    try {
+      if (!field.count("id") || !field.count("type")) throw std::runtime_error("record without .id / .type");
+      r.id = (uint32_t)std::stoul(strip(field["id"]));
+      r.type = strip(field["type"]);
+      r.outputs = terms(field["outputs"]);
+      r.inputs = terms(field["inputs"]);
+      r.scalars = terms(field["scalars"]);
+      r.remapables = terms(field["reamapables"]);  // sic: the producer's spelling
+      r.base_conv = field["base_conv"];
+      r.rots = numbers<int32_t>(field["rots"]);
+      r.sud = numbers<uint32_t>(field["sud"]);
+      r.pmu = numbers<uint32_t>(field["pmu"]);
+      r.rsv = numbers<uint32_t>(field["rsv"]);
+      r.bases = numbers<uint32_t>(field["bases"]);
+      r.comm_srcs = terms(field["comm_srcs"]);
+      r.comm_dests = terms(field["comm_dests"]);
+      if (!strip(field["comm_size"]).empty()) r.comm_size = std::stoul(strip(field["comm_size"]));
+      if (!strip(field["comm_num_limbs"]).empty()) r.comm_num_limbs = std::stoul(strip(field["comm_num_limbs"]));
+    } catch (const std::exception& e) {
+      err = "bad record in " + path + ": " + e.what();
+      return false;
+    }
+    out.push_back(std::move(r));
+  }
+  return true;
+}
+
+// "<b0: 0, 1, : 52, 53, ><b1: ...>" -> per unit: index, first list, second list
+struct BcuSpec {
+  int unit;
+  std::vector<uint32_t> first, second;
+};
+std::vector<BcuSpec> parse_base_conv(const std::string& v) {
+  std::vector<BcuSpec> out;
+  std::string s = strip(v);
+  size_t pos = 0;
+  while ((pos = s.find('<', pos)) != std::string::npos) {
+    const size_t end = s.find('>', pos);
+    if (end == std::string::npos) break;
+    std::string body = s.substr(pos + 1, end - pos - 1);
+    pos = end + 1;
+    if (body.size() < 2 || body[0] != 'b') continue;
+    std::vector<std::string> parts;
+    size_t a = 0, c;
+    while ((c = body.find(':', a)) != std::string::npos) {
+      parts.push_back(body.substr(a, c - a));
+      a = c + 1;
+    }
+    parts.push_back(body.substr(a));
+    BcuSpec b;
+    b.unit = std::stoi(parts[0].substr(1));
+    if (parts.size() > 1) b.first = numbers<uint32_t>(parts[1]);
+    if (parts.size() > 2) b.second = numbers<uint32_t>(parts[2]);
+    out.push_back(b);
+  }
+  return out;
+}
+
+}  // namespace
+
+#if !defined(CERIUM_EMU)
+
+namespace {
+
+using W = uint32_t;  // the reference's limb word; compiled programs exist for 32-bit contexts only
+using FunctionMapType = std::unordered_map<uint32_t, void*>;
+
+// launcher signatures of the plugin contract (cerium/runtime/execution/device_utils.cu:33-77)
+typedef void (*ewi_fn)(cudaStream_t&, W**, const W**, const W*, const W**, const size_t*, const uint32_t*, const W*,
+                       const W*, const uint32_t*, const uint32_t**);
+typedef void (*ntt_fn)(cudaStream_t&, W**, const W**, const uint32_t*, const size_t, const W*, const uint2*);
+typedef void (*sud_fn)(cudaStream_t&, W**, const W**, const uint32_t*, const size_t, const W*, const uint2*, const W*,
+                       const W*, const uint32_t*);
+typedef void (*bco_fn)(cudaStream_t&, W**, const size_t*, const W**, const size_t*, const W**, const W**, const W**,
+                       const W**, const size_t, const size_t);
+
+struct Unit {  // one base-conversion unit: input block, output block, the bases they hold right now
+  std::vector<uint32_t> in_ids, out_ids;
+  W* in_buf = nullptr;
+  W* out_buf = nullptr;
+};
+constexpr int kUnitMaxIn = 48, kUnitMaxOut = 64;  // DeviceBaseConverter's block sizes (evaluator.h:36-38)
+
+struct Step {
+  enum Kind { Ewi, Ntt, Int, Sud, Bco, Drm } kind;
+  // drm: host lists of the limbs to pack (this rank's sources) and to unpack (every rank's block)
+  std::vector<const W*> pack;
+  std::vector<W*> unpack;
+  W* staging = nullptr;
+  size_t comm_limbs = 0;
+  void* fn = nullptr;
+  uint32_t id = 0;
+  // device tables (owned by the program's arena)
+  W** outs = nullptr;
+  const W** ins = nullptr;
+  const W* scalars = nullptr;
+  const uint32_t* bases = nullptr;
+  size_t n_bases = 0;
+  const uint32_t** rotmaps = nullptr;
+  const W* sud_factors = nullptr;
+  // bco
+  const size_t *n_out = nullptr, *n_in = nullptr;
+  const W** factors = nullptr;
+  const W** out_moduli = nullptr;
+  const W** ratios = nullptr;
+  const W** ks = nullptr;
+  size_t smem = 0, count = 0;
+};
+
+}  // namespace
+
+struct cerium_program {
+  cerium_context* ctx = nullptr;
+  cerium_comm* comm = nullptr;
+  void* plugin = nullptr;
+  std::vector<Step> steps;
+  std::vector<void*> allocs;                          // everything cudaMalloc'ed for this program
+  W* regs = nullptr;
+  std::map<std::string, W*> memory;                    // named program memory, one limb per term
+  std::map<int, Unit> units;
+  std::map<uint32_t, const uint32_t*> rot_tables;      // Galois element -> device inverse table
+  const W *d_moduli = nullptr, *d_ratios = nullptr;
+  const uint32_t* d_k = nullptr;
+};
+
+namespace {
+
+struct Loader {
+  cerium_program* p;
+  cerium_context* ctx;
+  std::string err;
+
+  void* dev_alloc(size_t bytes) {
+    void* d = nullptr;
+    if (cudaMalloc(&d, bytes ? bytes : 16) != cudaSuccess) throw std::runtime_error("cudaMalloc failed");
+    p->allocs.push_back(d);
+    return d;
+  }
+  template <typename T>
+  T* upload(const std::vector<T>& v) {
+    T* d = static_cast<T*>(dev_alloc(v.size() * sizeof(T)));
+    if (!v.empty() && cudaMemcpy(d, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice) != cudaSuccess)
+      throw std::runtime_error("cudaMemcpy failed");
+    return d;
+  }
+  W* limb_alloc(size_t limbs) {
+    W* d = static_cast<W*>(dev_alloc(limbs * kN * sizeof(W)));
+    if (cudaMemset(d, 0, limbs * kN * sizeof(W)) != cudaSuccess) throw std::runtime_error("cudaMemset failed");
+    return d;
+  }
+
+  Unit& unit(int k) {
+    auto it = p->units.find(k);
+    if (it != p->units.end()) return it->second;
+    Unit u;
+    u.in_buf = limb_alloc(kUnitMaxIn);
+    u.out_buf = limb_alloc(kUnitMaxOut);
+    return p->units.emplace(k, u).first->second;
+  }
+
+  // DeviceBaseConverter::get_pointer: the inputs first, then the outputs
+  W* unit_pointer(int k, uint32_t base) {
+    Unit& u = unit(k);
+    for (size_t i = 0; i < u.in_ids.size(); i++)
+      if (u.in_ids[i] == base) return u.in_buf + i * kN;
+    for (size_t i = 0; i < u.out_ids.size(); i++)
+      if (u.out_ids[i] == base) return u.out_buf + i * kN;
+    throw std::runtime_error("base-conversion unit b" + std::to_string(k) + " holds no limb of prime " + std::to_string(base));
+  }
+
+  W* pointer(const Term& t) {
+    switch (t.type) {
+      case Term::Zero: return nullptr;
+      case Term::Reg: return p->regs + (size_t)std::stoul(t.s.substr(1)) * kN;
+      case Term::Bcu: {
+        const size_t l = t.s.find('('), r = t.s.find(')');
+        if (l == std::string::npos || r == std::string::npos) throw std::runtime_error("bad unit term " + t.s);
+        return unit_pointer(std::stoi(t.s.substr(1, l - 1)), (uint32_t)std::stoul(t.s.substr(l + 1, r - l - 1)));
+      }
+      default: {  // named program memory (and function arguments, which a single function treats alike)
+        auto it = p->memory.find(t.s);
+        if (it != p->memory.end()) return it->second;
+        W* d = limb_alloc(1);
+        p->memory[t.s] = d;
+        return d;
+      }
+    }
+  }
+
+  std::vector<W*> pointers(const std::vector<Term>& ts) {
+    std::vector<W*> v;
+    for (const Term& t : ts) v.push_back(pointer(t));
+    return v;
+  }
+
+  uint64_t product_mod(const std::vector<uint32_t>& ids, uint64_t q) {
+    uint64_t r = 1 % q;
+    for (uint32_t i : ids) {
+      if (i >= (uint32_t)ctx->n_primes) throw std::runtime_error("prime index out of range in a factor list");
+      r = host::mulmod(r, ctx->moduli[i] % q, q);
+    }
+    return r;
+  }
+
+  const uint32_t* rotation_table(int32_t step) {
+    const uint32_t elt = cerium_galois_elt_from_step(step, kLogN);
+    if (elt == 0) throw std::runtime_error("rotation step out of range");
+    auto it = p->rot_tables.find(elt);
+    if (it != p->rot_tables.end()) return it->second;
+    // generate_table_ntt, then its inverse: inv[table[i]] = i (cerium/runtime/math/galois.cpp:30-77;
+    // the generated kernels scatter through it, evaluator.cpp:241-249)
+    std::vector<uint32_t> inv(kN);
+    auto brev = [](uint32_t x, int bits) {
+      uint32_t r = 0;
+      for (int b = 0; b < bits; b++) r |= ((x >> b) & 1u) << (bits - 1 - b);
+      return r;
+    };
+    for (uint32_t i = 0; i < (uint32_t)kN; i++) {
+      const uint32_t reversed = brev(i + (uint32_t)kN, kLogN + 1);
+      const uint64_t raw = (((uint64_t)elt * reversed) >> 1) & (uint64_t)(kN - 1);
+      inv[brev((uint32_t)raw, kLogN)] = i;
+    }
+    const uint32_t* d = upload(inv);
+    p->rot_tables[elt] = d;
+    return d;
+  }
+
+  void reference_tables() {
+    // EvaluatorContext::init_params: modulus, floor(2^58 / q), 58 per prime
+    std::vector<W> mod, ratio;
+    std::vector<uint32_t> k;
+    for (int i = 0; i < ctx->n_primes; i++) {
+      mod.push_back((W)ctx->moduli[i]);
+      ratio.push_back((W)(((uint64_t)1 << 58) / ctx->moduli[i]));
+      k.push_back(58);
+    }
+    p->d_moduli = upload(mod);
+    p->d_ratios = upload(ratio);
+    p->d_k = upload(k);
+  }
+
+  void build(const std::vector<Record>& recs, const FunctionMapType& fmap,
+             const std::map<std::string, uint64_t>& scalar_values) {
+    // register file: as many registers as the records name
+    size_t max_reg = 0;
+    bool any_reg = false;
+    for (const Record& r : recs)
+      for (const auto* list : {&r.outputs, &r.inputs})
+        for (const Term& t : *list)
+          if (t.type == Term::Reg) {
+            max_reg = std::max(max_reg, (size_t)std::stoul(t.s.substr(1)));
+            any_reg = true;
+          }
+    if (any_reg) p->regs = limb_alloc(max_reg + 1);
+    reference_tables();
+    for (const Record& r : recs) {
+      const std::string& ty = r.type;
+      if (ty == "mov") continue;  // outputs alias inputs: nothing to run (the reference skips them too)
+      if (ty == "rsv" || ty == "call" || ty == "ags" || ty == "ard")
+        throw std::runtime_error("record " + std::to_string(r.id) + " of type '" + ty + "' is not served by this executor");
+      const std::vector<BcuSpec> specs = parse_base_conv(r.base_conv);
+      // unit state changes happen BEFORE the record's terms are resolved (parse_term_base_conv_vec)
+      if (ty == "generic" || ty == "int" || ty == "drm")
+        for (const BcuSpec& b : specs) {
+          Unit& u = unit(b.unit);
+          u.in_ids.insert(u.in_ids.end(), b.first.begin(), b.first.end());
+          if (u.in_ids.size() > (size_t)kUnitMaxIn) throw std::runtime_error("base-conversion unit overflows its input block");
+        }
+      if (ty == "bco")
+        for (const BcuSpec& b : specs) {
+          Unit& u = unit(b.unit);
+          u.out_ids = b.second;
+          if (u.out_ids.size() > (size_t)kUnitMaxOut) throw std::runtime_error("base-conversion unit overflows its output block");
+        }
+      if (ty == "drm") {
+        cerium_comm* comm = p->comm;
+        if (comm == nullptr) throw std::runtime_error("record " + std::to_string(r.id) + " is a drm (all-gather) record: the function needs a communicator");
+        if ((size_t)comm->world != r.comm_size) throw std::runtime_error("drm record " + std::to_string(r.id) + " was compiled for " + std::to_string(r.comm_size) + " partitions");
+        if (r.comm_srcs.size() > r.comm_num_limbs || r.comm_dests.size() > r.comm_size * r.comm_num_limbs)
+          throw std::runtime_error("drm record " + std::to_string(r.id) + " lists more limbs than it exchanges");
+        Step s{};
+        s.kind = Step::Drm;
+        s.id = r.id;
+        s.comm_limbs = r.comm_num_limbs;
+        s.staging = limb_alloc(r.comm_size * r.comm_num_limbs);
+        for (const Term& t : r.comm_srcs) s.pack.push_back(pointer(t));      // null = a zero limb
+        for (const Term& t : r.comm_dests) s.unpack.push_back(pointer(t));   // null = not wanted here
+        p->steps.push_back(s);
+        continue;
+      }
+      auto it = fmap.find(r.id);
+      if (it == fmap.end() || it->second == nullptr)
+        throw std::runtime_error("the plugin has no launcher for record " + std::to_string(r.id) + " (" + ty + ")");
+      Step s{};
+      s.fn = it->second;
+      s.id = r.id;
+      if (ty == "bco") {
+        if (specs.empty()) continue;
+        std::vector<W*> outs;
+        std::vector<const W*> ins, facs, omods, ratios, ks;
+        std::vector<size_t> n_out, n_in;
+        size_t smem_words = 0;
+        for (const BcuSpec& b : specs) {
+          Unit& u = unit(b.unit);
+          if (u.in_ids != b.first) throw std::runtime_error("base-conversion unit b" + std::to_string(b.unit) + " does not hold the inputs record " + std::to_string(r.id) + " converts");
+          const size_t I = u.in_ids.size(), O = u.out_ids.size();
+          if (I == 0 || O == 0) throw std::runtime_error("empty base conversion");
+          // F[j][i] = [Qhat_i^-1]_{q_i} * (Qhat_i mod p_j) mod p_j  (DeviceBaseConverter::set_output_bases)
+          std::vector<uint64_t> inv(I);
+          for (size_t i = 0; i < I; i++) {
+            const uint64_t qi = ctx->moduli[u.in_ids[i]];
+            uint64_t prod = 1 % qi;
+            for (size_t k = 0; k < I; k++)
+              if (k != i) prod = host::mulmod(prod, ctx->moduli[u.in_ids[k]] % qi, qi);
+            inv[i] = I > 1 ? host::invmod(prod, qi) : 1;
+          }
+          std::vector<W> F(O * I), om(O), ra(O);
+          std::vector<uint32_t> kk(O, 58);
+          for (size_t j = 0; j < O; j++) {
+            if (u.out_ids[j] >= (uint32_t)ctx->n_primes) throw std::runtime_error("prime index out of range");
+            const uint64_t pj = ctx->moduli[u.out_ids[j]];
+            om[j] = (W)pj;
+            ra[j] = (W)(((uint64_t)1 << 58) / pj);
+            for (size_t i = 0; i < I; i++) {
+              uint64_t qhat = 1 % pj;
+              for (size_t k = 0; k < I; k++)
+                if (k != i) qhat = host::mulmod(qhat, ctx->moduli[u.in_ids[k]] % pj, pj);
+              F[j * I + i] = (W)host::mulmod(inv[i] % pj, qhat, pj);
+            }
+          }
+          outs.push_back(u.out_buf);
+          ins.push_back(u.in_buf);
+          n_out.push_back(O);
+          n_in.push_back(I);
+          facs.push_back(upload(F));
+          omods.push_back(upload(om));
+          ratios.push_back(upload(ra));
+          ks.push_back(reinterpret_cast<const W*>(upload(kk)));
+          // Evaluator::fn_bco's shared-memory size
+          smem_words = std::max(smem_words, (O * I / 32 + 1) * 32 + I * 256);
+          u.in_ids.clear();  // set_input_bases({}) after the conversion is built (evaluator.cpp:939)
+        }
+        s.kind = Step::Bco;
+        s.outs = upload(outs);
+        s.ins = upload(ins);
+        s.n_out = upload(n_out);
+        s.n_in = upload(n_in);
+        s.factors = upload(facs);
+        s.out_moduli = upload(omods);
+        s.ratios = upload(ratios);
+        s.ks = upload(ks);
+        s.smem = smem_words * sizeof(W);
+        s.count = specs.size();
+        p->steps.push_back(s);
+        continue;
+      }
+      if (r.outputs.empty()) continue;
+      if (!r.remapables.empty()) throw std::runtime_error("record " + std::to_string(r.id) + " reads remapable inputs, which this executor does not serve");
+      std::vector<W*> ins_h = pointers(r.inputs);
+      std::vector<W*> outs_h = pointers(r.outputs);
+      std::vector<const W*> ins_c(ins_h.begin(), ins_h.end());
+      s.outs = upload(outs_h);
+      s.ins = upload(ins_c);
+      for (uint32_t b : r.bases)
+        if (b >= (uint32_t)ctx->n_primes) throw std::runtime_error("prime index out of range in .bases");
+      s.bases = upload(r.bases);
+      s.n_bases = r.bases.size();
+      if (ty == "generic" || ty == "pmu") {
+        s.kind = Step::Ewi;
+        std::vector<W> sc;
+        if (ty == "pmu") {
+          // compute_pmu_factors: [prod pmu bases] mod q_i for every prime of the context
+          for (int i = 0; i < ctx->n_primes; i++) sc.push_back((W)product_mod(r.pmu, ctx->moduli[i]));
+        } else {
+          for (const Term& t : r.scalars) {
+            auto sv = scalar_values.find(t.s);
+            if (sv == scalar_values.end()) throw std::runtime_error("no value given for scalar " + t.s);
+            sc.push_back((W)sv->second);
+          }
+        }
+        s.scalars = upload(sc);
+        if (!r.rots.empty()) {
+          std::vector<const uint32_t*> maps;
+          for (int32_t amt : r.rots) maps.push_back(rotation_table(amt));
+          s.rotmaps = upload(maps);
+        }
+      } else if (ty == "ntt") {
+        s.kind = Step::Ntt;
+      } else if (ty == "int") {
+        s.kind = Step::Int;
+      } else if (ty == "sud") {
+        s.kind = Step::Sud;
+        // compute_sud_factors: [(prod divide bases)^-1] mod q_i for every prime (0 where not invertible)
+        std::vector<W> fac;
+        for (int i = 0; i < ctx->n_primes; i++) {
+          const uint64_t q = ctx->moduli[i];
+          fac.push_back((W)host::invmod(product_mod(r.sud, q), q));
+        }
+        s.sud_factors = upload(fac);
+      } else {
+        throw std::runtime_error("unknown record type '" + ty + "'");
+      }
+      p->steps.push_back(s);
+    }
+  }
+};
+
+}  // namespace
+
+extern "C" {
+
+int cerium_program_load(cerium_context* ctx, cerium_program** out, const char* functions_path, const char* plugin_path,
+                        const char* const* scalar_terms, const uint64_t* scalar_values, int n_scalars, cerium_comm* comm) {
+  if (!ctx || !out || !functions_path || !plugin_path) return fail(CERIUM_ERR_INVALID, "program_load: null argument");
+  if (n_scalars < 0 || (n_scalars > 0 && (!scalar_terms || !scalar_values))) return fail(CERIUM_ERR_INVALID, "program_load: bad scalar list");
+  if (ctx->word_bits != 32)
+    return fail(CERIUM_ERR_UNSUPPORTED, "program_load: compiled programs carry generated 32-bit kernels; the context must use 32-bit words");
+  std::vector<Record> recs;
+  std::string err;
+  if (!parse_records(functions_path, recs, err)) return fail(CERIUM_ERR_INVALID, "program_load: " + err);
+  DeviceGuard guard(ctx->device);
+  if (!guard.ok) return fail(CERIUM_ERR_CUDA, "program_load: cannot select device");
+  void* h = dlopen(plugin_path, RTLD_LAZY | RTLD_LOCAL);
+  if (!h) return fail(CERIUM_ERR_INVALID, std::string("program_load: cannot load the plugin: ") + dlerror());
+  typedef const FunctionMapType& (*getter_t)();
+  getter_t getter = (getter_t)dlsym(h, "__GET_FUNCTION_MAP__");
+  if (!getter) {
+    dlclose(h);
+    return fail(CERIUM_ERR_INVALID, "program_load: the plugin does not export __GET_FUNCTION_MAP__");
+  }
+  auto* p = new cerium_program();
+  p->ctx = ctx;
+  p->comm = comm;
+  p->plugin = h;
+  std::map<std::string, uint64_t> scalars;
+  for (int i = 0; i < n_scalars; i++) scalars[strip(scalar_terms[i])] = scalar_values[i];
+  try {
+    const FunctionMapType& fmap = getter();
+    Loader ld{p, ctx, {}};
+    ld.build(recs, fmap, scalars);
+  } catch (const std::exception& e) {
+    const std::string msg = e.what();
+    cerium_program_destroy(p);
+    return fail(CERIUM_ERR_INVALID, "program_load: " + msg);
+  }
+  *out = p;
+  return CERIUM_OK;
+}
+
+int cerium_program_destroy(cerium_program* p) {
+  if (!p) return CERIUM_OK;
+  DeviceGuard guard(p->ctx->device);
+  for (void* d : p->allocs) cudaFree(d);
+  // the plugin stays loaded: its maps are referenced for the life of the process
+  delete p;
+  return CERIUM_OK;
+}
+
+int cerium_program_num_steps(const cerium_program* p) { return p ? (int)p->steps.size() : 0; }
+
+int cerium_program_memory(cerium_program* p, const char* term, void** device_ptr) {
+  if (!p || !term || !device_ptr) return fail(CERIUM_ERR_INVALID, "program_memory: null argument");
+  auto it = p->memory.find(strip(term));
+  if (it == p->memory.end()) return fail(CERIUM_ERR_INVALID, std::string("program_memory: the function names no memory term '") + term + "'");
+  *device_ptr = it->second;
+  return CERIUM_OK;
+}
+
+int cerium_program_run(cerium_program* p, void* stream) {
+  if (!p) return fail(CERIUM_ERR_INVALID, "program_run: null program");
+  cerium_context* ctx = p->ctx;
+  DeviceGuard guard(ctx->device);
+  if (!guard.ok) return fail(CERIUM_ERR_CUDA, "program_run: cannot select device");
+  // the launchers of this library find their tables through the context bound to the device
+  if (int rc = cerium_function_map_bind(ctx, ctx->device)) return fail(rc, "program_run: cannot bind the context");
+  cudaStream_t st = (cudaStream_t)stream;
+  try {
+    for (const Step& s : p->steps) {
+      switch (s.kind) {
+        case Step::Ewi:
+          ((ewi_fn)s.fn)(st, s.outs, s.ins, s.scalars, nullptr, nullptr, s.bases, p->d_moduli, p->d_ratios, p->d_k, s.rotmaps);
+          break;
+        case Step::Ntt:
+        case Step::Int:
+          // the reference's root tables are not rebuilt here: the transform records are expected to run on
+          // this library's launchers, which use the bound context's tables
+          ((ntt_fn)s.fn)(st, s.outs, s.ins, s.bases, s.n_bases, p->d_moduli, nullptr);
+          break;
+        case Step::Sud:
+          ((sud_fn)s.fn)(st, s.outs, s.ins, s.bases, s.n_bases, p->d_moduli, nullptr, s.sud_factors, p->d_ratios, p->d_k);
+          break;
+        case Step::Bco:
+          ((bco_fn)s.fn)(st, s.outs, s.n_out, s.ins, s.n_in, s.factors, s.out_moduli, s.ratios, s.ks, s.smem, s.count);
+          break;
+        case Step::Drm: {
+          const size_t limb = (size_t)kN * sizeof(W);
+          W* mine = s.staging + (size_t)p->comm->rank * s.comm_limbs * kN;
+          for (size_t i = 0; i < s.pack.size(); i++) {
+            if (s.pack[i] == nullptr) CERIUM_CUDA(cudaMemsetAsync(mine + i * kN, 0, limb, st));
+            else CERIUM_CUDA(cudaMemcpyAsync(mine + i * kN, s.pack[i], limb, cudaMemcpyDeviceToDevice, st));
+          }
+          if (int rc = comm_allgather(p->comm, s.staging, mine, s.comm_limbs * limb, st)) return rc;
+          for (size_t j = 0; j < s.unpack.size(); j++)
+            if (s.unpack[j] != nullptr)
+              CERIUM_CUDA(cudaMemcpyAsync(s.unpack[j], s.staging + j * kN, limb, cudaMemcpyDeviceToDevice, st));
+          break;
+        }
+      }
+    }
+  } catch (const std::exception& e) {
+    return fail(CERIUM_ERR_CUDA, std::string("program_run: ") + e.what());
+  }
+  CERIUM_LAUNCH_CHECK("program_run");
+  return CERIUM_OK;
+}
+
+}  // extern "C"
+
+#else  // CERIUM_EMU: the executor drives a kernel plugin, which needs the CUDA runtime
+
+struct cerium_program {};
+extern "C" {
+int cerium_program_load(cerium_context*, cerium_program**, const char*, const char*, const char* const*, const uint64_t*, int,
+                        cerium_comm*) {
+  return fail(CERIUM_ERR_UNSUPPORTED, "program_load: not part of the host-only test build");
+}
+int cerium_program_destroy(cerium_program*) { return CERIUM_OK; }
+int cerium_program_num_steps(const cerium_program*) { return 0; }
+int cerium_program_memory(cerium_program*, const char*, void**) { return CERIUM_ERR_UNSUPPORTED; }
+int cerium_program_run(cerium_program*, void*) { return CERIUM_ERR_UNSUPPORTED; }
+}
+
+#endif  // !CERIUM_EMU
+
+extern "C" int cerium_program_inspect(const char* functions_path, char* buf, size_t buf_bytes, int* n_records) {
+  if (!functions_path || !n_records) return fail(CERIUM_ERR_INVALID, "program_inspect: null argument");
+  std::vector<Record> recs;
+  std::string err;
+  if (!parse_records(functions_path, recs, err)) return fail(CERIUM_ERR_INVALID, "program_inspect: " + err);
+  *n_records = (int)recs.size();
+  std::ostringstream s;
+  for (const Record& r : recs) {
+    s << r.id << ' ' << r.type << ' ' << r.outputs.size() << ' ' << r.inputs.size() << ' ' << r.bases.size() << ' '
+      << r.rots.size() << ' ' << parse_base_conv(r.base_conv).size() << ' ' << r.sud.size() << ' ' << r.pmu.size() << '\n';
+  }
+  const std::string text = s.str();
+  if (buf && buf_bytes > 0) {
+    const size_t n = std::min(text.size(), buf_bytes - 1);
+    std::memcpy(buf, text.data(), n);
+    buf[n] = 0;
+  }
+  return CERIUM_OK;
+}

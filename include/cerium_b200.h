@@ -66,6 +66,7 @@ typedef struct cerium_context cerium_context;
 typedef struct cerium_bconv cerium_bconv;
 typedef struct cerium_keyswitch cerium_keyswitch;
 typedef struct cerium_comm cerium_comm;
+typedef struct cerium_program cerium_program;
 
 /* Library version (major * 10000 + minor * 100 + patch). */
 CERIUM_API int cerium_version(void);
@@ -544,6 +545,44 @@ CERIUM_API const char *cerium_function_map_error(void);
 CERIUM_API int cerium_function_map_size(const char *functions_path, int cugraph);
 CERIUM_API void *cerium_function_map_lookup(const char *functions_path, int cugraph, uint32_t kernel_id);
 CERIUM_API void *cerium_function_map_launcher(const char *type, int cugraph);
+
+/*
+ * Executor of one partition of a compiled Cerium function: what CeriumFunction::make_program /
+ * run_program do in the reference runtime for one GPU, in stream mode
+ * (cerium/runtime/execution/function_execution.cpp:124-360 builds the argument tables, :437-611 replays
+ * them).  cerium_program_load parses the compiler's kernel stream `functions<p>` (the ll.functions
+ * records, cerium/compiler/backend/cuda_kernel.cc:1707-1916; fields as FunctionMetaData reads them,
+ * cerium/runtime/execution/function.h:269-347), loads the kernel plugin function_map_<p>.so of the
+ * function and resolves every term: `r<n>` in a register file, `b<k>(<prime>)` in the base-conversion
+ * units (stateful like DeviceBaseConverter, evaluator.cpp:1483-1608), anything else as named program
+ * memory, one limb per term (function.cpp:464-503).  The tables every record's launcher takes are built
+ * once: pointer tables, `bases`, SuD and PMU factors (function.cpp:685-755), conversion matrices, and -
+ * for the element-wise launchers the compiler generated - the modulus / Barrett / rotation tables of the
+ * reference's EvaluatorContext.  cerium_program_run replays the records on a stream through the
+ * plugin's launchers, by kernel id.  With this library's plugin shim installed, ntt / int / sud / bco
+ * records run on this library's kernels and generic / pmu records on the program's generated ones.
+ *   scalar_terms / scalar_values   values of the `.scalars` terms of generic records (may be empty)
+ *   cerium_program_memory          device address of a named memory term, e.g. "i1(0)": the caller
+ *                                  writes inputs and keys there before a run and reads outputs after it
+ *                                  (names and meanings are listed in the function's `inputs<p>` file)
+ *   cerium_program_inspect         parses only (no device): one line per record,
+ *                                  "id type #outputs #inputs #bases #rots #units #sud #pmu"
+ *   comm                           the partitions of a function compiled for several GPUs run as the
+ *                                  ranks of this communicator, one process each (partition p = rank p);
+ *                                  its drm records (the all-gather of limbs between partitions,
+ *                                  Evaluator::drm, evaluator.cpp:1154-1251) run on it.  NULL for a
+ *                                  function compiled for one GPU.
+ * 32-bit contexts (the generated kernels are 32-bit).  Not served: rsv, call, ags / ard records and
+ * remapable inputs; a function that has one is refused at load.
+ */
+CERIUM_API int cerium_program_load(cerium_context *ctx, cerium_program **out, const char *functions_path,
+                                   const char *plugin_path, const char *const *scalar_terms,
+                                   const uint64_t *scalar_values, int n_scalars, cerium_comm *comm);
+CERIUM_API int cerium_program_destroy(cerium_program *prog);
+CERIUM_API int cerium_program_num_steps(const cerium_program *prog);
+CERIUM_API int cerium_program_memory(cerium_program *prog, const char *term, void **device_ptr);
+CERIUM_API int cerium_program_run(cerium_program *prog, void *stream);
+CERIUM_API int cerium_program_inspect(const char *functions_path, char *buf, size_t buf_bytes, int *n_records);
 
 #ifdef __cplusplus
 }
