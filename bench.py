@@ -695,8 +695,124 @@ class BsgsWorkload(HRotWorkload):
         return v / (2 * (self.G - 1)), sample + " (one rotation timed; a transform is counted as its 14 rotations)"
 
 
+class BootstrapWorkload(Workload):
+    """One CKKS bootstrap as the operator list of cerium_b200/bootstrap.py (the structure of the reference's
+    benchmarks/bootstrap_32K/bootstrap.py:299-358 for the parameterisation the benchmark names): ModRaise of
+    a two-limb ciphertext to 34 limbs, CoeffToSlot as three 8 x 8 BSGS multiply-accumulates with the rescale
+    folded in, conjugation split, a degree-63 Chebyshev polynomial (16 HMults) and two double-angle steps on
+    both parts, SlotToCoeff as three more BSGS stages: 15 levels, 103 key switches.  Keys, diagonals and
+    coefficients are seeded uniform residues of the real shapes (30 GB on the device)."""
+    name = "bootstrap_N65536_top34_K5_dnum7_c2s3_s2c3_cheb63_da2_u64"
+    metric = "bootstrap_latency_ms"
+    unit = "ms"
+    ops_per_step = 1
+    latency_metric = True
+
+    def __init__(self):
+        self.prm = params.config_hrot(LOGN, 35, 5, 7)
+
+    def _make(self, tag, lead, idx):
+        import zlib
+        gen = self.torch.Generator(device="cuda").manual_seed(zlib.crc32(repr(tag).encode()))
+        return _rand_limbs_gpu(self.torch, self.prm.moduli, list(idx), tuple(lead), gen)
+
+    def setup(self, lib, torch, rank, world=1, sharded=False):
+        from cerium_b200 import _capi, bootstrap as bs
+        self.torch, self.bs, self.lib = torch, bs, lib
+        prm = self.prm
+        self.ctx = _capi.Context(lib, prm.moduli, 64, device=torch.cuda.current_device())
+        self.shape = bs.BootstrapShape(top=prm.L - 1)
+        self.material = bs.BootstrapMaterial(prm.moduli, prm.q_idx, prm.p_idx, prm.dnum, self.shape, self._make,
+                                             lambda step: lib.galois_elt_from_step(step, LOGN))
+        self.ev = bs.GpuEvaluator(torch, _capi, self.ctx, self.material, _capi.BCONV_EXACT, _capi.ROUND_HALF)
+        gen = torch.Generator(device="cuda").manual_seed(0xCE210004 + rank)
+        self.ct2 = [_rand_limbs_gpu(torch, prm.moduli, prm.q_idx[:2], (), gen) for _ in range(2)]
+        self.host_in = torch.stack(self.ct2).cpu().pin_memory()
+        out_level = self.shape.top - self.shape.levels_used
+        self.out_shape = (2, out_level, N)
+        # the first run creates the plans, keys and diagonals of every level
+        self.step()
+        torch.cuda.synchronize()
+        n = self.ev.count.n
+        self.op_counts = dict(n)
+        # launches: ModRaise 19; a BSGS stage 5 + 7 * 6 + 2 + 2 + 8 * 6 + 5; an HMult 15; a conjugation 11;
+        # a rescale 4; every other pass 1
+        self.gpu_launches_per_step = (19 * n["mod_raise"] + 104 * n["bsgs"] + 15 * n["hmult"] + 11 + 4 * n["rescale"]
+                                      + n["ewise"] + 2 * n["pt_mac"])
+        self.ev.count.n = {}
+        self.alg_bytes = 0
+
+    def step(self):
+        self.ev.stream = self.torch.cuda.current_stream().cuda_stream
+        self.result = self.bs.bootstrap(self.ev, self.shape, self.ct2)
+
+    def verify(self, orc_mod):
+        """ModRaise and the first CoeffToSlot stage at full size against the oracle (15 key switches of 34
+        limbs, the plaintext products, one ModDown with the rescale folded in); the whole operator list is
+        compared with the oracle at a reduced shape by tests/test_gpu_bootstrap.py."""
+        from tests.bootstrap_checker import OracleEvaluator
+        torch, m = self.torch, self.material
+        u = lambda t: t.cpu().numpy().view(np.uint64)  # noqa: E731
+
+        class HostMaterial:
+            """The device material seen from the host: the same buffers, copied on first use."""
+            def __init__(self, dev):
+                self.d = dev
+                self.moduli, self.q_idx, self.p_idx, self.top = dev.moduli, dev.q_idx, dev.p_idx, dev.top
+                self.lift_key = u(dev.lift_key)
+                self.dnum_at = dev.dnum_at
+
+            def stage(self, stage, level):
+                st = self.d.stage(stage, level)
+                h = lambda t: None if t is None else u(t)  # noqa: E731
+                return type(st)(st.g, st.n_giant, [h(t) for t in st.pts], [h(t) for t in st.baby_keys], st.baby_elts,
+                                [h(t) for t in st.giant_keys], st.giant_elts)
+        oe = OracleEvaluator(HostMaterial(m), orc_mod.BCONV_EXACT, orc_mod.ROUND_HALF)
+        self.ev.stream = torch.cuda.current_stream().cuda_stream
+        g = self.ev.bsgs(self.ev.mod_raise(self.ct2), ("c2s", 0))
+        torch.cuda.synchronize()
+        w = oe.bsgs(oe.mod_raise([u(self.ct2[0]), u(self.ct2[1])]), ("c2s", 0))
+        self.ev.count.n = {}
+        return bool(np.array_equal(u(g.c0[:g.level]), w.c0) and np.array_equal(u(g.c1[:g.level]), w.c1))
+
+    def e2e_step(self):
+        if getattr(self, "pipe", None) is None:
+            from cerium_b200.host_pipeline import HostPipeline
+
+            def op(ins, outs, stream):
+                self.ev.stream = stream
+                r = self.bs.bootstrap(self.ev, self.shape, [ins[0][0], ins[0][1]])
+                outs[0][0].copy_(r.c0[:r.level], non_blocking=True)
+                outs[0][1].copy_(r.c1[:r.level], non_blocking=True)
+            self.pipe = HostPipeline(self.torch, [self.host_in.shape], [self.out_shape], op)
+        self.pipe.submit([self.host_in])
+        return self.pipe.in_bytes, self.pipe.out_bytes
+
+    def roofline_setup(self):
+        HRotWorkload.roofline_setup(self)
+
+    def roofline_step(self):
+        HRotWorkload.roofline_step(self)
+
+    def cpu_sample(self, orc_mod):
+        """One key switch of 34 limbs on the CPU port, scaled by the bootstrap's 103 key switches (they are
+        nine tenths of its time on the GPU as well)."""
+        prm = self.prm
+        rng = np.random.default_rng(1)
+        octx = orc_mod.OracleContext(LOGN, prm.moduli)
+        q_idx = prm.q_idx[:34]
+        all_idx = q_idx + prm.p_idx
+        rl = lambda idx: np.stack([rng.integers(0, prm.moduli[p], size=N, dtype=np.uint64) for p in idx])  # noqa: E731
+        c = rl(q_idx)
+        evk = np.stack([np.stack([rl(all_idx) for _ in range(2)]) for _ in range(7)])
+        t0 = time.perf_counter()
+        octx.keyswitch(orc_mod.BCONV_EXACT, orc_mod.ROUND_HALF, q_idx, prm.p_idx, 7, c, evk)
+        dt = time.perf_counter() - t0
+        return 103 * dt * 1e3, "one key switch (L=34, K=5, dnum=7) on the oracle port x the 103 key switches of a bootstrap"
+
+
 WORKLOADS = {"hrot": HRotWorkload, "hmult": HMultWorkload, "ntt": NttWorkload, "hoisted": HoistedWorkload,
-             "bsgs": BsgsWorkload}
+             "bsgs": BsgsWorkload, "bootstrap": BootstrapWorkload}
 
 
 # ---------------------------------------------------------------------------------------
@@ -723,8 +839,10 @@ def run_reference_arm(args, wl):
     ops = getattr(wl, "ops_per_step", 1)
     line = {
         "impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * ops / value,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+        "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": value if getattr(wl, "latency_metric", False) else 1e3 * ops / value,
+        "higher_is_better": not getattr(wl, "latency_metric", False), "scaling": "weak", "vs_baseline": None,
+        "dtype": "u64", "data": "synthetic",
         "config": {"workload": wl.name},
         "note": "CPU port of the reference algorithm (SEAL-based reference runtime not buildable here)",
         "cpu_baseline": {"value": value, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",
@@ -853,8 +971,9 @@ def main():
         args.warmup = args.warmup if args.warmup is not None else 1
         run_reference_arm(args, wl)
         return
-    args.steps = args.steps if args.steps is not None else 2000
-    args.warmup = max(3, args.warmup if args.warmup is not None else 50)
+    slow = args.workload in ("bootstrap", "bsgs")
+    args.steps = args.steps if args.steps is not None else (20 if args.workload == "bootstrap" else 200 if slow else 2000)
+    args.warmup = max(3, args.warmup if args.warmup is not None else (3 if slow else 50))
 
     import torch
     import torch.distributed as dist
@@ -992,11 +1111,12 @@ def main():
         e2e_s, copy_s = float(t[0].item()), float(t[1].item())
 
     if rank == 0:
-        value = job_ops * ops * args.steps / (ms / 1e3)
+        latency = getattr(wl, "latency_metric", False)
+        value = ms / args.steps if latency else job_ops * ops * args.steps / (ms / 1e3)
         per_step = sorted(b / args.steps for b in block_ms)
         line = {
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": not latency,
             "scaling": "strong" if sharded else "weak",
             "vs_baseline": None, "dtype": "u64", "data": "synthetic",
             "config": {"workload": wl.name},
@@ -1009,8 +1129,9 @@ def main():
                             else "independent ciphertexts per GPU"),
             "repeat": {"blocks": len(block_ms), "steps_per_block": args.steps, "ms_per_step_median": per_step[len(per_step) // 2],
                        "ms_per_step_min": per_step[0], "ms_per_step_max": per_step[-1]},
-            "e2e": {"value": job_ops * ops * e2e_steps / e2e_s, "unit": wl.unit, "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "copy_ceiling": job_ops * ops * e2e_steps / copy_s,
+            "e2e": {"value": (1e3 * e2e_s / e2e_steps if latency else job_ops * ops * e2e_steps / e2e_s), "unit": wl.unit,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "copy_ceiling": (1e3 * copy_s / e2e_steps if latency else job_ops * ops * e2e_steps / copy_s),
                     "copy_ceiling_note": "the same bytes up and down per step with nothing computed, same streams and buffers",
                     "numa_node": numa},
             "gpu_launches": wl.gpu_launches_per_step * args.steps,

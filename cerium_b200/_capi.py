@@ -82,6 +82,8 @@ SIGNATURES = {
     "cerium_keyswitch_workspace_bytes": (_sz, [_vp]),
     "cerium_keyswitch_apply": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "cerium_keyswitch_apply_rescale": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_int, _vp]),
+    "cerium_plaintext_mac": (C.c_int, [_vp, C.c_int, C.c_int, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
+                                       C.POINTER(_vp), _u32p, C.c_int, _vp]),
     "cerium_bsgs_work_limbs": (_sz, [_vp, C.c_int, C.c_int]),
     "cerium_bsgs_apply": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.POINTER(_vp), C.POINTER(_vp), _u32p,
                                     C.POINTER(_vp), _u32p, C.c_int, _vp, _vp]),
@@ -253,6 +255,14 @@ class Context:
         """Rescale of one rank's remaining limbs against the broadcast coefficient-form last limb."""
         self.lib.check(self.lib.dll.cerium_rescale_local(self.h, round_mode, out, inp, _u32(local_idx), len(local_idx),
                                                          last_prime, last_coef, n_polys, stream))
+
+    def plaintext_mac(self, out0: Sequence[int], out1: Sequence[int], src0: Sequence[int], src1: Sequence[int],
+                      plaintexts: Sequence[int], prime_idx: Sequence[int], stream: int = 0):
+        """out_i = sum_j pt[i][j] (.) src_j for both polynomials; plaintexts: len(out0) * len(src0) device
+        addresses, entry i * n_src + j, 0 = no such term."""
+        vp = lambda seq: (_vp * len(seq))(*[_vp(int(p)) if p else _vp() for p in seq])  # noqa: E731
+        self.lib.check(self.lib.dll.cerium_plaintext_mac(self.h, len(out0), len(src0), vp(out0), vp(out1), vp(src0),
+                                                         vp(src1), vp(plaintexts), _u32(prime_idx), len(prime_idx), stream))
 
     def rescale_sharded(self, comm: "Comm", out: int, inp: int, q_idx: Sequence[int], n_polys: int, last_coef: int,
                         round_mode: int = ROUND_FLOOR, stream: int = 0):

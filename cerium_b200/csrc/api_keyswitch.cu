@@ -1021,6 +1021,58 @@ int cerium_hmult(cerium_keyswitch* ks, void* out0, void* out1, const void* a0, c
   return rescale_impl(ctx, ks->round_mode, outs, pair_work, kso, ks->q_idx.data(), ks->L, 2, scratch, (cudaStream_t)stream);
 }
 
+int cerium_plaintext_mac(cerium_context* ctx, int n_out, int n_src, void* const* out0, void* const* out1,
+                         const void* const* src0, const void* const* src1, const void* const* plaintexts,
+                         const uint32_t* prime_idx, int count, void* stream) {
+  if (!ctx || !out0 || !out1 || !src0 || !src1 || !plaintexts || !prime_idx) return fail(CERIUM_ERR_INVALID, "plaintext_mac: null argument");
+  if (n_out < 1 || n_src < 1 || n_src > kBsgsMaxBaby) return fail(CERIUM_ERR_UNSUPPORTED, "plaintext_mac: 1..16 sources, at least one output");
+  if (count < 1 || count > kEwMaxLimbs) return fail(CERIUM_ERR_INVALID, "plaintext_mac: 1..128 limbs");
+  for (int b = 0; b < count; b++) {
+    if (prime_idx[b] >= (uint32_t)ctx->n_primes) return fail(CERIUM_ERR_INVALID, "plaintext_mac: prime index out of range");
+    const long double q = (long double)ctx->moduli[prime_idx[b]];
+    if (q * q * n_src >= (ctx->word_bits == 32 ? 1.8e19L : 3.4e38L))
+      return fail(CERIUM_ERR_UNSUPPORTED, "plaintext_mac: that many sources overflow the accumulator for primes this wide");
+  }
+  for (int j = 0; j < n_src; j++)
+    if (!src0[j] || !src1[j] || (((uintptr_t)src0[j] | (uintptr_t)src1[j]) & 15u)) return fail(CERIUM_ERR_INVALID, "plaintext_mac: bad source pointer");
+  for (int i = 0; i < n_out; i++)
+    if (!out0[i] || !out1[i] || (((uintptr_t)out0[i] | (uintptr_t)out1[i]) & 15u)) return fail(CERIUM_ERR_INVALID, "plaintext_mac: bad output pointer");
+  DeviceGuard guard(ctx->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  return dispatch_word(ctx->word_bits, [&](auto tag) -> int {
+    using W = decltype(tag);
+    const PrimeConst<W>* pcs = static_cast<const PrimeConst<W>*>(ctx->d_pcs);
+    for (int first = 0; first < n_out; first += kBsgsGroup) {
+      const int cnt = std::min(kBsgsGroup, n_out - first);
+      PtMacArgs<W> a{};
+      a.g = n_src;
+      for (int j = 0; j < n_src; j++) {
+        a.src0[j] = static_cast<const W*>(src0[j]);
+        a.src1[j] = static_cast<const W*>(src1[j]);
+      }
+      for (int i = 0; i < cnt; i++) {
+        a.out0[i] = static_cast<W*>(out0[first + i]);
+        a.out1[i] = static_cast<W*>(out1[first + i]);
+        for (int j = 0; j < n_src; j++) {
+          const void* p = plaintexts[(size_t)(first + i) * n_src + j];
+          if (p != nullptr && ((uintptr_t)p & 15u)) return fail(CERIUM_ERR_INVALID, "plaintext_mac: pointers must be 16-byte aligned");
+          a.pt[i][j] = static_cast<const W*>(p);
+        }
+      }
+      for (int b = 0; b < count; b++) a.prime[b] = (uint8_t)prime_idx[b];
+      const dim3 grid(kN / (kEwThreads * PtMacLanes<W>::kWords), count);
+      switch (cnt) {
+        case 1: { auto kfn = pt_mac_kernel<W, 1>; CERIUM_LAUNCH(kfn, grid, kEwThreads, 0, st, a, pcs); } break;
+        case 2: { auto kfn = pt_mac_kernel<W, 2>; CERIUM_LAUNCH(kfn, grid, kEwThreads, 0, st, a, pcs); } break;
+        case 3: { auto kfn = pt_mac_kernel<W, 3>; CERIUM_LAUNCH(kfn, grid, kEwThreads, 0, st, a, pcs); } break;
+        default: { auto kfn = pt_mac_kernel<W, 4>; CERIUM_LAUNCH(kfn, grid, kEwThreads, 0, st, a, pcs); } break;
+      }
+    }
+    CERIUM_LAUNCH_CHECK("plaintext_mac");
+    return CERIUM_OK;
+  });
+}
+
 size_t cerium_bsgs_work_limbs(const cerium_keyswitch* ks, int g, int n_giant) {
   if (!ks || g < 1 || n_giant < 1) return 0;
   // rotated copies of the input, the giant steps' inner sums, the two pre-addition sums

@@ -441,6 +441,17 @@ CERIUM_API int cerium_hmult(cerium_keyswitch *ks, void *out0, void *out1, const 
  *   out0, out1        [L - rescale_levels][N]; must not overlap the inputs
  * Every diagonal and every key is read exactly once; the rotated copies once per four giant steps.
  */
+/*
+ * Plaintext multiply-accumulate on its own: n_out ciphertexts out_i = sum_j pt[i][j] (.) src_j over
+ * n_src (1..16) source ciphertexts, both polynomials, `count` limbs - the MuP + Add kernel group of the
+ * reference's lowerings (cerium/compiler/backend/compiler.cc:2495-2522) as one pass per four outputs.
+ * All pointer arrays are HOST arrays of device pointers to [count][N] stacks; plaintexts has n_out *
+ * n_src entries, entry i * n_src + j, NULL = no such term.  Outputs must not overlap sources.
+ */
+CERIUM_API int cerium_plaintext_mac(cerium_context *ctx, int n_out, int n_src, void *const *out0, void *const *out1,
+                                    const void *const *src0, const void *const *src1,
+                                    const void *const *plaintexts, const uint32_t *prime_idx, int count,
+                                    void *stream);
 CERIUM_API size_t cerium_bsgs_work_limbs(const cerium_keyswitch *ks, int g, int n_giant);
 CERIUM_API int cerium_bsgs_apply(cerium_keyswitch *ks, void *out0, void *out1, const void *c0, const void *c1,
                                  int g, int n_giant, const void *const *plaintexts,
