@@ -52,6 +52,8 @@ SIGNATURES = {
     "cerium_tensor": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _u32p, C.c_int, _vp]),
     "cerium_galois_elt_from_step": (C.c_uint32, [C.c_int, C.c_int]),
     "cerium_automorph": (C.c_int, [_vp, _vp, _sz, _vp, _sz, C.c_uint32, C.c_int, _vp]),
+    "cerium_mul_plain_periodic": (C.c_int, [_vp, _vp, _sz, _vp, _sz, _vp, _sz, C.c_int, _vp, _sz, C.POINTER(C.c_uint32),
+                                            C.c_int, _vp]),
     "cerium_resolve2": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _sz, C.c_uint32, C.c_uint32, C.c_int, _vp]),
     "cerium_mod2": (C.c_int, [_vp, _vp, _sz, _vp, _vp, _u32p, C.c_int, _vp]),
     "cerium_bconv_create": (C.c_int, [_vp, C.POINTER(_vp), C.c_int, _u32p, C.c_int, _u32p, C.c_int]),
@@ -106,6 +108,8 @@ SIGNATURES = {
     "cerium_program_num_steps": (C.c_int, [_vp]),
     "cerium_program_memory": (C.c_int, [_vp, C.c_char_p, C.POINTER(_vp)]),
     "cerium_program_run": (C.c_int, [_vp, _vp]),
+    "cerium_program_write": (C.c_int, [_vp, C.c_char_p, C.POINTER(C.c_uint32), C.c_int, _vp, _vp]),
+    "cerium_program_read": (C.c_int, [_vp, C.c_char_p, C.POINTER(C.c_uint32), C.c_int, _vp, _vp]),
     "cerium_program_inspect": (C.c_int, [C.c_char_p, C.c_char_p, _sz, C.POINTER(C.c_int)]),
 }
 
@@ -233,6 +237,14 @@ class Context:
                stream: int = 0):
         self.lib.check(self.lib.dll.cerium_tensor(self.h, d0, d1, d2, a0, a1, b0, b1, self.n, _u32(prime_idx),
                                                   len(prime_idx), stream))
+
+    def mul_plain_periodic(self, out: int, a: int, pt: int, log2_repeat: int, prime_idx: Sequence[int], addend: int = 0,
+                           pt_stride: Optional[int] = None, stream: int = 0):
+        """out = a * pt[i >> log2_repeat] (+ addend): the plaintext is stored once per period."""
+        n = self.n
+        self.lib.check(self.lib.dll.cerium_mul_plain_periodic(self.h, out, n, a, n, pt, pt_stride or (n >> log2_repeat),
+                                                              log2_repeat, addend or None, n, _u32(prime_idx),
+                                                              len(prime_idx), stream))
 
     def automorph(self, out: int, inp: int, galois_elt: int, count: int, stream: int = 0):
         n = self.n
@@ -403,6 +415,17 @@ class Program:
         p = _vp()
         self.ctx.lib.check(self.ctx.lib.dll.cerium_program_memory(self.h, term.encode(), C.byref(p)))
         return int(p.value)
+
+    def write(self, name: str, limb_ids: Sequence[int], host, stream: int = 0):
+        """Copies host limbs ([len(limb_ids)][N] uint32, C-contiguous numpy) into the terms "name(limb)"."""
+        assert host.dtype.itemsize == 4 and host.flags.c_contiguous and host.size == len(limb_ids) * self.ctx.n
+        self.ctx.lib.check(self.ctx.lib.dll.cerium_program_write(self.h, name.encode(), _u32(limb_ids), len(limb_ids),
+                                                                 host.ctypes.data, stream))
+
+    def read(self, name: str, limb_ids: Sequence[int], host, stream: int = 0):
+        assert host.dtype.itemsize == 4 and host.flags.c_contiguous and host.size == len(limb_ids) * self.ctx.n
+        self.ctx.lib.check(self.ctx.lib.dll.cerium_program_read(self.h, name.encode(), _u32(limb_ids), len(limb_ids),
+                                                                host.ctypes.data, stream))
 
     def run(self, stream: int = 0):
         self.ctx.lib.check(self.ctx.lib.dll.cerium_program_run(self.h, stream))

@@ -917,6 +917,47 @@ int cerium_ewise(cerium_context* ctx, int op, void* out, size_t out_stride, cons
   });
 }
 
+int cerium_mul_plain_periodic(cerium_context* ctx, void* out, size_t out_stride, const void* a, size_t a_stride,
+                              const void* pt, size_t pt_stride, int log2_repeat, const void* addend, size_t addend_stride,
+                              const uint32_t* prime_idx, int count, void* stream) {
+  if (!ctx) return fail(CERIUM_ERR_INVALID, "mul_plain_periodic: null context");
+  if (count < 0) return fail(CERIUM_ERR_INVALID, "mul_plain_periodic: negative count");
+  if (log2_repeat < 0 || log2_repeat > ctx->logn) return fail(CERIUM_ERR_INVALID, "mul_plain_periodic: repeat count out of range");
+  if (count == 0) return CERIUM_OK;
+  if (!prime_idx) return fail(CERIUM_ERR_INVALID, "mul_plain_periodic: null prime_idx");
+  const size_t wb = ctx->word_bytes();
+  if (int rc = check_stack(out, out_stride, wb, "mul_plain_periodic: out")) return rc;
+  if (int rc = check_stack(a, a_stride, wb, "mul_plain_periodic: a")) return rc;
+  if (!pt) return fail(CERIUM_ERR_INVALID, "mul_plain_periodic: null plaintext");
+  if (pt_stride < ((size_t)kN >> log2_repeat)) return fail(CERIUM_ERR_INVALID, "mul_plain_periodic: plaintext stride is smaller than one period");
+  if (addend)
+    if (int rc = check_stack(addend, addend_stride, wb, "mul_plain_periodic: addend")) return rc;
+  for (int i = 0; i < count; i++)
+    if (prime_idx[i] >= (uint32_t)ctx->n_primes) return fail(CERIUM_ERR_INVALID, "mul_plain_periodic: prime index out of range");
+  DeviceGuard guard(ctx->device);
+  cudaStream_t s = (cudaStream_t)stream;
+  return dispatch_word(ctx->word_bits, [&](auto tag) -> int {
+    using W = decltype(tag);
+    using V = Vec16<W>;
+    const PrimeConst<W>* pcs = static_cast<const PrimeConst<W>*>(ctx->d_pcs);
+    for (int first = 0; first < count; first += kEwMaxLimbs) {
+      const int cnt = std::min(kEwMaxLimbs, count - first);
+      EwArgs<W> g{};
+      g.out = {static_cast<W*>(out) + (size_t)first * out_stride, out_stride};
+      g.a = {const_cast<W*>(static_cast<const W*>(a)) + (size_t)first * a_stride, a_stride};
+      g.b = {const_cast<W*>(static_cast<const W*>(pt)) + (size_t)first * pt_stride, pt_stride};
+      if (addend) g.c = {const_cast<W*>(static_cast<const W*>(addend)) + (size_t)first * addend_stride, addend_stride};
+      g.shift = log2_repeat;
+      for (int k = 0; k < cnt; k++) g.prime[k] = (uint8_t)prime_idx[first + k];
+      const dim3 grid(kN / (kEwThreads * V::kLanes), cnt);
+      if (addend) { auto kfn = ewise_kernel<W, kEwMadPeriodic>; CERIUM_LAUNCH(kfn, grid, kEwThreads, 0, s, g, pcs); }
+      else { auto kfn = ewise_kernel<W, kEwMulPeriodic>; CERIUM_LAUNCH(kfn, grid, kEwThreads, 0, s, g, pcs); }
+    }
+    CERIUM_LAUNCH_CHECK("mul_plain_periodic");
+    return CERIUM_OK;
+  });
+}
+
 int cerium_tensor(cerium_context* ctx, void* d0, void* d1, void* d2, const void* a0, const void* a1,
                   const void* b0, const void* b1, size_t stride, const uint32_t* prime_idx, int count,
                   void* stream) {

@@ -69,6 +69,8 @@ enum EwOp : int {
   kEwPmu = 5,   // out = a + b * s[limb]
   kEwMulScalar = 6,  // out = a * s[limb]
   kEwReduce = 7,     // out = a mod q for ANY word a (sums of residues after a reduce-scatter / all-reduce)
+  kEwMulPeriodic = 8,  // out = a * b[i >> shift]      (b: a plaintext that repeats, stored once per period)
+  kEwMadPeriodic = 9,  // out = a * b[i >> shift] + c
 };
 
 template <typename W>
@@ -77,6 +79,7 @@ struct EwArgs {
   W scalar[kEwMaxLimbs];        // per limb (kEwPmu, kEwMulScalar)
   W scalar_shoup[kEwMaxLimbs];  // per limb
   uint8_t prime[kEwMaxLimbs];
+  int shift;                    // kEwMulPeriodic / kEwMadPeriodic: log2 of the repeat count
 };
 
 // grid = (N / (256 * lanes), limbs), block = 256.
@@ -94,7 +97,11 @@ __global__ void __launch_bounds__(kEwThreads)
   V bb, cc;
   if (kOp == kEwAdd || kOp == kEwSub || kOp == kEwMul || kOp == kEwMad || kOp == kEwPmu)
     bb = V::load(g.b.at(b, idx));
-  if (kOp == kEwMad) cc = V::load(g.c.at(b, idx));
+  if (kOp == kEwMad || kOp == kEwMadPeriodic) cc = V::load(g.c.at(b, idx));
+  if (kOp == kEwMulPeriodic || kOp == kEwMadPeriodic) {
+#pragma unroll
+    for (int l = 0; l < V::kLanes; l++) bb.v[l] = *g.b.at(b, (idx + l) >> g.shift);
+  }
   W s = 0, ss = 0;
   if (kOp == kEwPmu || kOp == kEwMulScalar) {
     s = g.scalar[b];
@@ -105,8 +112,8 @@ __global__ void __launch_bounds__(kEwThreads)
     if (kOp == kEwAdd) o.v[l] = add_mod<W>(a.v[l], bb.v[l], pc.q);
     if (kOp == kEwSub) o.v[l] = sub_mod<W>(a.v[l], bb.v[l], pc.q);
     if (kOp == kEwNeg) o.v[l] = a.v[l] ? pc.q - a.v[l] : (W)0;
-    if (kOp == kEwMul) o.v[l] = mul_mod<W>(a.v[l], bb.v[l], pc);
-    if (kOp == kEwMad) o.v[l] = add_mod<W>(mul_mod<W>(a.v[l], bb.v[l], pc), cc.v[l], pc.q);
+    if (kOp == kEwMul || kOp == kEwMulPeriodic) o.v[l] = mul_mod<W>(a.v[l], bb.v[l], pc);
+    if (kOp == kEwMad || kOp == kEwMadPeriodic) o.v[l] = add_mod<W>(mul_mod<W>(a.v[l], bb.v[l], pc), cc.v[l], pc.q);
     if (kOp == kEwPmu)
       o.v[l] = add_mod<W>(a.v[l], csub<W>(mul_shoup_lazy<W>(bb.v[l], s, ss, pc.q), pc.q), pc.q);
     if (kOp == kEwMulScalar) o.v[l] = csub<W>(mul_shoup_lazy<W>(a.v[l], s, ss, pc.q), pc.q);

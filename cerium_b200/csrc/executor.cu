@@ -597,6 +597,37 @@ int cerium_program_memory(cerium_program* p, const char* term, void** device_ptr
   return CERIUM_OK;
 }
 
+static int program_copy(cerium_program* p, const char* name, const uint32_t* limb_ids, int n_limbs, void* host,
+                        void* stream, bool to_device) {
+  const char* what = to_device ? "program_write" : "program_read";
+  if (!p || !name || !limb_ids || !host || n_limbs < 0) return fail(CERIUM_ERR_INVALID, std::string(what) + ": null argument");
+  DeviceGuard guard(p->ctx->device);
+  if (!guard.ok) return fail(CERIUM_ERR_CUDA, std::string(what) + ": cannot select device");
+  const size_t bytes = ((size_t)1 << p->ctx->logn) * sizeof(uint32_t);
+  cudaStream_t st = (cudaStream_t)stream;
+  for (int i = 0; i < n_limbs; ++i) {
+    const std::string term = std::string(name) + "(" + std::to_string(limb_ids[i]) + ")";
+    auto it = p->memory.find(term);
+    if (it == p->memory.end()) return fail(CERIUM_ERR_INVALID, std::string(what) + ": the function names no memory term '" + term + "'");
+    char* h = (char*)host + (size_t)i * bytes;
+    cudaError_t e = to_device ? cudaMemcpyAsync(it->second, h, bytes, cudaMemcpyHostToDevice, st)
+                              : cudaMemcpyAsync(h, it->second, bytes, cudaMemcpyDeviceToHost, st);
+    if (e != cudaSuccess) return fail(CERIUM_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+  }
+  cudaError_t e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return fail(CERIUM_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+  return CERIUM_OK;
+}
+
+int cerium_program_write(cerium_program* p, const char* name, const uint32_t* limb_ids, int n_limbs, const void* host,
+                         void* stream) {
+  return program_copy(p, name, limb_ids, n_limbs, const_cast<void*>(host), stream, true);
+}
+
+int cerium_program_read(cerium_program* p, const char* name, const uint32_t* limb_ids, int n_limbs, void* host, void* stream) {
+  return program_copy(p, name, limb_ids, n_limbs, host, stream, false);
+}
+
 int cerium_program_run(cerium_program* p, void* stream) {
   if (!p) return fail(CERIUM_ERR_INVALID, "program_run: null program");
   cerium_context* ctx = p->ctx;
@@ -658,6 +689,8 @@ int cerium_program_load(cerium_context*, cerium_program**, const char*, const ch
 int cerium_program_destroy(cerium_program*) { return CERIUM_OK; }
 int cerium_program_num_steps(const cerium_program*) { return 0; }
 int cerium_program_memory(cerium_program*, const char*, void**) { return CERIUM_ERR_UNSUPPORTED; }
+int cerium_program_write(cerium_program*, const char*, const uint32_t*, int, const void*, void*) { return CERIUM_ERR_UNSUPPORTED; }
+int cerium_program_read(cerium_program*, const char*, const uint32_t*, int, void*, void*) { return CERIUM_ERR_UNSUPPORTED; }
 int cerium_program_run(cerium_program*, void*) { return CERIUM_ERR_UNSUPPORTED; }
 }
 

@@ -179,6 +179,19 @@ CERIUM_API int cerium_tensor(cerium_context *ctx, void *d0, void *d1, void *d2, 
                   const uint32_t *prime_idx, int count, void *stream);
 
 /*
+ * Multiplication by a PERIODIC plaintext: a plaintext whose slots repeat 2^log2_repeat times is stored
+ * once per period, N >> log2_repeat words per limb in NTT form (the reference's encoder transforms only
+ * the first log2(N) - log2_repeat levels, cerium/runtime/io/ckks-encoder.h:205-372), and the generated
+ * kernels read it as pt[i >> log2_repeat] (cerium/compiler/backend/cuda_kernel.cc:919-934):
+ *   out[l][i] = a[l][i] * pt[l][i >> log2_repeat] (+ addend[l][i] when addend is not NULL)   mod q_l
+ * pt_stride is the distance between the plaintext's limbs in words (>= N >> log2_repeat).
+ */
+CERIUM_API int cerium_mul_plain_periodic(cerium_context *ctx, void *out, size_t out_stride, const void *a,
+                                         size_t a_stride, const void *pt, size_t pt_stride, int log2_repeat,
+                                         const void *addend, size_t addend_stride, const uint32_t *prime_idx,
+                                         int count, void *stream);
+
+/*
  * Galois automorphism in NTT form: out[i][k] = in[i][pi(k)] for `count` limbs, pi as built by
  * GaloisTool::generate_table_ntt (cerium/runtime/math/galois.cpp:30-62).  in and out must not
  * overlap.  cerium_galois_elt_from_step restates get_elt_from_step (galois.cpp:79-113):
@@ -576,6 +589,11 @@ CERIUM_API void *cerium_function_map_launcher(const char *type, int cugraph);
  *   cerium_program_memory          device address of a named memory term, e.g. "i1(0)": the caller
  *                                  writes inputs and keys there before a run and reads outputs after it
  *                                  (names and meanings are listed in the function's `inputs<p>` file)
+ *   cerium_program_write / _read   copy `n_limbs` limbs between host memory ([n_limbs][N] 32-bit words) and
+ *                                  the memory terms "<name>(<limb_ids[i]>)", as the reference's
+ *                                  copy_ciphertext_inputs_to_gpu / get_program_outputs do
+ *                                  (cerium/runtime/execution/function_io.cpp:958-1100, :1360-1420);
+ *                                  both wait for `stream` before they return
  *   cerium_program_inspect         parses only (no device): one line per record,
  *                                  "id type #outputs #inputs #bases #rots #units #sud #pmu"
  *   comm                           the partitions of a function compiled for several GPUs run as the
@@ -592,6 +610,10 @@ CERIUM_API int cerium_program_load(cerium_context *ctx, cerium_program **out, co
 CERIUM_API int cerium_program_destroy(cerium_program *prog);
 CERIUM_API int cerium_program_num_steps(const cerium_program *prog);
 CERIUM_API int cerium_program_memory(cerium_program *prog, const char *term, void **device_ptr);
+CERIUM_API int cerium_program_write(cerium_program *prog, const char *name, const uint32_t *limb_ids, int n_limbs,
+                                    const void *host, void *stream);
+CERIUM_API int cerium_program_read(cerium_program *prog, const char *name, const uint32_t *limb_ids, int n_limbs,
+                                   void *host, void *stream);
 CERIUM_API int cerium_program_run(cerium_program *prog, void *stream);
 CERIUM_API int cerium_program_inspect(const char *functions_path, char *buf, size_t buf_bytes, int *n_records);
 

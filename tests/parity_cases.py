@@ -274,6 +274,16 @@ def case_ewise(be, word_bits):
     h.ctx.ewise(_capi.EW_MUL_SCALAR, h.p(out), h.p(da), idx, scalars=scal)
     want = np.stack([oracle.ew("mul", mods[p], a[i], np.full(N, scal[i], dtype=np.uint64)) for i, p in enumerate(idx)])
     assert np.array_equal(h.down(out), want)
+    # periodic plaintext: stored once per period, read as pt[i >> shift] (cuda_kernel.cc:919-934)
+    for shift in (0, 1, 6):
+        period = N >> shift
+        pt = np.stack([rng.integers(0, mods[p], size=period, dtype=np.uint64) for p in idx])
+        dpt = h.up(pt)
+        full = np.repeat(pt, 1 << shift, axis=1)
+        h.ctx.mul_plain_periodic(h.p(out), h.p(da), h.p(dpt), shift, idx)
+        assert np.array_equal(h.down(out), expect("mul", arrs=(a, full))), "periodic plaintext product, shift %d" % shift
+        h.ctx.mul_plain_periodic(h.p(out), h.p(da), h.p(dpt), shift, idx, addend=h.p(dc))
+        assert np.array_equal(h.down(out), expect("mad", arrs=(a, full, c))), "periodic plaintext multiply-add, shift %d" % shift
     # tensor product
     a1, b1 = rand_limbs(rng, mods, idx), rand_limbs(rng, mods, idx)
     d0, d1, d2 = h.new(len(idx), N), h.new(len(idx), N), h.new(len(idx), N)

@@ -1,0 +1,238 @@
+"""The reference's Python runtime surface (cerium.runtime names) over this library.
+
+CPU tests run the façade on the emulation build (host memory) and check its key material with the
+oracle's operators: a ciphertext it encrypts, rotated / multiplied by the ORACLE with keys it generated,
+must decrypt to the rotated / multiplied message.  GPU tests follow the reference's own example driver
+step for step (examples/common.py:83-142: context, keys, IOGenerator, FusedKernelProgram.make_program,
+copy_ciphertext_inputs_to_gpu, run, get_program_outputs, decrypt_and_decode, np.allclose with its
+tolerances) on the programs the reference's compiler produced for examples/rotation,
+examples/relinearization and examples/rescale, and report the precision in bits."""
+import os
+import random
+import shutil
+
+import numpy as np
+import pytest
+
+from cerium_b200 import params, runtime
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PROGS = os.path.join(ROOT, "tests", "golden", "programs")
+PLUGINS = os.path.join(ROOT, "oracle", "_ref", "programs")
+SLOTS, LEVEL = 32 * 1024, 12                                    # examples/common.py:26-27
+PRIMES = params.reference_primes_28bit(64, 16)                   # examples/primes.py
+Q_IDX = list(range(LEVEL))
+P_IDX = list(range(52, 64))
+
+
+def sample_vector(seed):
+    return np.random.default_rng(seed).integers(0, 5, size=SLOTS).astype(float)       # examples/common.py:67-69
+
+
+def _secret_key(rng, hamming_weight):                                                   # examples/common.py:72-76
+    key = [0] * (2 * SLOTS)
+    for position in rng.sample(range(2 * SLOTS), hamming_weight):
+        key[position] = rng.choice((-1, 1))
+    return key
+
+
+def _keys(context):
+    rng = random.Random(10)
+    seed = np.random.default_rng(10).integers(0, 2 ** 32, size=8, dtype=np.uint64).tolist()
+    ectx = runtime.CKKSEncryptorContext(context, _secret_key(rng, SLOTS), _secret_key(rng, 32), seed)
+    return ectx, runtime.CKKSEncryptor(ectx, seed)
+
+
+def _bits(actual, expected):
+    return float(-np.log2(np.max(np.abs(np.asarray(actual) - np.asarray(expected))) + 2.0 ** -200))
+
+
+# ---------------------------------------------------------------------------------------------------------
+# CPU: the façade on the emulation build, evaluated by the oracle
+# ---------------------------------------------------------------------------------------------------------
+
+@pytest.fixture(scope="module")
+def emu():
+    from tests.backends import EmuBackend
+    be = EmuBackend()
+    context = runtime.Context(SLOTS, PRIMES, lib=be.lib, memory="host")
+    assert context.coeff_count == 2 * SLOTS
+    ectx, enc = _keys(context)
+    return context, ectx, enc
+
+
+def test_encrypt_decrypt_round_trip(emu):
+    _context, _ectx, enc = emu
+    x = sample_vector(1)
+    for scale in (1 << 56, 1 << 84):
+        ct = enc.encode_and_encrypt(x, scale, Q_IDX)
+        assert ct.c0.shape == (LEVEL, 2 * SLOTS) and ct.c0.dtype == np.uint32 and ct.rns_base_ids == Q_IDX
+        assert _bits(enc.decrypt_and_decode(ct, scale), x) > 40
+    z = np.exp(2j * np.pi * np.arange(SLOTS) / SLOTS)                     # complex slots
+    ct = enc.encode_and_encrypt(z, 1 << 56, Q_IDX[:3])
+    assert _bits(enc.decrypt_and_decode(ct, 1 << 56), z) > 40
+    ct = enc.encode_and_encrypt(2.5, 1 << 56, Q_IDX[:3])                  # a scalar fills every slot
+    assert _bits(enc.decrypt_and_decode(ct, 1 << 56), np.full(SLOTS, 2.5)) > 40
+
+
+def _key_tensor(enc, key_type, rot):
+    """One-digit key in the oracle's layout [1][2][Q limbs, extension limbs ascending][n]."""
+    c0, c1 = enc.generate_evalkey(key_type, LEVEL, LEVEL, rot, Q_IDX)
+    ids = enc.key_rns_base_ids(LEVEL, LEVEL)
+    assert ids == Q_IDX + P_IDX[::-1]                                     # extension primes from the top of the chain
+    order = [ids.index(p) for p in Q_IDX + P_IDX]
+    return np.stack([np.stack([c0.numpy()[order], c1.numpy()[order]])]).astype(np.uint64)
+
+
+def test_generated_keys_work_under_the_oracles_operators(emu):
+    import oracle
+    context, _ectx, enc = emu
+    orc = oracle.OracleContext(16, PRIMES)
+    x, y = sample_vector(1), sample_vector(2)
+    cx = enc.encode_and_encrypt(x, 1 << 84, Q_IDX)
+    # rotation by one slot to the left with the key of step 1 (examples/rotation)
+    evk = _key_tensor(enc, runtime.KEY_ROT, 1)
+    elt = oracle.galois_elt_from_step(1, 16)
+    r0, r1 = orc.hrot(oracle.BCONV_LAZY, oracle.ROUND_FLOOR, Q_IDX, P_IDX, 1, elt,
+                      cx.c0.astype(np.uint64), cx.c1.astype(np.uint64), evk)
+    got = enc.decrypt_and_decode(runtime.Ciphertext(r0.astype(np.uint32), r1.astype(np.uint32), Q_IDX), 1 << 84)
+    assert np.allclose(got, np.roll(x, -1), rtol=1e-5, atol=1e-4), _bits(got, np.roll(x, -1))
+    # conjugation key: step 0
+    z = np.exp(2j * np.pi * np.arange(SLOTS) / SLOTS)
+    cz = enc.encode_and_encrypt(z, 1 << 84, Q_IDX)
+    evk = _key_tensor(enc, runtime.KEY_CON, 0)
+    r0, r1 = orc.hrot(oracle.BCONV_LAZY, oracle.ROUND_FLOOR, Q_IDX, P_IDX, 1, 2 * context.n - 1,
+                      cz.c0.astype(np.uint64), cz.c1.astype(np.uint64), evk)
+    got = enc.decrypt_and_decode(runtime.Ciphertext(r0.astype(np.uint32), r1.astype(np.uint32), Q_IDX), 1 << 84)
+    assert np.allclose(got, np.conj(z), rtol=1e-5, atol=1e-4)
+    # multiplication + relinearisation with the key of s^2 (examples/relinearization)
+    ax = enc.encode_and_encrypt(x, 1 << 56, Q_IDX)
+    ay = enc.encode_and_encrypt(y, 1 << 56, Q_IDX)
+    evk = _key_tensor(enc, runtime.KEY_MUL, 0)
+    u = [a.astype(np.uint64) for a in (ax.c0, ax.c1, ay.c0, ay.c1)]
+    r0, r1 = orc.hmult_relin(oracle.BCONV_LAZY, oracle.ROUND_FLOOR, False, Q_IDX, P_IDX, 1, *u, evk)
+    got = enc.decrypt_and_decode(runtime.Ciphertext(r0.astype(np.uint32), r1.astype(np.uint32), Q_IDX), float(1 << 112))
+    assert np.allclose(got, x * y, rtol=1e-5, atol=1e-4), _bits(got, x * y)
+
+
+def test_generator_writes_what_program_inputs_asks_for(emu, tmp_path):
+    from cerium_b200 import containers
+    context, ectx, _enc = emu
+    gen = runtime.IOGenerator(context)
+    # evaluation keys of the compiled rotation: one entry (one digit), both polynomials on Q and extension limbs
+    pin = os.path.join(PROGS, "rotation_1gpu", "program_inputs")
+    streams = runtime.parse_program_inputs(pin)
+    assert [t for t, _, _ in streams["Ciphertext Stream"]] == ["i2", "i1"]
+    assert len(streams["Evalkey Stream"]) == 4 and streams["Plaintext Stream"] == []
+    gen.generate_and_serialize_evalkeys(str(tmp_path / "evalkeys"), pin, ectx)
+    c = containers.read(str(tmp_path / "evalkeys"))
+    assert c.kind == "evalkeys" and list(c.entries) == ["1:12:12:1:[0,1,2,3,4,5,6,7,8,9,10,11]"]
+    assert sorted(c.entries["1:12:12:1:[0,1,2,3,4,5,6,7,8,9,10,11]"].limb_ids()) == Q_IDX + P_IDX
+    assert containers.evalkey_tensor(c, 1, 12, 12, 1, Q_IDX + P_IDX).shape == (1, 2, 24, 2 * SLOTS)
+    # the plaintext of the compiled rescale program, and ciphertext inputs by name
+    pin = os.path.join(PROGS, "rescale_1gpu", "program_inputs")
+    raw = runtime.RawInputsWrapper({"x": (sample_vector(1), 1 << 56), "factor": (sample_vector(2) + 1, 1 << 28)})
+    gen.generate_and_serialize_plaintexts(str(tmp_path / "plaintexts"), pin, raw)
+    c = containers.read(str(tmp_path / "plaintexts"))
+    assert list(c.entries) == ["factor"] and c.entries["factor"].limb_ids() == Q_IDX
+    cts = gen.generate_ciphertext_inputs(pin, raw, ectx)
+    assert list(cts) == ["x"] and cts["x"].rns_base_ids == Q_IDX
+    gen.generate_and_serialize_ciphertexts(str(tmp_path / "ciphertexts"), pin, raw, ectx)
+    back = runtime.IOGenerator.deserialize_ciphertexts(context, str(tmp_path / "ciphertexts"))
+    assert list(back) == ["x"] and back["x"].c0.shape == (LEVEL, 2 * SLOTS)
+    with pytest.raises(KeyError):
+        gen.generate_ciphertext_inputs(pin, runtime.RawInputsWrapper({}), ectx)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# GPU: the reference's example driver, with this module in place of cerium.runtime
+# ---------------------------------------------------------------------------------------------------------
+
+def _compiled(tmp_path, example):
+    """<compiled>/main_1gpus/ as the reference's build leaves it: records, input lists, the generated plugin."""
+    src = os.path.join(PROGS, example + "_1gpu")
+    orig = os.path.join(PLUGINS, example + "_1gpu", "function_map_0.orig.so")
+    if not os.path.exists(orig):
+        pytest.skip("the generated plugin of %s was not built (tests/golden/programs/make_programs.py)" % example)
+    d = tmp_path / "compiled" / "main_1gpus"
+    d.mkdir(parents=True)
+    for f in ("functions0", "inputs0", "program_inputs"):
+        shutil.copy(os.path.join(src, f), d / f)
+    shutil.copy(orig, d / "function_map_0.so")
+    return tmp_path / "compiled"
+
+
+def run_program(tmp_path, example, raw_inputs, expected, output_scale, atol=1e-4):
+    """examples/common.py:83-142 with one import changed."""
+    name, gpus = "main_1gpus", 1
+    compiled = _compiled(tmp_path, example)
+    context = runtime.Context(SLOTS, PRIMES)
+    encryptor_context, encryptor = _keys(context)
+    inputs = runtime.RawInputsWrapper(raw_inputs)
+    generator = runtime.IOGenerator(context)
+    program_inputs = str(compiled / name / "program_inputs")
+    for function_dir in sorted(compiled.glob("*_%dgpus" % gpus)):
+        function_inputs = function_dir / "program_inputs"
+        generator.generate_and_serialize_evalkeys(str(function_dir / "evalkeys"), str(function_inputs), encryptor_context)
+        generator.generate_and_serialize_plaintexts(str(function_dir / "plaintexts"), str(function_inputs), inputs)
+    program = runtime.FusedKernelProgram(context, str(compiled), name)
+    functions = program.make_program(gpus, {name: {"use_cudagraph": "True"}}, inputs)
+    encrypted_inputs = generator.generate_ciphertext_inputs(program_inputs, inputs, encryptor_context)
+    functions[name].copy_ciphertext_inputs_to_gpu(str(compiled / name / "inputs"), gpus, encrypted_inputs)
+    program.run()
+    encrypted_output = functions[name].get_program_outputs()["z"]
+    actual = np.asarray(encryptor.decrypt_and_decode(encrypted_output, output_scale))
+    expected = np.asarray(expected)
+    bits = _bits(actual, expected)
+    print("%s: maximum absolute error %.3e (%.1f bits)" % (example, float(np.max(np.abs(actual - expected))), bits))
+    assert np.allclose(actual, expected, rtol=1e-5, atol=atol), "%s output differs from its expected result" % example
+    return bits
+
+
+@pytest.mark.gpu
+def test_rotation_example(tmp_path):
+    x = sample_vector(1)
+    scale = 1 << 84
+    assert run_program(tmp_path, "rotation", {"x": (x, scale)}, np.roll(x, -1), scale) > 13      # examples/rotation/runner.py
+
+
+@pytest.mark.gpu
+def test_relinearization_example(tmp_path):
+    x, y = sample_vector(1), sample_vector(2)
+    scale = 1 << 56
+    assert run_program(tmp_path, "relinearization", {"x": (x, scale), "y": (y, scale)}, x * y, float(scale * scale)) > 13
+
+
+@pytest.mark.gpu
+def test_rescale_example(tmp_path):
+    x, factor = sample_vector(1), sample_vector(2) + 1
+    ciphertext_scale, plaintext_scale = 1 << 56, 1 << 28
+    output_scale = ciphertext_scale * plaintext_scale / PRIMES[LEVEL - 1]                    # examples/rescale/runner.py
+    assert run_program(tmp_path, "rescale", {"x": (x, ciphertext_scale), "factor": (factor, plaintext_scale)},
+                       x * factor, output_scale) > 13
+
+
+def test_periodic_plaintext_is_the_subsampled_transform(emu):
+    """A plaintext that repeats every 1024 slots: the compact form (one word per run of 32) expands to the
+    full transform, and multiplying by it through the library's periodic entry point gives the product slots."""
+    import torch
+    context, _ectx, enc = emu
+    pe = runtime._PlainEncoder(context)
+    period = 1024
+    v = np.random.default_rng(3).integers(1, 5, size=period).astype(float)
+    idx = Q_IDX[:3]
+    compact = pe.encode(v, 1 << 28, idx, period)
+    full = pe.encode(np.tile(v, SLOTS // period), 1 << 28, idx)
+    assert compact.shape == (3, 2 * period)
+    assert torch.equal(compact.repeat_interleave(SLOTS // period, dim=1), full)
+    x = sample_vector(1)
+    ct = enc.encode_and_encrypt(x, 1 << 28, idx)
+    pt = compact.to(torch.int32).contiguous()
+    outs = []
+    for c in (ct.c0, ct.c1):
+        a = torch.from_numpy(c.view(np.int32).copy())
+        o = torch.empty_like(a)
+        context.handle.mul_plain_periodic(o.data_ptr(), a.data_ptr(), pt.data_ptr(), 5, idx)
+        outs.append(o.numpy().view(np.uint32))
+    got = enc.decrypt_and_decode(runtime.Ciphertext(outs[0], outs[1], idx), float(1 << 56))
+    assert np.allclose(got, x * np.tile(v, SLOTS // period), rtol=1e-5, atol=1e-4)
