@@ -21,8 +21,11 @@
 // evaluator.cpp:58-92, 233-260), since they are part of that launcher contract.  A drm record (the
 // all-gather of limbs between partitions, Evaluator::drm, evaluator.cpp:1154-1251) runs on the
 // communicator given at load: its sources are packed into this rank's block of a staging buffer,
-// gathered in place, and unpacked to the record's destinations.  Not served: rsv, call, ags and ard
-// records - a function that holds one is refused at load.
+// gathered in place, and unpacked to the record's destinations.  A call record loads the called function
+// from the same program directory and binds its argument and result limbs to the caller's (the reference
+// copies them in and out, function_execution.cpp:265-331, 508-600).  Not served: rsv, ags and ard records
+// and remapable inputs - a function that holds one is refused at load.
+#include <algorithm>
 #include <cstring>
 #include <fstream>
 #include <map>
@@ -53,6 +56,8 @@ struct Record {
   std::string base_conv;
   std::vector<int32_t> rots;
   std::vector<uint32_t> sud, pmu, rsv, bases;
+  std::string function_name;    // call records: the callee
+  std::string function_args;    // call records: "<var:c0(limb)~caller term>, ..."
 };
 
 std::string strip(const std::string& v) {
@@ -145,6 +150,8 @@ bool parse_records(const std::string& path, std::vector<Record>& out, std::strin
       r.bases = numbers<uint32_t>(field["bases"]);
       r.comm_srcs = terms(field["comm_srcs"]);
       r.comm_dests = terms(field["comm_dests"]);
+      r.function_name = strip(field["function_name"]);
+      r.function_args = strip(field["function_args"]);
       if (!strip(field["comm_size"]).empty()) r.comm_size = std::stoul(strip(field["comm_size"]));
       if (!strip(field["comm_num_limbs"]).empty()) r.comm_num_limbs = std::stoul(strip(field["comm_num_limbs"]));
     } catch (const std::exception& e) {
@@ -187,6 +194,61 @@ std::vector<BcuSpec> parse_base_conv(const std::string& v) {
   return out;
 }
 
+// "<value:c0(3)~i1(3)>, <doubled:c1(0)~v4(0)>" -> (callee object "value:c0", limb 3, caller term "i1(3)")
+struct CallArg {
+  std::string object;
+  uint32_t limb;
+  std::string caller_term;
+};
+std::vector<CallArg> parse_call_args(const std::string& v) {
+  std::vector<CallArg> out;
+  const std::string s = strip(v);
+  size_t pos = 0;
+  while ((pos = s.find('<', pos)) != std::string::npos) {
+    const size_t end = s.find('>', pos);
+    if (end == std::string::npos) break;
+    const std::string body = s.substr(pos + 1, end - pos - 1);
+    pos = end + 1;
+    const size_t tilde = body.find('~'), l = body.find('('), r = body.find(')');
+    if (tilde == std::string::npos || l == std::string::npos || r == std::string::npos || l > tilde || r > tilde)
+      throw std::runtime_error("bad call argument <" + body + ">");
+    out.push_back({body.substr(0, l), (uint32_t)std::stoul(body.substr(l + 1, r - l - 1)), body.substr(tilde + 1)});
+  }
+  return out;
+}
+
+// The "Function Input Stream" / "Function Output Stream" lines of a callee's inputs<p> file
+// ("f1 | value:c0 | [0,1,...]"): object -> the callee's own term for it.
+bool parse_function_streams(const std::string& path, std::map<std::string, std::string>& object_to_term,
+                            std::map<std::string, bool>& is_output, std::string& err) {
+  std::ifstream f(path);
+  if (!f.is_open()) {
+    err = "cannot open " + path;
+    return false;
+  }
+  std::string line;
+  bool inside = false, output = false;
+  while (std::getline(f, line)) {
+    const std::string t = strip(line);
+    if (t.empty()) continue;
+    if (t.size() > 7 && t.compare(t.size() - 7, 7, "Stream:") == 0) {
+      inside = t.compare(0, 8, "Function") == 0;
+      output = t.find("Output") != std::string::npos;
+      continue;
+    }
+    if (t == ";") {
+      inside = false;
+      continue;
+    }
+    if (!inside) continue;
+    const size_t a = t.find('|'), b = t.find('|', a + 1);
+    if (a == std::string::npos || b == std::string::npos) continue;
+    object_to_term[t.substr(a + 1, b - a - 1)] = t.substr(0, a);
+    is_output[t.substr(a + 1, b - a - 1)] = output;
+  }
+  return true;
+}
+
 }  // namespace
 
 #if !defined(CERIUM_EMU)
@@ -213,7 +275,9 @@ struct Unit {  // one base-conversion unit: input block, output block, the bases
 constexpr int kUnitMaxIn = 48, kUnitMaxOut = 64;  // DeviceBaseConverter's block sizes (evaluator.h:36-38)
 
 struct Step {
-  enum Kind { Ewi, Ntt, Int, Sud, Bco, Drm } kind;
+  enum Kind { Ewi, Ntt, Int, Sud, Bco, Drm, Call } kind;
+  cerium_program* callee = nullptr;  // call: the called function, its argument terms bound to this function's memory
+  std::vector<std::pair<W*, const W*>> copy_back;  // call: results whose destination is also an argument (dst, src)
   // drm: host lists of the limbs to pack (this rank's sources) and to unpack (every rank's block)
   std::vector<const W*> pack;
   std::vector<W*> unpack;
@@ -252,7 +316,17 @@ struct cerium_program {
   std::map<uint32_t, const uint32_t*> rot_tables;      // Galois element -> device inverse table
   const W *d_moduli = nullptr, *d_ratios = nullptr;
   const uint32_t* d_k = nullptr;
+  std::vector<cerium_program*> callees;               // functions this one calls (owned)
+  std::string functions_path;                          // <programs>/<function>/functions<p>
+  int depth = 0;
 };
+
+namespace {
+constexpr int kMaxCallDepth = 16;
+cerium_program* load_program(cerium_context* ctx, const std::string& functions_path, const std::string& plugin_path,
+                             const std::map<std::string, uint64_t>& scalars, cerium_comm* comm,
+                             const std::map<std::string, W*>& bound, int depth);
+}
 
 namespace {
 
@@ -387,8 +461,63 @@ struct Loader {
     for (const Record& r : recs) {
       const std::string& ty = r.type;
       if (ty == "mov") continue;  // outputs alias inputs: nothing to run (the reference skips them too)
-      if (ty == "rsv" || ty == "call" || ty == "ags" || ty == "ard")
+      if (ty == "rsv" || ty == "ags" || ty == "ard")
         throw std::runtime_error("record " + std::to_string(r.id) + " of type '" + ty + "' is not served by this executor");
+      if (ty == "call") {
+        // The call case of CeriumFunction::make_program / run (function_execution.cpp:265-331, 508-600): the callee
+        // is the function `function_name` of the same program directory; .function_args pairs its argument and
+        // result limbs with THIS function's terms.  The reference copies arguments in and results out around
+        // the callee's run; here the callee's terms are bound to the caller's limbs (no copies), except a
+        // result whose destination is also an argument, which keeps the copy.
+        if (r.function_name.empty()) throw std::runtime_error("call record " + std::to_string(r.id) + " names no function");
+        if (p->depth + 1 > kMaxCallDepth) throw std::runtime_error("calls nest deeper than " + std::to_string(kMaxCallDepth));
+        const size_t slash = p->functions_path.find_last_of('/');
+        const std::string file = slash == std::string::npos ? p->functions_path : p->functions_path.substr(slash + 1);
+        const std::string fdir = slash == std::string::npos ? std::string(".") : p->functions_path.substr(0, slash);
+        const size_t up = fdir.find_last_of('/');
+        const std::string base = up == std::string::npos ? std::string(".") : fdir.substr(0, up);
+        if (file.compare(0, 9, "functions") != 0) throw std::runtime_error("a function that calls another must be loaded from <programs>/<function>/functions<p>");
+        const std::string part = file.substr(9);
+        const std::string cdir = base + "/" + r.function_name;
+        std::map<std::string, std::string> object_to_term;
+        std::map<std::string, bool> is_output;
+        std::string perr;
+        if (!parse_function_streams(cdir + "/inputs" + part, object_to_term, is_output, perr))
+          throw std::runtime_error("call record " + std::to_string(r.id) + ": " + perr);
+        const std::vector<CallArg> args = parse_call_args(r.function_args);
+        std::map<std::string, W*> bound;
+        std::vector<W*> arg_ptrs;
+        std::vector<std::pair<std::string, W*>> late;  // results that must be copied after the run
+        for (int pass = 0; pass < 2; pass++)           // arguments first, so that results can be checked against them
+          for (const CallArg& a : args) {
+            auto ot = object_to_term.find(a.object);
+            if (ot == object_to_term.end()) throw std::runtime_error("function " + r.function_name + " has no argument or result '" + a.object + "'");
+            if (is_output[a.object] != (pass == 1)) continue;
+            const std::string term = ot->second + "(" + std::to_string(a.limb) + ")";
+            W* here = pointer(make_term(a.caller_term));
+            if (pass == 0) {
+              bound[term] = here;
+              arg_ptrs.push_back(here);
+            } else if (std::find(arg_ptrs.begin(), arg_ptrs.end(), here) != arg_ptrs.end()) {
+              late.push_back({term, here});
+            } else {
+              bound[term] = here;
+            }
+          }
+        cerium_program* callee = load_program(ctx, cdir + "/functions" + part, cdir + "/function_map_" + part + ".so",
+                                              scalar_values, p->comm, bound, p->depth + 1);
+        p->callees.push_back(callee);
+        Step s{};
+        s.kind = Step::Call;
+        s.id = r.id;
+        s.callee = callee;
+        for (const auto& l : late) {
+          auto m = callee->memory.find(l.first);
+          if (m != callee->memory.end()) s.copy_back.push_back({l.second, m->second});
+        }
+        p->steps.push_back(s);
+        continue;
+      }
       const std::vector<BcuSpec> specs = parse_base_conv(r.base_conv);
       // unit state changes happen BEFORE the record's terms are resolved (parse_term_base_conv_vec)
       if (ty == "generic" || ty == "int" || ty == "drm")
@@ -536,6 +665,38 @@ struct Loader {
   }
 };
 
+cerium_program* load_program(cerium_context* ctx, const std::string& functions_path, const std::string& plugin_path,
+                             const std::map<std::string, uint64_t>& scalars, cerium_comm* comm,
+                             const std::map<std::string, W*>& bound, int depth) {
+  std::vector<Record> recs;
+  std::string err;
+  if (!parse_records(functions_path, recs, err)) throw std::runtime_error(err);
+  void* h = dlopen(plugin_path.c_str(), RTLD_LAZY | RTLD_LOCAL);
+  if (!h) throw std::runtime_error(std::string("cannot load the plugin: ") + dlerror());
+  typedef const FunctionMapType& (*getter_t)();
+  getter_t getter = (getter_t)dlsym(h, "__GET_FUNCTION_MAP__");
+  if (!getter) {
+    dlclose(h);
+    throw std::runtime_error("the plugin " + plugin_path + " does not export __GET_FUNCTION_MAP__");
+  }
+  auto* p = new cerium_program();
+  p->ctx = ctx;
+  p->comm = comm;
+  p->plugin = h;
+  p->functions_path = functions_path;
+  p->depth = depth;
+  p->memory = bound;  // a called function's argument and result limbs live in its caller
+  try {
+    const FunctionMapType& fmap = getter();
+    Loader ld{p, ctx, {}};
+    ld.build(recs, fmap, scalars);
+  } catch (...) {
+    cerium_program_destroy(p);
+    throw;
+  }
+  return p;
+}
+
 }  // namespace
 
 extern "C" {
@@ -546,41 +707,22 @@ int cerium_program_load(cerium_context* ctx, cerium_program** out, const char* f
   if (n_scalars < 0 || (n_scalars > 0 && (!scalar_terms || !scalar_values))) return fail(CERIUM_ERR_INVALID, "program_load: bad scalar list");
   if (ctx->word_bits != 32)
     return fail(CERIUM_ERR_UNSUPPORTED, "program_load: compiled programs carry generated 32-bit kernels; the context must use 32-bit words");
-  std::vector<Record> recs;
-  std::string err;
-  if (!parse_records(functions_path, recs, err)) return fail(CERIUM_ERR_INVALID, "program_load: " + err);
   DeviceGuard guard(ctx->device);
   if (!guard.ok) return fail(CERIUM_ERR_CUDA, "program_load: cannot select device");
-  void* h = dlopen(plugin_path, RTLD_LAZY | RTLD_LOCAL);
-  if (!h) return fail(CERIUM_ERR_INVALID, std::string("program_load: cannot load the plugin: ") + dlerror());
-  typedef const FunctionMapType& (*getter_t)();
-  getter_t getter = (getter_t)dlsym(h, "__GET_FUNCTION_MAP__");
-  if (!getter) {
-    dlclose(h);
-    return fail(CERIUM_ERR_INVALID, "program_load: the plugin does not export __GET_FUNCTION_MAP__");
-  }
-  auto* p = new cerium_program();
-  p->ctx = ctx;
-  p->comm = comm;
-  p->plugin = h;
   std::map<std::string, uint64_t> scalars;
   for (int i = 0; i < n_scalars; i++) scalars[strip(scalar_terms[i])] = scalar_values[i];
   try {
-    const FunctionMapType& fmap = getter();
-    Loader ld{p, ctx, {}};
-    ld.build(recs, fmap, scalars);
+    *out = load_program(ctx, functions_path, plugin_path, scalars, comm, {}, 0);
   } catch (const std::exception& e) {
-    const std::string msg = e.what();
-    cerium_program_destroy(p);
-    return fail(CERIUM_ERR_INVALID, "program_load: " + msg);
+    return fail(CERIUM_ERR_INVALID, std::string("program_load: ") + e.what());
   }
-  *out = p;
   return CERIUM_OK;
 }
 
 int cerium_program_destroy(cerium_program* p) {
   if (!p) return CERIUM_OK;
   DeviceGuard guard(p->ctx->device);
+  for (cerium_program* c : p->callees) cerium_program_destroy(c);
   for (void* d : p->allocs) cudaFree(d);
   // the plugin stays loaded: its maps are referenced for the life of the process
   delete p;
@@ -628,14 +770,7 @@ int cerium_program_read(cerium_program* p, const char* name, const uint32_t* lim
   return program_copy(p, name, limb_ids, n_limbs, host, stream, false);
 }
 
-int cerium_program_run(cerium_program* p, void* stream) {
-  if (!p) return fail(CERIUM_ERR_INVALID, "program_run: null program");
-  cerium_context* ctx = p->ctx;
-  DeviceGuard guard(ctx->device);
-  if (!guard.ok) return fail(CERIUM_ERR_CUDA, "program_run: cannot select device");
-  // the launchers of this library find their tables through the context bound to the device
-  if (int rc = cerium_function_map_bind(ctx, ctx->device)) return fail(rc, "program_run: cannot bind the context");
-  cudaStream_t st = (cudaStream_t)stream;
+static int run_steps(cerium_program* p, cudaStream_t st) {
   try {
     for (const Step& s : p->steps) {
       switch (s.kind) {
@@ -654,6 +789,12 @@ int cerium_program_run(cerium_program* p, void* stream) {
         case Step::Bco:
           ((bco_fn)s.fn)(st, s.outs, s.n_out, s.ins, s.n_in, s.factors, s.out_moduli, s.ratios, s.ks, s.smem, s.count);
           break;
+        case Step::Call: {
+          if (int rc = run_steps(s.callee, st)) return rc;
+          for (const auto& c : s.copy_back)
+            CERIUM_CUDA(cudaMemcpyAsync(c.first, c.second, (size_t)kN * sizeof(W), cudaMemcpyDeviceToDevice, st));
+          break;
+        }
         case Step::Drm: {
           const size_t limb = (size_t)kN * sizeof(W);
           W* mine = s.staging + (size_t)p->comm->rank * s.comm_limbs * kN;
@@ -674,6 +815,17 @@ int cerium_program_run(cerium_program* p, void* stream) {
   }
   CERIUM_LAUNCH_CHECK("program_run");
   return CERIUM_OK;
+}
+
+
+int cerium_program_run(cerium_program* p, void* stream) {
+  if (!p) return fail(CERIUM_ERR_INVALID, "program_run: null program");
+  cerium_context* ctx = p->ctx;
+  DeviceGuard guard(ctx->device);
+  if (!guard.ok) return fail(CERIUM_ERR_CUDA, "program_run: cannot select device");
+  // the launchers of this library find their tables through the context bound to the device
+  if (int rc = cerium_function_map_bind(ctx, ctx->device)) return fail(rc, "program_run: cannot bind the context");
+  return run_steps(p, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -499,7 +499,10 @@ class CeriumFunctionExecutor:
         pts = containers.read(plaintexts_file_name) if self.streams.get("Plaintext Stream") else None
         for term, desc, bases in self.streams.get("Plaintext Stream", []):
             e = pts.entries[desc.split(":")[0]]
-            self._put(term, bases, e.stack(0, bases), bases)
+            rows = e.stack(0, bases)
+            if rows.shape[1] < self.context.n:          # a periodic plaintext fills the head of its limb
+                rows = np.pad(rows, ((0, 0), (0, self.context.n - rows.shape[1])))
+            self._put(term, bases, rows, bases)
 
     def copy_inputs_to_device(self):
         """Inputs are written straight into device memory by generate_inputs; nothing is staged."""
@@ -538,7 +541,8 @@ class FusedKernelProgram:
     ``program_inputs``, the kernel plugin, and the ``evalkeys`` / ``plaintexts`` containers if the function has
     such inputs - and returns ``{function name: CeriumFunctionExecutor}``.  For ``gpus > 1`` this process is
     one partition: pass ``partition`` and ``comm`` (the reference runs all partitions from one process).
-    Functions that call other functions are refused by the executor at load."""
+    Functions the entry function calls are loaded with it by the executor, from their own directories under
+    ``directory_base``; their plugins are installed here first."""
 
     def __init__(self, context: Context, directory_base: str, top_level_function: str):
         self.context = context
@@ -551,7 +555,13 @@ class FusedKernelProgram:
         del options, inputs                     # graph mode and raw inputs: replay is in stream mode, inputs come from files
         if gpus > 1 and comm is None:
             raise ValueError("a function compiled for %d GPUs runs as %d processes: pass partition= and comm=" % (gpus, gpus))
+        from . import plugin
         d = os.path.join(self.directory_base, self.top)
+        for other in sorted(os.listdir(self.directory_base)):       # called functions: the executor loads their shims
+            od = os.path.join(self.directory_base, other)
+            if other != self.top and os.path.isfile(os.path.join(od, "function_map_%d.so" % partition)) and \
+                    not os.path.exists(os.path.join(od, "function_map_%d.orig.so" % partition)):
+                plugin.install(od)
         f = CeriumFunctionExecutor(self.context, self.top)
         f._load(d, partition, comm)
         f.generate_inputs(os.path.join(d, "evalkeys"), os.path.join(d, "plaintexts"))

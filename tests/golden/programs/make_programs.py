@@ -31,7 +31,8 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(HERE)))
 OUT_REF = os.path.join(ROOT, "oracle", "_ref")
-PROGRAMS = [("rotation", 1), ("relinearization", 1), ("rescale", 1), ("rotation", 2)]
+PROGRAMS = [("rotation", 1), ("relinearization", 1), ("rescale", 1), ("rotation", 2), ("relinearization", 2), ("rescale", 2),
+            ("addition", 1), ("multiplication", 1), ("periodic_plaintext_matrix", 1), ("function_calling", 1)]
 
 
 def build_compiler(ref: str) -> str:
@@ -87,23 +88,29 @@ def main():
     for name, gpus in PROGRAMS:
         src = compile_example(ref, pkg, name, gpus)
         tag = "%s_%dgpu" % (name, gpus)
-        dst = os.path.join(HERE, tag)
-        os.makedirs(dst, exist_ok=True)
-        for f in ("program_inputs", "compile_config", "calls"):
-            shutil.copy(os.path.join(src, f), dst)
-        plug = os.path.join(OUT_REF, "programs", tag)
-        os.makedirs(plug, exist_ok=True)
-        for p in range(gpus):
-            part = os.path.join(src, "partition_%d" % p)
-            shutil.copy(os.path.join(part, "ll.functions"), os.path.join(dst, "functions%d" % p))
-            shutil.copy(os.path.join(part, "inputs%d" % p), dst)
-            cu = sorted(glob.glob(os.path.join(part, "kernels_*.cu"))) + [os.path.join(part, "function_map.cu"),
-                                                                           os.path.join(HERE, "plugin_stubs.cu")]
-            subprocess.check_call(["nvcc", "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a",
-                                   "-Xcudafe", "--diag_suppress=177", "-Xcompiler", "-fPIC", "-shared",
-                                   "-D__FNAME__=main_%dgpus" % gpus, "-I" + kern,
-                                   "-o", os.path.join(plug, "function_map_%d.orig.so" % p)] + cu)
-        print("made", tag)
+        # every function of the program (the entry function and the ones it calls); a program of one function is
+        # stored flat, a program of several with one directory per function, as the compiler lays them out
+        functions = sorted(d for d in os.listdir(os.path.dirname(src)) if os.path.isdir(os.path.join(os.path.dirname(src), d)))
+        for fn in functions:
+            fsrc = os.path.join(os.path.dirname(src), fn)
+            sub = fn if len(functions) > 1 else ""
+            dst = os.path.join(HERE, tag, sub)
+            os.makedirs(dst, exist_ok=True)
+            for f in ("program_inputs", "compile_config", "calls"):
+                shutil.copy(os.path.join(fsrc, f), dst)
+            plug = os.path.join(OUT_REF, "programs", tag, sub)
+            os.makedirs(plug, exist_ok=True)
+            for p in range(gpus):
+                part = os.path.join(fsrc, "partition_%d" % p)
+                shutil.copy(os.path.join(part, "ll.functions"), os.path.join(dst, "functions%d" % p))
+                shutil.copy(os.path.join(part, "inputs%d" % p), dst)
+                cu = sorted(glob.glob(os.path.join(part, "kernels_*.cu"))) + [os.path.join(part, "function_map.cu"),
+                                                                               os.path.join(HERE, "plugin_stubs.cu")]
+                subprocess.check_call(["nvcc", "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a",
+                                       "-Xcudafe", "--diag_suppress=177", "-Xcompiler", "-fPIC", "-shared",
+                                       "-D__FNAME__=%s" % fn, "-I" + kern,
+                                       "-o", os.path.join(plug, "function_map_%d.orig.so" % p)] + cu)
+        print("made", tag, functions)
 
 
 if __name__ == "__main__":

@@ -148,25 +148,35 @@ def test_generator_writes_what_program_inputs_asks_for(emu, tmp_path):
 # GPU: the reference's example driver, with this module in place of cerium.runtime
 # ---------------------------------------------------------------------------------------------------------
 
-def _compiled(tmp_path, example):
-    """<compiled>/main_1gpus/ as the reference's build leaves it: records, input lists, the generated plugin."""
-    src = os.path.join(PROGS, example + "_1gpu")
-    orig = os.path.join(PLUGINS, example + "_1gpu", "function_map_0.orig.so")
-    if not os.path.exists(orig):
-        pytest.skip("the generated plugin of %s was not built (tests/golden/programs/make_programs.py)" % example)
-    d = tmp_path / "compiled" / "main_1gpus"
-    d.mkdir(parents=True)
-    for f in ("functions0", "inputs0", "program_inputs"):
-        shutil.copy(os.path.join(src, f), d / f)
-    shutil.copy(orig, d / "function_map_0.so")
+def _compiled(tmp_path, example, gpus=1):
+    """<compiled>/<function>_<g>gpus/ for every function of the program, as the reference's build leaves them:
+    records, input lists and the generated plugin of each partition."""
+    tag = "%s_%dgpu" % (example, gpus)
+    src, plug = os.path.join(PROGS, tag), os.path.join(PLUGINS, tag)
+    main = "main_%dgpus" % gpus
+    functions = [main] if os.path.exists(os.path.join(src, "program_inputs")) else sorted(os.listdir(src))
+    for fn in functions:
+        fsrc, fplug = (src, plug) if functions == [main] else (os.path.join(src, fn), os.path.join(plug, fn))
+        d = tmp_path / "compiled" / fn
+        d.mkdir(parents=True)
+        shutil.copy(os.path.join(fsrc, "program_inputs"), d / "program_inputs")
+        for p in range(gpus):
+            orig = os.path.join(fplug, "function_map_%d.orig.so" % p)
+            if not os.path.exists(orig):
+                pytest.skip("the generated plugin of %s was not built (tests/golden/programs/make_programs.py)" % tag)
+            shutil.copy(os.path.join(fsrc, "functions%d" % p), d / ("functions%d" % p))
+            shutil.copy(os.path.join(fsrc, "inputs%d" % p), d / ("inputs%d" % p))
+            shutil.copy(orig, d / ("function_map_%d.so" % p))
     return tmp_path / "compiled"
 
 
-def run_program(tmp_path, example, raw_inputs, expected, output_scale, atol=1e-4):
-    """examples/common.py:83-142 with one import changed."""
-    name, gpus = "main_1gpus", 1
-    compiled = _compiled(tmp_path, example)
-    context = runtime.Context(SLOTS, PRIMES)
+def run_program(tmp_path, example, raw_inputs, expected, output_scale, atol=1e-4, gpus=1, partition=0, comm=None,
+                gather=None, device=0):
+    """examples/common.py:83-142 with one import changed.  With gpus > 1 this process is one partition (the
+    reference drives all partitions from one process): `gather` collects the output limbs of all partitions."""
+    name = "main_%dgpus" % gpus
+    compiled = _compiled(tmp_path, example, gpus)
+    context = runtime.Context(SLOTS, PRIMES, device=device)
     encryptor_context, encryptor = _keys(context)
     inputs = runtime.RawInputsWrapper(raw_inputs)
     generator = runtime.IOGenerator(context)
@@ -176,11 +186,17 @@ def run_program(tmp_path, example, raw_inputs, expected, output_scale, atol=1e-4
         generator.generate_and_serialize_evalkeys(str(function_dir / "evalkeys"), str(function_inputs), encryptor_context)
         generator.generate_and_serialize_plaintexts(str(function_dir / "plaintexts"), str(function_inputs), inputs)
     program = runtime.FusedKernelProgram(context, str(compiled), name)
-    functions = program.make_program(gpus, {name: {"use_cudagraph": "True"}}, inputs)
+    if gpus == 1:
+        functions = program.make_program(gpus, {name: {"use_cudagraph": "True"}}, inputs)
+    else:
+        functions = program.make_program(gpus, {name: {"use_cudagraph": "True"}}, inputs, partition=partition, comm=comm)
     encrypted_inputs = generator.generate_ciphertext_inputs(program_inputs, inputs, encryptor_context)
     functions[name].copy_ciphertext_inputs_to_gpu(str(compiled / name / "inputs"), gpus, encrypted_inputs)
     program.run()
+    program.run()                                   # a program is built once and run many times
     encrypted_output = functions[name].get_program_outputs()["z"]
+    if gather is not None:
+        encrypted_output = gather(encrypted_output)
     actual = np.asarray(encryptor.decrypt_and_decode(encrypted_output, output_scale))
     expected = np.asarray(expected)
     bits = _bits(actual, expected)
@@ -210,6 +226,107 @@ def test_rescale_example(tmp_path):
     output_scale = ciphertext_scale * plaintext_scale / PRIMES[LEVEL - 1]                    # examples/rescale/runner.py
     assert run_program(tmp_path, "rescale", {"x": (x, ciphertext_scale), "factor": (factor, plaintext_scale)},
                        x * factor, output_scale) > 13
+
+
+@pytest.mark.gpu
+def test_addition_example(tmp_path):
+    x, y = sample_vector(1), sample_vector(2)
+    scale = 1 << 56
+    assert run_program(tmp_path, "addition", {"x": (x, scale), "y": (y, scale)}, x + y, scale) > 13
+
+
+@pytest.mark.gpu
+def test_multiplication_example(tmp_path):
+    x, factor = sample_vector(1), sample_vector(2) + 1
+    scale = 1 << 28
+    assert run_program(tmp_path, "multiplication", {"x": (x, scale), "factor": (factor, scale)}, x * factor, scale * scale) > 13
+
+
+@pytest.mark.gpu
+def test_periodic_plaintext_matrix_example(tmp_path):
+    """Plaintexts that repeat every 2 slots (stored as 4 words per limb) and rotations by +1 and -1."""
+    x = sample_vector(1)
+    expected = np.empty_like(x)
+    expected[0::2] = 2 * x[0::2] + x[1::2]
+    expected[1::2] = x[0::2] + 3 * x[1::2]
+    scale, ciphertext_scale = 1 << 28, 1 << 84
+    raw = {"x": (x, ciphertext_scale), "diagonal": (np.array([2.0, 3.0]), scale),
+           "left_mask": (np.array([1.0, 0.0]), scale), "right_mask": (np.array([0.0, 1.0]), scale)}
+    assert run_program(tmp_path, "periodic_plaintext_matrix", raw, expected, float(ciphertext_scale * scale)) > 13
+
+
+@pytest.mark.gpu
+def test_function_calling_example(tmp_path):
+    """The entry function is one call record; the called function's limbs are bound to the caller's."""
+    x = sample_vector(1)
+    scale = 1 << 56
+    assert run_program(tmp_path, "function_calling", {"x": (x, scale)}, 2 * x, scale) > 13
+
+
+# a function compiled for two GPUs: one process per partition, drm records on NCCL ------------------------
+
+def _two_gpu_worker(rank, world, port, workdir, example, ret):
+    import sys
+    import pathlib
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from cerium_b200 import _capi, sharded
+    comm = sharded.nccl_comm(_capi.load(), rank, world, rank)
+
+    def gather(ct):
+        parts = [None] * world
+        dist.all_gather_object(parts, (ct.rns_base_ids, ct.c0, ct.c1))
+        ids = sorted(i for p in parts for i in p[0])
+        rows0 = {i: p[1][k] for p in parts for k, i in enumerate(p[0])}
+        rows1 = {i: p[2][k] for p in parts for k, i in enumerate(p[0])}
+        return runtime.Ciphertext(np.stack([rows0[i] for i in ids]), np.stack([rows1[i] for i in ids]), ids)
+
+    x, y = sample_vector(1), sample_vector(2)
+    cases = {"rotation": ({"x": (x, 1 << 84)}, np.roll(x, -1), float(1 << 84)),
+             "relinearization": ({"x": (x, 1 << 56), "y": (y, 1 << 56)}, x * y, float(1 << 112)),
+             "rescale": ({"x": (x, 1 << 56), "factor": (y + 1, 1 << 28)}, x * (y + 1), (1 << 84) / PRIMES[LEVEL - 1])}
+    raw, expected, out_scale = cases[example]
+    try:
+        bits = run_program(pathlib.Path(workdir) / ("rank%d" % rank), example, raw, expected, out_scale, gpus=world,
+                           partition=rank, comm=comm, gather=gather, device=rank)
+        ret[rank] = bits
+    finally:
+        comm.close()
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("example", ["rotation", "relinearization", "rescale"])
+def test_two_gpu_examples(tmp_path, example):
+    import socket
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    if not os.path.exists(os.path.join(PLUGINS, example + "_2gpu", "function_map_1.orig.so")):
+        pytest.skip("the generated plugins of %s_2gpu were not built" % example)
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_two_gpu_worker, args=(r, 2, port, str(tmp_path), example, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(600)
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    assert all(ret.get(r, 0) > 13 for r in range(2)), dict(ret)
 
 
 def test_periodic_plaintext_is_the_subsampled_transform(emu):
