@@ -23,7 +23,8 @@
 // communicator given at load: its sources are packed into this rank's block of a staging buffer,
 // gathered in place, and unpacked to the record's destinations.  A call record loads the called function
 // from the same program directory and binds its argument and result limbs to the caller's (the reference
-// copies them in and out, function_execution.cpp:265-331, 508-600).  Not served: rsv, ags and ard records
+// copies them in and out, function_execution.cpp:265-331, 508-600).  An rsv record (two-limb CRT composition) runs on the
+// program's generated kernel with the factors of compute_rsv_factors.  Not served: ags and ard records
 // and remapable inputs - a function that holds one is refused at load.
 #include <algorithm>
 #include <cstring>
@@ -264,6 +265,7 @@ typedef void (*ewi_fn)(cudaStream_t&, W**, const W**, const W*, const W**, const
 typedef void (*ntt_fn)(cudaStream_t&, W**, const W**, const uint32_t*, const size_t, const W*, const uint2*);
 typedef void (*sud_fn)(cudaStream_t&, W**, const W**, const uint32_t*, const size_t, const W*, const uint2*, const W*,
                        const W*, const uint32_t*);
+typedef void (*rsv_fn)(cudaStream_t&, W**, const W**, const W*, const W*, const W*, const uint32_t);
 typedef void (*bco_fn)(cudaStream_t&, W**, const size_t*, const W**, const size_t*, const W**, const W**, const W**,
                        const W**, const size_t, const size_t);
 
@@ -275,7 +277,10 @@ struct Unit {  // one base-conversion unit: input block, output block, the bases
 constexpr int kUnitMaxIn = 48, kUnitMaxOut = 64;  // DeviceBaseConverter's block sizes (evaluator.h:36-38)
 
 struct Step {
-  enum Kind { Ewi, Ntt, Int, Sud, Bco, Drm, Call } kind;
+  enum Kind { Ewi, Ntt, Int, Sud, Bco, Drm, Call, Rsv } kind;
+  // rsv: CRT factors, the modulus product, its Barrett ratio (all as words) and the Barrett shift
+  const W *rsv_factors = nullptr, *rsv_modulus = nullptr, *rsv_ratio = nullptr;
+  uint32_t rsv_k = 0;
   cerium_program* callee = nullptr;  // call: the called function, its argument terms bound to this function's memory
   std::vector<std::pair<W*, const W*>> copy_back;  // call: results whose destination is also an argument (dst, src)
   // drm: host lists of the limbs to pack (this rank's sources) and to unpack (every rank's block)
@@ -461,7 +466,7 @@ struct Loader {
     for (const Record& r : recs) {
       const std::string& ty = r.type;
       if (ty == "mov") continue;  // outputs alias inputs: nothing to run (the reference skips them too)
-      if (ty == "rsv" || ty == "ags" || ty == "ard")
+      if (ty == "ags" || ty == "ard")
         throw std::runtime_error("record " + std::to_string(r.id) + " of type '" + ty + "' is not served by this executor");
       if (ty == "call") {
         // The call case of CeriumFunction::make_program / run (function_execution.cpp:265-331, 508-600): the callee
@@ -644,6 +649,31 @@ struct Loader {
           for (int32_t amt : r.rots) maps.push_back(rotation_table(amt));
           s.rotmaps = upload(maps);
         }
+      } else if (ty == "rsv") {
+        // compute_rsv_factors (function_execution.cpp:53-99): for the primes of .rsv, factor_i =
+        // (Q / q_i) * [(Q / q_i)^-1]_{q_i} as a multi-word integer (one 64-bit word per prime, stored as
+        // 32-bit words), the product Q, and floor(2^k / Q) with k = floor(log2 Q) + 63.  The generated
+        // kernel composes x = sum x_i * factor_i mod Q from them.  Two primes below 2^32: everything fits
+        // in 64-bit words, which is the only shape the compiler emits (double rescale, ModRaise).
+        s.kind = Step::Rsv;
+        if (r.rsv.size() != 2) throw std::runtime_error("rsv record " + std::to_string(r.id) + " resolves " + std::to_string(r.rsv.size()) + " primes; two are served");
+        for (uint32_t b : r.rsv)
+          if (b >= (uint32_t)ctx->n_primes) throw std::runtime_error("prime index out of range in .rsv");
+        const uint64_t q0 = ctx->moduli[r.rsv[0]], q1 = ctx->moduli[r.rsv[1]];
+        if (q0 >> 32 || q1 >> 32) throw std::runtime_error("rsv primes must be below 2^32");
+        const uint64_t Q = q0 * q1;
+        const uint64_t f0 = q1 * host::invmod(q1 % q0, q0), f1 = q0 * host::invmod(q0 % q1, q1);
+        std::vector<W> fac = {(W)f0, (W)(f0 >> 32), (W)f1, (W)(f1 >> 32)};
+        std::vector<W> mod = {(W)Q, (W)(Q >> 32)};
+        uint32_t log2q = 0;
+        while ((Q >> (log2q + 1)) != 0) log2q++;
+        const uint32_t k = log2q + 63;
+        const unsigned __int128 ratio = ((unsigned __int128)1 << k) / Q;
+        std::vector<W> rat = {(W)(uint64_t)ratio, (W)((uint64_t)ratio >> 32)};
+        s.rsv_factors = upload(fac);
+        s.rsv_modulus = upload(mod);
+        s.rsv_ratio = upload(rat);
+        s.rsv_k = k;
       } else if (ty == "ntt") {
         s.kind = Step::Ntt;
       } else if (ty == "int") {
@@ -788,6 +818,9 @@ static int run_steps(cerium_program* p, cudaStream_t st) {
           break;
         case Step::Bco:
           ((bco_fn)s.fn)(st, s.outs, s.n_out, s.ins, s.n_in, s.factors, s.out_moduli, s.ratios, s.ks, s.smem, s.count);
+          break;
+        case Step::Rsv:
+          ((rsv_fn)s.fn)(st, s.outs, s.ins, s.rsv_factors, s.rsv_modulus, s.rsv_ratio, s.rsv_k);
           break;
         case Step::Call: {
           if (int rc = run_steps(s.callee, st)) return rc;

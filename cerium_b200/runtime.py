@@ -462,7 +462,23 @@ class CeriumFunctionExecutor:
         self.program: Optional[_capi.Program] = None
         self.streams: Dict[str, list] = {}
 
-    def _load(self, directory: str, partition: int, comm):
+    def _scalars(self, raw_inputs: Optional[RawInputsWrapper]) -> Dict[str, int]:
+        """Scalar Stream: `term | name:s | [ids]` -> {"term(id)": round(value * scale) mod q_id}, the constant
+        plaintext the reference's encode_scalar produces (cerium/runtime/execution/function_io.cpp:306-381)."""
+        out: Dict[str, int] = {}
+        for term, desc, bases in self.streams.get("Scalar Stream", []):
+            var, kind = desc.split(":")
+            if kind != "s":
+                raise ValueError("invalid scalar entry %r" % desc)
+            if raw_inputs is None or var not in raw_inputs.raw_inputs:
+                raise KeyError("Raw Inputs key error: " + var)
+            value, scale = raw_inputs.raw_inputs[var]
+            c = int(np.rint(float(np.real(value)) * float(scale)))
+            for b in bases:
+                out["%s(%d)" % (term, b)] = c % self.context.moduli[b]
+        return out
+
+    def _load(self, directory: str, partition: int, comm, raw_inputs: Optional[RawInputsWrapper] = None):
         from . import plugin
         functions = os.path.join(directory, "functions%d" % partition)
         shim = os.path.join(directory, "function_map_%d.so" % partition)
@@ -470,7 +486,7 @@ class CeriumFunctionExecutor:
             plugin.install(directory)           # keeps the generated plugin as .orig.so, installs this library's launchers
         self.directory, self.partition = directory, partition
         self.streams = parse_program_inputs(os.path.join(directory, "program_inputs"))
-        self.program = _capi.Program(self.context.handle, functions, shim, comm=comm)
+        self.program = _capi.Program(self.context.handle, functions, shim, scalars=self._scalars(raw_inputs), comm=comm)
 
     def _mine(self, term: str, ids: Sequence[int]) -> List[int]:
         """The limbs of `term` that this partition's function names (a partition holds its own limbs only)."""
@@ -503,6 +519,38 @@ class CeriumFunctionExecutor:
             if rows.shape[1] < self.context.n:          # a periodic plaintext fills the head of its limb
                 rows = np.pad(rows, ((0, 0), (0, self.context.n - rows.shape[1])))
             self._put(term, bases, rows, bases)
+
+    def generate_inputs_direct(self, encryptor_context: Optional["CKKSEncryptorContext"],
+                               raw_inputs: Optional[RawInputsWrapper]):
+        """The same inputs without the container files: every key digit and plaintext is generated and written
+        straight into program memory (a bootstrapping function holds gigabytes of keys)."""
+        if self.streams.get("Evalkey Stream"):
+            if encryptor_context is None:
+                raise ValueError("the function takes evaluation keys: pass encryptor_context or write the evalkeys file")
+            enc = CKKSEncryptor(encryptor_context)
+            by_key: Dict[str, list] = {}
+            for term, desc, bases in self.streams["Evalkey Stream"]:
+                by_key.setdefault(parse_evalkey_description(desc)[0], []).append((term, desc, bases))
+            for ident, lines in by_key.items():
+                _id, t, level, ext, rot, _poly, digit = parse_evalkey_description(lines[0][1])
+                polys = [_words(c) for c in enc.generate_evalkey(t, level, ext, rot, digit)]
+                ids = enc.key_rns_base_ids(level, ext)
+                for term, desc, bases in lines:
+                    poly = parse_evalkey_description(desc)[5]
+                    self._put(term, bases, polys[poly][[ids.index(b) for b in bases]], bases)
+        if self.streams.get("Plaintext Stream"):
+            if raw_inputs is None:
+                raise ValueError("the function takes plaintexts: pass the raw inputs or write the plaintexts file")
+            pe = _PlainEncoder(self.context)
+            for term, desc, bases in self.streams["Plaintext Stream"]:
+                var, kind, elt = desc.split(":")
+                if var not in raw_inputs.raw_inputs:
+                    raise KeyError("Raw Inputs key error: " + var)
+                values, scale = raw_inputs.raw_inputs[var]
+                rows = _words(pe.encode(values, scale, bases, int(elt)))
+                if rows.shape[1] < self.context.n:
+                    rows = np.pad(rows, ((0, 0), (0, self.context.n - rows.shape[1])))
+                self._put(term, bases, rows, bases)
 
     def copy_inputs_to_device(self):
         """Inputs are written straight into device memory by generate_inputs; nothing is staged."""
@@ -542,7 +590,9 @@ class FusedKernelProgram:
     such inputs - and returns ``{function name: CeriumFunctionExecutor}``.  For ``gpus > 1`` this process is
     one partition: pass ``partition`` and ``comm`` (the reference runs all partitions from one process).
     Functions the entry function calls are loaded with it by the executor, from their own directories under
-    ``directory_base``; their plugins are installed here first."""
+    ``directory_base``; their plugins are installed here first.  With ``encryptor_context`` given and no
+    ``evalkeys`` file in the function directory, keys and plaintexts are generated straight into device
+    memory instead of being read from container files."""
 
     def __init__(self, context: Context, directory_base: str, top_level_function: str):
         self.context = context
@@ -551,8 +601,9 @@ class FusedKernelProgram:
         self.functions: Dict[str, CeriumFunctionExecutor] = {}
 
     def make_program(self, gpus: int = 1, options: Optional[dict] = None, inputs: Optional[RawInputsWrapper] = None,
-                     partition: int = 0, comm=None) -> Dict[str, CeriumFunctionExecutor]:
-        del options, inputs                     # graph mode and raw inputs: replay is in stream mode, inputs come from files
+                     partition: int = 0, comm=None, encryptor_context: Optional[CKKSEncryptorContext] = None
+                     ) -> Dict[str, CeriumFunctionExecutor]:
+        del options                             # graph mode: replay is in stream mode
         if gpus > 1 and comm is None:
             raise ValueError("a function compiled for %d GPUs runs as %d processes: pass partition= and comm=" % (gpus, gpus))
         from . import plugin
@@ -563,8 +614,11 @@ class FusedKernelProgram:
                     not os.path.exists(os.path.join(od, "function_map_%d.orig.so" % partition)):
                 plugin.install(od)
         f = CeriumFunctionExecutor(self.context, self.top)
-        f._load(d, partition, comm)
-        f.generate_inputs(os.path.join(d, "evalkeys"), os.path.join(d, "plaintexts"))
+        f._load(d, partition, comm, inputs)
+        if encryptor_context is not None and not os.path.exists(os.path.join(d, "evalkeys")):
+            f.generate_inputs_direct(encryptor_context, inputs)      # no container files: generate into device memory
+        else:
+            f.generate_inputs(os.path.join(d, "evalkeys"), os.path.join(d, "plaintexts"))
         self.functions = {self.top: f}
         return self.functions
 

@@ -605,7 +605,7 @@ CERIUM_API void *cerium_function_map_launcher(const char *type, int cugraph);
  *                                  (<programs>/<function_name>/functions<p>, inputs<p>, function_map_<p>.so,
  *                                  so functions_path must be <programs>/<function>/functions<p>); its
  *                                  argument and result limbs are bound to the caller's limbs
- * 32-bit contexts (the generated kernels are 32-bit).  Not served: rsv, ags / ard records and
+ * 32-bit contexts (the generated kernels are 32-bit).  Not served: ags / ard records and
  * remapable inputs; a function that has one is refused at load.
  */
 CERIUM_API int cerium_program_load(cerium_context *ctx, cerium_program **out, const char *functions_path,

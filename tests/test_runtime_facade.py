@@ -353,3 +353,95 @@ def test_periodic_plaintext_is_the_subsampled_transform(emu):
         outs.append(o.numpy().view(np.uint32))
     got = enc.decrypt_and_decode(runtime.Ciphertext(outs[0], outs[1], idx), float(1 << 56))
     assert np.allclose(got, x * np.tile(v, SLOTS // period), rtol=1e-5, atol=1e-4)
+
+
+# the reference's bootstrapping benchmark ---------------------------------------------------------------
+
+BOOT_TAG, BOOT_FN = "bootstrap_32K_1gpu", "bootstrap_32Kslots_33levels_1gpus"
+
+
+def bootstrap_directory(tmp_path):
+    """<compiled>/<function>/ of the compiled bootstrapping benchmark (benchmarks/bootstrap_32K, one GPU)."""
+    import lzma
+    orig = os.path.join(PLUGINS, BOOT_TAG, "function_map_0.orig.so")
+    if not os.path.exists(orig):
+        pytest.skip("the generated plugin of %s was not built (tests/golden/programs/make_programs.py)" % BOOT_TAG)
+    d = tmp_path / "compiled" / BOOT_FN
+    d.mkdir(parents=True)
+    for f in ("functions0", "inputs0", "program_inputs"):
+        with lzma.open(os.path.join(PROGS, BOOT_TAG, f + ".xz"), "rb") as src, open(d / f, "wb") as dst:
+            dst.write(src.read())
+    shutil.copy(orig, d / "function_map_0.so")
+    return tmp_path / "compiled"
+
+
+def bootstrap_raw_inputs():
+    z = np.load(os.path.join(PLUGINS, BOOT_TAG, "raw_inputs.npz"))
+    return {k[2:]: (z[k][()] if z[k].ndim == 0 else z[k], float(z["s:" + k[2:]])) for k in z.files if k.startswith("v:")}
+
+
+def test_bootstrap_program_records():
+    """The compiled benchmark as the executor's parser sees it: 462 records, ten of them two-limb CRT
+    compositions (rsv), no exchange records on one GPU."""
+    import lzma
+    import tempfile
+    from cerium_b200 import _capi
+    with tempfile.TemporaryDirectory() as t:
+        path = os.path.join(t, "functions0")
+        with lzma.open(os.path.join(PROGS, BOOT_TAG, "functions0.xz"), "rb") as src, open(path, "wb") as dst:
+            dst.write(src.read())
+        recs = _capi.inspect_program(_capi.load(), path)
+    kinds = {}
+    for r in recs:
+        kinds[r["type"]] = kinds.get(r["type"], 0) + 1
+    assert kinds == {"int": 62, "bco": 56, "ntt": 26, "generic": 137, "pmu": 19, "mov": 115, "sud": 37, "rsv": 10}
+
+
+@pytest.mark.gpu
+def test_bootstrap_benchmark_program(tmp_path):
+    """benchmarks/bootstrap_32K/bootstrap_runner.py:83-170 with this module in place of cerium.runtime: a level-2
+    ciphertext of unit-modulus complex slots is bootstrapped to level 18 by the reference's compiled program
+    (195 key digits, 259 plaintexts, 31 scalars, 347 launches) and decrypted; the precision is printed the way
+    the runner prints it."""
+    import time
+    import torch
+    raw_path = os.path.join(PLUGINS, BOOT_TAG, "raw_inputs.npz")
+    compiled = bootstrap_directory(tmp_path)
+    if not os.path.exists(raw_path):
+        pytest.skip("the benchmark's plaintext values were not generated (tests/golden/programs/make_programs.py)")
+    rnd = random.Random(10)
+
+    def generate_secret_key(hamming_weight):                       # bootstrap_runner.py:29-43
+        key = [0] * (2 * SLOTS)
+        for position in rnd.sample(range(2 * SLOTS), hamming_weight):
+            key[position] = rnd.choice((-1, 1))
+        return key
+    raw_inputs = runtime.RawInputsWrapper(bootstrap_raw_inputs())
+    context = runtime.Context(SLOTS, PRIMES)
+    seed = np.random.default_rng(10).integers(0, 2 ** 32 - 1, size=8).tolist()
+    encryptor_context = runtime.CKKSEncryptorContext(context, generate_secret_key(SLOTS), generate_secret_key(32), seed)
+    encryptor = runtime.CKKSEncryptor(encryptor_context, seed)
+    inp_scale = PRIMES[1] * PRIMES[0] / (1 << 5)                   # log_message_ratio = 5
+    arr = np.exp(1j * np.random.default_rng(10).uniform(0, 2 * np.pi, SLOTS))
+    inputs = runtime.RawInputsWrapper({"x": (arr, inp_scale)})
+    program = runtime.FusedKernelProgram(context, str(compiled), BOOT_FN)
+    t0 = time.time()
+    functions = program.make_program(1, {BOOT_FN: {"use_cudagraph": "True"}}, raw_inputs, encryptor_context=encryptor_context)
+    t_setup = time.time() - t0
+    main = functions[BOOT_FN]
+    generator = runtime.IOGenerator(context)
+    encrypted_inputs = generator.generate_ciphertext_inputs(str(compiled / BOOT_FN / "program_inputs"), inputs, encryptor_context)
+    main.copy_ciphertext_inputs_to_gpu(str(compiled / BOOT_FN / "inputs"), 1, encrypted_inputs)
+    program.run()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    stream = context.stream()
+    e0.record()
+    for _ in range(5):
+        main.program.run(stream)
+    e1.record()
+    torch.cuda.synchronize()
+    z = np.asarray(encryptor.decrypt_and_decode(main.get_program_outputs()["z"], inp_scale))
+    err = float(np.max(np.abs(z - arr)))
+    print("bootstrap program: %d steps, setup %.1f s, %.2f ms per run; max absolute error %.2e, precision bits %.2f"
+          % (main.program.num_steps, t_setup, e0.elapsed_time(e1) / 5, err, -np.log2(err)))
+    assert -np.log2(err) > 10, "the bootstrapped ciphertext does not decrypt to its input"
