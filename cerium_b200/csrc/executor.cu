@@ -24,8 +24,9 @@
 // gathered in place, and unpacked to the record's destinations.  A call record loads the called function
 // from the same program directory and binds its argument and result limbs to the caller's (the reference
 // copies them in and out, function_execution.cpp:265-331, 508-600).  An rsv record (two-limb CRT composition) runs on the
-// program's generated kernel with the factors of compute_rsv_factors.  Not served: ags and ard records
-// and remapable inputs - a function that holds one is refused at load.
+// program's generated kernel with the factors of compute_rsv_factors.  ags / ard records (sums over the
+// partitions: reduce-scatter / all-reduce, then reduction modulo each limb's prime) run on the communicator
+// like drm.  Not served: remapable inputs - a function that holds one is refused at load.
 #include <algorithm>
 #include <cstring>
 #include <fstream>
@@ -269,6 +270,35 @@ typedef void (*rsv_fn)(cudaStream_t&, W**, const W**, const W*, const W*, const 
 typedef void (*bco_fn)(cudaStream_t&, W**, const size_t*, const W**, const size_t*, const W**, const W**, const W**,
                        const W**, const size_t, const size_t);
 
+// Pack / unpack of the exchange records (the reference's _copy_to_nccl_buffer_ / _copy_from_nccl_buffer_with_mod_,
+// cerium/runtime/execution/device_utils.cu:290-340): limbs named by a pointer table <-> one contiguous staging
+// buffer, 16 bytes per thread.  A null source packs zeros, a null destination is skipped; `bases` != null reduces
+// every word modulo its limb's prime (sums of up to 16 residues below 2^28 arrive unreduced).
+constexpr int kPackThreads = 256;
+__global__ void __launch_bounds__(kPackThreads) pack_limbs_kernel(W* __restrict__ staging, const W* const* __restrict__ ins) {
+  const W* src = ins[blockIdx.y];
+  const size_t i = ((size_t)blockIdx.x * kPackThreads + threadIdx.x) * 4;
+  uint4 v = make_uint4(0, 0, 0, 0);
+  if (src != nullptr) v = *reinterpret_cast<const uint4*>(src + i);
+  *reinterpret_cast<uint4*>(staging + (size_t)blockIdx.y * kN + i) = v;
+}
+__global__ void __launch_bounds__(kPackThreads)
+    unpack_limbs_kernel(W* const* __restrict__ outs, const W* __restrict__ staging, const uint32_t* __restrict__ bases,
+                        const W* __restrict__ moduli) {
+  W* dst = outs[blockIdx.y];
+  if (dst == nullptr) return;
+  const size_t i = ((size_t)blockIdx.x * kPackThreads + threadIdx.x) * 4;
+  uint4 v = *reinterpret_cast<const uint4*>(staging + (size_t)blockIdx.y * kN + i);
+  if (bases != nullptr) {
+    const W q = moduli[bases[blockIdx.y]];
+    v.x %= q;
+    v.y %= q;
+    v.z %= q;
+    v.w %= q;
+  }
+  *reinterpret_cast<uint4*>(dst + i) = v;
+}
+
 struct Unit {  // one base-conversion unit: input block, output block, the bases they hold right now
   std::vector<uint32_t> in_ids, out_ids;
   W* in_buf = nullptr;
@@ -277,7 +307,12 @@ struct Unit {  // one base-conversion unit: input block, output block, the bases
 constexpr int kUnitMaxIn = 48, kUnitMaxOut = 64;  // DeviceBaseConverter's block sizes (evaluator.h:36-38)
 
 struct Step {
-  enum Kind { Ewi, Ntt, Int, Sud, Bco, Drm, Call, Rsv } kind;
+  enum Kind { Ewi, Ntt, Int, Sud, Bco, Drm, Call, Rsv, Ags, Ard } kind;
+  // exchange records: device pointer tables of the limbs to pack and to unpack, prime index per unpacked limb
+  const W* const* pack_tab = nullptr;
+  W* const* unpack_tab = nullptr;
+  const uint32_t* unpack_bases = nullptr;
+  size_t n_pack = 0, n_unpack = 0;
   // rsv: CRT factors, the modulus product, its Barrett ratio (all as words) and the Barrett shift
   const W *rsv_factors = nullptr, *rsv_modulus = nullptr, *rsv_ratio = nullptr;
   uint32_t rsv_k = 0;
@@ -466,8 +501,36 @@ struct Loader {
     for (const Record& r : recs) {
       const std::string& ty = r.type;
       if (ty == "mov") continue;  // outputs alias inputs: nothing to run (the reference skips them too)
-      if (ty == "ags" || ty == "ard")
-        throw std::runtime_error("record " + std::to_string(r.id) + " of type '" + ty + "' is not served by this executor");
+      if (ty == "ags" || ty == "ard") {
+        // Evaluator::ags / ard (evaluator.cpp:1253-1481): the `gather` list (.comm_dests; world x limbs for ags,
+        // limbs for ard; Z = a zero limb) is packed into a staging buffer, summed over the partitions - ags:
+        // reduce-scatter, this partition keeps block `rank`; ard: all-reduce - and the `scatter` list
+        // (.comm_srcs) receives the sums reduced modulo the primes of .bases.
+        cerium_comm* comm = p->comm;
+        if (comm == nullptr) throw std::runtime_error("record " + std::to_string(r.id) + " is an " + ty + " record: the function needs a communicator");
+        if ((size_t)comm->world != r.comm_size) throw std::runtime_error(ty + " record " + std::to_string(r.id) + " was compiled for " + std::to_string(r.comm_size) + " partitions");
+        const size_t blocks = ty == "ags" ? r.comm_size : 1;
+        if (r.comm_dests.size() > blocks * r.comm_num_limbs || r.comm_srcs.size() > r.comm_num_limbs || r.bases.size() < r.comm_srcs.size())
+          throw std::runtime_error(ty + " record " + std::to_string(r.id) + " lists more limbs than it exchanges");
+        for (uint32_t b : r.bases)
+          if (b >= (uint32_t)ctx->n_primes) throw std::runtime_error("prime index out of range in .bases");
+        Step s{};
+        s.kind = ty == "ags" ? Step::Ags : Step::Ard;
+        s.id = r.id;
+        s.comm_limbs = r.comm_num_limbs;
+        // zero-filled: limbs past the gather list stay zero; ags receives into a block of its own behind them
+        s.staging = limb_alloc((blocks + (ty == "ags" ? 1 : 0)) * r.comm_num_limbs);
+        std::vector<const W*> gather;
+        for (const Term& t : r.comm_dests) gather.push_back(pointer(t));
+        std::vector<W*> scatter = pointers(r.comm_srcs);
+        s.pack_tab = upload(gather);
+        s.unpack_tab = upload(scatter);
+        s.unpack_bases = upload(r.bases);
+        s.n_pack = gather.size();
+        s.n_unpack = scatter.size();
+        p->steps.push_back(s);
+        continue;
+      }
       if (ty == "call") {
         // The call case of CeriumFunction::make_program / run (function_execution.cpp:265-331, 508-600): the callee
         // is the function `function_name` of the same program directory; .function_args pairs its argument and
@@ -550,6 +613,10 @@ struct Loader {
         s.staging = limb_alloc(r.comm_size * r.comm_num_limbs);
         for (const Term& t : r.comm_srcs) s.pack.push_back(pointer(t));      // null = a zero limb
         for (const Term& t : r.comm_dests) s.unpack.push_back(pointer(t));   // null = not wanted here
+        s.pack_tab = upload(s.pack);
+        s.unpack_tab = upload(s.unpack);
+        s.n_pack = s.pack.size();
+        s.n_unpack = s.unpack.size();
         p->steps.push_back(s);
         continue;
       }
@@ -831,14 +898,27 @@ static int run_steps(cerium_program* p, cudaStream_t st) {
         case Step::Drm: {
           const size_t limb = (size_t)kN * sizeof(W);
           W* mine = s.staging + (size_t)p->comm->rank * s.comm_limbs * kN;
-          for (size_t i = 0; i < s.pack.size(); i++) {
-            if (s.pack[i] == nullptr) CERIUM_CUDA(cudaMemsetAsync(mine + i * kN, 0, limb, st));
-            else CERIUM_CUDA(cudaMemcpyAsync(mine + i * kN, s.pack[i], limb, cudaMemcpyDeviceToDevice, st));
-          }
+          const dim3 grid(kN / (kPackThreads * 4));
+          if (s.n_pack) pack_limbs_kernel<<<dim3(grid.x, (unsigned)s.n_pack), kPackThreads, 0, st>>>(mine, s.pack_tab);
           if (int rc = comm_allgather(p->comm, s.staging, mine, s.comm_limbs * limb, st)) return rc;
-          for (size_t j = 0; j < s.unpack.size(); j++)
-            if (s.unpack[j] != nullptr)
-              CERIUM_CUDA(cudaMemcpyAsync(s.unpack[j], s.staging + j * kN, limb, cudaMemcpyDeviceToDevice, st));
+          if (s.n_unpack)
+            unpack_limbs_kernel<<<dim3(grid.x, (unsigned)s.n_unpack), kPackThreads, 0, st>>>(s.unpack_tab, s.staging, nullptr, nullptr);
+          break;
+        }
+        case Step::Ags:
+        case Step::Ard: {
+          const dim3 grid(kN / (kPackThreads * 4));
+          if (s.n_pack) pack_limbs_kernel<<<dim3(grid.x, (unsigned)s.n_pack), kPackThreads, 0, st>>>(s.staging, s.pack_tab);
+          const W* sums = s.staging;
+          if (s.kind == Step::Ags) {
+            W* mine = s.staging + (size_t)p->comm->world * s.comm_limbs * kN;
+            if (int rc = comm_reducescatter_sum(p->comm, mine, s.staging, s.comm_limbs * kN, 32, st)) return rc;
+            sums = mine;
+          } else {
+            if (int rc = comm_allreduce_sum(p->comm, s.staging, s.staging, s.comm_limbs * kN, 32, st)) return rc;
+          }
+          if (s.n_unpack)
+            unpack_limbs_kernel<<<dim3(grid.x, (unsigned)s.n_unpack), kPackThreads, 0, st>>>(s.unpack_tab, sums, s.unpack_bases, p->d_moduli);
           break;
         }
       }

@@ -599,14 +599,15 @@ CERIUM_API void *cerium_function_map_launcher(const char *type, int cugraph);
  *   comm                           the partitions of a function compiled for several GPUs run as the
  *                                  ranks of this communicator, one process each (partition p = rank p);
  *                                  its drm records (the all-gather of limbs between partitions,
- *                                  Evaluator::drm, evaluator.cpp:1154-1251) run on it.  NULL for a
+ *                                  Evaluator::drm, evaluator.cpp:1154-1251) and its ags / ard records
+ *                                  (reduce-scatter / all-reduce of partial sums, then reduction modulo
+ *                                  each limb's prime, evaluator.cpp:1253-1481) run on it.  NULL for a
  *                                  function compiled for one GPU.
  *   call records                   the called function is loaded from the same program directory
  *                                  (<programs>/<function_name>/functions<p>, inputs<p>, function_map_<p>.so,
  *                                  so functions_path must be <programs>/<function>/functions<p>); its
  *                                  argument and result limbs are bound to the caller's limbs
- * 32-bit contexts (the generated kernels are 32-bit).  Not served: ags / ard records and
- * remapable inputs; a function that has one is refused at load.
+ * 32-bit contexts (the generated kernels are 32-bit).  Not served: remapable inputs; a function that has one is refused at load.
  */
 CERIUM_API int cerium_program_load(cerium_context *ctx, cerium_program **out, const char *functions_path,
                                    const char *plugin_path, const char *const *scalar_terms,

@@ -14,11 +14,11 @@
    reference's kernel headers, with plugin_stubs.cu standing in for kernels/function.cu (which needs
    CUDA 13), into oracle/_ref/programs/<name>_<g>gpu/function_map_<p>.orig.so (git-ignored, travels to
    the GPU host like every built object).  The generated sources themselves are not kept.
-4. The reference's bootstrapping benchmark (benchmarks/bootstrap_32K/bootstrap.py, one GPU: 462 records, 195 key
-   digits, 259 plaintexts): the same three steps, the text artefacts xz-compressed under
-   tests/golden/programs/bootstrap_32K_1gpu/; and the benchmark's own plaintext / scalar VALUES (FFT-factor
+4. The reference's bootstrapping benchmark (benchmarks/bootstrap_32K/bootstrap.py, built for 1, 2, 4 and 8 GPUs;
+   one GPU: 462 records, 195 key digits, 259 plaintexts): the same three steps, the text artefacts xz-compressed
+   under tests/golden/programs/bootstrap_32K_<g>gpu/; and the benchmark's own plaintext / scalar VALUES (FFT-factor
    diagonals, sine-approximation coefficients: benchmarks/bootstrap_32K/bootstrap_values.py, imported here) saved
-   as oracle/_ref/programs/bootstrap_32K_1gpu/raw_inputs.npz (30 MB, git-ignored like the plugins, travels with
+   as oracle/_ref/programs/bootstrap_32K_<g>gpu/raw_inputs.npz (20 MB each, git-ignored like the plugins, travels with
    the tree), so that the GPU test can decrypt a bootstrapped ciphertext and report its precision.
 Nothing here runs at test time: tests read the committed text files and load the built plugins.
 """
@@ -84,46 +84,50 @@ def compile_example(ref: str, pkg: str, name: str, gpus: int) -> str:
     return os.path.join(run, "examples", name, "outputs", name, "main_%dgpus" % gpus)
 
 
-def make_bootstrap(ref: str, pkg: str, kern: str):
+def make_bootstrap(ref: str, pkg: str, kern: str, gpus: int = 1):
     import lzma
-    import numpy as np
-    tag, fn = "bootstrap_32K_1gpu", "bootstrap_32Kslots_33levels_1gpus"
+    tag, fn = "bootstrap_32K_%dgpu" % gpus, "bootstrap_32Kslots_33levels_%dgpus" % gpus
     run = os.path.join(OUT_REF, "refcompiler", "run_bootstrap")
     if os.path.isdir(run):
         shutil.rmtree(run)
     shutil.copytree(os.path.join(ref, "benchmarks", "bootstrap_32K"), run)
     env = dict(os.environ, PYTHONPATH=pkg)
-    subprocess.check_call([sys.executable, "bootstrap.py", "--gpus", "1", "--prefix", os.path.join(run, "out") + "/"], cwd=run, env=env)
+    subprocess.check_call([sys.executable, "bootstrap.py", "--gpus", str(gpus), "--prefix", os.path.join(run, "out") + "/"], cwd=run, env=env)
     src = os.path.join(run, "out", fn)
     dst = os.path.join(HERE, tag)
     os.makedirs(dst, exist_ok=True)
-    part = os.path.join(src, "partition_0")
-    for path, name in ((os.path.join(src, "program_inputs"), "program_inputs"), (os.path.join(part, "ll.functions"), "functions0"),
-                       (os.path.join(part, "inputs0"), "inputs0")):
-        with open(path, "rb") as f, lzma.open(os.path.join(dst, name + ".xz"), "wb", preset=9) as g:
-            g.write(f.read())
     plug = os.path.join(OUT_REF, "programs", tag)
     os.makedirs(plug, exist_ok=True)
-    # one object per generated source, in parallel: the kernel files are large
-    srcs = sorted(glob.glob(os.path.join(part, "kernels_*.cu"))) + [os.path.join(part, "function_map.cu"),
-                                                                    os.path.join(HERE, "plugin_stubs.cu")]
     flags = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcudafe", "--diag_suppress=177",
              "-Xcompiler", "-fPIC", "-D__FNAME__=%s" % fn, "-I" + kern]
+    texts = [(os.path.join(src, "program_inputs"), "program_inputs")]
+    jobs = []
+    for p in range(gpus):
+        part = os.path.join(src, "partition_%d" % p)
+        texts += [(os.path.join(part, "ll.functions"), "functions%d" % p), (os.path.join(part, "inputs%d" % p), "inputs%d" % p)]
+        for c in sorted(glob.glob(os.path.join(part, "kernels_*.cu"))) + [os.path.join(part, "function_map.cu"),
+                                                                           os.path.join(HERE, "plugin_stubs.cu")]:
+            jobs.append((p, c, os.path.join(plug, "p%d_%s.o" % (p, os.path.basename(c)))))
+    for path, name in texts:
+        with open(path, "rb") as f, lzma.open(os.path.join(dst, name + ".xz"), "wb", preset=9) as g:
+            g.write(f.read())
 
-    def comp(s):
-        o = os.path.join(plug, os.path.basename(s) + ".o")
-        subprocess.check_call(["nvcc"] + flags + ["-c", s, "-o", o])
-        return o
+    def comp(job):       # one object per generated source, in parallel: the kernel files are large
+        subprocess.check_call(["nvcc"] + flags + ["-c", job[1], "-o", job[2]])
     with ThreadPoolExecutor(8) as ex:
-        objs = list(ex.map(comp, srcs))
-    subprocess.check_call(["nvcc", "-shared", "-o", os.path.join(plug, "function_map_0.orig.so")] + objs)
-    for o in objs:
-        os.remove(o)
-    # the benchmark's plaintext and scalar values, by input name
+        list(ex.map(comp, jobs))
+    for p in range(gpus):
+        objs = [o for q, _, o in jobs if q == p]
+        subprocess.check_call(["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o",
+                               os.path.join(plug, "function_map_%d.orig.so" % p)] + objs)
+        for o in objs:
+            os.remove(o)
+    # the benchmark's plaintext and scalar values, by input name (bootstrap_runner.py:84-87)
+    config = "b33" if gpus == 1 else "b33_multi"
     code = ("import sys, numpy as np; sys.path.insert(0, %r); from bootstrap_values import get_bootstrap_runner_inputs; "
-            "raw = get_bootstrap_runner_inputs('b33', 18); "
+            "raw = get_bootstrap_runner_inputs(%r, 18); "
             "np.savez_compressed(%r, **{'v:' + k: np.asarray(v[0]) for k, v in raw.items()}, "
-            "**{'s:' + k: np.asarray(float(v[1])) for k, v in raw.items()})") % (run, os.path.join(plug, "raw_inputs.npz"))
+            "**{'s:' + k: np.asarray(float(v[1])) for k, v in raw.items()})") % (run, config, os.path.join(plug, "raw_inputs.npz"))
     subprocess.check_call([sys.executable, "-c", code], cwd=run)
     print("made", tag)
 
@@ -161,7 +165,8 @@ def main():
                                        "-D__FNAME__=%s" % fn, "-I" + kern,
                                        "-o", os.path.join(plug, "function_map_%d.orig.so" % p)] + cu)
         print("made", tag, functions)
-    make_bootstrap(ref, pkg, kern)
+    for gpus in (1, 2, 4, 8):
+        make_bootstrap(ref, pkg, kern, gpus)
 
 
 if __name__ == "__main__":

@@ -357,27 +357,84 @@ def test_periodic_plaintext_is_the_subsampled_transform(emu):
 
 # the reference's bootstrapping benchmark ---------------------------------------------------------------
 
-BOOT_TAG, BOOT_FN = "bootstrap_32K_1gpu", "bootstrap_32Kslots_33levels_1gpus"
+BOOT_TAG, BOOT_FN = "bootstrap_32K_%dgpu", "bootstrap_32Kslots_33levels_%dgpus"
 
 
-def bootstrap_directory(tmp_path):
-    """<compiled>/<function>/ of the compiled bootstrapping benchmark (benchmarks/bootstrap_32K, one GPU)."""
+def bootstrap_directory(tmp_path, gpus=1):
+    """<compiled>/<function>/ of the compiled bootstrapping benchmark (benchmarks/bootstrap_32K)."""
     import lzma
-    orig = os.path.join(PLUGINS, BOOT_TAG, "function_map_0.orig.so")
-    if not os.path.exists(orig):
-        pytest.skip("the generated plugin of %s was not built (tests/golden/programs/make_programs.py)" % BOOT_TAG)
-    d = tmp_path / "compiled" / BOOT_FN
+    tag, fn = BOOT_TAG % gpus, BOOT_FN % gpus
+    d = tmp_path / "compiled" / fn
     d.mkdir(parents=True)
-    for f in ("functions0", "inputs0", "program_inputs"):
-        with lzma.open(os.path.join(PROGS, BOOT_TAG, f + ".xz"), "rb") as src, open(d / f, "wb") as dst:
+    names = ["program_inputs"] + ["%s%d" % (f, p) for p in range(gpus) for f in ("functions", "inputs")]
+    for f in names:
+        with lzma.open(os.path.join(PROGS, tag, f + ".xz"), "rb") as src, open(d / f, "wb") as dst:
             dst.write(src.read())
-    shutil.copy(orig, d / "function_map_0.so")
+    for p in range(gpus):
+        shutil.copy(os.path.join(PLUGINS, tag, "function_map_%d.orig.so" % p), d / ("function_map_%d.so" % p))
     return tmp_path / "compiled"
 
 
-def bootstrap_raw_inputs():
-    z = np.load(os.path.join(PLUGINS, BOOT_TAG, "raw_inputs.npz"))
+def bootstrap_built(gpus=1):
+    tag = BOOT_TAG % gpus
+    return all(os.path.exists(os.path.join(PLUGINS, tag, f)) for f in
+               ["raw_inputs.npz"] + ["function_map_%d.orig.so" % p for p in range(gpus)])
+
+
+def bootstrap_raw_inputs(gpus=1):
+    z = np.load(os.path.join(PLUGINS, BOOT_TAG % gpus, "raw_inputs.npz"))
     return {k[2:]: (z[k][()] if z[k].ndim == 0 else z[k], float(z["s:" + k[2:]])) for k in z.files if k.startswith("v:")}
+
+
+def bootstrap_run(tmp_path, gpus=1, partition=0, comm=None, gather=None, device=0, barrier=None, runs=5):
+    """benchmarks/bootstrap_32K/bootstrap_runner.py:83-170 with this module in place of cerium.runtime: a level-2
+    ciphertext of unit-modulus complex slots is bootstrapped to level 18 by the reference's compiled program
+    (one GPU: 195 key digits, 259 plaintexts, 31 scalars, 347 launches) and decrypted.
+    Returns (milliseconds per run, precision bits as the runner prints them, steps, setup seconds)."""
+    import time
+    import torch
+    fn = BOOT_FN % gpus
+    compiled = bootstrap_directory(tmp_path, gpus)
+    rnd = random.Random(10)
+
+    def generate_secret_key(hamming_weight):                       # bootstrap_runner.py:29-43
+        key = [0] * (2 * SLOTS)
+        for position in rnd.sample(range(2 * SLOTS), hamming_weight):
+            key[position] = rnd.choice((-1, 1))
+        return key
+    raw_inputs = runtime.RawInputsWrapper(bootstrap_raw_inputs(gpus))
+    context = runtime.Context(SLOTS, PRIMES, device=device)
+    seed = np.random.default_rng(10).integers(0, 2 ** 32 - 1, size=8).tolist()
+    encryptor_context = runtime.CKKSEncryptorContext(context, generate_secret_key(SLOTS), generate_secret_key(32), seed)
+    encryptor = runtime.CKKSEncryptor(encryptor_context, seed)
+    inp_scale = PRIMES[1] * PRIMES[0] / (1 << 5)                   # log_message_ratio = 5
+    arr = np.exp(1j * np.random.default_rng(10).uniform(0, 2 * np.pi, SLOTS))
+    inputs = runtime.RawInputsWrapper({"x": (arr, inp_scale)})
+    program = runtime.FusedKernelProgram(context, str(compiled), fn)
+    t0 = time.time()
+    functions = program.make_program(gpus, {fn: {"use_cudagraph": "True"}}, raw_inputs, partition=partition, comm=comm,
+                                     encryptor_context=encryptor_context)
+    t_setup = time.time() - t0
+    main = functions[fn]
+    generator = runtime.IOGenerator(context)
+    encrypted_inputs = generator.generate_ciphertext_inputs(str(compiled / fn / "program_inputs"), inputs, encryptor_context)
+    main.copy_ciphertext_inputs_to_gpu(str(compiled / fn / "inputs"), gpus, encrypted_inputs)
+    program.run()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    stream = context.stream()
+    if barrier is not None:
+        barrier()
+    e0.record()
+    for _ in range(runs):
+        main.program.run(stream)
+    e1.record()
+    torch.cuda.synchronize()
+    out = main.get_program_outputs()["z"]
+    if gather is not None:
+        out = gather(out)
+    z = np.asarray(encryptor.decrypt_and_decode(out, inp_scale))
+    err = float(np.max(np.abs(z - arr)))
+    return e0.elapsed_time(e1) / runs, float(-np.log2(err)), main.program.num_steps, t_setup
 
 
 def test_bootstrap_program_records():
@@ -388,60 +445,87 @@ def test_bootstrap_program_records():
     from cerium_b200 import _capi
     with tempfile.TemporaryDirectory() as t:
         path = os.path.join(t, "functions0")
-        with lzma.open(os.path.join(PROGS, BOOT_TAG, "functions0.xz"), "rb") as src, open(path, "wb") as dst:
-            dst.write(src.read())
-        recs = _capi.inspect_program(_capi.load(), path)
-    kinds = {}
-    for r in recs:
-        kinds[r["type"]] = kinds.get(r["type"], 0) + 1
-    assert kinds == {"int": 62, "bco": 56, "ntt": 26, "generic": 137, "pmu": 19, "mov": 115, "sud": 37, "rsv": 10}
+        def kinds(gpus, part):
+            with lzma.open(os.path.join(PROGS, BOOT_TAG % gpus, "functions%d.xz" % part), "rb") as src, open(path, "wb") as dst:
+                dst.write(src.read())
+            out = {}
+            for r in _capi.inspect_program(_capi.load(), path):
+                out[r["type"]] = out.get(r["type"], 0) + 1
+            return out
+        assert kinds(1, 0) == {"int": 62, "bco": 56, "ntt": 26, "generic": 137, "pmu": 19, "mov": 115, "sud": 37, "rsv": 10}
+        # the builds for several GPUs exchange limbs: all-gathers, reduce-scatters and all-reduces
+        k8 = kinds(8, 0)
+        assert (k8["drm"], k8["ags"], k8["ard"], k8["rsv"]) == (27, 8, 6, 11)
 
 
 @pytest.mark.gpu
 def test_bootstrap_benchmark_program(tmp_path):
-    """benchmarks/bootstrap_32K/bootstrap_runner.py:83-170 with this module in place of cerium.runtime: a level-2
-    ciphertext of unit-modulus complex slots is bootstrapped to level 18 by the reference's compiled program
-    (195 key digits, 259 plaintexts, 31 scalars, 347 launches) and decrypted; the precision is printed the way
-    the runner prints it."""
-    import time
-    import torch
-    raw_path = os.path.join(PLUGINS, BOOT_TAG, "raw_inputs.npz")
-    compiled = bootstrap_directory(tmp_path)
-    if not os.path.exists(raw_path):
-        pytest.skip("the benchmark's plaintext values were not generated (tests/golden/programs/make_programs.py)")
-    rnd = random.Random(10)
+    if not bootstrap_built(1):
+        pytest.skip("the benchmark's plugin and plaintext values were not built (tests/golden/programs/make_programs.py)")
+    ms, bits, steps, setup = bootstrap_run(tmp_path)
+    print("bootstrap program, 1 GPU: %d steps, setup %.1f s, %.2f ms per run, precision bits %.2f" % (steps, setup, ms, bits))
+    assert steps == 347 and bits > 15, "the bootstrapped ciphertext does not decrypt to its input"
 
-    def generate_secret_key(hamming_weight):                       # bootstrap_runner.py:29-43
-        key = [0] * (2 * SLOTS)
-        for position in rnd.sample(range(2 * SLOTS), hamming_weight):
-            key[position] = rnd.choice((-1, 1))
-        return key
-    raw_inputs = runtime.RawInputsWrapper(bootstrap_raw_inputs())
-    context = runtime.Context(SLOTS, PRIMES)
-    seed = np.random.default_rng(10).integers(0, 2 ** 32 - 1, size=8).tolist()
-    encryptor_context = runtime.CKKSEncryptorContext(context, generate_secret_key(SLOTS), generate_secret_key(32), seed)
-    encryptor = runtime.CKKSEncryptor(encryptor_context, seed)
-    inp_scale = PRIMES[1] * PRIMES[0] / (1 << 5)                   # log_message_ratio = 5
-    arr = np.exp(1j * np.random.default_rng(10).uniform(0, 2 * np.pi, SLOTS))
-    inputs = runtime.RawInputsWrapper({"x": (arr, inp_scale)})
-    program = runtime.FusedKernelProgram(context, str(compiled), BOOT_FN)
-    t0 = time.time()
-    functions = program.make_program(1, {BOOT_FN: {"use_cudagraph": "True"}}, raw_inputs, encryptor_context=encryptor_context)
-    t_setup = time.time() - t0
-    main = functions[BOOT_FN]
-    generator = runtime.IOGenerator(context)
-    encrypted_inputs = generator.generate_ciphertext_inputs(str(compiled / BOOT_FN / "program_inputs"), inputs, encryptor_context)
-    main.copy_ciphertext_inputs_to_gpu(str(compiled / BOOT_FN / "inputs"), 1, encrypted_inputs)
-    program.run()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    stream = context.stream()
-    e0.record()
-    for _ in range(5):
-        main.program.run(stream)
-    e1.record()
-    torch.cuda.synchronize()
-    z = np.asarray(encryptor.decrypt_and_decode(main.get_program_outputs()["z"], inp_scale))
-    err = float(np.max(np.abs(z - arr)))
-    print("bootstrap program: %d steps, setup %.1f s, %.2f ms per run; max absolute error %.2e, precision bits %.2f"
-          % (main.program.num_steps, t_setup, e0.elapsed_time(e1) / 5, err, -np.log2(err)))
-    assert -np.log2(err) > 10, "the bootstrapped ciphertext does not decrypt to its input"
+
+def _bootstrap_worker(rank, world, port, workdir, ret):
+    import sys
+    import pathlib
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from cerium_b200 import _capi, sharded
+    comm = sharded.nccl_comm(_capi.load(), rank, world, rank)
+
+    def gather(ct):
+        parts = [None] * world
+        dist.all_gather_object(parts, (ct.rns_base_ids, ct.c0, ct.c1))
+        ids = sorted(i for p in parts for i in p[0])
+        rows0 = {i: p[1][k] for p in parts for k, i in enumerate(p[0])}
+        rows1 = {i: p[2][k] for p in parts for k, i in enumerate(p[0])}
+        return runtime.Ciphertext(np.stack([rows0[i] for i in ids]), np.stack([rows1[i] for i in ids]), ids)
+    try:
+        ms, bits, steps, setup = bootstrap_run(pathlib.Path(workdir) / ("rank%d" % rank), world, rank, comm, gather, rank,
+                                               barrier=dist.barrier)
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ret[rank] = (float(t.item()), bits, steps, setup)
+    finally:
+        comm.close()
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_bootstrap_benchmark_program_multi_gpu(tmp_path, world):
+    """The benchmark compiled for several GPUs: one process per partition; drm, ags and ard records on NCCL."""
+    import socket
+    import torch
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    if not bootstrap_built(world):
+        pytest.skip("the benchmark's plugins and plaintext values were not built (tests/golden/programs/make_programs.py)")
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_bootstrap_worker, args=(r, world, port, str(tmp_path), ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(900)
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    ms, bits, steps, setup = ret[0]
+    print("bootstrap program, %d GPUs: %d steps on partition 0, setup %.1f s, %.2f ms per run (max over ranks), "
+          "precision bits %.2f" % (world, steps, setup, ms, bits))
+    assert all(ret[r][1] > 15 for r in range(world)), dict(ret)
