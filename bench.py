@@ -811,8 +811,165 @@ class BootstrapWorkload(Workload):
         return 103 * dt * 1e3, "one key switch (L=34, K=5, dnum=7) on the oracle port x the 103 key switches of a bootstrap"
 
 
+class _DevicePtr:
+    """A raw device limb as something torch can wrap without a copy."""
+    def __init__(self, ptr, words):
+        self.__cuda_array_interface__ = {"shape": (words,), "typestr": "<i4", "data": (int(ptr), False), "version": 2}
+
+
+class BootstrapProgramWorkload(Workload):
+    """The reference's OWN bootstrapping benchmark (benchmarks/bootstrap_32K/bootstrap.py: 2^15 slots, 33 levels,
+    28-bit primes, sparse-secret encapsulation; one GPU: 462 records, 195 key digits, 259 plaintexts), compiled by
+    the reference's compiler (tests/golden/programs/make_programs.py) and replayed by this library's executor
+    through the Python surface of cerium_b200/runtime.py - the sequence of benchmarks/bootstrap_32K/
+    bootstrap_runner.py:83-170.  The transform, base-conversion and SuD records run on this library's kernels; the
+    element-wise records run on the kernels the compiler generated for the program (the plugin contract).  With
+    --gpus N the build of the program for N GPUs runs as N processes, its drm / ags / ard records on NCCL.
+    Keys are generated here from a seeded secret; plaintext diagonals and coefficients are the benchmark's own
+    values.  `verified` = the bootstrapped ciphertext decrypts to its input slots with at least 15 bits."""
+    name = "reference_bootstrap_32K_33levels_compiled_program_u32"
+    metric = "bootstrap_latency_ms"
+    unit = "ms"
+    ops_per_step = 1
+    latency_metric = True
+    dtype = "u32"
+    inflight = 1
+
+    def setup(self, lib, torch, rank, world=1, sharded=False, comm=None, **_):
+        import lzma
+        import random
+        import shutil
+        import tempfile
+        from cerium_b200 import _capi, runtime
+        self.torch, self.rank, self.world, self.comm = torch, rank, world, comm
+        root = os.path.dirname(os.path.abspath(__file__))
+        tag, fn = "bootstrap_32K_%dgpu" % world, "bootstrap_32Kslots_33levels_%dgpus" % world
+        fixtures = os.path.join(root, "tests", "golden", "programs", tag)
+        built = os.path.join(root, "oracle", "_ref", "programs", tag)
+        need = [os.path.join(built, "raw_inputs.npz")] + [os.path.join(built, "function_map_%d.orig.so" % p) for p in range(world)]
+        if not os.path.isdir(fixtures) or not all(os.path.exists(f) for f in need):
+            raise SystemExit("bench.py: the compiled bootstrapping program for %d GPU(s) is not built "
+                             "(python tests/golden/programs/make_programs.py)" % world)
+        self.tmp = tempfile.mkdtemp(prefix="cerium_boot_r%d_" % rank)
+        d = os.path.join(self.tmp, fn)
+        os.makedirs(d)
+        for f in ["program_inputs"] + ["%s%d" % (k, p) for p in range(world) for k in ("functions", "inputs")]:
+            with lzma.open(os.path.join(fixtures, f + ".xz"), "rb") as src, open(os.path.join(d, f), "wb") as dst:
+                dst.write(src.read())
+        for p in range(world):
+            shutil.copy(os.path.join(built, "function_map_%d.orig.so" % p), os.path.join(d, "function_map_%d.so" % p))
+        z = np.load(os.path.join(built, "raw_inputs.npz"))
+        raw = {k[2:]: (z[k][()] if z[k].ndim == 0 else z[k], float(z["s:" + k[2:]])) for k in z.files if k.startswith("v:")}
+        slots = N // 2
+        primes = params.reference_primes_28bit(64, LOGN)
+        rnd = random.Random(10)
+
+        def secret(weight):
+            key = [0] * N
+            for pos in rnd.sample(range(N), weight):
+                key[pos] = rnd.choice((-1, 1))
+            return key
+        self.context = runtime.Context(slots, primes, lib=lib, device=torch.cuda.current_device())
+        seed = np.random.default_rng(10).integers(0, 2 ** 32 - 1, size=8).tolist()
+        self.ectx = runtime.CKKSEncryptorContext(self.context, secret(slots), secret(32), seed)
+        self.encryptor = runtime.CKKSEncryptor(self.ectx, seed)
+        self.scale = primes[1] * primes[0] / (1 << 5)
+        self.slots_in = np.exp(1j * np.random.default_rng(10).uniform(0, 2 * np.pi, slots))
+        prog = runtime.FusedKernelProgram(self.context, self.tmp, fn)
+        self.fn = prog.make_program(world, {}, runtime.RawInputsWrapper(raw), partition=rank, comm=comm,
+                                    encryptor_context=self.ectx)[fn]
+        gen = runtime.IOGenerator(self.context)
+        self.ct_in = gen.generate_ciphertext_inputs(os.path.join(d, "program_inputs"),
+                                                    runtime.RawInputsWrapper({"x": (self.slots_in, self.scale)}), self.ectx)
+        self.fn.copy_ciphertext_inputs_to_gpu("", world, self.ct_in)
+        self.program = self.fn.program
+        recs = _capi.inspect_program(lib, os.path.join(d, "functions%d" % rank))
+        self.gpu_launches_per_step = self.program.num_steps
+        self.transform_limbs = sum(r["outputs"] for r in recs if r["type"] in ("ntt", "int"))
+        self.ntt_limbs = max(r["outputs"] for r in recs if r["type"] == "ntt")
+        # algorithmic bytes of a run: every record reads its inputs and writes its outputs once
+        self.alg_bytes = sum((r["outputs"] + r["inputs"]) * N * 4 for r in recs if r["type"] != "mov")
+        # the limbs of the input and output terms this partition holds, as torch views of program memory
+        def views(stream_name):
+            out = []
+            for term, desc, bases in self.fn.streams.get(stream_name, []):
+                for l in self.fn._mine(term, bases):
+                    t = torch.as_tensor(_DevicePtr(self.program.memory("%s(%d)" % (term, l)), N), device="cuda")
+                    out.append((desc, l, t))
+            return out
+        self.in_views, self.out_views = views("Ciphertext Stream"), views("Output Stream")
+
+    def step(self):
+        self.program.run(self.torch.cuda.current_stream().cuda_stream)
+
+    def verify(self, orc_mod):
+        import torch.distributed as dist
+        del orc_mod                                  # checked by decryption, not by the CPU restatement
+        self.step()
+        self.torch.cuda.synchronize()
+        ct = self.fn.get_program_outputs()["z"]
+        if self.world > 1:
+            from cerium_b200 import runtime
+            parts = [None] * self.world
+            dist.all_gather_object(parts, (ct.rns_base_ids, ct.c0, ct.c1))
+            ids = sorted(i for p in parts for i in p[0])
+            r0 = {i: p[1][k] for p in parts for k, i in enumerate(p[0])}
+            r1 = {i: p[2][k] for p in parts for k, i in enumerate(p[0])}
+            ct = runtime.Ciphertext(np.stack([r0[i] for i in ids]), np.stack([r1[i] for i in ids]), ids)
+        z = np.asarray(self.encryptor.decrypt_and_decode(ct, self.scale))
+        self.precision_bits = float(-np.log2(np.max(np.abs(z - self.slots_in))))
+        return bool(self.precision_bits > 15)
+
+    def e2e_step(self):
+        if getattr(self, "pipe", None) is None:
+            from cerium_b200.host_pipeline import HostPipeline
+            torch = self.torch
+
+            def op(ins, outs, stream):
+                for k, (_, _, view) in enumerate(self.in_views):
+                    view.copy_(ins[0][k], non_blocking=True)
+                self.program.run(stream)
+                for k, (_, _, view) in enumerate(self.out_views):
+                    outs[0][k].copy_(view, non_blocking=True)
+            self.pipe = HostPipeline(torch, [(len(self.in_views), N)], [(len(self.out_views), N)], op, dtype=torch.int32)
+            rows = []
+            for desc, l, _ in self.in_views:
+                var, poly = desc.split(":")
+                ct = self.ct_in[var]
+                rows.append((ct.c0 if poly == "c0" else ct.c1)[ct.rns_base_ids.index(l)])
+            self.host_in = torch.from_numpy(np.stack(rows).view(np.int32).copy()).pin_memory()
+        self.pipe.submit([self.host_in])
+        return self.pipe.in_bytes, self.pipe.out_bytes
+
+    def roofline_setup(self):
+        self.rl_idx = list(range(min(self.ntt_limbs, 64)))
+        gen = self.torch.Generator(device="cuda").manual_seed(5)
+        self.rl_buf = self.torch.randint(0, 1 << 27, (len(self.rl_idx), N), dtype=self.torch.int32, device="cuda", generator=gen)
+        self.rl_bytes = 2 * len(self.rl_idx) * N * 4
+        self.rl_name = "forward NTT (column pass + row pass), %d limbs u32 (the program's widest ntt record)" % len(self.rl_idx)
+
+    def roofline_step(self):
+        self.context.handle.ntt_forward(self.rl_buf.data_ptr(), self.rl_buf.data_ptr(), self.rl_idx,
+                                        stream=self.torch.cuda.current_stream().cuda_stream)
+
+    def cpu_sample(self, orc_mod):
+        """The transforms of one run on the CPU port (a lower bound of the CPU time: element-wise products, base
+        conversions and divisions are left out)."""
+        rng = np.random.default_rng(1)
+        primes = params.reference_primes_28bit(64, LOGN)
+        octx = orc_mod.OracleContext(LOGN, primes)
+        idx = list(range(48))
+        x = np.stack([rng.integers(0, primes[p], size=N, dtype=np.uint64) for p in idx])
+        t0 = time.perf_counter()
+        octx.ntt_forward(x, idx)
+        dt = time.perf_counter() - t0
+        limbs = getattr(self, "transform_limbs", 4200)
+        return dt / len(idx) * limbs * 1e3, ("48 forward NTTs on the oracle port, scaled to the %d limb transforms of one run; "
+                                             "lower bound, the other records are left out" % limbs)
+
+
 WORKLOADS = {"hrot": HRotWorkload, "hmult": HMultWorkload, "ntt": NttWorkload, "hoisted": HoistedWorkload,
-             "bsgs": BsgsWorkload, "bootstrap": BootstrapWorkload}
+             "bsgs": BsgsWorkload, "bootstrap": BootstrapWorkload, "bootstrap_program": BootstrapProgramWorkload}
 
 
 # ---------------------------------------------------------------------------------------
@@ -842,7 +999,7 @@ def run_reference_arm(args, wl):
         "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": value if getattr(wl, "latency_metric", False) else 1e3 * ops / value,
         "higher_is_better": not getattr(wl, "latency_metric", False), "scaling": "weak", "vs_baseline": None,
-        "dtype": "u64", "data": "synthetic",
+        "dtype": getattr(wl, "dtype", "u64"), "data": "synthetic",
         "config": {"workload": wl.name},
         "note": "CPU port of the reference algorithm (SEAL-based reference runtime not buildable here)",
         "cpu_baseline": {"value": value, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",
@@ -911,10 +1068,12 @@ def roofline_of(torch, wl, peak, peak_kind, iters=20):
     torch.cuda.synchronize()
     rl_ms = r0.elapsed_time(r1) / iters
     achieved = wl.rl_bytes / (rl_ms / 1e3) / 1e9
-    limbs = wl.rl_bytes // (2 * N * 8)
+    u32 = getattr(wl, "dtype", "u64") == "u32"
+    limbs = wl.rl_bytes // (2 * N * (4 if u32 else 8))
     return {"bound": "hbm", "kernel": wl.rl_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
-            "frac": achieved / peak, "traffic": NTT_PAIR_DRAM_BYTES_PER_LIMB * limbs,
-            "traffic_source": "profiles/ (ncu capture of the forward NTT pair, scaled by limbs)",
+            "frac": achieved / peak, "traffic": None if u32 else NTT_PAIR_DRAM_BYTES_PER_LIMB * limbs,
+            "traffic_source": ("no ncu capture of the 32-bit transform pair" if u32 else
+                               "profiles/ (ncu capture of the forward NTT pair, scaled by limbs)"),
             "peak_kind": peak_kind, "ms_per_launch_pair": rl_ms, "algorithmic_bytes": wl.rl_bytes}, rl_ms, limbs
 
 
@@ -971,8 +1130,8 @@ def main():
         args.warmup = args.warmup if args.warmup is not None else 1
         run_reference_arm(args, wl)
         return
-    slow = args.workload in ("bootstrap", "bsgs")
-    args.steps = args.steps if args.steps is not None else (20 if args.workload == "bootstrap" else 200 if slow else 2000)
+    slow = args.workload in ("bootstrap", "bsgs", "bootstrap_program")
+    args.steps = args.steps if args.steps is not None else (20 if args.workload == "bootstrap" else 50 if args.workload == "bootstrap_program" else 200 if slow else 2000)
     args.warmup = max(3, args.warmup if args.warmup is not None else (3 if slow else 50))
 
     import torch
@@ -989,9 +1148,13 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     lib = _capi.load()
-    sharded = world > 1 and args.parallelism in ("auto", "limb") and args.workload == "hrot"
+    sharded = world > 1 and ((args.parallelism in ("auto", "limb") and args.workload == "hrot") or args.workload == "bootstrap_program")
     comm = None
-    if sharded:
+    if sharded and args.workload == "bootstrap_program":
+        from cerium_b200 import sharded as sh
+        comm = sh.nccl_comm(lib, rank, world, local_rank)
+        wl.setup(lib, torch, rank, world, True, comm=comm)
+    elif sharded:
         from cerium_b200 import sharded as sh
         comm = sh.nccl_comm(lib, rank, world, local_rank)
         wl.setup(lib, torch, rank, world, True, comm=comm, ext_split=args.ext == "split",
@@ -1053,7 +1216,7 @@ def main():
         side["latency_ms_one_op_in_flight"] = time_blocks(torch, dist, world, wl, lsteps, 1, barrier)[0] / lsteps
         wl.inflight = keep
     # N > 1: the other parallelism beside the headline, and the collectives of one sharded operation alone
-    if sharded:
+    if sharded and args.workload == "hrot":
         for _ in range(5):
             wl.collective_step()
         barrier()
@@ -1118,14 +1281,17 @@ def main():
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": not latency,
             "scaling": "strong" if sharded else "weak",
-            "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+            "vs_baseline": None, "dtype": getattr(wl, "dtype", "u64"), "data": "synthetic",
             "config": {"workload": wl.name},
             "verified": verified,
             "l2": "working set larger than L2 (keys + ciphertexts + workspace > 126 MB)",
             "inflight": getattr(wl, "inflight", 1),
             "parallelism": ("single GPU" if world == 1 else
                             "every ciphertext and key limb-sharded over %d ranks (%s extension limbs), NCCL all-gather "
-                            "where limbs must meet, %d operations in flight" % (world, args.ext, wl.inflight) if sharded
+                            "where limbs must meet, %d operations in flight" % (world, args.ext, wl.inflight)
+                            if sharded and args.workload == "hrot" else
+                            "the program as the reference's compiler partitioned it over %d GPUs, one process per partition, "
+                            "drm / ags / ard records on NCCL" % world if sharded
                             else "independent ciphertexts per GPU"),
             "repeat": {"blocks": len(block_ms), "steps_per_block": args.steps, "ms_per_step_median": per_step[len(per_step) // 2],
                        "ms_per_step_min": per_step[0], "ms_per_step_max": per_step[-1]},
@@ -1139,14 +1305,20 @@ def main():
             # the 64-bit transforms are also bound by arithmetic: butterflies per second of the same launch
             # pair against the register-only rate of the butterfly these primes use (FP64 pipe for primes
             # below 2^50), measured on this GPU just now
-            "arith_roofline": {"pipe": "fp64", "achieved_gbutterfly_s": rl_limbs * (N // 2) * 16 / (rl_ms / 1e3) / 1e9,
-                               "peak_gbutterfly_s": probe["butterfly_u64_fp64"], "probe": probe},
+            "arith_roofline": ({"pipe": "int32", "achieved_gbutterfly_s": rl_limbs * (N // 2) * 16 / (rl_ms / 1e3) / 1e9,
+                                "peak_gbutterfly_s": probe["butterfly_u32"], "probe": probe}
+                               if getattr(wl, "dtype", "u64") == "u32" else
+                               {"pipe": "fp64", "achieved_gbutterfly_s": rl_limbs * (N // 2) * 16 / (rl_ms / 1e3) / 1e9,
+                                "peak_gbutterfly_s": probe["butterfly_u64_fp64"], "probe": probe}),
             "step_algorithmic_gbs": job_ops * wl.alg_bytes * args.steps / (ms / 1e3) / 1e9,
             "clocks": clocks,
         }
         line["arith_roofline"]["frac"] = (line["arith_roofline"]["achieved_gbutterfly_s"]
                                           / line["arith_roofline"]["peak_gbutterfly_s"])
         line.update(side)
+        if hasattr(wl, "precision_bits"):
+            line["precision_bits"] = wl.precision_bits
+            line["verified_by"] = "decryption: the output ciphertext against the input slots (bootstrap_runner.py:159-170)"
         if world == 1 and args.workload == "hrot" and not args.no_sub:
             line["sub"] = {name: sub_measurement(torch, lib, name, 200, peak, peak_kind, oracle) for name in ("hmult", "ntt")}
         if not args.no_cpu_baseline and world == 1:
