@@ -1199,7 +1199,14 @@ def main():
     wl.join()
     barrier()
     sampler.mark_start()
+    # under a profiler started with its collection off, only the timed blocks are collected
+    profile_range = bool(os.environ.get("CERIUM_BENCH_PROFILE_RANGE"))
+    if profile_range:
+        torch.cuda.profiler.start()
     block_ms = time_blocks(torch, dist, world, wl, args.steps, max(1, args.blocks), barrier)
+    if profile_range:
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
     ms = block_ms[0]
 
     peak, peak_kind = measured_peaks()

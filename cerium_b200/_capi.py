@@ -108,6 +108,7 @@ SIGNATURES = {
     "cerium_program_num_steps": (C.c_int, [_vp]),
     "cerium_program_memory": (C.c_int, [_vp, C.c_char_p, C.POINTER(_vp)]),
     "cerium_program_run": (C.c_int, [_vp, _vp]),
+    "cerium_program_capture": (C.c_int, [_vp]),
     "cerium_program_write": (C.c_int, [_vp, C.c_char_p, C.POINTER(C.c_uint32), C.c_int, _vp, _vp]),
     "cerium_program_read": (C.c_int, [_vp, C.c_char_p, C.POINTER(C.c_uint32), C.c_int, _vp, _vp]),
     "cerium_program_inspect": (C.c_int, [C.c_char_p, C.c_char_p, _sz, C.POINTER(C.c_int)]),
@@ -429,6 +430,10 @@ class Program:
 
     def run(self, stream: int = 0):
         self.ctx.lib.check(self.ctx.lib.dll.cerium_program_run(self.h, stream))
+
+    def capture(self):
+        """Records one run into a CUDA graph; later runs replay it."""
+        self.ctx.lib.check(self.ctx.lib.dll.cerium_program_capture(self.h))
 
     def close(self):
         if getattr(self, "h", None) and self.ctx.h:

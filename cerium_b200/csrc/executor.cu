@@ -356,6 +356,7 @@ struct cerium_program {
   std::map<uint32_t, const uint32_t*> rot_tables;      // Galois element -> device inverse table
   const W *d_moduli = nullptr, *d_ratios = nullptr;
   const uint32_t* d_k = nullptr;
+  cudaGraphExec_t graph = nullptr;                    // one captured run (cerium_program_capture), replayed by run
   std::vector<cerium_program*> callees;               // functions this one calls (owned)
   std::string functions_path;                          // <programs>/<function>/functions<p>
   int depth = 0;
@@ -820,6 +821,7 @@ int cerium_program_destroy(cerium_program* p) {
   if (!p) return CERIUM_OK;
   DeviceGuard guard(p->ctx->device);
   for (cerium_program* c : p->callees) cerium_program_destroy(c);
+  if (p->graph != nullptr) cudaGraphExecDestroy(p->graph);
   for (void* d : p->allocs) cudaFree(d);
   // the plugin stays loaded: its maps are referenced for the life of the process
   delete p;
@@ -936,9 +938,45 @@ int cerium_program_run(cerium_program* p, void* stream) {
   cerium_context* ctx = p->ctx;
   DeviceGuard guard(ctx->device);
   if (!guard.ok) return fail(CERIUM_ERR_CUDA, "program_run: cannot select device");
+  if (p->graph != nullptr) {
+    CERIUM_CUDA(cudaGraphLaunch(p->graph, (cudaStream_t)stream));
+    return CERIUM_OK;
+  }
   // the launchers of this library find their tables through the context bound to the device
   if (int rc = cerium_function_map_bind(ctx, ctx->device)) return fail(rc, "program_run: cannot bind the context");
   return run_steps(p, (cudaStream_t)stream);
+}
+
+// One run recorded into a CUDA graph on a stream of its own (every table a record's launcher takes was built
+// at load and never changes, so the recording stays valid for the life of the program); exchange records
+// are captured with it.  The reference builds its graph node by node (function_execution.cpp:670-1096).
+int cerium_program_capture(cerium_program* p) {
+  if (!p) return fail(CERIUM_ERR_INVALID, "program_capture: null program");
+  if (p->graph != nullptr) return CERIUM_OK;
+  cerium_context* ctx = p->ctx;
+  DeviceGuard guard(ctx->device);
+  if (!guard.ok) return fail(CERIUM_ERR_CUDA, "program_capture: cannot select device");
+  if (int rc = cerium_function_map_bind(ctx, ctx->device)) return fail(rc, "program_capture: cannot bind the context");
+  cudaStream_t st = nullptr;
+  CERIUM_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+  cudaGraph_t g = nullptr;
+  cudaError_t e = cudaStreamBeginCapture(st, cudaStreamCaptureModeRelaxed);
+  int rc = CERIUM_OK;
+  if (e == cudaSuccess) {
+    rc = run_steps(p, st);
+    e = cudaStreamEndCapture(st, &g);   // always ended, also after a failed step, so that the stream leaves capture mode
+  }
+  cudaGraphExec_t exec = nullptr;
+  if (rc == CERIUM_OK && e == cudaSuccess && g != nullptr) e = cudaGraphInstantiate(&exec, g, 0);
+  if (g != nullptr) cudaGraphDestroy(g);
+  cudaStreamDestroy(st);
+  if (rc != CERIUM_OK) return rc;
+  if (e != cudaSuccess || exec == nullptr) {
+    cudaGetLastError();
+    return fail(CERIUM_ERR_CUDA, std::string("program_capture: ") + cudaGetErrorString(e));
+  }
+  p->graph = exec;
+  return CERIUM_OK;
 }
 
 }  // extern "C"
@@ -957,6 +995,7 @@ int cerium_program_memory(cerium_program*, const char*, void**) { return CERIUM_
 int cerium_program_write(cerium_program*, const char*, const uint32_t*, int, const void*, void*) { return CERIUM_ERR_UNSUPPORTED; }
 int cerium_program_read(cerium_program*, const char*, const uint32_t*, int, void*, void*) { return CERIUM_ERR_UNSUPPORTED; }
 int cerium_program_run(cerium_program*, void*) { return CERIUM_ERR_UNSUPPORTED; }
+int cerium_program_capture(cerium_program*) { return CERIUM_ERR_UNSUPPORTED; }
 }
 
 #endif  // !CERIUM_EMU

@@ -603,7 +603,7 @@ class FusedKernelProgram:
     def make_program(self, gpus: int = 1, options: Optional[dict] = None, inputs: Optional[RawInputsWrapper] = None,
                      partition: int = 0, comm=None, encryptor_context: Optional[CKKSEncryptorContext] = None
                      ) -> Dict[str, CeriumFunctionExecutor]:
-        del options                             # graph mode: replay is in stream mode
+        graph = str(((options or {}).get(self.top) or {}).get("use_cudagraph", "False")).lower() in ("true", "1", "yes")
         if gpus > 1 and comm is None:
             raise ValueError("a function compiled for %d GPUs runs as %d processes: pass partition= and comm=" % (gpus, gpus))
         from . import plugin
@@ -619,6 +619,10 @@ class FusedKernelProgram:
             f.generate_inputs_direct(encryptor_context, inputs)      # no container files: generate into device memory
         else:
             f.generate_inputs(os.path.join(d, "evalkeys"), os.path.join(d, "plaintexts"))
+        if graph:
+            f.program.run(self.context.stream())    # once eagerly (lazy set-up inside the launchers), then recorded
+            self.context._sync()
+            f.program.capture()
         self.functions = {self.top: f}
         return self.functions
 

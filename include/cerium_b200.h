@@ -594,6 +594,10 @@ CERIUM_API void *cerium_function_map_launcher(const char *type, int cugraph);
  *                                  copy_ciphertext_inputs_to_gpu / get_program_outputs do
  *                                  (cerium/runtime/execution/function_io.cpp:958-1100, :1360-1420);
  *                                  both wait for `stream` before they return
+ *   cerium_program_capture         records one run into a CUDA graph (stream capture, the exchange records
+ *                                  included); every later cerium_program_run launches that graph on the
+ *                                  caller's stream - the reference's use_cudagraph mode
+ *                                  (function_execution.cpp:670-1096 builds its graph node by node)
  *   cerium_program_inspect         parses only (no device): one line per record,
  *                                  "id type #outputs #inputs #bases #rots #units #sud #pmu"
  *   comm                           the partitions of a function compiled for several GPUs run as the
@@ -620,6 +624,7 @@ CERIUM_API int cerium_program_write(cerium_program *prog, const char *name, cons
 CERIUM_API int cerium_program_read(cerium_program *prog, const char *name, const uint32_t *limb_ids, int n_limbs,
                                    void *host, void *stream);
 CERIUM_API int cerium_program_run(cerium_program *prog, void *stream);
+CERIUM_API int cerium_program_capture(cerium_program *prog);
 CERIUM_API int cerium_program_inspect(const char *functions_path, char *buf, size_t buf_bytes, int *n_records);
 
 #ifdef __cplusplus

@@ -386,7 +386,7 @@ def bootstrap_raw_inputs(gpus=1):
     return {k[2:]: (z[k][()] if z[k].ndim == 0 else z[k], float(z["s:" + k[2:]])) for k in z.files if k.startswith("v:")}
 
 
-def bootstrap_run(tmp_path, gpus=1, partition=0, comm=None, gather=None, device=0, barrier=None, runs=5):
+def bootstrap_run(tmp_path, gpus=1, partition=0, comm=None, gather=None, device=0, barrier=None, runs=5, graph=False):
     """benchmarks/bootstrap_32K/bootstrap_runner.py:83-170 with this module in place of cerium.runtime: a level-2
     ciphertext of unit-modulus complex slots is bootstrapped to level 18 by the reference's compiled program
     (one GPU: 195 key digits, 259 plaintexts, 31 scalars, 347 launches) and decrypted.
@@ -412,7 +412,7 @@ def bootstrap_run(tmp_path, gpus=1, partition=0, comm=None, gather=None, device=
     inputs = runtime.RawInputsWrapper({"x": (arr, inp_scale)})
     program = runtime.FusedKernelProgram(context, str(compiled), fn)
     t0 = time.time()
-    functions = program.make_program(gpus, {fn: {"use_cudagraph": "True"}}, raw_inputs, partition=partition, comm=comm,
+    functions = program.make_program(gpus, {fn: {"use_cudagraph": str(graph)}}, raw_inputs, partition=partition, comm=comm,
                                      encryptor_context=encryptor_context)
     t_setup = time.time() - t0
     main = functions[fn]
@@ -434,7 +434,23 @@ def bootstrap_run(tmp_path, gpus=1, partition=0, comm=None, gather=None, device=
         out = gather(out)
     z = np.asarray(encryptor.decrypt_and_decode(out, inp_scale))
     err = float(np.max(np.abs(z - arr)))
-    return e0.elapsed_time(e1) / runs, float(-np.log2(err)), main.program.num_steps, t_setup
+    ms = e0.elapsed_time(e1) / runs
+    if gpus == 1 and not graph:
+        # the same program recorded into a CUDA graph (the reference's default mode): same result, replayed
+        before = {k: (v.c0.copy(), v.c1.copy()) for k, v in main.get_program_outputs().items()}
+        main.program.capture()
+        main.program.run(stream)
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(runs):
+            main.program.run(stream)
+        g1.record()
+        torch.cuda.synchronize()
+        after = main.get_program_outputs()
+        assert all(np.array_equal(after[k].c0, before[k][0]) and np.array_equal(after[k].c1, before[k][1]) for k in before), \
+            "graph replay differs from stream replay"
+        print("bootstrap program as a CUDA graph: %.2f ms per run (stream mode %.2f)" % (g0.elapsed_time(g1) / runs, ms))
+    return ms, float(-np.log2(err)), main.program.num_steps, t_setup
 
 
 def test_bootstrap_program_records():
