@@ -70,6 +70,7 @@ SIGNATURES = {
     "cerium_comm_unique_id": (C.c_int, [_vp, _sz]),
     "cerium_comm_init": (C.c_int, [C.POINTER(_vp), _vp, _sz, C.c_int, C.c_int, C.c_int]),
     "cerium_comm_init_callbacks": (C.c_int, [C.POINTER(_vp), C.c_int, C.c_int, C.c_int, _vp]),
+    "cerium_comm_split": (C.c_int, [_vp, C.c_int, C.POINTER(_vp)]),
     "cerium_comm_destroy": (C.c_int, [_vp]),
     "cerium_comm_rank": (C.c_int, [_vp]),
     "cerium_comm_world": (C.c_int, [_vp]),
@@ -382,13 +383,14 @@ class Comm:
 def inspect_program(lib: Library, functions_path: str):
     """Parses a compiled function's kernel stream (no device): list of dicts, one per record."""
     n = C.c_int()
-    buf = C.create_string_buffer(1 << 20)
+    buf = C.create_string_buffer(1 << 22)
     lib.check(lib.dll.cerium_program_inspect(functions_path.encode(), buf, len(buf), C.byref(n)))
-    keys = ("id", "type", "outputs", "inputs", "bases", "rots", "units", "sud", "pmu")
+    keys = ("id", "type", "outputs", "inputs", "bases", "rots", "units", "sud", "pmu", "rsv", "scalars", "comm_size",
+            "comm_num_limbs", "comm_srcs", "comm_dests", "call_args", "callee")
     out = []
     for line in buf.value.decode().splitlines():
         f = line.split()
-        out.append({k: (v if k == "type" else int(v)) for k, v in zip(keys, f)})
+        out.append({k: (v if k in ("type", "callee") else int(v)) for k, v in zip(keys, f)})
     assert len(out) == n.value
     return out
 

@@ -44,6 +44,7 @@ struct NcclApi {
   ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
   ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*CommSplit)(ncclComm_t, int, int, ncclComm_t*, void*) = nullptr;  // NCCL 2.18 and later
   ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*ReduceScatter)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
@@ -78,6 +79,7 @@ NcclApi* nccl_api() {
     api.AllReduce = (decltype(api.AllReduce))sym("ncclAllReduce");
     api.Broadcast = (decltype(api.Broadcast))sym("ncclBroadcast");
     api.GetErrorString = (decltype(api.GetErrorString))sym("ncclGetErrorString");
+    api.CommSplit = (decltype(api.CommSplit))dlsym(api.handle, "ncclCommSplit");  // optional
   });
   return &api;
 }
@@ -102,6 +104,38 @@ int check_comm(const cerium_comm* comm, const char* what) {
 }  // namespace
 
 namespace cerium {
+
+int comm_subgroup(cerium_comm* comm, int size, cerium_comm** out) {
+  if (int rc = check_comm(comm, "comm_split")) return rc;
+  if (size <= 0 || size > comm->world || comm->world % size) return fail(CERIUM_ERR_INVALID, "comm_split: the group size must divide the number of ranks");
+  if (size == comm->world) {
+    *out = comm;
+    return CERIUM_OK;
+  }
+  auto it = comm->subgroups.find(size);
+  if (it != comm->subgroups.end()) {
+    *out = it->second;
+    return CERIUM_OK;
+  }
+  if (comm->has_cb) return fail(CERIUM_ERR_UNSUPPORTED, "comm_split: the caller's transport has no sub-groups");
+#if !defined(CERIUM_EMU)
+  NcclApi* api = nccl_api();
+  if (!api->CommSplit) return fail(CERIUM_ERR_UNSUPPORTED, "comm_split: this NCCL has no ncclCommSplit (2.18 or later is needed)");
+  DeviceGuard guard(comm->device);
+  ncclComm_t sub = nullptr;
+  CERIUM_NCCL(api->CommSplit((ncclComm_t)comm->nccl, comm->rank / size, comm->rank % size, &sub, nullptr), "ncclCommSplit");
+  auto* c = new cerium_comm();
+  c->rank = comm->rank % size;
+  c->world = size;
+  c->device = comm->device;
+  c->nccl = sub;
+  comm->subgroups[size] = c;
+  *out = c;
+  return CERIUM_OK;
+#else
+  return fail(CERIUM_ERR_UNSUPPORTED, "comm_split: no transport");
+#endif
+}
 
 int comm_allgather(cerium_comm* comm, void* recv, const void* send, size_t bytes_per_rank, cudaStream_t stream) {
   if (int rc = check_comm(comm, "allgather")) return rc;
@@ -248,8 +282,15 @@ int cerium_comm_init_callbacks(cerium_comm** out, int rank, int world, int devic
   return CERIUM_OK;
 }
 
+int cerium_comm_split(cerium_comm* comm, int size, cerium_comm** out) {
+  if (!out) return fail(CERIUM_ERR_INVALID, "comm_split: null argument");
+  return comm_subgroup(comm, size, out);
+}
+
 int cerium_comm_destroy(cerium_comm* comm) {
   if (!comm) return CERIUM_OK;
+  for (auto& kv : comm->subgroups) cerium_comm_destroy(kv.second);
+  comm->subgroups.clear();
 #if !defined(CERIUM_EMU)
   if (comm->nccl) {
     DeviceGuard guard(comm->device);

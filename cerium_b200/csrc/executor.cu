@@ -316,6 +316,7 @@ struct Step {
   // rsv: CRT factors, the modulus product, its Barrett ratio (all as words) and the Barrett shift
   const W *rsv_factors = nullptr, *rsv_modulus = nullptr, *rsv_ratio = nullptr;
   uint32_t rsv_k = 0;
+  cerium_comm* comm = nullptr;       // exchange records: the group of partitions the record spans
   cerium_program* callee = nullptr;  // call: the called function, its argument terms bound to this function's memory
   std::vector<std::pair<W*, const W*>> copy_back;  // call: results whose destination is also an argument (dst, src)
   // drm: host lists of the limbs to pack (this rank's sources) and to unpack (every rank's block)
@@ -485,6 +486,16 @@ struct Loader {
     p->d_k = upload(k);
   }
 
+  // The communicator an exchange record runs on: all partitions, or the group of .comm_size consecutive
+  // partitions that holds this one (cerium/runtime/cuda/nccl_ops.cu:185-215).
+  cerium_comm* group(const Record& r, const char* what) {
+    cerium_comm* c = nullptr;
+    if (r.comm_size == 0 || comm_subgroup(p->comm, (int)r.comm_size, &c) != CERIUM_OK)
+      throw std::runtime_error(std::string(what) + " record " + std::to_string(r.id) + " spans " + std::to_string(r.comm_size) +
+                               " partitions: " + cerium_last_error());
+    return c;
+  }
+
   void build(const std::vector<Record>& recs, const FunctionMapType& fmap,
              const std::map<std::string, uint64_t>& scalar_values) {
     // register file: as many registers as the records name
@@ -499,6 +510,19 @@ struct Loader {
           }
     if (any_reg) p->regs = limb_alloc(max_reg + 1);
     reference_tables();
+    // sub-group communicators are created collectively: every partition asks for them in the same order
+    if (p->comm != nullptr) {
+      std::vector<int> sizes;
+      for (const Record& r : recs)
+        if ((r.type == "drm" || r.type == "ags" || r.type == "ard") && r.comm_size > 0 && (int)r.comm_size != p->comm->world &&
+            std::find(sizes.begin(), sizes.end(), (int)r.comm_size) == sizes.end())
+          sizes.push_back((int)r.comm_size);
+      std::sort(sizes.rbegin(), sizes.rend());
+      for (int sz : sizes) {
+        cerium_comm* c = nullptr;
+        if (comm_subgroup(p->comm, sz, &c) != CERIUM_OK) throw std::runtime_error(cerium_last_error());
+      }
+    }
     for (const Record& r : recs) {
       const std::string& ty = r.type;
       if (ty == "mov") continue;  // outputs alias inputs: nothing to run (the reference skips them too)
@@ -509,7 +533,7 @@ struct Loader {
         // (.comm_srcs) receives the sums reduced modulo the primes of .bases.
         cerium_comm* comm = p->comm;
         if (comm == nullptr) throw std::runtime_error("record " + std::to_string(r.id) + " is an " + ty + " record: the function needs a communicator");
-        if ((size_t)comm->world != r.comm_size) throw std::runtime_error(ty + " record " + std::to_string(r.id) + " was compiled for " + std::to_string(r.comm_size) + " partitions");
+        comm = group(r, ty.c_str());
         const size_t blocks = ty == "ags" ? r.comm_size : 1;
         if (r.comm_dests.size() > blocks * r.comm_num_limbs || r.comm_srcs.size() > r.comm_num_limbs || r.bases.size() < r.comm_srcs.size())
           throw std::runtime_error(ty + " record " + std::to_string(r.id) + " lists more limbs than it exchanges");
@@ -517,6 +541,7 @@ struct Loader {
           if (b >= (uint32_t)ctx->n_primes) throw std::runtime_error("prime index out of range in .bases");
         Step s{};
         s.kind = ty == "ags" ? Step::Ags : Step::Ard;
+        s.comm = comm;
         s.id = r.id;
         s.comm_limbs = r.comm_num_limbs;
         // zero-filled: limbs past the gather list stay zero; ags receives into a block of its own behind them
@@ -604,11 +629,12 @@ struct Loader {
       if (ty == "drm") {
         cerium_comm* comm = p->comm;
         if (comm == nullptr) throw std::runtime_error("record " + std::to_string(r.id) + " is a drm (all-gather) record: the function needs a communicator");
-        if ((size_t)comm->world != r.comm_size) throw std::runtime_error("drm record " + std::to_string(r.id) + " was compiled for " + std::to_string(r.comm_size) + " partitions");
+        comm = group(r, "drm");
         if (r.comm_srcs.size() > r.comm_num_limbs || r.comm_dests.size() > r.comm_size * r.comm_num_limbs)
           throw std::runtime_error("drm record " + std::to_string(r.id) + " lists more limbs than it exchanges");
         Step s{};
         s.kind = Step::Drm;
+        s.comm = comm;
         s.id = r.id;
         s.comm_limbs = r.comm_num_limbs;
         s.staging = limb_alloc(r.comm_size * r.comm_num_limbs);
@@ -899,10 +925,10 @@ static int run_steps(cerium_program* p, cudaStream_t st) {
         }
         case Step::Drm: {
           const size_t limb = (size_t)kN * sizeof(W);
-          W* mine = s.staging + (size_t)p->comm->rank * s.comm_limbs * kN;
+          W* mine = s.staging + (size_t)s.comm->rank * s.comm_limbs * kN;
           const dim3 grid(kN / (kPackThreads * 4));
           if (s.n_pack) pack_limbs_kernel<<<dim3(grid.x, (unsigned)s.n_pack), kPackThreads, 0, st>>>(mine, s.pack_tab);
-          if (int rc = comm_allgather(p->comm, s.staging, mine, s.comm_limbs * limb, st)) return rc;
+          if (int rc = comm_allgather(s.comm, s.staging, mine, s.comm_limbs * limb, st)) return rc;
           if (s.n_unpack)
             unpack_limbs_kernel<<<dim3(grid.x, (unsigned)s.n_unpack), kPackThreads, 0, st>>>(s.unpack_tab, s.staging, nullptr, nullptr);
           break;
@@ -913,11 +939,11 @@ static int run_steps(cerium_program* p, cudaStream_t st) {
           if (s.n_pack) pack_limbs_kernel<<<dim3(grid.x, (unsigned)s.n_pack), kPackThreads, 0, st>>>(s.staging, s.pack_tab);
           const W* sums = s.staging;
           if (s.kind == Step::Ags) {
-            W* mine = s.staging + (size_t)p->comm->world * s.comm_limbs * kN;
-            if (int rc = comm_reducescatter_sum(p->comm, mine, s.staging, s.comm_limbs * kN, 32, st)) return rc;
+            W* mine = s.staging + (size_t)s.comm->world * s.comm_limbs * kN;
+            if (int rc = comm_reducescatter_sum(s.comm, mine, s.staging, s.comm_limbs * kN, 32, st)) return rc;
             sums = mine;
           } else {
-            if (int rc = comm_allreduce_sum(p->comm, s.staging, s.staging, s.comm_limbs * kN, 32, st)) return rc;
+            if (int rc = comm_allreduce_sum(s.comm, s.staging, s.staging, s.comm_limbs * kN, 32, st)) return rc;
           }
           if (s.n_unpack)
             unpack_limbs_kernel<<<dim3(grid.x, (unsigned)s.n_unpack), kPackThreads, 0, st>>>(s.unpack_tab, sums, s.unpack_bases, p->d_moduli);
@@ -1008,8 +1034,16 @@ extern "C" int cerium_program_inspect(const char* functions_path, char* buf, siz
   *n_records = (int)recs.size();
   std::ostringstream s;
   for (const Record& r : recs) {
+    size_t call_args = 0;
+    try {
+      call_args = parse_call_args(r.function_args).size();
+    } catch (const std::exception& e) {
+      return fail(CERIUM_ERR_INVALID, std::string("program_inspect: ") + e.what());
+    }
     s << r.id << ' ' << r.type << ' ' << r.outputs.size() << ' ' << r.inputs.size() << ' ' << r.bases.size() << ' '
-      << r.rots.size() << ' ' << parse_base_conv(r.base_conv).size() << ' ' << r.sud.size() << ' ' << r.pmu.size() << '\n';
+      << r.rots.size() << ' ' << parse_base_conv(r.base_conv).size() << ' ' << r.sud.size() << ' ' << r.pmu.size() << ' '
+      << r.rsv.size() << ' ' << r.scalars.size() << ' ' << r.comm_size << ' ' << r.comm_num_limbs << ' ' << r.comm_srcs.size()
+      << ' ' << r.comm_dests.size() << ' ' << call_args << ' ' << (r.function_name.empty() ? "-" : r.function_name) << '\n';
   }
   const std::string text = s.str();
   if (buf && buf_bytes > 0) {

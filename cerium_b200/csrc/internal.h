@@ -8,6 +8,7 @@
 
 #include <cstdint>
 #include <cstdio>
+#include <map>
 #include <string>
 #include <utility>
 #include <vector>
@@ -142,6 +143,7 @@ struct cerium_comm {
   void* nccl = nullptr;  // ncclComm_t when the transport is NCCL
   cerium_comm_callbacks cb = {};
   bool has_cb = false;
+  std::map<int, cerium_comm*> subgroups;  // communicators of `size` consecutive ranks holding this rank (owned)
 };
 
 namespace cerium {
@@ -153,6 +155,10 @@ int comm_reducescatter_sum(cerium_comm* comm, void* recv, const void* send, size
                            cudaStream_t stream);
 int comm_allreduce_sum(cerium_comm* comm, void* recv, const void* send, size_t words, int word_bits, cudaStream_t stream);
 int comm_broadcast(cerium_comm* comm, void* buf, size_t bytes, int root, cudaStream_t stream);
+// The communicator of the `size` consecutive ranks [rank / size * size, ...) that hold this rank (`comm` itself
+// when size is its world); created on first use - a collective call: every rank of `comm` makes it, in the
+// same order - and owned by `comm`.
+int comm_subgroup(cerium_comm* comm, int size, cerium_comm** out);
 
 // Options of create_bconv beyond the public entry point.
 struct BconvOptions {

@@ -286,6 +286,11 @@ CERIUM_API int cerium_comm_unique_id(void *id, size_t id_bytes);
 CERIUM_API int cerium_comm_init(cerium_comm **out, const void *id, size_t id_bytes, int rank, int world, int device);
 CERIUM_API int cerium_comm_init_callbacks(cerium_comm **out, int rank, int world, int device,
                                           const cerium_comm_callbacks *cb);
+/* The communicator of the `size` consecutive ranks that hold this rank (rank / size * size ...), the
+ * reference's comms[n][comm_size][device] (cerium/runtime/cuda/nccl_ops.cu:185-215): programs compiled
+ * for 4 or 8 GPUs also exchange limbs inside half-size groups.  Collective over `comm` (every rank calls it,
+ * in the same order); the result is owned by `comm`.  NCCL transport only. */
+CERIUM_API int cerium_comm_split(cerium_comm *comm, int size, cerium_comm **out);
 CERIUM_API int cerium_comm_destroy(cerium_comm *comm);
 CERIUM_API int cerium_comm_rank(const cerium_comm *comm);
 CERIUM_API int cerium_comm_world(const cerium_comm *comm);
@@ -599,7 +604,8 @@ CERIUM_API void *cerium_function_map_launcher(const char *type, int cugraph);
  *                                  caller's stream - the reference's use_cudagraph mode
  *                                  (function_execution.cpp:670-1096 builds its graph node by node)
  *   cerium_program_inspect         parses only (no device): one line per record,
- *                                  "id type #outputs #inputs #bases #rots #units #sud #pmu"
+ *                                  "id type #outputs #inputs #bases #rots #units #sud #pmu #rsv #scalars
+ *                                  comm_size comm_num_limbs #comm_srcs #comm_dests #call_args callee"
  *   comm                           the partitions of a function compiled for several GPUs run as the
  *                                  ranks of this communicator, one process each (partition p = rank p);
  *                                  its drm records (the all-gather of limbs between partitions,
