@@ -288,6 +288,66 @@ __device__ __forceinline__ void bconv_body_pair32(const BconvDesc<uint32_t>& d,
   }
 }
 
+// 32-bit words, 9 to 32 inputs (the digits of the reference's 28-bit parameter sets hold 10 to 28 limbs): one
+// coefficient per thread, every input in a register, the factor rows padded with zeros to kP = a multiple of
+// four words and read as 16-byte vectors (one shared-memory load per four terms, the same address in every
+// lane).  Residues and factors are below 2^30 (the widest primes a 32-bit context takes), a product is below
+// 2^60, so sixteen of them fit one 64-bit sum: a multiply-accumulate is one wide multiply-add, and an output
+// takes one Barrett reduction (two and an addition beyond sixteen inputs) - against a two-word accumulator
+// with carries and a shared-memory column of inputs in the generic path.  Like the path for at most eight
+// inputs, this one takes canonical residues.
+template <int kP>
+__device__ __forceinline__ void bconv_body_wide32(const BconvDesc<uint32_t>& d, const PrimeConst<uint32_t>* __restrict__ pcs,
+                                                  const uint32_t* sfac, const BconvOut<uint32_t>* sout, int coeff) {
+  static_assert(kP % 4 == 0 && kP > 8 && kP <= 32, "padded input count");
+  uint32_t y[kP];
+#pragma unroll
+  for (int i = 0; i < kP; i++) y[i] = i < d.I ? bconv_input<uint32_t>(d, pcs, i, coeff) : 0u;
+  const int O = d.O;
+#pragma unroll 2
+  for (int j = 0; j < O; j++) {
+    const uint4* f = reinterpret_cast<const uint4*>(sfac + (size_t)j * kP);
+    uint64_t a = 0, b = 0;  // inputs 0..15 and 16..31
+#pragma unroll
+    for (int g = 0; g < kP / 4; g++) {
+      const uint4 v = f[g];
+      uint64_t t = (uint64_t)y[4 * g] * v.x;
+      t += (uint64_t)y[4 * g + 1] * v.y;
+      t += (uint64_t)y[4 * g + 2] * v.z;
+      t += (uint64_t)y[4 * g + 3] * v.w;
+      if (g < 4) a += t; else b += t;
+    }
+    const BconvOut<uint32_t> o = sout[j];
+    PrimeConst<uint32_t> pc;
+    pc.q = o.q;
+    pc.q2 = o.q2;
+    pc.mu_hi = o.mu_hi;
+    pc.mu_lo = o.mu_lo;
+    uint32_t r = barrett2<uint32_t>((uint32_t)(a >> 32), (uint32_t)a, pc);
+    if (kP > 16) r = add_mod<uint32_t>(r, barrett2<uint32_t>((uint32_t)(b >> 32), (uint32_t)b, pc), o.q);
+    if (o.has_sub) r = sub_mod<uint32_t>(r, o.sub, o.q);
+    d.out[(size_t)o.pos * d.out_stride + coeff] = r;
+  }
+}
+
+// The wide path's dispatch on the padded input count.
+__device__ __forceinline__ void bconv_wide32(const BconvDesc<uint32_t>& d, const PrimeConst<uint32_t>* __restrict__ pcs,
+                                             const uint32_t* sfac, const BconvOut<uint32_t>* sout, int coeff) {
+  switch ((d.I + 3) / 4) {
+    case 3: bconv_body_wide32<12>(d, pcs, sfac, sout, coeff); break;
+    case 4: bconv_body_wide32<16>(d, pcs, sfac, sout, coeff); break;
+    case 5: bconv_body_wide32<20>(d, pcs, sfac, sout, coeff); break;
+    case 6: bconv_body_wide32<24>(d, pcs, sfac, sout, coeff); break;
+    case 7: bconv_body_wide32<28>(d, pcs, sfac, sout, coeff); break;
+    default: bconv_body_wide32<32>(d, pcs, sfac, sout, coeff); break;
+  }
+}
+constexpr int kBconvWideMaxInputs = 32;
+template <typename W>
+__host__ __device__ inline bool bconv_is_wide32(int I) {
+  return sizeof(W) == 4 && I > kBconvRegInputs && I <= kBconvWideMaxInputs;
+}
+
 constexpr int kBconvMaxBatch = 24;  // conversions per launch (descriptors travel as parameters)
 
 template <typename W>
@@ -303,6 +363,10 @@ __host__ __device__ inline size_t bconv_smem_bytes(int I, int O) {
   n = (n + 15) / 16 * 16 + ((size_t)O * sizeof(BconvOut<W>) + 15) / 16 * 16;
   if (I > kBconvRegInputs) n += (size_t)I * kBconvThreads * sizeof(W);
   else if (sizeof(W) == 8) n += (size_t)O * I * 16;  // double-precision factor pairs
+  if (bconv_is_wide32<W>(I)) {  // padded factor rows in place of the plain matrix (and no input column)
+    const size_t wide = ((size_t)O * ((I + 3) / 4 * 4) * sizeof(W) + 15) / 16 * 16 + ((size_t)O * sizeof(BconvOut<W>) + 15) / 16 * 16;
+    if (wide > n) n = wide;
+  }
   return n;
 }
 
@@ -324,14 +388,22 @@ __global__ void __launch_bounds__(kBconvThreads, 5)
   d.factors += (size_t)j_first * I;
   d.O = O;
   W* sfac = reinterpret_cast<W*>(smem_raw);
-  const size_t fac_bytes = ((size_t)O * I * sizeof(W) + 15) / 16 * 16;
+  const bool wide = !kPair && bconv_is_wide32<W>(I);
+  const int P = wide ? (I + 3) / 4 * 4 : I;  // words per staged factor row
+  const size_t fac_bytes = ((size_t)O * P * sizeof(W) + 15) / 16 * 16;
   BconvOut<W>* sout = reinterpret_cast<BconvOut<W>*>(smem_raw + fac_bytes);
   const size_t out_bytes = ((size_t)O * sizeof(BconvOut<W>) + 15) / 16 * 16;
   W* scol = reinterpret_cast<W*>(smem_raw + fac_bytes + out_bytes);
   double2* sfp = reinterpret_cast<double2*>(smem_raw + fac_bytes + out_bytes);  // split path only (no scol then)
   const bool split = sizeof(W) == 8 && I <= kBconvRegInputs;
   // stage this CTA's slice of the converter's tables
-  for (int k = threadIdx.x; k < O * I; k += kBconvThreads) {
+  if (wide) {
+    for (int k = threadIdx.x; k < O * P; k += kBconvThreads) {
+      const int j = k / P, i = k - j * P;
+      sfac[k] = i < I ? d.factors[(size_t)j * I + i] : (W)0;
+    }
+  }
+  for (int k = threadIdx.x; k < (wide ? 0 : O * I); k += kBconvThreads) {
     if (split) {
       reinterpret_cast<uint2*>(sfac)[k] = d.split_fac[(size_t)j_first * I + k];
       if (d.fp_in != 0) sfp[k] = d.fp_fac[(size_t)j_first * I + k];
@@ -363,6 +435,11 @@ __global__ void __launch_bounds__(kBconvThreads, 5)
   }
   const int coeff = blockIdx.x * kBconvThreads + threadIdx.x;
   if (coeff >= kN) return;  // partial last block (after the only barrier)
+  if (wide) {
+    bconv_wide32(reinterpret_cast<const BconvDesc<uint32_t>&>(d), reinterpret_cast<const PrimeConst<uint32_t>*>(pcs),
+                 reinterpret_cast<const uint32_t*>(sfac), reinterpret_cast<const BconvOut<uint32_t>*>(sout), coeff);
+    return;
+  }
   if (sizeof(W) == 8 && I <= kBconvRegInputs) {
     const BconvDesc<uint64_t>& d64 = reinterpret_cast<const BconvDesc<uint64_t>&>(d);
     const PrimeConst<uint64_t>* p64 = reinterpret_cast<const PrimeConst<uint64_t>*>(pcs);
@@ -429,13 +506,18 @@ __global__ void __launch_bounds__(kBconvThreads, 5)
   d.I = I;
   d.O = O;
   W* sfac = reinterpret_cast<W*>(smem_raw);
-  const size_t fac_bytes = ((size_t)O * I * sizeof(W) + 15) / 16 * 16;
+  const bool wide = bconv_is_wide32<W>(I);
+  const int P = wide ? (I + 3) / 4 * 4 : I;  // words per staged factor row
+  const size_t fac_bytes = ((size_t)O * P * sizeof(W) + 15) / 16 * 16;
   BconvOut<W>* sout = reinterpret_cast<BconvOut<W>*>(smem_raw + fac_bytes);
   const size_t out_bytes = ((size_t)O * sizeof(BconvOut<W>) + 15) / 16 * 16;
   W* scol = reinterpret_cast<W*>(smem_raw + fac_bytes + out_bytes);
   const W* fac = factors[j];
   const W* omod = out_moduli[j];
-  for (int k = threadIdx.x; k < O * I; k += kBconvThreads) sfac[k] = fac[k];
+  for (int k = threadIdx.x; k < O * P; k += kBconvThreads) {
+    const int jj = k / P, i = k - jj * P;
+    sfac[k] = i < I ? fac[(size_t)jj * I + i] : (W)0;
+  }
   for (int o = threadIdx.x; o < O; o += kBconvThreads) {
     const W q = omod[o];
     BconvOut<W> c{};
@@ -468,6 +550,11 @@ __global__ void __launch_bounds__(kBconvThreads, 5)
   __syncthreads();
   const int coeff = blockIdx.x * kBconvThreads + threadIdx.x;
   if (coeff >= kN) return;
+  if (wide) {
+    bconv_wide32(reinterpret_cast<const BconvDesc<uint32_t>&>(d), nullptr, reinterpret_cast<const uint32_t*>(sfac),
+                 reinterpret_cast<const BconvOut<uint32_t>*>(sout), coeff);
+    return;
+  }
   switch (I) {
     case 1: bconv_body<W, 1>(d, nullptr, sfac, sout, scol, coeff); break;
     case 2: bconv_body<W, 2>(d, nullptr, sfac, sout, scol, coeff); break;

@@ -197,12 +197,14 @@ def case_sud_ptrs(be, word_bits):
 def case_bconv_ptrs(be, word_bits):
     """Base conversion from device tables only (shapes, factor matrices and output primes), two
     conversions of different shape in one launch, one of them with more than eight inputs."""
-    n_mod = 14
+    n_mod = 36
     mods = moduli_for(word_bits, n_mod, 0)
     h = Harness(be, word_bits, mods)
     rng = np.random.default_rng(72)
     wdt = np.uint32 if word_bits == 32 else np.uint64
-    shapes = [([0, 1, 2], [3, 4, 5, 6, 7]), (list(range(9)), [9, 10, 11, 12, 13])]
+    # the last two take the 32-bit path for 9 to 32 inputs (13 inputs: padded rows; 17: two partial sums)
+    shapes = [([0, 1, 2], [3, 4, 5, 6, 7]), (list(range(9)), [9, 10, 11, 12, 13]),
+              (list(range(13)), list(range(13, 20))), (list(range(17)), list(range(17, 36)))]
     keep, outs, ins, facs, omods, wants, d_out = [], [], [], [], [], [], []
     for in_idx, out_idx in shapes:
         x = rand_limbs(rng, mods, in_idx)
@@ -223,7 +225,7 @@ def case_bconv_ptrs(be, word_bits):
     d_outs, d_ins, d_facs, d_omods = t(outs), t(ins), t(facs), t(omods)
     d_nin, d_nout = t([len(a) for a, _ in shapes]), t([len(b) for _, b in shapes])
     h.ctx.bconv_ptrs(be.ptr(d_outs), be.ptr(d_nout), be.ptr(d_ins), be.ptr(d_nin), be.ptr(d_facs), be.ptr(d_omods),
-                     9, 5, len(shapes))
+                     17, 19, len(shapes))
     for do, want in zip(d_out, wants):
         assert np.array_equal(h.down(do), want)
     # a table entry above the launch's shape bounds (9 inputs against max_in = 8) is skipped on the
@@ -240,7 +242,8 @@ def case_bconv_ptrs(be, word_bits):
     assert e.value.code == _capi.ERR_INVALID and "shape bounds" in e.value.message
     h.ctx.check()                                            # reading the status cleared it
     assert np.array_equal(h.down(d_out[0]), wants[0])
-    assert not h.down(d_out[1]).any(), "the over-bound conversion wrote its outputs"
+    for k in (1, 2, 3):
+        assert not h.down(d_out[k]).any(), "an over-bound conversion wrote its outputs"
 
 
 def case_ewise(be, word_bits):
@@ -320,6 +323,8 @@ def case_bconv(be, word_bits, n_in, n_out, mode):
     out_idx = list(range(n_in, n_in + n_out))
     x = rand_limbs(rng, mods, in_idx)
     x[0, :8] = mods[0] - 1
+    for i in in_idx:
+        x[i, 8:16] = mods[i] - 1                          # every residue at its maximum: the largest sums
     dx = h.up(x)
     out = h.new(n_out, N)
     bc = _capi.BaseConverter(h.ctx, in_idx, out_idx, mode)
@@ -370,6 +375,8 @@ def case_u32_widest_primes(be):
     try:
         assert min(moduli_for(32, 6)) > 0.99 * 2**30
         case_sud(be, 32)
+        case_bconv(be, 32, 15, 3, _capi.BCONV_LAZY)          # fifteen products just below 2^60 in one 64-bit sum:
+        case_bconv(be, 32, 15, 2, _capi.BCONV_EXACT)         # the most inputs the library takes at this width
         case_rescale(be, 32, 0)
         case_rescale(be, 32, 1, L=3, n_polys=1)
         case_double_rescale(be, 32)

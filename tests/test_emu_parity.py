@@ -40,7 +40,8 @@ def test_automorph(be, word_bits):
 @pytest.mark.parametrize("word_bits,n_in,n_out,mode", [
     (64, 1, 3, _capi.BCONV_LAZY), (64, 3, 5, _capi.BCONV_LAZY), (64, 3, 5, _capi.BCONV_EXACT),
     (64, 6, 2, _capi.BCONV_EXACT), (64, 10, 3, _capi.BCONV_LAZY),
-    (32, 5, 4, _capi.BCONV_LAZY), (32, 9, 3, _capi.BCONV_EXACT),
+    (32, 5, 4, _capi.BCONV_LAZY), (32, 9, 3, _capi.BCONV_EXACT), (32, 13, 5, _capi.BCONV_LAZY),
+    (32, 16, 3, _capi.BCONV_EXACT), (32, 17, 2, _capi.BCONV_LAZY), (32, 32, 2, _capi.BCONV_LAZY), (32, 33, 2, _capi.BCONV_LAZY),
 ])
 def test_bconv(be, word_bits, n_in, n_out, mode):
     pc.case_bconv(be, word_bits, n_in, n_out, mode)

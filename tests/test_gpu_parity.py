@@ -43,6 +43,8 @@ def test_automorph(be, word_bits):
     (64, 1, 3, _capi.BCONV_LAZY), (64, 5, 35, _capi.BCONV_LAZY), (64, 5, 35, _capi.BCONV_EXACT),
     (64, 8, 4, _capi.BCONV_EXACT), (64, 24, 6, _capi.BCONV_LAZY), (64, 48, 16, _capi.BCONV_EXACT),
     (32, 5, 30, _capi.BCONV_LAZY), (32, 18, 12, _capi.BCONV_LAZY), (32, 48, 16, _capi.BCONV_LAZY),
+    (32, 13, 51, _capi.BCONV_LAZY), (32, 16, 47, _capi.BCONV_EXACT), (32, 17, 34, _capi.BCONV_LAZY), (32, 28, 28, _capi.BCONV_LAZY),
+    (32, 32, 8, _capi.BCONV_LAZY), (32, 33, 8, _capi.BCONV_LAZY),
 ])
 def test_bconv(be, word_bits, n_in, n_out, mode):
     pc.case_bconv(be, word_bits, n_in, n_out, mode)
