@@ -89,6 +89,32 @@ def probe_int_pipe(device):
     return dict(zip(PROBE_NAMES, [float(v) for v in buf]))
 
 
+class Watchdog:
+    """Ends the process when the benchmark makes no progress for `limit_s` seconds (a collective whose peers never
+    arrive would otherwise wait until the caller's own limit): the stage it was in goes to stderr, exit code 3."""
+
+    def __init__(self, limit_s: float):
+        self.limit_s = limit_s
+        self.stage = "start"
+        self.t = time.monotonic()
+        self.done = False
+        if limit_s > 0:
+            threading.Thread(target=self._watch, daemon=True).start()
+
+    def at(self, stage: str):
+        self.stage = stage
+        self.t = time.monotonic()
+
+    def _watch(self):
+        while not self.done:
+            time.sleep(5)
+            if time.monotonic() - self.t > self.limit_s:
+                sys.stderr.write("bench.py: no progress for %d s in stage '%s' (rank %s); giving up\n"
+                                 % (self.limit_s, self.stage, os.environ.get("RANK", "0")))
+                sys.stderr.flush()
+                os._exit(3)
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
 
@@ -901,6 +927,11 @@ class BootstrapProgramWorkload(Workload):
 
     def step(self):
         self.program.run(self.torch.cuda.current_stream().cuda_stream)
+        self.queued = getattr(self, "queued", 0) + 1
+        if self.world > 1 and self.queued % 8 == 0:
+            # a run holds tens of exchange records on up to three communicators: the host stays at most eight
+            # runs ahead of the GPUs (a run takes milliseconds, the wait is not seen in the timing)
+            self.torch.cuda.current_stream().synchronize()
 
     def verify(self, orc_mod):
         import torch.distributed as dist
@@ -1134,6 +1165,14 @@ def main():
     args.steps = args.steps if args.steps is not None else (20 if args.workload == "bootstrap" else 50 if args.workload == "bootstrap_program" else 200 if slow else 2000)
     args.warmup = max(3, args.warmup if args.warmup is not None else (3 if slow else 50))
 
+    # a stage that stops making progress (a collective whose peers never arrive) ends the run instead of waiting for
+    # the caller's limit; CERIUM_BENCH_WATCHDOG_S=0 switches it off
+    dog = Watchdog(float(os.environ.get("CERIUM_BENCH_WATCHDOG_S", "600")))
+    if args.workload == "bootstrap_program" and env_int("WORLD_SIZE", 1) > 1:
+        # the configuration tests/test_runtime_facade.py runs the program's builds for 2 and 4 GPUs in: groups of
+        # neighbouring ranks get communicators of their own, and NVLink multicast stays out of it
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+
     import torch
     import torch.distributed as dist
     from cerium_b200 import _capi
@@ -1148,6 +1187,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     lib = _capi.load()
+    dog.at("setup")
     sharded = world > 1 and ((args.parallelism in ("auto", "limb") and args.workload == "hrot") or args.workload == "bootstrap_program")
     comm = None
     if sharded and args.workload == "bootstrap_program":
@@ -1179,6 +1219,7 @@ def main():
     # a path whose result is wrong
     verified = None
     oracle = None
+    dog.at("verify")
     if not args.no_verify:
         import oracle
         oracle.set_num_threads(max(1, len(os.sched_getaffinity(0)) // max(1, world)))
@@ -1190,6 +1231,7 @@ def main():
         if verified is False:
             raise SystemExit("bench.py: %s does not match the oracle on the benchmark inputs; nothing is timed" % wl.name)
 
+    dog.at("warm-up")
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -1203,18 +1245,21 @@ def main():
     profile_range = bool(os.environ.get("CERIUM_BENCH_PROFILE_RANGE"))
     if profile_range:
         torch.cuda.profiler.start()
+    dog.at("timed blocks")
     block_ms = time_blocks(torch, dist, world, wl, args.steps, max(1, args.blocks), barrier)
     if profile_range:
         torch.cuda.synchronize()
         torch.cuda.profiler.stop()
     ms = block_ms[0]
 
+    dog.at("roofline kernel and probe")
     peak, peak_kind = measured_peaks()
     roofline, rl_ms, rl_limbs = roofline_of(torch, wl, peak, peak_kind)
     clocks = sampler.stop() if rank == 0 else None
     probe = probe_int_pipe(local_rank) if rank == 0 else None
 
     # latency of ONE operation (nothing else in flight) beside the throughput of several
+    dog.at("side measurements")
     side = {}
     if getattr(wl, "inflight", 1) > 1 and args.workload == "hrot":
         keep = wl.inflight
@@ -1249,6 +1294,7 @@ def main():
         torch.cuda.empty_cache()
 
     # end to end: pinned host buffers in and out through the same C ABI calls, three streams
+    dog.at("end to end")
     e2e_steps = max(5, min(args.steps, 200))
     for _ in range(3):
         wl.e2e_step()
@@ -1280,6 +1326,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s, copy_s = float(t[0].item()), float(t[1].item())
 
+    dog.at("report")
     if rank == 0:
         latency = getattr(wl, "latency_metric", False)
         value = ms / args.steps if latency else job_ops * ops * args.steps / (ms / 1e3)
@@ -1335,10 +1382,12 @@ def main():
             line["cpu_baseline"] = {"value": v, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",
                                     "port_quality": PORT_QUALITY, "sample": sample}
         print(json.dumps(line), flush=True)
+    dog.at("shutdown")
     if comm is not None:
         comm.close()
     if world > 1:
         dist.destroy_process_group()
+    dog.done = True
 
 
 if __name__ == "__main__":

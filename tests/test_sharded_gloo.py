@@ -115,6 +115,7 @@ def _worker(rank, world, port, word_bits, L, K, dnum, bconv_mode, round_mode, ex
     (2, 64, 5, 3, 3, 1, 1, True),    # extension limbs split 1 / 2, exact conversion with rounding
     (3, 64, 4, 2, 2, 0, 0, True),    # a rank without extension limbs
     (3, 32, 6, 3, 3, 1, 0, True),    # world = dnum: every rank's limbs belong to one digit
+    (8, 64, 11, 5, 4, 1, 1, True),   # eight ranks as the benchmark runs them: 2,2,2,1,1,1,1,1 limbs, extension limbs on ranks 3..7 only
 ])
 def test_sharded_keyswitch_matches_single_device(world, word_bits, L, K, dnum, bm, rm, ext_split):
     sys.path.insert(0, os.path.join(ROOT, "tests", "emu"))
