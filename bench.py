@@ -968,7 +968,9 @@ class BootstrapProgramWorkload(Workload):
                 var, poly = desc.split(":")
                 ct = self.ct_in[var]
                 rows.append((ct.c0 if poly == "c0" else ct.c1)[ct.rns_base_ids.index(l)])
-            self.host_in = torch.from_numpy(np.stack(rows).view(np.int32).copy()).pin_memory()
+            # a partition of a build for many GPUs may hold none of the (two-limb) input ciphertext
+            stacked = np.stack(rows).view(np.int32).copy() if rows else np.zeros((0, N), dtype=np.int32)
+            self.host_in = torch.from_numpy(stacked).pin_memory()
         self.pipe.submit([self.host_in])
         return self.pipe.in_bytes, self.pipe.out_bytes
 
