@@ -73,6 +73,8 @@ def test_rescale(be, word_bits, round_mode):
     (64, 5, 2, 3, _capi.BCONV_EXACT, _capi.ROUND_HALF),   # ragged digits: sizes 2, 2, 1
     (32, 4, 2, 2, _capi.BCONV_LAZY, _capi.ROUND_FLOOR),
     (32, 3, 1, 3, _capi.BCONV_LAZY, _capi.ROUND_FLOOR),   # one-limb digits: raise without converters
+    (32, 12, 12, 1, _capi.BCONV_EXACT, _capi.ROUND_HALF), # the reference examples' shape: one digit of 12 limbs, 12 extension
+                                                          # limbs - conversions of 12 inputs (register path for 9 to 32 inputs)
 ])
 def test_keyswitch_hrot_hmult(be, word_bits, L, K, dnum, bm, rm):
     pc.case_keyswitch(be, word_bits, L, K, dnum, bm, rm)

@@ -79,6 +79,8 @@ def test_rescale(be, word_bits, round_mode):
     (32, 8, 4, 2, _capi.BCONV_LAZY, _capi.ROUND_FLOOR),
     (32, 6, 2, 3, _capi.BCONV_EXACT, _capi.ROUND_FLOOR),
     (32, 5, 1, 5, _capi.BCONV_LAZY, _capi.ROUND_FLOOR),    # one-limb digits, 32-bit
+    (32, 12, 12, 1, _capi.BCONV_EXACT, _capi.ROUND_HALF),  # the reference examples' shape: conversions of 12 inputs
+    (32, 24, 13, 2, _capi.BCONV_LAZY, _capi.ROUND_FLOOR),  # two digits of 12 limbs, 13 extension limbs
 ])
 def test_keyswitch_hrot_hmult(be, word_bits, L, K, dnum, bm, rm):
     pc.case_keyswitch(be, word_bits, L, K, dnum, bm, rm)
