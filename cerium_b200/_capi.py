@@ -354,6 +354,13 @@ class Comm:
         lib.check(lib.dll.cerium_comm_unique_id(buf, COMM_ID_BYTES))
         return buf.raw
 
+    def split(self, size: int) -> int:
+        """Handle of the communicator of the `size` consecutive ranks that hold this rank (owned by this one);
+        collective over all ranks.  Raises where the transport has no sub-groups."""
+        h = _vp()
+        self.lib.check(self.lib.dll.cerium_comm_split(self.h, size, C.byref(h)))
+        return int(h.value)
+
     def allgather_limbs(self, ctx: "Context", gathered: int, send: int, limbs_per_rank: int, stream: int = 0):
         self.lib.check(self.lib.dll.cerium_allgather_limbs(self.h, ctx.h, gathered, send, limbs_per_rank, stream))
 

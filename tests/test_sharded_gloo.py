@@ -137,6 +137,27 @@ def test_sharded_keyswitch_matches_single_device(world, word_bits, L, K, dnum, b
     assert all(ret.get(r) == 1 for r in range(world)), dict(ret)
 
 
+def test_comm_split_on_a_callers_transport():
+    """Groups of consecutive ranks exist for the NCCL transport only: a caller's transport gets its own
+    communicator back for the full size and a clear refusal for a smaller one."""
+    import pytest
+    from cerium_b200 import _capi
+    sys.path.insert(0, os.path.join(ROOT, "tests", "emu"))
+    import build_emu
+    lib = _capi.Library(build_emu.build())
+
+    class Nothing:
+        pass
+    comm = _capi.Comm(lib, 1, 4, transport=Nothing())
+    assert comm.split(4) == comm.h.value
+    with pytest.raises(_capi.CeriumError) as e:
+        comm.split(2)
+    assert e.value.code == _capi.ERR_UNSUPPORTED and "sub-groups" in e.value.message
+    with pytest.raises(_capi.CeriumError):
+        comm.split(3)                                   # does not divide the number of ranks
+    comm.close()
+
+
 def test_local_limb_indices():
     from cerium_b200 import sharded
     assert sharded.local_limb_indices(35, 0, 8) == [0, 8, 16, 24, 32]
