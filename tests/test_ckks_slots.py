@@ -101,6 +101,53 @@ def test_oracle_hmult_relin_rescale_decrypts_to_product():
     assert np.allclose(got, x * y, rtol=1e-5, atol=1e-4)
 
 
+def test_oracle_hmult_precision_at_the_benchmark_configuration():
+    """The HMult benchmark's own parameters: N = 2^16, 24 limbs (one 60-bit, 23 of 50 bits), one 60-bit special
+    prime, one digit per limb, slots uniform in [-1, 1] at scale 2^50, ternary secret of Hamming weight 192,
+    errors of standard deviation 3.2.  HMult + relinearise + rescale as two divisions and as the single division
+    by P * q_last; the precision of the decrypted product is printed in bits (GPU and oracle agree on every
+    limb at this shape: tests/test_gpu_bench_shapes.py)."""
+    prm = params.config_hmult(LOGN, 24)
+    ck = CkksRef(prm, seed=21, hamming_weight=192, sigma=3.2)
+    rng = np.random.default_rng(22)
+    x, y = rng.uniform(-1, 1, N // 2), rng.uniform(-1, 1, N // 2)
+    scale = 2.0 ** 50
+    a0, a1 = ck.encrypt(x, scale)
+    b0, b1 = ck.encrypt(y, scale)
+    evk = ck.relin_key()
+    q_last = prm.moduli[prm.q_idx[-1]]
+    o0, o1 = ck.octx.hmult_relin(oracle.BCONV_EXACT, oracle.ROUND_HALF, True, prm.q_idx, prm.p_idx, prm.dnum,
+                                 a0, a1, b0, b1, evk)
+    two = ck.decrypt(o0, o1, scale * scale / q_last).real
+    f0, f1 = ck.octx.hmult_relin_fused(oracle.BCONV_EXACT, oracle.ROUND_HALF, prm.q_idx, prm.p_idx, prm.dnum,
+                                       a0, a1, b0, b1, evk)
+    one = ck.decrypt(f0, f1, scale * scale / q_last).real
+    bits_two = -np.log2(np.max(np.abs(two - x * y)))
+    bits_one = -np.log2(np.max(np.abs(one - x * y)))
+    print("HMult at L=24, dnum=24, scale 2^50: %.1f bits with two divisions, %.1f bits with one" % (bits_two, bits_one))
+    assert bits_two > 20 and bits_one > 20
+    assert np.max(np.abs(one - two)) < 2.0 ** -30                    # the two roundings differ in the last bits only
+
+
+def test_oracle_hrot_precision_at_the_benchmark_configuration():
+    """The HRot benchmark's own parameters (N = 2^16, L = 35 of 50 bits, K = 5 of 60 bits, dnum = 7) with a real key
+    and message: rotation by the benchmark's seeded step, precision of the decrypted slots in bits."""
+    prm = params.config_hrot(LOGN, 35, 5, 7)
+    ck = CkksRef(prm, seed=23, hamming_weight=192, sigma=3.2)
+    rng = np.random.default_rng(24)
+    z = rng.uniform(-1, 1, N // 2)
+    scale = 2.0 ** 50
+    c0, c1 = ck.encrypt(z, scale)
+    step = int(np.random.default_rng(0xCE210003).integers(1, 1 << 15))
+    elt = oracle.galois_elt_from_step(step, LOGN)
+    evk = ck.rotation_key(elt)
+    o0, o1 = ck.octx.hrot(oracle.BCONV_EXACT, oracle.ROUND_HALF, prm.q_idx, prm.p_idx, prm.dnum, elt, c0, c1, evk)
+    got = ck.decrypt(o0, o1, scale).real
+    bits = -np.log2(np.max(np.abs(got - np.roll(z, -step))))
+    print("HRot at L=35, K=5, dnum=7, scale 2^50: %.1f bits" % bits)
+    assert bits > 25
+
+
 @pytest.mark.gpu
 def test_gpu_rotation_and_product_decrypt_correctly():
     import torch
