@@ -167,6 +167,10 @@ def main():
         print("made", tag, functions)
     for gpus in (1, 2, 4, 8):
         make_bootstrap(ref, pkg, kern, gpus)
+    # the working copies of the reference's example and benchmark directories (the compiler writes beside the
+    # program it compiles) and what it generated there are scratch: only the files copied out above are kept
+    for scratch in ("run", "run_bootstrap"):
+        shutil.rmtree(os.path.join(OUT_REF, "refcompiler", scratch), ignore_errors=True)
 
 
 if __name__ == "__main__":
