@@ -545,3 +545,24 @@ def test_bootstrap_benchmark_program_multi_gpu(tmp_path, world):
     print("bootstrap program, %d GPUs: %d steps on partition 0, setup %.1f s, %.2f ms per run (max over ranks), "
           "precision bits %.2f" % (world, steps, setup, ms, bits))
     assert all(ret[r][1] > 15 for r in range(world)), dict(ret)
+
+
+def test_importable_under_the_references_module_name():
+    """A driver that says `import cerium.runtime as runtime` finds the same classes with cerium_b200/as_cerium on
+    its path."""
+    import importlib
+    import sys
+    path = os.path.join(ROOT, "cerium_b200", "as_cerium")
+    saved = {k: sys.modules.pop(k) for k in list(sys.modules) if k == "cerium" or k.startswith("cerium.")}
+    sys.path.insert(0, path)
+    try:
+        mod = importlib.import_module("cerium.runtime")
+        for name in ("Context", "Ciphertext", "CKKSEncryptor", "CKKSEncryptorContext", "IOGenerator",
+                     "CeriumFunctionExecutor", "RawInputsWrapper", "FusedKernelProgram"):     # wrapper.cpp:62-235
+            assert getattr(mod, name) is getattr(runtime, name)
+        assert callable(mod.FusedKernelProgram.make_program) and callable(mod.FusedKernelProgram.run)
+    finally:
+        sys.path.remove(path)
+        for k in [k for k in sys.modules if k == "cerium" or k.startswith("cerium.")]:
+            del sys.modules[k]
+        sys.modules.update(saved)
