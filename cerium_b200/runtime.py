@@ -552,6 +552,17 @@ class CeriumFunctionExecutor:
                     rows = np.pad(rows, ((0, 0), (0, self.context.n - rows.shape[1])))
                 self._put(term, bases, rows, bases)
 
+    # wrapper.cpp:196-200: inputs that a caller re-maps between calls of one function (the weights of a layer).
+    # The executor refuses functions that read them, so these only say so.
+    def generate_remapable_inputs(self, remapables_file_name, plaintexts_file_name, map_key, remapables_use_uvm=False):
+        raise NotImplementedError("re-mappable inputs are not served by the executor")
+
+    def copy_remapable_inputs_to_device(self, *args):
+        raise NotImplementedError("re-mappable inputs are not served by the executor")
+
+    def create_remapable_offsets(self, *args):
+        raise NotImplementedError("re-mappable inputs are not served by the executor")
+
     def copy_inputs_to_device(self):
         """Inputs are written straight into device memory by generate_inputs; nothing is staged."""
 
