@@ -1254,6 +1254,7 @@ def main():
         torch.cuda.profiler.stop()
     ms = block_ms[0]
 
+    clocks = sampler.stop() if rank == 0 else None     # the clock record covers the timed blocks only
     dog.at("roofline kernel and probe")
     peak, peak_kind = measured_peaks()
     # the roofline kernel is timed alone against the burst copy rate: give the GPU a moment off the timed loop's
@@ -1261,7 +1262,6 @@ def main():
     torch.cuda.synchronize()
     time.sleep(1.5)
     roofline, rl_ms, rl_limbs = roofline_of(torch, wl, peak, peak_kind)
-    clocks = sampler.stop() if rank == 0 else None
     probe = probe_int_pipe(local_rank) if rank == 0 else None
 
     # latency of ONE operation (nothing else in flight) beside the throughput of several
